@@ -1,0 +1,99 @@
+// Shared declarations of the kernel library: dtype codes, error reporting, loads
+// and stores that go through fp32, and block reductions.
+//
+// Every entry point is `extern "C" int pl_<name>(..., cudaStream_t stream)`, takes
+// raw device pointers, launches on `stream`, never synchronises and never
+// allocates. It returns 0, or a non-zero code after storing a message that
+// `pl_last_error()` returns (sizes it refuses, a failed launch).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+
+#define PL_API extern "C" __attribute__((visibility("default")))
+
+enum pl_dtype : int { PL_F32 = 0, PL_BF16 = 1 };
+
+// Stores a printf-style message for pl_last_error() and returns `code`.
+int pl_fail(int code, const char* format, ...);
+
+#define PL_REQUIRE(cond, ...)                     \
+    do {                                          \
+        if (!(cond)) {                            \
+            return pl_fail(2, __VA_ARGS__);       \
+        }                                         \
+    } while (0)
+
+#define PL_CHECK_LAUNCH(name)                                                         \
+    do {                                                                              \
+        cudaError_t pl_err_ = cudaGetLastError();                                     \
+        if (pl_err_ != cudaSuccess) {                                                 \
+            return pl_fail(3, "%s: launch failed: %s", name, cudaGetErrorString(pl_err_)); \
+        }                                                                             \
+    } while (0)
+
+// Dispatch on a dtype code: binds `scalar_t` to float or __nv_bfloat16.
+#define PL_DISPATCH_DTYPE(code, name, ...)                                  \
+    do {                                                                    \
+        if ((code) == PL_F32) {                                             \
+            using scalar_t = float;                                         \
+            __VA_ARGS__                                                     \
+        } else if ((code) == PL_BF16) {                                     \
+            using scalar_t = __nv_bfloat16;                                 \
+            __VA_ARGS__                                                     \
+        } else {                                                            \
+            return pl_fail(2, "%s: unknown dtype code %d", name, (code));   \
+        }                                                                   \
+    } while (0)
+
+__device__ __forceinline__ float pl_load(const float* p) { return *p; }
+__device__ __forceinline__ float pl_load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void pl_store(float* p, float v) { *p = v; }
+__device__ __forceinline__ void pl_store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float pl_warp_sum(float v) {
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        v += __shfl_xor_sync(0xffffffffu, v, offset);
+    }
+    return v;
+}
+
+__device__ __forceinline__ float pl_warp_max(float v) {
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, offset));
+    }
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; `scratch` holds 32 floats. Every thread
+// gets the result. The order of additions is fixed by the block size alone.
+__device__ __forceinline__ float pl_block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = pl_warp_sum(v);
+    __syncthreads();
+    if (lane == 0) {
+        scratch[warp] = v;
+    }
+    __syncthreads();
+    const int warps = (blockDim.x + 31) >> 5;
+    float total = lane < warps ? scratch[lane] : 0.0f;
+    return pl_warp_sum(total);
+}
+
+__device__ __forceinline__ float pl_block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = pl_warp_max(v);
+    __syncthreads();
+    if (lane == 0) {
+        scratch[warp] = v;
+    }
+    __syncthreads();
+    const int warps = (blockDim.x + 31) >> 5;
+    float total = lane < warps ? scratch[lane] : -INFINITY;
+    return pl_warp_max(total);
+}

@@ -1,0 +1,174 @@
+// Embedding gather, fused residual-add + RMSNorm, and SwiGLU.
+//
+// The residual stream is fp32 in both engine dtypes: sums of layer outputs are
+// never rounded to bfloat16. Norm statistics, the SiLU and the products are fp32
+// with one rounding on store.
+#include "common.cuh"
+
+#include <algorithm>
+
+namespace {
+
+// x[t, :] = table[tokens[t], :] as fp32. An id outside [0, vocab) writes zeros and
+// raises bit 0 of *status (the host validates ids first; this only keeps a bad id
+// from reading outside the table).
+template <typename scalar_t>
+__global__ void embed_kernel(const scalar_t* __restrict__ table, const int32_t* __restrict__ tokens,
+                             float* __restrict__ x, int hidden, int vocab, int32_t* status) {
+    const int t = blockIdx.x;
+    const int token = tokens[t];
+    float* row = x + static_cast<int64_t>(t) * hidden;
+    if (token < 0 || token >= vocab) {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            row[i] = 0.0f;
+        }
+        if (threadIdx.x == 0 && status != nullptr) {
+            atomicOr(status, 1);
+        }
+        return;
+    }
+    const scalar_t* src = table + static_cast<int64_t>(token) * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        row[i] = pl_load(src + i);
+    }
+}
+
+// One block per output row r; source row s = rows ? rows[r] : r.
+//   v = x[s] + delta[s]   (delta optional)
+//   x[s] = v              (only when rows == nullptr)
+//   out[r] = v * rsqrt(mean(v^2) + eps) * weight
+// The block size depends on `hidden` alone, so a row's sum of squares is added in
+// the same order whatever else is in the batch.
+template <typename scalar_t, typename weight_t>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const scalar_t* __restrict__ delta,
+                                   const weight_t* __restrict__ weight, scalar_t* __restrict__ out,
+                                   const int32_t* __restrict__ rows, int hidden, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int64_t s = rows != nullptr ? rows[r] : r;
+    float* xr = x + s * hidden;
+    const scalar_t* dr = delta != nullptr ? delta + s * hidden : nullptr;
+    scalar_t* outr = out + static_cast<int64_t>(r) * hidden;
+    const bool write_back = rows == nullptr && dr != nullptr;
+
+    float local = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = xr[i];
+        if (dr != nullptr) {
+            v += pl_load(dr + i);
+        }
+        if (write_back) {
+            xr[i] = v;
+        }
+        local += v * v;
+    }
+    const float total = pl_block_sum(local, scratch);
+    const float inv_rms = rsqrtf(total / static_cast<float>(hidden) + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = xr[i];
+        if (dr != nullptr && !write_back) {
+            v += pl_load(dr + i);
+        }
+        pl_store(outr + i, v * inv_rms * pl_load(weight + i));
+    }
+}
+
+// out[t, i] = silu(in[t, i]) * in[t, width + i], silu(z) = z / (1 + exp(-z)).
+template <typename scalar_t>
+__global__ void swiglu_kernel(const scalar_t* __restrict__ in, scalar_t* __restrict__ out, int64_t tokens,
+                              int width) {
+    const int64_t total = tokens * width;
+    for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t t = idx / width;
+        const int i = static_cast<int>(idx - t * width);
+        const float g = pl_load(in + t * 2 * width + i);
+        const float u = pl_load(in + t * 2 * width + width + i);
+        pl_store(out + idx, g / (1.0f + expf(-g)) * u);
+    }
+}
+
+// dst[i] = float(src[i]).
+__global__ void bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, int64_t n) {
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        dst[i] = __bfloat162float(src[i]);
+    }
+}
+
+int norm_threads(int hidden) {
+    int threads = 32;
+    while (threads < 1024 && threads * 4 < hidden) {
+        threads *= 2;
+    }
+    return threads;
+}
+
+}  // namespace
+
+PL_API int pl_embed(const void* table, const int32_t* tokens, float* x, int n_tokens, int hidden, int vocab,
+                    int dtype, int32_t* status, cudaStream_t stream) {
+    PL_REQUIRE(n_tokens >= 0 && hidden > 0 && vocab > 0, "embed: bad sizes tokens=%d hidden=%d vocab=%d", n_tokens,
+               hidden, vocab);
+    if (n_tokens == 0) {
+        return 0;
+    }
+    const int threads = hidden >= 1024 ? 256 : 128;
+    PL_DISPATCH_DTYPE(dtype, "embed", {
+        embed_kernel<scalar_t><<<n_tokens, threads, 0, stream>>>(static_cast<const scalar_t*>(table), tokens, x,
+                                                                  hidden, vocab, status);
+    });
+    PL_CHECK_LAUNCH("embed");
+    return 0;
+}
+
+PL_API int pl_add_rmsnorm(float* x, const void* delta, const void* weight, int weight_dtype, void* out,
+                          const int32_t* rows, int n_rows, int hidden, float eps, int dtype, cudaStream_t stream) {
+    PL_REQUIRE(n_rows >= 0 && hidden > 0, "add_rmsnorm: bad sizes rows=%d hidden=%d", n_rows, hidden);
+    PL_REQUIRE(weight_dtype == PL_F32 || weight_dtype == dtype,
+               "add_rmsnorm: weight dtype %d must be fp32 or the engine dtype %d", weight_dtype, dtype);
+    if (n_rows == 0) {
+        return 0;
+    }
+    const int threads = norm_threads(hidden);
+    PL_DISPATCH_DTYPE(dtype, "add_rmsnorm", {
+        if (weight_dtype == PL_F32) {
+            add_rmsnorm_kernel<scalar_t, float><<<n_rows, threads, 0, stream>>>(
+                x, static_cast<const scalar_t*>(delta), static_cast<const float*>(weight),
+                static_cast<scalar_t*>(out), rows, hidden, eps);
+        } else {
+            add_rmsnorm_kernel<scalar_t, scalar_t><<<n_rows, threads, 0, stream>>>(
+                x, static_cast<const scalar_t*>(delta), static_cast<const scalar_t*>(weight),
+                static_cast<scalar_t*>(out), rows, hidden, eps);
+        }
+    });
+    PL_CHECK_LAUNCH("add_rmsnorm");
+    return 0;
+}
+
+PL_API int pl_swiglu(const void* in, void* out, int n_tokens, int width, int dtype, cudaStream_t stream) {
+    PL_REQUIRE(n_tokens >= 0 && width > 0, "swiglu: bad sizes tokens=%d width=%d", n_tokens, width);
+    if (n_tokens == 0) {
+        return 0;
+    }
+    const int64_t total = static_cast<int64_t>(n_tokens) * width;
+    const int threads = 256;
+    const int blocks = static_cast<int>(std::min<int64_t>((total + threads - 1) / threads, 148 * 16));
+    PL_DISPATCH_DTYPE(dtype, "swiglu", {
+        swiglu_kernel<scalar_t><<<blocks, threads, 0, stream>>>(static_cast<const scalar_t*>(in),
+                                                                 static_cast<scalar_t*>(out), n_tokens, width);
+    });
+    PL_CHECK_LAUNCH("swiglu");
+    return 0;
+}
+
+PL_API int pl_bf16_to_f32(const void* src, float* dst, int64_t n, cudaStream_t stream) {
+    if (n <= 0) {
+        return 0;
+    }
+    const int threads = 256;
+    const int blocks = static_cast<int>(std::min<int64_t>((n + threads - 1) / threads, 148 * 16));
+    bf16_to_f32_kernel<<<blocks, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), dst, n);
+    PL_CHECK_LAUNCH("bf16_to_f32");
+    return 0;
+}

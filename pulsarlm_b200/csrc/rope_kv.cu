@@ -1,0 +1,121 @@
+// Rotary position encoding of q and k, and the write of k and v into cache pages.
+//
+// One launch per layer: q is rotated in place; k is rotated and stored, with v, at
+// the token's place in the paged cache (keys are stored rotated: positions are
+// absolute and never change). The angle pos * f_j is formed in fp64 from an fp64
+// table, reduced to (-pi, pi] in fp64, and only then rounded to fp32 for sincosf;
+// the rotation itself is fp32. The reference rotates q in
+// pulsarlm-core/src/kernels/rope.cu:33-84 and writes k, v in
+// src/kernels/paged_attention.cu:52-98.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ void rope_sincos(int pos, double radians_per_position, float& c, float& s) {
+    const double kInvTwoPi = 0.15915494309189533576888376337251436;
+    const double kTwoPi = 6.28318530717958647692528676655900577;
+    const double turns = static_cast<double>(pos) * radians_per_position * kInvTwoPi;
+    const double frac = turns - rint(turns);
+    sincosf(static_cast<float>(frac * kTwoPi), &s, &c);
+}
+
+// Block t handles token t. Rotated pairs are (j, j + rotary/2) for j < rotary/2;
+// dims >= rotary pass through unchanged.
+template <typename scalar_t>
+__global__ void rope_kv_write_kernel(scalar_t* __restrict__ q, const scalar_t* __restrict__ k,
+                                     const scalar_t* __restrict__ v, int64_t row_stride,
+                                     const int32_t* __restrict__ pos, const int32_t* __restrict__ entry,
+                                     const int32_t* __restrict__ table, int table_width,
+                                     scalar_t* __restrict__ k_pool, scalar_t* __restrict__ v_pool,
+                                     int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
+                                     const double* __restrict__ inv_freq, int rotary, int n_heads, int n_kv_heads,
+                                     int head_dim, int32_t* status) {
+    extern __shared__ float sincos[];  // [rotary/2] cos then [rotary/2] sin
+    const int t = blockIdx.x;
+    const int p = pos[t];
+    const int half = rotary / 2;
+    float* cs = sincos;
+    float* sn = sincos + half;
+    if (inv_freq != nullptr) {
+        for (int j = threadIdx.x; j < half; j += blockDim.x) {
+            rope_sincos(p, inv_freq[j], cs[j], sn[j]);
+        }
+    }
+    __syncthreads();
+
+    scalar_t* qrow = q + t * row_stride;
+    if (inv_freq != nullptr) {
+        for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
+            const int h = idx / half, j = idx - h * half;
+            scalar_t* x = qrow + h * head_dim;
+            const float lo = pl_load(x + j), hi = pl_load(x + j + half);
+            pl_store(x + j, lo * cs[j] - hi * sn[j]);
+            pl_store(x + j + half, hi * cs[j] + lo * sn[j]);
+        }
+    }
+    if (k_pool == nullptr) {
+        return;
+    }
+
+    const int page = table[static_cast<int64_t>(entry[t]) * table_width + p / page_size];
+    if (page < 0 || page >= n_pages) {
+        if (threadIdx.x == 0 && status != nullptr) {
+            atomicOr(status, 2);
+        }
+        return;
+    }
+    const int slot = p % page_size;
+    const scalar_t* krow = k + t * row_stride;
+    const scalar_t* vrow = v + t * row_stride;
+    scalar_t* kdst = k_pool + page * page_stride + static_cast<int64_t>(slot) * head_dim;
+    scalar_t* vdst = v_pool + page * page_stride + static_cast<int64_t>(slot) * head_dim;
+    for (int idx = threadIdx.x; idx < n_kv_heads * head_dim; idx += blockDim.x) {
+        const int h = idx / head_dim, d = idx - h * head_dim;
+        const scalar_t* x = krow + h * head_dim;
+        float value;
+        if (inv_freq != nullptr && d < rotary) {
+            if (d < half) {
+                value = pl_load(x + d) * cs[d] - pl_load(x + d + half) * sn[d];
+            } else {
+                value = pl_load(x + d) * cs[d - half] + pl_load(x + d - half) * sn[d - half];
+            }
+        } else {
+            value = pl_load(x + d);
+        }
+        pl_store(kdst + h * head_stride + d, value);
+        vdst[h * head_stride + d] = vrow[idx];
+    }
+}
+
+}  // namespace
+
+// q [T, n_heads, head_dim], k and v [T, n_kv_heads, head_dim], all with `row_stride`
+// elements between tokens (they may be slices of one fused projection output).
+// Pools: element (page, head, slot, d) of K at k_pool[page * page_stride + head *
+// head_stride + slot * head_dim + d], V likewise. inv_freq == nullptr: no rotation.
+// k_pool == nullptr: only q is rotated (a layer that reads another layer's cache).
+PL_API int pl_rope_kv_write(void* q, const void* k, const void* v, int64_t row_stride, const int32_t* pos,
+                            const int32_t* entry, const int32_t* table, int table_width, void* k_pool,
+                            void* v_pool, int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
+                            const double* inv_freq, int rotary, int n_tokens, int n_heads, int n_kv_heads,
+                            int head_dim, int dtype, int32_t* status, cudaStream_t stream) {
+    PL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && head_dim > 0 && page_size > 0,
+               "rope_kv_write: bad sizes tokens=%d heads=%d kv_heads=%d head_dim=%d page=%d", n_tokens, n_heads,
+               n_kv_heads, head_dim, page_size);
+    PL_REQUIRE(rotary >= 0 && rotary <= head_dim && rotary % 2 == 0,
+               "rope_kv_write: rotary width %d must be even and at most head_dim %d", rotary, head_dim);
+    if (n_tokens == 0) {
+        return 0;
+    }
+    const int threads = 128;
+    const size_t smem = static_cast<size_t>(rotary) * sizeof(float);
+    PL_REQUIRE(smem <= 48 * 1024, "rope_kv_write: rotary width %d is too large", rotary);
+    PL_DISPATCH_DTYPE(dtype, "rope_kv_write", {
+        rope_kv_write_kernel<scalar_t><<<n_tokens, threads, smem, stream>>>(
+            static_cast<scalar_t*>(q), static_cast<const scalar_t*>(k), static_cast<const scalar_t*>(v), row_stride,
+            pos, entry, table, table_width, static_cast<scalar_t*>(k_pool), static_cast<scalar_t*>(v_pool),
+            page_stride, head_stride, page_size, n_pages, inv_freq, rotary, n_heads, n_kv_heads, head_dim, status);
+    });
+    PL_CHECK_LAUNCH("rope_kv_write");
+    return 0;
+}

@@ -1,0 +1,171 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A step runs only the tokens it is given, as one batch, against the cache that
+earlier steps left: portions of prompts beside single decoded tokens, cut
+anywhere. It reserves the pages the tokens need, uploads the batch's index
+arrays in one copy, runs the model once over all tokens, and returns fp32
+logits at the wanted places. The reference builds two groups per step and runs
+the model over each (pulsarlm-core/src/engine/executor.cpp:187-268,
+src/engine/model/paged_forward.cpp:136-145); here prompt portions and decode
+tokens share one pass.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..kernels import ops
+from ..models.model import Model, StepBatch
+
+
+class OutOfPages(RuntimeError):
+    """The cache has too few free pages (or slots) for a step's entry."""
+
+    def __init__(self, request, message: str):
+        super().__init__(message)
+        self.request = request
+
+
+@dataclasses.dataclass
+class StepEntry:
+    """`tokens`: the request's next tokens (at least one). `want`: indices into
+    `tokens` whose logits the step returns, in this order."""
+
+    request: object
+    tokens: list[int]
+    want: list[int] = dataclasses.field(default_factory=list)
+
+
+STATUS_MESSAGES = {
+    1: "a token id outside the vocabulary reached the embedding kernel",
+    2: "a token's block-table entry was not a page of the pool when its key was written",
+    4: "a block-table entry was not a page of the pool when attention read it",
+}
+
+
+class ModelRunner:
+    def __init__(self, model: Model, cache: CacheManager):
+        ops.require_device()
+        self.model = model
+        self.cache = cache
+        self.device = model.ctx.device
+        self.vocab = model.spec.vocab_size
+        model.bind_caches(cache.bindings())
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._staging: torch.Tensor | None = None
+        self.steps = 0
+        self.tokens_run = 0
+
+    # ------------------------------------------------------------------ helpers
+    def _stage(self, arrays: list[np.ndarray]) -> list[torch.Tensor]:
+        """Copies int32 arrays to the device through one pinned buffer and one copy;
+        returns device views in the same order."""
+        sizes = [a.size for a in arrays]
+        # Views start on 16-byte boundaries (4 int32), which vector loads may rely on.
+        starts, total = [], 0
+        for s in sizes:
+            starts.append(total)
+            total += -(-s // 4) * 4
+        total = max(total, 4)
+        if self._staging is None or self._staging.numel() < total:
+            self._staging = torch.empty(max(total, 4096), dtype=torch.int32, pin_memory=True)
+        host = self._staging[:total]
+        flat = host.numpy()
+        for a, start in zip(arrays, starts):
+            flat[start : start + a.size] = a.reshape(-1)
+        dev = torch.empty(total, dtype=torch.int32, device=self.device)
+        dev.copy_(host, non_blocking=True)
+        # The pinned buffer is reused by the next step: the copy must have left it.
+        self._copy_done = torch.cuda.Event()
+        self._copy_done.record()
+        return [dev[start : start + a.size].view(a.shape) for a, start in zip(arrays, starts)]
+
+    def prepare(self, entries: list[StepEntry]) -> tuple[StepBatch, list[int]]:
+        """Reserves pages and builds the device batch; returns it with each entry's
+        new length (to commit after the forward)."""
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        seen = set()
+        for e in entries:
+            if e.request in seen:
+                raise ValueError(f"request {e.request!r} appears twice in one step")
+            seen.add(e.request)
+            if len(e.tokens) == 0:
+                raise ValueError(f"request {e.request!r}: a step entry needs at least one token")
+            bad = [t for t in e.tokens if not 0 <= int(t) < self.vocab]
+            if bad:
+                raise ValueError(f"request {e.request!r}: token id {bad[0]} is outside [0, {self.vocab})")
+            if any(not 0 <= w < len(e.tokens) for w in e.want):
+                raise ValueError(f"request {e.request!r}: wanted places {e.want} are outside its {len(e.tokens)} tokens")
+        new_lens = []
+        for e in entries:
+            if not self.cache.is_open(e.request):
+                if self.cache.open(e.request) is None:
+                    raise OutOfPages(e.request, f"no free slot for request {e.request!r}")
+            new_len = self.cache.length(e.request) + len(e.tokens)
+            if not self.cache.reserve(e.request, new_len):
+                raise OutOfPages(e.request, f"too few free pages for request {e.request!r} to reach {new_len} tokens")
+            new_lens.append(new_len)
+
+        if getattr(self, "_copy_done", None) is not None:
+            self._copy_done.synchronize()
+        n_tokens = sum(len(e.tokens) for e in entries)
+        tokens = np.empty(n_tokens, dtype=np.int32)
+        pos = np.empty(n_tokens, dtype=np.int32)
+        entry = np.empty(n_tokens, dtype=np.int32)
+        want_rows: list[int] = []
+        at = 0
+        for i, e in enumerate(entries):
+            n = len(e.tokens)
+            start = self.cache.length(e.request)
+            tokens[at : at + n] = e.tokens
+            pos[at : at + n] = np.arange(start, start + n, dtype=np.int32)
+            entry[at : at + n] = i
+            want_rows.extend(at + w for w in e.want)
+            at += n
+        requests = [e.request for e in entries]
+        slots = np.array([self.cache.slot(r) for r in requests], dtype=np.int32)
+        tables = [self.cache.table_rows(g.index, requests) for g in self.cache.groups]
+        arrays = [tokens, pos, entry, slots, np.array(want_rows, dtype=np.int32), *tables]
+        dev = self._stage(arrays)
+        batch = StepBatch(
+            tokens=dev[0], pos=dev[1], entry=dev[2],
+            tables={g.index: dev[5 + i] for i, g in enumerate(self.cache.groups)},
+            slots=dev[3],
+            want_rows=dev[4] if want_rows else None,
+            status=self.status,
+            n_tokens=n_tokens,
+            n_entries=len(entries),
+            host_query_lens=[len(e.tokens) for e in entries],
+            host_context_lens=list(new_lens),
+        )
+        return batch, new_lens
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """Runs the entries' tokens; returns fp32 logits [wanted, vocab] on the device
+        in the order of the entries and of each entry's `want`, or None."""
+        batch, new_lens = self.prepare(entries)
+        logits = self.model.forward(batch)
+        for e, new_len in zip(entries, new_lens):
+            self.cache.commit(e.request, new_len)
+        self.steps += 1
+        self.tokens_run += batch.n_tokens
+        return logits
+
+    def end(self, request) -> None:
+        """Gives back what the request holds."""
+        if self.cache.is_open(request):
+            self.cache.close(request)
+
+    def check_status(self) -> None:
+        """Raises if a kernel flagged an error since the last check (synchronises)."""
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            reasons = [m for bit, m in STATUS_MESSAGES.items() if code & bit]
+            raise RuntimeError("kernel status %d: %s" % (code, "; ".join(reasons) or "unknown"))

@@ -1,0 +1,241 @@
+"""Python face of the CUDA kernel library: one function per entry point.
+
+The library is loaded with ctypes on first use (and built first if stale). There
+is no fallback: if it cannot be built or loaded, or the device is not sm_100,
+the call raises. Every function launches on torch's current CUDA stream and
+takes torch tensors on the device; shapes and dtypes are checked here, sizes a
+kernel refuses come back as KernelError with the kernel's message.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+
+import torch
+
+from . import build
+
+_I32 = ctypes.c_int
+_I64 = ctypes.c_int64
+_F32 = ctypes.c_float
+_PTR = ctypes.c_void_p
+
+_lib = None
+_lock = threading.Lock()
+
+ABI_VERSION = 7
+
+DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or failed to launch."""
+
+
+_SIGNATURES = {
+    "pl_embed": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _PTR, _PTR],
+    "pl_add_rmsnorm": [_PTR, _PTR, _PTR, _I32, _PTR, _PTR, _I32, _I32, _F32, _I32, _PTR],
+    "pl_swiglu": [_PTR, _PTR, _I32, _I32, _I32, _PTR],
+    "pl_bf16_to_f32": [_PTR, _PTR, _I64, _PTR],
+    "pl_gemm_f32": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _PTR],
+    "pl_rope_kv_write": [_PTR, _PTR, _PTR, _I64, _PTR, _PTR, _PTR, _I32, _PTR, _PTR, _I64, _I64, _I32, _I32,
+                         _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _PTR, _PTR],
+    "pl_attention_simt": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
+                          _I32, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR],
+    "pl_sample": [_PTR, _I64, _I32, _I32, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR],
+}
+
+
+def library() -> ctypes.CDLL:
+    """The loaded kernel library; builds it on first use."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        path = build.library_path(build=True)
+        lib = ctypes.CDLL(path)
+        lib.pl_last_error.restype = ctypes.c_char_p
+        lib.pl_abi_version.restype = _I32
+        if lib.pl_abi_version() != ABI_VERSION:
+            raise KernelError(f"{path}: ABI version {lib.pl_abi_version()} does not match the package's "
+                              f"{ABI_VERSION}; delete the build folder and try again")
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = _I32
+        lib.pl_device_arch.restype = _I32
+        _lib = lib
+    return _lib
+
+
+_device_checked = False
+
+
+def require_device() -> None:
+    """Raises unless a CUDA device of compute capability 10.x is current."""
+    global _device_checked
+    if _device_checked:
+        return
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device: the engine runs on a B200 (sm_100) only and has no CPU path")
+    torch.cuda.init()
+    arch = library().pl_device_arch()
+    if arch // 10 != 10:
+        raise KernelError(f"the kernels are built for sm_100a; the current device is sm_{arch}")
+    _device_checked = True
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _call(name: str, *args) -> None:
+    code = getattr(library(), name)(*args)
+    if code != 0:
+        raise KernelError(library().pl_last_error().decode("utf-8", "replace"))
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"unsupported dtype {dtype}; the kernels take float32 and bfloat16") from None
+
+
+def _dev(*tensors: torch.Tensor | None) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernel arguments must be CUDA tensors")
+
+
+# ----------------------------------------------------------------------------- ops
+
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, status: torch.Tensor | None = None) -> None:
+    """out[t] (fp32 [T, H]) = table[tokens[t]]; tokens int32 [T]."""
+    _dev(table, tokens, out, status)
+    assert table.is_contiguous() and out.is_contiguous() and out.dtype == torch.float32
+    assert tokens.dtype == torch.int32 and tokens.is_contiguous()
+    vocab, hidden = table.shape
+    _call("pl_embed", _p(table), _p(tokens), _p(out), tokens.numel(), hidden, vocab, _code(table.dtype),
+          _p(status), _stream())
+
+
+def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                rows: torch.Tensor | None = None) -> None:
+    """x fp32 [T, H] residual stream; x += delta (when rows is None); out = norm(x + delta) * weight.
+    With rows (int32 [R]), output row r is made from source row rows[r] and x is left as it was."""
+    _dev(x, delta, weight, out, rows)
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+    hidden = x.shape[-1]
+    n_rows = rows.numel() if rows is not None else x.shape[0]
+    assert out.shape == (n_rows, hidden) and weight.shape == (hidden,) and weight.is_contiguous()
+    if delta is not None:
+        assert delta.shape == x.shape and delta.dtype == out.dtype and delta.is_contiguous()
+    if rows is not None:
+        assert rows.dtype == torch.int32 and rows.is_contiguous()
+    _call("pl_add_rmsnorm", _p(x), _p(delta), _p(weight), _code(weight.dtype), _p(out), _p(rows), n_rows, hidden,
+          float(eps), _code(out.dtype), _stream())
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    _dev(gate_up, out)
+    tokens, two_i = gate_up.shape
+    assert two_i % 2 == 0 and out.shape == (tokens, two_i // 2) and out.dtype == gate_up.dtype
+    assert gate_up.is_contiguous() and out.is_contiguous()
+    _call("pl_swiglu", _p(gate_up), _p(out), tokens, two_i // 2, _code(out.dtype), _stream())
+
+
+def bf16_to_f32(src: torch.Tensor, dst: torch.Tensor) -> None:
+    _dev(src, dst)
+    assert src.dtype == torch.bfloat16 and dst.dtype == torch.float32 and src.numel() == dst.numel()
+    assert src.is_contiguous() and dst.is_contiguous()
+    _call("pl_bf16_to_f32", _p(src), _p(dst), src.numel(), _stream())
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """out[M, N] (+)= a[M, K] @ w[N, K]^T in true fp32 (CUDA-core FMA)."""
+    _dev(a, w, out)
+    assert a.dtype == w.dtype == out.dtype == torch.float32
+    assert a.dim() == 2 and w.dim() == 2 and out.dim() == 2
+    m, k = a.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and out.shape == (m, n)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    _call("pl_gemm_f32", _p(a), _p(w), _p(out), m, n, k, a.stride(0) if m > 1 else k, w.stride(0) if n > 1 else k,
+          out.stride(0) if m > 1 else n, int(accumulate), _stream())
+
+
+def rope_kv_write(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | None, pos: torch.Tensor,
+                  entry: torch.Tensor, table: torch.Tensor, k_pool: torch.Tensor | None,
+                  v_pool: torch.Tensor | None, page_size: int, inv_freq: torch.Tensor | None, rotary: int,
+                  status: torch.Tensor | None = None) -> None:
+    """Rotates q [T, nh, hd] in place and writes rotated k and v [T, nkv, hd] into
+    the pools [pages, nkv, page_size, hd] (views of one layer's K and V)."""
+    _dev(q, k, v, pos, entry, table, k_pool, v_pool, inv_freq, status)
+    tokens, n_heads, head_dim = q.shape
+    assert q.stride(2) == 1 and q.stride(1) == head_dim
+    row_stride = q.stride(0)
+    n_kv = n_heads
+    page_stride = head_stride = n_pages = 0
+    if k_pool is not None:
+        assert k is not None and v is not None and v_pool is not None
+        n_kv = k.shape[1]
+        for t in (k, v):
+            assert t.shape == (tokens, n_kv, head_dim) and t.stride(2) == 1 and t.stride(1) == head_dim
+            assert (tokens == 1 or t.stride(0) == row_stride) and t.dtype == q.dtype
+        n_pages = k_pool.shape[0]
+        assert k_pool.shape == (n_pages, n_kv, page_size, head_dim) == v_pool.shape
+        assert k_pool.stride() == v_pool.stride() and k_pool.stride(3) == 1 and k_pool.stride(2) == head_dim
+        assert k_pool.dtype == q.dtype == v_pool.dtype
+        page_stride, head_stride = k_pool.stride(0), k_pool.stride(1)
+    assert pos.dtype == torch.int32 and entry.dtype == torch.int32 and table.dtype == torch.int32
+    assert pos.numel() == tokens and entry.numel() == tokens and table.dim() == 2 and table.is_contiguous()
+    if inv_freq is not None:
+        assert inv_freq.dtype == torch.float64 and inv_freq.numel() == rotary // 2 and inv_freq.is_contiguous()
+    _call("pl_rope_kv_write", _p(q), _p(k), _p(v), row_stride, _p(pos), _p(entry), _p(table), table.shape[1],
+          _p(k_pool), _p(v_pool), page_stride, head_stride, page_size, n_pages, _p(inv_freq), rotary, tokens,
+          n_heads, n_kv, head_dim, _code(q.dtype), _p(status), _stream())
+
+
+def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,
+                   pos: torch.Tensor, entry: torch.Tensor, out: torch.Tensor, page_size: int, window: int | None,
+                   scale: float, status: torch.Tensor | None = None) -> None:
+    """Causal paged attention; q and out [T, nh, hd] (row strides free), pools
+    [pages, nkv, page_size, hd]."""
+    _dev(q, k_pool, v_pool, table, pos, entry, out, status)
+    tokens, n_heads, head_dim = q.shape
+    n_pages, n_kv = k_pool.shape[0], k_pool.shape[1]
+    assert q.stride(2) == 1 and q.stride(1) == head_dim and out.stride(2) == 1 and out.stride(1) == head_dim
+    assert out.shape == q.shape and out.dtype == q.dtype == k_pool.dtype == v_pool.dtype
+    assert k_pool.shape == (n_pages, n_kv, page_size, head_dim) == v_pool.shape
+    assert k_pool.stride() == v_pool.stride() and k_pool.stride(3) == 1 and k_pool.stride(2) == head_dim
+    assert pos.dtype == torch.int32 and entry.dtype == torch.int32 and table.dtype == torch.int32
+    assert table.dim() == 2 and table.is_contiguous()
+    _call("pl_attention_simt", _p(q), q.stride(0), _p(k_pool), _p(v_pool), k_pool.stride(0), k_pool.stride(1),
+          page_size, n_pages, _p(table), table.shape[1], _p(pos), _p(entry), _p(out), out.stride(0), tokens,
+          n_heads, n_kv, head_dim, int(window or 0), float(scale), _code(q.dtype), _p(status), _stream())
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor | None,
+           top_p: torch.Tensor | None, seed: torch.Tensor, draw_count: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] (int32) = a token drawn from row r of fp32 logits [R, V]."""
+    _dev(logits, temperature, top_k, top_p, seed, draw_count, out)
+    rows, vocab = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert temperature.dtype == torch.float32 and temperature.numel() == rows
+    assert seed.dtype == torch.int64 and draw_count.dtype == torch.int64 and out.dtype == torch.int32
+    assert seed.numel() == rows and draw_count.numel() == rows and out.numel() == rows
+    if top_k is not None:
+        assert top_k.dtype == torch.int32 and top_k.numel() == rows
+    if top_p is not None:
+        assert top_p.dtype == torch.float32 and top_p.numel() == rows
+    _call("pl_sample", _p(logits), logits.stride(0) if rows > 1 else vocab, rows, vocab, _p(temperature),
+          _p(top_k), _p(top_p), _p(seed), _p(draw_count), _p(out), _stream())

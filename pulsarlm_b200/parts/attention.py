@@ -1,0 +1,105 @@
+"""The attention mixer: grouped-query causal attention over the paged cache."""
+
+from __future__ import annotations
+
+import dataclasses
+import math
+
+import torch
+
+from ..kernels import ops
+from .linear import linear
+from .registry import BuildContext, Part, build_part, register_part
+from .spec import KVCacheNeed, PartSpec, TensorNeed
+
+
+@dataclasses.dataclass
+class KVBinding:
+    """What the cache manager hands a mixer that asked for a KVCacheNeed: this
+    layer's key and value pools [pages, n_kv_heads, page_size, head_dim] and the
+    group whose block table (`batch.tables[group]`) indexes them."""
+
+    group: int
+    k_pool: torch.Tensor
+    v_pool: torch.Tensor
+    page_size: int
+
+
+@register_part("mixer", "attention")
+class Attention(Part):
+    """q, k, v projections (bias-free), position encoding on q and k, causal
+    softmax attention with scale (default 1/sqrt(head_dim)) where query head h
+    reads kv head h // (n_heads / n_kv_heads), then the o projection
+    (pulsarlm-core/src/engine/model/llama.cpp:61-82).
+
+    params: hidden_size, n_heads, n_kv_heads, head_dim, position (a PartSpec of the
+    "position" registry), scale (optional), window (optional: a query reads only
+    the last `window` keys), cache_from (optional: index of the layer whose cache
+    this layer reads; it then has no k and v projections and writes nothing).
+    tensors: q [nh*hd, H], k and v [nkv*hd, H], o [H, nh*hd]. q, k and v are
+    stacked into one operand at load.
+    """
+
+    def __init__(self, spec: PartSpec, ctx: BuildContext):
+        super().__init__(spec, ctx)
+        p = spec.params
+        self.hidden = int(self.param("hidden_size"))
+        self.n_heads = int(self.param("n_heads"))
+        self.n_kv = int(self.param("n_kv_heads"))
+        self.head_dim = int(self.param("head_dim"))
+        if self.n_heads % self.n_kv:
+            raise ValueError(f"attention: {self.n_heads} heads are not a multiple of {self.n_kv} kv heads")
+        self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.head_dim)
+        self.window = int(p["window"]) if p.get("window") else None
+        self.cache_from = p.get("cache_from")
+        self.position = build_part("position", self.param("position"), ctx)
+        self.qkv: torch.Tensor | None = None
+        self.o: torch.Tensor | None = None
+        self.cache: KVBinding | None = None
+
+    @classmethod
+    def tensor_needs(cls, spec: PartSpec) -> dict[str, TensorNeed]:
+        p, t = spec.params, spec.tensors
+        h, nh, nkv, hd = (int(p[k]) for k in ("hidden_size", "n_heads", "n_kv_heads", "head_dim"))
+        needs = {t["q"]: TensorNeed((nh * hd, h)), t["o"]: TensorNeed((h, nh * hd))}
+        if p.get("cache_from") is None:
+            needs[t["k"]] = TensorNeed((nkv * hd, h))
+            needs[t["v"]] = TensorNeed((nkv * hd, h))
+        return needs
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        t = self.spec.tensors
+        if self.cache_from is None:
+            self.qkv = torch.cat([tensors[t["q"]], tensors[t["k"]], tensors[t["v"]]], dim=0).contiguous()
+        else:
+            self.qkv = tensors[t["q"]].contiguous()
+        self.o = tensors[t["o"]].contiguous()
+
+    def cache_need(self) -> KVCacheNeed | None:
+        if self.cache_from is not None:
+            return None
+        return KVCacheNeed(self.n_kv, self.head_dim, self.window)
+
+    def bind_cache(self, binding: KVBinding) -> None:
+        self.cache = binding
+
+    def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
+        tokens = h.shape[0]
+        nh, nkv, hd = self.n_heads, self.n_kv, self.head_dim
+        cache = self.cache
+        table = batch.tables[cache.group]
+        qkv = linear(h, self.qkv)
+        q = qkv[:, : nh * hd].view(tokens, nh, hd)
+        inv_freq, rotary = self.position.table()
+        if self.cache_from is None:
+            k = qkv[:, nh * hd : (nh + nkv) * hd].view(tokens, nkv, hd)
+            v = qkv[:, (nh + nkv) * hd :].view(tokens, nkv, hd)
+            ops.rope_kv_write(q, k, v, batch.pos, batch.entry, table, cache.k_pool, cache.v_pool, cache.page_size,
+                              inv_freq, rotary, batch.status)
+        else:
+            ops.rope_kv_write(q, None, None, batch.pos, batch.entry, table, None, None, cache.page_size, inv_freq,
+                              rotary, batch.status)
+        out = torch.empty((tokens, nh, hd), dtype=h.dtype, device=h.device)
+        ops.attention_simt(q, cache.k_pool, cache.v_pool, table, batch.pos, batch.entry, out, cache.page_size,
+                           self.window, self.scale, batch.status)
+        return linear(out.view(tokens, nh * hd), self.o)
