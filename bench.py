@@ -1,0 +1,331 @@
+"""Decode and prefill throughput of the engine at the Llama-3.1-8B shape.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line. `value`: decoded tokens per second at batch 8, timed on the device
+with CUDA events over K decode steps after W warm-up steps, each request holding
+a 2,048-token prompt (real prefill through the engine) and decoding from there.
+`e2e`: the same through the Python entry point (Engine.submit / Engine.step),
+host token lists in and host token ids out every step. `prefill`: one 2,048-token
+prompt in one step. `roofline`: bytes the decode step must read (every weight
+once, the cache of the live requests) over its time, against the measured copy
+bandwidth. `points`: decode at batch 1 and 64 (their caches are filled with
+random keys and values instead of being prefilled: a decode step's time does not
+depend on the cache's contents). Weights are random (N(0, 0.02)) and drawn on the
+device; token ids are uniform random. The weights (16 GB) and caches are far
+larger than L2 (126 MB), so no L2 flush is needed between steps.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA31_8B = {
+    "architectures": ["LlamaForCausalLM"],
+    "model_type": "llama",
+    "num_hidden_layers": 32,
+    "hidden_size": 4096,
+    "num_attention_heads": 32,
+    "num_key_value_heads": 8,
+    "head_dim": 128,
+    "intermediate_size": 14336,
+    "vocab_size": 128256,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False,
+    "max_position_embeddings": 131072,
+}
+PROMPT_LEN = 2048
+CONTEXT_LEN = 4096
+PAGE_SIZE = 16
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while timed work runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+
+    def __init__(self, index: int = 0):
+        self.index = index
+        self.samples: list[list[str]] = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=5)
+
+    def summary(self) -> dict:
+        sm, sm_max, reasons = [], [], set()
+        for row in self.samples:
+            try:
+                sm.append(float(row[0]))
+                sm_max.append(float(row[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, cell in zip(self.NAMES, row[2:]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(sm_max) if sm_max else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_config(layers: int) -> dict:
+    cfg = dict(LLAMA31_8B)
+    cfg["num_hidden_layers"] = layers
+    return cfg
+
+
+def weight_bytes(cfg: dict, width: int = 2) -> int:
+    """Bytes of every weight a decode step reads once: all layer matrices and norms,
+    the final norm and the lm_head (embedding rows are gathered, not streamed)."""
+    h, i = cfg["hidden_size"], cfg["intermediate_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = (nh + 2 * nkv) * hd * h + h * nh * hd + 3 * i * h + 2 * h
+    return (cfg["num_hidden_layers"] * per_layer + cfg["vocab_size"] * h + h) * width
+
+
+def kv_bytes_per_token(cfg: dict, width: int = 2) -> int:
+    return cfg["num_hidden_layers"] * 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * width
+
+
+def prefill_flops(cfg: dict, tokens: int, logit_rows: int = 1) -> float:
+    h, i = cfg["hidden_size"], cfg["intermediate_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = 2.0 * tokens * ((nh + 2 * nkv) * hd * h + h * nh * hd + 3 * i * h)
+    attention = 4.0 * nh * hd * tokens * (tokens + 1) / 2
+    return cfg["num_hidden_layers"] * (per_layer + attention) + 2.0 * logit_rows * cfg["vocab_size"] * h
+
+
+def fill_cache(engine, batch: int, length: int, tag: str) -> list:
+    """Opens `batch` requests holding `length` tokens each without running a
+    prefill; the pools are filled with small random numbers once."""
+    ids = []
+    for b in range(batch):
+        rid = (tag, b)
+        assert engine.cache.open(rid) is not None, "too few slots"
+        assert engine.cache.reserve(rid, length), "too few pages"
+        engine.cache.commit(rid, length)
+        ids.append(rid)
+    return ids
+
+
+def time_decode(engine, ids: list, steps: int, warmup: int, vocab: int):
+    """K graph-replayed decode steps on the device (CUDA events). Tokens fed are
+    fixed (the step's time does not depend on them); positions advance."""
+    import torch
+
+    from pulsarlm_b200.engine.runner import StepEntry
+    from pulsarlm_b200.sampling.params import SamplingParams
+
+    params = [SamplingParams()] * len(ids)
+    seeds = [0] * len(ids)
+    entries = [StepEntry(r, [(7 * i + 3) % vocab], [0]) for i, r in enumerate(ids)]
+    for _ in range(warmup):
+        engine.runner.decode_step(entries, params, seeds, [0] * len(ids))
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    from pulsarlm_b200.kernels import ops
+
+    before_steps = engine.runner.graph_steps
+    start.record()
+    for _ in range(steps):
+        engine.runner.decode_step(entries, params, seeds, [0] * len(ids))
+    end.record()
+    torch.cuda.synchronize()
+    engine.runner.check_status()
+    graph = next(g for (n, _), g in engine.runner._graphs.items() if n == len(ids))
+    launches = graph.launches * (engine.runner.graph_steps - before_steps)
+    return start.elapsed_time(end) / steps, launches
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    from pulsarlm_b200 import Engine, SamplingParams
+    from pulsarlm_b200.engine.runner import StepEntry
+
+    pk = peaks()
+    cfg = model_config(args.layers)
+    batch = args.batch
+    torch.manual_seed(0)
+    device = "cuda:0"
+    max_batch = max(64, batch)
+    tokens_room = max_batch * (PROMPT_LEN + args.steps + args.warmup + 64) + 4 * PROMPT_LEN
+    n_pages = -(-tokens_room // PAGE_SIZE)
+    t0 = time.time()
+    engine = Engine(cfg, dtype="bfloat16", device=device, n_pages=n_pages, page_size=PAGE_SIZE,
+                    prefill_tokens_per_step=PROMPT_LEN, max_requests=max_batch + 2, seed=0)
+    for g in engine.cache.groups:
+        g.tensor.normal_(0.0, 0.5)
+    vocab = cfg["vocab_size"]
+    gen = torch.Generator().manual_seed(1)
+    setup_s = time.time() - t0
+
+    # ---- prefill: one 2,048-token prompt in one step, logits of the last token.
+    prompt = torch.randint(0, vocab, (PROMPT_LEN,), generator=gen).tolist()
+    times = []
+    with ClockSampler() as prefill_clocks:
+        for i in range(3 + 5):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            engine.runner.step([StepEntry(("prefill", i), prompt, [PROMPT_LEN - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            engine.runner.end(("prefill", i))
+            if i >= 3:
+                times.append(start.elapsed_time(end))
+    prefill_ms = statistics.median(times)
+    flops = prefill_flops(cfg, PROMPT_LEN)
+    prefill = {"value": PROMPT_LEN / (prefill_ms / 1e3), "tokens": PROMPT_LEN, "ms": prefill_ms,
+               "frac": flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), "unit": "tok/s",
+               "peak_tflops": pk["bf16_tflops"]}
+
+    # ---- end to end through the public API: batch prompts in, tokens out per step.
+    prompts = [torch.randint(0, vocab, (PROMPT_LEN,), generator=gen).tolist() for _ in range(batch)]
+    sampling = SamplingParams(temperature=0.0)
+    total_new = args.warmup + args.steps + 1
+    requests = [engine.submit(p, sampling=sampling, max_tokens=total_new, ignore_eos=True) for p in prompts]
+    while any(len(r.output) < 1 for r in requests):
+        engine.step()  # prefill (untimed)
+    for _ in range(args.warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    with ClockSampler() as e2e_clocks:
+        t_start = time.perf_counter()
+        for _ in range(args.steps):
+            engine.step()
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t_start
+    assert all(len(r.output) == args.warmup + args.steps + 1 for r in requests)
+    graph = next(g for (n, _), g in engine.runner._graphs.items() if n == batch)
+    e2e = {"value": batch * args.steps / e2e_s, "unit": "tok/s", "ms_per_step": e2e_s / args.steps * 1e3,
+           "h2d_bytes_per_step": graph.layout.nbytes, "d2h_bytes_per_step": 4 * batch}
+    for r in requests:
+        r.cancel()
+    engine.step()
+
+    # ---- device-timed decode at the headline batch, same context.
+    ids = fill_cache(engine, batch, PROMPT_LEN + args.warmup, "main")
+    with ClockSampler() as clocks:
+        ms_per_step, launches = time_decode(engine, ids, args.steps, args.warmup, vocab)
+    mid_context = PROMPT_LEN + 2 * args.warmup + args.steps / 2
+    step_bytes = weight_bytes(cfg) + batch * mid_context * kv_bytes_per_token(cfg)
+    achieved = step_bytes / (ms_per_step / 1e3) / 1e9
+    for rid in ids:
+        engine.cache.close(rid)
+
+    # ---- other batch sizes.
+    points = {}
+    for b in (1, 64):
+        ids = fill_cache(engine, b, PROMPT_LEN, f"b{b}")
+        ms, _ = time_decode(engine, ids, max(8, args.steps // 2), args.warmup, vocab)
+        points[f"decode_b{b}"] = b / (ms / 1e3)
+        for rid in ids:
+            engine.cache.close(rid)
+
+    clock_summary = clocks.summary()
+    return {
+        "metric": "decode tok/s at batch 8 (Llama-3.1-8B shape, 2,048-token prompts)",
+        "value": batch / (ms_per_step / 1e3),
+        "unit": "tok/s",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": ms_per_step,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic: random weights N(0,0.02) drawn on the device, uniform random token ids",
+        "impl": "ours",
+        "config": {
+            "model": "Llama-3.1-8B shape", "layers": cfg["num_hidden_layers"], "layers_full": 32,
+            "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+            "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+            "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+            "global_batch": batch, "seq_len": CONTEXT_LEN, "prompt_len": PROMPT_LEN,
+            "decode_context_start": PROMPT_LEN + args.warmup, "page_size": PAGE_SIZE,
+            "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 16 GB)",
+            "peaks": pk["source"],
+        },
+        "e2e": e2e,
+        "gpu_launches": launches,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "bytes_per_step": step_bytes},
+        "points": points,
+        "clocks": {"sm_mhz": clock_summary["sm_mhz"], "sm_max_mhz": clock_summary["sm_max_mhz"],
+                   "reasons": clock_summary["reasons"]},
+        "setup_s": setup_s,
+    }
+
+
+def main() -> int:
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=128)
+    p.add_argument("--warmup", type=int, default=8)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--layers", type=int, default=32, help="fewer layers than the model's 32 (named in config)")
+    args = p.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "cosmonomic/pulsarlm does not install offline here: its build needs hatchling, Python >= 3.13, "
+                          "torch 2.15, xmake, CUDA 13.2 and gcc 15, none of which this image has"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run with --gpus 1")
+        return 2
+    args.warmup = max(3, args.warmup)
+    print(json.dumps(run_ours(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

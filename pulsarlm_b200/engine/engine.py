@@ -32,7 +32,8 @@ DEFAULT_PAGE_SIZE = 16
 class Engine:
     def __init__(self, model, dtype="bfloat16", device="cuda:0", kv_cache_gib: float = 4.0,
                  page_size: int = DEFAULT_PAGE_SIZE, prefill_tokens_per_step: int = 256,
-                 max_requests: int = 64, n_pages: int | None = None, stop_ids=None, seed: int | None = None):
+                 max_requests: int = 64, n_pages: int | None = None, stop_ids=None, seed: int | None = None,
+                 cuda_graphs: bool = True):
         """model: a model folder, a built Model, or a config.json dict (random
         weights from `seed`). kv_cache_gib sizes the page pools unless n_pages
         gives the number of pages outright. stop_ids default to config.json's
@@ -58,6 +59,7 @@ class Engine:
         self.sampler = Sampler(self.device)
         stops = self.model.spec.eos_token_ids if stop_ids is None else stop_ids
         self.scheduler = Scheduler(self.cache, stops, prefill_tokens_per_step)
+        self.cuda_graphs = cuda_graphs and self.runner.graphs_allowed
         self._ids = itertools.count()
         self.vocab_size = self.model.spec.vocab_size
 
@@ -87,9 +89,17 @@ class Engine:
             return ended
         step_entries = [StepEntry(e.request.id, e.tokens, [len(e.tokens) - 1] if e.samples else [])
                         for e in entries]
-        logits = self.runner.step(step_entries)
         sampled: dict = {}
         samplers = [e for e in entries if e.samples]
+        if self.cuda_graphs and all(len(e.tokens) == 1 and e.samples and e.request.max_tokens != 0
+                                    for e in entries):
+            drawn = self.runner.decode_step(
+                step_entries, [e.request.sampling for e in entries], [e.request.seed for e in entries],
+                [e.request.draw_count for e in entries])
+            host = drawn.cpu().tolist()  # the step's one synchronisation
+            sampled = {e.request.id: t for e, t in zip(entries, host)}
+            return ended + self.scheduler.finish_step(entries, sampled)
+        logits = self.runner.step(step_entries)
         if samplers and logits is not None:
             drawn = self.sampler.sample(
                 logits, [e.request.sampling for e in samplers], [e.request.seed for e in samplers],

@@ -1,0 +1,102 @@
+"""CUDA graphs for steps made of single decode tokens.
+
+A decode step launches a few hundred small kernels; captured once per (number of
+entries, block-table width) and replayed, the host's part of a step is one
+buffer fill, one host-to-device copy and one graph launch. The captured work is
+the same Model.forward the eager step runs, followed by the sampling kernel;
+only where its inputs live differs (fixed device buffers).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from ..models.model import StepBatch
+
+_ALIGN = 16
+
+
+class _Layout:
+    """Typed arrays packed into one byte buffer, each starting on 16 bytes."""
+
+    def __init__(self, fields: list[tuple[str, np.dtype, tuple[int, ...]]]):
+        self.fields = {}
+        offset = 0
+        for name, dtype, shape in fields:
+            size = int(np.prod(shape)) * np.dtype(dtype).itemsize
+            self.fields[name] = (offset, np.dtype(dtype), shape, size)
+            offset += -(-size // _ALIGN) * _ALIGN
+        self.nbytes = max(offset, _ALIGN)
+
+    def host_views(self, buffer: np.ndarray) -> dict[str, np.ndarray]:
+        return {name: buffer[o : o + size].view(dt).reshape(shape)
+                for name, (o, dt, shape, size) in self.fields.items()}
+
+    def device_views(self, buffer: torch.Tensor) -> dict[str, torch.Tensor]:
+        kinds = {np.dtype(np.int32): torch.int32, np.dtype(np.float32): torch.float32,
+                 np.dtype(np.int64): torch.int64}
+        return {name: buffer[o : o + size].view(kinds[dt]).view(shape)
+                for name, (o, dt, shape, size) in self.fields.items()}
+
+
+class GraphedDecode:
+    """One captured decode step for `n` entries and block tables `width` wide."""
+
+    def __init__(self, runner, n: int, width: int):
+        self.runner = runner
+        self.n = n
+        self.width = width
+        cache = runner.cache
+        fields = [("tokens", np.int32, (n,)), ("pos", np.int32, (n,)), ("entry", np.int32, (n,)),
+                  ("slots", np.int32, (n,)), ("want", np.int32, (n,)), ("top_k", np.int32, (n,)),
+                  ("temperature", np.float32, (n,)), ("top_p", np.float32, (n,)),
+                  ("seed", np.int64, (n,)), ("count", np.int64, (n,))]
+        fields += [(f"table{g.index}", np.int32, (n, width)) for g in cache.groups]
+        self.layout = _Layout(fields)
+        self.host = torch.empty(self.layout.nbytes, dtype=torch.uint8, pin_memory=True)
+        self.h = self.layout.host_views(self.host.numpy())
+        self.dev = torch.zeros(self.layout.nbytes, dtype=torch.uint8, device=runner.device)
+        self.d = self.layout.device_views(self.dev)
+        self.h["entry"][:] = np.arange(n, dtype=np.int32)
+        self.h["want"][:] = np.arange(n, dtype=np.int32)
+        self.batch = StepBatch(
+            tokens=self.d["tokens"], pos=self.d["pos"], entry=self.d["entry"],
+            tables={g.index: self.d[f"table{g.index}"] for g in cache.groups},
+            slots=self.d["slots"], want_rows=self.d["want"], status=runner.status,
+            n_tokens=n, n_entries=n, host_query_lens=[1] * n, host_context_lens=[],
+            extras={"graph": True, "max_context": width * cache.page_size},
+        )
+        self.logits: torch.Tensor | None = None
+        self.ids: torch.Tensor | None = None
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.copied = torch.cuda.Event()
+        self.launches = 0
+
+    def _forward(self) -> None:
+        self.logits = self.runner.model.forward(self.batch)
+        self.ids = torch.empty(self.n, dtype=torch.int32, device=self.runner.device)
+        ops.sample(self.logits, self.d["temperature"], self.d["top_k"], self.d["top_p"], self.d["seed"],
+                   self.d["count"], self.ids)
+
+    def capture(self) -> None:
+        """Runs the step once eagerly on a side stream (libraries set themselves up),
+        then records it. The buffers must hold a valid batch."""
+        self.dev.copy_(self.host, non_blocking=True)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._forward()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
+        with torch.cuda.graph(self.graph):
+            self._forward()
+        self.launches = ops.launch_count() - before
+
+    def replay(self) -> None:
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copied.record()
+        self.graph.replay()

@@ -57,8 +57,14 @@ class ModelRunner:
         model.bind_caches(cache.bindings())
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._staging: torch.Tensor | None = None
+        self._graphs: dict = {}
+        # Replaying a captured step re-runs the capture's warm-up on the same tokens,
+        # which is harmless for caches written by position but not for states updated
+        # in place, so models with state slots step eagerly.
+        self.graphs_allowed = not cache.state_layers
         self.steps = 0
         self.tokens_run = 0
+        self.graph_steps = 0
 
     # ------------------------------------------------------------------ helpers
     def _stage(self, arrays: list[np.ndarray]) -> list[torch.Tensor]:
@@ -156,6 +162,59 @@ class ModelRunner:
         self.steps += 1
         self.tokens_run += batch.n_tokens
         return logits
+
+    def decode_step(self, entries: list[StepEntry], sampling, seeds: list[int], counts: list[int]) -> torch.Tensor:
+        """A step of single tokens, one per entry, each sampling its next token:
+        replays a CUDA graph captured for this number of entries. Returns int32
+        [entries] token ids in a device buffer that the next call overwrites."""
+        from .graphs import GraphedDecode
+
+        n = len(entries)
+        new_lens = []
+        for e in entries:
+            if len(e.tokens) != 1:
+                raise ValueError("decode_step takes entries of one token")
+            if not self.cache.is_open(e.request):
+                raise ValueError(f"request {e.request!r} has no cache to decode from")
+            new_len = self.cache.length(e.request) + 1
+            if not self.cache.reserve(e.request, new_len):
+                raise OutOfPages(e.request, f"too few free pages for request {e.request!r} to reach {new_len} tokens")
+            new_lens.append(new_len)
+        pages = -(-max(new_lens) // self.cache.page_size)
+        width = -(-pages // 64) * 64
+        key = (n, width)
+        graph = self._graphs.get(key)
+        fresh = graph is None
+        if fresh:
+            graph = self._graphs[key] = GraphedDecode(self, n, width)
+        else:
+            graph.copied.synchronize()
+        h = graph.h
+        requests = [e.request for e in entries]
+        for i, e in enumerate(entries):
+            h["tokens"][i] = e.tokens[0]
+            h["pos"][i] = new_lens[i] - 1
+            h["slots"][i] = self.cache.slot(e.request)
+            p = sampling[i]
+            h["temperature"][i] = p.temperature if p.draws else 0.0
+            h["top_k"][i] = p.top_k
+            h["top_p"][i] = p.top_p if 0.0 < p.top_p < 1.0 else 2.0
+            h["seed"][i] = np.uint64(seeds[i] & 0xFFFFFFFFFFFFFFFF).astype(np.int64)
+            h["count"][i] = counts[i]
+        for g in self.cache.groups:
+            rows = self.cache.table_rows(g.index, requests, width_multiple=1)
+            table = h[f"table{g.index}"]
+            table[:] = -1
+            table[:, : rows.shape[1]] = rows
+        if fresh:
+            graph.capture()
+        graph.replay()
+        for e, new_len in zip(entries, new_lens):
+            self.cache.commit(e.request, new_len)
+        self.steps += 1
+        self.graph_steps += 1
+        self.tokens_run += n
+        return graph.ids
 
     def end(self, request) -> None:
         """Gives back what the request holds."""

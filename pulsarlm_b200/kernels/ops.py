@@ -96,7 +96,17 @@ def _p(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernel entry points of this library have been called so far."""
+    return _launches
+
+
 def _call(name: str, *args) -> None:
+    global _launches
+    _launches += 1
     code = getattr(library(), name)(*args)
     if code != 0:
         raise KernelError(library().pl_last_error().decode("utf-8", "replace"))
