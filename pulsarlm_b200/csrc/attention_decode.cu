@@ -1,0 +1,417 @@
+// Paged attention for single decode tokens in bfloat16: split over the keys, the
+// query heads of a GQA group packed into one tensor-core tile.
+//
+// A decode token reads its request's whole cache once; the kernel is bound by HBM.
+// CTA (split, kv head, token) walks a contiguous share of the request's 16-key
+// tiles. Its warps take tiles round-robin; each warp streams K and V tiles into its
+// own ring of shared-memory stages with cp.async (16-byte chunks, XOR-swizzled so
+// ldmatrix is conflict-free) and keeps the group's (<= 16) query heads as the M
+// rows of m16n8k16 MMAs: S = Q K^T, online softmax in fp32 (base 2, the scale
+// folded into the exponent), O += P V with P rounded to bf16. Warps are merged
+// through shared memory; with more than one split the CTA writes an unnormalised
+// partial (o, m, l) to scratch and a second kernel merges the splits. Split
+// boundaries depend only on the request's length and the launch's split count.
+//
+// The reference's counterparts: attn_decode_tc_kernel and paged_decode_split /
+// combine kernels, pulsarlm-core/src/kernels/paged_attention.cu:432-584.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kTile = 16;  // keys per tile
+
+struct DecodeParams {
+    const __nv_bfloat16* q;
+    int64_t q_row_stride;
+    const __nv_bfloat16* k_pool;
+    const __nv_bfloat16* v_pool;
+    int64_t page_stride;
+    int64_t head_stride;
+    int page_size;
+    int n_pages;
+    const int32_t* table;
+    int table_width;
+    const int32_t* pos;
+    const int32_t* entry;
+    __nv_bfloat16* out;
+    int64_t out_row_stride;
+    float* part_o;   // [tokens, heads, splits, HD]
+    float* part_ml;  // [tokens, heads, splits, 2]
+    int n_heads;
+    int group;
+    int window;
+    float scale_log2;
+    int n_splits;
+    int32_t* status;
+};
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* global) {
+    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(global));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+    const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+    const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <int HD, int WARPS, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const DecodeParams p) {
+    constexpr int kRowBytes = HD * 2;
+    constexpr int kChunks = HD / 8;             // 16-byte chunks per row
+    constexpr int kTileBytes = kTile * kRowBytes;
+    constexpr int kStageBytes = 2 * kTileBytes;  // K tile then V tile
+    extern __shared__ __align__(128) unsigned char smem[];
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, tig = lane & 3;
+    const int split = blockIdx.x, kv_head = blockIdx.y, t = blockIdx.z;
+
+    const int ctx = p.pos[t] + 1;
+    const int first = p.window > 0 ? max(0, ctx - p.window) : 0;
+    const int tile_first = first / kTile, tile_end = (ctx + kTile - 1) / kTile;
+    const int per_split = (tile_end - tile_first + p.n_splits - 1) / p.n_splits;
+    const int t0 = tile_first + split * per_split;
+    const int t1 = min(t0 + per_split, tile_end);
+    const int32_t* row = p.table + static_cast<int64_t>(p.entry[t]) * p.table_width;
+
+    // Q fragments: rows g and g + 8 of the group's heads (zero past the group).
+    uint32_t qa[HD / 16][4];
+    {
+        const __nv_bfloat16* qbase = p.q + t * p.q_row_stride + static_cast<int64_t>(kv_head) * p.group * HD;
+        const bool lo_ok = g < p.group, hi_ok = g + 8 < p.group;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+            const int d = 16 * kk + 2 * tig;
+            qa[kk][0] = lo_ok ? *reinterpret_cast<const uint32_t*>(qbase + g * HD + d) : 0u;
+            qa[kk][1] = hi_ok ? *reinterpret_cast<const uint32_t*>(qbase + (g + 8) * HD + d) : 0u;
+            qa[kk][2] = lo_ok ? *reinterpret_cast<const uint32_t*>(qbase + g * HD + d + 8) : 0u;
+            qa[kk][3] = hi_ok ? *reinterpret_cast<const uint32_t*>(qbase + (g + 8) * HD + d + 8) : 0u;
+        }
+    }
+
+    unsigned char* ring = smem + warp * (STAGES * kStageBytes);
+    const int my_tiles = t1 > t0 + warp ? (t1 - t0 - warp + WARPS - 1) / WARPS : 0;
+
+    auto issue = [&](int i) {  // loads this warp's i-th tile into stage i % STAGES
+        if (i < my_tiles) {
+            const int tile = t0 + warp + i * WARPS;
+            const int key0 = tile * kTile;
+            int page = row[key0 / p.page_size];
+            if (page < 0 || page >= p.n_pages) {
+                if (lane == 0 && p.status != nullptr) {
+                    atomicOr(p.status, 4);
+                }
+                page = 0;  // stay in bounds; the result is flagged as wrong
+            }
+            const int64_t offset = page * p.page_stride + kv_head * p.head_stride +
+                static_cast<int64_t>(key0 % p.page_size) * HD;
+            const unsigned char* ksrc = reinterpret_cast<const unsigned char*>(p.k_pool + offset);
+            const unsigned char* vsrc = reinterpret_cast<const unsigned char*>(p.v_pool + offset);
+            unsigned char* stage = ring + (i % STAGES) * kStageBytes;
+#pragma unroll
+            for (int c = lane; c < kTile * kChunks; c += 32) {
+                const int r = c / kChunks, ch = c % kChunks;
+                const int dst = r * kRowBytes + ((ch ^ (r & 7)) * 16);
+                cp_async_16(stage + dst, ksrc + r * kRowBytes + ch * 16);
+                cp_async_16(stage + kTileBytes + dst, vsrc + r * kRowBytes + ch * 16);
+            }
+        }
+        cp_async_commit();
+    };
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+    }
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;
+
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) {
+        issue(i);
+    }
+    for (int i = 0; i < my_tiles; ++i) {
+        cp_async_wait<STAGES - 2>();
+        __syncwarp();
+        const unsigned char* stage = ring + (i % STAGES) * kStageBytes;
+        const int key0 = (t0 + warp + i * WARPS) * kTile;
+
+        float s[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+        {
+            const int mi = lane >> 3, r = lane & 7;
+            const int key = (mi >> 1) * 8 + r;
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                uint32_t b[4];
+                const int chunk = 2 * kk + (mi & 1);
+                ldmatrix_x4(b, stage + key * kRowBytes + ((chunk ^ (key & 7)) * 16));
+                mma_bf16(s[0], qa[kk], b[0], b[1]);
+                mma_bf16(s[1], qa[kk], b[2], b[3]);
+            }
+        }
+        // Mask keys outside [first, ctx); move to the base-2 exponent domain.
+        float tile_lo = -INFINITY, tile_hi = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = key0 + 8 * j + 2 * tig + (e & 1);
+                const bool ok = key >= first && key < ctx;
+                s[j][e] = ok ? s[j][e] * p.scale_log2 : -INFINITY;
+            }
+            tile_lo = fmaxf(tile_lo, fmaxf(s[j][0], s[j][1]));
+            tile_hi = fmaxf(tile_hi, fmaxf(s[j][2], s[j][3]));
+        }
+        tile_lo = fmaxf(tile_lo, __shfl_xor_sync(0xffffffffu, tile_lo, 1));
+        tile_lo = fmaxf(tile_lo, __shfl_xor_sync(0xffffffffu, tile_lo, 2));
+        tile_hi = fmaxf(tile_hi, __shfl_xor_sync(0xffffffffu, tile_hi, 1));
+        tile_hi = fmaxf(tile_hi, __shfl_xor_sync(0xffffffffu, tile_hi, 2));
+        const float new_lo = fmaxf(m_lo, tile_lo), new_hi = fmaxf(m_hi, tile_hi);
+        // A row that has seen no key yet keeps exponent base 0 (all its p are 0).
+        const float base_lo = new_lo == -INFINITY ? 0.0f : new_lo;
+        const float base_hi = new_hi == -INFINITY ? 0.0f : new_hi;
+        const float corr_lo = exp2f(m_lo - base_lo), corr_hi = exp2f(m_hi - base_hi);
+        m_lo = new_lo;
+        m_hi = new_hi;
+        uint32_t pa[4];
+        {
+            const float p00 = exp2f(s[0][0] - base_lo), p01 = exp2f(s[0][1] - base_lo);
+            const float p02 = exp2f(s[0][2] - base_hi), p03 = exp2f(s[0][3] - base_hi);
+            const float p10 = exp2f(s[1][0] - base_lo), p11 = exp2f(s[1][1] - base_lo);
+            const float p12 = exp2f(s[1][2] - base_hi), p13 = exp2f(s[1][3] - base_hi);
+            l_lo = l_lo * corr_lo + (p00 + p01 + p10 + p11);
+            l_hi = l_hi * corr_hi + (p02 + p03 + p12 + p13);
+            pa[0] = pack_bf16(p00, p01);
+            pa[1] = pack_bf16(p02, p03);
+            pa[2] = pack_bf16(p10, p11);
+            pa[3] = pack_bf16(p12, p13);
+        }
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) {
+            o[n][0] *= corr_lo;
+            o[n][1] *= corr_lo;
+            o[n][2] *= corr_hi;
+            o[n][3] *= corr_hi;
+        }
+        {
+            const int mi = lane >> 3, r = lane & 7;
+            const int key = (mi & 1) * 8 + r;
+            const unsigned char* vt = stage + kTileBytes;
+#pragma unroll
+            for (int dp = 0; dp < HD / 16; ++dp) {
+                uint32_t b[4];
+                const int chunk = 2 * dp + (mi >> 1);
+                ldmatrix_x4_trans(b, vt + key * kRowBytes + ((chunk ^ (key & 7)) * 16));
+                mma_bf16(o[2 * dp], pa, b[0], b[1]);
+                mma_bf16(o[2 * dp + 1], pa, b[2], b[3]);
+            }
+        }
+        __syncwarp();
+        issue(i + STAGES - 1);
+    }
+    cp_async_wait<0>();
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+
+    // Merge the warps through shared memory (the rings are done with).
+    __syncthreads();
+    float* red_o = reinterpret_cast<float*>(smem);        // [WARPS][16][HD]
+    float* red_m = red_o + WARPS * 16 * HD;               // [WARPS][16]
+    float* red_l = red_m + WARPS * 16;                    // [WARPS][16]
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        const int d = 8 * n + 2 * tig;
+        if (g < p.group) {
+            red_o[(warp * 16 + g) * HD + d] = o[n][0];
+            red_o[(warp * 16 + g) * HD + d + 1] = o[n][1];
+        }
+        if (g + 8 < p.group) {
+            red_o[(warp * 16 + g + 8) * HD + d] = o[n][2];
+            red_o[(warp * 16 + g + 8) * HD + d + 1] = o[n][3];
+        }
+    }
+    if (tig == 0) {
+        red_m[warp * 16 + g] = m_lo;
+        red_m[warp * 16 + g + 8] = m_hi;
+        red_l[warp * 16 + g] = l_lo;
+        red_l[warp * 16 + g + 8] = l_hi;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < p.group * HD; idx += WARPS * 32) {
+        const int r = idx / HD, d = idx % HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            m = fmaxf(m, red_m[w * 16 + r]);
+        }
+        float l = 0.0f, acc = 0.0f;
+        if (m > -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                const float scale = exp2f(red_m[w * 16 + r] - m);
+                l += red_l[w * 16 + r] * scale;
+                acc += red_o[(w * 16 + r) * HD + d] * scale;
+            }
+        }
+        const int h = kv_head * p.group + r;
+        if (p.n_splits == 1) {
+            p.out[t * p.out_row_stride + static_cast<int64_t>(h) * HD + d] =
+                __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+        } else {
+            const int64_t slot = (static_cast<int64_t>(t) * p.n_heads + h) * p.n_splits + split;
+            p.part_o[slot * HD + d] = acc;
+            if (d == 0) {
+                p.part_ml[slot * 2] = m;
+                p.part_ml[slot * 2 + 1] = l;
+            }
+        }
+    }
+}
+
+// One block per (token, head): merges the splits' partials.
+template <int HD>
+__global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                              __nv_bfloat16* __restrict__ out, int64_t out_row_stride, int n_heads,
+                                              int n_splits) {
+    const int t = blockIdx.y, h = blockIdx.x;
+    const int64_t base = (static_cast<int64_t>(t) * n_heads + h) * n_splits;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) {
+        m = fmaxf(m, part_ml[(base + s) * 2]);
+    }
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float l = 0.0f, acc = 0.0f;
+        if (m > -INFINITY) {
+            for (int s = 0; s < n_splits; ++s) {
+                const float scale = exp2f(part_ml[(base + s) * 2] - m);
+                l += part_ml[(base + s) * 2 + 1] * scale;
+                acc += part_o[(base + s) * HD + d] * scale;
+            }
+        }
+        out[t * out_row_stride + static_cast<int64_t>(h) * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+    }
+}
+
+constexpr int kWarps = 4;
+constexpr int kStages = 3;
+
+template <int HD>
+int launch_decode(const DecodeParams& p, int n_tokens, int n_kv_heads, cudaStream_t stream) {
+    constexpr int smem = kWarps * kStages * 2 * kTile * HD * 2;
+    static_assert(smem >= kWarps * 16 * (HD + 2) * 4, "the merge buffers must fit in the rings");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(attention_decode_kernel<HD, kWarps, kStages>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (err != cudaSuccess) {
+            return pl_fail(3, "attention_decode: cannot set shared memory size: %s", cudaGetErrorString(err));
+        }
+        configured = true;
+    }
+    const dim3 grid(p.n_splits, n_kv_heads, n_tokens);
+    attention_decode_kernel<HD, kWarps, kStages><<<grid, kWarps * 32, smem, stream>>>(p);
+    PL_CHECK_LAUNCH("attention_decode");
+    if (p.n_splits > 1) {
+        attention_decode_merge_kernel<HD><<<dim3(p.n_heads, n_tokens), HD <= 64 ? 64 : 128, 0, stream>>>(
+            p.part_o, p.part_ml, p.out, p.out_row_stride, p.n_heads, p.n_splits);
+        PL_CHECK_LAUNCH("attention_decode_merge");
+    }
+    return 0;
+}
+
+}  // namespace
+
+// 1 when pl_attention_decode takes this shape, else 0 (the caller then uses the
+// CUDA-core kernel, which takes every shape).
+PL_API int pl_attention_decode_supports(int head_dim, int group, int page_size, int dtype) {
+    return dtype == PL_BF16 && (head_dim == 64 || head_dim == 128) && group >= 1 && group <= 16 &&
+        page_size % kTile == 0;
+}
+
+// Scratch floats needed for `n_tokens` tokens at `n_splits` splits.
+PL_API int64_t pl_attention_decode_scratch_floats(int n_tokens, int n_heads, int head_dim, int n_splits) {
+    return n_splits <= 1 ? 0 : static_cast<int64_t>(n_tokens) * n_heads * n_splits * (head_dim + 2);
+}
+
+// bf16 only. q and out [T, n_heads, head_dim] with row strides; one query per token
+// at position pos[t]; pools and table as in pl_attention_simt. scratch: at least
+// pl_attention_decode_scratch_floats floats when n_splits > 1.
+PL_API int pl_attention_decode(const void* q, int64_t q_row_stride, const void* k_pool, const void* v_pool,
+                               int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
+                               const int32_t* table, int table_width, const int32_t* pos, const int32_t* entry,
+                               void* out, int64_t out_row_stride, int n_tokens, int n_heads, int n_kv_heads,
+                               int head_dim, int window, float scale, int n_splits, float* scratch,
+                               int32_t* status, cudaStream_t stream) {
+    PL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
+               "attention_decode: bad sizes tokens=%d heads=%d kv_heads=%d", n_tokens, n_heads, n_kv_heads);
+    const int group = n_heads / n_kv_heads;
+    PL_REQUIRE(pl_attention_decode_supports(head_dim, group, page_size, PL_BF16),
+               "attention_decode: unsupported shape head_dim=%d group=%d page=%d (takes head_dim 64 or 128, "
+               "groups of at most 16 heads, pages that are multiples of 16 tokens)",
+               head_dim, group, page_size);
+    PL_REQUIRE(n_splits >= 1 && n_splits <= 65535 && n_kv_heads <= 65535 && n_tokens <= 65535,
+               "attention_decode: grid too large (splits=%d kv_heads=%d tokens=%d)", n_splits, n_kv_heads, n_tokens);
+    PL_REQUIRE(n_splits == 1 || scratch != nullptr, "attention_decode: %d splits need scratch memory", n_splits);
+    PL_REQUIRE(q_row_stride % 2 == 0 && (reinterpret_cast<uintptr_t>(q) & 3) == 0,
+               "attention_decode: q must be 4-byte aligned with an even row stride");
+    PL_REQUIRE((reinterpret_cast<uintptr_t>(k_pool) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_pool) & 15) == 0 &&
+                   page_stride % 8 == 0 && head_stride % 8 == 0,
+               "attention_decode: pools must be 16-byte aligned with strides that are multiples of 8 elements");
+    if (n_tokens == 0) {
+        return 0;
+    }
+    DecodeParams p;
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.q_row_stride = q_row_stride;
+    p.k_pool = static_cast<const __nv_bfloat16*>(k_pool);
+    p.v_pool = static_cast<const __nv_bfloat16*>(v_pool);
+    p.page_stride = page_stride;
+    p.head_stride = head_stride;
+    p.page_size = page_size;
+    p.n_pages = n_pages;
+    p.table = table;
+    p.table_width = table_width;
+    p.pos = pos;
+    p.entry = entry;
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.out_row_stride = out_row_stride;
+    p.part_o = scratch;
+    p.part_ml = scratch != nullptr ? scratch + static_cast<int64_t>(n_tokens) * n_heads * n_splits * head_dim : nullptr;
+    p.n_heads = n_heads;
+    p.group = group;
+    p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.n_splits = n_splits;
+    p.status = status;
+    if (head_dim == 64) {
+        return launch_decode<64>(p, n_tokens, n_kv_heads, stream);
+    }
+    return launch_decode<128>(p, n_tokens, n_kv_heads, stream);
+}

@@ -65,7 +65,7 @@ class GraphedDecode:
             tokens=self.d["tokens"], pos=self.d["pos"], entry=self.d["entry"],
             tables={g.index: self.d[f"table{g.index}"] for g in cache.groups},
             slots=self.d["slots"], want_rows=self.d["want"], status=runner.status,
-            n_tokens=n, n_entries=n, host_query_lens=[1] * n, host_context_lens=[],
+            n_tokens=n, n_entries=n, n_decode=n, host_query_lens=[1] * n, host_context_lens=[],
             extras={"graph": True, "max_context": width * cache.page_size},
         )
         self.logits: torch.Tensor | None = None

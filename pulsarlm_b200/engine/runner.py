@@ -119,21 +119,28 @@ class ModelRunner:
 
         if getattr(self, "_copy_done", None) is not None:
             self._copy_done.synchronize()
+        # Entries of one token go first (the attention part sends the leading single
+        # tokens to its decode kernel); the wanted rows still come back in the
+        # caller's order of entries.
+        order = sorted(range(len(entries)), key=lambda i: len(entries[i].tokens) != 1)
+        n_decode = sum(1 for e in entries if len(e.tokens) == 1)
         n_tokens = sum(len(e.tokens) for e in entries)
         tokens = np.empty(n_tokens, dtype=np.int32)
         pos = np.empty(n_tokens, dtype=np.int32)
         entry = np.empty(n_tokens, dtype=np.int32)
-        want_rows: list[int] = []
+        first_row = [0] * len(entries)
         at = 0
-        for i, e in enumerate(entries):
+        for place, i in enumerate(order):
+            e = entries[i]
             n = len(e.tokens)
             start = self.cache.length(e.request)
             tokens[at : at + n] = e.tokens
             pos[at : at + n] = np.arange(start, start + n, dtype=np.int32)
-            entry[at : at + n] = i
-            want_rows.extend(at + w for w in e.want)
+            entry[at : at + n] = place
+            first_row[i] = at
             at += n
-        requests = [e.request for e in entries]
+        want_rows = [first_row[i] + w for i, e in enumerate(entries) for w in e.want]
+        requests = [entries[i].request for i in order]
         slots = np.array([self.cache.slot(r) for r in requests], dtype=np.int32)
         tables = [self.cache.table_rows(g.index, requests) for g in self.cache.groups]
         arrays = [tokens, pos, entry, slots, np.array(want_rows, dtype=np.int32), *tables]
@@ -146,8 +153,9 @@ class ModelRunner:
             status=self.status,
             n_tokens=n_tokens,
             n_entries=len(entries),
-            host_query_lens=[len(e.tokens) for e in entries],
-            host_context_lens=list(new_lens),
+            n_decode=n_decode,
+            host_query_lens=[len(entries[i].tokens) for i in order],
+            host_context_lens=[new_lens[i] for i in order],
         )
         return batch, new_lens
 

@@ -43,6 +43,9 @@ _SIGNATURES = {
                          _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _PTR, _PTR],
     "pl_attention_simt": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
                           _I32, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR],
+    "pl_attention_decode": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
+                            _I32, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR, _PTR],
+    "pl_attention_decode_supports": [_I32, _I32, _I32, _I32],
     "pl_sample": [_PTR, _I64, _I32, _I32, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR],
 }
 
@@ -67,6 +70,8 @@ def library() -> ctypes.CDLL:
             fn.argtypes = argtypes
             fn.restype = _I32
         lib.pl_device_arch.restype = _I32
+        lib.pl_attention_decode_scratch_floats.argtypes = [_I32, _I32, _I32, _I32]
+        lib.pl_attention_decode_scratch_floats.restype = _I64
         _lib = lib
     return _lib
 
@@ -232,6 +237,40 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
     _call("pl_attention_simt", _p(q), q.stride(0), _p(k_pool), _p(v_pool), k_pool.stride(0), k_pool.stride(1),
           page_size, n_pages, _p(table), table.shape[1], _p(pos), _p(entry), _p(out), out.stride(0), tokens,
           n_heads, n_kv, head_dim, int(window or 0), float(scale), _code(q.dtype), _p(status), _stream())
+
+
+def attention_decode_supports(head_dim: int, group: int, page_size: int, dtype: torch.dtype) -> bool:
+    """Whether the tensor-core decode kernel takes this shape."""
+    return bool(library().pl_attention_decode_supports(head_dim, group, page_size, DTYPE_CODE.get(dtype, -1)))
+
+
+def attention_decode_scratch_floats(n_tokens: int, n_heads: int, head_dim: int, n_splits: int) -> int:
+    return int(library().pl_attention_decode_scratch_floats(n_tokens, n_heads, head_dim, n_splits))
+
+
+def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,
+                     pos: torch.Tensor, entry: torch.Tensor, out: torch.Tensor, page_size: int, window: int | None,
+                     scale: float, n_splits: int, scratch: torch.Tensor | None,
+                     status: torch.Tensor | None = None) -> None:
+    """bf16 attention of single decode tokens, split over the keys `n_splits` ways;
+    shapes as attention_simt. `scratch`: fp32, attention_decode_scratch_floats long."""
+    _dev(q, k_pool, v_pool, table, pos, entry, out, scratch, status)
+    tokens, n_heads, head_dim = q.shape
+    n_pages, n_kv = k_pool.shape[0], k_pool.shape[1]
+    assert q.dtype == torch.bfloat16 == out.dtype == k_pool.dtype == v_pool.dtype
+    assert q.stride(2) == 1 and q.stride(1) == head_dim and out.stride(2) == 1 and out.stride(1) == head_dim
+    assert out.shape == q.shape
+    assert k_pool.shape == (n_pages, n_kv, page_size, head_dim) == v_pool.shape
+    assert k_pool.stride() == v_pool.stride() and k_pool.stride(3) == 1 and k_pool.stride(2) == head_dim
+    assert pos.dtype == torch.int32 and entry.dtype == torch.int32 and table.dtype == torch.int32
+    assert table.dim() == 2 and table.is_contiguous() and pos.numel() == tokens == entry.numel()
+    if n_splits > 1:
+        assert scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous()
+        assert scratch.numel() >= attention_decode_scratch_floats(tokens, n_heads, head_dim, n_splits)
+    _call("pl_attention_decode", _p(q), q.stride(0), _p(k_pool), _p(v_pool), k_pool.stride(0), k_pool.stride(1),
+          page_size, n_pages, _p(table), table.shape[1], _p(pos), _p(entry), _p(out), out.stride(0), tokens,
+          n_heads, n_kv, head_dim, int(window or 0), float(scale), int(n_splits), _p(scratch), _p(status),
+          _stream())
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor | None,

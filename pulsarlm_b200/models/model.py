@@ -25,7 +25,9 @@ class StepBatch:
     block-table rows of cache group g for this step's entries. slots: int32
     [entries], each entry's state slot. want_rows: int32 [R], indices into the T
     tokens whose logits are wanted (None: none). status: int32 [1] that kernels
-    OR error bits into. The host_* fields repeat sizes for kernels' launchers.
+    OR error bits into. Entries of a single token come first: the leading `n_decode`
+    tokens are each the one token of their entry. The host_* fields repeat sizes
+    for kernels' launchers.
     """
 
     tokens: torch.Tensor
@@ -37,6 +39,7 @@ class StepBatch:
     status: torch.Tensor
     n_tokens: int
     n_entries: int
+    n_decode: int = 0
     host_query_lens: list[int] = dataclasses.field(default_factory=list)
     host_context_lens: list[int] = dataclasses.field(default_factory=list)
     extras: dict = dataclasses.field(default_factory=dict)

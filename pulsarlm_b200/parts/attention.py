@@ -25,6 +25,21 @@ class KVBinding:
     page_size: int
 
 
+_SM_COUNT: dict = {}
+
+
+def decode_splits(n_ctas: int, max_context: int, device: torch.device) -> int:
+    """Ways to split each request's keys so that about two CTAs per SM run: as many
+    as fit, but no split shorter than eight 16-key tiles."""
+    if device not in _SM_COUNT:
+        _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    target = 2 * _SM_COUNT[device]
+    if n_ctas >= target:
+        return 1
+    tiles = -(-max_context // 16)
+    return max(1, min(target // n_ctas, tiles // 8))
+
+
 @register_part("mixer", "attention")
 class Attention(Part):
     """q, k, v projections (bias-free), position encoding on q and k, causal
@@ -56,6 +71,7 @@ class Attention(Part):
         self.qkv: torch.Tensor | None = None
         self.o: torch.Tensor | None = None
         self.cache: KVBinding | None = None
+        self._decode_kernel: bool | None = None
 
     @classmethod
     def tensor_needs(cls, spec: PartSpec) -> dict[str, TensorNeed]:
@@ -100,6 +116,36 @@ class Attention(Part):
             ops.rope_kv_write(q, None, None, batch.pos, batch.entry, table, None, None, cache.page_size, inv_freq,
                               rotary, batch.status)
         out = torch.empty((tokens, nh, hd), dtype=h.dtype, device=h.device)
-        ops.attention_simt(q, cache.k_pool, cache.v_pool, table, batch.pos, batch.entry, out, cache.page_size,
-                           self.window, self.scale, batch.status)
+        self.attend(q, out, table, batch)
         return linear(out.view(tokens, nh * hd), self.o)
+
+    def attend(self, q: torch.Tensor, out: torch.Tensor, table: torch.Tensor, batch) -> None:
+        """out = attention of q over the cache. The batch's leading `n_decode` tokens
+        are single tokens of their requests: in bfloat16 they go to the split-key
+        tensor-core kernel when it takes the shape; everything else (prompt
+        portions, float32, unusual shapes) goes to the CUDA-core kernel."""
+        cache = self.cache
+        tokens = q.shape[0]
+        n_decode = 0
+        if self._decode_kernel is None:
+            self._decode_kernel = ops.attention_decode_supports(
+                self.head_dim, self.n_heads // self.n_kv, cache.page_size, q.dtype)
+        if self._decode_kernel:
+            n_decode = min(int(getattr(batch, "n_decode", 0)), tokens)
+        if n_decode > 0:
+            max_context = batch.extras.get("max_context") or max(batch.host_context_lens[:n_decode])
+            if self.window:
+                max_context = min(max_context, self.window + 16)
+            splits = decode_splits(n_decode * self.n_kv, max_context, q.device)
+            scratch = None
+            if splits > 1:
+                scratch = torch.empty(ops.attention_decode_scratch_floats(n_decode, self.n_heads, self.head_dim,
+                                                                          splits),
+                                      dtype=torch.float32, device=q.device)
+            ops.attention_decode(q[:n_decode], cache.k_pool, cache.v_pool, table, batch.pos[:n_decode],
+                                 batch.entry[:n_decode], out[:n_decode], cache.page_size, self.window, self.scale,
+                                 splits, scratch, batch.status)
+        if n_decode < tokens:
+            ops.attention_simt(q[n_decode:], cache.k_pool, cache.v_pool, table, batch.pos[n_decode:],
+                               batch.entry[n_decode:], out[n_decode:], cache.page_size, self.window, self.scale,
+                               batch.status)

@@ -1,0 +1,437 @@
+"""Each CUDA kernel alone against a plain torch reference, at sizes other than the
+engine's tests use: widths and vocabularies that are no power of two, head sizes
+in steps of 16, any number of heads and groups, scattered pages. Where random
+inputs would hide a fault (one far key among hundreds, a window's edge, a page's
+edge) the inputs are built so that it shows."""
+
+import math
+
+import pytest
+import torch
+
+import plain_llama
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+TOL = {torch.float32: 1e-5, torch.bfloat16: 2e-2}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from pulsarlm_b200.kernels import ops as module
+
+    module.require_device()
+    return module
+
+
+def rel(got, want):
+    return float((got.double().cpu() - want.double().cpu()).abs().max() / want.double().abs().max().clamp_min(1e-30))
+
+
+# ----------------------------------------------------------------------------- elementwise
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden,vocab", [(100, 77), (4097, 513)])
+def test_embed(ops, dtype, hidden, vocab):
+    table = torch.randn(vocab, hidden, device=DEV).to(dtype)
+    tokens = torch.randint(0, vocab, (37,), device=DEV, dtype=torch.int32)
+    out = torch.empty(37, hidden, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.embed(table, tokens, out, status)
+    assert torch.equal(out, table[tokens.long()].float()) and int(status) == 0
+    tokens[5] = vocab
+    ops.embed(table, tokens, out, status)
+    assert int(status) == 1 and bool((out[5] == 0).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden", [64, 100, 4097])
+@pytest.mark.parametrize("weight_dtype", ["same", "float32"])
+def test_add_rmsnorm(ops, dtype, hidden, weight_dtype):
+    eps = 1e-5
+    x = torch.randn(19, hidden, device=DEV) * 3
+    x[4] = 0  # an all-zero row must give zeros, not NaN
+    delta = torch.randn(19, hidden, device=DEV).to(dtype)
+    delta[4] = 0
+    w = (1 + 0.1 * torch.randn(hidden, device=DEV)).to(dtype if weight_dtype == "same" else torch.float32)
+    want_x = x + delta.float()
+    want = plain_llama.rms_norm(want_x.double(), w.double(), eps)
+    x1 = x.clone()
+    out = torch.empty(19, hidden, device=DEV, dtype=dtype)
+    ops.add_rmsnorm(x1, delta, w, eps, out)
+    assert torch.equal(x1, want_x)  # the residual sum is exact fp32
+    assert rel(out, want) < TOL[dtype] and bool(torch.isfinite(out.float()).all())
+    # no delta: x untouched
+    x2 = x.clone()
+    ops.add_rmsnorm(x2, None, w, eps, out)
+    assert torch.equal(x2, x) and rel(out, plain_llama.rms_norm(x.double(), w.double(), eps)) < TOL[dtype]
+    # selected rows: x untouched, rows gathered
+    rows = torch.tensor([18, 0, 7], device=DEV, dtype=torch.int32)
+    x3 = x.clone()
+    picked = torch.empty(3, hidden, device=DEV, dtype=dtype)
+    ops.add_rmsnorm(x3, delta, w, eps, picked, rows)
+    assert torch.equal(x3, x) and rel(picked, want[rows.long()]) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width", [172, 1000])
+def test_swiglu(ops, dtype, width):
+    gate_up = (torch.randn(23, 2 * width, device=DEV) * 4).to(dtype)
+    out = torch.empty(23, width, device=DEV, dtype=dtype)
+    ops.swiglu(gate_up, out)
+    g, u = gate_up[:, :width].double(), gate_up[:, width:].double()
+    assert rel(out, g * torch.sigmoid(g) * u) < TOL[dtype]
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 7, 5), (3, 100, 172), (65, 130, 257), (200, 64, 64)])
+def test_gemm_f32_and_its_row_independence(ops, m, n, k):
+    a = torch.randn(m, k, device=DEV)
+    w = torch.randn(n, k, device=DEV)
+    out = torch.empty(m, n, device=DEV)
+    ops.gemm_f32(a, w, out)
+    assert rel(out, a.double() @ w.double().T) < 1e-5
+    one = torch.empty(1, n, device=DEV)
+    ops.gemm_f32(a[m // 2 : m // 2 + 1].contiguous(), w, one)
+    assert torch.equal(one[0], out[m // 2])  # a row's bits do not depend on the batch
+    acc = out.clone()
+    ops.gemm_f32(a, w, acc, accumulate=True)
+    assert torch.allclose(acc, 2 * out)
+
+
+def test_gemm_f32_is_true_fp32(ops):
+    # 1 + 2^-12 squared needs 24 bits of product mantissa: a tf32 or bf16 product
+    # would round the inputs to 1.
+    a = torch.full((4, 8), 1 + 2 ** -12, device=DEV)
+    w = torch.full((4, 8), 1 + 2 ** -12, device=DEV)
+    out = torch.empty(4, 4, device=DEV)
+    ops.gemm_f32(a, w, out)
+    assert abs(float(out[0, 0]) - 8 * (1 + 2 ** -12) ** 2) < 1e-5
+    assert abs(float(out[0, 0]) - 8.0) > 3e-3
+
+
+# ----------------------------------------------------------------------------- cache helpers
+
+def make_pools(n_pages, n_kv, page, hd, dtype, fill=None):
+    pool = torch.zeros(n_pages, 2, n_kv, page, hd, device=DEV, dtype=dtype)
+    if fill is not None:
+        pool.normal_(0, fill)
+    return pool[:, 0], pool[:, 1]
+
+
+def dense_from_pool(pool, table_row, length, page):
+    """[length, n_kv, hd] gathered through a block-table row."""
+    rows = []
+    for j in range(length):
+        rows.append(pool[table_row[j // page], :, j % page, :])
+    return torch.stack(rows)
+
+
+def scattered_tables(n_requests, pages_each, n_pages, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(n_pages, generator=g)[: n_requests * pages_each]
+    return perm.view(n_requests, pages_each).to(torch.int32)
+
+
+# ----------------------------------------------------------------------------- rope + kv write
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,rotary,page", [(4, 4, 16, 16, 16), (6, 2, 48, 48, 32), (5, 1, 80, 40, 8),
+                                                   (8, 2, 128, 128, 16)])
+def test_rope_kv_write(ops, dtype, nh, nkv, hd, rotary, page):
+    tokens = 29
+    llama3 = {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64.0}
+    inv_freq = plain_llama.rope_inverse_frequency(500000.0, hd, llama3)[: rotary // 2]
+    if rotary != hd:
+        inv_freq = plain_llama.rope_inverse_frequency(10000.0, rotary, None)
+    width = (nh + 2 * nkv) * hd
+    qkv = torch.randn(tokens, width, device=DEV).to(dtype)
+    q = qkv[:, : nh * hd].view(tokens, nh, hd)
+    k = qkv[:, nh * hd : (nh + nkv) * hd].view(tokens, nkv, hd)
+    v = qkv[:, (nh + nkv) * hd :].view(tokens, nkv, hd)
+    q0, k0, v0 = q.clone(), k.clone(), v.clone()
+    # two requests: 11 tokens from position 100 (crossing pages), 18 from position 131000
+    starts, counts = [100, 131000], [11, 18]
+    pos = torch.cat([torch.arange(s, s + c) for s, c in zip(starts, counts)]).to(torch.int32).to(DEV)
+    entry = torch.cat([torch.full((c,), i) for i, c in enumerate(counts)]).to(torch.int32).to(DEV)
+    pages_each = (131000 + 18) // page + 1
+    table = torch.full((2, pages_each), -1, dtype=torch.int32)
+    used = iter(torch.randperm(40, generator=torch.Generator().manual_seed(1)).tolist())
+    for i, (s, c) in enumerate(zip(starts, counts)):
+        for pg in range(s // page, (s + c - 1) // page + 1):
+            table[i, pg] = next(used)
+    kp, vp = make_pools(40, nkv, page, hd, dtype)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.rope_kv_write(q, k, v, pos, entry, table.to(DEV), kp, vp, page, inv_freq.to(DEV), rotary, status)
+    assert int(status) == 0
+
+    def rotate(x):
+        x = x.double().cpu()
+        rot = plain_llama.rope_rotate(x[..., :rotary], pos.cpu().long(), inv_freq)
+        return torch.cat([rot, x[..., rotary:]], dim=-1)
+
+    tol = 2e-6 if dtype == torch.float32 else 1e-2
+    assert rel(q, rotate(q0)) < tol
+    want_k = rotate(k0)
+    for t in range(tokens):
+        p = int(pos[t])
+        page_id = int(table[int(entry[t]), p // page])
+        assert rel(kp[page_id, :, p % page, :], want_k[t]) < tol, t
+        assert torch.equal(vp[page_id, :, p % page, :], v0[t]), t
+    if rotary < hd:  # dims past the rotary width pass through bit for bit
+        assert torch.equal(q[..., rotary:], q0[..., rotary:])
+    # nothing else was written
+    written = torch.zeros(40, page, dtype=torch.bool)
+    for t in range(tokens):
+        written[int(table[int(entry[t]), int(pos[t]) // page]), int(pos[t]) % page] = True
+    assert bool((kp.float().abs().sum(dim=(1, 3)).cpu()[~written] == 0).all())
+
+
+def test_rope_kv_write_flags_a_missing_page(ops):
+    q = torch.randn(2, 2, 16, device=DEV)
+    k, v = torch.randn(2, 2, 16, device=DEV), torch.randn(2, 2, 16, device=DEV)
+    qkv = torch.cat([q, k, v], dim=1).contiguous()
+    kp, vp = make_pools(4, 2, 16, 16, torch.float32)
+    table = torch.tensor([[0, -1]], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([3, 16], dtype=torch.int32, device=DEV)
+    entry = torch.zeros(2, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.rope_kv_write(qkv[:, 0:2], qkv[:, 2:4], qkv[:, 4:6], pos, entry, table, kp, vp, 16, None, 0, status)
+    assert int(status) == 2
+
+
+# ----------------------------------------------------------------------------- attention
+
+def reference_attention(q, kp, vp, table, pos, entry, page, window, scale):
+    """Plain attention of each query over its request's keys 0..pos (dense gather)."""
+    out = torch.empty(q.shape, dtype=torch.float64)
+    qd, kd, vd = q.double().cpu(), kp.double().cpu(), vp.double().cpu()
+    group = q.shape[1] // kp.shape[1]
+    for t in range(q.shape[0]):
+        p = int(pos[t])
+        first = max(0, p - window + 1) if window else 0
+        row = table[int(entry[t])].tolist()
+        keys = torch.stack([kd[row[j // page], :, j % page, :] for j in range(first, p + 1)])  # [n, nkv, hd]
+        vals = torch.stack([vd[row[j // page], :, j % page, :] for j in range(first, p + 1)])
+        for h in range(q.shape[1]):
+            s = (keys[:, h // group, :] @ qd[t, h]) * scale
+            out[t, h] = torch.softmax(s, 0) @ vals[:, h // group, :]
+    return out
+
+
+ATTENTION_SHAPES = [
+    # nh, nkv, hd, page
+    (4, 4, 16, 16),
+    (6, 2, 32, 32),
+    (3, 1, 48, 8),
+    (8, 2, 64, 16),
+    (5, 5, 80, 16),
+    (8, 1, 128, 16),
+    (4, 2, 256, 32),
+    (14, 2, 128, 64),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,page", ATTENTION_SHAPES)
+@pytest.mark.parametrize("window", [None, 21])
+def test_attention_simt(ops, dtype, nh, nkv, hd, page, window):
+    lengths = [1, 37, 130]
+    pages_each = -(-max(lengths) // page)
+    table = scattered_tables(len(lengths), pages_each, 3 * pages_each + 5, seed=hd)
+    kp, vp = make_pools(3 * pages_each + 5, nkv, page, hd, dtype, fill=1.0)
+    # queries: the last min(len, 9) positions of each request (a portion), one query for the first
+    pos, entry = [], []
+    for i, n in enumerate(lengths):
+        for p in range(max(0, n - 9), n):
+            pos.append(p)
+            entry.append(i)
+    q = torch.randn(len(pos), nh, hd, device=DEV).to(dtype)
+    out = torch.empty_like(q)
+    pos_t = torch.tensor(pos, dtype=torch.int32, device=DEV)
+    entry_t = torch.tensor(entry, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    ops.attention_simt(q, kp, vp, table.to(DEV), pos_t, entry_t, out, page, window, scale, status)
+    want = reference_attention(q, kp, vp, table, pos, entry, page, window, scale)
+    assert int(status) == 0 and rel(out, want) < (1e-5 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page", [(8, 2, 64, 16), (8, 1, 128, 16), (32, 8, 128, 16), (16, 1, 64, 32),
+                                            (6, 2, 128, 64), (4, 4, 64, 16)])
+@pytest.mark.parametrize("splits", [1, 2, 5])
+@pytest.mark.parametrize("window", [None, 100])
+def test_attention_decode(ops, nh, nkv, hd, page, splits, window):
+    dtype = torch.bfloat16
+    assert ops.attention_decode_supports(hd, nh // nkv, page, dtype)
+    lengths = [1, 15, 16, 17, 250, 700]
+    pages_each = -(-max(lengths) // page)
+    n_pages = len(lengths) * pages_each + 3
+    table = scattered_tables(len(lengths), pages_each, n_pages, seed=hd + page)
+    kp, vp = make_pools(n_pages, nkv, page, hd, dtype, fill=1.0)
+    pos = [n - 1 for n in lengths]
+    entry = list(range(len(lengths)))
+    q = torch.randn(len(pos), nh, hd, device=DEV).to(dtype)
+    out = torch.full_like(q, float("nan"))
+    pos_t = torch.tensor(pos, dtype=torch.int32, device=DEV)
+    entry_t = torch.tensor(entry, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    scratch = torch.full((ops.attention_decode_scratch_floats(len(pos), nh, hd, splits),), float("nan"),
+                         device=DEV) if splits > 1 else None
+    ops.attention_decode(q, kp, vp, table.to(DEV), pos_t, entry_t, out, page, window, scale, splits, scratch, status)
+    want = reference_attention(q, kp, vp, table, pos, entry, page, window, scale)
+    assert int(status) == 0 and rel(out, want) < 1e-2
+
+
+def test_attention_decode_refuses_what_it_cannot_do(ops):
+    assert not ops.attention_decode_supports(80, 1, 16, torch.bfloat16)
+    assert not ops.attention_decode_supports(128, 32, 16, torch.bfloat16)
+    assert not ops.attention_decode_supports(128, 4, 8, torch.bfloat16)
+    assert not ops.attention_decode_supports(128, 4, 16, torch.float32)
+    q = torch.randn(1, 2, 80, device=DEV).to(torch.bfloat16)
+    kp, vp = make_pools(2, 2, 16, 80, torch.bfloat16)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(ops.KernelError) as error:
+        ops.attention_decode(q, kp, vp, torch.zeros(1, 1, dtype=torch.int32, device=DEV), z, z, torch.empty_like(q),
+                             16, None, 1.0, 1, None)
+    assert "head_dim=80" in str(error.value)
+
+
+@pytest.mark.parametrize("kernel", ["simt_f32", "simt_bf16", "decode"])
+@pytest.mark.parametrize("far_key", [0, 15, 16, 511, 512, 1203])
+def test_one_far_key_among_many_is_found(ops, kernel, far_key):
+    """One key (at a page's first slot, last slot, far back) matches the query
+    strongly; the output must be that key's value. A kernel that skips a tile, a
+    page or a split loses it."""
+    dtype = torch.float32 if kernel == "simt_f32" else torch.bfloat16
+    nh, nkv, hd, page, n = 4, 2, 64, 16, 1204
+    pages_each = -(-n // page)
+    table = scattered_tables(1, pages_each, pages_each + 7, seed=3)
+    kp, vp = make_pools(pages_each + 7, nkv, page, hd, dtype, fill=0.3)
+    q = torch.randn(1, nh, hd, device=DEV).to(dtype)
+    page_id = int(table[0, far_key // page])
+    for kvh in range(nkv):
+        # the key is the mean of the group's queries, scaled up: its score dominates
+        direction = q[0, kvh * 2 : kvh * 2 + 2].float().mean(0)
+        kp[page_id, kvh, far_key % page] = (direction * 12).to(dtype)
+    vp[page_id, :, far_key % page] = 5.0
+    out = torch.empty_like(q)
+    pos_t = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+    entry_t = torch.zeros(1, dtype=torch.int32, device=DEV)
+    if kernel == "decode":
+        scratch = torch.empty(ops.attention_decode_scratch_floats(1, nh, hd, 7), device=DEV)
+        ops.attention_decode(q, kp, vp, table.to(DEV), pos_t, entry_t, out, page, None, 1.0, 7, scratch)
+    else:
+        ops.attention_simt(q, kp, vp, table.to(DEV), pos_t, entry_t, out, page, None, 1.0)
+    want = reference_attention(q, kp, vp, table, [n - 1], [0], page, None, 1.0)
+    assert float(want.min()) > 4.0  # the construction works: the far key takes nearly all the weight
+    assert rel(out, want) < (1e-5 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("kernel", ["simt_f32", "simt_bf16", "decode"])
+def test_window_edges(ops, kernel):
+    """A loud key just inside the window must be read, the same key just outside
+    must not."""
+    dtype = torch.float32 if kernel == "simt_f32" else torch.bfloat16
+    nh, nkv, hd, page, n, window = 2, 1, 64, 16, 300, 100
+    pages_each = -(-n // page)
+    table = scattered_tables(1, pages_each, pages_each + 2, seed=5)
+    q = torch.randn(1, nh, hd, device=DEV).to(dtype)
+    for loud, inside in ((n - window, True), (n - window - 1, False)):
+        kp, vp = make_pools(pages_each + 2, nkv, page, hd, dtype, fill=0.3)
+        page_id = int(table[0, loud // page])
+        kp[page_id, 0, loud % page] = (q[0].float().mean(0) * 12).to(dtype)
+        vp[page_id, 0, loud % page] = 5.0
+        out = torch.empty_like(q)
+        pos_t = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+        entry_t = torch.zeros(1, dtype=torch.int32, device=DEV)
+        if kernel == "decode":
+            scratch = torch.empty(ops.attention_decode_scratch_floats(1, nh, hd, 3), device=DEV)
+            ops.attention_decode(q, kp, vp, table.to(DEV), pos_t, entry_t, out, page, window, 1.0, 3, scratch)
+        else:
+            ops.attention_simt(q, kp, vp, table.to(DEV), pos_t, entry_t, out, page, window, 1.0)
+        want = reference_attention(q, kp, vp, table, [n - 1], [0], page, window, 1.0)
+        assert (float(want.min()) > 4.0) == inside
+        assert rel(out, want) < (1e-5 if dtype == torch.float32 else 1e-2)
+
+
+def test_pages_before_the_window_are_never_read(ops):
+    """Block-table entries before the window are -1 (given back): reading them would
+    raise the status flag."""
+    for kernel in ("simt", "decode"):
+        nh, nkv, hd, page, n, window = 2, 1, 64, 16, 200, 40
+        pages_each = -(-n // page)
+        table = scattered_tables(1, pages_each, pages_each, seed=1)
+        table[0, : (n - window) // page] = -1
+        kp, vp = make_pools(pages_each, nkv, page, hd, torch.bfloat16, fill=1.0)
+        q = torch.randn(1, nh, hd, device=DEV).to(torch.bfloat16)
+        out = torch.empty_like(q)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        pos_t = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+        entry_t = torch.zeros(1, dtype=torch.int32, device=DEV)
+        if kernel == "decode":
+            ops.attention_decode(q, kp, vp, table.to(DEV), pos_t, entry_t, out, page, window, 0.125, 1, None, status)
+        else:
+            ops.attention_simt(q, kp, vp, table.to(DEV), pos_t, entry_t, out, page, window, 0.125, status)
+        assert int(status) == 0, kernel
+
+
+# ----------------------------------------------------------------------------- sampling
+
+def run_sample(ops, logits, temperature, top_k=None, top_p=None, seeds=None, counts=None):
+    rows = logits.shape[0]
+    t = torch.tensor(temperature, dtype=torch.float32, device=DEV).expand(rows).contiguous()
+    k = None if top_k is None else torch.tensor(top_k, dtype=torch.int32, device=DEV).expand(rows).contiguous()
+    p = None if top_p is None else torch.tensor(top_p, dtype=torch.float32, device=DEV).expand(rows).contiguous()
+    seeds = torch.arange(rows) if seeds is None else torch.as_tensor(seeds)
+    counts = torch.zeros(rows, dtype=torch.int64) if counts is None else torch.as_tensor(counts)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.sample(logits, t, k, p, seeds.to(torch.int64).to(DEV), counts.to(torch.int64).to(DEV), out)
+    return out.cpu()
+
+
+def test_sampling_argmax_and_ties(ops):
+    logits = torch.randn(9, 1000, device=DEV)
+    logits[3, 17] = logits[3, 900] = 50.0  # a tie goes to the lower index
+    got = run_sample(ops, logits, 0.0)
+    want = logits.argmax(dim=1).cpu()
+    want[3] = 17
+    assert got.tolist() == want.tolist()
+    assert run_sample(ops, logits, 1.0, top_k=1).tolist() == want.tolist()  # top_k = 1 is the argmax
+
+
+def test_sampling_frequencies_match_the_distribution(ops):
+    probabilities = torch.tensor([0.5, 0.25, 0.15, 0.07, 0.03])
+    logits = torch.log(probabilities).repeat(6000, 1).to(DEV) * 0.7  # then T = 0.7 restores them
+    for top_k, top_p in ((None, None), (2, None), (None, 0.8), (3, 0.6)):
+        got = run_sample(ops, logits.contiguous(), 0.7, top_k, top_p)
+        freq = torch.bincount(got, minlength=5).double() / 6000
+        want = plain_llama.sampling_distribution(torch.log(probabilities) * 0.7, 0.7, top_k or 0, top_p or 1.0)
+        assert (freq - want).abs().max() < 0.03, (top_k, top_p, freq, want)
+        assert bool((freq[want == 0] == 0).all())
+
+
+def test_sampling_is_keyed_by_seed_and_count_not_by_neighbours(ops):
+    logits = torch.randn(6, 50000, device=DEV)
+    a = run_sample(ops, logits, 1.0, seeds=[7, 7, 8, 9, 10, 11], counts=[0, 0, 0, 0, 0, 0])
+    same_logits = logits.clone()
+    same_logits[1] = logits[0]
+    b = run_sample(ops, same_logits, 1.0, seeds=[7, 7, 8, 9, 10, 11], counts=[0, 0, 0, 0, 0, 0])
+    assert b[0] == b[1] == a[0]  # same seed, count and logits: same token
+    alone = run_sample(ops, logits[2:3].contiguous(), 1.0, seeds=[8], counts=[0])
+    assert alone[0] == a[2]  # a row's draw does not depend on its neighbours
+    later = run_sample(ops, logits, 1.0, seeds=[7, 7, 8, 9, 10, 11], counts=[1, 1, 1, 1, 1, 1])
+    assert later.tolist() != a.tolist()  # another draw count: other noise
+    mixed = run_sample(ops, logits, torch.tensor([0.0, 1.0, 0.0, 1.0, 0.0, 1.0]).tolist(),
+                       seeds=[7, 7, 8, 9, 10, 11])
+    assert mixed[0] == logits[0].argmax().cpu() and mixed[3] == a[3]  # greedy rows beside drawing rows
+
+
+def test_sampling_never_picks_a_hopeless_token_in_a_wide_vocabulary(ops):
+    vocab = 262144 + 3
+    logits = torch.full((64, vocab), -1e4, device=DEV)
+    logits[:, 1000:1010] = 0.0
+    got = run_sample(ops, logits, 1.0)
+    assert bool(((got >= 1000) & (got < 1010)).all())
+    assert len(set(got.tolist())) > 3
