@@ -195,7 +195,7 @@ def run_ours(args) -> dict:
     torch.manual_seed(0)
     device = "cuda:0"
     max_batch = max(64, batch)
-    tokens_room = max_batch * (PROMPT_LEN + args.steps + args.warmup + 64) + 4 * PROMPT_LEN
+    tokens_room = max_batch * (PROMPT_LEN + 2 * (args.steps + args.warmup) + 128) + 4 * PROMPT_LEN
     n_pages = -(-tokens_room // PAGE_SIZE)
     t0 = time.time()
     engine = Engine(cfg, dtype="bfloat16", device=device, n_pages=n_pages, page_size=PAGE_SIZE,
@@ -206,10 +206,16 @@ def run_ours(args) -> dict:
     gen = torch.Generator().manual_seed(1)
     setup_s = time.time() - t0
 
+    phases = set(args.phases.split(","))
+    prefill = e2e = None
+    points: dict = {}
+    ms_per_step, launches, achieved, step_bytes = None, 0, None, None
+    clocks = ClockSampler()
+
     # ---- prefill: one 2,048-token prompt in one step, logits of the last token.
-    prompt = torch.randint(0, vocab, (PROMPT_LEN,), generator=gen).tolist()
-    times = []
-    with ClockSampler() as prefill_clocks:
+    if "prefill" in phases:
+        prompt = torch.randint(0, vocab, (PROMPT_LEN,), generator=gen).tolist()
+        times = []
         for i in range(3 + 5):
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
@@ -219,59 +225,62 @@ def run_ours(args) -> dict:
             engine.runner.end(("prefill", i))
             if i >= 3:
                 times.append(start.elapsed_time(end))
-    prefill_ms = statistics.median(times)
-    flops = prefill_flops(cfg, PROMPT_LEN)
-    prefill = {"value": PROMPT_LEN / (prefill_ms / 1e3), "tokens": PROMPT_LEN, "ms": prefill_ms,
-               "frac": flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), "unit": "tok/s",
-               "peak_tflops": pk["bf16_tflops"]}
+        prefill_ms = statistics.median(times)
+        flops = prefill_flops(cfg, PROMPT_LEN)
+        prefill = {"value": PROMPT_LEN / (prefill_ms / 1e3), "tokens": PROMPT_LEN, "ms": prefill_ms,
+                   "frac": flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), "unit": "tok/s",
+                   "peak_tflops": pk["bf16_tflops"]}
 
     # ---- end to end through the public API: batch prompts in, tokens out per step.
-    prompts = [torch.randint(0, vocab, (PROMPT_LEN,), generator=gen).tolist() for _ in range(batch)]
-    sampling = SamplingParams(temperature=0.0)
-    total_new = args.warmup + args.steps + 1
-    requests = [engine.submit(p, sampling=sampling, max_tokens=total_new, ignore_eos=True) for p in prompts]
-    while any(len(r.output) < 1 for r in requests):
-        engine.step()  # prefill (untimed)
-    for _ in range(args.warmup):
-        engine.step()
-    torch.cuda.synchronize()
-    with ClockSampler() as e2e_clocks:
+    if "e2e" in phases:
+        prompts = [torch.randint(0, vocab, (PROMPT_LEN,), generator=gen).tolist() for _ in range(batch)]
+        sampling = SamplingParams(temperature=0.0)
+        # Requests finish their prompts one step apart, so the first is `batch` tokens
+        # ahead of the last: give all of them room to still be decoding at the end.
+        total_new = args.warmup + args.steps + batch + 8
+        requests = [engine.submit(p, sampling=sampling, max_tokens=total_new, ignore_eos=True) for p in prompts]
+        while any(len(r.output) < 1 for r in requests):
+            engine.step()  # prefill (untimed)
+        for _ in range(args.warmup):
+            engine.step()
+        torch.cuda.synchronize()
         t_start = time.perf_counter()
         for _ in range(args.steps):
             engine.step()
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t_start
-    assert all(len(r.output) == args.warmup + args.steps + 1 for r in requests)
-    graph = next(g for (n, _), g in engine.runner._graphs.items() if n == batch)
-    e2e = {"value": batch * args.steps / e2e_s, "unit": "tok/s", "ms_per_step": e2e_s / args.steps * 1e3,
-           "h2d_bytes_per_step": graph.layout.nbytes, "d2h_bytes_per_step": 4 * batch}
-    for r in requests:
-        r.cancel()
-    engine.step()
+        assert all(not r.finished and len(r.output) >= args.warmup + args.steps + 1 for r in requests)
+        graph = next(g for (n, _), g in engine.runner._graphs.items() if n == batch)
+        e2e = {"value": batch * args.steps / e2e_s, "unit": "tok/s", "ms_per_step": e2e_s / args.steps * 1e3,
+               "h2d_bytes_per_step": graph.layout.nbytes, "d2h_bytes_per_step": 4 * batch}
+        for r in requests:
+            r.cancel()
+        engine.step()
 
     # ---- device-timed decode at the headline batch, same context.
-    ids = fill_cache(engine, batch, PROMPT_LEN + args.warmup, "main")
-    with ClockSampler() as clocks:
-        ms_per_step, launches = time_decode(engine, ids, args.steps, args.warmup, vocab)
-    mid_context = PROMPT_LEN + 2 * args.warmup + args.steps / 2
-    step_bytes = weight_bytes(cfg) + batch * mid_context * kv_bytes_per_token(cfg)
-    achieved = step_bytes / (ms_per_step / 1e3) / 1e9
-    for rid in ids:
-        engine.cache.close(rid)
-
-    # ---- other batch sizes.
-    points = {}
-    for b in (1, 64):
-        ids = fill_cache(engine, b, PROMPT_LEN, f"b{b}")
-        ms, _ = time_decode(engine, ids, max(8, args.steps // 2), args.warmup, vocab)
-        points[f"decode_b{b}"] = b / (ms / 1e3)
+    if "decode" in phases:
+        ids = fill_cache(engine, batch, PROMPT_LEN + args.warmup, "main")
+        with clocks:
+            ms_per_step, launches = time_decode(engine, ids, args.steps, args.warmup, vocab)
+        mid_context = PROMPT_LEN + 2 * args.warmup + args.steps / 2
+        step_bytes = weight_bytes(cfg) + batch * mid_context * kv_bytes_per_token(cfg)
+        achieved = step_bytes / (ms_per_step / 1e3) / 1e9
         for rid in ids:
             engine.cache.close(rid)
+
+    # ---- other batch sizes.
+    if "points" in phases:
+        for b in (1, 64):
+            ids = fill_cache(engine, b, PROMPT_LEN, f"b{b}")
+            ms, _ = time_decode(engine, ids, max(8, args.steps // 2), args.warmup, vocab)
+            points[f"decode_b{b}"] = b / (ms / 1e3)
+            for rid in ids:
+                engine.cache.close(rid)
 
     clock_summary = clocks.summary()
     return {
         "metric": "decode tok/s at batch 8 (Llama-3.1-8B shape, 2,048-token prompts)",
-        "value": batch / (ms_per_step / 1e3),
+        "value": batch / (ms_per_step / 1e3) if ms_per_step else None,
         "unit": "tok/s",
         "n_gpus": 1,
         "steps": args.steps,
@@ -297,7 +306,7 @@ def run_ours(args) -> dict:
         "gpu_launches": launches,
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / pk["hbm_gbs"], "bytes_per_step": step_bytes},
+                     "frac": achieved / pk["hbm_gbs"] if achieved else None, "bytes_per_step": step_bytes},
         "points": points,
         "clocks": {"sm_mhz": clock_summary["sm_mhz"], "sm_max_mhz": clock_summary["sm_max_mhz"],
                    "reasons": clock_summary["reasons"]},
@@ -313,6 +322,8 @@ def main() -> int:
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--layers", type=int, default=32, help="fewer layers than the model's 32 (named in config)")
+    p.add_argument("--phases", default="prefill,e2e,decode,points",
+                   help="which measurements to run (a profiler run wants one): prefill,e2e,decode,points")
     args = p.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

@@ -19,8 +19,13 @@ __device__ __forceinline__ void rope_sincos(int pos, double radians_per_position
     sincosf(static_cast<float>(frac * kTwoPi), &s, &c);
 }
 
-// Block t handles token t. Rotated pairs are (j, j + rotary/2) for j < rotary/2;
-// dims >= rotary pass through unchanged.
+constexpr int kHeadsPerBlock = 4;
+
+// Block (t, y) handles token t and head slots 4y .. 4y+3, where slots 0 .. n_heads-1
+// are q heads (rotated in place) and the next n_kv_heads are k heads (rotated and
+// stored with their v head). Many small blocks: a decode step has few tokens, and
+// one block per token would walk its heads one after the other. Rotated pairs are
+// (j, j + rotary/2) for j < rotary/2; dims >= rotary pass through unchanged.
 template <typename scalar_t>
 __global__ void rope_kv_write_kernel(scalar_t* __restrict__ q, const scalar_t* __restrict__ k,
                                      const scalar_t* __restrict__ v, int64_t row_stride,
@@ -43,47 +48,52 @@ __global__ void rope_kv_write_kernel(scalar_t* __restrict__ q, const scalar_t* _
     }
     __syncthreads();
 
-    scalar_t* qrow = q + t * row_stride;
-    if (inv_freq != nullptr) {
-        for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
-            const int h = idx / half, j = idx - h * half;
-            scalar_t* x = qrow + h * head_dim;
+    const int n_slots = n_heads + (k_pool != nullptr ? n_kv_heads : 0);
+    const int slot0 = blockIdx.y * kHeadsPerBlock;
+    const int slot1 = min(slot0 + kHeadsPerBlock, n_slots);
+    int page = -1;
+    if (slot1 > n_heads) {
+        page = table[static_cast<int64_t>(entry[t]) * table_width + p / page_size];
+        if (page < 0 || page >= n_pages) {
+            if (threadIdx.x == 0 && status != nullptr) {
+                atomicOr(status, 2);
+            }
+            page = -1;
+        }
+    }
+    const int pairs = head_dim - half;  // per head: `half` rotated pairs, then the unrotated dims
+    for (int idx = threadIdx.x; idx < (slot1 - slot0) * pairs; idx += blockDim.x) {
+        const int slot = slot0 + idx / pairs, j = idx % pairs;
+        if (slot < n_heads) {
+            if (inv_freq == nullptr || j >= half) {
+                continue;  // q passes through
+            }
+            scalar_t* x = q + t * row_stride + static_cast<int64_t>(slot) * head_dim;
             const float lo = pl_load(x + j), hi = pl_load(x + j + half);
             pl_store(x + j, lo * cs[j] - hi * sn[j]);
             pl_store(x + j + half, hi * cs[j] + lo * sn[j]);
-        }
-    }
-    if (k_pool == nullptr) {
-        return;
-    }
-
-    const int page = table[static_cast<int64_t>(entry[t]) * table_width + p / page_size];
-    if (page < 0 || page >= n_pages) {
-        if (threadIdx.x == 0 && status != nullptr) {
-            atomicOr(status, 2);
-        }
-        return;
-    }
-    const int slot = p % page_size;
-    const scalar_t* krow = k + t * row_stride;
-    const scalar_t* vrow = v + t * row_stride;
-    scalar_t* kdst = k_pool + page * page_stride + static_cast<int64_t>(slot) * head_dim;
-    scalar_t* vdst = v_pool + page * page_stride + static_cast<int64_t>(slot) * head_dim;
-    for (int idx = threadIdx.x; idx < n_kv_heads * head_dim; idx += blockDim.x) {
-        const int h = idx / head_dim, d = idx - h * head_dim;
-        const scalar_t* x = krow + h * head_dim;
-        float value;
-        if (inv_freq != nullptr && d < rotary) {
-            if (d < half) {
-                value = pl_load(x + d) * cs[d] - pl_load(x + d + half) * sn[d];
+        } else if (page >= 0) {
+            const int h = slot - n_heads;
+            const scalar_t* x = k + t * row_stride + static_cast<int64_t>(h) * head_dim;
+            const scalar_t* y = v + t * row_stride + static_cast<int64_t>(h) * head_dim;
+            const int64_t at = page * page_stride + h * head_stride + static_cast<int64_t>(p % page_size) * head_dim;
+            if (j < half) {
+                const float lo = pl_load(x + j), hi = pl_load(x + j + half);
+                if (inv_freq != nullptr) {
+                    pl_store(k_pool + at + j, lo * cs[j] - hi * sn[j]);
+                    pl_store(k_pool + at + j + half, hi * cs[j] + lo * sn[j]);
+                } else {
+                    k_pool[at + j] = x[j];
+                    k_pool[at + j + half] = x[j + half];
+                }
+                v_pool[at + j] = y[j];
+                v_pool[at + j + half] = y[j + half];
             } else {
-                value = pl_load(x + d) * cs[d - half] + pl_load(x + d - half) * sn[d - half];
+                const int d = j + half;  // dims rotary .. head_dim-1
+                k_pool[at + d] = x[d];
+                v_pool[at + d] = y[d];
             }
-        } else {
-            value = pl_load(x + d);
         }
-        pl_store(kdst + h * head_stride + d, value);
-        vdst[h * head_stride + d] = vrow[idx];
     }
 }
 
@@ -107,11 +117,15 @@ PL_API int pl_rope_kv_write(void* q, const void* k, const void* v, int64_t row_s
     if (n_tokens == 0) {
         return 0;
     }
-    const int threads = 128;
     const size_t smem = static_cast<size_t>(rotary) * sizeof(float);
     PL_REQUIRE(smem <= 48 * 1024, "rope_kv_write: rotary width %d is too large", rotary);
+    const int n_slots = n_heads + (k_pool != nullptr ? n_kv_heads : 0);
+    const int items = kHeadsPerBlock * (head_dim - rotary / 2);
+    const int threads = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
+    const dim3 grid(n_tokens, (n_slots + kHeadsPerBlock - 1) / kHeadsPerBlock);
+    PL_REQUIRE(grid.y <= 65535, "rope_kv_write: too many heads (%d)", n_slots);
     PL_DISPATCH_DTYPE(dtype, "rope_kv_write", {
-        rope_kv_write_kernel<scalar_t><<<n_tokens, threads, smem, stream>>>(
+        rope_kv_write_kernel<scalar_t><<<grid, threads, smem, stream>>>(
             static_cast<scalar_t*>(q), static_cast<const scalar_t*>(k), static_cast<const scalar_t*>(v), row_stride,
             pos, entry, table, table_width, static_cast<scalar_t*>(k_pool), static_cast<scalar_t*>(v_pool),
             page_stride, head_stride, page_size, n_pages, inv_freq, rotary, n_heads, n_kv_heads, head_dim, status);

@@ -1,0 +1,134 @@
+"""Generation through the Python entry point and the command line."""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_llama
+import tiny
+from harness import TinyModel
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("key", ["A", "B"])
+@pytest.mark.parametrize("graphs", [True, False])
+def test_greedy_generation_matches_the_plain_implementation(key, graphs):
+    from pulsarlm_b200 import Engine, SamplingParams
+
+    tm = TinyModel(key, "float32")
+    engine = Engine(tm.folder, dtype="float32", n_pages=24, page_size=tm.page, max_requests=4,
+                    prefill_tokens_per_step=13, cuda_graphs=graphs)
+    prompts = [tiny.random_tokens(tm.cfg, n, seed=n) for n in (5, 17, 33)]
+    got = engine.generate(prompts, SamplingParams(temperature=0.0), max_tokens=8, ignore_eos=True)
+    for prompt, tokens in zip(prompts, got):
+        assert tokens == plain_llama.greedy_generate(tm.cfg, tm.weights, prompt, 8)
+    assert engine.cache.free_pages() == 24
+    assert (engine.runner.graph_steps > 0) == graphs
+
+
+def test_greedy_generation_in_bfloat16_follows_the_plain_logits():
+    """bfloat16 may flip a near-tie, so each generated token is checked against the
+    plain logits of its own prefix: it must be the argmax or within the rounding
+    bar of it."""
+    from pulsarlm_b200 import Engine
+
+    tm = TinyModel("C", "bfloat16")
+    engine = Engine(tm.folder, dtype="bfloat16", n_pages=32, page_size=tm.page, max_requests=4)
+    prompt = tiny.random_tokens(tm.cfg, 40, seed=3)
+    out = engine.generate([prompt], max_tokens=12, ignore_eos=True)[0]
+    assert engine.runner.graph_steps > 0
+    seq = list(prompt)
+    for token in out:
+        logits = plain_llama.forward(tm.cfg, tm.weights, seq)[-1]
+        assert logits[token] >= logits.max() - 2e-2 * logits.abs().max()
+        seq.append(token)
+
+
+def test_temperature_sampling_is_seeded_and_chunking_does_not_change_it():
+    from pulsarlm_b200 import Engine, SamplingParams
+
+    tm = TinyModel("B", "float32")
+    prompts = [tiny.random_tokens(tm.cfg, n, seed=n) for n in (1, 7, 64, 100, 200)]
+    sampling = SamplingParams(temperature=0.7, seed=1234)
+
+    def run(budget, pages, graphs=True):
+        engine = Engine(tm.folder, dtype="float32", n_pages=pages, page_size=tm.page, max_requests=4,
+                        prefill_tokens_per_step=budget, cuda_graphs=graphs)
+        return engine.generate(prompts, sampling, max_tokens=10, ignore_eos=True), engine
+
+    base, _ = run(13, 64)
+    again, _ = run(13, 64)
+    assert base == again
+    other_cut, _ = run(256, 64, graphs=False)
+    assert base == other_cut  # float32 logits are cut-invariant bit for bit, so the draws are too
+    # 10 pages of 32 tokens cannot hold 140 + 240 tokens: the younger request is
+    # preempted and recomputed, and still draws the same tokens.
+    two = [prompts[3], prompts[4]]
+    roomy = Engine(tm.folder, dtype="float32", n_pages=64, page_size=tm.page, prefill_tokens_per_step=13)
+    tight = Engine(tm.folder, dtype="float32", n_pages=10, page_size=tm.page, prefill_tokens_per_step=13)
+    want = roomy.generate(two, sampling, max_tokens=40, ignore_eos=True)
+    assert tight.generate(two, sampling, max_tokens=40, ignore_eos=True) == want
+    assert tight.scheduler.preemptions > 0 and roomy.scheduler.preemptions == 0
+    assert want[0][:10] == base[3] and want[1][:10] == base[4]
+    different, _ = Engine(tm.folder, dtype="float32", n_pages=64, page_size=tm.page).generate(
+        prompts, SamplingParams(temperature=0.7, seed=99), max_tokens=10, ignore_eos=True), None
+    assert different != base
+
+
+def test_stop_ids_max_tokens_and_complete():
+    from pulsarlm_b200 import Engine, SamplingParams, complete
+
+    tm = TinyModel("A", "float32")
+    prompt = tiny.random_tokens(tm.cfg, 9, seed=1)
+    free_run = plain_llama.greedy_generate(tm.cfg, tm.weights, prompt, 8)
+    engine = Engine(tm.folder, dtype="float32", n_pages=8, page_size=tm.page, stop_ids=[free_run[3]])
+    stop_at = free_run.index(free_run[3])
+    assert engine.generate([prompt], max_tokens=8)[0] == free_run[: stop_at + 1]
+    assert engine.generate([prompt], max_tokens=8, ignore_eos=True)[0] == free_run
+    assert engine.generate([prompt], max_tokens=0)[0] == []
+    assert list(complete(engine, prompt, sampling=SamplingParams(), max_tokens=3)) == free_run[:3] or stop_at < 3
+    with pytest.raises(ValueError):
+        engine.submit([tm.cfg["vocab_size"]])
+    with pytest.raises(ValueError):
+        engine.submit([])
+    with pytest.raises(MemoryError):
+        engine.generate([tiny.random_tokens(tm.cfg, 200, seed=2)], max_tokens=1)
+
+
+def test_command_line_generate_and_random_model(tmp_path):
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(tiny.TINY_A))
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    out = subprocess.run([sys.executable, "-m", "pulsarlm_b200", "models", "random", str(tmp_path / "m"), "--config",
+                          str(cfg_path), "--seed", "3", "--dtype", "float32"], env=env, capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr
+    out = subprocess.run([sys.executable, "-m", "pulsarlm_b200", "generate", str(tmp_path / "m"), "--dtype", "float32",
+                          "--prompt_ids", "1,2,3,4", "--max_tokens", "5", "--kv_cache_gib", "0.01", "--ignore_eos"],
+                         env=env, capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr
+    record = json.loads(out.stdout.strip().splitlines()[-1])
+    assert record["prompt_ids"] == [1, 2, 3, 4] and len(record["output_ids"]) == 5
+
+    from pulsarlm_b200 import Engine
+
+    engine = Engine(str(tmp_path / "m"), dtype="float32", n_pages=8)
+    assert engine.generate([[1, 2, 3, 4]], max_tokens=5, ignore_eos=True)[0] == record["output_ids"]
+
+
+def test_a_folder_that_does_not_fit_fails_with_one_clear_error(tmp_path):
+    from pulsarlm_b200 import Engine
+    from pulsarlm_b200.weights.loader import WeightsError
+
+    w = tiny.random_weights(tiny.TINY_A, 1)
+    del w["model.layers.0.mlp.down_proj.weight"]
+    w["extra.weight"] = torch.zeros(3)
+    tiny.write_model_dir(str(tmp_path), tiny.TINY_A, w)
+    with pytest.raises(WeightsError) as error:
+        Engine(str(tmp_path), dtype="bfloat16", n_pages=4)
+    assert "down_proj" in str(error.value) and "extra.weight" in str(error.value)
