@@ -57,6 +57,7 @@ class ModelRunner:
         model.bind_caches(cache.bindings())
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._staging: torch.Tensor | None = None
+        self._tile_rows = ops.attention_prefill_tile_rows()
         self._graphs: dict = {}
         # Replaying a captured step re-runs the capture's warm-up on the same tokens,
         # which is harmless for caches written by position but not for states updated
@@ -129,6 +130,7 @@ class ModelRunner:
         pos = np.empty(n_tokens, dtype=np.int32)
         entry = np.empty(n_tokens, dtype=np.int32)
         first_row = [0] * len(entries)
+        tiles: list[tuple[int, int, int, int]] = []
         at = 0
         for place, i in enumerate(order):
             e = entries[i]
@@ -138,16 +140,21 @@ class ModelRunner:
             pos[at : at + n] = np.arange(start, start + n, dtype=np.int32)
             entry[at : at + n] = place
             first_row[i] = at
+            if n > 1:  # tiles of consecutive rows for the prompt-portion attention kernel
+                for r in range(0, n, self._tile_rows):
+                    tiles.append((at + r, min(self._tile_rows, n - r), start + r, place))
             at += n
+        tiles.sort(key=lambda t: -(t[2] + t[1]))  # the tiles with the most keys start first
         want_rows = [first_row[i] + w for i, e in enumerate(entries) for w in e.want]
         requests = [entries[i].request for i in order]
         slots = np.array([self.cache.slot(r) for r in requests], dtype=np.int32)
         tables = [self.cache.table_rows(g.index, requests) for g in self.cache.groups]
-        arrays = [tokens, pos, entry, slots, np.array(want_rows, dtype=np.int32), *tables]
+        tile_array = np.array(tiles, dtype=np.int32).reshape(len(tiles), 4)
+        arrays = [tokens, pos, entry, slots, np.array(want_rows, dtype=np.int32), tile_array, *tables]
         dev = self._stage(arrays)
         batch = StepBatch(
             tokens=dev[0], pos=dev[1], entry=dev[2],
-            tables={g.index: dev[5 + i] for i, g in enumerate(self.cache.groups)},
+            tables={g.index: dev[6 + i] for i, g in enumerate(self.cache.groups)},
             slots=dev[3],
             want_rows=dev[4] if want_rows else None,
             status=self.status,
@@ -156,6 +163,7 @@ class ModelRunner:
             n_decode=n_decode,
             host_query_lens=[len(entries[i].tokens) for i in order],
             host_context_lens=[new_lens[i] for i in order],
+            extras={"prefill_tiles": dev[5] if tiles else None},
         )
         return batch, new_lens
 

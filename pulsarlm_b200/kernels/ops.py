@@ -46,6 +46,10 @@ _SIGNATURES = {
     "pl_attention_decode": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
                             _I32, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR, _PTR],
     "pl_attention_decode_supports": [_I32, _I32, _I32, _I32],
+    "pl_attention_prefill": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _I32, _PTR, _I64,
+                             _I32, _I32, _I32, _I32, _F32, _PTR, _PTR],
+    "pl_attention_prefill_supports": [_I32, _I32, _I32],
+    "pl_attention_prefill_tile_rows": [],
     "pl_sample": [_PTR, _I64, _I32, _I32, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR],
 }
 
@@ -271,6 +275,35 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
           page_size, n_pages, _p(table), table.shape[1], _p(pos), _p(entry), _p(out), out.stride(0), tokens,
           n_heads, n_kv, head_dim, int(window or 0), float(scale), int(n_splits), _p(scratch), _p(status),
           _stream())
+
+
+def attention_prefill_supports(head_dim: int, page_size: int, dtype: torch.dtype) -> bool:
+    """Whether the tensor-core kernel for prompt portions takes this shape."""
+    return bool(library().pl_attention_prefill_supports(head_dim, page_size, DTYPE_CODE.get(dtype, -1)))
+
+
+def attention_prefill_tile_rows() -> int:
+    return int(library().pl_attention_prefill_tile_rows())
+
+
+def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,
+                      tiles: torch.Tensor, out: torch.Tensor, page_size: int, window: int | None, scale: float,
+                      status: torch.Tensor | None = None) -> None:
+    """bf16 causal attention of prompt portions. tiles int32 [n, 4]: {first token
+    row, rows, position of the first row, block-table row}; q, out [T, nh, hd]."""
+    _dev(q, k_pool, v_pool, table, tiles, out, status)
+    tokens, n_heads, head_dim = q.shape
+    n_pages, n_kv = k_pool.shape[0], k_pool.shape[1]
+    assert q.dtype == torch.bfloat16 == out.dtype == k_pool.dtype == v_pool.dtype
+    assert q.stride(2) == 1 and q.stride(1) == head_dim and out.stride(2) == 1 and out.stride(1) == head_dim
+    assert out.shape == q.shape
+    assert k_pool.shape == (n_pages, n_kv, page_size, head_dim) == v_pool.shape
+    assert k_pool.stride() == v_pool.stride() and k_pool.stride(3) == 1 and k_pool.stride(2) == head_dim
+    assert table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+    assert tiles.dtype == torch.int32 and tiles.dim() == 2 and tiles.shape[1] == 4 and tiles.is_contiguous()
+    _call("pl_attention_prefill", _p(q), q.stride(0), _p(k_pool), _p(v_pool), k_pool.stride(0), k_pool.stride(1),
+          page_size, n_pages, _p(table), table.shape[1], _p(tiles), tiles.shape[0], _p(out), out.stride(0),
+          n_heads, n_kv, head_dim, int(window or 0), float(scale), _p(status), _stream())
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor | None,

@@ -72,6 +72,7 @@ class Attention(Part):
         self.o: torch.Tensor | None = None
         self.cache: KVBinding | None = None
         self._decode_kernel: bool | None = None
+        self._prefill_kernel: bool | None = None
 
     @classmethod
     def tensor_needs(cls, spec: PartSpec) -> dict[str, TensorNeed]:
@@ -122,8 +123,9 @@ class Attention(Part):
     def attend(self, q: torch.Tensor, out: torch.Tensor, table: torch.Tensor, batch) -> None:
         """out = attention of q over the cache. The batch's leading `n_decode` tokens
         are single tokens of their requests: in bfloat16 they go to the split-key
-        tensor-core kernel when it takes the shape; everything else (prompt
-        portions, float32, unusual shapes) goes to the CUDA-core kernel."""
+        tensor-core kernel and prompt portions to the tiled tensor-core kernel when
+        those take the shape; everything else (float32, unusual shapes) goes to the
+        CUDA-core kernel."""
         cache = self.cache
         tokens = q.shape[0]
         n_decode = 0
@@ -145,7 +147,15 @@ class Attention(Part):
             ops.attention_decode(q[:n_decode], cache.k_pool, cache.v_pool, table, batch.pos[:n_decode],
                                  batch.entry[:n_decode], out[:n_decode], cache.page_size, self.window, self.scale,
                                  splits, scratch, batch.status)
-        if n_decode < tokens:
+        tiles = batch.extras.get("prefill_tiles")
+        if self._prefill_kernel is None:
+            self._prefill_kernel = ops.attention_prefill_supports(self.head_dim, cache.page_size, q.dtype)
+        if n_decode < tokens and self._prefill_kernel and tiles is not None and \
+                n_decode == int(getattr(batch, "n_decode", 0)):
+            # The tile list covers exactly the tokens after the leading single tokens.
+            ops.attention_prefill(q, cache.k_pool, cache.v_pool, table, tiles, out, cache.page_size, self.window,
+                                  self.scale, batch.status)
+        elif n_decode < tokens:
             ops.attention_simt(q[n_decode:], cache.k_pool, cache.v_pool, table, batch.pos[n_decode:],
                                batch.entry[n_decode:], out[n_decode:], cache.page_size, self.window, self.scale,
                                batch.status)

@@ -377,6 +377,100 @@ def test_pages_before_the_window_are_never_read(ops):
         assert int(status) == 0, kernel
 
 
+def make_tiles(portions, tile_rows=64):
+    """portions: [(first row, rows, first position, table row)] -> int32 [n, 4] tiles."""
+    tiles = []
+    for row0, n, pos0, entry in portions:
+        for r in range(0, n, tile_rows):
+            tiles.append((row0 + r, min(tile_rows, n - r), pos0 + r, entry))
+    tiles.sort(key=lambda t: -(t[2] + t[1]))
+    return torch.tensor(tiles, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page", [(8, 2, 64, 16), (4, 1, 128, 16), (6, 6, 64, 32), (5, 1, 128, 8),
+                                            (3, 3, 128, 64)])
+@pytest.mark.parametrize("window", [None, 70])
+def test_attention_prefill(ops, nh, nkv, hd, page, window):
+    dtype = torch.bfloat16
+    assert ops.attention_prefill_supports(hd, page, dtype)
+    # request 0: a whole prompt of 150 from position 0; request 1: a portion of 2 at 300..301;
+    # request 2: a portion of 131 starting at 77 (not aligned to anything)
+    lengths = [150, 302, 208]
+    portions = [(0, 150, 0, 0), (150, 2, 300, 1), (152, 131, 77, 2)]
+    pages_each = -(-max(lengths) // page)
+    n_pages = 3 * pages_each + 4
+    table = scattered_tables(3, pages_each, n_pages, seed=hd + page)
+    kp, vp = make_pools(n_pages, nkv, page, hd, dtype, fill=1.0)
+    pos, entry = [], []
+    for row0, n, pos0, e in portions:
+        pos += list(range(pos0, pos0 + n))
+        entry += [e] * n
+    q = torch.randn(len(pos), nh, hd, device=DEV).to(dtype)
+    out = torch.full_like(q, float("nan"))
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    ops.attention_prefill(q, kp, vp, table.to(DEV), make_tiles(portions), out, page, window, scale, status)
+    want = reference_attention(q, kp, vp, table, pos, entry, page, window, scale)
+    assert int(status) == 0 and rel(out, want) < 1e-2
+    # with an offset: the kernel is given only the rows after two leading ones, as in a mixed batch
+    out2 = torch.full_like(q, float("nan"))
+    later = [(row0, n, pos0, e) for row0, n, pos0, e in portions[1:]]
+    ops.attention_prefill(q, kp, vp, table.to(DEV), make_tiles(later), out2, page, window, scale, status)
+    assert rel(out2[150:], want[150:]) < 1e-2 and bool(torch.isnan(out2[:150].float()).all())
+
+
+@pytest.mark.parametrize("far_key", [0, 63, 64, 65, 1023, 1024, 1100])
+def test_prefill_finds_one_far_key_and_respects_causality(ops, far_key):
+    """A loud key: queries at or after it must return its value, queries before it
+    must not see it (a kernel that drops a tile, or reads past the diagonal, fails)."""
+    dtype = torch.bfloat16
+    nh, nkv, hd, page = 2, 1, 64, 16
+    n_ctx, n_q = 1204, 140  # the portion is the last 140 positions
+    pages_each = -(-n_ctx // page)
+    table = scattered_tables(1, pages_each, pages_each + 3, seed=9)
+    kp, vp = make_pools(pages_each + 3, nkv, page, hd, dtype, fill=0.3)
+    direction = torch.randn(hd, device=DEV)
+    q = (direction[None, None, :] + 0.05 * torch.randn(n_q, nh, hd, device=DEV)).to(dtype)
+    page_id = int(table[0, far_key // page])
+    kp[page_id, 0, far_key % page] = (direction * 12).to(dtype)
+    vp[page_id, 0, far_key % page] = 5.0
+    pos0 = n_ctx - n_q
+    out = torch.empty_like(q)
+    ops.attention_prefill(q, kp, vp, table.to(DEV), make_tiles([(0, n_q, pos0, 0)]), out, page, None, 1.0)
+    pos = list(range(pos0, n_ctx))
+    want = reference_attention(q, kp, vp, table, pos, [0] * n_q, page, None, 1.0)
+    sees = torch.tensor([p >= far_key for p in pos])
+    assert bool((want[sees].amin(dim=(1, 2)) > 4.0).all()) and (sees.all() or bool((want[~sees].amax(dim=(1, 2)) < 3.0).all()))
+    assert rel(out, want) < 1e-2
+
+
+def test_prefill_window_edges_and_released_pages(ops):
+    dtype = torch.bfloat16
+    nh, nkv, hd, page, window = 2, 1, 128, 16, 100
+    n_ctx, n_q = 400, 70
+    pos0 = n_ctx - n_q
+    pages_each = -(-n_ctx // page)
+    table = scattered_tables(1, pages_each, pages_each + 1, seed=2)
+    first_needed = pos0 - window + 1
+    table[0, : first_needed // page] = -1  # given back: must never be read
+    kp, vp = make_pools(pages_each + 1, nkv, page, hd, dtype, fill=0.3)
+    direction = torch.randn(hd, device=DEV)
+    q = (direction[None, None, :] + 0.05 * torch.randn(n_q, nh, hd, device=DEV)).to(dtype)
+    loud = pos0 - 60  # inside the window of the first 40 queries only
+    page_id = int(table[0, loud // page])
+    kp[page_id, 0, loud % page] = (direction * 10).to(dtype)
+    vp[page_id, 0, loud % page] = 5.0
+    out = torch.empty_like(q)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.attention_prefill(q, kp, vp, table.to(DEV), make_tiles([(0, n_q, pos0, 0)]), out, page, window, 1.0, status)
+    pos = list(range(pos0, n_ctx))
+    want = reference_attention(q, kp, vp, table, pos, [0] * n_q, page, window, 1.0)
+    inside = torch.tensor([p - window + 1 <= loud for p in pos])
+    assert inside.any() and (~inside).any()
+    assert bool((want[inside].amin(dim=(1, 2)) > 4.0).all()) and bool((want[~inside].amax(dim=(1, 2)) < 3.0).all())
+    assert int(status) == 0 and rel(out, want) < 1e-2
+
+
 # ----------------------------------------------------------------------------- sampling
 
 def run_sample(ops, logits, temperature, top_k=None, top_p=None, seeds=None, counts=None):
