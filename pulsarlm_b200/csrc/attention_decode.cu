@@ -381,3 +381,70 @@ PL_API int pl_attention_decode(const void* q, int64_t q_row_stride, const void* 
     }
     return launch_decode<128>(p, n_tokens, n_kv_heads, stream);
 }
+
+// ---------------------------------------------------------------------------
+// The same kernel for callers that cannot allocate: scratch from a built-in array.
+// See no_alloc.h for who this is for and the rules of use.
+#include "no_alloc.h"
+
+namespace {
+
+// In host code this name is only a stand-in for the symbol: it is not a device
+// address and must not be passed to a kernel. Host code asks the runtime for the
+// address (below); device code could name the array directly.
+static __device__ __align__(256) float static_scratch[PL_STATIC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+float* static_scratch_address[kMaxDevices] = {};
+
+// The array's address on the current device, looked up once per device.
+int find_static_scratch(float** address) {
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) {
+        return pl_fail(3, "attention_decode_static: cudaGetDevice failed: %s", cudaGetErrorString(err));
+    }
+    if (device < 0 || device >= kMaxDevices) {
+        return pl_fail(2, "attention_decode_static: device index %d is beyond the %d this entry point tracks", device,
+                       kMaxDevices);
+    }
+    if (static_scratch_address[device] == nullptr) {
+        float* found = nullptr;
+        err = cudaGetSymbolAddress(reinterpret_cast<void**>(&found), static_scratch);
+        if (err != cudaSuccess || found == nullptr) {
+            return pl_fail(3, "attention_decode_static: cannot find the built-in scratch on device %d: %s", device,
+                           cudaGetErrorString(err));
+        }
+        static_scratch_address[device] = found;
+    }
+    *address = static_scratch_address[device];
+    return 0;
+}
+
+}  // namespace
+
+PL_API int64_t pl_static_scratch_floats() { return PL_STATIC_SCRATCH_FLOATS; }
+
+PL_API int pl_attention_decode_static(const void* q, int64_t q_row_stride, const void* k_pool, const void* v_pool,
+                                      int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
+                                      const int32_t* table, int table_width, const int32_t* pos,
+                                      const int32_t* entry, void* out, int64_t out_row_stride, int n_tokens,
+                                      int n_heads, int n_kv_heads, int head_dim, int window, float scale,
+                                      int n_splits, int32_t* status, cudaStream_t stream) {
+    PL_REQUIRE(n_tokens >= 0 && n_heads > 0 && head_dim > 0 && n_splits >= 1,
+               "attention_decode_static: bad sizes tokens=%d heads=%d head_dim=%d splits=%d", n_tokens, n_heads,
+               head_dim, n_splits);
+    const int64_t needed = pl_attention_decode_scratch_floats(n_tokens, n_heads, head_dim, n_splits);
+    PL_REQUIRE(needed <= PL_STATIC_SCRATCH_FLOATS,
+               "attention_decode_static: %d tokens x %d heads x %d splits need %lld floats of scratch, the built-in "
+               "array holds %lld; use fewer splits or fewer tokens per call",
+               n_tokens, n_heads, n_splits, static_cast<long long>(needed),
+               static_cast<long long>(PL_STATIC_SCRATCH_FLOATS));
+    float* scratch = nullptr;
+    if (const int code = find_static_scratch(&scratch)) {
+        return code;
+    }
+    return pl_attention_decode(q, q_row_stride, k_pool, v_pool, page_stride, head_stride, page_size, n_pages, table,
+                               table_width, pos, entry, out, out_row_stride, n_tokens, n_heads, n_kv_heads, head_dim,
+                               window, scale, n_splits, scratch, status, stream);
+}
