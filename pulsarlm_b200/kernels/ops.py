@@ -24,7 +24,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 7
+ABI_VERSION = 8
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -50,6 +50,8 @@ _SIGNATURES = {
                              _I32, _I32, _I32, _I32, _F32, _PTR, _PTR],
     "pl_attention_prefill_supports": [_I32, _I32, _I32],
     "pl_attention_prefill_tile_rows": [],
+    "pl_gemm_bf16": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I64, _I64, _I64, _I32, _PTR, _PTR, _I32, _PTR, _PTR],
+    "pl_gemm_bf16_supports": [_I32, _I32, _I32, _I64, _I64],
     "pl_sample": [_PTR, _I64, _I32, _I32, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR],
 }
 
@@ -76,6 +78,8 @@ def library() -> ctypes.CDLL:
         lib.pl_device_arch.restype = _I32
         lib.pl_attention_decode_scratch_floats.argtypes = [_I32, _I32, _I32, _I32]
         lib.pl_attention_decode_scratch_floats.restype = _I64
+        lib.pl_gemm_bf16_scratch_floats.argtypes = [_I32, _I32, _I32]
+        lib.pl_gemm_bf16_scratch_floats.restype = _I64
         _lib = lib
     return _lib
 
@@ -190,6 +194,41 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bo
     assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
     _call("pl_gemm_f32", _p(a), _p(w), _p(out), m, n, k, a.stride(0) if m > 1 else k, w.stride(0) if n > 1 else k,
           out.stride(0) if m > 1 else n, int(accumulate), _stream())
+
+
+_GEMM_COUNTERS = 1 << 16
+_gemm_counter_buffers: dict = {}
+
+
+def _gemm_counters(device: torch.device) -> torch.Tensor:
+    """Tile counters of the split-k products: zero between launches (the kernel
+    resets what it used), one buffer per device, shared by the products of one
+    stream (they run one after the other)."""
+    if device not in _gemm_counter_buffers:
+        _gemm_counter_buffers[device] = torch.zeros(_GEMM_COUNTERS, dtype=torch.int32, device=device)
+    return _gemm_counter_buffers[device]
+
+
+def gemm_bf16_supports(t: int, n: int, k: int, ldx: int, ldw: int) -> bool:
+    return bool(library().pl_gemm_bf16_supports(t, n, k, ldx, ldw))
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor | None = None) -> None:
+    """out[T, N] (bf16 or fp32) = x[T, K] @ w[N, K]^T on the tcgen05 tensor cores."""
+    _dev(x, w, out, status)
+    assert x.dtype == w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
+    t, k = x.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and out.shape == (t, n)
+    assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    ldx = x.stride(0) if t > 1 else k
+    ldw = w.stride(0) if n > 1 else k
+    floats = int(library().pl_gemm_bf16_scratch_floats(t, n, k))
+    scratch = torch.empty(floats, dtype=torch.float32, device=x.device) if floats else None
+    counters = _gemm_counters(x.device) if floats else None
+    _call("pl_gemm_bf16", _p(x), _p(w), _p(out), t, n, k, ldx, ldw, out.stride(0) if t > 1 else n,
+          int(out.dtype == torch.float32), _p(scratch), _p(counters), _GEMM_COUNTERS if floats else 0, _p(status),
+          _stream())
 
 
 def rope_kv_write(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | None, pos: torch.Tensor,

@@ -110,6 +110,52 @@ def test_gemm_f32_is_true_fp32(ops):
     assert abs(float(out[0, 0]) - 8.0) > 3e-3
 
 
+@pytest.mark.parametrize("t,n,k", [(1, 128, 64), (8, 256, 128), (3, 100, 96), (37, 1000, 96), (300, 515, 160),
+                                   (64, 512, 1024), (130, 384, 512), (8, 4096, 4096), (17, 6144, 1024),
+                                   (600, 1536, 2048), (2048, 1024, 512)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_bf16_tcgen05(ops, t, n, k, out_dtype):
+    """The tensor-core product at token counts from one to thousands, widths that
+    are no multiple of the tile, k ranges shared between CTAs (few tiles) and whole
+    tiles (many)."""
+    x = torch.randn(t, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) / k ** 0.5).to(torch.bfloat16)
+    out = torch.full((t, n), float("nan"), device=DEV, dtype=out_dtype)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert ops.gemm_bf16_supports(t, n, k, k, k)
+    for _ in range(2):  # twice: the tile counters must be back at zero
+        ops.gemm_bf16(x, w, out, status)
+    want = x.double() @ w.double().T
+    assert int(status) == 0
+    assert rel(out, want) < (1e-5 if out_dtype == torch.float32 else 1e-2)
+
+
+def test_gemm_bf16_finds_one_large_product_among_many(ops):
+    """One x[t, k] * w[n, k] pair far larger than the rest, at the last k of a k
+    block, the first of the next, and in the tail: a dropped k block or a mis-stepped
+    descriptor loses it."""
+    t, n, k = 5, 200, 1000
+    for hot_k in (63, 64, 511, 959, 960, 999):
+        x = torch.zeros(t, k, device=DEV, dtype=torch.bfloat16)
+        w = torch.zeros(n, k, device=DEV, dtype=torch.bfloat16)
+        x[3, hot_k] = 3.0
+        w[150, hot_k] = 2.0
+        out = torch.empty(t, n, device=DEV, dtype=torch.float32)
+        ops.gemm_bf16(x, w, out)
+        want = torch.zeros(t, n)
+        want[3, 150] = 6.0
+        assert torch.equal(out.cpu(), want), hot_k
+
+
+def test_gemm_bf16_refuses_rows_that_do_not_start_on_16_bytes(ops):
+    assert not ops.gemm_bf16_supports(4, 64, 172, 172, 172)
+    x = torch.randn(4, 172, device=DEV).to(torch.bfloat16)
+    w = torch.randn(64, 172, device=DEV).to(torch.bfloat16)
+    with pytest.raises(ops.KernelError) as error:
+        ops.gemm_bf16(x, w, torch.empty(4, 64, device=DEV, dtype=torch.bfloat16))
+    assert "multiples of 8" in str(error.value)
+
+
 # ----------------------------------------------------------------------------- cache helpers
 
 def make_pools(n_pages, n_kv, page, hd, dtype, fill=None):
