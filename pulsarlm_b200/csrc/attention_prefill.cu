@@ -1,7 +1,7 @@
 // Paged causal attention for prompt portions in bfloat16 on tensor cores.
 //
-// CTA (query tile, query head): 64 consecutive query tokens of one request against
-// that request's keys, 64 keys at a time. The four warps own 16 query rows each and
+// CTA (query tile, query head): 128 consecutive query tokens of one request against
+// that request's keys, 64 keys at a time. The eight warps own 16 query rows each and
 // share the key and value tiles, which all threads copy from the cache pages with
 // cp.async into two shared-memory stages (rows of a tile come from up to four pages
 // through the block table; rows past the tile's last needed key are zero-filled, so
@@ -19,7 +19,8 @@
 
 namespace {
 
-constexpr int kBM = 64;  // query rows per CTA
+constexpr int kBM = 128;  // query rows per CTA (eight warps of 16)
+constexpr int kThreads = kBM / 16 * 32;
 constexpr int kBN = 64;  // keys per tile
 
 struct PrefillParams {
@@ -43,7 +44,7 @@ struct PrefillParams {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(128) attention_prefill_kernel(const PrefillParams p) {
+__global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const PrefillParams p) {
     constexpr int kRowBytes = HD * 2;
     constexpr int kChunks = HD / 8;
     constexpr int kTileBytes = kBN * kRowBytes;
@@ -63,7 +64,7 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const PrefillPar
     const int j0 = first_key / kBN, j1 = last_key / kBN;
 
     // Q tile -> shared memory (zero rows past the portion's end).
-    for (int c = threadIdx.x; c < kBM * kChunks; c += 128) {
+    for (int c = threadIdx.x; c < kBM * kChunks; c += kThreads) {
         const int r = c / kChunks, ch = c % kChunks;
         const __nv_bfloat16* src = p.q + (row0 + min(r, n_rows - 1)) * p.q_row_stride +
             static_cast<int64_t>(head) * HD + ch * 8;
@@ -74,7 +75,7 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const PrefillPar
     auto issue = [&](int j, int stage) {
         unsigned char* k_s = kv_s + stage * 2 * kTileBytes;
         unsigned char* v_s = k_s + kTileBytes;
-        for (int c = threadIdx.x; c < kBN * kChunks; c += 128) {
+        for (int c = threadIdx.x; c < kBN * kChunks; c += kThreads) {
             const int r = c / kChunks, ch = c % kChunks;
             const int key = j * kBN + r;
             bool valid = key <= last_key && key >= first_key;
@@ -159,16 +160,31 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const PrefillPar
                 }
             }
             float tile_lo = -INFINITY, tile_hi = -INFINITY;
+            // Only tiles that cross the diagonal or the window's edge need the mask.
+            const int warp_first = pos0 + warp * 16;
+            const bool edge = key0 + kBN - 1 > warp_first || (p.window > 0 && key0 < warp_last - p.window + 1);
+            if (edge) {
 #pragma unroll
-            for (int n = 0; n < kBN / 8; ++n) {
+                for (int n = 0; n < kBN / 8; ++n) {
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int key = key0 + 8 * n + 2 * tig + e;
-                    s[n][e] = (key <= pos_lo && key >= first_lo) ? s[n][e] * p.scale_log2 : -INFINITY;
-                    s[n][2 + e] = (key <= pos_hi && key >= first_hi) ? s[n][2 + e] * p.scale_log2 : -INFINITY;
+                    for (int e = 0; e < 2; ++e) {
+                        const int key = key0 + 8 * n + 2 * tig + e;
+                        s[n][e] = (key <= pos_lo && key >= first_lo) ? s[n][e] * p.scale_log2 : -INFINITY;
+                        s[n][2 + e] = (key <= pos_hi && key >= first_hi) ? s[n][2 + e] * p.scale_log2 : -INFINITY;
+                    }
+                    tile_lo = fmaxf(tile_lo, fmaxf(s[n][0], s[n][1]));
+                    tile_hi = fmaxf(tile_hi, fmaxf(s[n][2], s[n][3]));
                 }
-                tile_lo = fmaxf(tile_lo, fmaxf(s[n][0], s[n][1]));
-                tile_hi = fmaxf(tile_hi, fmaxf(s[n][2], s[n][3]));
+            } else {
+#pragma unroll
+                for (int n = 0; n < kBN / 8; ++n) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        s[n][e] *= p.scale_log2;
+                    }
+                    tile_lo = fmaxf(tile_lo, fmaxf(s[n][0], s[n][1]));
+                    tile_hi = fmaxf(tile_hi, fmaxf(s[n][2], s[n][3]));
+                }
             }
             tile_lo = fmaxf(tile_lo, __shfl_xor_sync(0xffffffffu, tile_lo, 1));
             tile_lo = fmaxf(tile_lo, __shfl_xor_sync(0xffffffffu, tile_lo, 2));
@@ -183,10 +199,10 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const PrefillPar
             float sum_lo = 0.0f, sum_hi = 0.0f;
 #pragma unroll
             for (int n = 0; n < kBN / 8; ++n) {
-                s[n][0] = exp2f(s[n][0] - base_lo);
-                s[n][1] = exp2f(s[n][1] - base_lo);
-                s[n][2] = exp2f(s[n][2] - base_hi);
-                s[n][3] = exp2f(s[n][3] - base_hi);
+                s[n][0] = fast_exp2(s[n][0] - base_lo);
+                s[n][1] = fast_exp2(s[n][1] - base_lo);
+                s[n][2] = fast_exp2(s[n][2] - base_hi);
+                s[n][3] = fast_exp2(s[n][3] - base_hi);
                 sum_lo += s[n][0] + s[n][1];
                 sum_hi += s[n][2] + s[n][3];
             }
@@ -254,7 +270,7 @@ int launch_prefill(const PrefillParams& p, int n_tiles, int n_heads, cudaStream_
         }
         configured = true;
     }
-    attention_prefill_kernel<HD><<<dim3(n_tiles, n_heads), 128, smem, stream>>>(p);
+    attention_prefill_kernel<HD><<<dim3(n_tiles, n_heads), kThreads, smem, stream>>>(p);
     PL_CHECK_LAUNCH("attention_prefill");
     return 0;
 }
@@ -268,7 +284,7 @@ PL_API int pl_attention_prefill_supports(int head_dim, int page_size, int dtype)
     return dtype == PL_BF16 && (head_dim == 64 || head_dim == 128) && page_size >= 1;
 }
 
-// bf16 only. tiles: int32 [n_tiles, 4] = {first token row, rows (1..64), position of
+// bf16 only. tiles: int32 [n_tiles, 4] = {first token row, rows (1..128), position of
 // the first row, block-table row}; a tile's rows are consecutive tokens of one
 // request at consecutive positions. q and out [T, n_heads, head_dim] with row
 // strides; pools and table as in pl_attention_simt.

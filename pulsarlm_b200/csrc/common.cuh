@@ -54,6 +54,24 @@ __device__ __forceinline__ float pl_load(const __nv_bfloat16* p) { return __bflo
 __device__ __forceinline__ void pl_store(float* p, float v) { *p = v; }
 __device__ __forceinline__ void pl_store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
+// Four elements at a time.
+struct alignas(8) bf16x4 {
+    __nv_bfloat162 lo, hi;
+};
+__device__ __forceinline__ float4 pl_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 pl_load4(const __nv_bfloat16* p) {
+    const bf16x4 v = *reinterpret_cast<const bf16x4*>(p);
+    const float2 a = __bfloat1622float2(v.lo), b = __bfloat1622float2(v.hi);
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void pl_store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void pl_store4(__nv_bfloat16* p, float4 v) {
+    bf16x4 o;
+    o.lo = __floats2bfloat162_rn(v.x, v.y);
+    o.hi = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<bf16x4*>(p) = o;
+}
+
 __device__ __forceinline__ float pl_warp_sum(float v) {
 #pragma unroll
     for (int offset = 16; offset > 0; offset >>= 1) {

@@ -73,6 +73,83 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const scalar_t* __rest
     }
 }
 
+// The same as add_rmsnorm_kernel for widths that are multiples of 4, with 16-byte
+// loads and the row kept in registers between the two passes (VECS float4 per
+// thread). The sum of squares is again added in an order fixed by the width.
+template <typename scalar_t, typename weight_t, int VECS>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const scalar_t* __restrict__ delta,
+                                       const weight_t* __restrict__ weight, scalar_t* __restrict__ out,
+                                       const int32_t* __restrict__ rows, int hidden, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int64_t s = rows != nullptr ? rows[r] : r;
+    float* xr = x + s * hidden;
+    const scalar_t* dr = delta != nullptr ? delta + s * hidden : nullptr;
+    scalar_t* outr = out + static_cast<int64_t>(r) * hidden;
+    const bool write_back = rows == nullptr && dr != nullptr;
+    const int n_vec = hidden / 4;
+
+    float4 v[VECS];
+    float local = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VECS; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < n_vec) {
+            v[i] = pl_load4(xr + 4 * c);
+            if (dr != nullptr) {
+                const float4 d = pl_load4(dr + 4 * c);
+                v[i].x += d.x;
+                v[i].y += d.y;
+                v[i].z += d.z;
+                v[i].w += d.w;
+            }
+            if (write_back) {
+                pl_store4(xr + 4 * c, v[i]);
+            }
+            local += v[i].x * v[i].x;
+            local += v[i].y * v[i].y;
+            local += v[i].z * v[i].z;
+            local += v[i].w * v[i].w;
+        }
+    }
+    const float total = pl_block_sum(local, scratch);
+    const float inv_rms = rsqrtf(total / static_cast<float>(hidden) + eps);
+#pragma unroll
+    for (int i = 0; i < VECS; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < n_vec) {
+            const float4 w = pl_load4(weight + 4 * c);
+            pl_store4(outr + 4 * c, make_float4(v[i].x * inv_rms * w.x, v[i].y * inv_rms * w.y,
+                                                v[i].z * inv_rms * w.z, v[i].w * inv_rms * w.w));
+        }
+    }
+}
+
+// out[t, i..i+7] = silu(gate) * up, eight elements (16 bytes of bf16) per thread.
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                     int64_t tokens, int width) {
+    const int chunks = width / 8;
+    const int64_t total = tokens * chunks;
+    for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t t = idx / chunks;
+        const int c = static_cast<int>(idx - t * chunks);
+        const uint4 g = *reinterpret_cast<const uint4*>(in + t * 2 * width + 8 * c);
+        const uint4 u = *reinterpret_cast<const uint4*>(in + t * 2 * width + width + 8 * c);
+        const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 gf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[i]));
+            const float2 uf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[i]));
+            const __nv_bfloat162 o = __floats2bfloat162_rn(gf.x / (1.0f + expf(-gf.x)) * uf.x,
+                                                           gf.y / (1.0f + expf(-gf.y)) * uf.y);
+            ow[i] = *reinterpret_cast<const uint32_t*>(&o);
+        }
+        *reinterpret_cast<uint4*>(out + t * width + 8 * c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
 // out[t, i] = silu(in[t, i]) * in[t, width + i], silu(z) = z / (1 + exp(-z)).
 template <typename scalar_t>
 __global__ void swiglu_kernel(const scalar_t* __restrict__ in, scalar_t* __restrict__ out, int64_t tokens,
@@ -130,6 +207,32 @@ PL_API int pl_add_rmsnorm(float* x, const void* delta, const void* weight, int w
     if (n_rows == 0) {
         return 0;
     }
+    const bool aligned = hidden % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(delta) & 15) == 0 && (reinterpret_cast<uintptr_t>(weight) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    if (aligned && hidden <= 16384) {
+        // Widths that are multiples of 4: 16-byte loads, one pass over memory.
+        const int n_vec = hidden / 4;
+        int threads = 32;
+        while (threads < 1024 && threads < n_vec) {
+            threads *= 2;
+        }
+        const int vecs = (n_vec + threads - 1) / threads;
+#define PL_LAUNCH_NORM(W, V)                                                                              \
+    add_rmsnorm_vec_kernel<scalar_t, W, V><<<n_rows, threads, 0, stream>>>(                               \
+        x, static_cast<const scalar_t*>(delta), static_cast<const W*>(weight), static_cast<scalar_t*>(out), \
+        rows, hidden, eps)
+        PL_DISPATCH_DTYPE(dtype, "add_rmsnorm", {
+            if (weight_dtype == PL_F32) {
+                if (vecs == 1) { PL_LAUNCH_NORM(float, 1); } else if (vecs == 2) { PL_LAUNCH_NORM(float, 2); } else { PL_LAUNCH_NORM(float, 4); }
+            } else {
+                if (vecs == 1) { PL_LAUNCH_NORM(scalar_t, 1); } else if (vecs == 2) { PL_LAUNCH_NORM(scalar_t, 2); } else { PL_LAUNCH_NORM(scalar_t, 4); }
+            }
+        });
+#undef PL_LAUNCH_NORM
+        PL_CHECK_LAUNCH("add_rmsnorm");
+        return 0;
+    }
     const int threads = norm_threads(hidden);
     PL_DISPATCH_DTYPE(dtype, "add_rmsnorm", {
         if (weight_dtype == PL_F32) {
@@ -151,8 +254,17 @@ PL_API int pl_swiglu(const void* in, void* out, int n_tokens, int width, int dty
     if (n_tokens == 0) {
         return 0;
     }
-    const int64_t total = static_cast<int64_t>(n_tokens) * width;
     const int threads = 256;
+    if (dtype == PL_BF16 && width % 8 == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+        const int64_t chunks = static_cast<int64_t>(n_tokens) * (width / 8);
+        const int blocks = static_cast<int>(std::min<int64_t>((chunks + threads - 1) / threads, 148 * 32));
+        swiglu_bf16x8_kernel<<<blocks, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(in),
+                                                            static_cast<__nv_bfloat16*>(out), n_tokens, width);
+        PL_CHECK_LAUNCH("swiglu");
+        return 0;
+    }
+    const int64_t total = static_cast<int64_t>(n_tokens) * width;
     const int blocks = static_cast<int>(std::min<int64_t>((total + threads - 1) / threads, 148 * 16));
     PL_DISPATCH_DTYPE(dtype, "swiglu", {
         swiglu_kernel<scalar_t><<<blocks, threads, 0, stream>>>(static_cast<const scalar_t*>(in),

@@ -46,6 +46,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+// 2^x by the hardware's approximation (2 ulp; -inf gives 0). The probabilities it
+// makes are rounded to bfloat16 right after, so the fp32 engine never uses it.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Byte offset of 16-byte chunk `chunk` of row `row` in a swizzled tile whose rows
 // are `row_bytes` long (a multiple of 128).
 __device__ __forceinline__ int swizzled(int row, int chunk, int row_bytes) {

@@ -97,6 +97,86 @@ __global__ void rope_kv_write_kernel(scalar_t* __restrict__ q, const scalar_t* _
     }
 }
 
+// The same with four consecutive dims per thread (8- or 16-byte loads), for shapes
+// where the rotated half, the unrotated tail and the row stride are multiples of 4.
+template <typename scalar_t>
+__global__ void rope_kv_write_vec_kernel(scalar_t* __restrict__ q, const scalar_t* __restrict__ k,
+                                         const scalar_t* __restrict__ v, int64_t row_stride,
+                                         const int32_t* __restrict__ pos, const int32_t* __restrict__ entry,
+                                         const int32_t* __restrict__ table, int table_width,
+                                         scalar_t* __restrict__ k_pool, scalar_t* __restrict__ v_pool,
+                                         int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
+                                         const double* __restrict__ inv_freq, int rotary, int n_heads,
+                                         int n_kv_heads, int head_dim, int32_t* status) {
+    extern __shared__ float sincos[];
+    const int t = blockIdx.x;
+    const int p = pos[t];
+    const int half = rotary / 2;
+    float* cs = sincos;
+    float* sn = sincos + half;
+    if (inv_freq != nullptr) {
+        for (int j = threadIdx.x; j < half; j += blockDim.x) {
+            rope_sincos(p, inv_freq[j], cs[j], sn[j]);
+        }
+    }
+    __syncthreads();
+
+    const int n_slots = n_heads + (k_pool != nullptr ? n_kv_heads : 0);
+    const int slot0 = blockIdx.y * kHeadsPerBlock;
+    const int slot1 = min(slot0 + kHeadsPerBlock, n_slots);
+    int page = -1;
+    if (slot1 > n_heads) {
+        page = table[static_cast<int64_t>(entry[t]) * table_width + p / page_size];
+        if (page < 0 || page >= n_pages) {
+            if (threadIdx.x == 0 && status != nullptr) {
+                atomicOr(status, 2);
+            }
+            page = -1;
+        }
+    }
+    const int groups = (head_dim - half) / 4;  // per head: half/4 rotated groups, then the unrotated tail
+    for (int idx = threadIdx.x; idx < (slot1 - slot0) * groups; idx += blockDim.x) {
+        const int slot = slot0 + idx / groups, j = 4 * (idx % groups);
+        if (slot < n_heads) {
+            if (inv_freq == nullptr || j >= half) {
+                continue;
+            }
+            scalar_t* x = q + t * row_stride + static_cast<int64_t>(slot) * head_dim;
+            const float4 lo = pl_load4(x + j), hi = pl_load4(x + j + half);
+            const float4 c = *reinterpret_cast<const float4*>(cs + j), s = *reinterpret_cast<const float4*>(sn + j);
+            pl_store4(x + j, make_float4(lo.x * c.x - hi.x * s.x, lo.y * c.y - hi.y * s.y, lo.z * c.z - hi.z * s.z,
+                                         lo.w * c.w - hi.w * s.w));
+            pl_store4(x + j + half, make_float4(hi.x * c.x + lo.x * s.x, hi.y * c.y + lo.y * s.y,
+                                                hi.z * c.z + lo.z * s.z, hi.w * c.w + lo.w * s.w));
+        } else if (page >= 0) {
+            const int h = slot - n_heads;
+            const scalar_t* x = k + t * row_stride + static_cast<int64_t>(h) * head_dim;
+            const scalar_t* y = v + t * row_stride + static_cast<int64_t>(h) * head_dim;
+            const int64_t at = page * page_stride + h * head_stride + static_cast<int64_t>(p % page_size) * head_dim;
+            if (j < half) {
+                const float4 lo = pl_load4(x + j), hi = pl_load4(x + j + half);
+                if (inv_freq != nullptr) {
+                    const float4 c = *reinterpret_cast<const float4*>(cs + j);
+                    const float4 s = *reinterpret_cast<const float4*>(sn + j);
+                    pl_store4(k_pool + at + j, make_float4(lo.x * c.x - hi.x * s.x, lo.y * c.y - hi.y * s.y,
+                                                           lo.z * c.z - hi.z * s.z, lo.w * c.w - hi.w * s.w));
+                    pl_store4(k_pool + at + j + half, make_float4(hi.x * c.x + lo.x * s.x, hi.y * c.y + lo.y * s.y,
+                                                                  hi.z * c.z + lo.z * s.z, hi.w * c.w + lo.w * s.w));
+                } else {
+                    pl_store4(k_pool + at + j, lo);
+                    pl_store4(k_pool + at + j + half, hi);
+                }
+                pl_store4(v_pool + at + j, pl_load4(y + j));
+                pl_store4(v_pool + at + j + half, pl_load4(y + j + half));
+            } else {
+                const int d = j + half;
+                pl_store4(k_pool + at + d, pl_load4(x + d));
+                pl_store4(v_pool + at + d, pl_load4(y + d));
+            }
+        }
+    }
+}
+
 }  // namespace
 
 // q [T, n_heads, head_dim], k and v [T, n_kv_heads, head_dim], all with `row_stride`
@@ -120,12 +200,19 @@ PL_API int pl_rope_kv_write(void* q, const void* k, const void* v, int64_t row_s
     const size_t smem = static_cast<size_t>(rotary) * sizeof(float);
     PL_REQUIRE(smem <= 48 * 1024, "rope_kv_write: rotary width %d is too large", rotary);
     const int n_slots = n_heads + (k_pool != nullptr ? n_kv_heads : 0);
-    const int items = kHeadsPerBlock * (head_dim - rotary / 2);
-    const int threads = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
     const dim3 grid(n_tokens, (n_slots + kHeadsPerBlock - 1) / kHeadsPerBlock);
     PL_REQUIRE(grid.y <= 65535, "rope_kv_write: too many heads (%d)", n_slots);
+    const int half = rotary / 2;
+    const uintptr_t align = dtype == PL_F32 ? 15 : 7;
+    const bool vec = half % 4 == 0 && (head_dim - rotary) % 4 == 0 && head_dim % 4 == 0 && row_stride % 4 == 0 &&
+        page_stride % 4 == 0 && head_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(q) & align) == 0 &&
+        (reinterpret_cast<uintptr_t>(k) & align) == 0 && (reinterpret_cast<uintptr_t>(v) & align) == 0 &&
+        (reinterpret_cast<uintptr_t>(k_pool) & align) == 0 && (reinterpret_cast<uintptr_t>(v_pool) & align) == 0;
+    const int items = kHeadsPerBlock * (head_dim - half) / (vec ? 4 : 1);
+    const int threads = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
     PL_DISPATCH_DTYPE(dtype, "rope_kv_write", {
-        rope_kv_write_kernel<scalar_t><<<grid, threads, smem, stream>>>(
+        auto kernel = vec ? rope_kv_write_vec_kernel<scalar_t> : rope_kv_write_kernel<scalar_t>;
+        kernel<<<grid, threads, smem, stream>>>(
             static_cast<scalar_t*>(q), static_cast<const scalar_t*>(k), static_cast<const scalar_t*>(v), row_stride,
             pos, entry, table, table_width, static_cast<scalar_t*>(k_pool), static_cast<scalar_t*>(v_pool),
             page_stride, head_stride, page_size, n_pages, inv_freq, rotary, n_heads, n_kv_heads, head_dim, status);
