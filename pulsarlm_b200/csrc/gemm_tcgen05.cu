@@ -32,16 +32,13 @@
 //
 // The reference leaves these products to a library (`at::linear`,
 // pulsarlm-core/src/engine/model/llama.cpp:67-69, 81, 91, 93).
-#include "common.cuh"
-
-#include <cuda.h>
+#include "tcgen05_helpers.cuh"
 
 namespace {
 
 constexpr int kTileM = 128;   // output features per tile (MMA M)
 constexpr int kBlockK = 64;   // k elements per stage: 128 bytes, one swizzle row
 constexpr int kThreads = 192;
-constexpr uint32_t kWaitLimit = 1u << 22;
 
 struct GemmParams {
     void* y;            // [T, N] bf16 or fp32
@@ -58,99 +55,6 @@ struct GemmParams {
     int32_t* counters;  // one per tile, zero between launches
     int32_t* status;
 };
-
-// ------------------------------------------------------------------ PTX helpers
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-// Bounded wait: false after kWaitLimit tries or once another role has given up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t tries = 0; tries < kWaitLimit; ++tries) {
-        if (mbar_try_wait(bar, parity)) {
-            return true;
-        }
-        if ((tries & 1023u) == 1023u && *abort_flag) {
-            return false;
-        }
-    }
-    *abort_flag = 1;
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-        : "memory");
-}
-__device__ __forceinline__ void tcgen05_alloc(uint32_t* slot, uint32_t columns) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)),
-                 "r"(columns)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tcgen05_dealloc(uint32_t address, uint32_t columns) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_before() {
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void tcgen05_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                            uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void tcgen05_ld16(uint32_t address, float (&v)[16]) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(address)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        v[i] = __uint_as_float(r[i]);
-    }
-}
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of
-// 128 bytes, groups of 8 rows 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_descriptor(const void* tile) {
-    const uint64_t address = (smem_u32(tile) >> 4) & 0x3FFFu;
-    return address | (1ull << 16) | (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
 
 __host__ __device__ constexpr int stages_for(int tn) {
     const int stage_bytes = kTileM * kBlockK * 2 + tn * kBlockK * 2;
@@ -402,43 +306,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
 // ------------------------------------------------------------------ host side
 
-using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_tiled() {
-    static EncodeTiled fn = nullptr;
-    if (fn == nullptr) {
-        void* found = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &found, cudaEnableDefault, &result) == cudaSuccess &&
-            result == cudaDriverEntryPointSuccess) {
-            fn = reinterpret_cast<EncodeTiled>(found);
-        }
-    }
-    return fn;
-}
-
-// A [rows, k] bf16 row-major matrix cut into boxes of box_rows x 64, 128-byte swizzle.
-int make_map(CUtensorMap* map, const void* base, int rows, int k, int64_t ld, int box_rows) {
-    EncodeTiled encode = encode_tiled();
-    if (encode == nullptr) {
-        return pl_fail(3, "gemm_tcgen05: the driver does not provide cuTensorMapEncodeTiled");
-    }
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-    const cuuint32_t box[2] = {kBlockK, static_cast<cuuint32_t>(box_rows)};
-    const cuuint32_t element_strides[2] = {1, 1};
-    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-                              element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        return pl_fail(3, "gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d (rows=%d k=%d ld=%lld)",
-                       static_cast<int>(r), rows, k, static_cast<long long>(ld));
-    }
-    return 0;
-}
-
 int sm_count() {
     static int count = 0;
     if (count == 0) {
@@ -536,10 +403,10 @@ PL_API int pl_gemm_bf16(const void* x, const void* w, void* y, int t, int n, int
     PL_REQUIRE(!plan.partials || plan.n_tiles * plan.t_tiles <= n_counters,
                "gemm_bf16: %d tiles need as many counters, %d were given", plan.n_tiles * plan.t_tiles, n_counters);
     CUtensorMap map_w, map_x;
-    if (const int code = make_map(&map_w, w, n, k, ldw, kTileM)) {
+    if (const int code = make_map(&map_w, w, n, k, ldw, kTileM, kBlockK)) {
         return code;
     }
-    if (const int code = make_map(&map_x, x, t, k, ldx, plan.tn)) {
+    if (const int code = make_map(&map_x, x, t, k, ldx, plan.tn, kBlockK)) {
         return code;
     }
     GemmParams p;

@@ -49,6 +49,9 @@ _SIGNATURES = {
     "pl_attention_prefill": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _I32, _PTR, _I64,
                              _I32, _I32, _I32, _I32, _F32, _PTR, _PTR],
     "pl_attention_prefill_supports": [_I32, _I32, _I32],
+    "pl_attention_prefill_tcgen05": [_PTR, _I64, _I32, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _I32,
+                                     _PTR, _I64, _I32, _I32, _I32, _I32, _F32, _PTR, _PTR],
+    "pl_attention_prefill_tcgen05_supports": [_I32, _I32, _I32, _I64, _I64, _I64, _I32],
     "pl_attention_prefill_tile_rows": [],
     "pl_gemm_bf16": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I64, _I64, _I64, _I32, _PTR, _PTR, _I32, _PTR, _PTR],
     "pl_gemm_bf16_supports": [_I32, _I32, _I32, _I64, _I64],
@@ -343,6 +346,32 @@ def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     _call("pl_attention_prefill", _p(q), q.stride(0), _p(k_pool), _p(v_pool), k_pool.stride(0), k_pool.stride(1),
           page_size, n_pages, _p(table), table.shape[1], _p(tiles), tiles.shape[0], _p(out), out.stride(0),
           n_heads, n_kv, head_dim, int(window or 0), float(scale), _p(status), _stream())
+
+
+def attention_prefill_tcgen05_supports(q: torch.Tensor, k_pool: torch.Tensor, page_size: int) -> bool:
+    """Whether the tcgen05 kernel for prompt portions takes this shape and cache layout."""
+    return bool(library().pl_attention_prefill_tcgen05_supports(
+        q.shape[2], page_size, k_pool.shape[1], k_pool.stride(0), k_pool.stride(1), q.stride(0),
+        DTYPE_CODE.get(q.dtype, -1)))
+
+
+def attention_prefill_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,
+                              tiles: torch.Tensor, out: torch.Tensor, page_size: int, window: int | None,
+                              scale: float, status: torch.Tensor | None = None) -> None:
+    """As attention_prefill, on the tcgen05 tensor cores."""
+    _dev(q, k_pool, v_pool, table, tiles, out, status)
+    tokens, n_heads, head_dim = q.shape
+    n_pages, n_kv = k_pool.shape[0], k_pool.shape[1]
+    assert q.dtype == torch.bfloat16 == out.dtype == k_pool.dtype == v_pool.dtype
+    assert q.stride(2) == 1 and q.stride(1) == head_dim and out.stride(2) == 1 and out.stride(1) == head_dim
+    assert out.shape == q.shape
+    assert k_pool.shape == (n_pages, n_kv, page_size, head_dim) == v_pool.shape
+    assert k_pool.stride() == v_pool.stride() and k_pool.stride(3) == 1 and k_pool.stride(2) == head_dim
+    assert table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+    assert tiles.dtype == torch.int32 and tiles.dim() == 2 and tiles.shape[1] == 4 and tiles.is_contiguous()
+    _call("pl_attention_prefill_tcgen05", _p(q), q.stride(0), tokens, _p(k_pool), _p(v_pool), k_pool.stride(0),
+          k_pool.stride(1), page_size, n_pages, _p(table), table.shape[1], _p(tiles), tiles.shape[0], _p(out),
+          out.stride(0), n_heads, n_kv, head_dim, int(window or 0), float(scale), _p(status), _stream())
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor | None,

@@ -73,6 +73,7 @@ class Attention(Part):
         self.cache: KVBinding | None = None
         self._decode_kernel: bool | None = None
         self._prefill_kernel: bool | None = None
+        self._prefill_tcgen05: bool | None = None
 
     @classmethod
     def tensor_needs(cls, spec: PartSpec) -> dict[str, TensorNeed]:
@@ -123,9 +124,9 @@ class Attention(Part):
     def attend(self, q: torch.Tensor, out: torch.Tensor, table: torch.Tensor, batch) -> None:
         """out = attention of q over the cache. The batch's leading `n_decode` tokens
         are single tokens of their requests: in bfloat16 they go to the split-key
-        tensor-core kernel and prompt portions to the tiled tensor-core kernel when
-        those take the shape; everything else (float32, unusual shapes) goes to the
-        CUDA-core kernel."""
+        tensor-core kernel and prompt portions to the tiled tensor-core kernel (tcgen05
+        when the cache layout allows TMA, else mma.sync) when those take the shape;
+        everything else (float32, unusual shapes) goes to the CUDA-core kernel."""
         cache = self.cache
         tokens = q.shape[0]
         n_decode = 0
@@ -153,8 +154,11 @@ class Attention(Part):
         if n_decode < tokens and self._prefill_kernel and tiles is not None and \
                 n_decode == int(getattr(batch, "n_decode", 0)):
             # The tile list covers exactly the tokens after the leading single tokens.
-            ops.attention_prefill(q, cache.k_pool, cache.v_pool, table, tiles, out, cache.page_size, self.window,
-                                  self.scale, batch.status)
+            if self._prefill_tcgen05 is None:
+                self._prefill_tcgen05 = ops.attention_prefill_tcgen05_supports(q, cache.k_pool, cache.page_size)
+            kernel = ops.attention_prefill_tcgen05 if self._prefill_tcgen05 else ops.attention_prefill
+            kernel(q, cache.k_pool, cache.v_pool, table, tiles, out, cache.page_size, self.window, self.scale,
+                   batch.status)
         elif n_decode < tokens:
             ops.attention_simt(q[n_decode:], cache.k_pool, cache.v_pool, table, batch.pos[n_decode:],
                                batch.entry[n_decode:], out[n_decode:], cache.page_size, self.window, self.scale,

@@ -423,7 +423,7 @@ def test_pages_before_the_window_are_never_read(ops):
         assert int(status) == 0, kernel
 
 
-def make_tiles(portions, tile_rows=64):
+def make_tiles(portions, tile_rows=128):
     """portions: [(first row, rows, first position, table row)] -> int32 [n, 4] tiles."""
     tiles = []
     for row0, n, pos0, entry in portions:
@@ -433,12 +433,19 @@ def make_tiles(portions, tile_rows=64):
     return torch.tensor(tiles, dtype=torch.int32, device=DEV)
 
 
+def prefill_kernel(ops, name):
+    return ops.attention_prefill_tcgen05 if name == "tcgen05" else ops.attention_prefill
+
+
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
 @pytest.mark.parametrize("nh,nkv,hd,page", [(8, 2, 64, 16), (4, 1, 128, 16), (6, 6, 64, 32), (5, 1, 128, 8),
                                             (3, 3, 128, 64)])
 @pytest.mark.parametrize("window", [None, 70])
-def test_attention_prefill(ops, nh, nkv, hd, page, window):
+def test_attention_prefill(ops, kernel, nh, nkv, hd, page, window):
     dtype = torch.bfloat16
     assert ops.attention_prefill_supports(hd, page, dtype)
+    if kernel == "tcgen05" and page % 16:
+        pytest.skip("the tcgen05 kernel takes pages that are multiples of 16 tokens")
     # request 0: a whole prompt of 150 from position 0; request 1: a portion of 2 at 300..301;
     # request 2: a portion of 131 starting at 77 (not aligned to anything)
     lengths = [150, 302, 208]
@@ -455,18 +462,22 @@ def test_attention_prefill(ops, nh, nkv, hd, page, window):
     out = torch.full_like(q, float("nan"))
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     scale = 1 / math.sqrt(hd)
-    ops.attention_prefill(q, kp, vp, table.to(DEV), make_tiles(portions), out, page, window, scale, status)
+    if kernel == "tcgen05":
+        assert ops.attention_prefill_tcgen05_supports(q, kp, page)
+    run = prefill_kernel(ops, kernel)
+    run(q, kp, vp, table.to(DEV), make_tiles(portions, 128), out, page, window, scale, status)
     want = reference_attention(q, kp, vp, table, pos, entry, page, window, scale)
     assert int(status) == 0 and rel(out, want) < 1e-2
     # with an offset: the kernel is given only the rows after two leading ones, as in a mixed batch
     out2 = torch.full_like(q, float("nan"))
     later = [(row0, n, pos0, e) for row0, n, pos0, e in portions[1:]]
-    ops.attention_prefill(q, kp, vp, table.to(DEV), make_tiles(later), out2, page, window, scale, status)
+    run(q, kp, vp, table.to(DEV), make_tiles(later, 128), out2, page, window, scale, status)
     assert rel(out2[150:], want[150:]) < 1e-2 and bool(torch.isnan(out2[:150].float()).all())
 
 
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
 @pytest.mark.parametrize("far_key", [0, 63, 64, 65, 1023, 1024, 1100])
-def test_prefill_finds_one_far_key_and_respects_causality(ops, far_key):
+def test_prefill_finds_one_far_key_and_respects_causality(ops, kernel, far_key):
     """A loud key: queries at or after it must return its value, queries before it
     must not see it (a kernel that drops a tile, or reads past the diagonal, fails)."""
     dtype = torch.bfloat16
@@ -482,7 +493,7 @@ def test_prefill_finds_one_far_key_and_respects_causality(ops, far_key):
     vp[page_id, 0, far_key % page] = 5.0
     pos0 = n_ctx - n_q
     out = torch.empty_like(q)
-    ops.attention_prefill(q, kp, vp, table.to(DEV), make_tiles([(0, n_q, pos0, 0)]), out, page, None, 1.0)
+    prefill_kernel(ops, kernel)(q, kp, vp, table.to(DEV), make_tiles([(0, n_q, pos0, 0)], 128), out, page, None, 1.0)
     pos = list(range(pos0, n_ctx))
     want = reference_attention(q, kp, vp, table, pos, [0] * n_q, page, None, 1.0)
     sees = torch.tensor([p >= far_key for p in pos])
@@ -490,7 +501,8 @@ def test_prefill_finds_one_far_key_and_respects_causality(ops, far_key):
     assert rel(out, want) < 1e-2
 
 
-def test_prefill_window_edges_and_released_pages(ops):
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
+def test_prefill_window_edges_and_released_pages(ops, kernel):
     dtype = torch.bfloat16
     nh, nkv, hd, page, window = 2, 1, 128, 16, 100
     n_ctx, n_q = 400, 70
@@ -508,7 +520,8 @@ def test_prefill_window_edges_and_released_pages(ops):
     vp[page_id, 0, loud % page] = 5.0
     out = torch.empty_like(q)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    ops.attention_prefill(q, kp, vp, table.to(DEV), make_tiles([(0, n_q, pos0, 0)]), out, page, window, 1.0, status)
+    prefill_kernel(ops, kernel)(q, kp, vp, table.to(DEV), make_tiles([(0, n_q, pos0, 0)], 128), out, page, window,
+                                1.0, status)
     pos = list(range(pos0, n_ctx))
     want = reference_attention(q, kp, vp, table, pos, [0] * n_q, page, window, 1.0)
     inside = torch.tensor([p - window + 1 <= loud for p in pos])
