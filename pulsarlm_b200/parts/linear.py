@@ -1,17 +1,31 @@
 """Matrix products of the engine: y = x W^T, W stored [out, in] as checkpoints do.
 
 float32: the library's own CUDA-core kernel (true fp32, no tensor cores, no
-TF32), whose result for a row does not depend on the other rows. bfloat16:
-a library matrix product (cuBLAS through torch), as the reference's engine does
-for every projection (`at::linear`, pulsarlm-core/src/engine/model/llama.cpp:67-69,
-81, 91, 93), with fp32 accumulation.
+TF32), whose result for a row does not depend on the other rows. bfloat16, fp32
+accumulation, by one of two routes chosen by $PULSARLM_B200_GEMM:
+
+* "library" (the default): a library matrix product (cuBLAS through torch), as
+  the reference's engine does for every projection (`at::linear`,
+  pulsarlm-core/src/engine/model/llama.cpp:67-69, 81, 91, 93);
+* "tcgen05": this package's own tcgen05/TMEM kernel fed by TMA
+  (csrc/gemm_tcgen05.cu) wherever it takes the sizes (rows starting on 16 bytes),
+  the library elsewhere.
+
+The default is whichever measured faster on the Llama-3.1-8B shapes; see
+profiles/gemm_tcgen05_vs_library.md.
 """
 
 from __future__ import annotations
 
 import torch
 
+import os
+
 from ..kernels import ops
+
+GEMM_ROUTE = os.environ.get("PULSARLM_B200_GEMM", "library")
+if GEMM_ROUTE not in ("library", "tcgen05"):
+    raise ValueError(f"PULSARLM_B200_GEMM must be 'library' or 'tcgen05', got {GEMM_ROUTE!r}")
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
@@ -25,6 +39,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         ops.gemm_f32(x, weight, out)
         return out
     if x.dtype == torch.bfloat16:
+        k = x.shape[1]
+        if GEMM_ROUTE == "tcgen05" and x.stride(1) == 1 and weight.stride(1) == 1 and ops.gemm_bf16_supports(
+                tokens, n, k, x.stride(0) if tokens > 1 else k, weight.stride(0) if n > 1 else k):
+            out = torch.empty((tokens, n), dtype=out_dtype or torch.bfloat16, device=x.device)
+            ops.gemm_bf16(x, weight, out)
+            return out
         if out_dtype == torch.float32:
             # bf16 operands, fp32 accumulator written out unrounded.
             return torch.mm(x, weight.t(), out_dtype=torch.float32)
