@@ -6,11 +6,14 @@
 //   PV = P V     M 128 x N head_dim x K 64 keys   (P K-major, V as stored: N-major)
 // Roles: warp 0 loads tiles with TMA (Q once; per 64-key tile the K and V rows of
 // four 16-key page pieces, found through the block table), warp 1 issues the MMAs,
-// warps 2-5 own one query row per thread: they read S from tensor memory, do the
-// online softmax in fp32 (base 2, scale folded in), write P as bf16 into shared
-// memory for the second product, and fold each tile's PV into an fp32 output row
-// kept in registers (o = o * correction + PV). S, P and PV are double-buffered, so
-// the MMAs of tile j+1 run while the softmax of tile j is computed.
+// warps 2-9 are two softmax warpgroups that share each query row: thread pairs
+// (one per warpgroup) read the two halves of the row's S from tensor memory, agree
+// on the row maximum through shared memory, do the online softmax in fp32 (base 2,
+// scale folded in), write their half of P as bf16 into shared memory for the second
+// product, and fold their half of each tile's PV into an fp32 output row kept in
+// registers (o = o * correction + PV). Two warps per scheduler hide each other's
+// latencies. S, P and PV are double-buffered, so the MMAs of tile j+1 run while the
+// softmax of tile j is computed.
 //
 // Every mbarrier wait is bounded; on a timeout the CTA raises bit 8 of the status
 // word, stops, lets loads in flight land, frees its tensor memory and returns.
@@ -27,7 +30,7 @@ constexpr int kRows = 128;     // query rows per CTA
 constexpr int kKeys = 64;      // keys per tile
 constexpr int kPiece = 16;     // keys per TMA box (a page, or a part of one)
 constexpr int kStagesKV = 3;
-constexpr int kThreadsTc = 192;
+constexpr int kThreadsTc = 320;  // TMA warp, MMA warp, two softmax warpgroups
 
 struct TcPrefillParams {
     const int32_t* table;
@@ -86,6 +89,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     __shared__ __align__(8) uint64_t s_full[2], s_free[2], p_full[2], p_free[2], pv_full[2], pv_free[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
+    __shared__ float half_max[2][2 * kRows];  // [tile parity][warpgroup * 128 + row]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int4 tile = p.tiles[blockIdx.x];
@@ -103,11 +107,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&s_full[b], 1);
-            mbar_init(&s_free[b], 4);
-            mbar_init(&p_full[b], 4);
+            mbar_init(&s_free[b], 8);  // one arrival per softmax warp
+            mbar_init(&p_full[b], 8);
             mbar_init(&p_free[b], 1);
             mbar_init(&pv_full[b], 1);
-            mbar_init(&pv_free[b], 4);
+            mbar_init(&pv_free[b], 8);
         }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -123,38 +127,56 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 
     if (warp == 0) {
         // ------------------------------------------------ producer
+        // Lane 0 waits and issues; all lanes look up block-table entries, 32 pieces
+        // (eight tiles) at a time in one load each, so that the table's latency is
+        // paid once per eight tiles and not once per piece.
         if (lane == 0) {
             mbar_expect_tx(&q_full, kBytesQ);
             for (int h = 0; h < kHalves; ++h) {
                 tma_load_2d(q_s + h * (kRows * 128), &map_q, head * HD + h * 64, row0, &q_full);
             }
-            const int32_t* table_row = p.table + static_cast<int64_t>(tile.w) * p.table_width;
-            for (int j = 0; j < n_tiles; ++j) {
-                const int stage = j % kStagesKV;
-                if (!mbar_wait(&kv_empty[stage], ((j / kStagesKV) & 1) ^ 1u, &abort_flag)) {
-                    break;
+        }
+        const int32_t* table_row = p.table + static_cast<int64_t>(tile.w) * p.table_width;
+        constexpr int kPieces = kKeys / kPiece;  // per tile
+        int my_key = 0, my_page = 0;
+        for (int j = 0; j < n_tiles; ++j) {
+            if (j % (32 / kPieces) == 0) {
+                // Pieces outside [first_key, last_key] are never attended (masked): they
+                // are filled from the nearest needed piece, whose page is held.
+                my_key = (j0 + j) * kKeys + lane * kPiece;
+                my_key = min(max(my_key, (first_key / kPiece) * kPiece), (last_key / kPiece) * kPiece);
+                my_page = table_row[my_key / p.page_size];
+                if (my_page < 0 || my_page >= p.n_pages) {
+                    if (my_key <= (last_key / kPiece) * kPiece && p.status != nullptr) {
+                        atomicOr(p.status, 4);
+                    }
+                    my_page = 0;
                 }
-                unsigned char* k_s = kv_s + stage * kBytesStage;
-                unsigned char* v_s = k_s + kBytesK;
+            }
+            const int stage = j % kStagesKV;
+            int ok = 1;
+            if (lane == 0) {
+                ok = mbar_wait(&kv_empty[stage], ((j / kStagesKV) & 1) ^ 1u, &abort_flag) ? 1 : 0;
+            }
+            if (!__shfl_sync(0xffffffffu, ok, 0)) {
+                break;
+            }
+            unsigned char* k_s = kv_s + stage * kBytesStage;
+            unsigned char* v_s = k_s + kBytesK;
+            if (lane == 0) {
                 mbar_expect_tx(&kv_full[stage], kBytesStage);
-                for (int piece = 0; piece < kKeys / kPiece; ++piece) {
-                    // Pieces outside [first_key, last_key] are never attended (masked):
-                    // they are filled from the nearest needed piece, whose page is held.
-                    int key = (j0 + j) * kKeys + piece * kPiece;
-                    key = min(max(key, (first_key / kPiece) * kPiece), (last_key / kPiece) * kPiece);
-                    int page = table_row[key / p.page_size];
-                    if (page < 0 || page >= p.n_pages) {
-                        if (p.status != nullptr) {
-                            atomicOr(p.status, 4);
-                        }
-                        page = 0;
-                    }
+            }
+            // One warp instruction issues the tile's loads: lane = (piece, half, K or V).
+            __syncwarp();
+            {
+                const int piece = lane / (2 * kHalves), h = (lane / 2) % kHalves, is_v = lane & 1;
+                const int from = (j % (32 / kPieces)) * kPieces + (piece % kPieces);
+                const int key = __shfl_sync(0xffffffffu, my_key, from);
+                const int page = __shfl_sync(0xffffffffu, my_page, from);
+                if (lane < kPieces * kHalves * 2) {
                     const int row = ((page * 2) * p.n_kv_heads + kv_head) * p.page_size + key % p.page_size;
-                    for (int h = 0; h < kHalves; ++h) {
-                        const int at = h * (kKeys * 128) + piece * (kPiece * 128);
-                        tma_load_2d(k_s + at, &map_k, h * 64, row, &kv_full[stage]);
-                        tma_load_2d(v_s + at, &map_v, h * 64, row, &kv_full[stage]);
-                    }
+                    const int at = h * (kKeys * 128) + piece * (kPiece * 128);
+                    tma_load_2d((is_v ? v_s : k_s) + at, is_v ? &map_v : &map_k, h * 64, row, &kv_full[stage]);
                 }
             }
         }
@@ -213,33 +235,42 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
         }
     } else {
-        // ------------------------------------------------ softmax and output (warps 2..5)
-        const int lane_group = warp & 3;
+        // ------------------------------------------------ softmax and output (warps 2..9)
+        constexpr int kHalfKeys = kKeys / 2, kHalfDims = HD / 2;
+        const int wg = (warp - 2) >> 2;        // which half of the row's keys and dims
+        const int lane_group = warp & 3;       // the TMEM lanes this warp may read
         const int r = lane_group * 32 + lane;  // this thread's query row
         const uint32_t lane_bits = static_cast<uint32_t>(lane_group * 32) << 16;
         const int pos = pos0 + r;
         const int first = p.window > 0 ? pos - p.window + 1 : 0;
-        float o[HD];
+        float o[kHalfDims];
 #pragma unroll
-        for (int d = 0; d < HD; ++d) {
+        for (int d = 0; d < kHalfDims; ++d) {
             o[d] = 0.0f;
         }
         float m = -INFINITY, l = 0.0f, corr_prev = 1.0f;
         bool ok = true;
 
-        auto fold_pv = [&](int j, float corr) {  // o = o * corr + PV_j
+        auto fold_pv = [&](int j, float corr) {  // o = o * corr + this thread's half of PV_j
             const int b = j & 1;
             if (!mbar_wait(&pv_full[b], (j >> 1) & 1, &abort_flag)) {
                 return false;
             }
             tcgen05_fence_after();
+            {
+                // all of this thread's PV columns in flight, then one wait
+                uint32_t v[kHalfDims / 32][32];
 #pragma unroll
-            for (int c0 = 0; c0 < HD; c0 += 16) {
-                float v[16];
-                tcgen05_ld16(tmem_pv + lane_bits + b * kColsPV + c0, v);
+                for (int g = 0; g < kHalfDims / 32; ++g) {
+                    tcgen05_ld32_nowait(tmem_pv + lane_bits + b * kColsPV + wg * kHalfDims + 32 * g, v[g]);
+                }
+                tcgen05_wait_ld();
 #pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    o[c0 + c] = fmaf(o[c0 + c], corr, v[c]);
+                for (int g = 0; g < kHalfDims / 32; ++g) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        o[32 * g + c] = fmaf(o[32 * g + c], corr, __uint_as_float(v[g][c]));
+                    }
                 }
             }
             tcgen05_fence_before();
@@ -257,14 +288,15 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 break;
             }
             tcgen05_fence_after();
-            float s[kKeys];
+            float s[kHalfKeys];
+            {
+                static_assert(kHalfKeys == 32, "one 32-column load per thread");
+                uint32_t v[32];
+                tcgen05_ld32_nowait(tmem_s + lane_bits + b * kColsS + wg * kHalfKeys, v);
+                tcgen05_wait_ld();
 #pragma unroll
-            for (int c0 = 0; c0 < kKeys; c0 += 16) {
-                float v[16];
-                tcgen05_ld16(tmem_s + lane_bits + b * kColsS + c0, v);
-#pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    s[c0 + c] = v[c];
+                for (int c = 0; c < 32; ++c) {
+                    s[c] = __uint_as_float(v[c]);
                 }
             }
             tcgen05_fence_before();
@@ -277,32 +309,36 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             float tile_max = -INFINITY;
             if (edge) {
 #pragma unroll
-                for (int c = 0; c < kKeys; ++c) {
-                    const int key = key0 + c;
+                for (int c = 0; c < kHalfKeys; ++c) {
+                    const int key = key0 + wg * kHalfKeys + c;
                     s[c] = (key <= pos && key >= first) ? s[c] * p.scale_log2 : -INFINITY;
                     tile_max = fmaxf(tile_max, s[c]);
                 }
             } else {
 #pragma unroll
-                for (int c = 0; c < kKeys; ++c) {
+                for (int c = 0; c < kHalfKeys; ++c) {
                     s[c] *= p.scale_log2;
                     tile_max = fmaxf(tile_max, s[c]);
                 }
             }
+            // The row's maximum over both halves: exchange through shared memory.
+            half_max[b][wg * kRows + r] = tile_max;
+            asm volatile("bar.sync 2, 256;" ::: "memory");
+            tile_max = fmaxf(tile_max, half_max[b][(wg ^ 1) * kRows + r]);
             const float m_new = fmaxf(m, tile_max);
             const float base = m_new == -INFINITY ? 0.0f : m_new;
             const float corr = ex2(m - base);
             m = m_new;
             float sum = 0.0f;
-            uint32_t packed[kKeys / 2];
+            uint32_t packed[kHalfKeys / 2];
 #pragma unroll
-            for (int c = 0; c < kKeys; c += 2) {
+            for (int c = 0; c < kHalfKeys; c += 2) {
                 const float p0 = ex2(s[c] - base), p1 = ex2(s[c + 1] - base);
                 sum += p0 + p1;
                 const __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
                 packed[c / 2] = *reinterpret_cast<const uint32_t*>(&pair);
             }
-            l = l * corr + sum;
+            l = l * corr + sum;  // this thread's half of the row sum; the halves meet at the end
             // P_j into its buffer (free once PV_{j-2} has read it), row r, swizzled.
             if (!mbar_wait(&p_free[b], ((j >> 1) & 1) ^ 1u, &abort_flag)) {
                 ok = false;
@@ -310,8 +346,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
             unsigned char* p_row = p_s + b * kBytesP + r * 128;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) * 16)) =
+            for (int c = 0; c < kHalfKeys / 8; ++c) {
+                const int chunk = wg * (kHalfKeys / 8) + c;
+                *reinterpret_cast<uint4*>(p_row + ((chunk ^ (r & 7)) * 16)) =
                     make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -328,11 +365,16 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         if (ok && n_tiles > 0) {
             ok = fold_pv(n_tiles - 1, corr_prev);
         }
+        // The row sum is the sum of the two halves' sums (both followed the same maxima).
+        half_max[0][wg * kRows + r] = l;
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        l += half_max[0][(wg ^ 1) * kRows + r];
         if (ok && r < n_rows) {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            __nv_bfloat16* dst = p.out + (row0 + r) * p.out_row_stride + static_cast<int64_t>(head) * HD;
+            __nv_bfloat16* dst = p.out + (row0 + r) * p.out_row_stride + static_cast<int64_t>(head) * HD +
+                wg * kHalfDims;
 #pragma unroll
-            for (int d = 0; d < HD; d += 8) {
+            for (int d = 0; d < kHalfDims; d += 8) {
                 uint32_t w[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
