@@ -1,0 +1,74 @@
+"""The engine at the Llama-3.1-8B layer sizes (two layers, the full 128,256-token
+vocabulary, llama3 RoPE scaling at its real parameters) against the plain
+implementation, in float32 and bfloat16: sizes at which an index that overflows, a
+tile that is dropped at the end of a wide matrix or a RoPE angle that loses
+precision would show. The prompt is cut into a long portion, a short one and
+single tokens, beside a second request."""
+
+import pytest
+import torch
+
+import plain_llama
+from harness import TOLERANCE
+
+pytestmark = pytest.mark.gpu
+
+CONFIG = {
+    "architectures": ["LlamaForCausalLM"],
+    "num_hidden_layers": 2,
+    "hidden_size": 4096,
+    "num_attention_heads": 32,
+    "num_key_value_heads": 8,
+    "head_dim": 128,
+    "intermediate_size": 14336,
+    "vocab_size": 128256,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False,
+}
+
+
+@pytest.fixture(scope="module")
+def weights():
+    import tiny
+
+    return tiny.random_weights(CONFIG, seed=3, dtype=torch.bfloat16)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_llama_8b_layer_sizes(weights, dtype):
+    from pulsarlm_b200 import models  # noqa: F401
+    from pulsarlm_b200.cache.manager import CacheManager
+    from pulsarlm_b200.config.registry import read_model_config
+    from pulsarlm_b200.engine.runner import ModelRunner, StepEntry
+    from pulsarlm_b200.models.model import Model
+    from pulsarlm_b200.weights.loader import check_tensors
+
+    device = torch.device("cuda:0")
+    torch_dtype = torch.float32 if dtype == "float32" else torch.bfloat16
+    arch, cfg = read_model_config(CONFIG)
+    model = Model(arch.describe(cfg), torch_dtype, device)
+    model.load(check_tensors("test", model.tensor_needs(), weights, torch_dtype, device))
+    runner = ModelRunner(model, CacheManager(model.cache_needs(), 16, 32, 2, torch_dtype, device))
+
+    gen = torch.Generator().manual_seed(1)
+    a = torch.randint(0, CONFIG["vocab_size"], (150,), generator=gen).tolist()
+    b = torch.randint(0, CONFIG["vocab_size"], (41,), generator=gen).tolist()
+    want = [0, 63, 129]
+    rows = {}
+    out = runner.step([StepEntry("a", a[:130], want)])
+    rows.update({("a", w): out[i] for i, w in enumerate(want)})
+    out = runner.step([StepEntry("b", b[:38], [37]), StepEntry("a", a[130:147], [16])])
+    rows[("b", 37)], rows[("a", 146)] = out[0], out[1]
+    for i in range(147, 150):
+        out = runner.step([StepEntry("a", a[i:i + 1], [0]), StepEntry("b", b[i - 109:i - 108], [0])])
+        rows[("a", i)], rows[("b", i - 109)] = out[0], out[1]
+    runner.check_status()
+
+    ref = {"a": plain_llama.forward(CONFIG, weights, a, dtype=torch.float32),
+           "b": plain_llama.forward(CONFIG, weights, b, dtype=torch.float32)}
+    for (request, position), got in rows.items():
+        err = plain_llama.max_relative_error(got.cpu(), ref[request][position])
+        assert err < TOLERANCE[dtype], (request, position, err)
