@@ -52,6 +52,11 @@ class _Group:
     layers: list[int]
     pool: PagePool
     tensor: torch.Tensor | None
+    # attention mass, when measured: accumulators and this step's sums
+    mass_sum: torch.Tensor | None = None     # [layers, pages, query heads]
+    weight_sum: torch.Tensor | None = None   # [layers, pages]
+    step_mass: torch.Tensor | None = None
+    step_weight: torch.Tensor | None = None
 
 
 @dataclasses.dataclass
@@ -67,11 +72,21 @@ _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": 
 
 class CacheManager:
     def __init__(self, needs: list, page_size: int, n_pages: int, max_requests: int, dtype: torch.dtype,
-                 device: torch.device | str | None, allocate: bool = True):
+                 device: torch.device | str | None, allocate: bool = True, mass_decay: float | None = None):
         """needs: per layer KVCacheNeed, StateNeed or None. n_pages: pages of every
-        group's pool. allocate=False keeps the bookkeeping only (no tensors)."""
+        group's pool. allocate=False keeps the bookkeeping only (no tensors).
+        mass_decay: when given (0 < a <= 1), per-page attention-mass accumulators are
+        kept: each step the attention kernel adds, for every page a query attends,
+        w * (the query's largest scaled score in the page) per head and w per page,
+        with w = a (1 - a)^age for the query `age` tokens before the end of its
+        portion; before a step's sums are added, what a request's pages hold is
+        scaled by (1 - a)^(tokens in the step)
+        (pulsarlm-core/src/engine/eviction.cpp:115-138). Nothing is evicted."""
         if page_size <= 0 or n_pages <= 0 or max_requests <= 0:
             raise ValueError("page_size, n_pages and max_requests must be positive")
+        if mass_decay is not None and not 0.0 < mass_decay <= 1.0:
+            raise ValueError("mass_decay must be in (0, 1]")
+        self.mass_decay = mass_decay
         self.page_size = page_size
         self.n_pages = n_pages
         self.max_requests = max_requests
@@ -100,11 +115,20 @@ class CacheManager:
                 n = group.need
                 group.tensor = torch.zeros(
                     (len(group.layers), n_pages, 2, n.n_kv_heads, page_size, n.head_dim), dtype=dtype, device=device)
+            if mass_decay is not None:
+                for group in self.groups:
+                    shape = (len(group.layers), n_pages, max(1, group.need.n_heads))
+                    group.mass_sum = torch.zeros(shape, dtype=torch.float32, device=device)
+                    group.step_mass = torch.zeros(shape, dtype=torch.float32, device=device)
+                    group.weight_sum = torch.zeros(shape[:2], dtype=torch.float32, device=device)
+                    group.step_weight = torch.zeros(shape[:2], dtype=torch.float32, device=device)
             for layer, need in self.state_layers.items():
                 self.states[layer] = torch.zeros((max_requests, *need.shape), dtype=_STATE_DTYPES[need.dtype],
                                                  device=device)
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self._requests: dict[object, _Request] = {}
+        # Pages taken since the last step (their mass accumulators must restart at zero).
+        self._fresh: list[set] = [set() for _ in self.groups]
 
     # ------------------------------------------------------------------ bindings
     def bindings(self) -> list:
@@ -114,7 +138,9 @@ class CacheManager:
         for layer, g in self.layer_group.items():
             group = self.groups[g]
             where = group.layers.index(layer)
-            out[layer] = KVBinding(g, group.tensor[where, :, 0], group.tensor[where, :, 1], self.page_size)
+            out[layer] = KVBinding(g, group.tensor[where, :, 0], group.tensor[where, :, 1], self.page_size,
+                                   group.step_mass[where] if group.step_mass is not None else None,
+                                   group.step_weight[where] if group.step_weight is not None else None)
         for layer in self.state_layers:
             out[layer] = StateBinding(self.states[layer])
         return out
@@ -170,7 +196,10 @@ class CacheManager:
         if any(m > g.pool.free_count for m, g in zip(missing, self.groups)):
             return False
         for m, g in zip(missing, self.groups):
-            r.pages[g.index].extend(g.pool.take(m))
+            taken = g.pool.take(m)
+            r.pages[g.index].extend(taken)
+            if self.mass_decay is not None:
+                self._fresh[g.index].update(taken)
         return True
 
     def commit(self, request, new_len: int) -> None:
@@ -213,6 +242,35 @@ class CacheManager:
 
     def held_pages(self, request, group: int) -> list[int]:
         return [p for p in self._requests[request].pages[group] if p >= 0]
+
+    # ------------------------------------------------------------------ attention mass
+    def take_fresh_pages(self, group: int) -> set:
+        """Pages of `group` taken since the last call: their accumulators hold a former
+        owner's sums until the next fold clears them."""
+        fresh, self._fresh[group] = self._fresh[group], set()
+        return fresh
+
+    def fold_mass(self, retained: dict[int, torch.Tensor]) -> None:
+        """After a step: accumulators = accumulators * retained[page] + the step's sums;
+        the step's sums are cleared. retained[g]: fp32 [pages] on the device (1 for
+        pages no entry of the step owns, 0 for pages taken in this step)."""
+        for group in self.groups:
+            if group.mass_sum is None:
+                continue
+            keep = retained[group.index]
+            group.mass_sum.mul_(keep[None, :, None]).add_(group.step_mass)
+            group.weight_sum.mul_(keep[None, :]).add_(group.step_weight)
+            group.step_mass.zero_()
+            group.step_weight.zero_()
+
+    def page_mass(self, request, group: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+        """(mass_sum [layers, pages of the request, heads], weight_sum [layers, pages])
+        of the pages the request holds in `group`, in the request's page order."""
+        g = self.groups[group]
+        if g.mass_sum is None:
+            raise CacheError("attention mass is not being measured (mass_decay was not given)")
+        pages = torch.tensor(self.held_pages(request, group), dtype=torch.long, device=g.mass_sum.device)
+        return g.mass_sum[:, pages], g.weight_sum[:, pages]
 
     # ------------------------------------------------------------------ figures
     def stats(self) -> dict:

@@ -71,7 +71,9 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
                                       const int32_t* __restrict__ table, int table_width,
                                       const int32_t* __restrict__ pos, const int32_t* __restrict__ entry,
                                       scalar_t* __restrict__ out, int64_t out_row_stride, int n_heads, int group,
-                                      int head_dim, int window, float scale, int32_t* status) {
+                                      int head_dim, int window, float scale, float* __restrict__ mass_sum,
+                                      float* __restrict__ weight_sum, const float* __restrict__ query_weights,
+                                      int32_t* status) {
     extern __shared__ float q_shared[];  // [warps][head_dim]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const int t = blockIdx.x;
@@ -97,6 +99,23 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
         for (int i = 0; i < kMaxAcc; ++i) {
             acc[i] = 0.0f;
         }
+        // Attention mass (optional): per page and head, this query's weight times its
+        // largest scaled score over the page's keys it attends; per page, the weight once.
+        int mass_page = -1;
+        float mass_max = -INFINITY;
+        auto add_mass = [&](int view_page, float page_max) {
+            if (view_page < 0 || lane != 0 || !(page_max > -INFINITY)) {
+                return;
+            }
+            const int page = row[view_page];
+            if (page >= 0 && page < n_pages) {
+                const float w = query_weights != nullptr ? query_weights[t] : 1.0f;
+                atomicAdd(mass_sum + static_cast<int64_t>(page) * n_heads + h, w * page_max);
+                if (h == 0) {
+                    atomicAdd(weight_sum + page, w);
+                }
+            }
+        };
 
         for (int base = (first / 32) * 32; base <= p; base += 32) {
             const int j = base + lane;
@@ -111,6 +130,21 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
                     s = dot_row<scalar_t>(qs, k_pool + offset, head_dim) * scale;
                 } else if (status != nullptr) {
                     atomicOr(status, 4);
+                }
+            }
+            if (mass_sum != nullptr) {
+                // Largest scaled score per page; a page may span several chunks, so the
+                // running maximum is flushed only when the walk leaves the page.
+                const int last = min(base + 31, p);
+                for (int pg = max(base, first) / page_size; pg <= last / page_size; ++pg) {
+                    const float chunk_max = pl_warp_max(valid && j / page_size == pg ? s : -INFINITY);
+                    if (pg != mass_page) {
+                        add_mass(mass_page, mass_max);
+                        mass_page = pg;
+                        mass_max = chunk_max;
+                    } else {
+                        mass_max = fmaxf(mass_max, chunk_max);
+                    }
                 }
             }
             const float m_new = fmaxf(m, pl_warp_max(s));
@@ -144,6 +178,9 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
             m = m_new;
         }
 
+        if (mass_sum != nullptr) {
+            add_mass(mass_page, mass_max);
+        }
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
         scalar_t* orow = out + t * out_row_stride + static_cast<int64_t>(h) * head_dim;
 #pragma unroll
@@ -161,13 +198,17 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
 // q [T, n_heads, head_dim] with q_row_stride elements between tokens; out likewise
 // with out_row_stride. Token t is the query at position pos[t] of the request whose
 // block-table row is table[entry[t]]; it attends keys max(0, pos - window + 1) ..
-// pos (window <= 0: from 0). Pools as in pl_rope_kv_write.
+// pos (window <= 0: from 0). Pools as in pl_rope_kv_write. mass_sum [n_pages,
+// n_heads] and weight_sum [n_pages] (fp32, may be nullptr) are added to: for every
+// page a query attends, query_weights[t] (1 when nullptr) times the query's largest
+// scaled score in the page, per head, and the weight itself once per page
+// (pulsarlm-core/inc/pulsarlm/kernels/ops.hpp:150-160).
 PL_API int pl_attention_simt(const void* q, int64_t q_row_stride, const void* k_pool, const void* v_pool,
                              int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
                              const int32_t* table, int table_width, const int32_t* pos, const int32_t* entry,
                              void* out, int64_t out_row_stride, int n_tokens, int n_heads, int n_kv_heads,
-                             int head_dim, int window, float scale, int dtype, int32_t* status,
-                             cudaStream_t stream) {
+                             int head_dim, int window, float scale, int dtype, float* mass_sum, float* weight_sum,
+                             const float* query_weights, int32_t* status, cudaStream_t stream) {
     PL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && head_dim > 0 && page_size > 0,
                "attention: bad sizes tokens=%d heads=%d kv_heads=%d head_dim=%d page=%d", n_tokens, n_heads,
                n_kv_heads, head_dim, page_size);
@@ -176,6 +217,7 @@ PL_API int pl_attention_simt(const void* q, int64_t q_row_stride, const void* k_
     PL_REQUIRE(head_dim <= 32 * kMaxAcc, "attention: head_dim %d exceeds the supported maximum %d", head_dim,
                32 * kMaxAcc);
     PL_REQUIRE(n_kv_heads <= 65535, "attention: %d kv heads exceed the grid limit", n_kv_heads);
+    PL_REQUIRE(mass_sum == nullptr || weight_sum != nullptr, "attention: attention mass needs weight_sum too");
     if (n_tokens == 0) {
         return 0;
     }
@@ -188,7 +230,7 @@ PL_API int pl_attention_simt(const void* q, int64_t q_row_stride, const void* k_
             static_cast<const scalar_t*>(q), q_row_stride, static_cast<const scalar_t*>(k_pool),
             static_cast<const scalar_t*>(v_pool), page_stride, head_stride, page_size, n_pages, table, table_width,
             pos, entry, static_cast<scalar_t*>(out), out_row_stride, n_heads, group, head_dim, window, scale,
-            status);
+            mass_sum, weight_sum, query_weights, status);
     });
     PL_CHECK_LAUNCH("attention");
     return 0;

@@ -33,11 +33,12 @@ class Engine:
     def __init__(self, model, dtype="bfloat16", device="cuda:0", kv_cache_gib: float = 4.0,
                  page_size: int = DEFAULT_PAGE_SIZE, prefill_tokens_per_step: int = 256,
                  max_requests: int = 64, n_pages: int | None = None, stop_ids=None, seed: int | None = None,
-                 cuda_graphs: bool = True):
+                 cuda_graphs: bool = True, attention_mass_decay: float | None = None):
         """model: a model folder, a built Model, or a config.json dict (random
         weights from `seed`). kv_cache_gib sizes the page pools unless n_pages
         gives the number of pages outright. stop_ids default to config.json's
-        eos_token_id."""
+        eos_token_id. attention_mass_decay: measure per-page attention mass with this
+        decay (see CacheManager; slower: attention then runs on the CUDA cores)."""
         ops.require_device()
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
@@ -54,7 +55,8 @@ class Engine:
             probe = CacheManager(needs, page_size, 1, 1, self.dtype, None, allocate=False)
             per_page = max(1, probe.bytes_per_page())
             n_pages = max(1, int(kv_cache_gib * (1 << 30)) // per_page)
-        self.cache = CacheManager(needs, page_size, n_pages, max_requests, self.dtype, self.device)
+        self.cache = CacheManager(needs, page_size, n_pages, max_requests, self.dtype, self.device,
+                                  mass_decay=attention_mass_decay)
         self.runner = ModelRunner(self.model, self.cache)
         self.sampler = Sampler(self.device)
         stops = self.model.spec.eos_token_ids if stop_ids is None else stop_ids

@@ -62,7 +62,7 @@ class ModelRunner:
         # Replaying a captured step re-runs the capture's warm-up on the same tokens,
         # which is harmless for caches written by position but not for states updated
         # in place, so models with state slots step eagerly.
-        self.graphs_allowed = not cache.state_layers
+        self.graphs_allowed = not cache.state_layers and cache.mass_decay is None
         self.steps = 0
         self.tokens_run = 0
         self.graph_steps = 0
@@ -151,6 +151,24 @@ class ModelRunner:
         tables = [self.cache.table_rows(g.index, requests) for g in self.cache.groups]
         tile_array = np.array(tiles, dtype=np.int32).reshape(len(tiles), 4)
         arrays = [tokens, pos, entry, slots, np.array(want_rows, dtype=np.int32), tile_array, *tables]
+        decay = self.cache.mass_decay
+        if decay is not None:
+            # Query weights a (1 - a)^age within each portion, and per page what the
+            # accumulators keep: (1 - a)^tokens for pages the step's requests held, 0
+            # for pages taken for this step (they may hold a former owner's sums).
+            weights = np.empty(n_tokens, dtype=np.float32)
+            at = 0
+            for i in order:
+                n = len(entries[i].tokens)
+                weights[at : at + n] = decay * (1.0 - decay) ** np.arange(n - 1, -1, -1, dtype=np.float64)
+                at += n
+            arrays.append(weights.view(np.int32))
+            for g in self.cache.groups:
+                keep = np.ones(self.cache.n_pages, dtype=np.float32)
+                for e in entries:
+                    keep[self.cache.held_pages(e.request, g.index)] = (1.0 - decay) ** len(e.tokens)
+                keep[list(self.cache.take_fresh_pages(g.index))] = 0.0
+                arrays.append(keep.view(np.int32))
         dev = self._stage(arrays)
         batch = StepBatch(
             tokens=dev[0], pos=dev[1], entry=dev[2],
@@ -165,6 +183,11 @@ class ModelRunner:
             host_context_lens=[new_lens[i] for i in order],
             extras={"prefill_tiles": dev[5] if tiles else None},
         )
+        if decay is not None:
+            n_groups = len(self.cache.groups)
+            batch.extras["query_weights"] = dev[6 + n_groups].view(torch.float32)
+            batch.extras["mass_retained"] = {g.index: dev[7 + n_groups + i].view(torch.float32)
+                                             for i, g in enumerate(self.cache.groups)}
         return batch, new_lens
 
     # ------------------------------------------------------------------ the step
@@ -173,6 +196,8 @@ class ModelRunner:
         in the order of the entries and of each entry's `want`, or None."""
         batch, new_lens = self.prepare(entries)
         logits = self.model.forward(batch)
+        if self.cache.mass_decay is not None:
+            self.cache.fold_mass(batch.extras["mass_retained"])
         for e, new_len in zip(entries, new_lens):
             self.cache.commit(e.request, new_len)
         self.steps += 1

@@ -24,7 +24,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 8
+ABI_VERSION = 9
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -42,7 +42,7 @@ _SIGNATURES = {
     "pl_rope_kv_write": [_PTR, _PTR, _PTR, _I64, _PTR, _PTR, _PTR, _I32, _PTR, _PTR, _I64, _I64, _I32, _I32,
                          _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _PTR, _PTR],
     "pl_attention_simt": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
-                          _I32, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR],
+                          _I32, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR, _PTR, _PTR, _PTR],
     "pl_attention_decode": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
                             _I32, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR, _PTR],
     "pl_attention_decode_supports": [_I32, _I32, _I32, _I32],
@@ -268,10 +268,20 @@ def rope_kv_write(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | Non
 
 def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,
                    pos: torch.Tensor, entry: torch.Tensor, out: torch.Tensor, page_size: int, window: int | None,
-                   scale: float, status: torch.Tensor | None = None) -> None:
+                   scale: float, status: torch.Tensor | None = None, mass_sum: torch.Tensor | None = None,
+                   weight_sum: torch.Tensor | None = None, query_weights: torch.Tensor | None = None) -> None:
     """Causal paged attention; q and out [T, nh, hd] (row strides free), pools
-    [pages, nkv, page_size, hd]."""
-    _dev(q, k_pool, v_pool, table, pos, entry, out, status)
+    [pages, nkv, page_size, hd]. With mass_sum fp32 [pages, nh] and weight_sum fp32
+    [pages], the attention mass of every attended page is added to them
+    (query_weights fp32 [T], all 1 when None)."""
+    _dev(q, k_pool, v_pool, table, pos, entry, out, status, mass_sum, weight_sum, query_weights)
+    if mass_sum is not None:
+        assert mass_sum.dtype == torch.float32 and mass_sum.shape == (k_pool.shape[0], q.shape[1])
+        assert mass_sum.is_contiguous() and weight_sum is not None and weight_sum.dtype == torch.float32
+        assert weight_sum.shape == (k_pool.shape[0],) and weight_sum.is_contiguous()
+        if query_weights is not None:
+            assert query_weights.dtype == torch.float32 and query_weights.numel() == q.shape[0]
+            assert query_weights.is_contiguous()
     tokens, n_heads, head_dim = q.shape
     n_pages, n_kv = k_pool.shape[0], k_pool.shape[1]
     assert q.stride(2) == 1 and q.stride(1) == head_dim and out.stride(2) == 1 and out.stride(1) == head_dim
@@ -282,7 +292,8 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
     assert table.dim() == 2 and table.is_contiguous()
     _call("pl_attention_simt", _p(q), q.stride(0), _p(k_pool), _p(v_pool), k_pool.stride(0), k_pool.stride(1),
           page_size, n_pages, _p(table), table.shape[1], _p(pos), _p(entry), _p(out), out.stride(0), tokens,
-          n_heads, n_kv, head_dim, int(window or 0), float(scale), _code(q.dtype), _p(status), _stream())
+          n_heads, n_kv, head_dim, int(window or 0), float(scale), _code(q.dtype), _p(mass_sum), _p(weight_sum),
+          _p(query_weights), _p(status), _stream())
 
 
 def attention_decode_supports(head_dim: int, group: int, page_size: int, dtype: torch.dtype) -> bool:

@@ -23,6 +23,10 @@ class KVBinding:
     k_pool: torch.Tensor
     v_pool: torch.Tensor
     page_size: int
+    # This step's attention mass [pages, n_heads] and weights [pages] of the layer,
+    # when the cache manager measures it (else None).
+    mass_sum: torch.Tensor | None = None
+    weight_sum: torch.Tensor | None = None
 
 
 _SM_COUNT: dict = {}
@@ -96,7 +100,7 @@ class Attention(Part):
     def cache_need(self) -> KVCacheNeed | None:
         if self.cache_from is not None:
             return None
-        return KVCacheNeed(self.n_kv, self.head_dim, self.window)
+        return KVCacheNeed(self.n_kv, self.head_dim, self.window, self.n_heads)
 
     def bind_cache(self, binding: KVBinding) -> None:
         self.cache = binding
@@ -129,6 +133,12 @@ class Attention(Part):
         everything else (float32, unusual shapes) goes to the CUDA-core kernel."""
         cache = self.cache
         tokens = q.shape[0]
+        if cache.mass_sum is not None and self.cache_from is None and batch.extras.get("query_weights") is not None:
+            # Measuring attention mass: the CUDA-core kernel writes it beside the output.
+            ops.attention_simt(q, cache.k_pool, cache.v_pool, table, batch.pos, batch.entry, out, cache.page_size,
+                               self.window, self.scale, batch.status, cache.mass_sum, cache.weight_sum,
+                               batch.extras["query_weights"])
+            return
         n_decode = 0
         if self._decode_kernel is None:
             self._decode_kernel = ops.attention_decode_supports(

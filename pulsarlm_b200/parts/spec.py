@@ -69,11 +69,14 @@ class TensorNeed:
 class KVCacheNeed:
     """A mixer that keeps keys and values: per token `n_kv_heads * head_dim` keys
     and as many values. `window` = None keeps every token; a number keeps only the
-    last `window` tokens readable, and pages wholly before them are given back."""
+    last `window` tokens readable, and pages wholly before them are given back.
+    `n_heads` is the number of query heads that read the cache; the cache manager
+    sizes the optional per-page attention-mass accumulators by it."""
 
     n_kv_heads: int
     head_dim: int
     window: int | None = None
+    n_heads: int = 0
 
 
 @dataclasses.dataclass(frozen=True)

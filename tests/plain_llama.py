@@ -105,7 +105,8 @@ def embed(table: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
 
 
 def causal_attention(
-    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, window: int | None = None
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, window: int | None = None,
+    scores_out: list | None = None
 ) -> torch.Tensor:
     """Dense causal softmax attention; q [T, nh, hd], k and v [T, nkv, hd] -> [T, nh, hd].
 
@@ -126,6 +127,8 @@ def causal_attention(
     if window is not None:
         keep = keep & (j > i - window)
     scores = scores.masked_fill(~keep, float("-inf"))
+    if scores_out is not None:
+        scores_out.append(scores)  # [heads, queries, keys], scaled, -inf where unattended
     probabilities = torch.softmax(scores, dim=-1)
     return torch.matmul(probabilities, vh).transpose(0, 1)
 
@@ -137,7 +140,8 @@ def swiglu_mlp(h: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torc
 
 
 def attention_block(
-    h: torch.Tensor, w: dict, prefix: str, cfg: dict, positions: torch.Tensor, window: int | None = None
+    h: torch.Tensor, w: dict, prefix: str, cfg: dict, positions: torch.Tensor, window: int | None = None,
+    scores_out: list | None = None
 ) -> torch.Tensor:
     """pulsarlm-core/src/engine/model/llama.cpp:61-82: bias-free q/k/v, RoPE on q and
     k, scale 1/sqrt(head_dim), o projection."""
@@ -152,13 +156,14 @@ def attention_block(
     v = (h @ w[prefix + "self_attn.v_proj.weight"].T).view(tokens, n_kv, hd)
     q = rope_rotate(q, positions, inv_freq)
     k = rope_rotate(k, positions, inv_freq)
-    o = causal_attention(q, k, v, 1.0 / math.sqrt(hd), window)
+    o = causal_attention(q, k, v, 1.0 / math.sqrt(hd), window, scores_out)
     return o.reshape(tokens, n_heads * hd) @ w[prefix + "self_attn.o_proj.weight"].T
 
 
 # --------------------------------------------------------------------------- model
 
-def forward(cfg: dict, weights: dict, tokens, dtype: torch.dtype = torch.float64) -> torch.Tensor:
+def forward(cfg: dict, weights: dict, tokens, dtype: torch.dtype = torch.float64,
+            scores_out: list | None = None) -> torch.Tensor:
     """Logits [tokens, vocab] of one whole sequence starting at position 0.
 
     pulsarlm-core/src/engine/model/llama.cpp:84-94: embed; per layer
@@ -174,7 +179,7 @@ def forward(cfg: dict, weights: dict, tokens, dtype: torch.dtype = torch.float64
     for layer in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{layer}."
         h = rms_norm(x, w[p + "input_layernorm.weight"], eps)
-        x = x + attention_block(h, w, p, cfg, positions)
+        x = x + attention_block(h, w, p, cfg, positions, None, scores_out)
         h = rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
         x = x + swiglu_mlp(
             h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"]
@@ -194,6 +199,33 @@ def greedy_generate(cfg: dict, weights: dict, prompt, n_new: int, dtype=torch.fl
         out.append(best)
         seq.append(best)
     return out
+
+
+def page_attention_mass(scores: torch.Tensor, portions: list, page_size: int, decay: float):
+    """Per-page attention mass of one layer after feeding the sequence in `portions`
+    ([first, last) position ranges, in order). scores: [heads, T, T] scaled, -inf
+    where unattended. Returns (mass_sum [pages, heads], weight_sum [pages]).
+
+    pulsarlm-core/tests/model/test_llama.cpp:150-178: a step adds, for each query p
+    of the portion and each page it attends, w_p * (its largest score in the page)
+    per head and w_p per page, w_p = decay * (1 - decay)^(last - 1 - p);
+    src/engine/eviction.cpp:122-138: before a step's sums are added, the
+    accumulators are scaled by (1 - decay)^(tokens in the step)."""
+    heads, total, _ = scores.shape
+    pages = -(-total // page_size)
+    mass = torch.zeros(pages, heads, dtype=torch.float64)
+    weight = torch.zeros(pages, dtype=torch.float64)
+    for first, last in portions:
+        retained = (1.0 - decay) ** (last - first)
+        mass *= retained
+        weight *= retained
+        for p in range(first, last):
+            w = decay * (1.0 - decay) ** (last - 1 - p)
+            for page in range(p // page_size + 1):
+                keys = scores[:, p, page * page_size : min((page + 1) * page_size, p + 1)]
+                mass[page] += w * keys.max(dim=1).values
+                weight[page] += w
+    return mass, weight
 
 
 # --------------------------------------------------------------------------- sampling
