@@ -14,6 +14,10 @@ A request's life: `open` (a slot) -> `reserve(new_len)` before each step (pages
 for the step's tokens, all groups or none) -> `commit(new_len)` after it (length
 recorded, passed window pages given back) -> `close` (everything given back).
 
+The bookkeeping (pools, slots, page lists) is C++: class CacheBook in
+pulsarlm_b200/csrc_host/host_core.cpp. This class owns the tensors, groups the
+layers, and maps the caller's request keys to the book's integer handles.
+
 The reference keeps one byte pool cut into per-layer "lines"
 (pulsarlm-core/src/engine/kv_cache.cpp:96-164, 310-423), releases lines at
 finish (src/engine/executor.cpp:695-700) and pages that slid out of a window
@@ -28,9 +32,12 @@ import dataclasses
 import numpy as np
 import torch
 
+import ctypes
+
+from ..host import core
 from ..parts.attention import KVBinding
 from ..parts.spec import KVCacheNeed, StateNeed
-from .pages import PagePool
+from .pages import GroupPoolView, PageError
 
 
 class CacheError(RuntimeError):
@@ -50,21 +57,13 @@ class _Group:
     index: int
     need: KVCacheNeed
     layers: list[int]
-    pool: PagePool
+    pool: GroupPoolView | None
     tensor: torch.Tensor | None
     # attention mass, when measured: accumulators and this step's sums
     mass_sum: torch.Tensor | None = None     # [layers, pages, query heads]
     weight_sum: torch.Tensor | None = None   # [layers, pages]
     step_mass: torch.Tensor | None = None
     step_weight: torch.Tensor | None = None
-
-
-@dataclasses.dataclass
-class _Request:
-    slot: int
-    length: int = 0
-    # Per group: page id of every page index so far, -1 once given back.
-    pages: list[list[int]] = dataclasses.field(default_factory=list)
 
 
 _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
@@ -101,7 +100,7 @@ class CacheManager:
             if isinstance(need, KVCacheNeed):
                 group = by_need.get(need)
                 if group is None:
-                    group = _Group(len(self.groups), need, [], PagePool(n_pages), None)
+                    group = _Group(len(self.groups), need, [], None, None)
                     by_need[need] = group
                     self.groups.append(group)
                 self.layer_group[layer] = group.index
@@ -125,10 +124,57 @@ class CacheManager:
             for layer, need in self.state_layers.items():
                 self.states[layer] = torch.zeros((max_requests, *need.shape), dtype=_STATE_DTYPES[need.dtype],
                                                  device=device)
-        self._free_slots = list(range(max_requests - 1, -1, -1))
-        self._requests: dict[object, _Request] = {}
-        # Pages taken since the last step (their mass accumulators must restart at zero).
-        self._fresh: list[set] = [set() for _ in self.groups]
+        self._lib = core.library()
+        windows = (ctypes.c_int32 * max(1, len(self.groups)))(
+            *[g.need.window if g.need.window is not None else -1 for g in self.groups])
+        self._book = self._lib.plh_cache_create(len(self.groups), windows, page_size, n_pages, max_requests,
+                                                int(mass_decay is not None))
+        for group in self.groups:
+            group.pool = GroupPoolView(self._lib, self._book, group.index, n_pages)
+        # The caller's request keys (any hashable) <-> the book's integer handles.
+        self._handles: dict[object, int] = {}
+        self._keys: dict[int, object] = {}
+        self._next_handle = 1
+        self._row = (ctypes.c_int32 * max(1, n_pages))()
+
+    def __del__(self):
+        if getattr(self, "_book", None):
+            self._lib.plh_cache_destroy(self._book)
+            self._book = None
+
+    # ------------------------------------------------------------------ handles
+    @property
+    def book(self):
+        """The C++ CacheBook (for the scheduler core, which works on the same book)."""
+        return self._book
+
+    def handle(self, request) -> int:
+        """The integer the book knows `request` by (made on first use)."""
+        h = self._handles.get(request)
+        if h is None:
+            h = self._handles[request] = self._next_handle
+            self._keys[h] = request
+            self._next_handle += 1
+        return h
+
+    def key_of(self, handle: int):
+        return self._keys[handle]
+
+    def forget(self, request) -> None:
+        """Drops the key <-> handle entry of a request that is closed for good."""
+        h = self._handles.pop(request, None)
+        if h is not None:
+            self._keys.pop(h, None)
+
+    def _known(self, request) -> int:
+        h = self._handles.get(request)
+        if h is None or not self._lib.plh_cache_is_open(self._book, h):
+            raise KeyError(request)
+        return h
+
+    def zero_states(self, slot: int) -> None:
+        for states in self.states.values():
+            states[slot].zero_()
 
     # ------------------------------------------------------------------ bindings
     def bindings(self) -> list:
@@ -153,102 +199,98 @@ class CacheManager:
     # ------------------------------------------------------------------ requests
     def open(self, request) -> int | None:
         """A slot for a new request (its states zeroed), or None when all are taken."""
-        if request in self._requests:
+        slot = self._lib.plh_cache_open(self._book, self.handle(request))
+        if slot == core.ALREADY_OPEN:
             raise CacheError(f"request {request!r} is already open")
-        if not self._free_slots:
+        if slot < 0:
             return None
-        slot = self._free_slots.pop()
-        self._requests[request] = _Request(slot, 0, [[] for _ in self.groups])
-        for states in self.states.values():
-            states[slot].zero_()
+        self.zero_states(slot)
         return slot
 
     def is_open(self, request) -> bool:
-        return request in self._requests
+        h = self._handles.get(request)
+        return h is not None and bool(self._lib.plh_cache_is_open(self._book, h))
 
     def slot(self, request) -> int:
-        return self._requests[request].slot
+        return self._lib.plh_cache_slot(self._book, self._known(request))
 
     def length(self, request) -> int:
-        return self._requests[request].length
-
-    def _first_needed_page(self, group: _Group, length: int) -> int:
-        """Index of the first page a query at position >= `length` can still read."""
-        if group.need.window is None:
-            return 0
-        first_key = max(0, length - group.need.window + 1)
-        return first_key // self.page_size
+        return self._lib.plh_cache_length(self._book, self._known(request))
 
     def pages_needed(self, request, new_len: int) -> int:
         """Pages `reserve(request, new_len)` would take, summed over groups."""
-        r = self._requests[request]
-        n_pages = -(-new_len // self.page_size)
-        return sum(max(0, n_pages - len(r.pages[g.index])) for g in self.groups)
+        return self._lib.plh_cache_pages_needed(self._book, self._known(request), new_len)
 
     def reserve(self, request, new_len: int) -> bool:
         """Pages so that tokens [0, new_len) have a place in every group. Takes all
         that is missing or nothing; False when some pool has too few free pages."""
-        r = self._requests[request]
-        if new_len < r.length:
-            raise CacheError(f"request {request!r} cannot shrink from {r.length} to {new_len} tokens")
-        n_pages = -(-new_len // self.page_size)
-        missing = [max(0, n_pages - len(r.pages[g.index])) for g in self.groups]
-        if any(m > g.pool.free_count for m, g in zip(missing, self.groups)):
-            return False
-        for m, g in zip(missing, self.groups):
-            taken = g.pool.take(m)
-            r.pages[g.index].extend(taken)
-            if self.mass_decay is not None:
-                self._fresh[g.index].update(taken)
-        return True
+        code = self._lib.plh_cache_reserve(self._book, self._known(request), new_len)
+        if code == core.SHRINK:
+            raise CacheError(f"request {request!r} cannot shrink from {self.length(request)} to {new_len} tokens")
+        if code < 0:
+            raise CacheError(f"request {request!r}: reserve({new_len}) failed with code {code}")
+        return code == core.OK
 
     def commit(self, request, new_len: int) -> None:
         """Records that tokens [0, new_len) are cached; gives back the pages of
         windowed groups that no later query can reach."""
-        r = self._requests[request]
-        if new_len < r.length or any(-(-new_len // self.page_size) > len(p) for p in r.pages):
+        code = self._lib.plh_cache_commit(self._book, self._known(request), new_len)
+        if code == core.NOT_RESERVED:
             raise CacheError(f"request {request!r}: commit({new_len}) without pages reserved")
-        r.length = new_len
-        for g in self.groups:
-            pages = r.pages[g.index]
-            first = self._first_needed_page(g, new_len)
-            passed = [i for i in range(min(first, len(pages))) if pages[i] >= 0]
-            if passed:
-                g.pool.give([pages[i] for i in passed])
-                for i in passed:
-                    pages[i] = -1
+        if code == core.BAD_PAGE:
+            raise PageError(f"request {request!r}: a page was given back twice")
+        if code < 0:
+            raise CacheError(f"request {request!r}: commit({new_len}) failed with code {code}")
 
     def close(self, request) -> None:
         """Gives back every page and the slot of the request."""
-        r = self._requests.pop(request)
-        for g in self.groups:
-            g.pool.give([p for p in r.pages[g.index] if p >= 0])
-        self._free_slots.append(r.slot)
+        code = self._lib.plh_cache_close(self._book, self._known(request))
+        self.forget(request)
+        if code == core.BAD_PAGE:
+            raise PageError(f"request {request!r}: a page was given back twice")
 
     def open_requests(self) -> list:
-        return list(self._requests)
+        out = (ctypes.c_int64 * self.max_requests)()
+        n = self._lib.plh_cache_open_requests(self._book, out, self.max_requests)
+        return [self._keys[h] for h in out[:n]]
 
     # ------------------------------------------------------------------ tables
     def table_rows(self, group: int, requests: list, width_multiple: int = 8) -> np.ndarray:
         """int32 [len(requests), W]: each request's page ids of `group`, -1 where it
         holds none; W is the longest row rounded up to `width_multiple`."""
-        rows = [self._requests[r].pages[group] for r in requests]
-        width = max([len(row) for row in rows] + [1])
-        width = -(-width // width_multiple) * width_multiple
-        table = np.full((len(rows), width), -1, dtype=np.int32)
-        for i, row in enumerate(rows):
-            table[i, : len(row)] = row
+        handles = [self._known(r) for r in requests]
+        longest = 1
+        for h in handles:
+            longest = max(longest, self._lib.plh_cache_table_row(self._book, group, h, self._row, 0))
+        width = -(-longest // width_multiple) * width_multiple
+        table = np.empty((len(handles), width), dtype=np.int32)
+        self.fill_tables(group, handles, table, None)
         return table
 
+    def fill_tables(self, group: int, handles: list[int], table: np.ndarray, slots: np.ndarray | None) -> int:
+        """Writes the block-table rows of `handles` into `table` (int32 [n, W], C order;
+        -1 where no page) and their slots into `slots`; returns the longest row."""
+        n = len(handles)
+        ids = (ctypes.c_int64 * max(1, n))(*handles)
+        longest = self._lib.plh_cache_fill_tables(
+            self._book, group, ids, n, table.ctypes.data_as(ctypes.c_void_p), table.shape[1],
+            slots.ctypes.data_as(ctypes.c_void_p) if slots is not None else None)
+        if longest < 0:
+            raise CacheError(f"fill_tables failed with code {longest}")
+        if longest > table.shape[1]:
+            raise CacheError(f"a block-table row of {longest} pages does not fit the table's width {table.shape[1]}")
+        return longest
+
     def held_pages(self, request, group: int) -> list[int]:
-        return [p for p in self._requests[request].pages[group] if p >= 0]
+        n = self._lib.plh_cache_held_pages(self._book, group, self._known(request), self._row, self.n_pages)
+        return list(self._row[:n])
 
     # ------------------------------------------------------------------ attention mass
-    def take_fresh_pages(self, group: int) -> set:
+    def take_fresh_pages(self, group: int) -> list[int]:
         """Pages of `group` taken since the last call: their accumulators hold a former
         owner's sums until the next fold clears them."""
-        fresh, self._fresh[group] = self._fresh[group], set()
-        return fresh
+        n = self._lib.plh_cache_take_fresh(self._book, group, self._row, self.n_pages)
+        return list(self._row[:n])
 
     def fold_mass(self, retained: dict[int, torch.Tensor]) -> None:
         """After a step: accumulators = accumulators * retained[page] + the step's sums;
@@ -282,9 +324,9 @@ class CacheManager:
                 for g in self.groups
             ],
             "slots": self.max_requests,
-            "slots_used": self.max_requests - len(self._free_slots),
+            "slots_used": self._lib.plh_cache_slots_used(self._book),
         }
 
     def free_pages(self) -> int:
         """Free pages of the fullest pool (what limits the next reservation)."""
-        return min((g.pool.free_count for g in self.groups), default=self.n_pages)
+        return self._lib.plh_cache_free_pages(self._book) if self.groups else self.n_pages

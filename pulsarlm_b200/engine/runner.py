@@ -235,18 +235,15 @@ class ModelRunner:
         for i, e in enumerate(entries):
             h["tokens"][i] = e.tokens[0]
             h["pos"][i] = new_lens[i] - 1
-            h["slots"][i] = self.cache.slot(e.request)
             p = sampling[i]
             h["temperature"][i] = p.temperature if p.draws else 0.0
             h["top_k"][i] = p.top_k
             h["top_p"][i] = p.top_p if 0.0 < p.top_p < 1.0 else 2.0
             h["seed"][i] = np.uint64(seeds[i] & 0xFFFFFFFFFFFFFFFF).astype(np.int64)
             h["count"][i] = counts[i]
+        handles = [self.cache.handle(r) for r in requests]
         for g in self.cache.groups:
-            rows = self.cache.table_rows(g.index, requests, width_multiple=1)
-            table = h[f"table{g.index}"]
-            table[:] = -1
-            table[:, : rows.shape[1]] = rows
+            self.cache.fill_tables(g.index, handles, h[f"table{g.index}"], h["slots"])
         if fresh:
             graph.capture()
         graph.replay()

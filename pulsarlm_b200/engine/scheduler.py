@@ -23,14 +23,18 @@ Decisions, all deterministic:
 
 The scheduler only does bookkeeping against the cache manager; the caller runs
 the model on what `plan()` returns and reports sampled tokens to `finish_step()`.
+The decisions are made in C++ (SchedulerCore, pulsarlm_b200/csrc_host); the class
+below keeps the Python-side Request objects and token lists in step with it.
 """
 
 from __future__ import annotations
 
+import ctypes
 import dataclasses
 from collections import deque
 
 from ..cache.manager import CacheManager
+from ..host import core
 from ..sampling.params import SamplingParams
 
 
@@ -79,17 +83,51 @@ class PlannedEntry:
 
 
 class Scheduler:
+    """The Python face of the scheduler core (C++, class SchedulerCore in
+    pulsarlm_b200/csrc_host/host_core.cpp), which makes the decisions above on
+    counts alone; this class keeps the token lists and the Request objects in step
+    with it."""
+
+    _CAPACITY = 4096
+
     def __init__(self, cache: CacheManager, stop_ids=(), prefill_tokens_per_step: int = 256,
                  max_step_entries: int | None = None):
         if prefill_tokens_per_step <= 0:
             raise ValueError("prefill_tokens_per_step must be positive")
         self.cache = cache
-        self.stop_ids = frozenset(int(s) for s in stop_ids)
         self.prefill_tokens_per_step = prefill_tokens_per_step
         self.max_step_entries = max_step_entries or cache.max_requests
+        self._lib = core.library()
+        self._core = self._lib.plh_sched_create(cache.book, prefill_tokens_per_step, self.max_step_entries)
+        self._requests: dict[int, Request] = {}  # by the cache's handle
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []  # admission order
-        self.preemptions = 0
+        self.stop_ids = stop_ids
+        n = self._CAPACITY
+        self._entries = (ctypes.c_int64 * (3 * n))()
+        self._ended = (ctypes.c_int64 * (2 * n))()
+        self._preempted = (ctypes.c_int64 * n)()
+        self._counts = (ctypes.c_int32 * 3)()
+        self._tokens = (ctypes.c_int32 * n)()
+
+    def __del__(self):
+        if getattr(self, "_core", None):
+            self._lib.plh_sched_destroy(self._core)
+            self._core = None
+
+    @property
+    def stop_ids(self) -> frozenset:
+        return self._stop_ids
+
+    @stop_ids.setter
+    def stop_ids(self, ids) -> None:
+        self._stop_ids = frozenset(int(s) for s in ids)
+        array = (ctypes.c_int32 * max(1, len(self._stop_ids)))(*sorted(self._stop_ids))
+        self._lib.plh_sched_set_stop_ids(self._core, array, len(self._stop_ids))
+
+    @property
+    def preemptions(self) -> int:
+        return self._lib.plh_sched_preemptions(self._core)
 
     # ------------------------------------------------------------------ intake
     def add(self, request: Request) -> None:
@@ -97,142 +135,86 @@ class Scheduler:
             raise ValueError(f"request {request.id!r}: the prompt is empty")
         if request.max_tokens is not None and request.max_tokens < 0:
             raise ValueError(f"request {request.id!r}: max_tokens must be >= 0")
+        handle = self.cache.handle(request.id)
+        code = self._lib.plh_sched_add(self._core, handle, len(request.prompt),
+                                       -1 if request.max_tokens is None else request.max_tokens,
+                                       int(request.ignore_eos))
+        if code != 0:
+            raise ValueError(f"request {request.id!r} cannot be added twice")
         request.pending = list(request.prompt)
         request.state = "waiting"
+        self._requests[handle] = request
         self.waiting.append(request)
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self._lib.plh_sched_has_work(self._core))
 
-    # ------------------------------------------------------------------ ending
-    def _finish(self, request: Request, reason: str) -> None:
-        if self.cache.is_open(request.id):
-            self.cache.close(request.id)
+    # ------------------------------------------------------------------ mirroring the core
+    def _end(self, handle: int, reason: str) -> Request:
+        request = self._requests.pop(handle)
         if request in self.running:
             self.running.remove(request)
+        elif request in self.waiting:
+            self.waiting.remove(request)
         request.state = "finished"
         request.finish_reason = reason
         request.pending = []
-
-    def _preempt(self, request: Request) -> None:
-        """Back to the front of the queue; everything it computed is recomputed later."""
-        self.cache.close(request.id)
-        self.running.remove(request)
-        request.pending = list(request.prompt) + list(request.output)
-        request.state = "waiting"
-        request.preemptions += 1
-        self.preemptions += 1
-        self.waiting.appendleft(request)
-
-    def _drop_cancelled(self) -> list[Request]:
-        ended = []
-        for request in [r for r in self.running if r.cancelled]:
-            self._finish(request, "cancelled")
-            ended.append(request)
-        for request in [r for r in self.waiting if r.cancelled]:
-            self.waiting.remove(request)
-            self._finish(request, "cancelled")
-            ended.append(request)
-        return ended
-
-    # ------------------------------------------------------------------ planning
-    def _reserve(self, request: Request, count: int, protected: set) -> bool:
-        """Pages for `count` more tokens of a running request, preempting the newest
-        other running request (never one in `protected`) while that helps."""
-        new_len = self.cache.length(request.id) + count
-        while not self.cache.reserve(request.id, new_len):
-            victims = [r for r in self.running if r is not request and id(r) not in protected]
-            if not victims:
-                return False
-            self._preempt(victims[-1])
-        return True
+        self.cache.forget(request.id)
+        return request
 
     def plan(self) -> tuple[list[PlannedEntry], list[Request]]:
-        """The next step's entries (decode entries first, then prompt portions), and
-        the requests that ended while planning (cancelled, or out of memory)."""
-        ended = self._drop_cancelled()
-        entries: list[PlannedEntry] = []
-        planned: set = set()
-
-        # 1. decoding requests, oldest first; a preempted one simply leaves `running`.
-        for request in list(self.running):
-            if request not in self.running or len(request.pending) != 1:
-                continue
-            if len(entries) >= self.max_step_entries:
-                break
-            if self._reserve(request, 1, planned):
-                entries.append(PlannedEntry(request, list(request.pending), True))
-                planned.add(id(request))
-            elif not planned and len(self.running) == 1:
-                self._finish(request, "oom")
-                ended.append(request)
-            # else: it waits for a later step, holding what it has.
-
-        # 2. prompt portions of running requests, then of newly admitted ones.
-        budget = self.prefill_tokens_per_step
-        for request in list(self.running):
-            if budget == 0 or len(entries) >= self.max_step_entries:
-                break
-            if request not in self.running or len(request.pending) <= 1 or id(request) in planned:
-                continue
-            count = min(len(request.pending), budget)
-            if self._reserve(request, count, planned):
-                entries.append(PlannedEntry(request, request.pending[:count], count == len(request.pending)))
-                planned.add(id(request))
-                budget -= count
-            elif not planned and len(self.running) == 1:
-                self._finish(request, "oom")
-                ended.append(request)
-
-        while self.waiting and budget > 0 and len(entries) < self.max_step_entries:
-            request = self.waiting[0]
-            count = min(len(request.pending), budget)
-            if self.cache.open(request.id) is None:
-                break
-            if not self.cache.reserve(request.id, count):
-                self.cache.close(request.id)
-                if not self.running:
-                    # Alone and still too large for the pool: it can never run.
-                    self.waiting.popleft()
-                    self._finish(request, "oom")
-                    ended.append(request)
-                    continue
-                break
-            self.waiting.popleft()
-            request.state = "running"
-            self.running.append(request)
-            # A lone token samples like a decode entry.
-            entries.append(PlannedEntry(request, request.pending[:count], count == len(request.pending)))
-            planned.add(id(request))
-            budget -= count
-        # Decode entries (one pending token) first, as the kernels' launchers like it.
-        entries.sort(key=lambda e: 0 if len(e.tokens) == 1 else 1)
+        """The next step's entries (single-token entries first, then prompt portions),
+        and the requests that ended while planning (cancelled, or out of memory)."""
+        for request in self._requests.values():
+            if request.cancelled:
+                self._lib.plh_sched_cancel(self._core, self.cache.handle(request.id))
+        code = self._lib.plh_sched_plan(self._core, self._entries, self._ended, self._preempted, self._CAPACITY,
+                                        self._counts)
+        if code != 0:
+            raise RuntimeError("the scheduler core planned more entries than fit its buffers")
+        n_entries, n_ended, n_preempted = self._counts[0], self._counts[1], self._counts[2]
+        for i in range(n_preempted):
+            request = self._requests[self._preempted[i]]
+            # Back to the front of the queue; everything it computed is recomputed later.
+            if request in self.running:
+                self.running.remove(request)
+            request.pending = list(request.prompt) + list(request.output)
+            request.state = "waiting"
+            request.preemptions += 1
+            self.waiting.appendleft(request)
+        ended = [self._end(self._ended[2 * i], core.REASONS[self._ended[2 * i + 1]]) for i in range(n_ended)]
+        entries = []
+        for i in range(n_entries):
+            request = self._requests[self._entries[3 * i]]
+            count, samples = self._entries[3 * i + 1], bool(self._entries[3 * i + 2])
+            if request.state == "waiting":  # admitted in this plan
+                self.waiting.remove(request)
+                self.running.append(request)
+                request.state = "running"
+                self.cache.zero_states(self.cache.slot(request.id))
+            entries.append(PlannedEntry(request, request.pending[:count], samples))
+        self._planned = [(self._entries[3 * i], self._entries[3 * i + 1], self._entries[3 * i + 2])
+                         for i in range(n_entries)]
         return entries, ended
 
     # ------------------------------------------------------------------ after a step
     def finish_step(self, entries: list[PlannedEntry], sampled: dict) -> list[Request]:
         """Records a step: `sampled[request.id]` is the token drawn for each entry
         that samples. Returns the requests that finished."""
-        ended = []
-        for entry in entries:
+        n = len(entries)
+        flat = (ctypes.c_int64 * (3 * max(1, n)))()
+        for i, entry in enumerate(entries):
+            flat[3 * i] = self.cache.handle(entry.request.id)
+            flat[3 * i + 1] = len(entry.tokens)
+            flat[3 * i + 2] = int(entry.samples)
+            token = sampled.get(entry.request.id, 0) if entry.samples else 0
+            self._tokens[i] = int(token)
             request = entry.request
             if request.state != "running":
                 continue
             del request.pending[: len(entry.tokens)]
-            if not entry.samples:
-                continue
-            if request.max_tokens == 0:
-                self._finish(request, "length")
-                ended.append(request)
-                continue
-            token = int(sampled[request.id])
-            request.output.append(token)
-            if token in self.stop_ids and not request.ignore_eos:
-                self._finish(request, "stop")
-                ended.append(request)
-            elif request.max_tokens is not None and len(request.output) >= request.max_tokens:
-                self._finish(request, "length")
-                ended.append(request)
-            else:
-                request.pending = [token]
-        return ended
+            if entry.samples and request.max_tokens != 0:
+                request.output.append(int(token))
+                request.pending = [int(token)]
+        n_ended = self._lib.plh_sched_finish_step(self._core, flat, self._tokens, n, self._ended, self._CAPACITY)
+        return [self._end(self._ended[2 * i], core.REASONS[self._ended[2 * i + 1]]) for i in range(n_ended)]

@@ -187,5 +187,45 @@ def library_path(build: bool = True, verbose: bool = True) -> str:
     return lib
 
 
+HOST_SRC = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "csrc_host"))
+HOST_LIB_NAME = "libpulsarlm_host.so"
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
+
+
+def host_library_path(build: bool = True, verbose: bool = True) -> str:
+    """Path of the host core (C++, no CUDA: page pools, block tables, scheduler),
+    built with g++ next to the kernel library when stale."""
+    folder = build_dir()
+    lib = os.path.join(folder, HOST_LIB_NAME)
+    stamp = os.path.join(folder, HOST_LIB_NAME + ".hash")
+    digest = hashlib.sha256(" ".join(HOST_FLAGS).encode())
+    files = sorted(n for n in os.listdir(HOST_SRC) if n.endswith((".cpp", ".hpp", ".h")))
+    for n in files:
+        with open(os.path.join(HOST_SRC, n), "rb") as f:
+            digest.update(n.encode())
+            digest.update(f.read())
+    current = None
+    if os.path.isfile(lib) and os.path.isfile(stamp):
+        with open(stamp) as f:
+            current = f.read().strip()
+    if current == digest.hexdigest():
+        return lib
+    if not build:
+        raise BuildError(f"{lib} is missing or stale")
+    compiler = shutil.which("g++") or shutil.which("c++")
+    if compiler is None:
+        raise BuildError("no C++ compiler (g++) found: the host core cannot be built")
+    if verbose:
+        _say(f"compiling the host core into {folder} (first call only)")
+    tmp = lib + f".tmp{os.getpid()}"
+    sources = [os.path.join(HOST_SRC, n) for n in files if n.endswith(".cpp")]
+    _run([compiler, *HOST_FLAGS, "-I", HOST_SRC, *sources, "-o", tmp], "compiling the host core")
+    os.replace(tmp, lib)
+    with open(stamp, "w") as f:
+        f.write(digest.hexdigest())
+    return lib
+
+
 if __name__ == "__main__":
+    print(host_library_path())
     print(library_path())
