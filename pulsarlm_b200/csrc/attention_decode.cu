@@ -83,17 +83,23 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Deco
     unsigned char* ring = smem + warp * (STAGES * kStageBytes);
     const int my_tiles = t1 > t0 + warp ? (t1 - t0 - warp + WARPS - 1) / WARPS : 0;
 
+    int my_page = 0;  // lane L holds the page of this warp's tile 32 * (i / 32) + L
     auto issue = [&](int i) {  // loads this warp's i-th tile into stage i % STAGES
+        if (i % 32 == 0 && i < my_tiles) {
+            // one coalesced look-up of the block table for the next 32 tiles
+            const int mine = i + lane;
+            my_page = mine < my_tiles ? row[((t0 + warp + mine * WARPS) * kTile) / p.page_size] : 0;
+            if (my_page < 0 || my_page >= p.n_pages) {
+                if (p.status != nullptr) {
+                    atomicOr(p.status, 4);
+                }
+                my_page = 0;  // stay in bounds; the result is flagged as wrong
+            }
+        }
         if (i < my_tiles) {
             const int tile = t0 + warp + i * WARPS;
             const int key0 = tile * kTile;
-            int page = row[key0 / p.page_size];
-            if (page < 0 || page >= p.n_pages) {
-                if (lane == 0 && p.status != nullptr) {
-                    atomicOr(p.status, 4);
-                }
-                page = 0;  // stay in bounds; the result is flagged as wrong
-            }
+            const int page = __shfl_sync(0xffffffffu, my_page, i % 32);
             const int64_t offset = page * p.page_stride + kv_head * p.head_stride +
                 static_cast<int64_t>(key0 % p.page_size) * HD;
             const unsigned char* ksrc = reinterpret_cast<const unsigned char*>(p.k_pool + offset);
