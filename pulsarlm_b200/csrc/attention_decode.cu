@@ -57,6 +57,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Deco
     const int g = lane >> 2, tig = lane & 3;
     const int split = blockIdx.x, kv_head = blockIdx.y, t = blockIdx.z;
 
+    pl_grid_trigger();  // positions and block tables are step inputs, read before the wait
     const int ctx = p.pos[t] + 1;
     const int first = p.window > 0 ? max(0, ctx - p.window) : 0;
     const int tile_first = first / kTile, tile_end = (ctx + kTile - 1) / kTile;
@@ -65,6 +66,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Deco
     const int t1 = min(t0 + per_split, tile_end);
     const int32_t* row = p.table + static_cast<int64_t>(p.entry[t]) * p.table_width;
 
+    pl_grid_wait();
     // Q fragments: rows g and g + 8 of the group's heads (zero past the group).
     uint32_t qa[HD / 16][4];
     {
@@ -272,6 +274,8 @@ template <int HD>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               __nv_bfloat16* __restrict__ out, int64_t out_row_stride, int n_heads,
                                               int n_splits) {
+    pl_grid_trigger();
+    pl_grid_wait();
     const int t = blockIdx.y, h = blockIdx.x;
     const int64_t base = (static_cast<int64_t>(t) * n_heads + h) * n_splits;
     float m = -INFINITY;
@@ -308,11 +312,11 @@ int launch_decode(const DecodeParams& p, int n_tokens, int n_kv_heads, cudaStrea
         configured = true;
     }
     const dim3 grid(p.n_splits, n_kv_heads, n_tokens);
-    attention_decode_kernel<HD, kWarps, kStages><<<grid, kWarps * 32, smem, stream>>>(p);
+    pl_launch_overlapped(attention_decode_kernel<HD, kWarps, kStages>, grid, kWarps * 32, smem, stream, p);
     PL_CHECK_LAUNCH("attention_decode");
     if (p.n_splits > 1) {
-        attention_decode_merge_kernel<HD><<<dim3(p.n_heads, n_tokens), HD <= 64 ? 64 : 128, 0, stream>>>(
-            p.part_o, p.part_ml, p.out, p.out_row_stride, p.n_heads, p.n_splits);
+        pl_launch_overlapped(attention_decode_merge_kernel<HD>, dim3(p.n_heads, n_tokens), HD <= 64 ? 64 : 128, 0,
+                             stream, p.part_o, p.part_ml, p.out, p.out_row_stride, p.n_heads, p.n_splits);
         PL_CHECK_LAUNCH("attention_decode_merge");
     }
     return 0;

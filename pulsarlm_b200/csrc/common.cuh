@@ -35,6 +35,40 @@ int pl_fail(int code, const char* format, ...);
         }                                                                             \
     } while (0)
 
+// Overlap of consecutive kernels in a stream (programmatic dependent launch).
+//
+// A kernel launched through pl_launch_overlapped may become resident while its
+// predecessor in the stream still runs. It calls pl_grid_trigger() at its top (its
+// own successor may then be made resident as soon as all of this grid's CTAs are)
+// and pl_grid_wait() before it first reads or writes anything that another kernel
+// writes or reads: the wait returns when every earlier kernel of the stream has
+// finished and its writes are visible. What a kernel does before the wait (barrier
+// set-up, tensor-memory allocation, loads of weights, which no kernel writes)
+// overlaps the predecessor's tail. Every kernel launched this way executes the wait
+// in every thread that touches global memory, so completion stays in stream order.
+// Without the launch attribute both calls do nothing.
+__device__ __forceinline__ void pl_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pl_grid_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// 1 unless pl_set_overlap(0) was called.
+int pl_overlap_enabled();
+
+template <typename... Params, typename... Args>
+cudaError_t pl_launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = pl_overlap_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 // Dispatch on a dtype code: binds `scalar_t` to float or __nv_bfloat16.
 #define PL_DISPATCH_DTYPE(code, name, ...)                                  \
     do {                                                                    \

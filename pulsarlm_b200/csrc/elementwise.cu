@@ -15,6 +15,8 @@ namespace {
 template <typename scalar_t>
 __global__ void embed_kernel(const scalar_t* __restrict__ table, const int32_t* __restrict__ tokens,
                              float* __restrict__ x, int hidden, int vocab, int32_t* status) {
+    pl_grid_trigger();
+    pl_grid_wait();
     const int t = blockIdx.x;
     const int token = tokens[t];
     float* row = x + static_cast<int64_t>(t) * hidden;
@@ -43,6 +45,8 @@ template <typename scalar_t, typename weight_t>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const scalar_t* __restrict__ delta,
                                    const weight_t* __restrict__ weight, scalar_t* __restrict__ out,
                                    const int32_t* __restrict__ rows, int hidden, float eps) {
+    pl_grid_trigger();
+    pl_grid_wait();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const int64_t s = rows != nullptr ? rows[r] : r;
@@ -80,6 +84,8 @@ template <typename scalar_t, typename weight_t, int VECS>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const scalar_t* __restrict__ delta,
                                        const weight_t* __restrict__ weight, scalar_t* __restrict__ out,
                                        const int32_t* __restrict__ rows, int hidden, float eps) {
+    pl_grid_trigger();
+    pl_grid_wait();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const int64_t s = rows != nullptr ? rows[r] : r;
@@ -128,6 +134,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const scalar_t* __
 // out[t, i..i+7] = silu(gate) * up, eight elements (16 bytes of bf16) per thread.
 __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
                                      int64_t tokens, int width) {
+    pl_grid_trigger();
+    pl_grid_wait();
     const int chunks = width / 8;
     const int64_t total = tokens * chunks;
     for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
@@ -154,6 +162,8 @@ __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ in, __nv_
 template <typename scalar_t>
 __global__ void swiglu_kernel(const scalar_t* __restrict__ in, scalar_t* __restrict__ out, int64_t tokens,
                               int width) {
+    pl_grid_trigger();
+    pl_grid_wait();
     const int64_t total = tokens * width;
     for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
          idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -192,8 +202,8 @@ PL_API int pl_embed(const void* table, const int32_t* tokens, float* x, int n_to
     }
     const int threads = hidden >= 1024 ? 256 : 128;
     PL_DISPATCH_DTYPE(dtype, "embed", {
-        embed_kernel<scalar_t><<<n_tokens, threads, 0, stream>>>(static_cast<const scalar_t*>(table), tokens, x,
-                                                                  hidden, vocab, status);
+        pl_launch_overlapped(embed_kernel<scalar_t>, n_tokens, threads, 0, stream,
+                             static_cast<const scalar_t*>(table), tokens, x, hidden, vocab, status);
     });
     PL_CHECK_LAUNCH("embed");
     return 0;
@@ -219,9 +229,9 @@ PL_API int pl_add_rmsnorm(float* x, const void* delta, const void* weight, int w
         }
         const int vecs = (n_vec + threads - 1) / threads;
 #define PL_LAUNCH_NORM(W, V)                                                                              \
-    add_rmsnorm_vec_kernel<scalar_t, W, V><<<n_rows, threads, 0, stream>>>(                               \
-        x, static_cast<const scalar_t*>(delta), static_cast<const W*>(weight), static_cast<scalar_t*>(out), \
-        rows, hidden, eps)
+    pl_launch_overlapped(add_rmsnorm_vec_kernel<scalar_t, W, V>, n_rows, threads, 0, stream, x,           \
+                         static_cast<const scalar_t*>(delta), static_cast<const W*>(weight),              \
+                         static_cast<scalar_t*>(out), rows, hidden, eps)
         PL_DISPATCH_DTYPE(dtype, "add_rmsnorm", {
             if (weight_dtype == PL_F32) {
                 if (vecs == 1) { PL_LAUNCH_NORM(float, 1); } else if (vecs == 2) { PL_LAUNCH_NORM(float, 2); } else { PL_LAUNCH_NORM(float, 4); }
@@ -236,13 +246,13 @@ PL_API int pl_add_rmsnorm(float* x, const void* delta, const void* weight, int w
     const int threads = norm_threads(hidden);
     PL_DISPATCH_DTYPE(dtype, "add_rmsnorm", {
         if (weight_dtype == PL_F32) {
-            add_rmsnorm_kernel<scalar_t, float><<<n_rows, threads, 0, stream>>>(
-                x, static_cast<const scalar_t*>(delta), static_cast<const float*>(weight),
-                static_cast<scalar_t*>(out), rows, hidden, eps);
+            pl_launch_overlapped(add_rmsnorm_kernel<scalar_t, float>, n_rows, threads, 0, stream, x,
+                                 static_cast<const scalar_t*>(delta), static_cast<const float*>(weight),
+                                 static_cast<scalar_t*>(out), rows, hidden, eps);
         } else {
-            add_rmsnorm_kernel<scalar_t, scalar_t><<<n_rows, threads, 0, stream>>>(
-                x, static_cast<const scalar_t*>(delta), static_cast<const scalar_t*>(weight),
-                static_cast<scalar_t*>(out), rows, hidden, eps);
+            pl_launch_overlapped(add_rmsnorm_kernel<scalar_t, scalar_t>, n_rows, threads, 0, stream, x,
+                                 static_cast<const scalar_t*>(delta), static_cast<const scalar_t*>(weight),
+                                 static_cast<scalar_t*>(out), rows, hidden, eps);
         }
     });
     PL_CHECK_LAUNCH("add_rmsnorm");
@@ -259,16 +269,16 @@ PL_API int pl_swiglu(const void* in, void* out, int n_tokens, int width, int dty
         (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
         const int64_t chunks = static_cast<int64_t>(n_tokens) * (width / 8);
         const int blocks = static_cast<int>(std::min<int64_t>((chunks + threads - 1) / threads, 148 * 32));
-        swiglu_bf16x8_kernel<<<blocks, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(in),
-                                                            static_cast<__nv_bfloat16*>(out), n_tokens, width);
+        pl_launch_overlapped(swiglu_bf16x8_kernel, blocks, threads, 0, stream, static_cast<const __nv_bfloat16*>(in),
+                             static_cast<__nv_bfloat16*>(out), n_tokens, width);
         PL_CHECK_LAUNCH("swiglu");
         return 0;
     }
     const int64_t total = static_cast<int64_t>(n_tokens) * width;
     const int blocks = static_cast<int>(std::min<int64_t>((total + threads - 1) / threads, 148 * 16));
     PL_DISPATCH_DTYPE(dtype, "swiglu", {
-        swiglu_kernel<scalar_t><<<blocks, threads, 0, stream>>>(static_cast<const scalar_t*>(in),
-                                                                 static_cast<scalar_t*>(out), n_tokens, width);
+        pl_launch_overlapped(swiglu_kernel<scalar_t>, blocks, threads, 0, stream, static_cast<const scalar_t*>(in),
+                             static_cast<scalar_t*>(out), n_tokens, width);
     });
     PL_CHECK_LAUNCH("swiglu");
     return 0;

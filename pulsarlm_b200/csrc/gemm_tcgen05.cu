@@ -88,6 +88,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __shared__ int last_piece;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pl_grid_trigger();
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full_bar[s], 1);
@@ -114,9 +115,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (warp == 0) {
         // ------------------------------------------------ producer
         if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            for (int unit = unit_begin; unit < unit_end; ++unit) {
+            // The first stages' weight tiles are asked for before the wait on earlier
+            // kernels (no kernel writes weights): they stream in under the predecessor's
+            // tail. The activation tiles of those stages follow after the wait.
+            const int early_end = min(unit_end, unit_begin + kStages);
+            for (int unit = unit_begin; unit < early_end; ++unit) {
+                const int tile = unit / p.k_blocks, kb = unit % p.k_blocks;
+                const int s = unit - unit_begin;
+                mbar_expect_tx(&full_bar[s], kStageBytes);
+                tma_load_2d(tiles + s * kStageBytes, &map_w, kb * kBlockK, (tile % p.n_tiles) * kTileM, &full_bar[s]);
+            }
+            pl_grid_wait();
+            for (int unit = unit_begin; unit < early_end; ++unit) {
+                const int tile = unit / p.k_blocks, kb = unit % p.k_blocks;
+                const int s = unit - unit_begin;
+                tma_load_2d(tiles + s * kStageBytes + kBytesA, &map_x, kb * kBlockK, (tile / p.n_tiles) * TN,
+                            &full_bar[s]);
+            }
+            int stage = (early_end - unit_begin) % kStages;
+            uint32_t phase = early_end - unit_begin == kStages ? 1u : 0u;
+            for (int unit = early_end; unit < unit_end; ++unit) {
                 const int tile = unit / p.k_blocks, kb = unit % p.k_blocks;
                 const int n0 = (tile % p.n_tiles) * kTileM, t0 = (tile / p.n_tiles) * TN;
                 if (!mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_flag)) {
@@ -135,6 +153,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issuer
         if (lane == 0) {
+            pl_grid_wait();  // so that the bounded waits below time this kernel's work only
             int stage = 0;
             uint32_t phase = 0;
             int run = 0;  // runs of units within one tile: accumulator run & 1
@@ -181,6 +200,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         // ------------------------------------------------ epilogue (warps 2..5)
         const int lane_group = warp & 3;  // the TMEM lanes a warp may read: 32 * (warp % 4)
         const int feature = lane_group * 32 + lane;
+        pl_grid_wait();  // before the first store: an earlier kernel may still read what this one overwrites
         int run = 0;
         int unit = unit_begin;
         while (unit < unit_end) {
@@ -361,7 +381,7 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmParams&
         }
         configured = true;
     }
-    gemm_tcgen05_kernel<TN><<<plan.grid, kThreads, smem, stream>>>(map_w, map_x, p);
+    pl_launch_overlapped(gemm_tcgen05_kernel<TN>, plan.grid, kThreads, smem, stream, map_w, map_x, p);
     PL_CHECK_LAUNCH("gemm_tcgen05");
     return 0;
 }

@@ -36,6 +36,7 @@ __global__ void rope_kv_write_kernel(scalar_t* __restrict__ q, const scalar_t* _
                                      const double* __restrict__ inv_freq, int rotary, int n_heads, int n_kv_heads,
                                      int head_dim, int32_t* status) {
     extern __shared__ float sincos[];  // [rotary/2] cos then [rotary/2] sin
+    pl_grid_trigger();  // positions are step inputs: the angles need not wait for the projection
     const int t = blockIdx.x;
     const int p = pos[t];
     const int half = rotary / 2;
@@ -46,6 +47,7 @@ __global__ void rope_kv_write_kernel(scalar_t* __restrict__ q, const scalar_t* _
             rope_sincos(p, inv_freq[j], cs[j], sn[j]);
         }
     }
+    pl_grid_wait();
     __syncthreads();
 
     const int n_slots = n_heads + (k_pool != nullptr ? n_kv_heads : 0);
@@ -109,6 +111,7 @@ __global__ void rope_kv_write_vec_kernel(scalar_t* __restrict__ q, const scalar_
                                          const double* __restrict__ inv_freq, int rotary, int n_heads,
                                          int n_kv_heads, int head_dim, int32_t* status) {
     extern __shared__ float sincos[];
+    pl_grid_trigger();
     const int t = blockIdx.x;
     const int p = pos[t];
     const int half = rotary / 2;
@@ -119,6 +122,7 @@ __global__ void rope_kv_write_vec_kernel(scalar_t* __restrict__ q, const scalar_
             rope_sincos(p, inv_freq[j], cs[j], sn[j]);
         }
     }
+    pl_grid_wait();
     __syncthreads();
 
     const int n_slots = n_heads + (k_pool != nullptr ? n_kv_heads : 0);
@@ -212,8 +216,8 @@ PL_API int pl_rope_kv_write(void* q, const void* k, const void* v, int64_t row_s
     const int threads = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
     PL_DISPATCH_DTYPE(dtype, "rope_kv_write", {
         auto kernel = vec ? rope_kv_write_vec_kernel<scalar_t> : rope_kv_write_kernel<scalar_t>;
-        kernel<<<grid, threads, smem, stream>>>(
-            static_cast<scalar_t*>(q), static_cast<const scalar_t*>(k), static_cast<const scalar_t*>(v), row_stride,
+        pl_launch_overlapped(
+            kernel, grid, threads, smem, stream, static_cast<scalar_t*>(q), static_cast<const scalar_t*>(k), static_cast<const scalar_t*>(v), row_stride,
             pos, entry, table, table_width, static_cast<scalar_t*>(k_pool), static_cast<scalar_t*>(v_pool),
             page_stride, head_stride, page_size, n_pages, inv_freq, rotary, n_heads, n_kv_heads, head_dim, status);
     });

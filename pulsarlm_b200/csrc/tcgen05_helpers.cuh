@@ -48,6 +48,57 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     *abort_flag = 1;
     return false;
 }
+
+// ---- thread-block clusters: a peer's shared memory and barriers
+// The address, in the cluster's shared window, of `local` in the CTA of rank `rank`.
+__device__ __forceinline__ uint32_t cluster_map(const void* local, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    return remote;
+}
+// Stores four floats into a peer's shared memory (16-byte aligned) and counts their
+// sixteen bytes on the peer's barrier, whose phase completes once the bytes it
+// expects have arrived: the values carry their own completion, no fence or arrival
+// follows.
+__device__ __forceinline__ void cluster_store4_counted(uint32_t remote, float4 v, uint32_t remote_bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(remote), "r"(__float_as_uint(v.x)), "r"(__float_as_uint(v.y)), "r"(__float_as_uint(v.z)),
+                 "r"(__float_as_uint(v.w)), "r"(remote_bar)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t tries = 0; tries < kWaitLimit; ++tries) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+        if (done) {
+            return true;
+        }
+        if ((tries & 1023u) == 1023u && *abort_flag) {
+            return false;
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+// The cluster's barrier in two halves: every thread of every CTA arrives (without
+// blocking); a thread that waits returns once all have arrived, and sees what they
+// wrote before arriving.
+__device__ __forceinline__ void cluster_arrive_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_all() {
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tensormap_prefetch(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

@@ -10,6 +10,7 @@ kernel refuses come back as KernelError with the kernel's message.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 
 import torch
@@ -24,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 9
+ABI_VERSION = 10
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -55,6 +56,9 @@ _SIGNATURES = {
     "pl_attention_prefill_tile_rows": [],
     "pl_gemm_bf16": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I64, _I64, _I64, _I32, _PTR, _PTR, _I32, _PTR, _PTR],
     "pl_gemm_bf16_supports": [_I32, _I32, _I32, _I64, _I64],
+    "pl_gemm_bf16_skinny": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I64, _I64, _I64, _I32, _PTR, _PTR],
+    "pl_gemm_bf16_skinny_max_tokens": [],
+    "pl_gemm_bf16_skinny_splits": [_I32, _I32, _I32],
     "pl_sample": [_PTR, _I64, _I32, _I32, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR],
 }
 
@@ -83,8 +87,19 @@ def library() -> ctypes.CDLL:
         lib.pl_attention_decode_scratch_floats.restype = _I64
         lib.pl_gemm_bf16_scratch_floats.argtypes = [_I32, _I32, _I32]
         lib.pl_gemm_bf16_scratch_floats.restype = _I64
+        lib.pl_set_overlap.argtypes = [_I32]
+        lib.pl_set_overlap.restype = _I32
+        if os.environ.get("PULSARLM_B200_OVERLAP", "1") == "0":
+            lib.pl_set_overlap(0)
         _lib = lib
     return _lib
+
+
+def set_overlap(enabled: bool) -> bool:
+    """Lets consecutive kernels of a stream overlap (programmatic dependent launch:
+    a kernel's set-up and weight loads run under its predecessor's tail). On by
+    default; `PULSARLM_B200_OVERLAP=0` starts with it off. Returns the old setting."""
+    return bool(library().pl_set_overlap(int(enabled)))
 
 
 _device_checked = False
@@ -216,8 +231,16 @@ def gemm_bf16_supports(t: int, n: int, k: int, ldx: int, ldw: int) -> bool:
     return bool(library().pl_gemm_bf16_supports(t, n, k, ldx, ldw))
 
 
-def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor | None = None) -> None:
-    """out[T, N] (bf16 or fp32) = x[T, K] @ w[N, K]^T on the tcgen05 tensor cores."""
+GEMM_SKINNY_MAX_TOKENS = 64
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor | None = None,
+              kernel: str | None = None) -> None:
+    """out[T, N] (bf16 or fp32) = x[T, K] @ w[N, K]^T on the tcgen05 tensor cores.
+
+    Two kernels: "skinny" for up to 64 tokens (one tile and part of k per CTA, the
+    parts added inside a thread-block cluster) and "persistent" for more (and for
+    any count when asked by name). `kernel=None` picks by the token count."""
     _dev(x, w, out, status)
     assert x.dtype == w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
     t, k = x.shape
@@ -226,6 +249,13 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch
     assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
     ldx = x.stride(0) if t > 1 else k
     ldw = w.stride(0) if n > 1 else k
+    if kernel is None:
+        kernel = "skinny" if t <= GEMM_SKINNY_MAX_TOKENS else "persistent"
+    if kernel == "skinny":
+        _call("pl_gemm_bf16_skinny", _p(x), _p(w), _p(out), t, n, k, ldx, ldw, out.stride(0) if t > 1 else n,
+              int(out.dtype == torch.float32), _p(status), _stream())
+        return
+    assert kernel == "persistent", kernel
     floats = int(library().pl_gemm_bf16_scratch_floats(t, n, k))
     scratch = torch.empty(floats, dtype=torch.float32, device=x.device) if floats else None
     counters = _gemm_counters(x.device) if floats else None

@@ -2,14 +2,18 @@
 
 float32: the library's own CUDA-core kernel (true fp32, no tensor cores, no
 TF32), whose result for a row does not depend on the other rows. bfloat16, fp32
-accumulation, by one of two routes chosen by $PULSARLM_B200_GEMM:
+accumulation, by one of three routes chosen by $PULSARLM_B200_GEMM:
 
-* "library" (the default): a library matrix product (cuBLAS through torch), as
-  the reference's engine does for every projection (`at::linear`,
-  pulsarlm-core/src/engine/model/llama.cpp:67-69, 81, 91, 93);
-* "tcgen05": this package's own tcgen05/TMEM kernel fed by TMA
-  (csrc/gemm_tcgen05.cu) wherever it takes the sizes (rows starting on 16 bytes),
-  the library elsewhere.
+* "mixed" (the default): up to 16 tokens (decode steps of small batches) this
+  package's own tcgen05/TMEM kernel fed by TMA (csrc/gemm_skinny.cu), which overlaps
+  its set-up and first weight loads with the kernel before it; above that a library
+  matrix product (cuBLAS through torch), as the reference's engine does for every
+  projection (`at::linear`, pulsarlm-core/src/engine/model/llama.cpp:67-69, 81, 91,
+  93);
+* "tcgen05": the own kernels at every size they take (rows starting on 16 bytes):
+  csrc/gemm_skinny.cu up to 64 tokens, csrc/gemm_tcgen05.cu above; the library
+  elsewhere;
+* "library": the library everywhere.
 
 The default is whichever measured faster on the Llama-3.1-8B shapes; see
 profiles/gemm_tcgen05_vs_library.md.
@@ -23,9 +27,10 @@ import os
 
 from ..kernels import ops
 
-GEMM_ROUTE = os.environ.get("PULSARLM_B200_GEMM", "library")
-if GEMM_ROUTE not in ("library", "tcgen05"):
-    raise ValueError(f"PULSARLM_B200_GEMM must be 'library' or 'tcgen05', got {GEMM_ROUTE!r}")
+GEMM_ROUTE = os.environ.get("PULSARLM_B200_GEMM", "mixed")
+MIXED_MAX_TOKENS = 16  # the own kernel is ahead of the library up to here
+if GEMM_ROUTE not in ("library", "tcgen05", "mixed"):
+    raise ValueError(f"PULSARLM_B200_GEMM must be 'library', 'tcgen05' or 'mixed', got {GEMM_ROUTE!r}")
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
@@ -40,7 +45,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         return out
     if x.dtype == torch.bfloat16:
         k = x.shape[1]
-        if GEMM_ROUTE == "tcgen05" and x.stride(1) == 1 and weight.stride(1) == 1 and ops.gemm_bf16_supports(
+        own = GEMM_ROUTE == "tcgen05" or (GEMM_ROUTE == "mixed" and tokens <= MIXED_MAX_TOKENS)
+        if own and x.stride(1) == 1 and weight.stride(1) == 1 and ops.gemm_bf16_supports(
                 tokens, n, k, x.stride(0) if tokens > 1 else k, weight.stride(0) if n > 1 else k):
             out = torch.empty((tokens, n), dtype=out_dtype or torch.bfloat16, device=x.device)
             ops.gemm_bf16(x, weight, out)

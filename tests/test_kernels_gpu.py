@@ -110,24 +110,33 @@ def test_gemm_f32_is_true_fp32(ops):
     assert abs(float(out[0, 0]) - 8.0) > 3e-3
 
 
-@pytest.mark.parametrize("t,n,k", [(1, 128, 64), (8, 256, 128), (3, 100, 96), (37, 1000, 96), (300, 515, 160),
-                                   (64, 512, 1024), (130, 384, 512), (8, 4096, 4096), (17, 6144, 1024),
-                                   (600, 1536, 2048), (2048, 1024, 512)])
+GEMM_SHAPES = [(1, 128, 64), (8, 256, 128), (3, 100, 96), (37, 1000, 96), (300, 515, 160), (64, 512, 1024),
+               (130, 384, 512), (8, 4096, 4096), (17, 6144, 1024), (600, 1536, 2048), (2048, 1024, 512),
+               (5, 128, 520), (3, 130, 4096), (8, 512, 14336), (64, 3584, 512), (33, 200, 64), (16, 28672, 256)]
+
+
+@pytest.mark.parametrize("t,n,k,kernel", [(t, n, k, kernel) for (t, n, k) in GEMM_SHAPES
+                                          for kernel in (("skinny", "persistent") if t <= 64 else ("persistent",))])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_gemm_bf16_tcgen05(ops, t, n, k, out_dtype):
-    """The tensor-core product at token counts from one to thousands, widths that
-    are no multiple of the tile, k ranges shared between CTAs (few tiles) and whole
-    tiles (many)."""
+def test_gemm_bf16_tcgen05(ops, t, n, k, kernel, out_dtype):
+    """The tensor-core products at token counts from one to thousands, widths that
+    are no multiple of the tile, k ranges shared between CTAs (few tiles: through
+    scratch memory in the persistent kernel, inside a cluster in the skinny one,
+    with more ranks than tokens and ranks with a shorter k range among the cases)
+    and whole tiles (many)."""
     x = torch.randn(t, k, device=DEV).to(torch.bfloat16)
     w = (torch.randn(n, k, device=DEV) / k ** 0.5).to(torch.bfloat16)
-    out = torch.full((t, n), float("nan"), device=DEV, dtype=out_dtype)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     assert ops.gemm_bf16_supports(t, n, k, k, k)
-    for _ in range(2):  # twice: the tile counters must be back at zero
-        ops.gemm_bf16(x, w, out, status)
+    outs = []
+    for _ in range(2):  # twice: the tile counters must be back at zero, and the bits the same
+        out = torch.full((t, n), float("nan"), device=DEV, dtype=out_dtype)
+        ops.gemm_bf16(x, w, out, status, kernel=kernel)
+        outs.append(out)
     want = x.double() @ w.double().T
     assert int(status) == 0
-    assert rel(out, want) < (1e-5 if out_dtype == torch.float32 else 1e-2)
+    assert rel(outs[0], want) < (1e-5 if out_dtype == torch.float32 else 1e-2)
+    assert torch.equal(outs[0], outs[1])
 
 
 def test_gemm_bf16_finds_one_large_product_among_many(ops):
@@ -140,11 +149,12 @@ def test_gemm_bf16_finds_one_large_product_among_many(ops):
         w = torch.zeros(n, k, device=DEV, dtype=torch.bfloat16)
         x[3, hot_k] = 3.0
         w[150, hot_k] = 2.0
-        out = torch.empty(t, n, device=DEV, dtype=torch.float32)
-        ops.gemm_bf16(x, w, out)
-        want = torch.zeros(t, n)
-        want[3, 150] = 6.0
-        assert torch.equal(out.cpu(), want), hot_k
+        for kernel in ("skinny", "persistent"):
+            out = torch.empty(t, n, device=DEV, dtype=torch.float32)
+            ops.gemm_bf16(x, w, out, kernel=kernel)
+            want = torch.zeros(t, n)
+            want[3, 150] = 6.0
+            assert torch.equal(out.cpu(), want), (hot_k, kernel)
 
 
 def test_gemm_bf16_refuses_rows_that_do_not_start_on_16_bytes(ops):
