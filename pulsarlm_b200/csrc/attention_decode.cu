@@ -8,12 +8,19 @@
 // ldmatrix is conflict-free) and keeps the group's (<= 16) query heads as the M
 // rows of m16n8k16 MMAs: S = Q K^T, online softmax in fp32 (base 2, the scale
 // folded into the exponent), O += P V with P rounded to bf16. Warps are merged
-// through shared memory; with more than one split the CTA writes an unnormalised
-// partial (o, m, l) to scratch and a second kernel merges the splits. Split
-// boundaries depend only on the request's length and the launch's split count.
+// through shared memory. The splits of one (kv head, token) are merged in one of two
+// ways. Up to eight splits form a thread-block cluster: the (head, dim) outputs are
+// dealt out to the ranks in contiguous runs, every rank sends its unnormalised
+// partial sums for a run to the owner's shared memory (st.async: stores that count
+// their bytes on the owner's barrier) and its (m, l) to everyone, and each owner
+// merges in rank order and writes its run. More splits than that write (o, m, l) to
+// scratch and a second kernel merges them, in the same order with the same
+// arithmetic. Split boundaries depend only on the request's length and the launch's
+// split count.
 //
 // The reference's counterparts: attn_decode_tc_kernel and paged_decode_split /
 // combine kernels, pulsarlm-core/src/kernels/paged_attention.cu:432-584.
+#include "cluster_helpers.cuh"
 #include "mma_helpers.cuh"
 
 namespace {
@@ -42,8 +49,21 @@ struct DecodeParams {
     int window;
     float scale_log2;
     int n_splits;
+    int cluster;  // 1: the splits are the ranks of a thread-block cluster and merge among themselves
     int32_t* status;
 };
+
+// In-cluster merge: outputs are counted in groups of four dims ("vecs"); rank r owns
+// vecs [first_vec(r), first_vec(r + 1)).
+__host__ __device__ constexpr int first_vec(int rank, int n_vec, int splits) {
+    return (rank * n_vec + splits - 1) / splits;
+}
+__host__ __device__ constexpr int owned_vecs_max(int n_vec, int splits) { return (n_vec + splits - 1) / splits; }
+// Bytes of the receive buffers behind the rings: partial sums [rank][vec of mine] as
+// float4, then (m, l) [rank][16] as float2.
+__host__ __device__ constexpr int merge_bytes(int n_vec, int splits) {
+    return splits * owned_vecs_max(n_vec, splits) * 16 + splits * 16 * 8;
+}
 
 template <int HD, int WARPS, int STAGES>
 __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const DecodeParams p) {
@@ -58,6 +78,22 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Deco
     const int split = blockIdx.x, kv_head = blockIdx.y, t = blockIdx.z;
 
     pl_grid_trigger();  // positions and block tables are step inputs, read before the wait
+    __shared__ __align__(8) uint64_t recv_bar;
+    __shared__ int abort_flag;
+    const int n_vec = p.group * (HD / 4);
+    const int my_first = first_vec(split, n_vec, p.n_splits);
+    const int my_vecs = first_vec(split + 1, n_vec, p.n_splits) - my_first;
+    if (p.cluster) {
+        if (threadIdx.x == 0) {
+            mbar_init(&recv_bar, 1);
+            abort_flag = 0;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            // what the other ranks will send: partial sums of my vecs, and their (m, l) of every head
+            mbar_expect_tx(&recv_bar, static_cast<uint32_t>(p.n_splits - 1) * (my_vecs * 16 + p.group * 8));
+        }
+        __syncthreads();
+        cluster_arrive_all();  // "my barrier is ready"; waited for before anything is sent
+    }
     const int ctx = p.pos[t] + 1;
     const int first = p.window > 0 ? max(0, ctx - p.window) : 0;
     const int tile_first = first / kTile, tile_end = (ctx + kTile - 1) / kTile;
@@ -238,6 +274,91 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Deco
         red_l[warp * 16 + g + 8] = l_hi;
     }
     __syncthreads();
+    if (p.cluster) {
+        float4* recv_o = reinterpret_cast<float4*>(smem + WARPS * STAGES * kStageBytes);
+        const int most = owned_vecs_max(n_vec, p.n_splits);
+        float2* recv_ml = reinterpret_cast<float2*>(recv_o + p.n_splits * most);
+        cluster_wait_all();  // long since complete: every rank arrived at its start
+        for (int vec = threadIdx.x; vec < n_vec; vec += WARPS * 32) {
+            const int r = vec / (HD / 4), d = (vec % (HD / 4)) * 4;
+            float m = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                m = fmaxf(m, red_m[w * 16 + r]);
+            }
+            float l = 0.0f;
+            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (m > -INFINITY) {
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w) {
+                    const float scale = exp2f(red_m[w * 16 + r] - m);
+                    const float4 part = *reinterpret_cast<const float4*>(&red_o[(w * 16 + r) * HD + d]);
+                    l += red_l[w * 16 + r] * scale;
+                    acc.x += part.x * scale;
+                    acc.y += part.y * scale;
+                    acc.z += part.z * scale;
+                    acc.w += part.w * scale;
+                }
+            }
+            const int owner = vec * p.n_splits / n_vec;
+            float4* at = recv_o + split * most + (vec - first_vec(owner, n_vec, p.n_splits));
+            if (owner == split) {
+                *at = acc;
+            } else {
+                cluster_store4_counted(cluster_map(at, owner), acc, cluster_map(&recv_bar, owner));
+            }
+            if (d == 0) {  // this head's (m, l) goes to every rank
+                float2* ml = recv_ml + split * 16 + r;
+                for (int peer = 0; peer < p.n_splits; ++peer) {
+                    if (peer == split) {
+                        *ml = make_float2(m, l);
+                    } else {
+                        cluster_store2_counted(cluster_map(ml, peer), make_float2(m, l), cluster_map(&recv_bar, peer));
+                    }
+                }
+            }
+        }
+        __syncthreads();  // what this rank kept for itself is in place
+        if (!mbar_wait_cluster(&recv_bar, 0u, &abort_flag)) {
+            if (threadIdx.x == 0 && p.status != nullptr) {
+                atomicOr(p.status, 8);
+            }
+            return;
+        }
+        for (int mine = threadIdx.x; mine < my_vecs; mine += WARPS * 32) {
+            const int vec = my_first + mine;
+            const int r = vec / (HD / 4), d = (vec % (HD / 4)) * 4;
+            float m = -INFINITY;
+            for (int s = 0; s < p.n_splits; ++s) {
+                m = fmaxf(m, recv_ml[s * 16 + r].x);
+            }
+            float l = 0.0f;
+            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (m > -INFINITY) {
+                for (int s = 0; s < p.n_splits; ++s) {  // rank order, whoever arrived first
+                    const float2 ml = recv_ml[s * 16 + r];
+                    const float scale = exp2f(ml.x - m);
+                    const float4 part = recv_o[s * most + mine];
+                    l += ml.y * scale;
+                    acc.x += part.x * scale;
+                    acc.y += part.y * scale;
+                    acc.z += part.z * scale;
+                    acc.w += part.w * scale;
+                }
+            }
+            const int h = kv_head * p.group + r;
+            __nv_bfloat16* dst = p.out + t * p.out_row_stride + static_cast<int64_t>(h) * HD + d;
+            if (l > 0.0f) {
+                dst[0] = __float2bfloat16_rn(acc.x / l);
+                dst[1] = __float2bfloat16_rn(acc.y / l);
+                dst[2] = __float2bfloat16_rn(acc.z / l);
+                dst[3] = __float2bfloat16_rn(acc.w / l);
+            } else {
+                dst[0] = dst[1] = dst[2] = dst[3] = __float2bfloat16_rn(0.0f);
+            }
+        }
+        return;
+    }
     for (int idx = threadIdx.x; idx < p.group * HD; idx += WARPS * 32) {
         const int r = idx / HD, d = idx % HD;
         float m = -INFINITY;
@@ -298,21 +419,47 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
 constexpr int kWarps = 4;
 constexpr int kStages = 3;
 
+constexpr int kClusterSplitsMax = 8;  // the portable cluster size
+
 template <int HD>
-int launch_decode(const DecodeParams& p, int n_tokens, int n_kv_heads, cudaStream_t stream) {
-    constexpr int smem = kWarps * kStages * 2 * kTile * HD * 2;
-    static_assert(smem >= kWarps * 16 * (HD + 2) * 4, "the merge buffers must fit in the rings");
+int launch_decode(const DecodeParams& params, int n_tokens, int n_kv_heads, bool allow_cluster, cudaStream_t stream) {
+    constexpr int rings = kWarps * kStages * 2 * kTile * HD * 2;
+    static_assert(rings >= kWarps * 16 * (HD + 2) * 4, "the merge buffers must fit in the rings");
+    constexpr int most_merge = merge_bytes(16 * (HD / 4), kClusterSplitsMax) + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(attention_decode_kernel<HD, kWarps, kStages>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, rings + most_merge);
         if (err != cudaSuccess) {
             return pl_fail(3, "attention_decode: cannot set shared memory size: %s", cudaGetErrorString(err));
         }
         configured = true;
     }
+    DecodeParams p = params;
+    p.cluster = allow_cluster && p.n_splits >= 2 && p.n_splits <= kClusterSplitsMax;
     const dim3 grid(p.n_splits, n_kv_heads, n_tokens);
-    pl_launch_overlapped(attention_decode_kernel<HD, kWarps, kStages>, grid, kWarps * 32, smem, stream, p);
+    if (p.cluster) {
+        cudaLaunchConfig_t config = {};
+        config.gridDim = grid;
+        config.blockDim = dim3(kWarps * 32);
+        config.dynamicSmemBytes = rings + merge_bytes(p.group * (HD / 4), p.n_splits);
+        config.stream = stream;
+        cudaLaunchAttribute attributes[2];
+        attributes[0].id = cudaLaunchAttributeClusterDimension;
+        attributes[0].val.clusterDim.x = p.n_splits;
+        attributes[0].val.clusterDim.y = 1;
+        attributes[0].val.clusterDim.z = 1;
+        attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attributes[1].val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = attributes;
+        config.numAttrs = pl_overlap_enabled() ? 2 : 1;
+        const cudaError_t err = cudaLaunchKernelEx(&config, attention_decode_kernel<HD, kWarps, kStages>, p);
+        if (err != cudaSuccess) {
+            return pl_fail(3, "attention_decode: launch failed: %s", cudaGetErrorString(err));
+        }
+        return 0;
+    }
+    pl_launch_overlapped(attention_decode_kernel<HD, kWarps, kStages>, grid, kWarps * 32, rings, stream, p);
     PL_CHECK_LAUNCH("attention_decode");
     if (p.n_splits > 1) {
         pl_launch_overlapped(attention_decode_merge_kernel<HD>, dim3(p.n_heads, n_tokens), HD <= 64 ? 64 : 128, 0,
@@ -336,10 +483,9 @@ PL_API int64_t pl_attention_decode_scratch_floats(int n_tokens, int n_heads, int
     return n_splits <= 1 ? 0 : static_cast<int64_t>(n_tokens) * n_heads * n_splits * (head_dim + 2);
 }
 
-// bf16 only. q and out [T, n_heads, head_dim] with row strides; one query per token
-// at position pos[t]; pools and table as in pl_attention_simt. scratch: at least
-// pl_attention_decode_scratch_floats floats when n_splits > 1.
-PL_API int pl_attention_decode(const void* q, int64_t q_row_stride, const void* k_pool, const void* v_pool,
+namespace {
+
+int run_attention_decode(bool allow_cluster, const void* q, int64_t q_row_stride, const void* k_pool, const void* v_pool,
                                int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
                                const int32_t* table, int table_width, const int32_t* pos, const int32_t* entry,
                                void* out, int64_t out_row_stride, int n_tokens, int n_heads, int n_kv_heads,
@@ -354,7 +500,8 @@ PL_API int pl_attention_decode(const void* q, int64_t q_row_stride, const void* 
                head_dim, group, page_size);
     PL_REQUIRE(n_splits >= 1 && n_splits <= 65535 && n_kv_heads <= 65535 && n_tokens <= 65535,
                "attention_decode: grid too large (splits=%d kv_heads=%d tokens=%d)", n_splits, n_kv_heads, n_tokens);
-    PL_REQUIRE(n_splits == 1 || scratch != nullptr, "attention_decode: %d splits need scratch memory", n_splits);
+    PL_REQUIRE((n_splits <= kClusterSplitsMax && allow_cluster) || n_splits == 1 || scratch != nullptr,
+               "attention_decode: %d splits need scratch memory", n_splits);
     PL_REQUIRE(q_row_stride % 2 == 0 && (reinterpret_cast<uintptr_t>(q) & 3) == 0,
                "attention_decode: q must be 4-byte aligned with an even row stride");
     PL_REQUIRE((reinterpret_cast<uintptr_t>(k_pool) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_pool) & 15) == 0 &&
@@ -387,9 +534,26 @@ PL_API int pl_attention_decode(const void* q, int64_t q_row_stride, const void* 
     p.n_splits = n_splits;
     p.status = status;
     if (head_dim == 64) {
-        return launch_decode<64>(p, n_tokens, n_kv_heads, stream);
+        return launch_decode<64>(p, n_tokens, n_kv_heads, allow_cluster, stream);
     }
-    return launch_decode<128>(p, n_tokens, n_kv_heads, stream);
+    return launch_decode<128>(p, n_tokens, n_kv_heads, allow_cluster, stream);
+}
+
+}  // namespace
+
+// bf16 only. q and out [T, n_heads, head_dim] with row strides; one query per token
+// at position pos[t]; pools and table as in pl_attention_simt. scratch: at least
+// pl_attention_decode_scratch_floats floats when n_splits > 8 (fewer splits merge
+// inside a cluster and leave it untouched).
+PL_API int pl_attention_decode(const void* q, int64_t q_row_stride, const void* k_pool, const void* v_pool,
+                               int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
+                               const int32_t* table, int table_width, const int32_t* pos, const int32_t* entry,
+                               void* out, int64_t out_row_stride, int n_tokens, int n_heads, int n_kv_heads,
+                               int head_dim, int window, float scale, int n_splits, float* scratch,
+                               int32_t* status, cudaStream_t stream) {
+    return run_attention_decode(true, q, q_row_stride, k_pool, v_pool, page_stride, head_stride, page_size, n_pages,
+                                table, table_width, pos, entry, out, out_row_stride, n_tokens, n_heads, n_kv_heads,
+                                head_dim, window, scale, n_splits, scratch, status, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -454,7 +618,7 @@ PL_API int pl_attention_decode_static(const void* q, int64_t q_row_stride, const
     if (const int code = find_static_scratch(&scratch)) {
         return code;
     }
-    return pl_attention_decode(q, q_row_stride, k_pool, v_pool, page_stride, head_stride, page_size, n_pages, table,
-                               table_width, pos, entry, out, out_row_stride, n_tokens, n_heads, n_kv_heads, head_dim,
-                               window, scale, n_splits, scratch, status, stream);
+    return run_attention_decode(false, q, q_row_stride, k_pool, v_pool, page_stride, head_stride, page_size, n_pages,
+                                table, table_width, pos, entry, out, out_row_stride, n_tokens, n_heads, n_kv_heads,
+                                head_dim, window, scale, n_splits, scratch, status, stream);
 }
