@@ -140,19 +140,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     if (warp == 0) {
         // ------------------------------------------------ producer
         if (lane == 0) {
-            // Tiles walk their k range from different starting points, so that the CTAs
-            // do not all ask L2 for the same activation tile at the same moment. The
-            // order of a tile's sum depends on the tile alone.
-            const int rotate = (tile * 5) % n_units;
-            auto kb_of = [&](int u) { return kb0 + (u + rotate) % n_units; };
             const int early = min(n_units, kStages);
             for (int u = 0; u < early; ++u) {  // weights: nobody writes them, no need to wait
                 mbar_expect_tx(&full_bar[u], kStageBytes);
-                tma_load_2d(tiles + u * kStageBytes, &map_w, kb_of(u) * kBlockK, n0, &full_bar[u]);
+                tma_load_2d(tiles + u * kStageBytes, &map_w, (kb0 + u) * kBlockK, n0, &full_bar[u]);
             }
             pl_grid_wait();
             for (int u = 0; u < early; ++u) {
-                tma_load_2d(tiles + u * kStageBytes + kBytesA, &map_x, kb_of(u) * kBlockK, 0, &full_bar[u]);
+                tma_load_2d(tiles + u * kStageBytes + kBytesA, &map_x, (kb0 + u) * kBlockK, 0, &full_bar[u]);
             }
             int stage = early % kStages;
             uint32_t phase = early == kStages ? 1u : 0u;
@@ -162,8 +157,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 }
                 unsigned char* a = tiles + stage * kStageBytes;
                 mbar_expect_tx(&full_bar[stage], kStageBytes);
-                tma_load_2d(a, &map_w, kb_of(u) * kBlockK, n0, &full_bar[stage]);
-                tma_load_2d(a + kBytesA, &map_x, kb_of(u) * kBlockK, 0, &full_bar[stage]);
+                tma_load_2d(a, &map_w, (kb0 + u) * kBlockK, n0, &full_bar[stage]);
+                tma_load_2d(a + kBytesA, &map_x, (kb0 + u) * kBlockK, 0, &full_bar[stage]);
                 if (++stage == kStages) {
                     stage = 0;
                     phase ^= 1u;

@@ -55,7 +55,19 @@ def register_part(kind: str, name: str, cls: type | None = None, replace: bool =
     return add if cls is None else add(cls)
 
 
+_builtins_loaded = False
+
+
+def _load_builtins() -> None:
+    """The package's own parts register themselves when their modules are imported."""
+    global _builtins_loaded
+    if not _builtins_loaded:
+        _builtins_loaded = True
+        from . import attention, basic, block  # noqa: F401
+
+
 def part_class(kind: str, name: str) -> type:
+    _load_builtins()
     try:
         return _REGISTRIES[kind][name]
     except KeyError:
@@ -68,6 +80,7 @@ def build_part(kind: str, spec: PartSpec, ctx: BuildContext, **extra: Any):
 
 
 def registered_parts(kind: str) -> list[str]:
+    _load_builtins()
     return sorted(_REGISTRIES[kind])
 
 
