@@ -3,11 +3,16 @@
     python -m pulsarlm_b200.kernels.microbench gemm [--shapes T,N,K ...]
     python -m pulsarlm_b200.kernels.microbench attention_prefill [--tokens 2048 ...]
     python -m pulsarlm_b200.kernels.microbench attention_decode [--batch 8 --context 2048 ...]
+    python -m pulsarlm_b200.kernels.microbench decode_timeline [--layers 8 --batch 8 --context 2048]
 
 Each timing replays a CUDA graph of several launches (so host time does not
 count) over inputs rotated through enough copies to exceed L2, after warm-up,
 between CUDA events. Prints one line per case with achieved GB/s and TFLOP/s.
-`gemm` times the tcgen05 kernel beside the library product torch.mm calls.
+`gemm` times the tcgen05 kernels beside the library product torch.mm calls.
+`decode_timeline` replays the engine's captured decode step of a Llama-3.1-8B-shaped
+model (random weights, fewer layers) under the torch profiler's CUDA activity trace and
+prints when each kernel of one layer starts and ends inside the graph: kernels overlap
+(programmatic dependent launch), so the differences of the END times are what each costs.
 """
 
 from __future__ import annotations
@@ -109,9 +114,82 @@ def bench_attention_decode(batches, contexts, n_heads, n_kv, head_dim, page) -> 
                   f"splits={splits}: {us:.1f} us, {gb / us * 1e6:.0f} GB/s", flush=True)
 
 
+LLAMA31_8B_SHAPE = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": 4096, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336, "vocab_size": 128256,
+    "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 131072,
+}
+
+
+def decode_timeline(layers: int, batch: int, context: int, page: int) -> None:
+    import collections
+    import re
+
+    from torch.profiler import ProfilerActivity, profile
+
+    from ..engine.engine import Engine
+    from ..engine.runner import StepEntry
+    from ..sampling.params import SamplingParams
+
+    config = dict(LLAMA31_8B_SHAPE, num_hidden_layers=layers)
+    n_pages = batch * (context + 256) // page + 64
+    engine = Engine(config, dtype="bfloat16", device="cuda:0", n_pages=n_pages, page_size=page,
+                    prefill_tokens_per_step=2048, max_requests=batch + 2, seed=0)
+    for group in engine.cache.groups:
+        group.tensor.normal_(0.0, 0.5)
+    ids = []
+    for b in range(batch):  # requests that hold `context` tokens, without running a prefill
+        engine.cache.open(("timeline", b))
+        engine.cache.reserve(("timeline", b), context)
+        engine.cache.commit(("timeline", b), context)
+        ids.append(("timeline", b))
+    params = [SamplingParams()] * batch
+    entries = [StepEntry(r, [(7 * i + 3) % 1000], [0]) for i, r in enumerate(ids)]
+
+    def step():
+        engine.runner.decode_step(entries, params, [0] * batch, [0] * batch)
+
+    for _ in range(5):
+        step()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+    events = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                    key=lambda e: e.time_range.start)
+    per_step = len(events) // 3
+    last = [(e.name, e.time_range.start, e.time_range.end) for e in events[-per_step:]]
+
+    def short(name: str) -> str:
+        name = name.replace("void ", "").replace("(anonymous namespace)::", "")
+        base = re.match(r"[\w:]+", name)
+        args = re.search(r"<([^>]{0,40})", name)
+        return (base.group(0) if base else name[:40]) + ("<" + args.group(1) + ">" if args else "")
+
+    t0 = last[0][1]
+    print(f"decode step: batch {batch}, context {context}, {layers} layers: {per_step} device activities, "
+          f"{last[-1][2] - t0:.1f} us from first start to last end")
+    totals = collections.OrderedDict()
+    for name, start, end in last:
+        entry = totals.setdefault(short(name), [0, 0.0])
+        entry[0] += 1
+        entry[1] += end - start
+    for name, (count, total) in totals.items():
+        print(f"  {name:58s} x{count:3d}  resident {total / count:7.2f} us each")
+    print("one layer from the middle of the step (us from the step's start; a kernel is resident from its start, "
+          "its work begins when its predecessor ends):")
+    middle = per_step // 2
+    previous_end = None
+    for name, start, end in last[middle: middle + 2 * max(1, (per_step - 4) // max(1, layers)) + 1]:
+        after = "" if previous_end is None else f"  (+{end - previous_end:6.2f} after the previous end)"
+        print(f"  start {start - t0:9.2f}  end {end - t0:9.2f}  {short(name)}{after}")
+        previous_end = end
+
+
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("what", choices=["gemm", "attention_prefill", "attention_decode"])
+    parser.add_argument("what", choices=["gemm", "attention_prefill", "attention_decode", "decode_timeline"])
     parser.add_argument("--shapes", nargs="*", default=None, help="T,N,K triples for gemm")
     parser.add_argument("--tokens", type=int, nargs="*", default=[2048, 8192])
     parser.add_argument("--batch", type=int, nargs="*", default=[1, 8, 64])
@@ -120,11 +198,15 @@ def main() -> None:
     parser.add_argument("--kv_heads", type=int, default=8)
     parser.add_argument("--head_dim", type=int, default=128)
     parser.add_argument("--page_size", type=int, default=16)
+    parser.add_argument("--layers", type=int, default=8, help="layers of the decode_timeline model")
     args = parser.parse_args()
     ops.require_device()
     if args.what == "gemm":
         shapes = LLAMA8B_SHAPES if not args.shapes else [tuple(int(v) for v in s.split(",")) for s in args.shapes]
         bench_gemm(shapes)
+    elif args.what == "decode_timeline":
+        decode_timeline(args.layers, args.batch[0] if len(args.batch) == 1 else 8,
+                        args.context[0] if len(args.context) == 1 else 2048, args.page_size)
     elif args.what == "attention_prefill":
         bench_attention_prefill(args.tokens, args.heads, args.kv_heads, args.head_dim, args.page_size)
     else:
