@@ -478,6 +478,45 @@ PL_API int pl_attention_decode_supports(int head_dim, int group, int page_size, 
         page_size % kTile == 0;
 }
 
+// How many clusters of `n_splits` CTAs of the decode kernel the device holds at once
+// (0: unknown or not a cluster size). A launch with more (kv head, token) pairs than
+// this runs its clusters in more than one wave.
+PL_API int pl_attention_decode_resident_clusters(int head_dim, int group, int n_splits) {
+    if (n_splits < 2 || n_splits > kClusterSplitsMax || (head_dim != 64 && head_dim != 128)) {
+        return 0;
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(n_splits, 64, 64);
+    config.blockDim = dim3(kWarps * 32);
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = n_splits;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    int clusters = 0;
+    cudaError_t err;
+    if (head_dim == 64) {
+        constexpr int rings = kWarps * kStages * 2 * kTile * 64 * 2;
+        cudaFuncSetAttribute(attention_decode_kernel<64, kWarps, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             rings + merge_bytes(16 * 16, kClusterSplitsMax) + 1024);
+        config.dynamicSmemBytes = rings + merge_bytes(group * 16, n_splits);
+        err = cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel<64, kWarps, kStages>, &config);
+    } else {
+        constexpr int rings = kWarps * kStages * 2 * kTile * 128 * 2;
+        cudaFuncSetAttribute(attention_decode_kernel<128, kWarps, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             rings + merge_bytes(16 * 32, kClusterSplitsMax) + 1024);
+        config.dynamicSmemBytes = rings + merge_bytes(group * 32, n_splits);
+        err = cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel<128, kWarps, kStages>, &config);
+    }
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return clusters;
+}
+
 // Scratch floats needed for `n_tokens` tokens at `n_splits` splits.
 PL_API int64_t pl_attention_decode_scratch_floats(int n_tokens, int n_heads, int head_dim, int n_splits) {
     return n_splits <= 1 ? 0 : static_cast<int64_t>(n_tokens) * n_heads * n_splits * (head_dim + 2);

@@ -6,14 +6,19 @@
 //   PV = P V     M 128 x N head_dim x K 64 keys   (P K-major, V as stored: N-major)
 // Roles: warp 0 loads tiles with TMA (Q once; per 64-key tile the K and V rows of
 // four 16-key page pieces, found through the block table), warp 1 issues the MMAs,
-// warps 2-9 are two softmax warpgroups that share each query row: thread pairs
-// (one per warpgroup) read the two halves of the row's S from tensor memory, agree
-// on the row maximum through shared memory, do the online softmax in fp32 (base 2,
-// scale folded in), write their half of P as bf16 into shared memory for the second
-// product, and fold their half of each tile's PV into an fp32 output row kept in
-// registers (o = o * correction + PV). Two warps per scheduler hide each other's
-// latencies. S, P and PV are double-buffered, so the MMAs of tile j+1 run while the
-// softmax of tile j is computed.
+// warps 2-9 are two softmax warpgroups. When the GQA group is even a CTA takes two
+// query heads of one kv head: they share every K and V tile, and each warpgroup
+// does one head's softmax with one thread per query row. Otherwise a CTA takes one
+// head and the warpgroups share each row (thread pairs read the two halves of the
+// row's S and agree on the row maximum through shared memory). The softmax is
+// online, in fp32, base 2 with the scale folded in; P goes as bf16 into shared
+// memory for the second product, whose output accumulates in tensor memory over all
+// tiles. The exponents' base follows the row maximum lazily: it moves only when a
+// tile's maximum exceeds it by more than 2^8 (P then stays below 256, which fp32
+// sums and bf16 P hold without loss), and only then is the row of O read from
+// tensor memory, scaled and written back, after the previous PV has completed; most
+// tiles never touch O. S is double-buffered, so S of tile j+1 is computed while the
+// softmax of tile j runs.
 //
 // Every mbarrier wait is bounded; on a timeout the CTA raises bit 8 of the status
 // word, stops, lets loads in flight land, frees its tensor memory and returns.
@@ -61,17 +66,24 @@ __device__ __forceinline__ uint64_t smem_descriptor_mn(const void* tile, uint32_
         (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 
-template <int HD>
+// HEADS query heads per CTA: 2 when the GQA group is even (two heads of one kv head
+// share every K and V tile, one softmax warpgroup each, one thread per query row), 1
+// otherwise (the two warpgroups share each row: one takes the tile's first 32 keys
+// and the first half of the output's dims, the other the rest).
+template <int HD, int HEADS>
 __global__ void __launch_bounds__(kThreadsTc, 1)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, const TcPrefillParams p) {
     constexpr int kHalves = HD / 64;                       // 64-dim (128-byte) column groups of a row
-    constexpr int kBytesQ = kRows * HD * 2;                // kHalves sub-tiles of [128 x 64]
+    constexpr int kBytesQ = kRows * HD * 2;                // per head: kHalves sub-tiles of [128 x 64]
     constexpr int kBytesK = kKeys * HD * 2;                // kHalves sub-tiles of [64 x 64]
     constexpr int kBytesStage = 2 * kBytesK;               // K then V
     constexpr int kBytesP = kRows * kKeys * 2;             // [128 x 64]
-    constexpr uint32_t kColsS = kKeys, kColsPV = HD;
-    constexpr uint32_t kColumns = 2 * kColsS + 2 * kColsPV <= 256 ? 256 : 512;
+    constexpr int kBuffersP = HEADS == 2 ? 1 : 2;          // P tiles per head in shared memory
+    constexpr int kWarpsPerHead = 8 / HEADS;               // softmax warps that arrive on a head's barriers
+    constexpr uint32_t kColsS = kKeys, kColsO = HD;
+    constexpr uint32_t kColumns = HEADS * (2 * kColsS + kColsO) <= 256 ? 256 : 512;
+    constexpr float kLazy = 8.0f;  // the base of the exponents may lag the row maximum by this much (log2)
     // instruction descriptors: fp32 accumulate, bf16 operands, M = 128
     constexpr uint32_t kIdescS = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kKeys >> 3) << 17) |
         (static_cast<uint32_t>(kRows >> 4) << 24);
@@ -81,20 +93,21 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     extern __shared__ unsigned char raw_smem[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
                                                            ~static_cast<uintptr_t>(1023));
-    unsigned char* q_s = smem;
-    unsigned char* kv_s = q_s + kBytesQ;
-    unsigned char* p_s = kv_s + kStagesKV * kBytesStage;
+    unsigned char* q_s = smem;                               // [head][half][128 rows x 128 bytes]
+    unsigned char* kv_s = q_s + HEADS * kBytesQ;
+    unsigned char* p_s = kv_s + kStagesKV * kBytesStage;     // [head][buffer][128 rows x 128 bytes]
 
     __shared__ __align__(8) uint64_t q_full, kv_full[kStagesKV], kv_empty[kStagesKV];
-    __shared__ __align__(8) uint64_t s_full[2], s_free[2], p_full[2], p_free[2], pv_full[2], pv_free[2];
+    __shared__ __align__(8) uint64_t s_full[HEADS][2], s_free[HEADS][2], p_full[HEADS][kBuffersP],
+        p_free[HEADS][kBuffersP], pv_done[HEADS];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
-    __shared__ float half_max[2][2 * kRows];  // [tile parity][warpgroup * 128 + row]
+    __shared__ float half_max[HEADS == 1 ? 2 : 1][HEADS == 1 ? 2 * kRows : 1];  // [tile parity][warpgroup * 128 + row]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int4 tile = p.tiles[blockIdx.x];
     const int row0 = tile.x, n_rows = tile.y, pos0 = tile.z;
-    const int head = blockIdx.y, kv_head = head / p.group;
+    const int head0 = blockIdx.y * HEADS, kv_head = head0 / p.group;
     const int last_key = pos0 + n_rows - 1;
     const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
     const int j0 = first_key / kKeys, n_tiles = last_key / kKeys - j0 + 1;
@@ -105,13 +118,16 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             mbar_init(&kv_full[s], 1);
             mbar_init(&kv_empty[s], 1);
         }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(&s_full[b], 1);
-            mbar_init(&s_free[b], 8);  // one arrival per softmax warp
-            mbar_init(&p_full[b], 8);
-            mbar_init(&p_free[b], 1);
-            mbar_init(&pv_full[b], 1);
-            mbar_init(&pv_free[b], 8);
+        for (int h = 0; h < HEADS; ++h) {
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(&s_full[h][b], 1);
+                mbar_init(&s_free[h][b], kWarpsPerHead);
+            }
+            for (int b = 0; b < kBuffersP; ++b) {
+                mbar_init(&p_full[h][b], kWarpsPerHead);
+                mbar_init(&p_free[h][b], 1);
+            }
+            mbar_init(&pv_done[h], 1);
         }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -123,7 +139,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
-    const uint32_t tmem_s = tmem_base, tmem_pv = tmem_base + 2 * kColsS;
+    const uint32_t tmem_s = tmem_base;                        // [head][2 buffers][64 columns]
+    const uint32_t tmem_o = tmem_base + HEADS * 2 * kColsS;   // [head][HD columns]
 
     if (warp == 0) {
         // ------------------------------------------------ producer
@@ -131,9 +148,12 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         // (eight tiles) at a time in one load each, so that the table's latency is
         // paid once per eight tiles and not once per piece.
         if (lane == 0) {
-            mbar_expect_tx(&q_full, kBytesQ);
-            for (int h = 0; h < kHalves; ++h) {
-                tma_load_2d(q_s + h * (kRows * 128), &map_q, head * HD + h * 64, row0, &q_full);
+            mbar_expect_tx(&q_full, HEADS * kBytesQ);
+            for (int hs = 0; hs < HEADS; ++hs) {
+                for (int h = 0; h < kHalves; ++h) {
+                    tma_load_2d(q_s + hs * kBytesQ + h * (kRows * 128), &map_q, (head0 + hs) * HD + h * 64, row0,
+                                &q_full);
+                }
             }
         }
         const int32_t* table_row = p.table + static_cast<int64_t>(tile.w) * p.table_width;
@@ -182,206 +202,234 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            auto issue_s = [&](int j) {  // S_j = Q K_j^T into buffer j & 1
-                const unsigned char* k_s = kv_s + (j % kStagesKV) * kBytesStage;
-                const uint32_t d = tmem_s + (j & 1) * kColsS;
+        // All lanes run the loop and wait; one elected lane issues. (Descriptors and
+        // counters then live in uniform registers, which the MMA instructions take.)
+        auto issue_s = [&](int j, int hs) {  // S_j = Q K_j^T of head hs into its buffer j & 1
+            const unsigned char* k_s = kv_s + (j % kStagesKV) * kBytesStage;
+            const uint32_t d = tmem_s + (hs * 2 + (j & 1)) * kColsS;
+            if (elect_one()) {
 #pragma unroll
                 for (int h = 0; h < kHalves; ++h) {
-                    const uint64_t da = smem_descriptor(q_s + h * (kRows * 128));
+                    const uint64_t da = smem_descriptor(q_s + hs * kBytesQ + h * (kRows * 128));
                     const uint64_t db = smem_descriptor(k_s + h * (kKeys * 128));
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         tcgen05_mma(d, da + 2 * k, db + 2 * k, kIdescS, (h > 0 || k > 0) ? 1u : 0u);
                     }
                 }
-                tcgen05_commit(&s_full[j & 1]);
-            };
-            bool ok = mbar_wait(&q_full, 0, &abort_flag) && mbar_wait(&kv_full[0], 0, &abort_flag);
-            if (ok) {
-                tcgen05_fence_after();
-                issue_s(0);
+                tcgen05_commit(&s_full[hs][j & 1]);
             }
-            for (int j = 0; ok && j < n_tiles; ++j) {
-                if (j + 1 < n_tiles) {
-                    const int next = j + 1;
-                    ok = mbar_wait(&kv_full[next % kStagesKV], (next / kStagesKV) & 1, &abort_flag) &&
-                        mbar_wait(&s_free[next & 1], ((next >> 1) & 1) ^ 1u, &abort_flag);
-                    if (!ok) {
-                        break;
+            __syncwarp();
+        };
+        bool ok = mbar_wait(&q_full, 0, &abort_flag) && mbar_wait(&kv_full[0], 0, &abort_flag);
+        if (ok) {
+            tcgen05_fence_after();
+            for (int hs = 0; hs < HEADS; ++hs) {
+                issue_s(0, hs);
+            }
+        }
+        for (int j = 0; ok && j < n_tiles; ++j) {
+            if (j + 1 < n_tiles) {
+                const int next = j + 1;
+                ok = mbar_wait(&kv_full[next % kStagesKV], (next / kStagesKV) & 1, &abort_flag);
+                for (int hs = 0; ok && hs < HEADS; ++hs) {
+                    ok = mbar_wait(&s_free[hs][next & 1], ((next >> 1) & 1) ^ 1u, &abort_flag);
+                    if (ok) {
+                        tcgen05_fence_after();
+                        issue_s(next, hs);
                     }
-                    tcgen05_fence_after();
-                    issue_s(next);
                 }
-                const int b = j & 1;
-                ok = mbar_wait(&p_full[b], (j >> 1) & 1, &abort_flag) &&
-                    mbar_wait(&pv_free[b], ((j >> 1) & 1) ^ 1u, &abort_flag);
+                if (!ok) {
+                    break;
+                }
+            }
+            const unsigned char* v_s = kv_s + (j % kStagesKV) * kBytesStage + kBytesK;
+            const uint64_t db = smem_descriptor_mn(v_s, kKeys * 128);
+            const int pb = j % kBuffersP;
+            for (int hs = 0; ok && hs < HEADS; ++hs) {
+                // P_j of this head is written, and its O rescaled if its base moved
+                ok = mbar_wait(&p_full[hs][pb], (j / kBuffersP) & 1, &abort_flag);
                 if (!ok) {
                     break;
                 }
                 tcgen05_fence_after();
-                const unsigned char* v_s = kv_s + (j % kStagesKV) * kBytesStage + kBytesK;
-                const uint64_t da = smem_descriptor(p_s + b * kBytesP);
-                const uint64_t db = smem_descriptor_mn(v_s, kKeys * 128);
+                const uint64_t da = smem_descriptor(p_s + (hs * kBuffersP + pb) * kBytesP);
+                if (elect_one()) {
 #pragma unroll
-                for (int k = 0; k < kKeys / 16; ++k) {
-                    // 16 keys further: 32 bytes along P's rows, 16 rows of 128 bytes in V
-                    tcgen05_mma(tmem_pv + b * kColsPV, da + 2 * k, db + k * ((16 * 128) >> 4), kIdescPV,
-                                k > 0 ? 1u : 0u);
+                    for (int k = 0; k < kKeys / 16; ++k) {
+                        // 16 keys further: 32 bytes along P's rows, 16 rows of 128 bytes in V
+                        tcgen05_mma(tmem_o + hs * kColsO, da + 2 * k, db + k * ((16 * 128) >> 4), kIdescPV,
+                                    (j > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit(&pv_done[hs]);
+                    tcgen05_commit(&p_free[hs][pb]);
+                    if (hs == HEADS - 1) {
+                        tcgen05_commit(&kv_empty[j % kStagesKV]);
+                    }
                 }
-                tcgen05_commit(&pv_full[b]);
-                tcgen05_commit(&p_free[b]);
-                tcgen05_commit(&kv_empty[j % kStagesKV]);
+                __syncwarp();
             }
         }
     } else {
         // ------------------------------------------------ softmax and output (warps 2..9)
-        constexpr int kHalfKeys = kKeys / 2, kHalfDims = HD / 2;
-        const int wg = (warp - 2) >> 2;        // which half of the row's keys and dims
-        const int lane_group = warp & 3;       // the TMEM lanes this warp may read
-        const int r = lane_group * 32 + lane;  // this thread's query row
+        const int wg = (warp - 2) >> 2;           // warpgroup 0 or 1
+        const int hs = HEADS == 2 ? wg : 0;       // the head it works on
+        const int part = HEADS == 2 ? 0 : wg;     // HEADS == 1: which half of the row's keys and dims
+        constexpr int kMyKeys = HEADS == 2 ? kKeys : kKeys / 2;
+        constexpr int kMyDims = HEADS == 2 ? HD : HD / 2;
+        const int lane_group = warp & 3;          // the TMEM lanes this warp may read
+        const int r = lane_group * 32 + lane;     // this thread's query row
         const uint32_t lane_bits = static_cast<uint32_t>(lane_group * 32) << 16;
+        const uint32_t my_s = tmem_s + lane_bits + hs * 2 * kColsS + part * kMyKeys;
+        const uint32_t my_o = tmem_o + lane_bits + hs * kColsO + part * kMyDims;
         const int pos = pos0 + r;
         const int first = p.window > 0 ? pos - p.window + 1 : 0;
-        float o[kHalfDims];
-#pragma unroll
-        for (int d = 0; d < kHalfDims; ++d) {
-            o[d] = 0.0f;
-        }
-        float m = -INFINITY, l = 0.0f, corr_prev = 1.0f;
+        float m = -INFINITY, l = 0.0f;  // m: the base of the exponents in use (lags the true maximum)
         bool ok = true;
 
-        auto fold_pv = [&](int j, float corr) {  // o = o * corr + this thread's half of PV_j
-            const int b = j & 1;
-            if (!mbar_wait(&pv_full[b], (j >> 1) & 1, &abort_flag)) {
-                return false;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int b = j & 1, pb = j % kBuffersP;
+            if (!mbar_wait(&s_full[hs][b], (j >> 1) & 1, &abort_flag)) {
+                ok = false;
+                break;
             }
             tcgen05_fence_after();
+            float s[kMyKeys];
             {
-                // all of this thread's PV columns in flight, then one wait
-                uint32_t v[kHalfDims / 32][32];
+                uint32_t v[kMyKeys / 32][32];
 #pragma unroll
-                for (int g = 0; g < kHalfDims / 32; ++g) {
-                    tcgen05_ld32_nowait(tmem_pv + lane_bits + b * kColsPV + wg * kHalfDims + 32 * g, v[g]);
+                for (int g = 0; g < kMyKeys / 32; ++g) {
+                    tcgen05_ld32_nowait(my_s + b * kColsS + 32 * g, v[g]);
                 }
                 tcgen05_wait_ld();
 #pragma unroll
-                for (int g = 0; g < kHalfDims / 32; ++g) {
+                for (int g = 0; g < kMyKeys / 32; ++g) {
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
-                        o[32 * g + c] = fmaf(o[32 * g + c], corr, __uint_as_float(v[g][c]));
+                        s[32 * g + c] = __uint_as_float(v[g][c]);
                     }
                 }
             }
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(&pv_free[b]);
+                mbar_arrive(&s_free[hs][b]);
             }
-            return true;
-        };
-
-        for (int j = 0; j < n_tiles; ++j) {
-            const int b = j & 1;
-            if (!mbar_wait(&s_full[b], (j >> 1) & 1, &abort_flag)) {
-                ok = false;
-                break;
-            }
-            tcgen05_fence_after();
-            float s[kHalfKeys];
-            {
-                static_assert(kHalfKeys == 32, "one 32-column load per thread");
-                uint32_t v[32];
-                tcgen05_ld32_nowait(tmem_s + lane_bits + b * kColsS + wg * kHalfKeys, v);
-                tcgen05_wait_ld();
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    s[c] = __uint_as_float(v[c]);
-                }
-            }
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&s_free[b]);
-            }
-            const int key0 = (j0 + j) * kKeys;
-            const bool edge = key0 + kKeys - 1 > pos0 || (p.window > 0 && key0 < pos0 + kRows - p.window);
+            const int key0 = (j0 + j) * kKeys + part * kMyKeys;
+            const bool edge = (j0 + j) * kKeys + kKeys - 1 > pos0 ||
+                (p.window > 0 && (j0 + j) * kKeys < pos0 + kRows - p.window);
             float tile_max = -INFINITY;
             if (edge) {
 #pragma unroll
-                for (int c = 0; c < kHalfKeys; ++c) {
-                    const int key = key0 + wg * kHalfKeys + c;
+                for (int c = 0; c < kMyKeys; ++c) {
+                    const int key = key0 + c;
                     s[c] = (key <= pos && key >= first) ? s[c] * p.scale_log2 : -INFINITY;
                     tile_max = fmaxf(tile_max, s[c]);
                 }
             } else {
 #pragma unroll
-                for (int c = 0; c < kHalfKeys; ++c) {
+                for (int c = 0; c < kMyKeys; ++c) {
                     s[c] *= p.scale_log2;
                     tile_max = fmaxf(tile_max, s[c]);
                 }
             }
-            // The row's maximum over both halves: exchange through shared memory.
-            half_max[b][wg * kRows + r] = tile_max;
-            asm volatile("bar.sync 2, 256;" ::: "memory");
-            tile_max = fmaxf(tile_max, half_max[b][(wg ^ 1) * kRows + r]);
-            const float m_new = fmaxf(m, tile_max);
-            const float base = m_new == -INFINITY ? 0.0f : m_new;
-            const float corr = ex2(m - base);
-            m = m_new;
-            float sum = 0.0f;
-            uint32_t packed[kHalfKeys / 2];
+            if (HEADS == 1) {
+                // The row's maximum over both halves: exchange through shared memory.
+                half_max[b][wg * kRows + r] = tile_max;
+                asm volatile("bar.sync 2, 256;" ::: "memory");
+                tile_max = fmaxf(tile_max, half_max[b][(wg ^ 1) * kRows + r]);
+            }
+            // Move the base only when the tile's maximum has run away from it. (With two
+            // threads to a row both see the same maximum and decide alike.)
+            const bool move = tile_max > m + kLazy;
+            float corr = 1.0f;
+            if (move) {
+                corr = ex2(m - tile_max);  // 0 when nothing was accumulated under the old base
+                m = tile_max;
+            }
+            if (j > 0 && __any_sync(0xffffffffu, move)) {
+                // Rows of this warp change base: scale their part of O where it lies. The
+                // previous PV must have landed; the next one waits for this tile's P.
+                if (!mbar_wait(&pv_done[hs], (j - 1) & 1, &abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tcgen05_fence_after();
 #pragma unroll
-            for (int c = 0; c < kHalfKeys; c += 2) {
+                for (int g = 0; g < kMyDims / 32; ++g) {
+                    uint32_t v[32];
+                    tcgen05_ld32_nowait(my_o + 32 * g, v);
+                    tcgen05_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        v[c] = __float_as_uint(__uint_as_float(v[c]) * corr);
+                    }
+                    tcgen05_st32_nowait(my_o + 32 * g, v);
+                }
+                tcgen05_wait_st();
+                tcgen05_fence_before();
+            }
+            const float base = m == -INFINITY ? 0.0f : m;
+            float sum = 0.0f;
+            uint32_t packed[kMyKeys / 2];
+#pragma unroll
+            for (int c = 0; c < kMyKeys; c += 2) {
                 const float p0 = ex2(s[c] - base), p1 = ex2(s[c + 1] - base);
                 sum += p0 + p1;
                 const __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
                 packed[c / 2] = *reinterpret_cast<const uint32_t*>(&pair);
             }
-            l = l * corr + sum;  // this thread's half of the row sum; the halves meet at the end
-            // P_j into its buffer (free once PV_{j-2} has read it), row r, swizzled.
-            if (!mbar_wait(&p_free[b], ((j >> 1) & 1) ^ 1u, &abort_flag)) {
+            l = l * corr + sum;  // (HEADS == 1: this thread's half of the row sum; the halves meet at the end)
+            // P_j into its buffer, free once the PV that last read it has completed; row r, swizzled.
+            if (!mbar_wait(&p_free[hs][pb], ((j / kBuffersP) & 1) ^ 1u, &abort_flag)) {
                 ok = false;
                 break;
             }
-            unsigned char* p_row = p_s + b * kBytesP + r * 128;
+            unsigned char* p_row = p_s + (hs * kBuffersP + pb) * kBytesP + r * 128;
 #pragma unroll
-            for (int c = 0; c < kHalfKeys / 8; ++c) {
-                const int chunk = wg * (kHalfKeys / 8) + c;
+            for (int c = 0; c < kMyKeys / 8; ++c) {
+                const int chunk = part * (kMyKeys / 8) + c;
                 *reinterpret_cast<uint4*>(p_row + ((chunk ^ (r & 7)) * 16)) =
                     make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(&p_full[b]);
+                mbar_arrive(&p_full[hs][pb]);
             }
-            if (j > 0 && !fold_pv(j - 1, corr_prev)) {
-                ok = false;
-                break;
-            }
-            corr_prev = corr;
+        }
+        if (HEADS == 1) {
+            // The row sum is the sum of the two halves' sums (both followed the same bases).
+            half_max[0][wg * kRows + r] = l;
+            asm volatile("bar.sync 2, 256;" ::: "memory");
+            l += half_max[0][(wg ^ 1) * kRows + r];
         }
         if (ok && n_tiles > 0) {
-            ok = fold_pv(n_tiles - 1, corr_prev);
+            ok = mbar_wait(&pv_done[hs], (n_tiles - 1) & 1, &abort_flag);
+            tcgen05_fence_after();
         }
-        // The row sum is the sum of the two halves' sums (both followed the same maxima).
-        half_max[0][wg * kRows + r] = l;
-        asm volatile("bar.sync 2, 256;" ::: "memory");
-        l += half_max[0][(wg ^ 1) * kRows + r];
-        if (ok && r < n_rows) {
+        if (ok) {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            __nv_bfloat16* dst = p.out + (row0 + r) * p.out_row_stride + static_cast<int64_t>(head) * HD +
-                wg * kHalfDims;
+            __nv_bfloat16* dst = p.out + (row0 + r) * p.out_row_stride + static_cast<int64_t>(head0 + hs) * HD +
+                part * kMyDims;
 #pragma unroll
-            for (int d = 0; d < kHalfDims; d += 8) {
-                uint32_t w[4];
+            for (int g = 0; g < kMyDims / 32; ++g) {
+                uint32_t v[32];
+                tcgen05_ld32_nowait(my_o + 32 * g, v);  // all lanes take part
+                tcgen05_wait_ld();
+                if (r < n_rows && n_tiles > 0) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const __nv_bfloat162 pair = __floats2bfloat162_rn(o[d + 2 * i] * inv, o[d + 2 * i + 1] * inv);
-                    w[i] = *reinterpret_cast<const uint32_t*>(&pair);
+                    for (int d = 0; d < 32; d += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const __nv_bfloat162 pair = __floats2bfloat162_rn(
+                                __uint_as_float(v[d + 2 * i]) * inv, __uint_as_float(v[d + 2 * i + 1]) * inv);
+                            w[i] = *reinterpret_cast<const uint32_t*>(&pair);
+                        }
+                        *reinterpret_cast<uint4*>(dst + 32 * g + d) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
                 }
-                *reinterpret_cast<uint4*>(dst + d) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
     }
@@ -407,13 +455,14 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     }
 }
 
-template <int HD>
+template <int HD, int HEADS>
 int launch_tc_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcPrefillParams& p,
                       int n_tiles, int n_heads, cudaStream_t stream) {
-    constexpr int smem = kRows * HD * 2 + kStagesKV * 2 * kKeys * HD * 2 + 2 * kRows * kKeys * 2 + 1024;
+    constexpr int smem = HEADS * kRows * HD * 2 + kStagesKV * 2 * kKeys * HD * 2 +
+        HEADS * (HEADS == 2 ? 1 : 2) * kRows * kKeys * 2 + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD>,
+        cudaError_t err = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD, HEADS>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (err != cudaSuccess) {
             return pl_fail(3, "attention_prefill_tcgen05: cannot set shared memory size: %s",
@@ -421,7 +470,8 @@ int launch_tc_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
         }
         configured = true;
     }
-    attention_prefill_tcgen05_kernel<HD><<<dim3(n_tiles, n_heads), kThreadsTc, smem, stream>>>(mq, mk, mv, p);
+    attention_prefill_tcgen05_kernel<HD, HEADS><<<dim3(n_tiles, n_heads / HEADS), kThreadsTc, smem, stream>>>(mq, mk,
+                                                                                                              mv, p);
     PL_CHECK_LAUNCH("attention_prefill_tcgen05");
     return 0;
 }
@@ -490,8 +540,11 @@ PL_API int pl_attention_prefill_tcgen05(const void* q, int64_t q_row_stride, int
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = status;
+    const bool pairs = p.group % 2 == 0;  // two heads of one kv head per CTA
     if (head_dim == 64) {
-        return launch_tc_prefill<64>(mq, mk, mv, p, n_tiles, n_heads, stream);
+        return pairs ? launch_tc_prefill<64, 2>(mq, mk, mv, p, n_tiles, n_heads, stream)
+                     : launch_tc_prefill<64, 1>(mq, mk, mv, p, n_tiles, n_heads, stream);
     }
-    return launch_tc_prefill<128>(mq, mk, mv, p, n_tiles, n_heads, stream);
+    return pairs ? launch_tc_prefill<128, 2>(mq, mk, mv, p, n_tiles, n_heads, stream)
+                 : launch_tc_prefill<128, 1>(mq, mk, mv, p, n_tiles, n_heads, stream);
 }

@@ -137,62 +137,76 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int n_units = min(p.kb_per_split, p.k_blocks - kb0);
     const int n0 = tile * kTileM;
 
+    // The producer and the issuer run their loops with all lanes of their warp, so that
+    // counters, addresses and descriptors stay in uniform registers, and let one elected
+    // lane issue.
     if (warp == 0) {
         // ------------------------------------------------ producer
-        if (lane == 0) {
-            const int early = min(n_units, kStages);
-            for (int u = 0; u < early; ++u) {  // weights: nobody writes them, no need to wait
+        const int early = min(n_units, kStages);
+        for (int u = 0; u < early; ++u) {  // weights: nobody writes them, no need to wait
+            if (elect_one()) {
                 mbar_expect_tx(&full_bar[u], kStageBytes);
                 tma_load_2d(tiles + u * kStageBytes, &map_w, (kb0 + u) * kBlockK, n0, &full_bar[u]);
             }
-            pl_grid_wait();
-            for (int u = 0; u < early; ++u) {
+            __syncwarp();
+        }
+        pl_grid_wait();
+        for (int u = 0; u < early; ++u) {
+            if (elect_one()) {
                 tma_load_2d(tiles + u * kStageBytes + kBytesA, &map_x, (kb0 + u) * kBlockK, 0, &full_bar[u]);
             }
-            int stage = early % kStages;
-            uint32_t phase = early == kStages ? 1u : 0u;
-            for (int u = early; u < n_units; ++u) {
-                if (!mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_flag)) {
-                    break;
-                }
-                unsigned char* a = tiles + stage * kStageBytes;
+            __syncwarp();
+        }
+        int stage = early % kStages;
+        uint32_t phase = early == kStages ? 1u : 0u;
+        for (int u = early; u < n_units; ++u) {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_flag)) {
+                break;
+            }
+            unsigned char* a = tiles + stage * kStageBytes;
+            if (elect_one()) {
                 mbar_expect_tx(&full_bar[stage], kStageBytes);
                 tma_load_2d(a, &map_w, (kb0 + u) * kBlockK, n0, &full_bar[stage]);
                 tma_load_2d(a + kBytesA, &map_x, (kb0 + u) * kBlockK, 0, &full_bar[stage]);
-                if (++stage == kStages) {
-                    stage = 0;
-                    phase ^= 1u;
-                }
+            }
+            __syncwarp();
+            if (++stage == kStages) {
+                stage = 0;
+                phase ^= 1u;
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            pl_grid_wait();  // the bounded waits below then time this kernel's own work only
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int u = 0; u < n_units; ++u) {
-                if (!mbar_wait(&full_bar[stage], phase, &abort_flag)) {
-                    ok = false;
-                    break;
-                }
-                tcgen05_fence_after();
-                const unsigned char* a = tiles + stage * kStageBytes;
-                const uint64_t desc_a = smem_descriptor(a), desc_b = smem_descriptor(a + kBytesA);
+        pl_grid_wait();  // the bounded waits below then time this kernel's own work only
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int u = 0; u < n_units; ++u) {
+            if (!mbar_wait(&full_bar[stage], phase, &abort_flag)) {
+                ok = false;
+                break;
+            }
+            tcgen05_fence_after();
+            const unsigned char* a = tiles + stage * kStageBytes;
+            const uint64_t desc_a = smem_descriptor(a), desc_b = smem_descriptor(a + kBytesA);
+            if (elect_one()) {
 #pragma unroll
                 for (int k = 0; k < kBlockK / 16; ++k) {
                     tcgen05_mma(tmem_base, desc_a + 2 * k, desc_b + 2 * k, kIdesc, (u > 0 || k > 0) ? 1u : 0u);
                 }
                 tcgen05_commit(&empty_bar[stage]);
-                if (++stage == kStages) {
-                    stage = 0;
-                    phase ^= 1u;
-                }
             }
-            if (ok) {
+            __syncwarp();
+            if (++stage == kStages) {
+                stage = 0;
+                phase ^= 1u;
+            }
+        }
+        if (ok) {
+            if (elect_one()) {
                 tcgen05_commit(&acc_full);
             }
+            __syncwarp();
         }
     }
     if (warp >= 2) {

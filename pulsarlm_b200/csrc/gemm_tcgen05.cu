@@ -112,89 +112,103 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int unit_begin = blockIdx.x * p.units_per_cta;
     const int unit_end = min(unit_begin + p.units_per_cta, p.total_units);
 
+    // The producer and the issuer run their loops with all lanes of their warp, so that
+    // counters, addresses and descriptors stay in uniform registers, and let one elected
+    // lane issue.
     if (warp == 0) {
         // ------------------------------------------------ producer
-        if (lane == 0) {
-            // The first stages' weight tiles are asked for before the wait on earlier
-            // kernels (no kernel writes weights): they stream in under the predecessor's
-            // tail. The activation tiles of those stages follow after the wait.
-            const int early_end = min(unit_end, unit_begin + kStages);
-            for (int unit = unit_begin; unit < early_end; ++unit) {
-                const int tile = unit / p.k_blocks, kb = unit % p.k_blocks;
-                const int s = unit - unit_begin;
+        // The first stages' weight tiles are asked for before the wait on earlier
+        // kernels (no kernel writes weights): they stream in under the predecessor's
+        // tail. The activation tiles of those stages follow after the wait.
+        const int early_end = min(unit_end, unit_begin + kStages);
+        for (int unit = unit_begin; unit < early_end; ++unit) {
+            const int tile = unit / p.k_blocks, kb = unit % p.k_blocks;
+            const int s = unit - unit_begin;
+            if (elect_one()) {
                 mbar_expect_tx(&full_bar[s], kStageBytes);
                 tma_load_2d(tiles + s * kStageBytes, &map_w, kb * kBlockK, (tile % p.n_tiles) * kTileM, &full_bar[s]);
             }
-            pl_grid_wait();
-            for (int unit = unit_begin; unit < early_end; ++unit) {
-                const int tile = unit / p.k_blocks, kb = unit % p.k_blocks;
-                const int s = unit - unit_begin;
+            __syncwarp();
+        }
+        pl_grid_wait();
+        for (int unit = unit_begin; unit < early_end; ++unit) {
+            const int tile = unit / p.k_blocks, kb = unit % p.k_blocks;
+            const int s = unit - unit_begin;
+            if (elect_one()) {
                 tma_load_2d(tiles + s * kStageBytes + kBytesA, &map_x, kb * kBlockK, (tile / p.n_tiles) * TN,
                             &full_bar[s]);
             }
-            int stage = (early_end - unit_begin) % kStages;
-            uint32_t phase = early_end - unit_begin == kStages ? 1u : 0u;
-            for (int unit = early_end; unit < unit_end; ++unit) {
-                const int tile = unit / p.k_blocks, kb = unit % p.k_blocks;
-                const int n0 = (tile % p.n_tiles) * kTileM, t0 = (tile / p.n_tiles) * TN;
-                if (!mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_flag)) {
-                    break;
-                }
-                unsigned char* a = tiles + stage * kStageBytes;
+            __syncwarp();
+        }
+        int stage = (early_end - unit_begin) % kStages;
+        uint32_t phase = early_end - unit_begin == kStages ? 1u : 0u;
+        for (int unit = early_end; unit < unit_end; ++unit) {
+            const int tile = unit / p.k_blocks, kb = unit % p.k_blocks;
+            const int n0 = (tile % p.n_tiles) * kTileM, t0 = (tile / p.n_tiles) * TN;
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_flag)) {
+                break;
+            }
+            unsigned char* a = tiles + stage * kStageBytes;
+            if (elect_one()) {
                 mbar_expect_tx(&full_bar[stage], kStageBytes);
                 tma_load_2d(a, &map_w, kb * kBlockK, n0, &full_bar[stage]);
                 tma_load_2d(a + kBytesA, &map_x, kb * kBlockK, t0, &full_bar[stage]);
-                if (++stage == kStages) {
-                    stage = 0;
-                    phase ^= 1u;
-                }
+            }
+            __syncwarp();
+            if (++stage == kStages) {
+                stage = 0;
+                phase ^= 1u;
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            pl_grid_wait();  // so that the bounded waits below time this kernel's work only
-            int stage = 0;
-            uint32_t phase = 0;
-            int run = 0;  // runs of units within one tile: accumulator run & 1
-            int unit = unit_begin;
-            bool ok = true;
-            while (ok && unit < unit_end) {
-                const int tile = unit / p.k_blocks;
-                const int run_end = min(unit_end, (tile + 1) * p.k_blocks);
-                const int acc = run & 1;
-                const uint32_t acc_phase = (run >> 1) & 1u;
-                if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, &abort_flag)) {
+        pl_grid_wait();  // so that the bounded waits below time this kernel's work only
+        int stage = 0;
+        uint32_t phase = 0;
+        int run = 0;  // runs of units within one tile: accumulator run & 1
+        int unit = unit_begin;
+        bool ok = true;
+        while (ok && unit < unit_end) {
+            const int tile = unit / p.k_blocks;
+            const int run_end = min(unit_end, (tile + 1) * p.k_blocks);
+            const int acc = run & 1;
+            const uint32_t acc_phase = (run >> 1) & 1u;
+            if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, &abort_flag)) {
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t tmem_d = tmem_base + acc * TN;
+            for (int u = unit; u < run_end; ++u) {
+                if (!mbar_wait(&full_bar[stage], phase, &abort_flag)) {
+                    ok = false;
                     break;
                 }
                 tcgen05_fence_after();
-                const uint32_t tmem_d = tmem_base + acc * TN;
-                for (int u = unit; u < run_end; ++u) {
-                    if (!mbar_wait(&full_bar[stage], phase, &abort_flag)) {
-                        ok = false;
-                        break;
-                    }
-                    tcgen05_fence_after();
-                    const unsigned char* a = tiles + stage * kStageBytes;
-                    const uint64_t desc_a = smem_descriptor(a), desc_b = smem_descriptor(a + kBytesA);
+                const unsigned char* a = tiles + stage * kStageBytes;
+                const uint64_t desc_a = smem_descriptor(a), desc_b = smem_descriptor(a + kBytesA);
+                if (elect_one()) {
 #pragma unroll
                     for (int k = 0; k < kBlockK / 16; ++k) {
                         // 16 k elements are 32 bytes: 2 in the descriptor's 16-byte units
                         tcgen05_mma(tmem_d, desc_a + 2 * k, desc_b + 2 * k, kIdesc, (u > unit || k > 0) ? 1u : 0u);
                     }
                     tcgen05_commit(&empty_bar[stage]);
-                    if (++stage == kStages) {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
                 }
-                if (!ok) {
-                    break;
+                __syncwarp();
+                if (++stage == kStages) {
+                    stage = 0;
+                    phase ^= 1u;
                 }
-                tcgen05_commit(&acc_full[acc]);
-                unit = run_end;
-                ++run;
             }
+            if (!ok) {
+                break;
+            }
+            if (elect_one()) {
+                tcgen05_commit(&acc_full[acc]);
+            }
+            __syncwarp();
+            unit = run_end;
+            ++run;
         }
     } else {
         // ------------------------------------------------ epilogue (warps 2..5)

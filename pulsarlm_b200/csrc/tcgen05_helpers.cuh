@@ -9,6 +9,19 @@
 
 namespace {
 
+// True in exactly one lane of a converged warp. The warps that issue MMAs and TMA
+// loads run their loops with all lanes (so that addresses, descriptors and loop
+// counters stay in the uniform datapath) and let the elected lane issue.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t chosen;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(chosen));
+    return chosen != 0;
+}
+
 __device__ __forceinline__ void tensormap_prefetch(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -75,6 +88,21 @@ __device__ __forceinline__ void tcgen05_ld32_nowait(uint32_t address, uint32_t (
         : "memory");
 }
 __device__ __forceinline__ void tcgen05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// 32 columns of this warp's 32 lanes back into tensor memory; complete after
+// tcgen05_wait_st().
+__device__ __forceinline__ void tcgen05_st32_nowait(uint32_t address, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(address), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of
 // 128 bytes, groups of 8 rows 1024 bytes apart.

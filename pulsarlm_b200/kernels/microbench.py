@@ -103,7 +103,7 @@ def bench_attention_decode(batches, contexts, n_heads, n_kv, head_dim, page) -> 
             out = torch.empty_like(q)
             pos = torch.full((batch,), context - 1, dtype=torch.int32, device="cuda")
             entry = torch.arange(batch, dtype=torch.int32, device="cuda")
-            splits = decode_splits(batch * n_kv, context, q.device)
+            splits = decode_splits(batch * n_kv, context, q.device, head_dim, n_heads // n_kv)
             scratch = torch.empty(max(1, ops.attention_decode_scratch_floats(batch, n_heads, head_dim, splits)),
                                   device="cuda")
             scale = 1 / math.sqrt(head_dim)

@@ -58,6 +58,7 @@ _SIGNATURES = {
     "pl_gemm_bf16_supports": [_I32, _I32, _I32, _I64, _I64],
     "pl_gemm_bf16_skinny": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I64, _I64, _I64, _I32, _PTR, _PTR],
     "pl_gemm_bf16_skinny_max_tokens": [],
+    "pl_attention_decode_resident_clusters": [_I32, _I32, _I32],
     "pl_gemm_bf16_skinny_splits": [_I32, _I32, _I32],
     "pl_sample": [_PTR, _I64, _I32, _I32, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR],
 }

@@ -32,16 +32,30 @@ class KVBinding:
 _SM_COUNT: dict = {}
 
 
-def decode_splits(n_ctas: int, max_context: int, device: torch.device) -> int:
+_CLUSTER_ROOM: dict[tuple, int] = {}
+
+
+def decode_splits(n_ctas: int, max_context: int, device: torch.device, head_dim: int = 128, group: int = 4) -> int:
     """Ways to split each request's keys so that about two CTAs per SM run: as many
-    as fit, but no split shorter than eight 16-key tiles."""
+    as fit, but no split shorter than eight 16-key tiles. Up to eight splits are the
+    ranks of a thread-block cluster; their number is then lowered until all clusters
+    of the launch are resident at once (a launch in two waves takes twice as long)."""
     if device not in _SM_COUNT:
         _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
     target = 2 * _SM_COUNT[device]
     if n_ctas >= target:
         return 1
     tiles = -(-max_context // 16)
-    return max(1, min(target // n_ctas, tiles // 8))
+    splits = max(1, min(target // n_ctas, tiles // 8))
+    while 2 <= splits <= 8:
+        key = (device, head_dim, group, splits)
+        if key not in _CLUSTER_ROOM:
+            _CLUSTER_ROOM[key] = ops.library().pl_attention_decode_resident_clusters(head_dim, group, splits)
+        room = _CLUSTER_ROOM[key]
+        if room <= 0 or n_ctas <= room:
+            break
+        splits -= 1
+    return splits
 
 
 @register_part("mixer", "attention")
@@ -149,7 +163,8 @@ class Attention(Part):
             max_context = batch.extras.get("max_context") or max(batch.host_context_lens[:n_decode])
             if self.window:
                 max_context = min(max_context, self.window + 16)
-            splits = decode_splits(n_decode * self.n_kv, max_context, q.device)
+            splits = decode_splits(n_decode * self.n_kv, max_context, q.device, self.head_dim,
+                                   self.n_heads // self.n_kv)
             scratch = None
             if splits > 1:
                 scratch = torch.empty(ops.attention_decode_scratch_floats(n_decode, self.n_heads, self.head_dim,
