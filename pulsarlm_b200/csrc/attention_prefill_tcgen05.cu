@@ -3,7 +3,7 @@
 // CTA (query tile of 128 tokens, query head). Both products run as tcgen05 MMAs with
 // M = 128 query rows and accumulators in tensor memory:
 //   S  = Q K^T   M 128 x N 64 keys  x K head_dim  (Q and K tiles K-major in smem)
-//   PV = P V     M 128 x N head_dim x K 64 keys   (P K-major, V as stored: N-major)
+//   PV = P V     M 128 x N head_dim x K 64 keys   (P in tensor memory, V as stored: N-major)
 // Roles: warp 0 loads tiles with TMA (Q once; per 64-key tile the K and V rows of
 // four 16-key page pieces, found through the block table), warp 1 issues the MMAs,
 // warps 2-9 are two softmax warpgroups. When the GQA group is even a CTA takes two
@@ -11,9 +11,11 @@
 // does one head's softmax with one thread per query row. Otherwise a CTA takes one
 // head and the warpgroups share each row (thread pairs read the two halves of the
 // row's S and agree on the row maximum through shared memory). The softmax is
-// online, in fp32, base 2 with the scale folded in; P goes as bf16 into shared
-// memory for the second product, whose output accumulates in tensor memory over all
-// tiles. The exponents' base follows the row maximum lazily: it moves only when a
+// online, in fp32, base 2 with the scale folded in; P goes as bf16 into tensor
+// memory, over the columns its S came from (each thread stores its own row's values
+// where the second product reads its A operand: lane = row, two keys per column),
+// so the second product reads only V from shared memory. Its output accumulates in
+// tensor memory over all tiles. The exponents' base follows the row maximum lazily: it moves only when a
 // tile's maximum exceeds it by more than 2^8 (P then stays below 256, which fp32
 // sums and bf16 P hold without loss), and only then is the row of O read from
 // tensor memory, scaled and written back, after the previous PV has completed; most
@@ -34,7 +36,7 @@ namespace {
 constexpr int kRows = 128;     // query rows per CTA
 constexpr int kKeys = 64;      // keys per tile
 constexpr int kPiece = 16;     // keys per TMA box (a page, or a part of one)
-constexpr int kStagesKV = 3;
+constexpr int kStagesKV = 4;
 constexpr int kThreadsTc = 320;  // TMA warp, MMA warp, two softmax warpgroups
 
 struct TcPrefillParams {
@@ -78,8 +80,6 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     constexpr int kBytesQ = kRows * HD * 2;                // per head: kHalves sub-tiles of [128 x 64]
     constexpr int kBytesK = kKeys * HD * 2;                // kHalves sub-tiles of [64 x 64]
     constexpr int kBytesStage = 2 * kBytesK;               // K then V
-    constexpr int kBytesP = kRows * kKeys * 2;             // [128 x 64]
-    constexpr int kBuffersP = HEADS == 2 ? 1 : 2;          // P tiles per head in shared memory
     constexpr int kWarpsPerHead = 8 / HEADS;               // softmax warps that arrive on a head's barriers
     constexpr uint32_t kColsS = kKeys, kColsO = HD;
     constexpr uint32_t kColumns = HEADS * (2 * kColsS + kColsO) <= 256 ? 256 : 512;
@@ -95,11 +95,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                                            ~static_cast<uintptr_t>(1023));
     unsigned char* q_s = smem;                               // [head][half][128 rows x 128 bytes]
     unsigned char* kv_s = q_s + HEADS * kBytesQ;
-    unsigned char* p_s = kv_s + kStagesKV * kBytesStage;     // [head][buffer][128 rows x 128 bytes]
 
     __shared__ __align__(8) uint64_t q_full, kv_full[kStagesKV], kv_empty[kStagesKV];
-    __shared__ __align__(8) uint64_t s_full[HEADS][2], s_free[HEADS][2], p_full[HEADS][kBuffersP],
-        p_free[HEADS][kBuffersP], pv_done[HEADS];
+    __shared__ __align__(8) uint64_t s_full[HEADS][2], s_free[HEADS][2], p_full[HEADS][2], pv_done[HEADS];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
     __shared__ float half_max[HEADS == 1 ? 2 : 1][HEADS == 1 ? 2 * kRows : 1];  // [tile parity][warpgroup * 128 + row]
@@ -122,10 +120,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             for (int b = 0; b < 2; ++b) {
                 mbar_init(&s_full[h][b], 1);
                 mbar_init(&s_free[h][b], kWarpsPerHead);
-            }
-            for (int b = 0; b < kBuffersP; ++b) {
                 mbar_init(&p_full[h][b], kWarpsPerHead);
-                mbar_init(&p_free[h][b], 1);
             }
             mbar_init(&pv_done[h], 1);
         }
@@ -139,7 +134,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
-    const uint32_t tmem_s = tmem_base;                        // [head][2 buffers][64 columns]
+    const uint32_t tmem_s = tmem_base;                        // [head][2 buffers][64 columns]: S, then P in its first 32
     const uint32_t tmem_o = tmem_base + HEADS * 2 * kColsS;   // [head][HD columns]
 
     if (warp == 0) {
@@ -245,24 +240,24 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
             const unsigned char* v_s = kv_s + (j % kStagesKV) * kBytesStage + kBytesK;
             const uint64_t db = smem_descriptor_mn(v_s, kKeys * 128);
-            const int pb = j % kBuffersP;
             for (int hs = 0; ok && hs < HEADS; ++hs) {
-                // P_j of this head is written, and its O rescaled if its base moved
-                ok = mbar_wait(&p_full[hs][pb], (j / kBuffersP) & 1, &abort_flag);
+                // P_j of this head is in tensor memory, and its O rescaled if its base moved.
+                // (The buffer is written next by S_{j+2}, issued after this product: the
+                // tensor pipe runs in order, so P is read before it is overwritten.)
+                ok = mbar_wait(&p_full[hs][j & 1], (j >> 1) & 1, &abort_flag);
                 if (!ok) {
                     break;
                 }
                 tcgen05_fence_after();
-                const uint64_t da = smem_descriptor(p_s + (hs * kBuffersP + pb) * kBytesP);
+                const uint32_t pa = tmem_s + (hs * 2 + (j & 1)) * kColsS;
                 if (elect_one()) {
 #pragma unroll
                     for (int k = 0; k < kKeys / 16; ++k) {
-                        // 16 keys further: 32 bytes along P's rows, 16 rows of 128 bytes in V
-                        tcgen05_mma(tmem_o + hs * kColsO, da + 2 * k, db + k * ((16 * 128) >> 4), kIdescPV,
-                                    (j > 0 || k > 0) ? 1u : 0u);
+                        // 16 keys further: 8 columns of P, 16 rows of 128 bytes in V
+                        tcgen05_mma_a_tmem(tmem_o + hs * kColsO, pa + 8 * k, db + k * ((16 * 128) >> 4), kIdescPV,
+                                           (j > 0 || k > 0) ? 1u : 0u);
                     }
                     tcgen05_commit(&pv_done[hs]);
-                    tcgen05_commit(&p_free[hs][pb]);
                     if (hs == HEADS - 1) {
                         tcgen05_commit(&kv_empty[j % kStagesKV]);
                     }
@@ -288,7 +283,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         bool ok = true;
 
         for (int j = 0; j < n_tiles; ++j) {
-            const int b = j & 1, pb = j % kBuffersP;
+            const int b = j & 1;
             if (!mbar_wait(&s_full[hs][b], (j >> 1) & 1, &abort_flag)) {
                 ok = false;
                 break;
@@ -380,22 +375,18 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 packed[c / 2] = *reinterpret_cast<const uint32_t*>(&pair);
             }
             l = l * corr + sum;  // (HEADS == 1: this thread's half of the row sum; the halves meet at the end)
-            // P_j into its buffer, free once the PV that last read it has completed; row r, swizzled.
-            if (!mbar_wait(&p_free[hs][pb], ((j / kBuffersP) & 1) ^ 1u, &abort_flag)) {
-                ok = false;
-                break;
+            // P_j over the first columns of S_j (all of this row's S has been read: with two
+            // threads to a row the exchange above came after both loads).
+            if constexpr (kMyKeys == 64) {
+                tcgen05_st32_nowait(tmem_s + lane_bits + (hs * 2 + b) * kColsS, packed);
+            } else {
+                tcgen05_st16_nowait(tmem_s + lane_bits + (hs * 2 + b) * kColsS + part * (kMyKeys / 2), packed);
             }
-            unsigned char* p_row = p_s + (hs * kBuffersP + pb) * kBytesP + r * 128;
-#pragma unroll
-            for (int c = 0; c < kMyKeys / 8; ++c) {
-                const int chunk = part * (kMyKeys / 8) + c;
-                *reinterpret_cast<uint4*>(p_row + ((chunk ^ (r & 7)) * 16)) =
-                    make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tcgen05_wait_st();
+            tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(&p_full[hs][pb]);
+                mbar_arrive(&p_full[hs][b]);
             }
         }
         if (HEADS == 1) {
@@ -458,8 +449,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 template <int HD, int HEADS>
 int launch_tc_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcPrefillParams& p,
                       int n_tiles, int n_heads, cudaStream_t stream) {
-    constexpr int smem = HEADS * kRows * HD * 2 + kStagesKV * 2 * kKeys * HD * 2 +
-        HEADS * (HEADS == 2 ? 1 : 2) * kRows * kKeys * 2 + 1024;
+    constexpr int smem = HEADS * kRows * HD * 2 + kStagesKV * 2 * kKeys * HD * 2 + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD, HEADS>,
