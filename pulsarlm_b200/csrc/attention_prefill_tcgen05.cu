@@ -19,8 +19,12 @@
 // tile's maximum exceeds it by more than 2^8 (P then stays below 256, which fp32
 // sums and bf16 P hold without loss), and only then is the row of O read from
 // tensor memory, scaled and written back, after the previous PV has completed; most
-// tiles never touch O. S is double-buffered, so S of tile j+1 is computed while the
-// softmax of tile j runs.
+// tiles never touch O. With two heads per CTA the heads take turns on the tensor
+// pipe: Q sits in tensor memory too (each thread stores its own row there at the
+// start, so the first product reads only K from shared memory), and while one
+// warpgroup does the softmax of its head's tile the pipe runs the other head's PV and
+// next S. With one head per CTA, S is double-buffered instead, so that S of tile j+1
+// is computed while the softmax of tile j runs.
 //
 // Every mbarrier wait is bounded; on a timeout the CTA raises bit 8 of the status
 // word, stops, lets loads in flight land, frees its tensor memory and returns.
@@ -36,10 +40,12 @@ namespace {
 constexpr int kRows = 128;     // query rows per CTA
 constexpr int kKeys = 64;      // keys per tile
 constexpr int kPiece = 16;     // keys per TMA box (a page, or a part of one)
-constexpr int kStagesKV = 4;
+__host__ __device__ constexpr int stages_kv(int heads) { return heads == 2 ? 6 : 4; }
 constexpr int kThreadsTc = 320;  // TMA warp, MMA warp, two softmax warpgroups
 
 struct TcPrefillParams {
+    const __nv_bfloat16* q;
+    int64_t q_row_stride;
     const int32_t* table;
     int table_width;
     const int4* tiles;  // {first token row, rows, position of the first row, block-table row}
@@ -81,8 +87,12 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     constexpr int kBytesK = kKeys * HD * 2;                // kHalves sub-tiles of [64 x 64]
     constexpr int kBytesStage = 2 * kBytesK;               // K then V
     constexpr int kWarpsPerHead = 8 / HEADS;               // softmax warps that arrive on a head's barriers
-    constexpr uint32_t kColsS = kKeys, kColsO = HD;
-    constexpr uint32_t kColumns = HEADS * (2 * kColsS + kColsO) <= 256 ? 256 : 512;
+    constexpr bool kTurns = HEADS == 2;                    // the heads take turns: Q in tensor memory, one S buffer
+    constexpr int kBuffersS = kTurns ? 1 : 2;
+    constexpr int kStagesKV = stages_kv(HEADS);
+    constexpr uint32_t kColsS = kKeys, kColsO = HD, kColsQ = HD / 2;  // Q: two bf16 of a row per column
+    constexpr uint32_t kColumns =
+        HEADS * (kBuffersS * kColsS + kColsO) + (kTurns ? HEADS * kColsQ : 0) <= 256 ? 256 : 512;
     constexpr float kLazy = 8.0f;  // the base of the exponents may lag the row maximum by this much (log2)
     // instruction descriptors: fp32 accumulate, bf16 operands, M = 128
     constexpr uint32_t kIdescS = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kKeys >> 3) << 17) |
@@ -93,11 +103,12 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     extern __shared__ unsigned char raw_smem[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
                                                            ~static_cast<uintptr_t>(1023));
-    unsigned char* q_s = smem;                               // [head][half][128 rows x 128 bytes]
-    unsigned char* kv_s = q_s + HEADS * kBytesQ;
+    unsigned char* q_s = smem;                               // [head][half][128 rows x 128 bytes] (not with turns)
+    unsigned char* kv_s = q_s + (kTurns ? 0 : HEADS * kBytesQ);
 
     __shared__ __align__(8) uint64_t q_full, kv_full[kStagesKV], kv_empty[kStagesKV];
-    __shared__ __align__(8) uint64_t s_full[HEADS][2], s_free[HEADS][2], p_full[HEADS][2], pv_done[HEADS];
+    __shared__ __align__(8) uint64_t s_full[HEADS][2], s_free[HEADS][2], p_full[HEADS][2], pv_done[HEADS],
+        q_ready[HEADS];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
     __shared__ float half_max[HEADS == 1 ? 2 : 1][HEADS == 1 ? 2 * kRows : 1];  // [tile parity][warpgroup * 128 + row]
@@ -123,6 +134,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 mbar_init(&p_full[h][b], kWarpsPerHead);
             }
             mbar_init(&pv_done[h], 1);
+            mbar_init(&q_ready[h], kWarpsPerHead);
         }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -134,15 +146,16 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
-    const uint32_t tmem_s = tmem_base;                        // [head][2 buffers][64 columns]: S, then P in its first 32
-    const uint32_t tmem_o = tmem_base + HEADS * 2 * kColsS;   // [head][HD columns]
+    const uint32_t tmem_s = tmem_base;                                // [head][buffer][64 columns]: S, then P in its first 32
+    const uint32_t tmem_o = tmem_base + HEADS * kBuffersS * kColsS;   // [head][HD columns]
+    const uint32_t tmem_q = tmem_o + HEADS * kColsO;                  // [head][HD / 2 columns] (with turns)
 
     if (warp == 0) {
         // ------------------------------------------------ producer
         // Lane 0 waits and issues; all lanes look up block-table entries, 32 pieces
         // (eight tiles) at a time in one load each, so that the table's latency is
         // paid once per eight tiles and not once per piece.
-        if (lane == 0) {
+        if (lane == 0 && !kTurns) {
             mbar_expect_tx(&q_full, HEADS * kBytesQ);
             for (int hs = 0; hs < HEADS; ++hs) {
                 for (int h = 0; h < kHalves; ++h) {
@@ -199,70 +212,136 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         // ------------------------------------------------ MMA issuer
         // All lanes run the loop and wait; one elected lane issues. (Descriptors and
         // counters then live in uniform registers, which the MMA instructions take.)
-        auto issue_s = [&](int j, int hs) {  // S_j = Q K_j^T of head hs into its buffer j & 1
-            const unsigned char* k_s = kv_s + (j % kStagesKV) * kBytesStage;
-            const uint32_t d = tmem_s + (hs * 2 + (j & 1)) * kColsS;
-            if (elect_one()) {
+        if constexpr (kTurns) {
+            // S_j of head hs: A = Q from tensor memory, B = K_j from shared memory, into the
+            // head's one S buffer (free: the PV that read P from it was issued before).
+            auto issue_s = [&](int j, int hs) {
+                const unsigned char* k_s = kv_s + (j % kStagesKV) * kBytesStage;
+                uint64_t db[kHalves];
 #pragma unroll
                 for (int h = 0; h < kHalves; ++h) {
-                    const uint64_t da = smem_descriptor(q_s + hs * kBytesQ + h * (kRows * 128));
-                    const uint64_t db = smem_descriptor(k_s + h * (kKeys * 128));
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        tcgen05_mma(d, da + 2 * k, db + 2 * k, kIdescS, (h > 0 || k > 0) ? 1u : 0u);
-                    }
+                    db[h] = smem_descriptor(k_s + h * (kKeys * 128));
                 }
-                tcgen05_commit(&s_full[hs][j & 1]);
-            }
-            __syncwarp();
-        };
-        bool ok = mbar_wait(&q_full, 0, &abort_flag) && mbar_wait(&kv_full[0], 0, &abort_flag);
-        if (ok) {
-            tcgen05_fence_after();
-            for (int hs = 0; hs < HEADS; ++hs) {
-                issue_s(0, hs);
-            }
-        }
-        for (int j = 0; ok && j < n_tiles; ++j) {
-            if (j + 1 < n_tiles) {
-                const int next = j + 1;
-                ok = mbar_wait(&kv_full[next % kStagesKV], (next / kStagesKV) & 1, &abort_flag);
-                for (int hs = 0; ok && hs < HEADS; ++hs) {
-                    ok = mbar_wait(&s_free[hs][next & 1], ((next >> 1) & 1) ^ 1u, &abort_flag);
-                    if (ok) {
-                        tcgen05_fence_after();
-                        issue_s(next, hs);
-                    }
-                }
-                if (!ok) {
-                    break;
-                }
-            }
-            const unsigned char* v_s = kv_s + (j % kStagesKV) * kBytesStage + kBytesK;
-            const uint64_t db = smem_descriptor_mn(v_s, kKeys * 128);
-            for (int hs = 0; ok && hs < HEADS; ++hs) {
-                // P_j of this head is in tensor memory, and its O rescaled if its base moved.
-                // (The buffer is written next by S_{j+2}, issued after this product: the
-                // tensor pipe runs in order, so P is read before it is overwritten.)
-                ok = mbar_wait(&p_full[hs][j & 1], (j >> 1) & 1, &abort_flag);
-                if (!ok) {
-                    break;
-                }
-                tcgen05_fence_after();
-                const uint32_t pa = tmem_s + (hs * 2 + (j & 1)) * kColsS;
                 if (elect_one()) {
 #pragma unroll
-                    for (int k = 0; k < kKeys / 16; ++k) {
-                        // 16 keys further: 8 columns of P, 16 rows of 128 bytes in V
-                        tcgen05_mma_a_tmem(tmem_o + hs * kColsO, pa + 8 * k, db + k * ((16 * 128) >> 4), kIdescPV,
-                                           (j > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < HD / 16; ++k) {
+                        tcgen05_mma_a_tmem(tmem_s + hs * kColsS, tmem_q + hs * kColsQ + 8 * k, db[k / 4] + 2 * (k % 4),
+                                           kIdescS, k > 0 ? 1u : 0u);
                     }
-                    tcgen05_commit(&pv_done[hs]);
-                    if (hs == HEADS - 1) {
-                        tcgen05_commit(&kv_empty[j % kStagesKV]);
-                    }
+                    tcgen05_commit(&s_full[hs][0]);
                 }
                 __syncwarp();
+            };
+            bool ok = mbar_wait(&kv_full[0], 0, &abort_flag);
+            for (int hs = 0; ok && hs < HEADS; ++hs) {
+                ok = mbar_wait(&q_ready[hs], 0, &abort_flag);
+                if (ok) {
+                    tcgen05_fence_after();
+                    issue_s(0, hs);
+                }
+            }
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                const unsigned char* v_s = kv_s + (j % kStagesKV) * kBytesStage + kBytesK;
+                const uint64_t db = smem_descriptor_mn(v_s, kKeys * 128);
+                for (int hs = 0; ok && hs < HEADS; ++hs) {
+                    // P_j of this head lies over its S_j, and its O is rescaled if its base moved
+                    ok = mbar_wait(&p_full[hs][0], j & 1, &abort_flag);
+                    if (!ok) {
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    if (elect_one()) {
+#pragma unroll
+                        for (int k = 0; k < kKeys / 16; ++k) {
+                            // 16 keys further: 8 columns of P, 16 rows of 128 bytes in V
+                            tcgen05_mma_a_tmem(tmem_o + hs * kColsO, tmem_s + hs * kColsS + 8 * k,
+                                               db + k * ((16 * 128) >> 4), kIdescPV, (j > 0 || k > 0) ? 1u : 0u);
+                        }
+                        tcgen05_commit(&pv_done[hs]);
+                        if (hs == HEADS - 1) {
+                            tcgen05_commit(&kv_empty[j % kStagesKV]);
+                        }
+                    }
+                    __syncwarp();
+                    if (j + 1 < n_tiles) {
+                        // this head's next S at once: it runs while the other head's softmax does
+                        if (hs == 0) {
+                            ok = mbar_wait(&kv_full[(j + 1) % kStagesKV], ((j + 1) / kStagesKV) & 1, &abort_flag);
+                            if (!ok) {
+                                break;
+                            }
+                            tcgen05_fence_after();
+                        }
+                        issue_s(j + 1, hs);
+                    }
+                }
+            }
+        } else {
+            auto issue_s = [&](int j, int hs) {  // S_j = Q K_j^T of head hs into its buffer j & 1
+                const unsigned char* k_s = kv_s + (j % kStagesKV) * kBytesStage;
+                const uint32_t d = tmem_s + (hs * 2 + (j & 1)) * kColsS;
+                if (elect_one()) {
+    #pragma unroll
+                    for (int h = 0; h < kHalves; ++h) {
+                        const uint64_t da = smem_descriptor(q_s + hs * kBytesQ + h * (kRows * 128));
+                        const uint64_t db = smem_descriptor(k_s + h * (kKeys * 128));
+    #pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            tcgen05_mma(d, da + 2 * k, db + 2 * k, kIdescS, (h > 0 || k > 0) ? 1u : 0u);
+                        }
+                    }
+                    tcgen05_commit(&s_full[hs][j & 1]);
+                }
+                __syncwarp();
+            };
+            bool ok = mbar_wait(&q_full, 0, &abort_flag) && mbar_wait(&kv_full[0], 0, &abort_flag);
+            if (ok) {
+                tcgen05_fence_after();
+                for (int hs = 0; hs < HEADS; ++hs) {
+                    issue_s(0, hs);
+                }
+            }
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                if (j + 1 < n_tiles) {
+                    const int next = j + 1;
+                    ok = mbar_wait(&kv_full[next % kStagesKV], (next / kStagesKV) & 1, &abort_flag);
+                    for (int hs = 0; ok && hs < HEADS; ++hs) {
+                        ok = mbar_wait(&s_free[hs][next & 1], ((next >> 1) & 1) ^ 1u, &abort_flag);
+                        if (ok) {
+                            tcgen05_fence_after();
+                            issue_s(next, hs);
+                        }
+                    }
+                    if (!ok) {
+                        break;
+                    }
+                }
+                const unsigned char* v_s = kv_s + (j % kStagesKV) * kBytesStage + kBytesK;
+                const uint64_t db = smem_descriptor_mn(v_s, kKeys * 128);
+                for (int hs = 0; ok && hs < HEADS; ++hs) {
+                    // P_j of this head is in tensor memory, and its O rescaled if its base moved.
+                    // (The buffer is written next by S_{j+2}, issued after this product: the
+                    // tensor pipe runs in order, so P is read before it is overwritten.)
+                    ok = mbar_wait(&p_full[hs][j & 1], (j >> 1) & 1, &abort_flag);
+                    if (!ok) {
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t pa = tmem_s + (hs * 2 + (j & 1)) * kColsS;
+                    if (elect_one()) {
+    #pragma unroll
+                        for (int k = 0; k < kKeys / 16; ++k) {
+                            // 16 keys further: 8 columns of P, 16 rows of 128 bytes in V
+                            tcgen05_mma_a_tmem(tmem_o + hs * kColsO, pa + 8 * k, db + k * ((16 * 128) >> 4), kIdescPV,
+                                               (j > 0 || k > 0) ? 1u : 0u);
+                        }
+                        tcgen05_commit(&pv_done[hs]);
+                        if (hs == HEADS - 1) {
+                            tcgen05_commit(&kv_empty[j % kStagesKV]);
+                        }
+                    }
+                    __syncwarp();
+                }
             }
         }
     } else {
@@ -275,16 +354,42 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const int lane_group = warp & 3;          // the TMEM lanes this warp may read
         const int r = lane_group * 32 + lane;     // this thread's query row
         const uint32_t lane_bits = static_cast<uint32_t>(lane_group * 32) << 16;
-        const uint32_t my_s = tmem_s + lane_bits + hs * 2 * kColsS + part * kMyKeys;
+        const uint32_t my_s = tmem_s + lane_bits + hs * kBuffersS * kColsS + part * kMyKeys;
         const uint32_t my_o = tmem_o + lane_bits + hs * kColsO + part * kMyDims;
         const int pos = pos0 + r;
         const int first = p.window > 0 ? pos - p.window + 1 : 0;
         float m = -INFINITY, l = 0.0f;  // m: the base of the exponents in use (lags the true maximum)
         bool ok = true;
+        if constexpr (kTurns) {
+            // This thread's row of Q into tensor memory, where the first product reads its A
+            // operand: lane = row, column c = dims 2c and 2c + 1 (rows past the tile: zeros).
+            const uint4* src = reinterpret_cast<const uint4*>(p.q + (row0 + r) * p.q_row_stride +
+                                                              static_cast<int64_t>(head0 + hs) * HD);
+#pragma unroll
+            for (int g = 0; g < HD / 64; ++g) {
+                uint32_t v[32];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 four = r < n_rows ? src[8 * g + c] : make_uint4(0u, 0u, 0u, 0u);
+                    v[4 * c] = four.x;
+                    v[4 * c + 1] = four.y;
+                    v[4 * c + 2] = four.z;
+                    v[4 * c + 3] = four.w;
+                }
+                tcgen05_st32_nowait(tmem_q + lane_bits + hs * kColsQ + 32 * g, v);
+            }
+            tcgen05_wait_st();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&q_ready[hs]);
+            }
+        }
 
         for (int j = 0; j < n_tiles; ++j) {
-            const int b = j & 1;
-            if (!mbar_wait(&s_full[hs][b], (j >> 1) & 1, &abort_flag)) {
+            const int b = kTurns ? 0 : (j & 1);              // the S buffer of this tile,
+            const uint32_t use = kTurns ? (j & 1) : ((j >> 1) & 1);  // and the parity of its use
+            if (!mbar_wait(&s_full[hs][b], use, &abort_flag)) {
                 ok = false;
                 break;
             }
@@ -307,7 +412,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) {
+            if (!kTurns && lane == 0) {
                 mbar_arrive(&s_free[hs][b]);
             }
             const int key0 = (j0 + j) * kKeys + part * kMyKeys;
@@ -378,9 +483,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             // P_j over the first columns of S_j (all of this row's S has been read: with two
             // threads to a row the exchange above came after both loads).
             if constexpr (kMyKeys == 64) {
-                tcgen05_st32_nowait(tmem_s + lane_bits + (hs * 2 + b) * kColsS, packed);
+                tcgen05_st32_nowait(tmem_s + lane_bits + (hs * kBuffersS + b) * kColsS, packed);
             } else {
-                tcgen05_st16_nowait(tmem_s + lane_bits + (hs * 2 + b) * kColsS + part * (kMyKeys / 2), packed);
+                tcgen05_st16_nowait(tmem_s + lane_bits + (hs * kBuffersS + b) * kColsS + part * (kMyKeys / 2), packed);
             }
             tcgen05_wait_st();
             tcgen05_fence_before();
@@ -449,7 +554,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 template <int HD, int HEADS>
 int launch_tc_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcPrefillParams& p,
                       int n_tiles, int n_heads, cudaStream_t stream) {
-    constexpr int smem = HEADS * kRows * HD * 2 + kStagesKV * 2 * kKeys * HD * 2 + 1024;
+    constexpr int smem = (HEADS == 2 ? 0 : kRows * HD * 2) + stages_kv(HEADS) * 2 * kKeys * HD * 2 + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD, HEADS>,
@@ -518,6 +623,8 @@ PL_API int pl_attention_prefill_tcgen05(const void* q, int64_t q_row_stride, int
         return code;
     }
     TcPrefillParams p;
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.q_row_stride = q_row_stride;
     p.table = table;
     p.table_width = table_width;
     p.tiles = reinterpret_cast<const int4*>(tiles);
