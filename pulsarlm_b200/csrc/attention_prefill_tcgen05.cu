@@ -418,21 +418,24 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             const int key0 = (j0 + j) * kKeys + part * kMyKeys;
             const bool edge = (j0 + j) * kKeys + kKeys - 1 > pos0 ||
                 (p.window > 0 && (j0 + j) * kKeys < pos0 + kRows - p.window);
-            float tile_max = -INFINITY;
+            // The tile's maximum, on the raw products (the scale is positive), four running
+            // maxima side by side so that the chain of dependent instructions stays short.
             if (edge) {
 #pragma unroll
                 for (int c = 0; c < kMyKeys; ++c) {
                     const int key = key0 + c;
-                    s[c] = (key <= pos && key >= first) ? s[c] * p.scale_log2 : -INFINITY;
-                    tile_max = fmaxf(tile_max, s[c]);
-                }
-            } else {
-#pragma unroll
-                for (int c = 0; c < kMyKeys; ++c) {
-                    s[c] *= p.scale_log2;
-                    tile_max = fmaxf(tile_max, s[c]);
+                    s[c] = (key <= pos && key >= first) ? s[c] : -INFINITY;
                 }
             }
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < kMyKeys; c += 4) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    mx[i] = fmaxf(mx[i], s[c + i]);
+                }
+            }
+            float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
             if (HEADS == 1) {
                 // The row's maximum over both halves: exchange through shared memory.
                 half_max[b][wg * kRows + r] = tile_max;
@@ -469,16 +472,21 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 tcgen05_wait_st();
                 tcgen05_fence_before();
             }
-            const float base = m == -INFINITY ? 0.0f : m;
-            float sum = 0.0f;
+            const float minus_base = m == -INFINITY ? 0.0f : -m;
+            float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             uint32_t packed[kMyKeys / 2];
 #pragma unroll
-            for (int c = 0; c < kMyKeys; c += 2) {
-                const float p0 = ex2(s[c] - base), p1 = ex2(s[c + 1] - base);
-                sum += p0 + p1;
-                const __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
-                packed[c / 2] = *reinterpret_cast<const uint32_t*>(&pair);
+            for (int c = 0; c < kMyKeys; c += 8) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float p0 = ex2(fmaf(s[c + 2 * i], p.scale_log2, minus_base));
+                    const float p1 = ex2(fmaf(s[c + 2 * i + 1], p.scale_log2, minus_base));
+                    sums[i] += p0 + p1;
+                    const __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+                    packed[c / 2 + i] = *reinterpret_cast<const uint32_t*>(&pair);
+                }
             }
+            const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
             l = l * corr + sum;  // (HEADS == 1: this thread's half of the row sum; the halves meet at the end)
             // P_j over the first columns of S_j (all of this row's S has been read: with two
             // threads to a row the exchange above came after both loads).
@@ -605,6 +613,7 @@ PL_API int pl_attention_prefill_tcgen05(const void* q, int64_t q_row_stride, int
                    (reinterpret_cast<uintptr_t>(tiles) & 15) == 0,
                "attention_prefill_tcgen05: q, the pools, out and the tile list must be 16-byte aligned");
     PL_REQUIRE(n_heads <= 65535, "attention_prefill_tcgen05: too many heads (%d)", n_heads);
+    PL_REQUIRE(scale > 0.0f, "attention_prefill_tcgen05: the scale must be positive (%g)", static_cast<double>(scale));
     if (n_tiles == 0) {
         return 0;
     }
