@@ -54,9 +54,10 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, tig = lane & 3;
-    const int4 tile = p.tiles[blockIdx.x];
+    // heads vary fastest: with the tile list sorted longest first, a wave's CTAs are of similar length
+    const int4 tile = p.tiles[blockIdx.y];
     const int row0 = tile.x, n_rows = tile.y, pos0 = tile.z;
-    const int head = blockIdx.y, kv_head = head / p.group;
+    const int head = blockIdx.x, kv_head = head / p.group;
     const int32_t* table_row = p.table + static_cast<int64_t>(tile.w) * p.table_width;
 
     const int last_key = pos0 + n_rows - 1;
@@ -270,7 +271,7 @@ int launch_prefill(const PrefillParams& p, int n_tiles, int n_heads, cudaStream_
         }
         configured = true;
     }
-    attention_prefill_kernel<HD><<<dim3(n_tiles, n_heads), kThreads, smem, stream>>>(p);
+    attention_prefill_kernel<HD><<<dim3(n_heads, n_tiles), kThreads, smem, stream>>>(p);
     PL_CHECK_LAUNCH("attention_prefill");
     return 0;
 }

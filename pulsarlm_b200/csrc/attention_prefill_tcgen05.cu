@@ -114,9 +114,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     __shared__ float half_max[HEADS == 1 ? 2 : 1][HEADS == 1 ? 2 * kRows : 1];  // [tile parity][warpgroup * 128 + row]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int4 tile = p.tiles[blockIdx.x];
+    // Heads vary fastest in the grid and the tile list is sorted longest first, so the
+    // CTAs of a wave are of similar length and the short ones fill the end.
+    const int4 tile = p.tiles[blockIdx.y];
     const int row0 = tile.x, n_rows = tile.y, pos0 = tile.z;
-    const int head0 = blockIdx.y * HEADS, kv_head = head0 / p.group;
+    const int head0 = blockIdx.x * HEADS, kv_head = head0 / p.group;
     const int last_key = pos0 + n_rows - 1;
     const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
     const int j0 = first_key / kKeys, n_tiles = last_key / kKeys - j0 + 1;
@@ -573,7 +575,7 @@ int launch_tc_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
         }
         configured = true;
     }
-    attention_prefill_tcgen05_kernel<HD, HEADS><<<dim3(n_tiles, n_heads / HEADS), kThreadsTc, smem, stream>>>(mq, mk,
+    attention_prefill_tcgen05_kernel<HD, HEADS><<<dim3(n_heads / HEADS, n_tiles), kThreadsTc, smem, stream>>>(mq, mk,
                                                                                                               mv, p);
     PL_CHECK_LAUNCH("attention_prefill_tcgen05");
     return 0;
@@ -612,7 +614,7 @@ PL_API int pl_attention_prefill_tcgen05(const void* q, int64_t q_row_stride, int
                    (reinterpret_cast<uintptr_t>(out) & 15) == 0 && out_row_stride % 8 == 0 &&
                    (reinterpret_cast<uintptr_t>(tiles) & 15) == 0,
                "attention_prefill_tcgen05: q, the pools, out and the tile list must be 16-byte aligned");
-    PL_REQUIRE(n_heads <= 65535, "attention_prefill_tcgen05: too many heads (%d)", n_heads);
+    PL_REQUIRE(n_tiles <= 65535, "attention_prefill_tcgen05: too many tiles in one launch (%d)", n_tiles);
     PL_REQUIRE(scale > 0.0f, "attention_prefill_tcgen05: the scale must be positive (%g)", static_cast<double>(scale));
     if (n_tiles == 0) {
         return 0;
