@@ -243,10 +243,12 @@ def run_ours(args) -> dict:
             engine.step()  # prefill (untimed)
         for _ in range(args.warmup):
             engine.step()
+        engine.sync()  # the engine pipelines decode steps one deep: nothing in flight at the start,
         torch.cuda.synchronize()
         t_start = time.perf_counter()
         for _ in range(args.steps):
             engine.step()
+        engine.sync()  # and every timed step's tokens read on the host at the end
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t_start
         assert all(not r.finished and len(r.output) >= args.warmup + args.steps + 1 for r in requests)

@@ -29,16 +29,26 @@ from .scheduler import PlannedEntry, Request, Scheduler
 DEFAULT_PAGE_SIZE = 16
 
 
+class _Flight:
+    """A decode step that was launched and whose sampled ids have not been read yet."""
+
+    def __init__(self, entries: list[PlannedEntry], ids: torch.Tensor, pending):
+        self.entries = entries
+        self.ids = ids          # int32 [entries] on the device
+        self.pending = pending  # their copy to the host
+
+
 class Engine:
     def __init__(self, model, dtype="bfloat16", device="cuda:0", kv_cache_gib: float = 4.0,
                  page_size: int = DEFAULT_PAGE_SIZE, prefill_tokens_per_step: int = 256,
                  max_requests: int = 64, n_pages: int | None = None, stop_ids=None, seed: int | None = None,
-                 cuda_graphs: bool = True, attention_mass_decay: float | None = None):
+                 cuda_graphs: bool = True, attention_mass_decay: float | None = None, lookahead: bool = True):
         """model: a model folder, a built Model, or a config.json dict (random
         weights from `seed`). kv_cache_gib sizes the page pools unless n_pages
         gives the number of pages outright. stop_ids default to config.json's
         eos_token_id. attention_mass_decay: measure per-page attention mass with this
-        decay (see CacheManager; slower: attention then runs on the CUDA cores)."""
+        decay (see CacheManager; slower: attention then runs on the CUDA cores).
+        lookahead: pipeline decode steps one deep (see step())."""
         ops.require_device()
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
@@ -62,6 +72,8 @@ class Engine:
         stops = self.model.spec.eos_token_ids if stop_ids is None else stop_ids
         self.scheduler = Scheduler(self.cache, stops, prefill_tokens_per_step)
         self.cuda_graphs = cuda_graphs and self.runner.graphs_allowed
+        self.lookahead = lookahead and self.cuda_graphs
+        self._inflight: _Flight | None = None
         self._ids = itertools.count()
         self.vocab_size = self.model.spec.vocab_size
 
@@ -82,25 +94,60 @@ class Engine:
         return request
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None
 
     def step(self) -> list[Request]:
-        """Runs one scheduler step on the GPU; returns the requests that ended in it."""
+        """Advances the engine by one scheduler step on the GPU; returns the requests
+        that ended.
+
+        Steps made of single decode tokens are pipelined one deep (`lookahead`): the
+        call launches the step and returns; the next call first launches the step
+        after it, whose tokens the GPU takes from the ids the earlier step is still
+        sampling, and only then reads the earlier step's ids. The host's work for a
+        step thus overlaps the GPU's, and a request's output lags its step by one
+        call. The step after is launched early only when it is certain to be the same
+        requests again (nobody waiting or cancelled, nobody at its token limit, pages
+        to spare); a request that ends on a stop token has then computed one token too
+        many, which is dropped."""
+        done: list[Request] = []
+        flight = self._inflight
+        if flight is not None:
+            self._inflight = None
+            if self._can_look_ahead(flight):
+                entries, ended = self.scheduler.plan()
+                same = not ended and len(entries) == len(flight.entries) and all(
+                    e.request is f.request and len(e.tokens) == 1 and e.samples
+                    for e, f in zip(entries, flight.entries))
+                if same:
+                    ahead = self._launch_decode(entries, device_tokens=flight.ids, count_offset=1)
+                    done = self._finish(flight)
+                    self._inflight = ahead
+                    return done
+                # (not expected under the conditions checked) finish, then run what was planned
+                done = self._finish(flight)
+                entries = [PlannedEntry(e.request, e.request.pending[: len(e.tokens)], e.samples)
+                           for e in entries if e.request.state == "running"]
+                return done + ended + self._execute(entries)
+            done = self._finish(flight)
         entries, ended = self.scheduler.plan()
+        return done + ended + self._execute(entries)
+
+    def _execute(self, entries: list[PlannedEntry]) -> list[Request]:
+        """Runs planned entries; returns the requests that ended (none yet when the step
+        stays in flight)."""
         if not entries:
-            return ended
+            return []
+        if self.cuda_graphs and all(len(e.tokens) == 1 and e.samples and e.request.max_tokens != 0
+                                    for e in entries):
+            flight = self._launch_decode(entries)
+            if self.lookahead:
+                self._inflight = flight
+                return []
+            return self._finish(flight)
         step_entries = [StepEntry(e.request.id, e.tokens, [len(e.tokens) - 1] if e.samples else [])
                         for e in entries]
         sampled: dict = {}
         samplers = [e for e in entries if e.samples]
-        if self.cuda_graphs and all(len(e.tokens) == 1 and e.samples and e.request.max_tokens != 0
-                                    for e in entries):
-            drawn = self.runner.decode_step(
-                step_entries, [e.request.sampling for e in entries], [e.request.seed for e in entries],
-                [e.request.draw_count for e in entries])
-            host = drawn.cpu().tolist()  # the step's one synchronisation
-            sampled = {e.request.id: t for e, t in zip(entries, host)}
-            return ended + self.scheduler.finish_step(entries, sampled)
         logits = self.runner.step(step_entries)
         if samplers and logits is not None:
             drawn = self.sampler.sample(
@@ -108,7 +155,36 @@ class Engine:
                 [e.request.draw_count for e in samplers])
             host = drawn.cpu().tolist()  # the step's one synchronisation
             sampled = {e.request.id: t for e, t in zip(samplers, host)}
-        return ended + self.scheduler.finish_step(entries, sampled)
+        return self.scheduler.finish_step(entries, sampled)
+
+    def _launch_decode(self, entries: list[PlannedEntry], device_tokens: torch.Tensor | None = None,
+                       count_offset: int = 0) -> "_Flight":
+        step_entries = [StepEntry(e.request.id, e.tokens, [0]) for e in entries]
+        ids = self.runner.decode_step(
+            step_entries, [e.request.sampling for e in entries], [e.request.seed for e in entries],
+            [e.request.draw_count + count_offset for e in entries], device_tokens=device_tokens)
+        return _Flight(entries, ids, self.runner.last_graph.read_back())
+
+    def _finish(self, flight: "_Flight") -> list[Request]:
+        host = flight.pending.wait()
+        return self.scheduler.finish_step(flight.entries, {e.request.id: t for e, t in zip(flight.entries, host)})
+
+    def _can_look_ahead(self, flight: "_Flight") -> bool:
+        """True when the step after `flight` is certain to be its requests again."""
+        if not self.lookahead or self.scheduler.waiting or len(self.scheduler.running) != len(flight.entries):
+            return False
+        for e in flight.entries:
+            r = e.request
+            if r.cancelled or r.state != "running":
+                return False
+            if r.max_tokens is not None and len(r.output) + 1 >= r.max_tokens:
+                return False  # the step in flight brings it to its limit
+        return self.cache.free_pages() >= len(flight.entries)
+
+    def sync(self) -> list[Request]:
+        """Reads a step still in flight; returns the requests that ended in it."""
+        flight, self._inflight = self._inflight, None
+        return self._finish(flight) if flight is not None else []
 
     # ------------------------------------------------------------------ whole runs
     def generate(self, prompts: list[list[int]], sampling=None, max_tokens: int | None = 16,

@@ -73,6 +73,9 @@ class GraphedDecode:
         self.graph: torch.cuda.CUDAGraph | None = None
         self.copied = torch.cuda.Event()
         self.launches = 0
+        self._results: list[torch.Tensor] | None = None
+        self._result_events: list[torch.cuda.Event] = []
+        self._turn = 0
 
     def _forward(self) -> None:
         self.logits = self.runner.model.forward(self.batch)
@@ -96,7 +99,36 @@ class GraphedDecode:
             self._forward()
         self.launches = ops.launch_count() - before
 
-    def replay(self) -> None:
+    def replay(self, device_tokens: torch.Tensor | None = None) -> None:
+        """Copies the packed inputs and launches the graph. With `device_tokens` (int32 [n],
+        e.g. the ids another replay sampled) the step's tokens are taken from there
+        instead of from the host buffer: the copy is ordered after whatever wrote them."""
         self.dev.copy_(self.host, non_blocking=True)
         self.copied.record()
+        if device_tokens is not None:
+            self.d["tokens"].copy_(device_tokens, non_blocking=True)
         self.graph.replay()
+
+    def read_back(self) -> "PendingIds":
+        """Starts the copy of this replay's sampled ids to the host; `wait()` on the result
+        gives them. Two host buffers alternate, so one earlier result may still be unread."""
+        if self._results is None:
+            self._results = [torch.empty(self.n, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+            self._result_events = [torch.cuda.Event(), torch.cuda.Event()]
+        slot = self._turn
+        self._turn ^= 1
+        self._results[slot].copy_(self.ids, non_blocking=True)
+        self._result_events[slot].record()
+        return PendingIds(self._results[slot], self._result_events[slot])
+
+
+class PendingIds:
+    """Sampled token ids on their way to the host."""
+
+    def __init__(self, host: torch.Tensor, event: torch.cuda.Event):
+        self._host = host
+        self._event = event
+
+    def wait(self) -> list[int]:
+        self._event.synchronize()  # the step's one synchronisation
+        return self._host.tolist()

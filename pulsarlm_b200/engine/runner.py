@@ -204,10 +204,14 @@ class ModelRunner:
         self.tokens_run += batch.n_tokens
         return logits
 
-    def decode_step(self, entries: list[StepEntry], sampling, seeds: list[int], counts: list[int]) -> torch.Tensor:
+    def decode_step(self, entries: list[StepEntry], sampling, seeds: list[int], counts: list[int],
+                    device_tokens: torch.Tensor | None = None) -> torch.Tensor:
         """A step of single tokens, one per entry, each sampling its next token:
         replays a CUDA graph captured for this number of entries. Returns int32
-        [entries] token ids in a device buffer that the next call overwrites."""
+        [entries] token ids in a device buffer that the next call overwrites
+        (`self.last_graph.read_back()` starts their copy to the host). With
+        `device_tokens` the entries' tokens are read from that device tensor (the ids
+        a step still in flight is sampling) and the entries' own tokens are ignored."""
         from .graphs import GraphedDecode
 
         n = len(entries)
@@ -246,7 +250,8 @@ class ModelRunner:
             self.cache.fill_tables(g.index, handles, h[f"table{g.index}"], h["slots"])
         if fresh:
             graph.capture()
-        graph.replay()
+        graph.replay(device_tokens)
+        self.last_graph = graph
         for e, new_len in zip(entries, new_lens):
             self.cache.commit(e.request, new_len)
         self.steps += 1

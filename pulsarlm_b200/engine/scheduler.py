@@ -201,6 +201,8 @@ class Scheduler:
     def finish_step(self, entries: list[PlannedEntry], sampled: dict) -> list[Request]:
         """Records a step: `sampled[request.id]` is the token drawn for each entry
         that samples. Returns the requests that finished."""
+        # (an entry whose request ended while its step was in flight has nothing to record)
+        entries = [e for e in entries if e.request.state == "running"]
         n = len(entries)
         flat = (ctypes.c_int64 * (3 * max(1, n)))()
         for i, entry in enumerate(entries):

@@ -101,6 +101,46 @@ def test_stop_ids_max_tokens_and_complete():
         engine.generate([tiny.random_tokens(tm.cfg, 200, seed=2)], max_tokens=1)
 
 
+def test_pipelined_decode_steps_change_nothing_but_the_timing():
+    """With decode steps pipelined one deep (the next step is launched on the ids the
+    GPU is still sampling) the tokens, the finish reasons and the freed pages are those
+    of the unpipelined engine: requests that end on a stop token in mid-flight (their
+    extra token is dropped), at their token limit, with different limits, sampled with
+    a temperature, and with a request that arrives while the others decode."""
+    from pulsarlm_b200 import Engine, SamplingParams
+
+    tm = TinyModel("B", "float32")
+    prompts = [tiny.random_tokens(tm.cfg, n, seed=10 + n) for n in (3, 20, 41, 70)]
+    greedy = [plain_llama.greedy_generate(tm.cfg, tm.weights, p, 14) for p in prompts]
+    stops = [greedy[1][5], greedy[2][9]]  # requests 1 and 2 stop in the middle of the others' decoding
+
+    def run(lookahead):
+        engine = Engine(tm.folder, dtype="float32", n_pages=40, page_size=tm.page, max_requests=6,
+                        prefill_tokens_per_step=32, stop_ids=stops, lookahead=lookahead)
+        limits = [14, 14, 14, 6]
+        requests = [engine.submit(p, sampling=SamplingParams(temperature=0.0), max_tokens=m)
+                    for p, m in zip(prompts, limits)]
+        late = None
+        calls = 0
+        while any(not r.finished for r in requests) or late is None or not late.finished:
+            engine.step()
+            calls += 1
+            if calls == 6:  # arrives while the others decode
+                late = engine.submit(tiny.random_tokens(tm.cfg, 25, seed=99),
+                                     sampling=SamplingParams(temperature=0.8, seed=7), max_tokens=9, ignore_eos=True)
+        engine.sync()
+        engine.runner.check_status()
+        assert engine.cache.free_pages() == 40
+        assert engine.runner.graph_steps > 0
+        return [(list(r.output), r.finish_reason) for r in requests + [late]]
+
+    piped, plain = run(True), run(False)
+    assert piped == plain
+    for (tokens, reason), want in zip(plain[:4], greedy):
+        assert tokens == want[: len(tokens)]
+    assert plain[1][1] == "stop" and plain[3][1] == "length" and len(plain[3][0]) == 6
+
+
 def test_command_line_generate_and_random_model(tmp_path):
     cfg_path = tmp_path / "cfg.json"
     cfg_path.write_text(json.dumps(tiny.TINY_A))
