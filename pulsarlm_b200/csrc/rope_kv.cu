@@ -19,12 +19,12 @@ __device__ __forceinline__ void rope_sincos(int pos, double radians_per_position
     sincosf(static_cast<float>(frac * kTwoPi), &s, &c);
 }
 
-constexpr int kHeadsPerBlock = 4;
-
-// Block (t, y) handles token t and head slots 4y .. 4y+3, where slots 0 .. n_heads-1
-// are q heads (rotated in place) and the next n_kv_heads are k heads (rotated and
-// stored with their v head). Many small blocks: a decode step has few tokens, and
-// one block per token would walk its heads one after the other. Rotated pairs are
+// Block (t, y) handles token t and `heads_per_block` head slots from y * heads_per_block,
+// where slots 0 .. n_heads-1 are q heads (rotated in place) and the next n_kv_heads are
+// k heads (rotated and stored with their v head). A decode step has few tokens: many
+// small blocks (four slots each), else one block per token would walk its heads one
+// after the other. A prompt portion has many: one block per token, so that the
+// token's angles (fp64) are formed once and not once per four heads. Rotated pairs are
 // (j, j + rotary/2) for j < rotary/2; dims >= rotary pass through unchanged.
 template <typename scalar_t>
 __global__ void rope_kv_write_kernel(scalar_t* __restrict__ q, const scalar_t* __restrict__ k,
@@ -34,7 +34,7 @@ __global__ void rope_kv_write_kernel(scalar_t* __restrict__ q, const scalar_t* _
                                      scalar_t* __restrict__ k_pool, scalar_t* __restrict__ v_pool,
                                      int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
                                      const double* __restrict__ inv_freq, int rotary, int n_heads, int n_kv_heads,
-                                     int head_dim, int32_t* status) {
+                                     int head_dim, int heads_per_block, int32_t* status) {
     extern __shared__ float sincos[];  // [rotary/2] cos then [rotary/2] sin
     pl_grid_trigger();  // positions are step inputs: the angles need not wait for the projection
     const int t = blockIdx.x;
@@ -51,8 +51,8 @@ __global__ void rope_kv_write_kernel(scalar_t* __restrict__ q, const scalar_t* _
     __syncthreads();
 
     const int n_slots = n_heads + (k_pool != nullptr ? n_kv_heads : 0);
-    const int slot0 = blockIdx.y * kHeadsPerBlock;
-    const int slot1 = min(slot0 + kHeadsPerBlock, n_slots);
+    const int slot0 = blockIdx.y * heads_per_block;
+    const int slot1 = min(slot0 + heads_per_block, n_slots);
     int page = -1;
     if (slot1 > n_heads) {
         page = table[static_cast<int64_t>(entry[t]) * table_width + p / page_size];
@@ -109,7 +109,7 @@ __global__ void rope_kv_write_vec_kernel(scalar_t* __restrict__ q, const scalar_
                                          scalar_t* __restrict__ k_pool, scalar_t* __restrict__ v_pool,
                                          int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
                                          const double* __restrict__ inv_freq, int rotary, int n_heads,
-                                         int n_kv_heads, int head_dim, int32_t* status) {
+                                         int n_kv_heads, int head_dim, int heads_per_block, int32_t* status) {
     extern __shared__ float sincos[];
     pl_grid_trigger();
     const int t = blockIdx.x;
@@ -126,8 +126,8 @@ __global__ void rope_kv_write_vec_kernel(scalar_t* __restrict__ q, const scalar_
     __syncthreads();
 
     const int n_slots = n_heads + (k_pool != nullptr ? n_kv_heads : 0);
-    const int slot0 = blockIdx.y * kHeadsPerBlock;
-    const int slot1 = min(slot0 + kHeadsPerBlock, n_slots);
+    const int slot0 = blockIdx.y * heads_per_block;
+    const int slot1 = min(slot0 + heads_per_block, n_slots);
     int page = -1;
     if (slot1 > n_heads) {
         page = table[static_cast<int64_t>(entry[t]) * table_width + p / page_size];
@@ -204,7 +204,8 @@ PL_API int pl_rope_kv_write(void* q, const void* k, const void* v, int64_t row_s
     const size_t smem = static_cast<size_t>(rotary) * sizeof(float);
     PL_REQUIRE(smem <= 48 * 1024, "rope_kv_write: rotary width %d is too large", rotary);
     const int n_slots = n_heads + (k_pool != nullptr ? n_kv_heads : 0);
-    const dim3 grid(n_tokens, (n_slots + kHeadsPerBlock - 1) / kHeadsPerBlock);
+    const int heads_per_block = n_tokens >= 64 ? n_slots : 4;
+    const dim3 grid(n_tokens, (n_slots + heads_per_block - 1) / heads_per_block);
     PL_REQUIRE(grid.y <= 65535, "rope_kv_write: too many heads (%d)", n_slots);
     const int half = rotary / 2;
     const uintptr_t align = dtype == PL_F32 ? 15 : 7;
@@ -212,14 +213,15 @@ PL_API int pl_rope_kv_write(void* q, const void* k, const void* v, int64_t row_s
         page_stride % 4 == 0 && head_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(q) & align) == 0 &&
         (reinterpret_cast<uintptr_t>(k) & align) == 0 && (reinterpret_cast<uintptr_t>(v) & align) == 0 &&
         (reinterpret_cast<uintptr_t>(k_pool) & align) == 0 && (reinterpret_cast<uintptr_t>(v_pool) & align) == 0;
-    const int items = kHeadsPerBlock * (head_dim - half) / (vec ? 4 : 1);
+    const int items = heads_per_block * (head_dim - half) / (vec ? 4 : 1);
     const int threads = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
     PL_DISPATCH_DTYPE(dtype, "rope_kv_write", {
         auto kernel = vec ? rope_kv_write_vec_kernel<scalar_t> : rope_kv_write_kernel<scalar_t>;
         pl_launch_overlapped(
             kernel, grid, threads, smem, stream, static_cast<scalar_t*>(q), static_cast<const scalar_t*>(k), static_cast<const scalar_t*>(v), row_stride,
             pos, entry, table, table_width, static_cast<scalar_t*>(k_pool), static_cast<scalar_t*>(v_pool),
-            page_stride, head_stride, page_size, n_pages, inv_freq, rotary, n_heads, n_kv_heads, head_dim, status);
+            page_stride, head_stride, page_size, n_pages, inv_freq, rotary, n_heads, n_kv_heads, head_dim,
+            heads_per_block, status);
     });
     PL_CHECK_LAUNCH("rope_kv_write");
     return 0;
