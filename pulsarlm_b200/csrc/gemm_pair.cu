@@ -1,0 +1,369 @@
+// bfloat16 matrix product for prompts on pairs of SMs:
+//   Y[T, N] = X[T, K] * W[N, K]^T,  fp32 accumulation, T in the hundreds and up.
+//
+// Two CTAs of a cluster work on one 256-feature x 256-token tile with
+// `tcgen05.mma.cta_group::2` (M = 256 over the pair, N = 256, K = 16 per instruction).
+// The weights sit on the MMA's M axis and the tokens on its N axis, as in the other
+// products of this library. Each CTA loads its own 128 features of W and its own 128
+// of the tile's 256 tokens of X per 64-deep k block (32 KB where a lone CTA with the
+// same tile per SM would need 48 KB: one SM takes in about 64 bytes a clock, which is
+// what bounds the single-CTA kernel in gemm_tcgen05.cu); the instruction reads both
+// CTAs' shared memory and writes each CTA's 128 rows of the accumulator into that
+// CTA's tensor memory.
+//
+// Roles per CTA (192 threads): warp 0 loads with TMA (`.cta_group::2` loads, whose
+// bytes are counted on the barrier of the pair's first CTA); warp 1 of the first CTA
+// issues the MMAs for the pair and commits them to both CTAs' barriers
+// (`tcgen05.commit ... multicast::cluster`), and owns (in both CTAs) the tensor
+// memory allocation; warps 2-5 read their CTA's accumulator rows and store them.
+// Two accumulators let the epilogue of one tile overlap the MMAs of the next; the
+// second CTA's epilogue releases an accumulator by arriving on the first CTA's barrier.
+// A pair is persistent and takes every P-th whole tile (P pairs), token tiles fastest:
+// the P tiles in work at one time are then neighbours that share a few weight tiles, so
+// each weight tile comes from HBM once and is served to the other pairs from L2 (with a
+// contiguous run of tiles per pair the pairs' weight tiles together overflow the L2 and
+// every token tile re-reads its weights from HBM: 2.07 GB instead of 0.25 GB for the
+// 2048 x 28672 x 4096 product).
+//
+// Every wait on an mbarrier is bounded: after the limit the CTA raises bit 8 of the
+// status word, stops issuing work, lets what is in flight land, meets its partner,
+// frees its tensor memory and returns.
+//
+// The reference leaves these products to a library (`at::linear`,
+// pulsarlm-core/src/engine/model/llama.cpp:67-69, 81, 91, 93).
+#include "tcgen05_helpers.cuh"
+
+namespace {
+
+constexpr int kTileM = 128;    // features per CTA, 256 per pair
+constexpr int kPairN = 256;    // tokens per tile, 128 loaded by each CTA
+constexpr int kBlockK = 64;
+constexpr int kThreads = 192;
+constexpr int kStages = 6;
+constexpr int kBytesA = kTileM * kBlockK * 2;
+constexpr int kBytesB = (kPairN / 2) * kBlockK * 2;
+constexpr int kStageBytes = kBytesA + kBytesB;  // per CTA
+
+struct PairParams {
+    void* y;  // [T, N] bf16 or fp32
+    int t, n, k;
+    int64_t ldy;
+    int out_f32;
+    int n_tiles;  // tiles along N (256 features each)
+    int t_tiles;  // tiles along T (256 tokens each)
+    int k_blocks;
+    int total_tiles;
+    int32_t* status;
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    return rank;
+}
+__device__ __forceinline__ void tcgen05_alloc_pair(uint32_t* slot, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)),
+                 "r"(columns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_dealloc_pair(uint32_t address, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+// A tile load whose bytes are counted on the barrier at the same address in the pair's
+// first CTA (both CTAs of the pair issue such loads for a stage).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
+        "[%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(cluster_map(bar, 0)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    const uint32_t zero = 0;  // no output lanes switched off
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(zero)
+        : "memory");
+}
+// One arrival, once the MMAs issued so far have completed, on the barrier at this
+// address in both CTAs of the pair.
+__device__ __forceinline__ void tcgen05_commit_pair(uint64_t* bar) {
+    const uint16_t both = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(smem_u32(bar)), "h"(both)
+        : "memory");
+}
+// One arrival on the barrier at this address in the pair's first CTA.
+__device__ __forceinline__ void arrive_on_first(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_map(bar, 0))
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                 const PairParams p) {
+    constexpr uint32_t kColumns = 2 * kPairN;  // two accumulators
+    constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kPairN >> 3) << 17) |
+        (static_cast<uint32_t>((2 * kTileM) >> 4) << 24);
+
+    extern __shared__ unsigned char raw_smem[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
+                                                            ~static_cast<uintptr_t>(1023));
+    __shared__ __align__(8) uint64_t full_bar[kStages];   // waited on in the first CTA only
+    __shared__ __align__(8) uint64_t empty_bar[kStages];
+    __shared__ __align__(8) uint64_t acc_full[2];
+    __shared__ __align__(8) uint64_t acc_empty[2];         // waited on in the first CTA only
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = static_cast<int>(cluster_rank());
+    const int pair = blockIdx.x >> 1;
+    pl_grid_trigger();
+    if (threadIdx.x == 0) {
+        tensormap_prefetch(&map_w);
+        tensormap_prefetch(&map_x);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_empty[a], 8);  // the epilogue warps of both CTAs
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tcgen05_alloc_pair(&tmem_base_slot, kColumns);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_base_slot, 0);
+    cluster_arrive_all();  // both CTAs' barriers exist before either signals the other's
+    cluster_wait_all();
+    pl_grid_wait();
+
+    const int tile_begin = pair, tile_end = p.total_tiles, tile_step = gridDim.x >> 1;
+
+    if (warp == 0) {
+        // ------------------------------------------------ producer (both CTAs)
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = tile_begin; ok && tile < tile_end; tile += tile_step) {
+            const int n0 = (tile / p.t_tiles) * (2 * kTileM) + rank * kTileM;
+            const int t0 = (tile % p.t_tiles) * kPairN + rank * (kPairN / 2);
+            for (int kb = 0; kb < p.k_blocks; ++kb) {
+                if (!mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                unsigned char* a = tiles + stage * kStageBytes;
+                if (elect_one()) {
+                    if (rank == 0) {
+                        mbar_expect_tx(&full_bar[stage], 2 * kStageBytes);  // both CTAs' loads of this stage
+                    }
+                    tma_load_2d_pair(a, &map_w, kb * kBlockK, n0, &full_bar[stage]);
+                    tma_load_2d_pair(a + kBytesA, &map_x, kb * kBlockK, t0, &full_bar[stage]);
+                }
+                __syncwarp();
+                if (++stage == kStages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp == 1 && rank == 0) {
+        // ------------------------------------------------ MMA issuer (the pair's first CTA)
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = tile_begin; ok && tile < tile_end; tile += tile_step) {
+            const int run = (tile - tile_begin) / tile_step;
+            const int acc = run & 1;
+            if (!mbar_wait_cluster(&acc_empty[acc], ((run >> 1) & 1u) ^ 1u, &abort_flag)) {
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t tmem_d = tmem_base + acc * kPairN;
+            for (int kb = 0; kb < p.k_blocks; ++kb) {
+                if (!mbar_wait(&full_bar[stage], phase, &abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tcgen05_fence_after();
+                const unsigned char* a = tiles + stage * kStageBytes;
+                const uint64_t desc_a = smem_descriptor(a), desc_b = smem_descriptor(a + kBytesA);
+                if (elect_one()) {
+#pragma unroll
+                    for (int k = 0; k < kBlockK / 16; ++k) {
+                        tcgen05_mma_pair(tmem_d, desc_a + 2 * k, desc_b + 2 * k, kIdesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit_pair(&empty_bar[stage]);  // frees the stage in both CTAs
+                }
+                __syncwarp();
+                if (++stage == kStages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+            if (!ok) {
+                break;
+            }
+            if (elect_one()) {
+                tcgen05_commit_pair(&acc_full[acc]);  // both CTAs' epilogues may read
+            }
+            __syncwarp();
+        }
+    } else if (warp >= 2) {
+        // ------------------------------------------------ epilogue (warps 2..5, both CTAs)
+        const int lane_group = warp & 3;  // the tensor-memory lanes a warp may read: 32 * (warp % 4)
+        const int feature = lane_group * 32 + lane;
+        for (int tile = tile_begin; tile < tile_end; tile += tile_step) {
+            const int run = (tile - tile_begin) / tile_step;
+            const int acc = run & 1;
+            if (!mbar_wait(&acc_full[acc], (run >> 1) & 1u, &abort_flag)) {
+                break;
+            }
+            tcgen05_fence_after();
+            const int n = (tile / p.t_tiles) * (2 * kTileM) + rank * kTileM + feature;
+            const int t0 = (tile % p.t_tiles) * kPairN;
+            const uint32_t tmem_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + acc * kPairN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < kPairN && t0 + c0 < p.t; c0 += 32) {
+                uint32_t v[32];
+                tcgen05_ld32_nowait(tmem_row + c0, v);
+                tcgen05_wait_ld();
+                if (n < p.n) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int t = t0 + c0 + c;
+                        if (t < p.t) {
+                            if (p.out_f32) {
+                                static_cast<float*>(p.y)[t * p.ldy + n] = __uint_as_float(v[c]);
+                            } else {
+                                static_cast<__nv_bfloat16*>(p.y)[t * p.ldy + n] =
+                                    __float2bfloat16_rn(__uint_as_float(v[c]));
+                            }
+                        }
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                arrive_on_first(&acc_empty[acc]);
+            }
+        }
+    }
+
+    // ---------------------------------------------------- teardown
+    __syncwarp();
+    tcgen05_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        if (threadIdx.x == 0) {
+            if (p.status != nullptr) {
+                atomicOr(p.status, 8);
+            }
+            for (uint32_t spin = 0; spin < (1u << 16); ++spin) {
+                __nanosleep(64);  // loads in flight land meanwhile
+            }
+        }
+        __syncthreads();
+    }
+    // Neither CTA leaves while its partner may still read its shared memory (MMAs) or
+    // arrive on its barriers.
+    cluster_arrive_all();
+    cluster_wait_all();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tcgen05_dealloc_pair(tmem_base, kColumns);
+    }
+}
+
+int pair_count() {
+    static int pairs = 0;
+    if (pairs == 0) {
+        int device = 0, sms = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        pairs = sms / 2;
+    }
+    return pairs;
+}
+
+}  // namespace
+
+// 1 when pl_gemm_bf16_pair takes these sizes (rows of X and W on 16-byte boundaries).
+PL_API int pl_gemm_bf16_pair_supports(int t, int n, int k, int64_t ldx, int64_t ldw) {
+    return t >= 1 && n >= 1 && k >= 8 && k % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0;
+}
+
+// y[T, N] (bf16, or fp32 when out_f32) = x[T, K] w[N, K]^T with bf16 x and w, on
+// pairs of SMs; meant for hundreds of tokens and more (a tile is 256 x 256).
+PL_API int pl_gemm_bf16_pair(const void* x, const void* w, void* y, int t, int n, int k, int64_t ldx, int64_t ldw,
+                             int64_t ldy, int out_f32, int32_t* status, cudaStream_t stream) {
+    PL_REQUIRE(pl_gemm_bf16_pair_supports(t, n, k, ldx, ldw),
+               "gemm_bf16_pair: unsupported sizes t=%d n=%d k=%d ldx=%lld ldw=%lld (k and the leading dimensions "
+               "must be multiples of 8)",
+               t, n, k, static_cast<long long>(ldx), static_cast<long long>(ldw));
+    PL_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+               "gemm_bf16_pair: operands must be 16-byte aligned");
+    PL_REQUIRE(ldy >= n, "gemm_bf16_pair: ldy=%lld is smaller than n=%d", static_cast<long long>(ldy), n);
+    CUtensorMap map_w, map_x;
+    if (const int code = make_map(&map_w, w, n, k, ldw, kTileM, kBlockK)) {
+        return code;
+    }
+    if (const int code = make_map(&map_x, x, t, k, ldx, kPairN / 2, kBlockK)) {
+        return code;
+    }
+    PairParams p;
+    p.y = y;
+    p.t = t;
+    p.n = n;
+    p.k = k;
+    p.ldy = ldy;
+    p.out_f32 = out_f32;
+    p.n_tiles = (n + 2 * kTileM - 1) / (2 * kTileM);
+    p.t_tiles = (t + kPairN - 1) / kPairN;
+    p.k_blocks = (k + kBlockK - 1) / kBlockK;
+    p.total_tiles = p.n_tiles * p.t_tiles;
+    const int used_pairs = p.total_tiles < pair_count() ? p.total_tiles : pair_count();
+    p.status = status;
+    constexpr int smem = kStages * kStageBytes + 1024;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t err = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (err != cudaSuccess) {
+            return pl_fail(3, "gemm_bf16_pair: cannot set shared memory size: %s", cudaGetErrorString(err));
+        }
+        configured = true;
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2 * used_pairs);
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    attributes[0].id = cudaLaunchAttributeClusterDimension;
+    attributes[0].val.clusterDim.x = 2;
+    attributes[0].val.clusterDim.y = 1;
+    attributes[0].val.clusterDim.z = 1;
+    attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attributes;
+    config.numAttrs = pl_overlap_enabled() ? 2 : 1;
+    const cudaError_t err = cudaLaunchKernelEx(&config, gemm_pair_kernel, map_w, map_x, p);
+    if (err != cudaSuccess) {
+        return pl_fail(3, "gemm_bf16_pair: launch failed: %s", cudaGetErrorString(err));
+    }
+    return 0;
+}

@@ -63,10 +63,18 @@ def bench_gemm(shapes) -> None:
             torch.mm(x, weights[turn[0] % copies].t(), out=out)
             turn[0] += 1
 
+        def pair():
+            ops.gemm_bf16(x, weights[turn[0] % copies], out, kernel="pair")
+            turn[0] += 1
+
         gb, tf = n * k * 2 / 1e9, 2.0 * t * n * k / 1e12
         a, b = graph_time_us(own), graph_time_us(library)
-        print(f"gemm t={t} n={n} k={k}: tcgen05 {a:.1f} us ({gb / a * 1e6:.0f} GB/s, {tf / a * 1e6:.0f} TFLOP/s)"
-              f" | library {b:.1f} us ({gb / b * 1e6:.0f} GB/s, {tf / b * 1e6:.0f} TFLOP/s)", flush=True)
+        line = (f"gemm t={t} n={n} k={k}: tcgen05 {a:.1f} us ({gb / a * 1e6:.0f} GB/s, {tf / a * 1e6:.0f} TFLOP/s)"
+                f" | library {b:.1f} us ({gb / b * 1e6:.0f} GB/s, {tf / b * 1e6:.0f} TFLOP/s)")
+        if t >= 256:
+            c = graph_time_us(pair)
+            line += f" | pair of SMs {c:.1f} us ({tf / c * 1e6:.0f} TFLOP/s)"
+        print(line, flush=True)
 
 
 def bench_attention_prefill(tokens_list, n_heads, n_kv, head_dim, page) -> None:

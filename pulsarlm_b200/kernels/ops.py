@@ -58,6 +58,7 @@ _SIGNATURES = {
     "pl_gemm_bf16_supports": [_I32, _I32, _I32, _I64, _I64],
     "pl_gemm_bf16_skinny": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I64, _I64, _I64, _I32, _PTR, _PTR],
     "pl_gemm_bf16_skinny_max_tokens": [],
+    "pl_gemm_bf16_pair": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I64, _I64, _I64, _I32, _PTR, _PTR],
     "pl_attention_decode_resident_clusters": [_I32, _I32, _I32],
     "pl_gemm_bf16_skinny_splits": [_I32, _I32, _I32],
     "pl_sample": [_PTR, _I64, _I32, _I32, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR],
@@ -254,6 +255,10 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch
         kernel = "skinny" if t <= GEMM_SKINNY_MAX_TOKENS else "persistent"
     if kernel == "skinny":
         _call("pl_gemm_bf16_skinny", _p(x), _p(w), _p(out), t, n, k, ldx, ldw, out.stride(0) if t > 1 else n,
+              int(out.dtype == torch.float32), _p(status), _stream())
+        return
+    if kernel == "pair":
+        _call("pl_gemm_bf16_pair", _p(x), _p(w), _p(out), t, n, k, ldx, ldw, out.stride(0) if t > 1 else n,
               int(out.dtype == torch.float32), _p(status), _stream())
         return
     assert kernel == "persistent", kernel

@@ -116,14 +116,15 @@ GEMM_SHAPES = [(1, 128, 64), (8, 256, 128), (3, 100, 96), (37, 1000, 96), (300, 
 
 
 @pytest.mark.parametrize("t,n,k,kernel", [(t, n, k, kernel) for (t, n, k) in GEMM_SHAPES
-                                          for kernel in (("skinny", "persistent") if t <= 64 else ("persistent",))])
+                                          for kernel in (("skinny", "persistent", "pair") if t <= 64
+                                                         else ("persistent", "pair"))])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_bf16_tcgen05(ops, t, n, k, kernel, out_dtype):
     """The tensor-core products at token counts from one to thousands, widths that
     are no multiple of the tile, k ranges shared between CTAs (few tiles: through
     scratch memory in the persistent kernel, inside a cluster in the skinny one,
     with more ranks than tokens and ranks with a shorter k range among the cases)
-    and whole tiles (many)."""
+    and whole tiles (many); and the kernel that runs a tile on a pair of SMs."""
     x = torch.randn(t, k, device=DEV).to(torch.bfloat16)
     w = (torch.randn(n, k, device=DEV) / k ** 0.5).to(torch.bfloat16)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
@@ -135,7 +136,11 @@ def test_gemm_bf16_tcgen05(ops, t, n, k, kernel, out_dtype):
         outs.append(out)
     want = x.double() @ w.double().T
     assert int(status) == 0
-    assert rel(outs[0], want) < (1e-5 if out_dtype == torch.float32 else 1e-2)
+    # fp32 results carry the rounding of one fp32 accumulator over k terms, which grows
+    # with sqrt(k) (the kernels that cut k among CTAs add shorter partial sums): four
+    # standard deviations of that, and no less than 1e-5.
+    fp32_bar = max(1e-5, 4 * k ** 0.5 * 2.0 ** -24)
+    assert rel(outs[0], want) < (fp32_bar if out_dtype == torch.float32 else 1e-2)
     assert torch.equal(outs[0], outs[1])
 
 
@@ -149,7 +154,7 @@ def test_gemm_bf16_finds_one_large_product_among_many(ops):
         w = torch.zeros(n, k, device=DEV, dtype=torch.bfloat16)
         x[3, hot_k] = 3.0
         w[150, hot_k] = 2.0
-        for kernel in ("skinny", "persistent"):
+        for kernel in ("skinny", "persistent", "pair"):
             out = torch.empty(t, n, device=DEV, dtype=torch.float32)
             ops.gemm_bf16(x, w, out, kernel=kernel)
             want = torch.zeros(t, n)
