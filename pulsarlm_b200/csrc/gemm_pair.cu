@@ -25,6 +25,13 @@
 // every token tile re-reads its weights from HBM: 2.07 GB instead of 0.25 GB for the
 // 2048 x 28672 x 4096 product).
 //
+// Gated mode: W holds two stacked matrices, gate over up ([2N, K]), and the kernel
+// writes silu(gate x) * (up x) ([T, N]). A CTA's 128 rows are then 64 gate rows over
+// the 64 up rows of the same features (two TMA boxes per stage); in the epilogue the
+// warps that hold the up rows pass them through shared memory to the warps that hold
+// the gate rows, which round both to bfloat16 (as a product that stored them would)
+// and apply the activation.
+//
 // Every wait on an mbarrier is bounded: after the limit the CTA raises bit 8 of the
 // status word, stops issuing work, lets what is in flight land, meets its partner,
 // frees its tensor memory and returns.
@@ -46,7 +53,7 @@ constexpr int kStageBytes = kBytesA + kBytesB;  // per CTA
 
 struct PairParams {
     void* y;  // [T, N] bf16 or fp32
-    int t, n, k;
+    int t, n, k;  // n: output features (gated: W has 2n rows)
     int64_t ldy;
     int out_f32;
     int n_tiles;  // tiles along N (256 features each)
@@ -104,6 +111,10 @@ __device__ __forceinline__ void arrive_on_first(uint64_t* bar) {
                  : "memory");
 }
 
+constexpr int kGateRow = 17;  // 16 token columns handed over per thread and chunk, padded against bank conflicts
+constexpr int kGateBytes = 2 * 2 * (kTileM / 2) * kGateRow * 4;  // two buffers of [gate side, up side][64][17] floats
+
+template <bool GATED>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                  const PairParams p) {
@@ -114,6 +125,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     extern __shared__ unsigned char raw_smem[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
                                                             ~static_cast<uintptr_t>(1023));
+    float* handover = reinterpret_cast<float*>(tiles + kStages * kStageBytes);  // gated: [2][2][64][17]
+    constexpr int kPer = GATED ? kTileM / 2 : kTileM;      // output features per CTA and tile
     __shared__ __align__(8) uint64_t full_bar[kStages];   // waited on in the first CTA only
     __shared__ __align__(8) uint64_t empty_bar[kStages];
     __shared__ __align__(8) uint64_t acc_full[2];
@@ -158,7 +171,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         uint32_t phase = 0;
         bool ok = true;
         for (int tile = tile_begin; ok && tile < tile_end; tile += tile_step) {
-            const int n0 = (tile / p.t_tiles) * (2 * kTileM) + rank * kTileM;
+            const int n0 = (tile / p.t_tiles) * (2 * kPer) + rank * kPer;
             const int t0 = (tile % p.t_tiles) * kPairN + rank * (kPairN / 2);
             for (int kb = 0; kb < p.k_blocks; ++kb) {
                 if (!mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_flag)) {
@@ -171,6 +184,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                         mbar_expect_tx(&full_bar[stage], 2 * kStageBytes);  // both CTAs' loads of this stage
                     }
                     tma_load_2d_pair(a, &map_w, kb * kBlockK, n0, &full_bar[stage]);
+                    if (GATED) {  // the up rows of the same features under the gate rows
+                        tma_load_2d_pair(a + kBytesA / 2, &map_w, kb * kBlockK, p.n + n0, &full_bar[stage]);
+                    }
                     tma_load_2d_pair(a + kBytesA, &map_x, kb * kBlockK, t0, &full_bar[stage]);
                 }
                 __syncwarp();
@@ -233,7 +249,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 break;
             }
             tcgen05_fence_after();
-            const int n = (tile / p.t_tiles) * (2 * kTileM) + rank * kTileM + feature;
+            const int n = (tile / p.t_tiles) * (2 * kPer) + rank * kPer + (GATED ? feature % kPer : feature);
             const int t0 = (tile % p.t_tiles) * kPairN;
             const uint32_t tmem_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + acc * kPairN;
 #pragma unroll 1
@@ -241,7 +257,50 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 uint32_t v[32];
                 tcgen05_ld32_nowait(tmem_row + c0, v);
                 tcgen05_wait_ld();
-                if (n < p.n) {
+                if (GATED) {
+                    // Lanes 0..63 hold gate rows, lanes 64..127 the up rows of the same features.
+                    // Each side hands the other half of its chunk: the gate threads then have
+                    // both values for the chunk's first 16 tokens, the up threads for the last 16.
+                    const bool is_up = feature >= kPer;
+                    const int mine = is_up ? 16 : 0;  // the columns this thread finishes
+                    float* buffer = handover + ((c0 >> 5) & 1) * (2 * kPer * kGateRow) +
+                        (is_up ? 0 : kPer * kGateRow) + (feature % kPer) * kGateRow;
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        buffer[c] = __uint_as_float(v[(16 - mine) + c]);  // the half the partner finishes
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");  // (two buffers: one barrier per chunk is enough)
+                    if (n < p.n) {
+                        // (loads, arithmetic and stores in separate sweeps: a store between two
+                        // loads would keep the compiler from overlapping the elements' latencies)
+                        const float* theirs = handover + ((c0 >> 5) & 1) * (2 * kPer * kGateRow) +
+                            (is_up ? kPer * kGateRow : 0) + (feature % kPer) * kGateRow;
+                        float other[16], act[16];
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            other[c] = theirs[c];
+                        }
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            const float own = __uint_as_float(v[mine + c]);
+                            // both products rounded as a product that stored them would round them
+                            const float g = __bfloat162float(__float2bfloat16_rn(is_up ? other[c] : own));
+                            const float u = __bfloat162float(__float2bfloat16_rn(is_up ? own : other[c]));
+                            act[c] = __fdividef(g, 1.0f + __expf(-g)) * u;
+                        }
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            const int t = t0 + c0 + mine + c;
+                            if (t < p.t) {
+                                if (p.out_f32) {
+                                    static_cast<float*>(p.y)[t * p.ldy + n] = act[c];
+                                } else {
+                                    static_cast<__nv_bfloat16*>(p.y)[t * p.ldy + n] = __float2bfloat16_rn(act[c]);
+                                }
+                            }
+                        }
+                    }
+                } else if (n < p.n) {
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
                         const int t = t0 + c0 + c;
@@ -307,41 +366,16 @@ PL_API int pl_gemm_bf16_pair_supports(int t, int n, int k, int64_t ldx, int64_t 
     return t >= 1 && n >= 1 && k >= 8 && k % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0;
 }
 
-// y[T, N] (bf16, or fp32 when out_f32) = x[T, K] w[N, K]^T with bf16 x and w, on
-// pairs of SMs; meant for hundreds of tokens and more (a tile is 256 x 256).
-PL_API int pl_gemm_bf16_pair(const void* x, const void* w, void* y, int t, int n, int k, int64_t ldx, int64_t ldw,
-                             int64_t ldy, int out_f32, int32_t* status, cudaStream_t stream) {
-    PL_REQUIRE(pl_gemm_bf16_pair_supports(t, n, k, ldx, ldw),
-               "gemm_bf16_pair: unsupported sizes t=%d n=%d k=%d ldx=%lld ldw=%lld (k and the leading dimensions "
-               "must be multiples of 8)",
-               t, n, k, static_cast<long long>(ldx), static_cast<long long>(ldw));
-    PL_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
-               "gemm_bf16_pair: operands must be 16-byte aligned");
-    PL_REQUIRE(ldy >= n, "gemm_bf16_pair: ldy=%lld is smaller than n=%d", static_cast<long long>(ldy), n);
-    CUtensorMap map_w, map_x;
-    if (const int code = make_map(&map_w, w, n, k, ldw, kTileM, kBlockK)) {
-        return code;
-    }
-    if (const int code = make_map(&map_x, x, t, k, ldx, kPairN / 2, kBlockK)) {
-        return code;
-    }
-    PairParams p;
-    p.y = y;
-    p.t = t;
-    p.n = n;
-    p.k = k;
-    p.ldy = ldy;
-    p.out_f32 = out_f32;
-    p.n_tiles = (n + 2 * kTileM - 1) / (2 * kTileM);
-    p.t_tiles = (t + kPairN - 1) / kPairN;
-    p.k_blocks = (k + kBlockK - 1) / kBlockK;
-    p.total_tiles = p.n_tiles * p.t_tiles;
-    const int used_pairs = p.total_tiles < pair_count() ? p.total_tiles : pair_count();
-    p.status = status;
-    constexpr int smem = kStages * kStageBytes + 1024;
+namespace {
+
+template <bool GATED>
+int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, const PairParams& p, int used_pairs,
+                cudaStream_t stream) {
+    constexpr int smem = kStages * kStageBytes + (GATED ? kGateBytes : 0) + 1024;
     static bool configured = false;
     if (!configured) {
-        const cudaError_t err = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        const cudaError_t err = cudaFuncSetAttribute(gemm_pair_kernel<GATED>,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (err != cudaSuccess) {
             return pl_fail(3, "gemm_bf16_pair: cannot set shared memory size: %s", cudaGetErrorString(err));
         }
@@ -361,9 +395,51 @@ PL_API int pl_gemm_bf16_pair(const void* x, const void* w, void* y, int t, int n
     attributes[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attributes;
     config.numAttrs = pl_overlap_enabled() ? 2 : 1;
-    const cudaError_t err = cudaLaunchKernelEx(&config, gemm_pair_kernel, map_w, map_x, p);
+    const cudaError_t err = cudaLaunchKernelEx(&config, gemm_pair_kernel<GATED>, map_w, map_x, p);
     if (err != cudaSuccess) {
         return pl_fail(3, "gemm_bf16_pair: launch failed: %s", cudaGetErrorString(err));
     }
     return 0;
+}
+
+}  // namespace
+
+// y[T, N] (bf16, or fp32 when out_f32) = x[T, K] w[N, K]^T with bf16 x and w, on
+// pairs of SMs; meant for hundreds of tokens and more (a tile is 256 x 256). With
+// `gated`, w is [2N, K] (a gate matrix over an up matrix) and
+// y = silu(x gate^T) * (x up^T), both products rounded to bfloat16 first (a tile is
+// then 128 output features x 256 tokens).
+PL_API int pl_gemm_bf16_pair(const void* x, const void* w, void* y, int t, int n, int k, int64_t ldx, int64_t ldw,
+                             int64_t ldy, int out_f32, int gated, int32_t* status, cudaStream_t stream) {
+    PL_REQUIRE(pl_gemm_bf16_pair_supports(t, n, k, ldx, ldw),
+               "gemm_bf16_pair: unsupported sizes t=%d n=%d k=%d ldx=%lld ldw=%lld (k and the leading dimensions "
+               "must be multiples of 8)",
+               t, n, k, static_cast<long long>(ldx), static_cast<long long>(ldw));
+    PL_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+               "gemm_bf16_pair: operands must be 16-byte aligned");
+    PL_REQUIRE(ldy >= n, "gemm_bf16_pair: ldy=%lld is smaller than n=%d", static_cast<long long>(ldy), n);
+    const int per_pair = gated ? kTileM : 2 * kTileM;  // output features of a tile
+    CUtensorMap map_w, map_x;
+    if (const int code = make_map(&map_w, w, gated ? 2 * static_cast<int64_t>(n) : n, k, ldw,
+                                  gated ? kTileM / 2 : kTileM, kBlockK)) {
+        return code;
+    }
+    if (const int code = make_map(&map_x, x, t, k, ldx, kPairN / 2, kBlockK)) {
+        return code;
+    }
+    PairParams p;
+    p.y = y;
+    p.t = t;
+    p.n = n;
+    p.k = k;
+    p.ldy = ldy;
+    p.out_f32 = out_f32;
+    p.n_tiles = (n + per_pair - 1) / per_pair;
+    p.t_tiles = (t + kPairN - 1) / kPairN;
+    p.k_blocks = (k + kBlockK - 1) / kBlockK;
+    p.total_tiles = p.n_tiles * p.t_tiles;
+    const int used_pairs = p.total_tiles < pair_count() ? p.total_tiles : pair_count();
+    p.status = status;
+    return gated ? launch_pair<true>(map_w, map_x, p, used_pairs, stream)
+                 : launch_pair<false>(map_w, map_x, p, used_pairs, stream);
 }

@@ -58,7 +58,7 @@ _SIGNATURES = {
     "pl_gemm_bf16_supports": [_I32, _I32, _I32, _I64, _I64],
     "pl_gemm_bf16_skinny": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I64, _I64, _I64, _I32, _PTR, _PTR],
     "pl_gemm_bf16_skinny_max_tokens": [],
-    "pl_gemm_bf16_pair": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I64, _I64, _I64, _I32, _PTR, _PTR],
+    "pl_gemm_bf16_pair": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I64, _I64, _I64, _I32, _I32, _PTR, _PTR],
     "pl_attention_decode_resident_clusters": [_I32, _I32, _I32],
     "pl_gemm_bf16_skinny_splits": [_I32, _I32, _I32],
     "pl_sample": [_PTR, _I64, _I32, _I32, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR],
@@ -237,30 +237,36 @@ GEMM_SKINNY_MAX_TOKENS = 64
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor | None = None,
-              kernel: str | None = None) -> None:
+              kernel: str | None = None, gated: bool = False) -> None:
     """out[T, N] (bf16 or fp32) = x[T, K] @ w[N, K]^T on the tcgen05 tensor cores.
 
-    Two kernels: "skinny" for up to 64 tokens (one tile and part of k per CTA, the
-    parts added inside a thread-block cluster) and "persistent" for more (and for
-    any count when asked by name). `kernel=None` picks by the token count."""
+    Three kernels: "skinny" for up to 64 tokens (one tile and part of k per CTA, the
+    parts added inside a thread-block cluster), "pair" for prompts (256 x 256 tiles on
+    pairs of SMs) and "persistent" (one CTA per tile, any token count). `kernel=None`
+    picks skinny or pair by the token count.
+
+    gated (pair only): w is [2N, K], a gate matrix over an up matrix, and
+    out = silu(x gate^T) * (x up^T), both products rounded to bfloat16 first."""
     _dev(x, w, out, status)
     assert x.dtype == w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
     t, k = x.shape
-    n = w.shape[0]
-    assert w.shape[1] == k and out.shape == (t, n)
+    n = w.shape[0] // 2 if gated else w.shape[0]
+    assert w.shape[1] == k and out.shape == (t, n) and (not gated or w.shape[0] == 2 * n)
     assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
     ldx = x.stride(0) if t > 1 else k
-    ldw = w.stride(0) if n > 1 else k
+    ldw = w.stride(0) if w.shape[0] > 1 else k
     if kernel is None:
-        kernel = "skinny" if t <= GEMM_SKINNY_MAX_TOKENS else "persistent"
+        kernel = "skinny" if t <= GEMM_SKINNY_MAX_TOKENS and not gated else "pair"
     if kernel == "skinny":
+        assert not gated, "only the pair kernel has the gated epilogue"
         _call("pl_gemm_bf16_skinny", _p(x), _p(w), _p(out), t, n, k, ldx, ldw, out.stride(0) if t > 1 else n,
               int(out.dtype == torch.float32), _p(status), _stream())
         return
     if kernel == "pair":
         _call("pl_gemm_bf16_pair", _p(x), _p(w), _p(out), t, n, k, ldx, ldw, out.stride(0) if t > 1 else n,
-              int(out.dtype == torch.float32), _p(status), _stream())
+              int(out.dtype == torch.float32), int(gated), _p(status), _stream())
         return
+    assert not gated, "only the pair kernel has the gated epilogue"
     assert kernel == "persistent", kernel
     floats = int(library().pl_gemm_bf16_scratch_floats(t, n, k))
     scratch = torch.empty(floats, dtype=torch.float32, device=x.device) if floats else None

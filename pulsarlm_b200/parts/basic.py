@@ -11,7 +11,7 @@ import math
 import torch
 
 from ..kernels import ops
-from .linear import linear
+from .linear import gated_linear, linear
 from .registry import BuildContext, Part, register_part
 from .spec import PartSpec, TensorNeed
 
@@ -192,7 +192,4 @@ class GatedMLP(Part):
         self.down = tensors[t["down"]].contiguous()
 
     def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
-        gate_up = linear(h, self.gate_up)
-        act = torch.empty((h.shape[0], self.inter), dtype=h.dtype, device=h.device)
-        ops.swiglu(gate_up, act)
-        return linear(act, self.down)
+        return linear(gated_linear(h, self.gate_up), self.down)

@@ -4,14 +4,17 @@ float32: the library's own CUDA-core kernel (true fp32, no tensor cores, no
 TF32), whose result for a row does not depend on the other rows. bfloat16, fp32
 accumulation, by one of three routes chosen by $PULSARLM_B200_GEMM:
 
-* "mixed" (the default): up to 16 tokens (decode steps of small batches) this
-  package's own tcgen05/TMEM kernel fed by TMA (csrc/gemm_skinny.cu), which overlaps
-  its set-up and first weight loads with the kernel before it; above that a library
-  matrix product (cuBLAS through torch), as the reference's engine does for every
-  projection (`at::linear`, pulsarlm-core/src/engine/model/llama.cpp:67-69, 81, 91,
-  93);
+* "mixed" (the default): the own tcgen05/TMEM kernels where they measured faster than
+  the library, the library elsewhere. Up to 16 tokens (decode steps of small
+  batches) csrc/gemm_skinny.cu, which overlaps its set-up and first weight loads
+  with the kernel before it; products of at least four 256 x 256 tiles per pair of
+  SMs (a prompt portion's gate/up projection, every projection of long portions)
+  csrc/gemm_pair.cu, which runs a tile on two SMs (`cta_group::2`); in between a
+  library matrix product (cuBLAS through torch), as the reference's engine does for
+  every projection (`at::linear`, pulsarlm-core/src/engine/model/llama.cpp:67-69,
+  81, 91, 93);
 * "tcgen05": the own kernels at every size they take (rows starting on 16 bytes):
-  csrc/gemm_skinny.cu up to 64 tokens, csrc/gemm_tcgen05.cu above; the library
+  csrc/gemm_skinny.cu up to 64 tokens, csrc/gemm_pair.cu above; the library
   elsewhere;
 * "library": the library everywhere.
 
@@ -28,9 +31,28 @@ import os
 from ..kernels import ops
 
 GEMM_ROUTE = os.environ.get("PULSARLM_B200_GEMM", "mixed")
-MIXED_MAX_TOKENS = 16  # the own kernel is ahead of the library up to here
+MIXED_MAX_TOKENS = 16  # the skinny kernel is ahead of the library up to here,
+MIXED_MIN_TILES_PER_PAIR = 4  # and the pair kernel from this many 256 x 256 tiles per pair of SMs
 if GEMM_ROUTE not in ("library", "tcgen05", "mixed"):
     raise ValueError(f"PULSARLM_B200_GEMM must be 'library', 'tcgen05' or 'mixed', got {GEMM_ROUTE!r}")
+
+
+_PAIRS: dict[torch.device, int] = {}
+
+
+def own_kernel_for(tokens: int, n: int, device: torch.device) -> str | None:
+    """Which of the package's own tcgen05 kernels the route gives a [tokens, n] product
+    to ("skinny", "pair"), or None for the library."""
+    if GEMM_ROUTE == "library":
+        return None
+    if GEMM_ROUTE == "tcgen05":
+        return "skinny" if tokens <= ops.GEMM_SKINNY_MAX_TOKENS else "pair"
+    if tokens <= MIXED_MAX_TOKENS:
+        return "skinny"
+    if device not in _PAIRS:
+        _PAIRS[device] = torch.cuda.get_device_properties(device).multi_processor_count // 2
+    tiles = -(-n // 256) * -(-tokens // 256)
+    return "pair" if tiles >= MIXED_MIN_TILES_PER_PAIR * _PAIRS[device] else None
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
@@ -45,14 +67,32 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         return out
     if x.dtype == torch.bfloat16:
         k = x.shape[1]
-        own = GEMM_ROUTE == "tcgen05" or (GEMM_ROUTE == "mixed" and tokens <= MIXED_MAX_TOKENS)
-        if own and x.stride(1) == 1 and weight.stride(1) == 1 and ops.gemm_bf16_supports(
+        kernel = own_kernel_for(tokens, n, x.device)
+        if kernel is not None and x.stride(1) == 1 and weight.stride(1) == 1 and ops.gemm_bf16_supports(
                 tokens, n, k, x.stride(0) if tokens > 1 else k, weight.stride(0) if n > 1 else k):
             out = torch.empty((tokens, n), dtype=out_dtype or torch.bfloat16, device=x.device)
-            ops.gemm_bf16(x, weight, out)
+            ops.gemm_bf16(x, weight, out, kernel=kernel)
             return out
         if out_dtype == torch.float32:
             # bf16 operands, fp32 accumulator written out unrounded.
             return torch.mm(x, weight.t(), out_dtype=torch.float32)
         return torch.mm(x, weight.t())
     raise ops.KernelError(f"linear: unsupported dtype {x.dtype}")
+
+
+def gated_linear(x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) for gate_up = [Wg; Wu] stacked [2I, K] -> [T, I].
+
+    Both products are rounded to the activation dtype before the activation. Where the
+    pair kernel runs the product, the activation happens in its epilogue (the [T, 2I]
+    intermediate is never written); else the product is followed by the SwiGLU kernel."""
+    tokens, k = x.shape
+    inter = gate_up.shape[0] // 2
+    act = torch.empty((tokens, inter), dtype=x.dtype, device=x.device)
+    if (x.dtype == torch.bfloat16 == gate_up.dtype and own_kernel_for(tokens, 2 * inter, x.device) == "pair"
+            and x.stride(1) == 1 and gate_up.stride(1) == 1
+            and ops.gemm_bf16_supports(tokens, inter, k, x.stride(0) if tokens > 1 else k, gate_up.stride(0))):
+        ops.gemm_bf16(x, gate_up, act, kernel="pair", gated=True)
+        return act
+    ops.swiglu(linear(x, gate_up), act)
+    return act

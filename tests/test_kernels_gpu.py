@@ -144,6 +144,30 @@ def test_gemm_bf16_tcgen05(ops, t, n, k, kernel, out_dtype):
     assert torch.equal(outs[0], outs[1])
 
 
+@pytest.mark.parametrize("t,n,k", [(1, 64, 64), (8, 172, 64), (300, 336, 160), (600, 1000, 520), (2048, 1792, 256),
+                                   (257, 96, 4096)])
+def test_gemm_bf16_gated_epilogue(ops, t, n, k):
+    """silu(x gate^T) * (x up^T) from the pair kernel's epilogue: against the two
+    products rounded to bfloat16 and the activation in fp64, and bit for bit against
+    the plain product followed by the SwiGLU kernel; widths that are no multiple of
+    the 64-feature half tile, token counts that are no multiple of the tile."""
+    x = torch.randn(t, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * n, k, device=DEV) / k ** 0.5 * 2).to(torch.bfloat16)
+    out = torch.full((t, n), float("nan"), device=DEV, dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.gemm_bf16(x, w, out, status, kernel="pair", gated=True)
+    both = (x.double() @ w.double().T).to(torch.bfloat16).double()
+    gate, up = both[:, :n], both[:, n:]
+    want = gate / (1 + torch.exp(-gate)) * up
+    assert int(status) == 0
+    assert rel(out, want) < 1e-2
+    plain = torch.empty(t, 2 * n, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_bf16(x, w, plain, kernel="pair")
+    two_step = torch.empty_like(out)
+    ops.swiglu(plain, two_step)
+    assert torch.equal(out, two_step)
+
+
 def test_gemm_bf16_finds_one_large_product_among_many(ops):
     """One x[t, k] * w[n, k] pair far larger than the rest, at the last k of a k
     block, the first of the next, and in the tail: a dropped k block or a mis-stepped
