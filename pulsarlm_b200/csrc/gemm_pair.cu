@@ -5,10 +5,10 @@
 // `tcgen05.mma.cta_group::2` (M = 256 over the pair, N = 256, K = 16 per instruction).
 // The weights sit on the MMA's M axis and the tokens on its N axis, as in the other
 // products of this library. Each CTA loads its own 128 features of W and its own 128
-// of the tile's 256 tokens of X per 64-deep k block (32 KB where a lone CTA with the
-// same tile per SM would need 48 KB: one SM takes in about 64 bytes a clock, which is
-// what bounds the single-CTA kernel in gemm_tcgen05.cu); the instruction reads both
-// CTAs' shared memory and writes each CTA's 128 rows of the accumulator into that
+// of the tile's 256 tokens of X per 64-deep k block (32 KB where a lone CTA with a
+// 128 x 256 tile of its own would need 48 KB for the same number of MMA cycles: one SM
+// takes in about 64 bytes a clock, which held a single-CTA kernel of that tile to 0.6 -
+// 0.7 of the GEMM peak); the instruction reads both CTAs' shared memory and writes each CTA's 128 rows of the accumulator into that
 // CTA's tensor memory.
 //
 // Roles per CTA (192 threads): warp 0 loads with TMA (`.cta_group::2` loads, whose

@@ -5,7 +5,7 @@
 // SM's loads in flight and around the time between the last byte and the result:
 //
 // * The weights sit on the MMA's M axis (tiles of 128 output features), the tokens
-//   on its N axis (16, 32 or 64), as in the large-product kernel (gemm_tcgen05.cu):
+//   on its N axis (16, 32 or 64), as in the large-product kernel (gemm_pair.cu):
 //   `tcgen05.mma.cta_group::1.kind::f16`, operands in shared memory through TMA with
 //   128-byte swizzle, the accumulator in tensor memory.
 // * One CTA computes one tile over one part of k. The grid is (splits, tiles) with

@@ -8,7 +8,8 @@
 Each timing replays a CUDA graph of several launches (so host time does not
 count) over inputs rotated through enough copies to exceed L2, after warm-up,
 between CUDA events. Prints one line per case with achieved GB/s and TFLOP/s.
-`gemm` times the tcgen05 kernels beside the library product torch.mm calls.
+`gemm` times the tcgen05 kernels (skinny up to 64 tokens, pair above) beside the library
+product torch.mm calls.
 `decode_timeline` replays the engine's captured decode step of a Llama-3.1-8B-shaped
 model (random weights, fewer layers) under the torch profiler's CUDA activity trace and
 prints when each kernel of one layer starts and ends inside the graph: kernels overlap
@@ -63,17 +64,11 @@ def bench_gemm(shapes) -> None:
             torch.mm(x, weights[turn[0] % copies].t(), out=out)
             turn[0] += 1
 
-        def pair():
-            ops.gemm_bf16(x, weights[turn[0] % copies], out, kernel="pair")
-            turn[0] += 1
-
         gb, tf = n * k * 2 / 1e9, 2.0 * t * n * k / 1e12
         a, b = graph_time_us(own), graph_time_us(library)
-        line = (f"gemm t={t} n={n} k={k}: tcgen05 {a:.1f} us ({gb / a * 1e6:.0f} GB/s, {tf / a * 1e6:.0f} TFLOP/s)"
+        name = "skinny" if t <= ops.GEMM_SKINNY_MAX_TOKENS else "pair"
+        line = (f"gemm t={t} n={n} k={k}: {name} {a:.1f} us ({gb / a * 1e6:.0f} GB/s, {tf / a * 1e6:.0f} TFLOP/s)"
                 f" | library {b:.1f} us ({gb / b * 1e6:.0f} GB/s, {tf / b * 1e6:.0f} TFLOP/s)")
-        if t >= 256:
-            c = graph_time_us(pair)
-            line += f" | pair of SMs {c:.1f} us ({tf / c * 1e6:.0f} TFLOP/s)"
         print(line, flush=True)
 
 

@@ -54,8 +54,7 @@ _SIGNATURES = {
                                      _PTR, _I64, _I32, _I32, _I32, _I32, _F32, _PTR, _PTR],
     "pl_attention_prefill_tcgen05_supports": [_I32, _I32, _I32, _I64, _I64, _I64, _I32],
     "pl_attention_prefill_tile_rows": [],
-    "pl_gemm_bf16": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I64, _I64, _I64, _I32, _PTR, _PTR, _I32, _PTR, _PTR],
-    "pl_gemm_bf16_supports": [_I32, _I32, _I32, _I64, _I64],
+    "pl_gemm_bf16_pair_supports": [_I32, _I32, _I32, _I64, _I64],
     "pl_gemm_bf16_skinny": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I64, _I64, _I64, _I32, _PTR, _PTR],
     "pl_gemm_bf16_skinny_max_tokens": [],
     "pl_gemm_bf16_pair": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I64, _I64, _I64, _I32, _I32, _PTR, _PTR],
@@ -87,8 +86,6 @@ def library() -> ctypes.CDLL:
         lib.pl_device_arch.restype = _I32
         lib.pl_attention_decode_scratch_floats.argtypes = [_I32, _I32, _I32, _I32]
         lib.pl_attention_decode_scratch_floats.restype = _I64
-        lib.pl_gemm_bf16_scratch_floats.argtypes = [_I32, _I32, _I32]
-        lib.pl_gemm_bf16_scratch_floats.restype = _I64
         lib.pl_set_overlap.argtypes = [_I32]
         lib.pl_set_overlap.restype = _I32
         if os.environ.get("PULSARLM_B200_OVERLAP", "1") == "0":
@@ -216,21 +213,10 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bo
           out.stride(0) if m > 1 else n, int(accumulate), _stream())
 
 
-_GEMM_COUNTERS = 1 << 16
-_gemm_counter_buffers: dict = {}
-
-
-def _gemm_counters(device: torch.device) -> torch.Tensor:
-    """Tile counters of the split-k products: zero between launches (the kernel
-    resets what it used), one buffer per device, shared by the products of one
-    stream (they run one after the other)."""
-    if device not in _gemm_counter_buffers:
-        _gemm_counter_buffers[device] = torch.zeros(_GEMM_COUNTERS, dtype=torch.int32, device=device)
-    return _gemm_counter_buffers[device]
-
-
 def gemm_bf16_supports(t: int, n: int, k: int, ldx: int, ldw: int) -> bool:
-    return bool(library().pl_gemm_bf16_supports(t, n, k, ldx, ldw))
+    """True when the tcgen05 products take these sizes: rows of both operands must start
+    on 16 bytes (k and the leading dimensions multiples of 8)."""
+    return bool(library().pl_gemm_bf16_pair_supports(t, n, k, ldx, ldw))
 
 
 GEMM_SKINNY_MAX_TOKENS = 64
@@ -240,10 +226,9 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch
               kernel: str | None = None, gated: bool = False) -> None:
     """out[T, N] (bf16 or fp32) = x[T, K] @ w[N, K]^T on the tcgen05 tensor cores.
 
-    Three kernels: "skinny" for up to 64 tokens (one tile and part of k per CTA, the
-    parts added inside a thread-block cluster), "pair" for prompts (256 x 256 tiles on
-    pairs of SMs) and "persistent" (one CTA per tile, any token count). `kernel=None`
-    picks skinny or pair by the token count.
+    Two kernels: "skinny" for up to 64 tokens (one tile and part of k per CTA, the parts
+    added inside a thread-block cluster) and "pair" (256 x 256 tiles on pairs of SMs,
+    any token count, meant for prompts). `kernel=None` picks by the token count.
 
     gated (pair only): w is [2N, K], a gate matrix over an up matrix, and
     out = silu(x gate^T) * (x up^T), both products rounded to bfloat16 first."""
@@ -266,15 +251,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch
         _call("pl_gemm_bf16_pair", _p(x), _p(w), _p(out), t, n, k, ldx, ldw, out.stride(0) if t > 1 else n,
               int(out.dtype == torch.float32), int(gated), _p(status), _stream())
         return
-    assert not gated, "only the pair kernel has the gated epilogue"
-    assert kernel == "persistent", kernel
-    floats = int(library().pl_gemm_bf16_scratch_floats(t, n, k))
-    scratch = torch.empty(floats, dtype=torch.float32, device=x.device) if floats else None
-    counters = _gemm_counters(x.device) if floats else None
-    _call("pl_gemm_bf16", _p(x), _p(w), _p(out), t, n, k, ldx, ldw, out.stride(0) if t > 1 else n,
-          int(out.dtype == torch.float32), _p(scratch), _p(counters), _GEMM_COUNTERS if floats else 0, _p(status),
-          _stream())
-
+    raise ValueError(f"gemm_bf16: unknown kernel {kernel!r}")
 
 def rope_kv_write(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | None, pos: torch.Tensor,
                   entry: torch.Tensor, table: torch.Tensor, k_pool: torch.Tensor | None,

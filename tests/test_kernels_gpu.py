@@ -116,21 +116,19 @@ GEMM_SHAPES = [(1, 128, 64), (8, 256, 128), (3, 100, 96), (37, 1000, 96), (300, 
 
 
 @pytest.mark.parametrize("t,n,k,kernel", [(t, n, k, kernel) for (t, n, k) in GEMM_SHAPES
-                                          for kernel in (("skinny", "persistent", "pair") if t <= 64
-                                                         else ("persistent", "pair"))])
+                                          for kernel in (("skinny", "pair") if t <= 64 else ("pair",))])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_bf16_tcgen05(ops, t, n, k, kernel, out_dtype):
-    """The tensor-core products at token counts from one to thousands, widths that
-    are no multiple of the tile, k ranges shared between CTAs (few tiles: through
-    scratch memory in the persistent kernel, inside a cluster in the skinny one,
-    with more ranks than tokens and ranks with a shorter k range among the cases)
-    and whole tiles (many); and the kernel that runs a tile on a pair of SMs."""
+    """The tensor-core products at token counts from one to thousands and widths that
+    are no multiple of the tile: the skinny kernel (k ranges shared between the CTAs
+    of a cluster, with more ranks than tokens and ranks with a shorter k range among
+    the cases) and the kernel that runs a tile on a pair of SMs."""
     x = torch.randn(t, k, device=DEV).to(torch.bfloat16)
     w = (torch.randn(n, k, device=DEV) / k ** 0.5).to(torch.bfloat16)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     assert ops.gemm_bf16_supports(t, n, k, k, k)
     outs = []
-    for _ in range(2):  # twice: the tile counters must be back at zero, and the bits the same
+    for _ in range(2):  # twice: the bits must be the same
         out = torch.full((t, n), float("nan"), device=DEV, dtype=out_dtype)
         ops.gemm_bf16(x, w, out, status, kernel=kernel)
         outs.append(out)
@@ -178,7 +176,7 @@ def test_gemm_bf16_finds_one_large_product_among_many(ops):
         w = torch.zeros(n, k, device=DEV, dtype=torch.bfloat16)
         x[3, hot_k] = 3.0
         w[150, hot_k] = 2.0
-        for kernel in ("skinny", "persistent", "pair"):
+        for kernel in ("skinny", "pair"):
             out = torch.empty(t, n, device=DEV, dtype=torch.float32)
             ops.gemm_bf16(x, w, out, kernel=kernel)
             want = torch.zeros(t, n)
