@@ -167,3 +167,30 @@ def test_cutting_does_not_change_float32_bits_and_barely_bfloat16(dtype):
             scale = whole[p].abs().max()
             assert (whole[p] - cut[p]).abs().max() <= 2e-2 * scale, p
             assert (whole[p] - beside[p]).abs().max() <= 2e-2 * scale, p
+
+
+@pytest.mark.parametrize("route", ["tcgen05", "library"])
+@pytest.mark.parametrize("key", KEYS)
+def test_every_bfloat16_product_route_gives_the_same_model(key, route, monkeypatch):
+    """The default route picks a kernel by the size of the product; the tiny models
+    would leave the pair kernel and its SwiGLU epilogue idle. With the route forced,
+    every projection of the model runs on the own tcgen05 kernels (skinny up to 64
+    tokens, pairs of SMs above, the gate/up projection with the activation in its
+    epilogue), or on the library, and the logits still match the plain implementation:
+    prompts in one portion, in portions, and single tokens."""
+    from pulsarlm_b200.parts import linear
+
+    monkeypatch.setattr(linear, "GEMM_ROUTE", route)
+    tm = tiny_model(key, "bfloat16")
+    reqs = prompts(tm, [70, 100, 200, 300])
+    runner = tm.runner(n_pages=32)
+    steps = []
+    for r, t in reqs.items():
+        if len(t) == 300:  # 130 tokens, then 65, then the rest one by one over the last few
+            steps.append(([(r, t[:130], range(130))], []))
+            steps.append(([(r, t[130:295], range(165))], []))
+            for i in range(295, 300):
+                steps.append(([(r, t[i:i + 1], [0])], [r] if i == 299 else []))
+        else:
+            steps.append(([(r, t, range(len(t)))], [r]))
+    assert_matches_plain(tm, reqs, replay(runner, steps), f"route {route}")
