@@ -141,6 +141,31 @@ def test_pipelined_decode_steps_change_nothing_but_the_timing():
     assert plain[1][1] == "stop" and plain[3][1] == "length" and len(plain[3][0]) == 6
 
 
+def test_cancelling_a_request_while_its_step_is_in_flight():
+    """A request cancelled between two calls of step() (its decode step already
+    launched, the next not yet) ends as cancelled, keeps the tokens it had been given,
+    gives its pages back, and the others go on unharmed."""
+    from pulsarlm_b200 import Engine, SamplingParams
+
+    tm = TinyModel("A", "float32")
+    engine = Engine(tm.folder, dtype="float32", n_pages=24, page_size=tm.page, max_requests=4)
+    prompts = [tiny.random_tokens(tm.cfg, n, seed=30 + n) for n in (6, 11)]
+    keep, drop = (engine.submit(p, sampling=SamplingParams(temperature=0.0), max_tokens=12, ignore_eos=True)
+                  for p in prompts)
+    for _ in range(6):
+        engine.step()
+    assert engine._inflight is not None  # decode steps are pipelined by now
+    seen = len(drop.output)
+    drop.cancel()
+    while not keep.finished:
+        engine.step()
+    engine.sync()
+    assert drop.finished and drop.finish_reason == "cancelled" and seen <= len(drop.output) <= seen + 1
+    assert keep.output == plain_llama.greedy_generate(tm.cfg, tm.weights, prompts[0], 12)
+    assert drop.output == plain_llama.greedy_generate(tm.cfg, tm.weights, prompts[1], 12)[: len(drop.output)]
+    assert engine.cache.free_pages() == 24
+
+
 def test_command_line_generate_and_random_model(tmp_path):
     cfg_path = tmp_path / "cfg.json"
     cfg_path.write_text(json.dumps(tiny.TINY_A))
