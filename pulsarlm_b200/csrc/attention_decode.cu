@@ -102,22 +102,6 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Deco
     const int t1 = min(t0 + per_split, tile_end);
     const int32_t* row = p.table + static_cast<int64_t>(p.entry[t]) * p.table_width;
 
-    pl_grid_wait();
-    // Q fragments: rows g and g + 8 of the group's heads (zero past the group).
-    uint32_t qa[HD / 16][4];
-    {
-        const __nv_bfloat16* qbase = p.q + t * p.q_row_stride + static_cast<int64_t>(kv_head) * p.group * HD;
-        const bool lo_ok = g < p.group, hi_ok = g + 8 < p.group;
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-            const int d = 16 * kk + 2 * tig;
-            qa[kk][0] = lo_ok ? *reinterpret_cast<const uint32_t*>(qbase + g * HD + d) : 0u;
-            qa[kk][1] = hi_ok ? *reinterpret_cast<const uint32_t*>(qbase + (g + 8) * HD + d) : 0u;
-            qa[kk][2] = lo_ok ? *reinterpret_cast<const uint32_t*>(qbase + g * HD + d + 8) : 0u;
-            qa[kk][3] = hi_ok ? *reinterpret_cast<const uint32_t*>(qbase + (g + 8) * HD + d + 8) : 0u;
-        }
-    }
-
     unsigned char* ring = smem + warp * (STAGES * kStageBytes);
     const int my_tiles = t1 > t0 + warp ? (t1 - t0 - warp + WARPS - 1) / WARPS : 0;
 
@@ -161,9 +145,41 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Deco
     }
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;
 
+    // The first tiles are asked for before the wait on earlier kernels: they hold keys of
+    // earlier steps, which no kernel of this step writes. Only the tile with the newest
+    // key (the last of the request) is written by this step's RoPE kernel; a warp whose
+    // first tiles include it waits first.
+    bool early = true;
 #pragma unroll
     for (int i = 0; i < STAGES - 1; ++i) {
-        issue(i);
+        early = early && !(i < my_tiles && t0 + warp + i * WARPS == tile_end - 1);
+    }
+    if (early) {
+#pragma unroll
+        for (int i = 0; i < STAGES - 1; ++i) {
+            issue(i);
+        }
+    }
+    pl_grid_wait();
+    // Q fragments: rows g and g + 8 of the group's heads (zero past the group).
+    uint32_t qa[HD / 16][4];
+    {
+        const __nv_bfloat16* qbase = p.q + t * p.q_row_stride + static_cast<int64_t>(kv_head) * p.group * HD;
+        const bool lo_ok = g < p.group, hi_ok = g + 8 < p.group;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+            const int d = 16 * kk + 2 * tig;
+            qa[kk][0] = lo_ok ? *reinterpret_cast<const uint32_t*>(qbase + g * HD + d) : 0u;
+            qa[kk][1] = hi_ok ? *reinterpret_cast<const uint32_t*>(qbase + (g + 8) * HD + d) : 0u;
+            qa[kk][2] = lo_ok ? *reinterpret_cast<const uint32_t*>(qbase + g * HD + d + 8) : 0u;
+            qa[kk][3] = hi_ok ? *reinterpret_cast<const uint32_t*>(qbase + (g + 8) * HD + d + 8) : 0u;
+        }
+    }
+    if (!early) {
+#pragma unroll
+        for (int i = 0; i < STAGES - 1; ++i) {
+            issue(i);
+        }
     }
     for (int i = 0; i < my_tiles; ++i) {
         cp_async_wait<STAGES - 2>();

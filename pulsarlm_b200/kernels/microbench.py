@@ -99,8 +99,10 @@ def bench_attention_decode(batches, contexts, n_heads, n_kv, head_dim, page) -> 
         for context in contexts:
             pages_each = -(-context // page)
             n_pages = batch * pages_each
-            pool = (torch.randn(n_pages, 2, n_kv, page, head_dim, device="cuda") * 0.5).to(torch.bfloat16)
-            kp, vp = pool[:, 0], pool[:, 1]
+            pool_bytes = n_pages * 2 * n_kv * page * head_dim * 2
+            copies = max(1, min(8, int(300e6 // pool_bytes)))  # rotate through more cache than the L2 holds
+            pools = [(torch.randn(n_pages, 2, n_kv, page, head_dim, device="cuda") * 0.5).to(torch.bfloat16)
+                     for _ in range(copies)]
             table = torch.randperm(n_pages, device="cuda").to(torch.int32).view(batch, pages_each)
             q = torch.randn(batch, n_heads, head_dim, device="cuda").to(torch.bfloat16)
             out = torch.empty_like(q)
@@ -110,8 +112,15 @@ def bench_attention_decode(batches, contexts, n_heads, n_kv, head_dim, page) -> 
             scratch = torch.empty(max(1, ops.attention_decode_scratch_floats(batch, n_heads, head_dim, splits)),
                                   device="cuda")
             scale = 1 / math.sqrt(head_dim)
-            us = graph_time_us(lambda: ops.attention_decode(q, kp, vp, table, pos, entry, out, page, None, scale,
-                                                            splits, scratch))
+            turn = [0]
+
+            def run():
+                pool = pools[turn[0] % copies]
+                turn[0] += 1
+                ops.attention_decode(q, pool[:, 0], pool[:, 1], table, pos, entry, out, page, None, scale, splits,
+                                     scratch)
+
+            us = graph_time_us(run, reps=max(10, copies))
             gb = batch * context * 2 * n_kv * head_dim * 2 / 1e9
             print(f"attention_decode batch={batch} context={context} heads={n_heads}/{n_kv} head_dim={head_dim} "
                   f"splits={splits}: {us:.1f} us, {gb / us * 1e6:.0f} GB/s", flush=True)
