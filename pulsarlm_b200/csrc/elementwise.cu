@@ -85,15 +85,21 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const scalar_t* __
                                        const weight_t* __restrict__ weight, scalar_t* __restrict__ out,
                                        const int32_t* __restrict__ rows, int hidden, float eps) {
     pl_grid_trigger();
-    pl_grid_wait();
     __shared__ float scratch[32];
+    const int n_vec = hidden / 4;
+    float4 w[VECS];  // the norm's scale is a weight: read before the wait on earlier kernels
+#pragma unroll
+    for (int i = 0; i < VECS; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        w[i] = c < n_vec ? pl_load4(weight + 4 * c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    pl_grid_wait();
     const int r = blockIdx.x;
-    const int64_t s = rows != nullptr ? rows[r] : r;
+    const int64_t s = rows != nullptr ? rows[r] : r;  // (rows may be written by an earlier kernel: after the wait)
     float* xr = x + s * hidden;
     const scalar_t* dr = delta != nullptr ? delta + s * hidden : nullptr;
     scalar_t* outr = out + static_cast<int64_t>(r) * hidden;
     const bool write_back = rows == nullptr && dr != nullptr;
-    const int n_vec = hidden / 4;
 
     float4 v[VECS];
     float local = 0.0f;
@@ -124,9 +130,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const scalar_t* __
     for (int i = 0; i < VECS; ++i) {
         const int c = threadIdx.x + i * blockDim.x;
         if (c < n_vec) {
-            const float4 w = pl_load4(weight + 4 * c);
-            pl_store4(outr + 4 * c, make_float4(v[i].x * inv_rms * w.x, v[i].y * inv_rms * w.y,
-                                                v[i].z * inv_rms * w.z, v[i].w * inv_rms * w.w));
+            pl_store4(outr + 4 * c, make_float4(v[i].x * inv_rms * w[i].x, v[i].y * inv_rms * w[i].y,
+                                                v[i].z * inv_rms * w[i].z, v[i].w * inv_rms * w[i].w));
         }
     }
 }

@@ -47,14 +47,11 @@ __global__ void rope_kv_write_kernel(scalar_t* __restrict__ q, const scalar_t* _
             rope_sincos(p, inv_freq[j], cs[j], sn[j]);
         }
     }
-    pl_grid_wait();
-    __syncthreads();
-
     const int n_slots = n_heads + (k_pool != nullptr ? n_kv_heads : 0);
     const int slot0 = blockIdx.y * heads_per_block;
     const int slot1 = min(slot0 + heads_per_block, n_slots);
     int page = -1;
-    if (slot1 > n_heads) {
+    if (slot1 > n_heads) {  // (the block table is a step input too: looked up before the wait)
         page = table[static_cast<int64_t>(entry[t]) * table_width + p / page_size];
         if (page < 0 || page >= n_pages) {
             if (threadIdx.x == 0 && status != nullptr) {
@@ -63,6 +60,9 @@ __global__ void rope_kv_write_kernel(scalar_t* __restrict__ q, const scalar_t* _
             page = -1;
         }
     }
+    pl_grid_wait();
+    __syncthreads();
+
     const int pairs = head_dim - half;  // per head: `half` rotated pairs, then the unrotated dims
     for (int idx = threadIdx.x; idx < (slot1 - slot0) * pairs; idx += blockDim.x) {
         const int slot = slot0 + idx / pairs, j = idx % pairs;
@@ -122,14 +122,11 @@ __global__ void rope_kv_write_vec_kernel(scalar_t* __restrict__ q, const scalar_
             rope_sincos(p, inv_freq[j], cs[j], sn[j]);
         }
     }
-    pl_grid_wait();
-    __syncthreads();
-
     const int n_slots = n_heads + (k_pool != nullptr ? n_kv_heads : 0);
     const int slot0 = blockIdx.y * heads_per_block;
     const int slot1 = min(slot0 + heads_per_block, n_slots);
     int page = -1;
-    if (slot1 > n_heads) {
+    if (slot1 > n_heads) {  // (the block table is a step input too: looked up before the wait)
         page = table[static_cast<int64_t>(entry[t]) * table_width + p / page_size];
         if (page < 0 || page >= n_pages) {
             if (threadIdx.x == 0 && status != nullptr) {
@@ -138,6 +135,9 @@ __global__ void rope_kv_write_vec_kernel(scalar_t* __restrict__ q, const scalar_
             page = -1;
         }
     }
+    pl_grid_wait();
+    __syncthreads();
+
     const int groups = (head_dim - half) / 4;  // per head: half/4 rotated groups, then the unrotated tail
     for (int idx = threadIdx.x; idx < (slot1 - slot0) * groups; idx += blockDim.x) {
         const int slot = slot0 + idx / groups, j = 4 * (idx % groups);
