@@ -29,6 +29,24 @@ CONFIG = {
     "tie_word_embeddings": False,
 }
 
+# Two more layer shapes of the family (two layers each): small heads, a tied and very
+# wide vocabulary; and one kv head per query head, a width that is no power of two.
+CONFIG_1B = dict(CONFIG, hidden_size=2048, head_dim=64, intermediate_size=8192, tie_word_embeddings=True,
+                 rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                               "original_max_position_embeddings": 8192})
+CONFIG_13B = {
+    "architectures": ["LlamaForCausalLM"],
+    "num_hidden_layers": 2,
+    "hidden_size": 5120,
+    "num_attention_heads": 40,
+    "num_key_value_heads": 40,
+    "intermediate_size": 13824,
+    "vocab_size": 32000,
+    "rope_theta": 10000.0,
+    "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False,
+}
+
 
 @pytest.fixture(scope="module")
 def weights():
@@ -39,6 +57,17 @@ def weights():
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_llama_8b_layer_sizes(weights, dtype):
+    run_shape(CONFIG, weights, dtype)
+
+
+@pytest.mark.parametrize("config", [CONFIG_1B, CONFIG_13B], ids=["llama-3.2-1b", "llama-2-13b"])
+def test_other_layer_sizes_of_the_family(config):
+    import tiny
+
+    run_shape(config, tiny.random_weights(config, seed=5, dtype=torch.bfloat16), "bfloat16")
+
+
+def run_shape(CONFIG, weights, dtype):
     from pulsarlm_b200 import models  # noqa: F401
     from pulsarlm_b200.cache.manager import CacheManager
     from pulsarlm_b200.config.registry import read_model_config
