@@ -9,7 +9,7 @@
 // rows of m16n8k16 MMAs: S = Q K^T, online softmax in fp32 (base 2, the scale
 // folded into the exponent), O += P V with P rounded to bf16. Warps are merged
 // through shared memory. The splits of one (kv head, token) are merged in one of two
-// ways. Up to eight splits form a thread-block cluster: the (head, dim) outputs are
+// ways. Up to sixteen splits form a thread-block cluster: the (head, dim) outputs are
 // dealt out to the ranks in contiguous runs, every rank sends its unnormalised
 // partial sums for a run to the owner's shared memory (st.async: stores that count
 // their bytes on the owner's barrier) and its (m, l) to everyone, and each owner
@@ -22,6 +22,8 @@
 // combine kernels, pulsarlm-core/src/kernels/paged_attention.cu:432-584.
 #include "cluster_helpers.cuh"
 #include "mma_helpers.cuh"
+
+PL_API int pl_attention_decode_resident_clusters(int head_dim, int group, int n_splits);
 
 namespace {
 
@@ -435,24 +437,40 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
 constexpr int kWarps = 4;
 constexpr int kStages = 3;
 
-constexpr int kClusterSplitsMax = 8;  // the portable cluster size
+constexpr int kClusterSplitsMax = 16;  // the largest cluster the part takes (above 8: opted into per kernel)
 
 template <int HD>
 int launch_decode(const DecodeParams& params, int n_tokens, int n_kv_heads, bool allow_cluster, cudaStream_t stream) {
     constexpr int rings = kWarps * kStages * 2 * kTile * HD * 2;
     static_assert(rings >= kWarps * 16 * (HD + 2) * 4, "the merge buffers must fit in the rings");
     constexpr int most_merge = merge_bytes(16 * (HD / 4), kClusterSplitsMax) + 1024;
-    static bool configured = false;
+    static bool configured = false, big_clusters = false;
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(attention_decode_kernel<HD, kWarps, kStages>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, rings + most_merge);
         if (err != cudaSuccess) {
             return pl_fail(3, "attention_decode: cannot set shared memory size: %s", cudaGetErrorString(err));
         }
+        // clusters of more than eight CTAs (if the device refuses, such split counts go through scratch)
+        big_clusters = cudaFuncSetAttribute(attention_decode_kernel<HD, kWarps, kStages>,
+                                            cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        cudaGetLastError();
         configured = true;
     }
     DecodeParams p = params;
-    p.cluster = allow_cluster && p.n_splits >= 2 && p.n_splits <= kClusterSplitsMax;
+    p.cluster = allow_cluster && p.n_splits >= 2 && p.n_splits <= (big_clusters ? kClusterSplitsMax : 8);
+    if (p.cluster && p.n_splits > 8) {
+        // a cluster this large has to find its SMs within one GPC: ask once whether any fits
+        static int room[17][kClusterSplitsMax + 1] = {};
+        int& known = room[p.group][p.n_splits];
+        if (known == 0) {
+            known = pl_attention_decode_resident_clusters(HD, p.group, p.n_splits) > 0 ? 1 : -1;
+        }
+        p.cluster = known > 0;
+    }
+    if (!p.cluster && p.n_splits > 1 && p.part_o == nullptr) {
+        return pl_fail(2, "attention_decode: %d splits need scratch memory", p.n_splits);
+    }
     const dim3 grid(p.n_splits, n_kv_heads, n_tokens);
     if (p.cluster) {
         cudaLaunchConfig_t config = {};
@@ -517,12 +535,16 @@ PL_API int pl_attention_decode_resident_clusters(int head_dim, int group, int n_
         constexpr int rings = kWarps * kStages * 2 * kTile * 64 * 2;
         cudaFuncSetAttribute(attention_decode_kernel<64, kWarps, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              rings + merge_bytes(16 * 16, kClusterSplitsMax) + 1024);
+        cudaFuncSetAttribute(attention_decode_kernel<64, kWarps, kStages>,
+                             cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         config.dynamicSmemBytes = rings + merge_bytes(group * 16, n_splits);
         err = cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel<64, kWarps, kStages>, &config);
     } else {
         constexpr int rings = kWarps * kStages * 2 * kTile * 128 * 2;
         cudaFuncSetAttribute(attention_decode_kernel<128, kWarps, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              rings + merge_bytes(16 * 32, kClusterSplitsMax) + 1024);
+        cudaFuncSetAttribute(attention_decode_kernel<128, kWarps, kStages>,
+                             cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         config.dynamicSmemBytes = rings + merge_bytes(group * 32, n_splits);
         err = cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel<128, kWarps, kStages>, &config);
     }
@@ -555,7 +577,7 @@ int run_attention_decode(bool allow_cluster, const void* q, int64_t q_row_stride
                head_dim, group, page_size);
     PL_REQUIRE(n_splits >= 1 && n_splits <= 65535 && n_kv_heads <= 65535 && n_tokens <= 65535,
                "attention_decode: grid too large (splits=%d kv_heads=%d tokens=%d)", n_splits, n_kv_heads, n_tokens);
-    PL_REQUIRE((n_splits <= kClusterSplitsMax && allow_cluster) || n_splits == 1 || scratch != nullptr,
+    PL_REQUIRE((n_splits <= 8 && allow_cluster) || n_splits == 1 || scratch != nullptr,
                "attention_decode: %d splits need scratch memory", n_splits);
     PL_REQUIRE(q_row_stride % 2 == 0 && (reinterpret_cast<uintptr_t>(q) & 3) == 0,
                "attention_decode: q must be 4-byte aligned with an even row stride");

@@ -37,7 +37,7 @@ _CLUSTER_ROOM: dict[tuple, int] = {}
 
 def decode_splits(n_ctas: int, max_context: int, device: torch.device, head_dim: int = 128, group: int = 4) -> int:
     """Ways to split each request's keys so that about two CTAs per SM run: as many
-    as fit, but no split shorter than eight 16-key tiles. Up to eight splits are the
+    as fit, but no split shorter than eight 16-key tiles. Up to sixteen splits are the
     ranks of a thread-block cluster; their number is then lowered until all clusters
     of the launch are resident at once (a launch in two waves takes twice as long)."""
     if device not in _SM_COUNT:
@@ -47,7 +47,7 @@ def decode_splits(n_ctas: int, max_context: int, device: torch.device, head_dim:
         return 1
     tiles = -(-max_context // 16)
     splits = max(1, min(target // n_ctas, tiles // 8))
-    while 2 <= splits <= 8:
+    while 2 <= splits <= 16:
         key = (device, head_dim, group, splits)
         if key not in _CLUSTER_ROOM:
             _CLUSTER_ROOM[key] = ops.library().pl_attention_decode_resident_clusters(head_dim, group, splits)

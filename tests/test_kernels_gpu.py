@@ -342,7 +342,7 @@ def test_attention_simt(ops, dtype, nh, nkv, hd, page, window):
 
 @pytest.mark.parametrize("nh,nkv,hd,page", [(8, 2, 64, 16), (8, 1, 128, 16), (32, 8, 128, 16), (16, 1, 64, 32),
                                             (6, 2, 128, 64), (4, 4, 64, 16)])
-@pytest.mark.parametrize("splits", [1, 2, 5, 8, 12])
+@pytest.mark.parametrize("splits", [1, 2, 5, 8, 12, 16, 20])
 @pytest.mark.parametrize("window", [None, 100])
 def test_attention_decode(ops, nh, nkv, hd, page, splits, window):
     dtype = torch.bfloat16
