@@ -26,6 +26,11 @@
 // next S. With one head per CTA, S is double-buffered instead, so that S of tile j+1
 // is computed while the softmax of tile j runs.
 //
+// Few query tiles over many keys (a short portion of a long prompt) would leave most
+// SMs idle: the launch may then split every tile's keys `n_splits` ways (grid z). Each
+// CTA writes its unnormalised fp32 output and each row's (exponent base, sum) to
+// scratch, and a second kernel merges the splits in split order.
+//
 // Every mbarrier wait is bounded; on a timeout the CTA raises bit 8 of the status
 // word, stops, lets loads in flight land, frees its tensor memory and returns.
 //
@@ -33,6 +38,8 @@
 // manager's layout [page][K,V][kv head][slot][dim]; other shapes go to the mma.sync
 // kernel in attention_prefill.cu. The reference's counterpart: attn_prefill_tc_kernel,
 // pulsarlm-core/inc/pulsarlm/kernels/paged_prefill.cuh:58-328.
+#include <type_traits>
+
 #include "tcgen05_helpers.cuh"
 
 namespace {
@@ -58,6 +65,10 @@ struct TcPrefillParams {
     int window;
     float scale_log2;
     int32_t* status;
+    int n_heads;
+    int n_splits;     // > 1: partial results go to scratch [token][head][split]
+    float* part_o;    // ... [head_dim]: unnormalised output
+    float2* part_ml;  // ... (base of the exponents (log2), sum)
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -121,7 +132,22 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const int head0 = blockIdx.x * HEADS, kv_head = head0 / p.group;
     const int last_key = pos0 + n_rows - 1;
     const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-    const int j0 = first_key / kKeys, n_tiles = last_key / kKeys - j0 + 1;
+    // This CTA's share of the tile's 64-key tiles (all of them without splits).
+    const int all_tiles = last_key / kKeys - first_key / kKeys + 1;
+    const int per_split = (all_tiles + p.n_splits - 1) / p.n_splits;
+    const int j_begin = min(all_tiles, static_cast<int>(blockIdx.z) * per_split);
+    const int j0 = first_key / kKeys + j_begin, n_tiles = min(all_tiles, j_begin + per_split) - j_begin;
+    if (n_tiles == 0) {
+        // Nothing for this split: its rows say so (the merge skips a split whose base is -inf).
+        for (int i = threadIdx.x; i < HEADS * kRows; i += kThreadsTc) {
+            const int hs = i / kRows, r = i % kRows;
+            if (r < n_rows) {
+                p.part_ml[(static_cast<int64_t>(row0 + r) * p.n_heads + head0 + hs) * p.n_splits + blockIdx.z] =
+                    make_float2(-INFINITY, 0.0f);
+            }
+        }
+        return;
+    }
 
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
@@ -514,7 +540,26 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             ok = mbar_wait(&pv_done[hs], (n_tiles - 1) & 1, &abort_flag);
             tcgen05_fence_after();
         }
-        if (ok) {
+        if (ok && p.n_splits > 1) {
+            // One split of several: the unnormalised row, and what the merge needs to weigh it.
+            const int64_t slot = (static_cast<int64_t>(row0 + r) * p.n_heads + head0 + hs) * p.n_splits + blockIdx.z;
+            float* dst = p.part_o + slot * HD + part * kMyDims;
+            if (part == 0 && r < n_rows) {
+                p.part_ml[slot] = make_float2(m, l);
+            }
+#pragma unroll
+            for (int g = 0; g < kMyDims / 32; ++g) {
+                uint32_t v[32];
+                tcgen05_ld32_nowait(my_o + 32 * g, v);  // all lanes take part
+                tcgen05_wait_ld();
+                if (r < n_rows) {
+#pragma unroll
+                    for (int d = 0; d < 32; d += 4) {
+                        *reinterpret_cast<uint4*>(dst + 32 * g + d) = make_uint4(v[d], v[d + 1], v[d + 2], v[d + 3]);
+                    }
+                }
+            }
+        } else if (ok) {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             __nv_bfloat16* dst = p.out + (row0 + r) * p.out_row_stride + static_cast<int64_t>(head0 + hs) * HD +
                 part * kMyDims;
@@ -561,6 +606,64 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     }
 }
 
+// Merges the splits of one launch: one warp per (query row, head) adds the splits'
+// rows in split order, each weighed by 2^(its base - the largest base), and divides by
+// the sum of the equally weighed row sums. Grid (heads, tiles, 16 groups of 8 rows).
+template <int HD>
+__global__ void __launch_bounds__(256) attention_prefill_merge_kernel(const TcPrefillParams p) {
+    constexpr int kPer = HD / 32;  // dims per lane
+    using Vec = typename std::conditional<kPer == 4, float4, float2>::type;
+    const int4 tile = p.tiles[blockIdx.y];
+    const int head = blockIdx.x, lane = threadIdx.x & 31;
+    const int r = blockIdx.z * 8 + (threadIdx.x >> 5);
+    if (r >= tile.y) {
+        return;
+    }
+    const int64_t base = (static_cast<int64_t>(tile.x + r) * p.n_heads + head) * p.n_splits;
+    const float2 ml = lane < p.n_splits ? p.part_ml[base + lane] : make_float2(-INFINITY, 0.0f);
+    float top = ml.x;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, d));
+    }
+    const float weight = ml.x > -INFINITY ? exp2f(ml.x - top) : 0.0f;
+    float acc[kPer] = {};
+    float total = 0.0f;
+    const float* src = p.part_o + base * HD + lane * kPer;
+    for (int s0 = 0; s0 < p.n_splits; s0 += 4) {
+        // four splits' rows in flight at a time; a split without keys for this row wrote none
+        float w[4];
+        Vec v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            w[i] = __shfl_sync(0xffffffffu, weight, (s0 + i) & 31);
+            w[i] = s0 + i < p.n_splits ? w[i] : 0.0f;
+            if (w[i] > 0.0f) {
+                v[i] = *reinterpret_cast<const Vec*>(src + static_cast<int64_t>(s0 + i) * HD);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float l = __shfl_sync(0xffffffffu, ml.y, (s0 + i) & 31);
+            if (w[i] > 0.0f) {
+                total += w[i] * l;
+                acc[0] += w[i] * v[i].x;
+                acc[1] += w[i] * v[i].y;
+                if constexpr (kPer == 4) {
+                    acc[2] += w[i] * v[i].z;
+                    acc[3] += w[i] * v[i].w;
+                }
+            }
+        }
+    }
+    const float inv = total > 0.0f ? 1.0f / total : 0.0f;
+    __nv_bfloat16* dst = p.out + (tile.x + r) * p.out_row_stride + static_cast<int64_t>(head) * HD + lane * kPer;
+#pragma unroll
+    for (int i = 0; i < kPer; i += 2) {
+        *reinterpret_cast<__nv_bfloat162*>(dst + i) = __floats2bfloat162_rn(acc[i] * inv, acc[i + 1] * inv);
+    }
+}
+
 template <int HD, int HEADS>
 int launch_tc_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcPrefillParams& p,
                       int n_tiles, int n_heads, cudaStream_t stream) {
@@ -575,9 +678,13 @@ int launch_tc_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
         }
         configured = true;
     }
-    attention_prefill_tcgen05_kernel<HD, HEADS><<<dim3(n_heads / HEADS, n_tiles), kThreadsTc, smem, stream>>>(mq, mk,
-                                                                                                              mv, p);
+    attention_prefill_tcgen05_kernel<HD, HEADS>
+        <<<dim3(n_heads / HEADS, n_tiles, p.n_splits), kThreadsTc, smem, stream>>>(mq, mk, mv, p);
     PL_CHECK_LAUNCH("attention_prefill_tcgen05");
+    if (p.n_splits > 1) {
+        attention_prefill_merge_kernel<HD><<<dim3(n_heads, n_tiles, kRows / 8), 256, 0, stream>>>(p);
+        PL_CHECK_LAUNCH("attention_prefill_merge");
+    }
     return 0;
 }
 
@@ -591,15 +698,22 @@ PL_API int pl_attention_prefill_tcgen05_supports(int head_dim, int page_size, in
         page_stride == 2 * static_cast<int64_t>(n_kv_heads) * head_stride && q_row_stride % 8 == 0;
 }
 
+// Scratch floats that `n_splits` splits of the keys need for a step of `n_tokens` tokens.
+PL_API int64_t pl_attention_prefill_scratch_floats(int n_tokens, int n_heads, int head_dim, int n_splits) {
+    return n_splits <= 1 ? 0 : static_cast<int64_t>(n_tokens) * n_heads * n_splits * (head_dim + 2);
+}
+
 // As pl_attention_prefill (tiles of up to 128 rows), on tcgen05. The pools must be
 // the two halves of one [pages][2][kv heads][page][head_dim] tensor: v_pool is
-// k_pool + kv_heads * page * head_dim elements.
+// k_pool + kv_heads * page * head_dim elements. With n_splits > 1 (at most 32) every
+// tile's keys are shared out over that many CTAs and merged by a second kernel
+// through `scratch` (pl_attention_prefill_scratch_floats floats, 16-byte aligned).
 PL_API int pl_attention_prefill_tcgen05(const void* q, int64_t q_row_stride, int n_tokens, const void* k_pool,
                                         const void* v_pool, int64_t page_stride, int64_t head_stride, int page_size,
                                         int n_pages, const int32_t* table, int table_width, const int32_t* tiles,
                                         int n_tiles, void* out, int64_t out_row_stride, int n_heads, int n_kv_heads,
-                                        int head_dim, int window, float scale, int32_t* status,
-                                        cudaStream_t stream) {
+                                        int head_dim, int window, float scale, int n_splits, float* scratch,
+                                        int32_t* status, cudaStream_t stream) {
     PL_REQUIRE(n_tiles >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_tokens > 0,
                "attention_prefill_tcgen05: bad sizes tiles=%d heads=%d kv_heads=%d tokens=%d", n_tiles, n_heads,
                n_kv_heads, n_tokens);
@@ -615,6 +729,9 @@ PL_API int pl_attention_prefill_tcgen05(const void* q, int64_t q_row_stride, int
                    (reinterpret_cast<uintptr_t>(tiles) & 15) == 0,
                "attention_prefill_tcgen05: q, the pools, out and the tile list must be 16-byte aligned");
     PL_REQUIRE(n_tiles <= 65535, "attention_prefill_tcgen05: too many tiles in one launch (%d)", n_tiles);
+    PL_REQUIRE(n_splits >= 1 && n_splits <= 32, "attention_prefill_tcgen05: 1 to 32 splits, not %d", n_splits);
+    PL_REQUIRE(n_splits == 1 || (scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0),
+               "attention_prefill_tcgen05: %d splits need 16-byte aligned scratch memory", n_splits);
     PL_REQUIRE(scale > 0.0f, "attention_prefill_tcgen05: the scale must be positive (%g)", static_cast<double>(scale));
     if (n_tiles == 0) {
         return 0;
@@ -648,6 +765,12 @@ PL_API int pl_attention_prefill_tcgen05(const void* q, int64_t q_row_stride, int
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = status;
+    p.n_heads = n_heads;
+    p.n_splits = n_splits;
+    p.part_o = scratch;
+    p.part_ml = n_splits > 1
+        ? reinterpret_cast<float2*>(scratch + static_cast<int64_t>(n_tokens) * n_heads * n_splits * head_dim)
+        : nullptr;
     const bool pairs = p.group % 2 == 0;  // two heads of one kv head per CTA
     if (head_dim == 64) {
         return pairs ? launch_tc_prefill<64, 2>(mq, mk, mv, p, n_tiles, n_heads, stream)

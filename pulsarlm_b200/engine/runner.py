@@ -181,7 +181,9 @@ class ModelRunner:
             n_decode=n_decode,
             host_query_lens=[len(entries[i].tokens) for i in order],
             host_context_lens=[new_lens[i] for i in order],
-            extras={"prefill_tiles": dev[5] if tiles else None},
+            extras={"prefill_tiles": dev[5] if tiles else None,
+                    # the most keys any tile reads (the attention part sizes its launch by it)
+                    "prefill_max_keys": max((t[2] + t[1] for t in tiles), default=0)},
         )
         if decay is not None:
             n_groups = len(self.cache.groups)

@@ -72,9 +72,12 @@ def bench_gemm(shapes) -> None:
         print(line, flush=True)
 
 
-def bench_attention_prefill(tokens_list, n_heads, n_kv, head_dim, page) -> None:
+def bench_attention_prefill(tokens_list, n_heads, n_kv, head_dim, page, prior=0, force_splits=0) -> None:
+    """A portion of `tokens` queries that follows `prior` keys already in the cache."""
+    from ..parts.attention import prefill_splits
+
     for tokens in tokens_list:
-        n_pages = tokens // page + 4
+        n_pages = (tokens + prior) // page + 4
         pool = (torch.randn(n_pages, 2, n_kv, page, head_dim, device="cuda") * 0.5).to(torch.bfloat16)
         kp, vp = pool[:, 0], pool[:, 1]
         table = torch.randperm(n_pages, device="cuda").to(torch.int32).view(1, -1)
@@ -82,13 +85,23 @@ def bench_attention_prefill(tokens_list, n_heads, n_kv, head_dim, page) -> None:
         q = qkv[:, : n_heads * head_dim].view(tokens, n_heads, head_dim)
         out = torch.empty(tokens, n_heads, head_dim, device="cuda", dtype=torch.bfloat16)
         rows = ops.attention_prefill_tile_rows()
-        tiles = sorted(((r, min(rows, tokens - r), r, 0) for r in range(0, tokens, rows)), key=lambda t: -(t[1] + t[2]))
+        tiles = sorted(((r, min(rows, tokens - r), prior + r, 0) for r in range(0, tokens, rows)),
+                       key=lambda t: -(t[1] + t[2]))
         tiles = torch.tensor(tiles, dtype=torch.int32, device="cuda")
         scale = 1 / math.sqrt(head_dim)
-        flops = 4.0 * n_heads * head_dim * tokens * (tokens + 1) / 2
-        for name, kernel in (("tcgen05", ops.attention_prefill_tcgen05), ("mma.sync", ops.attention_prefill)):
+        flops = 4.0 * n_heads * head_dim * (tokens * (tokens + 1) / 2 + tokens * prior)
+        # the engine's choice: few tiles over many keys are split over the keys
+        ctas = tiles.shape[0] * (n_heads // 2 if (n_heads // n_kv) % 2 == 0 else n_heads)
+        splits = force_splits or prefill_splits(ctas, tokens + prior, tokens, n_heads, head_dim, q.device)
+        scratch = torch.empty(max(1, ops.attention_prefill_scratch_floats(tokens, n_heads, head_dim, splits)),
+                              device="cuda")
+
+        def tcgen05(*args):
+            ops.attention_prefill_tcgen05(*args, None, splits, scratch)
+
+        for name, kernel in ((f"tcgen05 splits={splits}", tcgen05), ("mma.sync", ops.attention_prefill)):
             us = graph_time_us(lambda: kernel(q, kp, vp, table, tiles, out, page, None, scale), reps=4)
-            print(f"attention_prefill {name} tokens={tokens} heads={n_heads}/{n_kv} head_dim={head_dim}: {us:.1f} us, "
+            print(f"attention_prefill {name} tokens={tokens} prior={prior} heads={n_heads}/{n_kv} head_dim={head_dim}: {us:.1f} us, "
                   f"{flops / us / 1e6:.0f} TFLOP/s (causal flops)", flush=True)
 
 
@@ -204,6 +217,9 @@ def main() -> None:
     parser.add_argument("what", choices=["gemm", "attention_prefill", "attention_decode", "decode_timeline"])
     parser.add_argument("--shapes", nargs="*", default=None, help="T,N,K triples for gemm")
     parser.add_argument("--tokens", type=int, nargs="*", default=[2048, 8192])
+    parser.add_argument("--prior", type=int, default=0, help="keys in the cache before an attention_prefill portion")
+    parser.add_argument("--splits", type=int, default=0, help="attention_prefill: split the keys this many ways "
+                        "(default: as the engine would)")
     parser.add_argument("--batch", type=int, nargs="*", default=[1, 8, 64])
     parser.add_argument("--context", type=int, nargs="*", default=[2048, 4096])
     parser.add_argument("--heads", type=int, default=32)
@@ -220,7 +236,8 @@ def main() -> None:
         decode_timeline(args.layers, args.batch[0] if len(args.batch) == 1 else 8,
                         args.context[0] if len(args.context) == 1 else 2048, args.page_size)
     elif args.what == "attention_prefill":
-        bench_attention_prefill(args.tokens, args.heads, args.kv_heads, args.head_dim, args.page_size)
+        bench_attention_prefill(args.tokens, args.heads, args.kv_heads, args.head_dim, args.page_size, args.prior,
+                                args.splits)
     else:
         bench_attention_decode(args.batch, args.context, args.heads, args.kv_heads, args.head_dim, args.page_size)
 

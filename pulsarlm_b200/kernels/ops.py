@@ -25,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 10
+ABI_VERSION = 11
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -51,7 +51,7 @@ _SIGNATURES = {
                              _I32, _I32, _I32, _I32, _F32, _PTR, _PTR],
     "pl_attention_prefill_supports": [_I32, _I32, _I32],
     "pl_attention_prefill_tcgen05": [_PTR, _I64, _I32, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _I32,
-                                     _PTR, _I64, _I32, _I32, _I32, _I32, _F32, _PTR, _PTR],
+                                     _PTR, _I64, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR, _PTR],
     "pl_attention_prefill_tcgen05_supports": [_I32, _I32, _I32, _I64, _I64, _I64, _I32],
     "pl_attention_prefill_tile_rows": [],
     "pl_gemm_bf16_pair_supports": [_I32, _I32, _I32, _I64, _I64],
@@ -86,6 +86,8 @@ def library() -> ctypes.CDLL:
         lib.pl_device_arch.restype = _I32
         lib.pl_attention_decode_scratch_floats.argtypes = [_I32, _I32, _I32, _I32]
         lib.pl_attention_decode_scratch_floats.restype = _I64
+        lib.pl_attention_prefill_scratch_floats.argtypes = [_I32, _I32, _I32, _I32]
+        lib.pl_attention_prefill_scratch_floats.restype = _I64
         lib.pl_set_overlap.argtypes = [_I32]
         lib.pl_set_overlap.restype = _I32
         if os.environ.get("PULSARLM_B200_OVERLAP", "1") == "0":
@@ -385,11 +387,24 @@ def attention_prefill_tcgen05_supports(q: torch.Tensor, k_pool: torch.Tensor, pa
         DTYPE_CODE.get(q.dtype, -1)))
 
 
+PREFILL_SPLITS_MAX = 32
+
+
+def attention_prefill_scratch_floats(n_tokens: int, n_heads: int, head_dim: int, n_splits: int) -> int:
+    return int(library().pl_attention_prefill_scratch_floats(n_tokens, n_heads, head_dim, n_splits))
+
+
 def attention_prefill_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,
                               tiles: torch.Tensor, out: torch.Tensor, page_size: int, window: int | None,
-                              scale: float, status: torch.Tensor | None = None) -> None:
-    """As attention_prefill, on the tcgen05 tensor cores."""
-    _dev(q, k_pool, v_pool, table, tiles, out, status)
+                              scale: float, status: torch.Tensor | None = None, n_splits: int = 1,
+                              scratch: torch.Tensor | None = None) -> None:
+    """As attention_prefill, on the tcgen05 tensor cores. With n_splits > 1 every tile's
+    keys are shared out over that many CTAs and merged through `scratch` (float32,
+    attention_prefill_scratch_floats elements): for few tiles over many keys."""
+    _dev(q, k_pool, v_pool, table, tiles, out, status, scratch)
+    if n_splits > 1:
+        need = attention_prefill_scratch_floats(q.shape[0], q.shape[1], q.shape[2], n_splits)
+        assert scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= need
     tokens, n_heads, head_dim = q.shape
     n_pages, n_kv = k_pool.shape[0], k_pool.shape[1]
     assert q.dtype == torch.bfloat16 == out.dtype == k_pool.dtype == v_pool.dtype
@@ -401,7 +416,8 @@ def attention_prefill_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
     assert tiles.dtype == torch.int32 and tiles.dim() == 2 and tiles.shape[1] == 4 and tiles.is_contiguous()
     _call("pl_attention_prefill_tcgen05", _p(q), q.stride(0), tokens, _p(k_pool), _p(v_pool), k_pool.stride(0),
           k_pool.stride(1), page_size, n_pages, _p(table), table.shape[1], _p(tiles), tiles.shape[0], _p(out),
-          out.stride(0), n_heads, n_kv, head_dim, int(window or 0), float(scale), _p(status), _stream())
+          out.stride(0), n_heads, n_kv, head_dim, int(window or 0), float(scale), int(n_splits), _p(scratch),
+          _p(status), _stream())
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor | None,

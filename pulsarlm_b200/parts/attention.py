@@ -58,6 +58,33 @@ def decode_splits(n_ctas: int, max_context: int, device: torch.device, head_dim:
     return splits
 
 
+def prefill_splits(n_ctas: int, max_keys: int, n_tokens: int, n_heads: int, head_dim: int,
+                   device: torch.device) -> int:
+    """Ways to split every prompt tile's keys when the tiles alone (`n_ctas` CTAs, one per
+    SM) leave SMs idle: a short portion of a long prompt. Picks the count with the least
+    estimated time: rounds of CTAs, each a fixed start plus its share of the keys, plus
+    what the partial rows cost to write and merge; the constants are measurements of the
+    kernel at head size 128 (17 ns per key and CTA, 6 us per round, 4 us and the
+    scratch traffic at 4 TB/s for the merge). Splits only if that saves a tenth."""
+    if device not in _SM_COUNT:
+        _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    sms = _SM_COUNT[device]
+    most = min(max_keys // 256, 16, ops.PREFILL_SPLITS_MAX)
+    if n_ctas <= 0 or n_ctas >= sms or most < 2:
+        return 1
+    per_key = 17.3e-9 * head_dim / 128
+
+    def cost(splits: int) -> float:
+        rounds = -(-n_ctas * splits // sms)
+        seconds = rounds * (6e-6 + max_keys / splits * per_key)
+        if splits > 1:
+            seconds += 4e-6 + n_tokens * n_heads * splits * (head_dim + 2) * 8 / 4e12
+        return seconds
+
+    best = min(range(1, most + 1), key=cost)
+    return best if cost(best) < 0.9 * cost(1) else 1
+
+
 @register_part("mixer", "attention")
 class Attention(Part):
     """q, k, v projections (bias-free), position encoding on q and k, causal
@@ -181,9 +208,23 @@ class Attention(Part):
             # The tile list covers exactly the tokens after the leading single tokens.
             if self._prefill_tcgen05 is None:
                 self._prefill_tcgen05 = ops.attention_prefill_tcgen05_supports(q, cache.k_pool, cache.page_size)
-            kernel = ops.attention_prefill_tcgen05 if self._prefill_tcgen05 else ops.attention_prefill
-            kernel(q, cache.k_pool, cache.v_pool, table, tiles, out, cache.page_size, self.window, self.scale,
-                   batch.status)
+            if self._prefill_tcgen05:
+                # two heads of a kv head share a CTA when the group is even
+                ctas = tiles.shape[0] * (self.n_heads // 2 if (self.n_heads // self.n_kv) % 2 == 0 else self.n_heads)
+                max_keys = int(batch.extras.get("prefill_max_keys") or 0)
+                if self.window:
+                    max_keys = min(max_keys, self.window + ops.attention_prefill_tile_rows())
+                splits = prefill_splits(ctas, max_keys, tokens - n_decode, self.n_heads, self.head_dim, q.device)
+                scratch = None
+                if splits > 1:
+                    scratch = torch.empty(ops.attention_prefill_scratch_floats(tokens, self.n_heads, self.head_dim,
+                                                                               splits),
+                                          dtype=torch.float32, device=q.device)
+                ops.attention_prefill_tcgen05(q, cache.k_pool, cache.v_pool, table, tiles, out, cache.page_size,
+                                              self.window, self.scale, batch.status, splits, scratch)
+            else:
+                ops.attention_prefill(q, cache.k_pool, cache.v_pool, table, tiles, out, cache.page_size,
+                                      self.window, self.scale, batch.status)
         elif n_decode < tokens:
             ops.attention_simt(q[n_decode:], cache.k_pool, cache.v_pool, table, batch.pos[n_decode:],
                                batch.entry[n_decode:], out[n_decode:], cache.page_size, self.window, self.scale,

@@ -538,6 +538,82 @@ def test_prefill_finds_one_far_key_and_respects_causality(ops, kernel, far_key):
     assert rel(out, want) < 1e-2
 
 
+def split_scratch(ops, q, splits):
+    """Scratch for `splits` splits of the keys, filled with NaN: what a split leaves
+    unwritten must never reach the output."""
+    n = ops.attention_prefill_scratch_floats(q.shape[0], q.shape[1], q.shape[2], splits)
+    return torch.full((max(n, 1),), float("nan"), device=DEV)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page", [(8, 2, 64, 16), (4, 1, 128, 16), (6, 6, 64, 32), (3, 3, 128, 64)])
+@pytest.mark.parametrize("splits,window", [(2, None), (3, 300), (7, None), (32, 300)])
+def test_attention_prefill_with_split_keys(ops, nh, nkv, hd, page, splits, window):
+    """Portions after long and short histories in one launch: tiles with many 64-key
+    tiles, with fewer than there are splits (some splits stay empty), and a whole
+    prompt from position 0 (early rows see nothing in the later splits)."""
+    dtype = torch.bfloat16
+    lengths = [1500, 900, 140, 40]
+    portions = [(0, 200, 1300, 0), (200, 2, 898, 1), (202, 140, 0, 2), (342, 3, 37, 3)]
+    pages_each = -(-max(lengths) // page)
+    n_pages = len(lengths) * pages_each + 4
+    table = scattered_tables(len(lengths), pages_each, n_pages, seed=hd + page + splits)
+    kp, vp = make_pools(n_pages, nkv, page, hd, dtype, fill=1.0)
+    pos, entry = [], []
+    for row0, n, pos0, e in portions:
+        pos += list(range(pos0, pos0 + n))
+        entry += [e] * n
+    q = torch.randn(len(pos), nh, hd, device=DEV).to(dtype)
+    scale = 1 / math.sqrt(hd)
+    tiles = make_tiles(portions, 128)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    whole = torch.full_like(q, float("nan"))
+    ops.attention_prefill_tcgen05(q, kp, vp, table.to(DEV), tiles, whole, page, window, scale, status)
+    out = torch.full_like(q, float("nan"))
+    ops.attention_prefill_tcgen05(q, kp, vp, table.to(DEV), tiles, out, page, window, scale, status, splits,
+                                  split_scratch(ops, q, splits))
+    want = reference_attention(q, kp, vp, table, pos, entry, page, window, scale)
+    assert int(status) == 0 and rel(out, want) < 1e-2
+    assert rel(out, whole.float()) <= 2.0 ** -7  # the splits change the rounding (one bfloat16 step) and nothing else
+
+
+@pytest.mark.parametrize("splits", [2, 5])
+@pytest.mark.parametrize("far_key", [0, 63, 64, 575, 576, 1023, 1100])
+def test_split_prefill_finds_one_far_key_and_respects_causality(ops, splits, far_key):
+    """As above with the keys split: the loud key lies in one split only, and the
+    merge must let it dominate (and a split must not read past the diagonal)."""
+    dtype = torch.bfloat16
+    nh, nkv, hd, page = 2, 1, 64, 16
+    n_ctx, n_q = 1204, 140
+    pages_each = -(-n_ctx // page)
+    table = scattered_tables(1, pages_each, pages_each + 3, seed=9)
+    kp, vp = make_pools(pages_each + 3, nkv, page, hd, dtype, fill=0.3)
+    direction = torch.randn(hd, device=DEV)
+    q = (direction[None, None, :] + 0.05 * torch.randn(n_q, nh, hd, device=DEV)).to(dtype)
+    page_id = int(table[0, far_key // page])
+    kp[page_id, 0, far_key % page] = (direction * 12).to(dtype)
+    vp[page_id, 0, far_key % page] = 5.0
+    pos0 = n_ctx - n_q
+    out = torch.empty_like(q)
+    ops.attention_prefill_tcgen05(q, kp, vp, table.to(DEV), make_tiles([(0, n_q, pos0, 0)], 128), out, page, None,
+                                  1.0, None, splits, split_scratch(ops, q, splits))
+    pos = list(range(pos0, n_ctx))
+    want = reference_attention(q, kp, vp, table, pos, [0] * n_q, page, None, 1.0)
+    sees = torch.tensor([p >= far_key for p in pos])
+    assert bool((want[sees].amin(dim=(1, 2)) > 4.0).all()) and (sees.all() or bool((want[~sees].amax(dim=(1, 2)) < 3.0).all()))
+    assert rel(out, want) < 1e-2
+
+
+def test_split_prefill_refuses_what_it_cannot_do(ops):
+    q = torch.randn(4, 2, 64, device=DEV).to(torch.bfloat16)
+    kp, vp = make_pools(2, 1, 16, 64, torch.bfloat16)
+    table = torch.zeros(1, 2, dtype=torch.int32, device=DEV)
+    tiles = make_tiles([(0, 4, 0, 0)], 128)
+    with pytest.raises(ops.KernelError) as error:
+        ops.attention_prefill_tcgen05(q, kp, vp, table, tiles, torch.empty_like(q), 16, None, 1.0, None, 33,
+                                      split_scratch(ops, q, 33))
+    assert "1 to 32 splits" in str(error.value)
+
+
 @pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
 def test_prefill_window_edges_and_released_pages(ops, kernel):
     dtype = torch.bfloat16

@@ -101,3 +101,41 @@ def run_shape(CONFIG, weights, dtype):
     for (request, position), got in rows.items():
         err = plain_llama.max_relative_error(got.cpu(), ref[request][position])
         assert err < TOLERANCE[dtype], (request, position, err)
+
+
+@pytest.mark.parametrize("config", [CONFIG, CONFIG_13B], ids=["llama-3.1-8b", "llama-2-13b"])
+def test_a_short_portion_after_a_long_history(config):
+    """1,100 tokens of a prompt in one step, then 100 beside another request's single
+    token: one tile of queries over 1,200 keys, which the attention part splits over the
+    keys (checked below), in both arrangements of the kernel (two heads of a kv head per
+    CTA; one head per CTA). A small vocabulary keeps the plain implementation quick."""
+    import tiny
+    from pulsarlm_b200 import models  # noqa: F401
+    from pulsarlm_b200.cache.manager import CacheManager
+    from pulsarlm_b200.config.registry import read_model_config
+    from pulsarlm_b200.engine.runner import ModelRunner, StepEntry
+    from pulsarlm_b200.models.model import Model
+    from pulsarlm_b200.parts.attention import prefill_splits
+    from pulsarlm_b200.weights.loader import check_tensors
+
+    config = dict(config, vocab_size=2048)
+    weights = tiny.random_weights(config, seed=7, dtype=torch.bfloat16)
+    device = torch.device("cuda:0")
+    arch, cfg = read_model_config(config)
+    model = Model(arch.describe(cfg), torch.bfloat16, device)
+    model.load(check_tensors("test", model.tensor_needs(), weights, torch.bfloat16, device))
+    runner = ModelRunner(model, CacheManager(model.cache_needs(), 16, 96, 2, torch.bfloat16, device))
+    heads, kv_heads = config["num_attention_heads"], config["num_key_value_heads"]
+    ctas = heads // 2 if (heads // kv_heads) % 2 == 0 else heads
+    assert prefill_splits(ctas, 1200, 100, heads, plain_llama.head_dim_of(config), device) > 1
+
+    gen = torch.Generator().manual_seed(2)
+    a = torch.randint(0, 2048, (1200,), generator=gen).tolist()
+    b = torch.randint(0, 2048, (31,), generator=gen).tolist()
+    runner.step([StepEntry("a", a[:1100], []), StepEntry("b", b[:30], [])])
+    out = runner.step([StepEntry("a", a[1100:], [0, 63, 99]), StepEntry("b", b[30:], [0])])
+    runner.check_status()
+    ref_a = plain_llama.forward(config, weights, a, dtype=torch.float32)
+    ref_b = plain_llama.forward(config, weights, b, dtype=torch.float32)
+    for got, expected in ((out[0], ref_a[1100]), (out[1], ref_a[1163]), (out[2], ref_a[1199]), (out[3], ref_b[30])):
+        assert plain_llama.max_relative_error(got.cpu(), expected) < TOLERANCE["bfloat16"]
