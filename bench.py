@@ -279,6 +279,19 @@ def run_ours(args) -> dict:
             for rid in ids:
                 engine.cache.close(rid)
 
+        # a long prompt in the default portions: 8,192 tokens, 256 a step (tokens a second)
+        long_prompt = torch.randint(0, vocab, (4 * PROMPT_LEN,), generator=gen).tolist()
+        for attempt in ("warm", "timed"):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for at in range(0, len(long_prompt), 256):
+                last = at + 256 >= len(long_prompt)
+                engine.runner.step([StepEntry(("long", attempt), long_prompt[at:at + 256], [255] if last else [])])
+            end.record()
+            torch.cuda.synchronize()
+            engine.runner.end(("long", attempt))
+        points["prefill_8192_by_256"] = len(long_prompt) / (start.elapsed_time(end) / 1e3)
+
     clock_summary = clocks.summary()
     return {
         "metric": "decode tok/s at batch 8 (Llama-3.1-8B shape, 2,048-token prompts)",
