@@ -105,7 +105,7 @@ def bench_attention_prefill(tokens_list, n_heads, n_kv, head_dim, page, prior=0,
                   f"{flops / us / 1e6:.0f} TFLOP/s (causal flops)", flush=True)
 
 
-def bench_attention_decode(batches, contexts, n_heads, n_kv, head_dim, page) -> None:
+def bench_attention_decode(batches, contexts, n_heads, n_kv, head_dim, page, force_splits=0) -> None:
     from ..parts.attention import decode_splits
 
     for batch in batches:
@@ -121,7 +121,7 @@ def bench_attention_decode(batches, contexts, n_heads, n_kv, head_dim, page) -> 
             out = torch.empty_like(q)
             pos = torch.full((batch,), context - 1, dtype=torch.int32, device="cuda")
             entry = torch.arange(batch, dtype=torch.int32, device="cuda")
-            splits = decode_splits(batch * n_kv, context, q.device, head_dim, n_heads // n_kv)
+            splits = force_splits or decode_splits(batch * n_kv, context, q.device, head_dim, n_heads // n_kv)
             scratch = torch.empty(max(1, ops.attention_decode_scratch_floats(batch, n_heads, head_dim, splits)),
                                   device="cuda")
             scale = 1 / math.sqrt(head_dim)
@@ -218,7 +218,7 @@ def main() -> None:
     parser.add_argument("--shapes", nargs="*", default=None, help="T,N,K triples for gemm")
     parser.add_argument("--tokens", type=int, nargs="*", default=[2048, 8192])
     parser.add_argument("--prior", type=int, default=0, help="keys in the cache before an attention_prefill portion")
-    parser.add_argument("--splits", type=int, default=0, help="attention_prefill: split the keys this many ways "
+    parser.add_argument("--splits", type=int, default=0, help="attention_prefill, attention_decode: split the keys this many ways "
                         "(default: as the engine would)")
     parser.add_argument("--batch", type=int, nargs="*", default=[1, 8, 64])
     parser.add_argument("--context", type=int, nargs="*", default=[2048, 4096])
@@ -239,7 +239,8 @@ def main() -> None:
         bench_attention_prefill(args.tokens, args.heads, args.kv_heads, args.head_dim, args.page_size, args.prior,
                                 args.splits)
     else:
-        bench_attention_decode(args.batch, args.context, args.heads, args.kv_heads, args.head_dim, args.page_size)
+        bench_attention_decode(args.batch, args.context, args.heads, args.kv_heads, args.head_dim, args.page_size,
+                               args.splits)
 
 
 if __name__ == "__main__":

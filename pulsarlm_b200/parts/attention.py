@@ -35,27 +35,50 @@ _SM_COUNT: dict = {}
 _CLUSTER_ROOM: dict[tuple, int] = {}
 
 
+def _cluster_room(device: torch.device, head_dim: int, group: int, splits: int) -> int:
+    key = (device, head_dim, group, splits)
+    if key not in _CLUSTER_ROOM:
+        _CLUSTER_ROOM[key] = ops.library().pl_attention_decode_resident_clusters(head_dim, group, splits)
+    return _CLUSTER_ROOM[key]
+
+
 def decode_splits(n_ctas: int, max_context: int, device: torch.device, head_dim: int = 128, group: int = 4) -> int:
-    """Ways to split each request's keys so that about two CTAs per SM run: as many
-    as fit, but no split shorter than eight 16-key tiles. Up to sixteen splits are the
-    ranks of a thread-block cluster; their number is then lowered until all clusters
-    of the launch are resident at once (a launch in two waves takes twice as long)."""
+    """Ways to split each request's keys among CTAs (`n_ctas` = tokens x kv heads without
+    splits): the count with the least estimated time. The CTAs of a launch run in rounds
+    of what the device holds at once (two CTAs per SM; with splits, the thread-block
+    clusters that fit); a round streams at the memory's bandwidth if it has CTAs enough
+    and at 36 GB/s per CTA if it has few, so few long CTAs, and a sparse last round of
+    them, are what splitting avoids. Constants measured with this kernel (they reproduce
+    its times at batch 1 to 64 within a tenth): 6.3 TB/s, 2 us per round, 2 us for the
+    merge inside a cluster (up to sixteen splits), 5 us for the merge kernel (more
+    splits, through scratch memory). No split shorter than eight 16-key tiles."""
     if device not in _SM_COUNT:
         _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
-    target = 2 * _SM_COUNT[device]
-    if n_ctas >= target:
-        return 1
-    tiles = -(-max_context // 16)
-    splits = max(1, min(target // n_ctas, tiles // 8))
-    while 2 <= splits <= 16:
-        key = (device, head_dim, group, splits)
-        if key not in _CLUSTER_ROOM:
-            _CLUSTER_ROOM[key] = ops.library().pl_attention_decode_resident_clusters(head_dim, group, splits)
-        room = _CLUSTER_ROOM[key]
-        if room <= 0 or n_ctas <= room:
-            break
-        splits -= 1
-    return splits
+    slots = 2 * _SM_COUNT[device]
+    most = max(1, min(-(-max_context // 16) // 8, max(16, slots // max(1, n_ctas))))
+    key_bytes = 4.0 * head_dim  # K and V of one key and kv head
+
+    def round_seconds(ctas: int, bytes_each: float) -> float:
+        return ctas * bytes_each / min(6.3e12, ctas * 36e9) + 2e-6
+
+    best, best_cost = 1, float("inf")
+    for splits in range(most, 0, -1):  # on a tie, the finer split
+        if splits == 1:
+            room = slots
+        elif splits <= 16:
+            room = (_cluster_room(device, head_dim, group, splits) or slots // splits) * splits
+        else:
+            room = slots
+        total = n_ctas * splits
+        bytes_each = max_context / splits * key_bytes
+        cost = (total // room) * round_seconds(room, bytes_each)
+        if total % room:
+            cost += round_seconds(total % room, bytes_each)
+        if splits > 1:
+            cost += 2e-6 if splits <= 16 else 5e-6
+        if cost < best_cost:
+            best, best_cost = splits, cost
+    return best
 
 
 def prefill_splits(n_ctas: int, max_keys: int, n_tokens: int, n_heads: int, head_dim: int,
