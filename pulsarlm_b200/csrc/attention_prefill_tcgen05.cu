@@ -114,7 +114,11 @@ __device__ __forceinline__ uint64_t smem_descriptor_mn(const void* tile, uint32_
 // share every K and V tile, one softmax warpgroup each, one thread per query row), 1
 // otherwise (the two warpgroups share each row: one takes the tile's first 32 keys
 // and the first half of the output's dims, the other the rest).
-template <int HD, int HEADS>
+//
+// WIDE (with HEADS == 2, for odd groups): the two "heads" of the CTA are the two
+// 128-row halves of one tile of up to 256 rows of ONE head: they share K and V just
+// the same, and everything that says head `hs` below means rows 128 hs ... of it.
+template <int HD, int HEADS, bool WIDE>
 __global__ void __launch_bounds__(kThreadsTc, 1)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, const TcPrefillParams p) {
@@ -153,8 +157,13 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     // Heads vary fastest in the grid and the tile list is sorted longest first, so the
     // CTAs of a wave are of similar length and the short ones fill the end.
     const int4 tile = p.tiles[blockIdx.y];
-    const int row0 = tile.x, n_rows = tile.y, pos0 = tile.z;
-    const int head0 = blockIdx.x * HEADS, kv_head = head0 / p.group;
+    static_assert(!WIDE || HEADS == 2, "a wide tile is two halves that take turns");
+    constexpr int kSpan = WIDE ? 2 * kRows : kRows;  // rows of a tile
+    const int row0 = tile.x, n_rows = min(tile.y, kSpan), pos0 = tile.z;
+    if (tile.y > kSpan && threadIdx.x == 0 && p.status != nullptr) {
+        atomicOr(p.status, 4);  // a tile with more rows than this arrangement takes
+    }
+    const int head0 = WIDE ? blockIdx.x : blockIdx.x * HEADS, kv_head = head0 / p.group;
     const int last_key = pos0 + n_rows - 1;
     const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
     // This CTA's share of the tile's 64-key tiles (all of them without splits).
@@ -165,9 +174,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     if (n_tiles == 0) {
         // Nothing for this split: its rows say so (the merge skips a split whose base is -inf).
         for (int i = threadIdx.x; i < HEADS * kRows; i += kThreadsTc) {
-            const int hs = i / kRows, r = i % kRows;
+            const int hs = i / kRows, r = WIDE ? i : i % kRows, head = head0 + (WIDE ? 0 : hs);
             if (r < n_rows) {
-                p.part_ml[(static_cast<int64_t>(row0 + r) * p.n_heads + head0 + hs) * p.n_splits + blockIdx.z] =
+                p.part_ml[(static_cast<int64_t>(row0 + r) * p.n_heads + head) * p.n_splits + blockIdx.z] =
                     make_float2(-INFINITY, 0.0f);
             }
         }
@@ -409,21 +418,23 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const uint32_t lane_bits = static_cast<uint32_t>(lane_group * 32) << 16;
         const uint32_t my_s = tmem_s + lane_bits + hs * kBuffersS * kColsS + part * kMyKeys;
         const uint32_t my_o = tmem_o + lane_bits + hs * kColsO + part * kMyDims;
-        const int pos = pos0 + r;
+        const int rr = r + (WIDE ? hs * kRows : 0);        // this thread's row within the tile,
+        const int head = head0 + (WIDE ? 0 : hs);          // and its query head
+        const int pos = pos0 + rr;
         const int first = p.window > 0 ? pos - p.window + 1 : 0;
         float m = -INFINITY, l = 0.0f;  // m: the base of the exponents in use (lags the true maximum)
         bool ok = true;
         if constexpr (kTurns) {
             // This thread's row of Q into tensor memory, where the first product reads its A
             // operand: lane = row, column c = dims 2c and 2c + 1 (rows past the tile: zeros).
-            const uint4* src = reinterpret_cast<const uint4*>(p.q + (row0 + r) * p.q_row_stride +
-                                                              static_cast<int64_t>(head0 + hs) * HD);
+            const uint4* src = reinterpret_cast<const uint4*>(p.q + (row0 + rr) * p.q_row_stride +
+                                                              static_cast<int64_t>(head) * HD);
 #pragma unroll
             for (int g = 0; g < HD / 64; ++g) {
                 uint32_t v[32];
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
-                    const uint4 four = r < n_rows ? src[8 * g + c] : make_uint4(0u, 0u, 0u, 0u);
+                    const uint4 four = rr < n_rows ? src[8 * g + c] : make_uint4(0u, 0u, 0u, 0u);
                     v[4 * c] = four.x;
                     v[4 * c + 1] = four.y;
                     v[4 * c + 2] = four.z;
@@ -470,7 +481,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
             const int key0 = (j0 + j) * kKeys + part * kMyKeys;
             const bool edge = (j0 + j) * kKeys + kKeys - 1 > pos0 ||
-                (p.window > 0 && (j0 + j) * kKeys < pos0 + kRows - p.window);
+                (p.window > 0 && (j0 + j) * kKeys < pos0 + kSpan - p.window);
             // The tile's maximum, on the raw products (the scale is positive), four running
             // maxima side by side so that the chain of dependent instructions stays short.
             if (edge) {
@@ -576,9 +587,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
         if (ok && p.n_splits > 1) {
             // One split of several: the unnormalised row, and what the merge needs to weigh it.
-            const int64_t slot = (static_cast<int64_t>(row0 + r) * p.n_heads + head0 + hs) * p.n_splits + blockIdx.z;
+            const int64_t slot = (static_cast<int64_t>(row0 + rr) * p.n_heads + head) * p.n_splits + blockIdx.z;
             float* dst = p.part_o + slot * HD + part * kMyDims;
-            if (part == 0 && r < n_rows) {
+            if (part == 0 && rr < n_rows) {
                 p.part_ml[slot] = make_float2(m, l);
             }
 #pragma unroll
@@ -586,7 +597,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 uint32_t v[32];
                 tcgen05_ld32_nowait(my_o + 32 * g, v);  // all lanes take part
                 tcgen05_wait_ld();
-                if (r < n_rows) {
+                if (rr < n_rows) {
 #pragma unroll
                     for (int d = 0; d < 32; d += 4) {
                         *reinterpret_cast<uint4*>(dst + 32 * g + d) = make_uint4(v[d], v[d + 1], v[d + 2], v[d + 3]);
@@ -595,14 +606,14 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
         } else if (ok) {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            __nv_bfloat16* dst = p.out + (row0 + r) * p.out_row_stride + static_cast<int64_t>(head0 + hs) * HD +
+            __nv_bfloat16* dst = p.out + (row0 + rr) * p.out_row_stride + static_cast<int64_t>(head) * HD +
                 part * kMyDims;
 #pragma unroll
             for (int g = 0; g < kMyDims / 32; ++g) {
                 uint32_t v[32];
                 tcgen05_ld32_nowait(my_o + 32 * g, v);  // all lanes take part
                 tcgen05_wait_ld();
-                if (r < n_rows && n_tiles > 0) {
+                if (rr < n_rows && n_tiles > 0) {
 #pragma unroll
                     for (int d = 0; d < 32; d += 8) {
                         uint32_t w[4];
@@ -698,13 +709,13 @@ __global__ void __launch_bounds__(256) attention_prefill_merge_kernel(const TcPr
     }
 }
 
-template <int HD, int HEADS>
+template <int HD, int HEADS, bool WIDE>
 int launch_tc_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcPrefillParams& p,
                       int n_tiles, int n_heads, cudaStream_t stream) {
     constexpr int smem = (HEADS == 2 ? 0 : kRows * HD * 2) + stages_kv(HEADS) * 2 * kKeys * HD * 2 + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD, HEADS>,
+        cudaError_t err = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD, HEADS, WIDE>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (err != cudaSuccess) {
             return pl_fail(3, "attention_prefill_tcgen05: cannot set shared memory size: %s",
@@ -712,11 +723,11 @@ int launch_tc_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
         }
         configured = true;
     }
-    attention_prefill_tcgen05_kernel<HD, HEADS>
-        <<<dim3(n_heads / HEADS, n_tiles, p.n_splits), kThreadsTc, smem, stream>>>(mq, mk, mv, p);
+    attention_prefill_tcgen05_kernel<HD, HEADS, WIDE>
+        <<<dim3(WIDE ? n_heads : n_heads / HEADS, n_tiles, p.n_splits), kThreadsTc, smem, stream>>>(mq, mk, mv, p);
     PL_CHECK_LAUNCH("attention_prefill_tcgen05");
     if (p.n_splits > 1) {
-        attention_prefill_merge_kernel<HD><<<dim3(n_heads, n_tiles, kRows / 8), 256, 0, stream>>>(p);
+        attention_prefill_merge_kernel<HD><<<dim3(n_heads, n_tiles, (WIDE ? 2 : 1) * kRows / 8), 256, 0, stream>>>(p);
         PL_CHECK_LAUNCH("attention_prefill_merge");
     }
     return 0;
@@ -732,6 +743,11 @@ PL_API int pl_attention_prefill_tcgen05_supports(int head_dim, int page_size, in
         page_stride == 2 * static_cast<int64_t>(n_kv_heads) * head_stride && q_row_stride % 8 == 0;
 }
 
+// Rows per tile that the kernel can take for this GQA group: with an odd group a CTA
+// works on one head and takes a tile twice as long (its halves share K and V the way
+// two heads of an even group do).
+PL_API int pl_attention_prefill_tcgen05_tile_rows(int group) { return group % 2 == 0 ? kRows : 2 * kRows; }
+
 // Scratch floats that `n_splits` splits of the keys need for a step of `n_tokens` tokens.
 PL_API int64_t pl_attention_prefill_scratch_floats(int n_tokens, int n_heads, int head_dim, int n_splits) {
     return n_splits <= 1 ? 0 : static_cast<int64_t>(n_tokens) * n_heads * n_splits * (head_dim + 2);
@@ -742,12 +758,14 @@ PL_API int64_t pl_attention_prefill_scratch_floats(int n_tokens, int n_heads, in
 // k_pool + kv_heads * page * head_dim elements. With n_splits > 1 (at most 32) every
 // tile's keys are shared out over that many CTAs and merged by a second kernel
 // through `scratch` (pl_attention_prefill_scratch_floats floats, 16-byte aligned).
+// `wide` (odd groups only; ignored for even ones): the tiles have up to 256 rows
+// (pl_attention_prefill_tcgen05_tile_rows), else up to 128.
 PL_API int pl_attention_prefill_tcgen05(const void* q, int64_t q_row_stride, int n_tokens, const void* k_pool,
                                         const void* v_pool, int64_t page_stride, int64_t head_stride, int page_size,
                                         int n_pages, const int32_t* table, int table_width, const int32_t* tiles,
                                         int n_tiles, void* out, int64_t out_row_stride, int n_heads, int n_kv_heads,
                                         int head_dim, int window, float scale, int n_splits, float* scratch,
-                                        int32_t* status, cudaStream_t stream) {
+                                        int wide, int32_t* status, cudaStream_t stream) {
     PL_REQUIRE(n_tiles >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_tokens > 0,
                "attention_prefill_tcgen05: bad sizes tiles=%d heads=%d kv_heads=%d tokens=%d", n_tiles, n_heads,
                n_kv_heads, n_tokens);
@@ -805,11 +823,16 @@ PL_API int pl_attention_prefill_tcgen05(const void* q, int64_t q_row_stride, int
     p.part_ml = n_splits > 1
         ? reinterpret_cast<float2*>(scratch + static_cast<int64_t>(n_tokens) * n_heads * n_splits * head_dim)
         : nullptr;
-    const bool pairs = p.group % 2 == 0;  // two heads of one kv head per CTA
+    // Two heads of one kv head per CTA when the group is even; else one head per CTA, and
+    // a tile of up to 256 rows as two halves (`wide`), or of up to 128 rows with both
+    // warpgroups on it.
+    const bool pairs = p.group % 2 == 0;
     if (head_dim == 64) {
-        return pairs ? launch_tc_prefill<64, 2>(mq, mk, mv, p, n_tiles, n_heads, stream)
-                     : launch_tc_prefill<64, 1>(mq, mk, mv, p, n_tiles, n_heads, stream);
+        return pairs ? launch_tc_prefill<64, 2, false>(mq, mk, mv, p, n_tiles, n_heads, stream)
+            : wide   ? launch_tc_prefill<64, 2, true>(mq, mk, mv, p, n_tiles, n_heads, stream)
+                     : launch_tc_prefill<64, 1, false>(mq, mk, mv, p, n_tiles, n_heads, stream);
     }
-    return pairs ? launch_tc_prefill<128, 2>(mq, mk, mv, p, n_tiles, n_heads, stream)
-                 : launch_tc_prefill<128, 1>(mq, mk, mv, p, n_tiles, n_heads, stream);
+    return pairs ? launch_tc_prefill<128, 2, false>(mq, mk, mv, p, n_tiles, n_heads, stream)
+        : wide   ? launch_tc_prefill<128, 2, true>(mq, mk, mv, p, n_tiles, n_heads, stream)
+                 : launch_tc_prefill<128, 1, false>(mq, mk, mv, p, n_tiles, n_heads, stream);
 }

@@ -131,6 +131,7 @@ class ModelRunner:
         entry = np.empty(n_tokens, dtype=np.int32)
         first_row = [0] * len(entries)
         tiles: list[tuple[int, int, int, int]] = []
+        wide_tiles: list[tuple[int, int, int, int]] = []  # the same rows in tiles twice as long
         at = 0
         for place, i in enumerate(order):
             e = entries[i]
@@ -143,8 +144,11 @@ class ModelRunner:
             if n > 1:  # tiles of consecutive rows for the prompt-portion attention kernel
                 for r in range(0, n, self._tile_rows):
                     tiles.append((at + r, min(self._tile_rows, n - r), start + r, place))
+                for r in range(0, n, 2 * self._tile_rows):
+                    wide_tiles.append((at + r, min(2 * self._tile_rows, n - r), start + r, place))
             at += n
         tiles.sort(key=lambda t: -(t[2] + t[1]))  # the tiles with the most keys start first
+        wide_tiles.sort(key=lambda t: -(t[2] + t[1]))
         want_rows = [first_row[i] + w for i, e in enumerate(entries) for w in e.want]
         requests = [entries[i].request for i in order]
         slots = np.array([self.cache.slot(r) for r in requests], dtype=np.int32)
@@ -169,6 +173,7 @@ class ModelRunner:
                     keep[self.cache.held_pages(e.request, g.index)] = (1.0 - decay) ** len(e.tokens)
                 keep[list(self.cache.take_fresh_pages(g.index))] = 0.0
                 arrays.append(keep.view(np.int32))
+        arrays.append(np.array(wide_tiles, dtype=np.int32).reshape(len(wide_tiles), 4))  # last: dev[-1]
         dev = self._stage(arrays)
         batch = StepBatch(
             tokens=dev[0], pos=dev[1], entry=dev[2],
@@ -182,6 +187,8 @@ class ModelRunner:
             host_query_lens=[len(entries[i].tokens) for i in order],
             host_context_lens=[new_lens[i] for i in order],
             extras={"prefill_tiles": dev[5] if tiles else None,
+                    # (worth using only if some portion is longer than one narrow tile)
+                    "prefill_tiles_wide": dev[-1] if any(t[1] > self._tile_rows for t in wide_tiles) else None,
                     # the most keys any tile reads (the attention part sizes its launch by it)
                     "prefill_max_keys": max((t[2] + t[1] for t in tiles), default=0)},
         )

@@ -84,20 +84,25 @@ def bench_attention_prefill(tokens_list, n_heads, n_kv, head_dim, page, prior=0,
         qkv = torch.randn(tokens, (n_heads + 2 * n_kv) * head_dim, device="cuda").to(torch.bfloat16)
         q = qkv[:, : n_heads * head_dim].view(tokens, n_heads, head_dim)
         out = torch.empty(tokens, n_heads, head_dim, device="cuda", dtype=torch.bfloat16)
-        rows = ops.attention_prefill_tile_rows()
-        tiles = sorted(((r, min(rows, tokens - r), prior + r, 0) for r in range(0, tokens, rows)),
-                       key=lambda t: -(t[1] + t[2]))
-        tiles = torch.tensor(tiles, dtype=torch.int32, device="cuda")
+        def tile_list(rows):
+            tiles = sorted(((r, min(rows, tokens - r), prior + r, 0) for r in range(0, tokens, rows)),
+                           key=lambda t: -(t[1] + t[2]))
+            return torch.tensor(tiles, dtype=torch.int32, device="cuda")
+
+        tiles = tile_list(ops.attention_prefill_tile_rows())
+        wide = (n_heads // n_kv) % 2 == 1  # one head per CTA: tiles of twice the rows
+        wide_tiles = tile_list(ops.attention_prefill_tcgen05_tile_rows(n_heads // n_kv))
         scale = 1 / math.sqrt(head_dim)
         flops = 4.0 * n_heads * head_dim * (tokens * (tokens + 1) / 2 + tokens * prior)
         # the engine's choice: few tiles over many keys are split over the keys
-        ctas = tiles.shape[0] * (n_heads // 2 if (n_heads // n_kv) % 2 == 0 else n_heads)
+        ctas = wide_tiles.shape[0] * n_heads if wide else tiles.shape[0] * n_heads // 2
         splits = force_splits or prefill_splits(ctas, tokens + prior, tokens, n_heads, head_dim, q.device)
         scratch = torch.empty(max(1, ops.attention_prefill_scratch_floats(tokens, n_heads, head_dim, splits)),
                               device="cuda")
 
-        def tcgen05(*args):
-            ops.attention_prefill_tcgen05(*args, None, splits, scratch)
+        def tcgen05(q, kp, vp, table, tiles, *args):
+            ops.attention_prefill_tcgen05(q, kp, vp, table, wide_tiles if wide else tiles, *args, None, splits,
+                                          scratch, wide)
 
         for name, kernel in ((f"tcgen05 splits={splits}", tcgen05), ("mma.sync", ops.attention_prefill)):
             us = graph_time_us(lambda: kernel(q, kp, vp, table, tiles, out, page, None, scale), reps=4)

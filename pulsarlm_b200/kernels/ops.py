@@ -25,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 11
+ABI_VERSION = 12
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -51,7 +51,8 @@ _SIGNATURES = {
                              _I32, _I32, _I32, _I32, _F32, _PTR, _PTR],
     "pl_attention_prefill_supports": [_I32, _I32, _I32],
     "pl_attention_prefill_tcgen05": [_PTR, _I64, _I32, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _I32,
-                                     _PTR, _I64, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR, _PTR],
+                                     _PTR, _I64, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _I32, _PTR, _PTR],
+    "pl_attention_prefill_tcgen05_tile_rows": [_I32],
     "pl_attention_prefill_tcgen05_supports": [_I32, _I32, _I32, _I64, _I64, _I64, _I32],
     "pl_attention_prefill_tile_rows": [],
     "pl_gemm_bf16_pair_supports": [_I32, _I32, _I32, _I64, _I64],
@@ -394,13 +395,21 @@ def attention_prefill_scratch_floats(n_tokens: int, n_heads: int, head_dim: int,
     return int(library().pl_attention_prefill_scratch_floats(n_tokens, n_heads, head_dim, n_splits))
 
 
+def attention_prefill_tcgen05_tile_rows(group: int) -> int:
+    """The most rows of a tile that attention_prefill_tcgen05 takes with `wide=True` for
+    this GQA group: 256 when the group is odd (a CTA then works on one head, and the
+    two halves of a tile share its keys), else 128."""
+    return int(library().pl_attention_prefill_tcgen05_tile_rows(group))
+
+
 def attention_prefill_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,
                               tiles: torch.Tensor, out: torch.Tensor, page_size: int, window: int | None,
                               scale: float, status: torch.Tensor | None = None, n_splits: int = 1,
-                              scratch: torch.Tensor | None = None) -> None:
+                              scratch: torch.Tensor | None = None, wide: bool = False) -> None:
     """As attention_prefill, on the tcgen05 tensor cores. With n_splits > 1 every tile's
     keys are shared out over that many CTAs and merged through `scratch` (float32,
-    attention_prefill_scratch_floats elements): for few tiles over many keys."""
+    attention_prefill_scratch_floats elements): for few tiles over many keys. `wide`: the
+    tiles have up to attention_prefill_tcgen05_tile_rows(group) rows instead of 128."""
     _dev(q, k_pool, v_pool, table, tiles, out, status, scratch)
     if n_splits > 1:
         need = attention_prefill_scratch_floats(q.shape[0], q.shape[1], q.shape[2], n_splits)
@@ -417,7 +426,7 @@ def attention_prefill_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
     _call("pl_attention_prefill_tcgen05", _p(q), q.stride(0), tokens, _p(k_pool), _p(v_pool), k_pool.stride(0),
           k_pool.stride(1), page_size, n_pages, _p(table), table.shape[1], _p(tiles), tiles.shape[0], _p(out),
           out.stride(0), n_heads, n_kv, head_dim, int(window or 0), float(scale), int(n_splits), _p(scratch),
-          _p(status), _stream())
+          int(wide), _p(status), _stream())
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor | None,

@@ -232,8 +232,13 @@ class Attention(Part):
             if self._prefill_tcgen05 is None:
                 self._prefill_tcgen05 = ops.attention_prefill_tcgen05_supports(q, cache.k_pool, cache.page_size)
             if self._prefill_tcgen05:
-                # two heads of a kv head share a CTA when the group is even
-                ctas = tiles.shape[0] * (self.n_heads // 2 if (self.n_heads // self.n_kv) % 2 == 0 else self.n_heads)
+                # Two heads of a kv head share a CTA when the group is even; else a CTA takes one
+                # head, and a tile of twice the rows if the step has portions that long (the two
+                # halves then share the keys; for shorter portions the narrow tiles are ahead).
+                wide = (self.n_heads // self.n_kv) % 2 == 1 and batch.extras.get("prefill_tiles_wide") is not None
+                if wide:
+                    tiles = batch.extras["prefill_tiles_wide"]
+                ctas = tiles.shape[0] * (self.n_heads if wide or (self.n_heads // self.n_kv) % 2 else self.n_heads // 2)
                 max_keys = int(batch.extras.get("prefill_max_keys") or 0)
                 if self.window:
                     max_keys = min(max_keys, self.window + ops.attention_prefill_tile_rows())
@@ -244,7 +249,7 @@ class Attention(Part):
                                                                                splits),
                                           dtype=torch.float32, device=q.device)
                 ops.attention_prefill_tcgen05(q, cache.k_pool, cache.v_pool, table, tiles, out, cache.page_size,
-                                              self.window, self.scale, batch.status, splits, scratch)
+                                              self.window, self.scale, batch.status, splits, scratch, wide)
             else:
                 ops.attention_prefill(q, cache.k_pool, cache.v_pool, table, tiles, out, cache.page_size,
                                       self.window, self.scale, batch.status)

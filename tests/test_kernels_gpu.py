@@ -510,6 +510,14 @@ def test_attention_prefill(ops, kernel, nh, nkv, hd, page, window):
     later = [(row0, n, pos0, e) for row0, n, pos0, e in portions[1:]]
     run(q, kp, vp, table.to(DEV), make_tiles(later, 128), out2, page, window, scale, status)
     assert rel(out2[150:], want[150:]) < 1e-2 and bool(torch.isnan(out2[:150].float()).all())
+    if kernel == "tcgen05" and (nh // nkv) % 2 == 1:
+        # an odd group: one head per CTA, and tiles of twice the rows whose halves share the keys
+        rows = ops.attention_prefill_tcgen05_tile_rows(nh // nkv)
+        assert rows == 256
+        out3 = torch.full_like(q, float("nan"))
+        ops.attention_prefill_tcgen05(q, kp, vp, table.to(DEV), make_tiles(portions, rows), out3, page, window,
+                                      scale, status, wide=True)
+        assert int(status) == 0 and rel(out3, want) < 1e-2
 
 
 @pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
@@ -566,23 +574,30 @@ def test_attention_prefill_with_split_keys(ops, nh, nkv, hd, page, splits, windo
     scale = 1 / math.sqrt(hd)
     tiles = make_tiles(portions, 128)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    wide = (nh // nkv) % 2 == 1  # (both arrangements for odd groups are covered: see the far-key test below)
+    if wide:
+        tiles = make_tiles(portions, ops.attention_prefill_tcgen05_tile_rows(nh // nkv))
     whole = torch.full_like(q, float("nan"))
-    ops.attention_prefill_tcgen05(q, kp, vp, table.to(DEV), tiles, whole, page, window, scale, status)
+    ops.attention_prefill_tcgen05(q, kp, vp, table.to(DEV), tiles, whole, page, window, scale, status, wide=wide)
     out = torch.full_like(q, float("nan"))
     ops.attention_prefill_tcgen05(q, kp, vp, table.to(DEV), tiles, out, page, window, scale, status, splits,
-                                  split_scratch(ops, q, splits))
+                                  split_scratch(ops, q, splits), wide)
     want = reference_attention(q, kp, vp, table, pos, entry, page, window, scale)
     assert int(status) == 0 and rel(out, want) < 1e-2
     assert rel(out, whole.float()) <= 2.0 ** -7  # the splits change the rounding (one bfloat16 step) and nothing else
 
 
-@pytest.mark.parametrize("splits", [2, 5])
+@pytest.mark.parametrize("splits,nh,wide", [(2, 2, False), (5, 2, False), (1, 1, False), (3, 1, False),
+                                            (1, 1, True), (3, 1, True)])
 @pytest.mark.parametrize("far_key", [0, 63, 64, 575, 576, 1023, 1100])
-def test_split_prefill_finds_one_far_key_and_respects_causality(ops, splits, far_key):
+def test_split_prefill_finds_one_far_key_and_respects_causality(ops, splits, nh, wide, far_key):
     """As above with the keys split: the loud key lies in one split only, and the
-    merge must let it dominate (and a split must not read past the diagonal)."""
+    merge must let it dominate (and a split must not read past the diagonal). With one
+    head to the kv head, in both arrangements the kernel has for odd groups: tiles of
+    128 rows, and tiles of 256 rows whose halves take turns (the portion of 140 rows is
+    then one tile, its second half mostly empty)."""
     dtype = torch.bfloat16
-    nh, nkv, hd, page = 2, 1, 64, 16
+    nkv, hd, page = 1, 64, 16
     n_ctx, n_q = 1204, 140
     pages_each = -(-n_ctx // page)
     table = scattered_tables(1, pages_each, pages_each + 3, seed=9)
@@ -594,8 +609,8 @@ def test_split_prefill_finds_one_far_key_and_respects_causality(ops, splits, far
     vp[page_id, 0, far_key % page] = 5.0
     pos0 = n_ctx - n_q
     out = torch.empty_like(q)
-    ops.attention_prefill_tcgen05(q, kp, vp, table.to(DEV), make_tiles([(0, n_q, pos0, 0)], 128), out, page, None,
-                                  1.0, None, splits, split_scratch(ops, q, splits))
+    ops.attention_prefill_tcgen05(q, kp, vp, table.to(DEV), make_tiles([(0, n_q, pos0, 0)], 256 if wide else 128),
+                                  out, page, None, 1.0, None, splits, split_scratch(ops, q, splits), wide)
     pos = list(range(pos0, n_ctx))
     want = reference_attention(q, kp, vp, table, pos, [0] * n_q, page, None, 1.0)
     sees = torch.tensor([p >= far_key for p in pos])
