@@ -121,7 +121,15 @@ def require_device() -> None:
     _device_checked = True
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current stream's handle (torch's; inside a graph capture, the capturing stream).
+    Asked through torch's C entry point when it has one: the Python object costs 15 us a
+    call, which a step of a few hundred launches notices."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 

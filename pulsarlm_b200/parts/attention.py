@@ -43,6 +43,19 @@ def _cluster_room(device: torch.device, head_dim: int, group: int, splits: int) 
 
 
 def decode_splits(n_ctas: int, max_context: int, device: torch.device, head_dim: int = 128, group: int = 4) -> int:
+    """(Remembered per argument list: every layer of a step asks the same question.)"""
+    key = (n_ctas, max_context, device, head_dim, group)
+    if key not in _DECODE_SPLITS:
+        if len(_DECODE_SPLITS) > 4096:
+            _DECODE_SPLITS.clear()
+        _DECODE_SPLITS[key] = _decode_splits(*key)
+    return _DECODE_SPLITS[key]
+
+
+_DECODE_SPLITS: dict[tuple, int] = {}
+
+
+def _decode_splits(n_ctas: int, max_context: int, device: torch.device, head_dim: int, group: int) -> int:
     """Ways to split each request's keys among CTAs (`n_ctas` = tokens x kv heads without
     splits): the count with the least estimated time. The CTAs of a launch run in rounds
     of what the device holds at once (two CTAs per SM; with splits, the thread-block
