@@ -196,6 +196,7 @@ def run_ours(args) -> dict:
     device = "cuda:0"
     max_batch = max(64, batch)
     tokens_room = max_batch * (PROMPT_LEN + 2 * (args.steps + args.warmup) + 128) + 4 * PROMPT_LEN
+    tokens_room = max(tokens_room, args.prefill_tokens + 4 * PROMPT_LEN)
     n_pages = -(-tokens_room // PAGE_SIZE)
     t0 = time.time()
     engine = Engine(cfg, dtype="bfloat16", device=device, n_pages=n_pages, page_size=PAGE_SIZE,
@@ -214,20 +215,21 @@ def run_ours(args) -> dict:
 
     # ---- prefill: one 2,048-token prompt in one step, logits of the last token.
     if "prefill" in phases:
-        prompt = torch.randint(0, vocab, (PROMPT_LEN,), generator=gen).tolist()
+        n_prompt = args.prefill_tokens
+        prompt = torch.randint(0, vocab, (n_prompt,), generator=gen).tolist()
         times = []
         for i in range(3 + 5):
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
-            engine.runner.step([StepEntry(("prefill", i), prompt, [PROMPT_LEN - 1])])
+            engine.runner.step([StepEntry(("prefill", i), prompt, [n_prompt - 1])])
             end.record()
             torch.cuda.synchronize()
             engine.runner.end(("prefill", i))
             if i >= 3:
                 times.append(start.elapsed_time(end))
         prefill_ms = statistics.median(times)
-        flops = prefill_flops(cfg, PROMPT_LEN)
-        prefill = {"value": PROMPT_LEN / (prefill_ms / 1e3), "tokens": PROMPT_LEN, "ms": prefill_ms,
+        flops = prefill_flops(cfg, n_prompt)
+        prefill = {"value": n_prompt / (prefill_ms / 1e3), "tokens": n_prompt, "ms": prefill_ms,
                    "frac": flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), "unit": "tok/s",
                    "peak_tflops": pk["bf16_tflops"]}
 
@@ -337,6 +339,8 @@ def main() -> int:
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--layers", type=int, default=32, help="fewer layers than the model's 32 (named in config)")
+    p.add_argument("--prefill_tokens", type=int, default=PROMPT_LEN,
+                   help="length of the prompt of the prefill phase (the contract's figure is the default's)")
     p.add_argument("--phases", default="prefill,e2e,decode,points",
                    help="which measurements to run (a profiler run wants one): prefill,e2e,decode,points")
     args = p.parse_args()
