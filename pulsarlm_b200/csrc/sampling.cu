@@ -81,7 +81,29 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
 
     if (!(temp > 0.0f)) {
         unsigned long long best = 0ull;
-        for (int i = tid; i < vocab; i += kThreads) {
+        // Four values a load where the row allows it, several loads in flight: one block
+        // reads the whole row, and its time is the latency of its loads.
+        const bool by_four = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+        const int quads = by_four ? vocab / 4 : 0;
+#pragma unroll 4
+        for (int quad = tid; quad < quads; quad += kThreads) {
+            const float4 v = reinterpret_cast<const float4*>(x)[quad];
+            // the largest of the four, the lowest index among equals
+            uint32_t top = ordered_bits(v.x);
+            int at = 0;
+            const uint32_t others[3] = {ordered_bits(v.y), ordered_bits(v.z), ordered_bits(v.w)};
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+                if (others[j] > top) {
+                    top = others[j];
+                    at = j + 1;
+                }
+            }
+            const unsigned long long key = (static_cast<unsigned long long>(top) << 32) |
+                (0xffffffffull - static_cast<uint32_t>(4 * quad + at));
+            best = key > best ? key : best;
+        }
+        for (int i = 4 * quads + tid; i < vocab; i += kThreads) {
             const unsigned long long key = race_key(x[i], i);
             best = key > best ? key : best;
         }
