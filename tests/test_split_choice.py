@@ -1,0 +1,55 @@
+"""How many ways the attention part splits the keys: the estimates are plain
+arithmetic over the device's size, checked here against a described device (148 SMs,
+the thread-block clusters a B200 was measured to hold) without one."""
+
+import pytest
+import torch
+
+DEVICE = torch.device("cpu")  # a key into the part's tables, nothing runs on it
+CLUSTERS = {2: 148, 3: 93, 4: 71, 5: 56, 6: 45, 7: 37, 8: 33, 9: 30, 10: 26, 11: 21, 12: 21, 13: 17, 14: 14, 15: 14,
+            16: 14}
+
+
+@pytest.fixture()
+def part(monkeypatch):
+    from pulsarlm_b200.parts import attention
+
+    monkeypatch.setitem(attention._SM_COUNT, DEVICE, 148)
+    for group in (1, 4):
+        for splits, room in CLUSTERS.items():
+            monkeypatch.setitem(attention._CLUSTER_ROOM, (DEVICE, 128, group, splits), room)
+    monkeypatch.setattr(attention, "_DECODE_SPLITS", {})
+    return attention
+
+
+def test_decode_splits_fill_the_device_without_a_sparse_last_round(part):
+    pick = lambda n, context, group=4: part.decode_splits(n, context, DEVICE, 128, group)  # noqa: E731
+    assert pick(64, 2048) == 4            # batch 8 x 8 kv heads: 256 CTAs in one round
+    assert pick(8, 2048) == 16            # batch 1: the largest cluster
+    assert pick(8, 32768) > 16            # batch 1, long history: through scratch memory
+    assert pick(128, 2048) == 2           # 128 CTAs alone stream at 36 GB/s each
+    assert pick(192, 2048) == 1 and pick(256, 2048) == 1 and pick(512, 2048) == 1
+    assert pick(320, 4096, group=1) > 1   # 320 CTAs unsplit leave a second round of 24 long ones
+    for n in (1, 3, 8, 40, 64, 100, 320, 1000):
+        for context in (1, 16, 200, 2048, 100000):
+            splits = pick(n, context)
+            assert splits >= 1
+            # no split shorter than eight 16-key tiles
+            assert splits == 1 or context // splits >= 8 * 16 - 16
+            # more than sixteen only when few CTAs would otherwise run
+            assert splits <= 16 or n * 32 <= 2 * 148 * 2
+
+
+def test_prefill_splits_only_for_few_tiles_over_many_keys(part):
+    pick = lambda ctas, keys, tokens: part.prefill_splits(ctas, keys, tokens, 32, 128, DEVICE)  # noqa: E731
+    assert pick(32, 256, 256) == 1                 # a short prompt: nothing to split
+    assert pick(32, 8192 + 256, 256) == 4          # 256 tokens after 8,192: 128 CTAs
+    assert pick(64, 8192 + 512, 512) == 2
+    assert pick(16, 32768 + 128, 128) == 9         # 144 CTAs
+    assert pick(128, 32768 + 1024, 1024) == 1      # 128 CTAs already: a second round would cost more
+    assert pick(256, 32768 + 2048, 2048) == 1
+    for ctas in (1, 16, 40, 80, 147, 148, 500):
+        for keys in (1, 300, 2048, 40000):
+            splits = pick(ctas, keys, 128)
+            assert 1 <= splits <= 16
+            assert splits == 1 or keys // splits >= 256
