@@ -1,0 +1,59 @@
+"""The engine under arrivals, page pressure and cancellations drawn at random (float32,
+greedy): whatever the scheduler decides (portions, preemption and recomputation,
+pipelined or plain decode steps, graphs or eager), every request that is not cancelled
+ends with exactly the tokens the plain implementation generates for it alone."""
+
+import random
+import tempfile
+
+import pytest
+import torch
+
+import plain_llama
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("seed", [1, 3, 5, 9, 14, 16, 40, 77])  # (1, 3, 9, 14 and 16 preempt)
+def test_random_arrivals_under_page_pressure(seed):
+    from pulsarlm_b200 import Engine, SamplingParams
+    from pulsarlm_b200.engine.loading import load_model
+
+    rng = random.Random(seed)
+    cfg, page = rng.choice([(tiny.TINY_A, tiny.PAGE_A), (tiny.TINY_B, tiny.PAGE_B)])
+    weights = tiny.random_weights(cfg, seed, torch.float32)
+    with tempfile.TemporaryDirectory() as folder:
+        model = load_model(tiny.write_model_dir(folder, cfg, weights), "float32", "cuda:0")
+    n_requests = rng.choice([3, 5, 8])
+    prompts = [tiny.random_tokens(cfg, rng.choice([1, 4, 20, 33, 70, 120]), seed * 100 + i) for i in range(n_requests)]
+    new_tokens = [rng.choice([1, 3, 9, 20]) for _ in range(n_requests)]
+    largest = max(len(p) + n for p, n in zip(prompts, new_tokens))
+    n_pages = -(-largest // page) + rng.choice([0, 1, 3, 10, 40])  # sometimes only one request fits at a time
+    engine = Engine(model, n_pages=n_pages, page_size=page, prefill_tokens_per_step=rng.choice([2, 7, 32, 256]),
+                    max_requests=rng.choice([2, 4, 8]), stop_ids=[], cuda_graphs=rng.random() < 0.7,
+                    lookahead=rng.random() < 0.7)
+    waiting = list(range(n_requests))
+    requests, cancelled = {}, set()
+    steps = 0
+    while waiting or any(not r.finished for r in requests.values()):
+        while waiting and rng.random() < 0.5:
+            i = waiting.pop(0)
+            requests[i] = engine.submit(prompts[i], sampling=SamplingParams(temperature=0.0),
+                                        max_tokens=new_tokens[i], ignore_eos=True)
+        if requests and rng.random() < 0.03:
+            i = rng.choice(list(requests))
+            if not requests[i].finished:
+                requests[i].cancel()
+                cancelled.add(i)
+        engine.step()
+        steps += 1
+        assert steps < 5000, "the engine makes no progress"
+    engine.sync()
+    engine.runner.check_status()
+    for i, request in requests.items():
+        if i not in cancelled:
+            want = plain_llama.greedy_generate(cfg, weights, prompts[i], new_tokens[i], dtype=torch.float32)
+            assert list(request.output) == want, (i, request.finish_reason)
+    stats = engine.cache.stats()  # everything given back: finished, cancelled and preempted alike
+    assert stats["slots_used"] == 0 and all(group["used"] == 0 for group in stats["groups"])
