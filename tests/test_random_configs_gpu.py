@@ -105,3 +105,52 @@ def test_a_configuration_drawn_at_random(seed, dtype):
             positions = sorted(rows)
             err = plain_llama.max_relative_error(torch.stack([rows[p] for p in positions]), plain[r][positions])
             assert err < TOLERANCE[dtype], (name, r, err, cfg)
+
+
+@pytest.mark.parametrize("seed", [0, 3, 5, 11, 12, 23])
+def test_longer_prompts_reach_the_tensor_core_attention_paths(seed):
+    """bfloat16 at head sizes 64 and 128 with histories of up to 1,500 tokens, three
+    requests advancing together in portions of 1 to 600 tokens: short portions after
+    long histories (keys split over CTAs and merged), portions longer than one tile
+    with odd groups (tiles of 256 rows), single tokens over many keys (splits merged
+    in a cluster), pages of 16, 32 or 64 tokens."""
+    from pulsarlm_b200.cache.manager import CacheManager
+    from pulsarlm_b200.engine.loading import load_model
+    from pulsarlm_b200.engine.runner import ModelRunner
+
+    rng = random.Random(seed)
+    n_kv = rng.choice([1, 2, 4])
+    cfg = {
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": rng.choice([1, 2]),
+        "hidden_size": rng.choice([256, 384, 520]), "num_attention_heads": n_kv * rng.choice([1, 2, 3, 4, 8]),
+        "num_key_value_heads": n_kv, "head_dim": rng.choice([64, 128]), "intermediate_size": rng.choice([512, 1000]),
+        "vocab_size": 512, "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+        "max_position_embeddings": 8192,
+    }
+    weights = tiny.random_weights(cfg, seed, torch.bfloat16)
+    with tempfile.TemporaryDirectory() as folder:
+        model = load_model(tiny.write_model_dir(folder, cfg, weights), "bfloat16", "cuda:0")
+    lengths = [rng.choice([700, 1100, 1500]), rng.choice([300, 900]), rng.choice([40, 200])]
+    requests = {f"r{i}": tiny.random_tokens(cfg, n, 7 * seed + i) for i, n in enumerate(lengths)}
+    plain = {r: plain_llama.forward(cfg, weights, t, dtype=torch.float32) for r, t in requests.items()}
+    fed = {r: 0 for r in requests}
+    live = list(requests)
+    steps = []
+    while live:
+        entries, ends = [], []
+        for r in list(live):
+            t = requests[r]
+            n = min(len(t) - fed[r], rng.choice([1, 1, 2, 13, 100, 129, 256, 300, 600]))
+            entries.append((r, t[fed[r] : fed[r] + n], sorted(set(rng.sample(range(n), min(n, 2)) + [n - 1]))))
+            fed[r] += n
+            if fed[r] >= len(t):
+                ends.append(r)
+                live.remove(r)
+        steps.append((entries, ends))
+    page = rng.choice([16, 32, 64])
+    cache = CacheManager(model.cache_needs(), page, sum(lengths) // page + 8, 4, torch.bfloat16, "cuda:0")
+    got = replay(ModelRunner(model, cache), steps)
+    for r, rows in got.items():
+        positions = sorted(rows)
+        err = plain_llama.max_relative_error(torch.stack([rows[p] for p in positions]), plain[r][positions])
+        assert err < TOLERANCE["bfloat16"], (r, err, cfg)
