@@ -221,3 +221,59 @@ def test_a_layer_reading_another_layers_cache(dtype, tol):
                                        wd[p + "mlp.down_proj.weight"])
     want = plain_llama.rms_norm(x, wd["model.norm.weight"], eps) @ wd["model.embed_tokens.weight"].T
     assert plain_llama.max_relative_error(got, want) < tol
+
+
+@pytest.mark.parametrize("seed", [3, 5, 7, 9])
+def test_windows_at_tensor_core_head_sizes_with_long_histories(seed):
+    """bfloat16, head sizes 64 and 128: layers with windows of 17 to 700 keys beside full
+    ones, two requests of up to 1,300 tokens advancing in portions of 1 to 600 tokens. The
+    windowed groups give pages back as the requests grow; a kernel that read one would
+    raise the status flag, which the replay checks."""
+    import random
+
+    from harness import TOLERANCE, replay
+    from pulsarlm_b200.cache.manager import CacheManager
+    from pulsarlm_b200.engine.runner import ModelRunner
+    from pulsarlm_b200.models.model import Model
+    from pulsarlm_b200.weights.loader import check_tensors
+
+    rng = random.Random(seed)
+    n_kv = rng.choice([1, 2])
+    cfg = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 2,
+           "hidden_size": rng.choice([128, 256]), "num_attention_heads": n_kv * rng.choice([1, 2, 3, 4]),
+           "num_key_value_heads": n_kv, "head_dim": rng.choice([64, 128]), "intermediate_size": 256,
+           "vocab_size": 300, "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+           "max_position_embeddings": 8192}
+    w = tiny.random_weights(cfg, seed, torch.bfloat16)
+    spec = llama_spec(cfg)
+    windows = {rng.choice([0, 1]): rng.choice([17, 64, 100, 129, 300, 700])}
+    if rng.random() < 0.5:
+        windows[1 - list(windows)[0]] = rng.choice([33, 250])
+    for layer, window in windows.items():
+        spec.layers[layer].mixer.params["window"] = window
+    model = Model(spec, torch.bfloat16, DEV)
+    model.load(check_tensors("test", model.tensor_needs(), w, torch.bfloat16, DEV))
+    lengths = [rng.choice([400, 900, 1300]), rng.choice([60, 500])]
+    requests = {f"r{i}": tiny.random_tokens(cfg, n, 7 * seed + i) for i, n in enumerate(lengths)}
+    want = {r: plain_variant(cfg, w, t, spec.order, windows=windows) for r, t in requests.items()}
+    fed = {r: 0 for r in requests}
+    live = list(requests)
+    steps = []
+    while live:
+        entries, ends = [], []
+        for r in list(live):
+            t = requests[r]
+            n = min(len(t) - fed[r], rng.choice([1, 1, 2, 13, 100, 129, 256, 300, 600]))
+            entries.append((r, t[fed[r] : fed[r] + n], sorted(set(rng.sample(range(n), min(n, 2)) + [n - 1]))))
+            fed[r] += n
+            if fed[r] >= len(t):
+                ends.append(r)
+                live.remove(r)
+        steps.append((entries, ends))
+    page = rng.choice([16, 32])
+    cache = CacheManager(model.cache_needs(), page, sum(lengths) // page + 8, 4, torch.bfloat16, DEV)
+    got = replay(ModelRunner(model, cache), steps)
+    for r, rows in got.items():
+        positions = sorted(rows)
+        err = plain_llama.max_relative_error(torch.stack([rows[p] for p in positions]), want[r][positions])
+        assert err < TOLERANCE["bfloat16"], (r, err, cfg, windows)
