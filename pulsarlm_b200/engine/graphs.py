@@ -9,6 +9,8 @@ only where its inputs live differs (fixed device buffers).
 
 from __future__ import annotations
 
+import gc
+
 import numpy as np
 import torch
 
@@ -95,8 +97,18 @@ class GraphedDecode:
         torch.cuda.synchronize()
         self.graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
-        with torch.cuda.graph(self.graph):
-            self._forward()
+        # Nothing else may touch the device while the stream records: above all not the
+        # collector, which could pick this moment to destroy another engine's graphs and
+        # pools (calls that are not permitted during a capture and would invalidate it).
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
+                self._forward()
+        finally:
+            if collecting:
+                gc.enable()
         self.launches = ops.launch_count() - before
 
     def replay(self, device_tokens: torch.Tensor | None = None) -> None:
