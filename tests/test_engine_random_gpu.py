@@ -57,3 +57,46 @@ def test_random_arrivals_under_page_pressure(seed):
             assert list(request.output) == want, (i, request.finish_reason)
     stats = engine.cache.stats()  # everything given back: finished, cancelled and preempted alike
     assert stats["slots_used"] == 0 and all(group["used"] == 0 for group in stats["groups"])
+
+
+@pytest.mark.parametrize("seed", [2, 4, 6, 8, 10, 12])
+def test_seeded_sampling_does_not_depend_on_the_company(seed):
+    """Temperature, top-k and top-p draws with a seed: a request gets the same tokens
+    among others, in portions, preempted and recomputed, with graphs and pipelined
+    steps, as when it runs alone (float32: the logits do not depend on the cutting, the
+    noise is a function of seed and draw count)."""
+    from pulsarlm_b200 import Engine, SamplingParams
+    from pulsarlm_b200.engine.loading import load_model
+
+    rng = random.Random(seed)
+    cfg, page = rng.choice([(tiny.TINY_A, tiny.PAGE_A), (tiny.TINY_B, tiny.PAGE_B)])
+    weights = tiny.random_weights(cfg, seed, torch.float32)
+    with tempfile.TemporaryDirectory() as folder:
+        model = load_model(tiny.write_model_dir(folder, cfg, weights), "float32", "cuda:0")
+    n_requests = rng.choice([3, 5, 8])
+    prompts = [tiny.random_tokens(cfg, rng.choice([1, 4, 20, 33, 70, 120]), seed * 100 + i) for i in range(n_requests)]
+    new_tokens = [rng.choice([1, 3, 9, 20]) for _ in range(n_requests)]
+    params = [SamplingParams(temperature=rng.choice([0.0, 0.7, 1.3]), top_k=rng.choice([0, 0, 5, 50]),
+                             top_p=rng.choice([1.0, 1.0, 0.9, 0.5]), seed=rng.randrange(1 << 40))
+              for _ in range(n_requests)]
+    largest = max(len(p) + n for p, n in zip(prompts, new_tokens))
+    alone = Engine(model, n_pages=-(-largest // page) + 2, page_size=page, max_requests=2, stop_ids=[],
+                   cuda_graphs=False, lookahead=False)
+    want = [alone.generate([p], s, max_tokens=n, ignore_eos=True)[0] for p, s, n in zip(prompts, params, new_tokens)]
+    engine = Engine(model, n_pages=-(-largest // page) + rng.choice([0, 1, 3, 10, 40]), page_size=page,
+                    prefill_tokens_per_step=rng.choice([2, 7, 32, 256]), max_requests=rng.choice([2, 4, 8]),
+                    stop_ids=[], cuda_graphs=rng.random() < 0.7, lookahead=rng.random() < 0.7)
+    waiting = list(range(n_requests))
+    requests = {}
+    steps = 0
+    while waiting or any(not r.finished for r in requests.values()):
+        while waiting and rng.random() < 0.5:
+            i = waiting.pop(0)
+            requests[i] = engine.submit(prompts[i], sampling=params[i], max_tokens=new_tokens[i], ignore_eos=True)
+        engine.step()
+        steps += 1
+        assert steps < 5000, "the engine makes no progress"
+    engine.sync()
+    engine.runner.check_status()
+    for i, request in requests.items():
+        assert list(request.output) == want[i], (i, params[i])
