@@ -100,3 +100,41 @@ def test_seeded_sampling_does_not_depend_on_the_company(seed):
     engine.runner.check_status()
     for i, request in requests.items():
         assert list(request.output) == want[i], (i, params[i])
+
+
+@pytest.mark.parametrize("seed", [1, 9, 17, 58])
+def test_bfloat16_generation_with_graphs_at_tensor_core_head_sizes(seed):
+    """bfloat16, head sizes 64 and 128, one to seventeen requests with prompts of up to
+    900 tokens through `Engine.generate` (scheduler's portions, graph-replayed and
+    pipelined decode steps): bfloat16 may flip a near-tie, so every generated token
+    must be the plain implementation's argmax for its own prefix or within the
+    rounding bar of it."""
+    import plain_llama as plain
+    from pulsarlm_b200 import Engine, SamplingParams
+    from pulsarlm_b200.engine.loading import load_model
+
+    rng = random.Random(seed)
+    n_kv = rng.choice([1, 2, 4])
+    cfg = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": rng.choice([1, 2]),
+           "hidden_size": rng.choice([256, 384]), "num_attention_heads": n_kv * rng.choice([1, 2, 3, 4, 8]),
+           "num_key_value_heads": n_kv, "head_dim": rng.choice([64, 128]), "intermediate_size": 512,
+           "vocab_size": 512, "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+           "max_position_embeddings": 8192}
+    weights = tiny.random_weights(cfg, seed, torch.bfloat16)
+    with tempfile.TemporaryDirectory() as folder:
+        model = load_model(tiny.write_model_dir(folder, cfg, weights), "bfloat16", "cuda:0")
+    n_requests = rng.choice([1, 2, 5, 9, 17])
+    prompts = [tiny.random_tokens(cfg, rng.choice([5, 100, 400, 900]), seed * 50 + i) for i in range(n_requests)]
+    new_tokens = rng.choice([4, 12])
+    page = rng.choice([16, 32])
+    engine = Engine(model, n_pages=sum(len(p) + new_tokens for p in prompts) // page + n_requests + 4, page_size=page,
+                    prefill_tokens_per_step=rng.choice([64, 256, 1024]), max_requests=32, stop_ids=[],
+                    lookahead=rng.random() < 0.7)
+    outputs = engine.generate(prompts, SamplingParams(temperature=0.0), max_tokens=new_tokens, ignore_eos=True)
+    assert engine.runner.graph_steps > 0
+    for prompt, output in zip(prompts, outputs):
+        assert len(output) == new_tokens
+        logits = plain.forward(cfg, weights, list(prompt) + list(output), dtype=torch.float32)
+        for i, token in enumerate(output):
+            row = logits[len(prompt) - 1 + i]
+            assert float((row.max() - row[token]) / row.abs().max()) <= 2e-2, (i, cfg)
