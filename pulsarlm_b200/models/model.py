@@ -43,6 +43,37 @@ class StepBatch:
     host_query_lens: list[int] = dataclasses.field(default_factory=list)
     host_context_lens: list[int] = dataclasses.field(default_factory=list)
     extras: dict = dataclasses.field(default_factory=dict)
+    # What the parts planned for this step on the host (see HostStep): plans[key][name]
+    # is a device tensor for every array a part's plan_step returned under `name`, and
+    # the value itself for everything else. `key` is the part's plan_key().
+    plans: dict = dataclasses.field(default_factory=dict)
+
+
+@dataclasses.dataclass
+class HostStep:
+    """What the host knows of a step before it runs: the sizes of its entries, in batch
+    order (entries of one token first). Parts that need index arrays of their own for
+    a step (tile lists, chunk boundaries, expert offsets) build them from this in
+    `plan_step`; the step function stages what they return with its own arrays and
+    hands it back in `StepBatch.plans`.
+
+    query_lens[e]: tokens of entry e in this step. context_lens[e]: tokens its
+    request holds after the step. first_rows[e]: row of its first token among the
+    step's tokens. A step that is captured once and replayed (`fixed_shape`) is
+    planned anew before every replay: the arrays a part returns must then have shapes
+    that depend only on n_entries and context_bound (the most tokens any entry of a
+    replay may hold), and what it returns besides arrays is kept from the first call,
+    so it must depend on nothing else either."""
+
+    n_entries: int
+    n_tokens: int
+    n_decode: int
+    query_lens: list[int]
+    context_lens: list[int]
+    first_rows: list[int]
+    page_size: int
+    fixed_shape: bool = False
+    context_bound: int | None = None
 
 
 def _all_part_specs(spec: ModelSpec):
@@ -117,6 +148,16 @@ class Model:
                 raise ValueError(f"layer {layer} reads the cache of layer {src}, which keeps none of its own")
         return sources
 
+    def planners(self) -> list:
+        """The parts that plan steps on the host, one per distinct plan_key()."""
+        seen: dict = {}
+        for part in self.parts():
+            key_of = getattr(part, "plan_key", None)
+            key = key_of() if key_of is not None else None
+            if key is not None and key not in seen:
+                seen[key] = part
+        return list(seen.items())
+
     def bind_caches(self, bindings: list) -> None:
         sources = self.cache_sources()
         for layer, b in enumerate(self.blocks):
@@ -130,7 +171,7 @@ class Model:
         [R, vocab] at `batch.want_rows`, or None when none are wanted."""
         if not self.loaded:
             raise RuntimeError("the model has no weights loaded")
-        x = self.embedding.forward(batch.tokens, batch.status)
+        x = self.embedding.forward(batch.tokens, batch)
         delta = None
         for index in self.spec.order:
             x, delta = self.blocks[index].forward(x, delta, batch)

@@ -5,6 +5,7 @@ from __future__ import annotations
 import dataclasses
 import math
 
+import numpy as np
 import torch
 
 from ..kernels import ops
@@ -202,6 +203,58 @@ class Attention(Part):
         self.attend(q, out, table, batch)
         return linear(out.view(tokens, nh * hd), self.o)
 
+    # ------------------------------------------------------------------ planning a step
+    def _kernels(self, dtype: torch.dtype) -> tuple[bool, bool]:
+        """Whether the tensor-core kernels for single tokens and for prompt portions take
+        this layer's shape (asked once)."""
+        if self._decode_kernel is None:
+            self._decode_kernel = ops.attention_decode_supports(
+                self.head_dim, self.n_heads // self.n_kv, self.cache.page_size, dtype)
+            self._prefill_kernel = ops.attention_prefill_supports(self.head_dim, self.cache.page_size, dtype)
+        return self._decode_kernel, self._prefill_kernel
+
+    def plan_key(self):
+        """Layers of equal tiling share one plan: the tile lists depend on the kernels'
+        tile heights only (twice as high when a CTA works on one head: an odd group)."""
+        if self.cache is None:
+            return None
+        wide = (self.n_heads // self.n_kv) % 2 == 1
+        return ("attention", self.cache.page_size, self.head_dim, self.n_heads // self.n_kv, wide,
+                self.ctx.dtype)
+
+    def plan_step(self, step) -> dict:
+        """The tile list of the prompt-portion kernels: int32 [tiles, 4] rows of {first
+        token row, rows, position of the first row, block-table row}, the tiles that read
+        the most keys first; `tiles_wide` the same in tiles twice as high (odd groups, and
+        only when some portion is longer than one narrow tile); `max_keys` the most keys a
+        tile reads; `max_context` the most keys a single decode token reads (in a step that
+        is captured and replayed: the most it may come to read)."""
+        decode_kernel, prefill_kernel = self._kernels(self.ctx.dtype)
+        plan: dict = {"tiles": None, "tiles_wide": None, "max_keys": 0, "max_context": 0}
+        n_decode = step.n_decode if decode_kernel else 0
+        if n_decode:
+            plan["max_context"] = step.context_bound if step.fixed_shape else max(step.context_lens[:n_decode])
+        if not prefill_kernel or step.n_decode == step.n_entries:
+            return plan
+        rows = ops.attention_prefill_tile_rows()
+        wide_rows = ops.attention_prefill_tcgen05_tile_rows(self.n_heads // self.n_kv)
+        tiles, wide_tiles = [], []
+        for e in range(step.n_decode, step.n_entries):
+            n, at = step.query_lens[e], step.first_rows[e]
+            start = step.context_lens[e] - n
+            for r in range(0, n, rows):
+                tiles.append((at + r, min(rows, n - r), start + r, e))
+            if wide_rows > rows:
+                for r in range(0, n, wide_rows):
+                    wide_tiles.append((at + r, min(wide_rows, n - r), start + r, e))
+        tiles.sort(key=lambda t: -(t[2] + t[1]))
+        plan["tiles"] = np.array(tiles, dtype=np.int32).reshape(len(tiles), 4)
+        plan["max_keys"] = max((t[2] + t[1] for t in tiles), default=0)
+        if any(t[1] > rows for t in wide_tiles):
+            wide_tiles.sort(key=lambda t: -(t[2] + t[1]))
+            plan["tiles_wide"] = np.array(wide_tiles, dtype=np.int32).reshape(len(wide_tiles), 4)
+        return plan
+
     def attend(self, q: torch.Tensor, out: torch.Tensor, table: torch.Tensor, batch) -> None:
         """out = attention of q over the cache. The batch's leading `n_decode` tokens
         are single tokens of their requests: in bfloat16 they go to the split-key
@@ -216,14 +269,11 @@ class Attention(Part):
                                self.window, self.scale, batch.status, cache.mass_sum, cache.weight_sum,
                                batch.extras["query_weights"])
             return
-        n_decode = 0
-        if self._decode_kernel is None:
-            self._decode_kernel = ops.attention_decode_supports(
-                self.head_dim, self.n_heads // self.n_kv, cache.page_size, q.dtype)
-        if self._decode_kernel:
-            n_decode = min(int(getattr(batch, "n_decode", 0)), tokens)
+        plan = batch.plans.get(self.plan_key()) or {}
+        decode_kernel, prefill_kernel = self._kernels(q.dtype)
+        n_decode = min(int(batch.n_decode), tokens) if decode_kernel else 0
         if n_decode > 0:
-            max_context = batch.extras.get("max_context") or max(batch.host_context_lens[:n_decode])
+            max_context = plan.get("max_context") or max(batch.host_context_lens[:n_decode])
             if self.window:
                 max_context = min(max_context, self.window + 16)
             splits = decode_splits(n_decode * self.n_kv, max_context, q.device, self.head_dim,
@@ -236,11 +286,8 @@ class Attention(Part):
             ops.attention_decode(q[:n_decode], cache.k_pool, cache.v_pool, table, batch.pos[:n_decode],
                                  batch.entry[:n_decode], out[:n_decode], cache.page_size, self.window, self.scale,
                                  splits, scratch, batch.status)
-        tiles = batch.extras.get("prefill_tiles")
-        if self._prefill_kernel is None:
-            self._prefill_kernel = ops.attention_prefill_supports(self.head_dim, cache.page_size, q.dtype)
-        if n_decode < tokens and self._prefill_kernel and tiles is not None and \
-                n_decode == int(getattr(batch, "n_decode", 0)):
+        tiles = plan.get("tiles")
+        if n_decode < tokens and prefill_kernel and tiles is not None and n_decode == int(batch.n_decode):
             # The tile list covers exactly the tokens after the leading single tokens.
             if self._prefill_tcgen05 is None:
                 self._prefill_tcgen05 = ops.attention_prefill_tcgen05_supports(q, cache.k_pool, cache.page_size)
@@ -248,11 +295,11 @@ class Attention(Part):
                 # Two heads of a kv head share a CTA when the group is even; else a CTA takes one
                 # head, and a tile of twice the rows if the step has portions that long (the two
                 # halves then share the keys; for shorter portions the narrow tiles are ahead).
-                wide = (self.n_heads // self.n_kv) % 2 == 1 and batch.extras.get("prefill_tiles_wide") is not None
+                wide = (self.n_heads // self.n_kv) % 2 == 1 and plan.get("tiles_wide") is not None
                 if wide:
-                    tiles = batch.extras["prefill_tiles_wide"]
+                    tiles = plan["tiles_wide"]
                 ctas = tiles.shape[0] * (self.n_heads if wide or (self.n_heads // self.n_kv) % 2 else self.n_heads // 2)
-                max_keys = int(batch.extras.get("prefill_max_keys") or 0)
+                max_keys = int(plan.get("max_keys") or 0)
                 if self.window:
                     max_keys = min(max_keys, self.window + ops.attention_prefill_tile_rows())
                 splits = prefill_splits(ctas, max_keys, tokens - n_decode, self.n_heads, self.head_dim, q.device)

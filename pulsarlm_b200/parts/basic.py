@@ -115,9 +115,11 @@ class Embedding(Part):
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         self.weight = tensors[self.spec.tensors["weight"]].contiguous()
 
-    def forward(self, tokens: torch.Tensor, status: torch.Tensor | None = None) -> torch.Tensor:
+    def forward(self, tokens: torch.Tensor, batch=None) -> torch.Tensor:
+        """`batch`: the step (an embedding that adds learned positions or scales by a
+        constant of the configuration reads batch.pos); this one uses its status word."""
         x = torch.empty((tokens.numel(), self.hidden), dtype=torch.float32, device=tokens.device)
-        ops.embed(self.weight, tokens, x, status)
+        ops.embed(self.weight, tokens, x, batch.status if batch is not None else None)
         return x
 
 

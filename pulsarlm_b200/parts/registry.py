@@ -8,6 +8,12 @@ Interfaces (duck-typed; the base classes below document them):
 
 * every part:  `tensor_needs(spec) -> {checkpoint name: TensorNeed}` (classmethod),
                `load(tensors)` with the checked tensors, by checkpoint name.
+               Optionally `plan_key()` and `plan_step(host_step)`: a part that needs
+               index arrays of its own for a step returns them (numpy int32 or
+               float32 arrays, by name) from `plan_step`; the step function copies
+               them to the device with its own arrays and the part finds them in
+               `batch.plans[plan_key()]`. Parts with equal keys share one plan.
+* embedding:   `forward(tokens, batch) -> x` fp32 [T, H].
 * norm:        `forward(x, delta=None, rows=None) -> h`: x is the fp32 residual
                stream [T, H]; `delta` (engine dtype) is first added into x in
                place; `rows` (int32) selects rows instead of running all.
@@ -97,6 +103,16 @@ class Part:
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         pass
+
+    def plan_key(self):
+        """A hashable naming this part's per-step plan, or None when it plans nothing.
+        Parts that return equal keys (the same mixer in every layer) are planned once."""
+        return None
+
+    def plan_step(self, step) -> dict:
+        """Host-side planning of one step (see models.model.HostStep): arrays by name,
+        and anything else the part wants to find in `batch.plans[plan_key()]`."""
+        return {}
 
     def param(self, name: str):
         try:

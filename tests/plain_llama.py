@@ -5,12 +5,17 @@ reads config.json keys and tensor names directly and computes every formula
 with dense torch ops on the CPU (float64 by default, so that it is more exact
 than either engine path it judges).
 
-It rests on the formulas of cosmonomic/pulsarlm (each function cites the file
-and lines it restates). The reference's model code cannot be built on a machine
-without a GPU (its ops require CUDA tensors and its sources need a newer
-compiler), so the model as a whole is anchored on the formulas; the RoPE
-frequency table is additionally anchored on the reference's own host code,
-see tests/golden/.
+It restates the formulas of cosmonomic/pulsarlm (each function cites the file
+and lines it restates) and is anchored on the reference's own output part by
+part: the reference's kernel library builds here from its unmodified sources
+(baseline/ref_kernels/build.py), and tests/test_plain.py compares rms_norm, the
+SwiGLU activation, rope_rotate, causal_attention (whole prompts, a portion after a
+cached prefix, a single decode token; sliding window; both RoPE settings),
+page_attention_mass and the argmax tie rule with outputs of those kernels recorded
+on a B200 (tests/golden/reference_kernels.json), and the RoPE frequency table with
+the reference's host code (tests/golden/rope_reference.json). The reference's
+whole-model code (C++23, gcc 15) does not build in this image, so the order of
+the parts in a layer rests on llama.cpp:84-94 as read.
 """
 
 from __future__ import annotations

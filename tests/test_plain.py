@@ -102,3 +102,113 @@ def test_kept_tokens_rules():
     assert plain_llama.kept_tokens(logits, 1.0, 0, 0.3).tolist() == [True, False, False, False, False]
     p = plain_llama.sampling_distribution(logits, 1.0, top_k=2)
     assert torch.allclose(p, torch.tensor([2 / 3, 1 / 3, 0, 0, 0], dtype=torch.float64))
+
+
+# --------------------------------------------------------------------------- the reference's own kernels
+# tests/golden/reference_kernels.json holds outputs of cosmonomic/pulsarlm's CUDA kernels (built
+# unmodified, run on a B200 by tests/golden/make_reference_kernel_golden.py); the inputs are
+# rebuilt here from the same formulas. Bars: the reference's own for these kernels in float32
+# (pulsarlm-core/tests/kernels/test_ops.cpp: 1e-5 on norm and rope, 1e-4 on attention, 1e-3 on mass).
+
+KERNEL_GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_kernels.json")
+
+
+def _kernel_golden():
+    import sys
+
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+    import make_reference_kernel_golden as made
+
+    with open(KERNEL_GOLDEN) as f:
+        return made, json.load(f), made.reference_kernel_inputs()
+
+
+def _llama3(values):
+    if values is None:
+        return None
+    return {"factor": values[0], "low": values[1], "high": values[2], "original": values[3]}
+
+
+def test_rms_norm_matches_reference_kernel():
+    made, golden, inputs = _kernel_golden()
+    for case, packed in zip(inputs["rmsnorm"], golden["rmsnorm"]):
+        want = made.unpack(packed).view_as(case["x"]).double()
+        got = plain_llama.rms_norm(case["x"].double(), case["w"].double(), case["eps"])
+        assert plain_llama.max_relative_error(got, want) < 1e-5
+
+
+def test_silu_times_up_matches_reference_kernel():
+    made, golden, inputs = _kernel_golden()
+    x = inputs["silu_mul"]["x"].double()
+    half = x.shape[1] // 2
+    want = made.unpack(golden["silu_mul"]).view(x.shape[0], half).double()
+    # the activation as swiglu_mlp computes it, with identity projections
+    eye = torch.eye(half, dtype=torch.float64)
+    got = plain_llama.swiglu_mlp(torch.cat([x[:, :half], x[:, half:]], dim=1),
+                                 torch.cat([eye, torch.zeros(half, half, dtype=torch.float64)], dim=1),
+                                 torch.cat([torch.zeros(half, half, dtype=torch.float64), eye], dim=1), eye)
+    assert plain_llama.max_relative_error(got, want) < 1e-5
+
+
+def test_rope_matches_reference_kernel():
+    made, golden, inputs = _kernel_golden()
+    x = inputs["rope"]["x"]  # [heads, positions, head_dim] as the reference's kernel takes it
+    pos = torch.tensor(inputs["rope"]["positions"])
+    for name, settings in made.ROPES.items():
+        inv_freq = plain_llama.rope_inverse_frequency(settings["theta"], x.shape[2], _llama3(settings["llama3"]))
+        got = plain_llama.rope_rotate(x.transpose(0, 1).double(), pos, inv_freq).transpose(0, 1)
+        want = made.unpack(golden["rope"][name]).view_as(x).double()
+        # float32 sine and cosine of angles up to 7e4 radians in the kernel: 1e-5 absolute on values <= 1.5
+        assert (got - want).abs().max() < 1e-5, name
+
+
+def _plain_attention_rows(made, inputs, rope_name, window, scores_out=None):
+    a = made.ATTENTION
+    settings = made.ROPES[rope_name]
+    inv_freq = plain_llama.rope_inverse_frequency(settings["theta"], a["head_dim"], _llama3(settings["llama3"]))
+    scale = a["scale_factor"] / math.sqrt(a["head_dim"])
+    rows = []
+    for seq in inputs["attention"]:
+        pos = torch.arange(seq["length"])
+        q = plain_llama.rope_rotate(seq["q"].double(), pos, inv_freq)
+        k = plain_llama.rope_rotate(seq["k"].double(), pos, inv_freq)
+        out = plain_llama.causal_attention(q, k, seq["v"].double(), scale, window, scores_out)
+        rows.append(out[seq["length"] - seq["chunk"]:])
+    return torch.cat(rows, dim=0)
+
+
+def test_causal_attention_matches_reference_kernel():
+    """Whole prompt, a portion after a cached prefix and a single decode token, over
+    scattered pages, with both RoPE settings and a sliding window: the plain attention
+    (keys rotated before they are stored) against the reference's scalar kernel (keys
+    stored unrotated and rotated as they are read)."""
+    made, golden, inputs = _kernel_golden()
+    a = made.ATTENTION
+    for record in golden["attention"]:
+        got = _plain_attention_rows(made, inputs, record["rope"], record["window"])
+        want = made.unpack(record["out"]).view(-1, a["n_heads"], a["head_dim"]).double()
+        assert got.shape == want.shape
+        assert plain_llama.max_relative_error(got, want) < 1e-4, (record["rope"], record["window"])
+
+
+def test_attention_mass_matches_reference_kernel():
+    made, golden, inputs = _kernel_golden()
+    a = made.ATTENTION
+    record = next(r for r in golden["attention"] if "mass_sum" in r)
+    scores: list = []
+    _plain_attention_rows(made, inputs, record["rope"], record["window"], scores)
+    want_mass = made.unpack(record["mass_sum"]).view(-1, a["n_heads"]).double()
+    want_weight = made.unpack(record["weight_sum"]).double()
+    at = 0
+    for seq, s, pages in zip(inputs["attention"], scores, record["pages_per_sequence"]):
+        first = seq["length"] - seq["chunk"]
+        mass, weight = plain_llama.page_attention_mass(s, [(first, seq["length"])], a["page_size"], a["decay"])
+        assert (mass - want_mass[at:at + pages]).abs().max() < 1e-3 * max(1.0, float(want_mass.abs().max()))
+        assert (weight - want_weight[at:at + pages]).abs().max() < 1e-5
+        at += pages
+
+
+def test_argmax_ties_go_to_the_lower_index_as_in_the_reference_kernel():
+    made, golden, inputs = _kernel_golden()
+    for row, want in zip(inputs["argmax"]["scores"], golden["argmax"]):
+        assert int(torch.nonzero(row == row.max())[0, 0]) == want
