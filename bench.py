@@ -9,11 +9,21 @@ a 2,048-token prompt (real prefill through the engine) and decoding from there.
 host token lists in and host token ids out every step. `prefill`: one 2,048-token
 prompt in one step. `roofline`: bytes the decode step must read (every weight
 once, the cache of the live requests) over its time, against the measured copy
-bandwidth. `points`: decode at batch 1 and 64 (their caches are filled with
-random keys and values instead of being prefilled: a decode step's time does not
-depend on the cache's contents). Weights are random (N(0, 0.02)) and drawn on the
-device; token ids are uniform random. The weights (16 GB) and caches are far
-larger than L2 (126 MB), so no L2 flush is needed between steps.
+bandwidth. `points`: decode at batch 1 and 64 at the same context, and at batch 1,
+8 and 64 at the end of the configuration's context (the K timed steps end at 4,096
+tokens); their caches are filled with random keys and values instead of being
+prefilled: a decode step's time does not depend on the cache's contents. Each has
+its own entry in `rooflines`. Two serving runs through Engine.submit / Engine.step
+follow, each with its own model (`serving`): `mixed_1b`, 64 requests with prompts of
+128 to 4,096 tokens on the Llama-3.2-1B shape, prompts cut into portions of 512
+beside the decoding requests, 512 new tokens each (and the same with a third of the
+pages, so that requests are preempted and recomputed); `serve_13b`, 32 requests of
+1,024 prompt tokens and 512 new tokens on the Llama-2-13B shape. They report
+all tokens per second (prompt and generated, over the whole run) and generated
+tokens per second of the phase in which every request decodes, against the bytes
+such a step must read. Weights are random (N(0, 0.02)) and drawn on the device;
+token ids are uniform random. The weights (16 GB) and caches are far larger than L2
+(126 MB), so no L2 flush is needed between steps.
 """
 
 from __future__ import annotations
@@ -46,6 +56,38 @@ LLAMA31_8B = {
     "rms_norm_eps": 1e-5,
     "tie_word_embeddings": False,
     "max_position_embeddings": 131072,
+}
+LLAMA32_1B = {
+    "architectures": ["LlamaForCausalLM"],
+    "model_type": "llama",
+    "num_hidden_layers": 16,
+    "hidden_size": 2048,
+    "num_attention_heads": 32,
+    "num_key_value_heads": 8,
+    "head_dim": 64,
+    "intermediate_size": 8192,
+    "vocab_size": 128256,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": True,
+    "max_position_embeddings": 131072,
+}
+LLAMA2_13B = {
+    "architectures": ["LlamaForCausalLM"],
+    "model_type": "llama",
+    "num_hidden_layers": 40,
+    "hidden_size": 5120,
+    "num_attention_heads": 40,
+    "num_key_value_heads": 40,
+    "head_dim": 128,
+    "intermediate_size": 13824,
+    "vocab_size": 32000,
+    "rope_theta": 10000.0,
+    "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False,
+    "max_position_embeddings": 4096,
 }
 PROMPT_LEN = 2048
 CONTEXT_LEN = 4096
@@ -183,6 +225,103 @@ def time_decode(engine, ids: list, steps: int, warmup: int, vocab: int):
     return start.elapsed_time(end) / steps, launches
 
 
+def describe(cfg: dict) -> str:
+    return (f"{cfg['num_hidden_layers']} layers, hidden {cfg['hidden_size']}, heads {cfg['num_attention_heads']}/"
+            f"{cfg['num_key_value_heads']}, head_dim {cfg['head_dim']}, intermediate {cfg['intermediate_size']}, "
+            f"vocab {cfg['vocab_size']}, {'tied' if cfg['tie_word_embeddings'] else 'untied'} head")
+
+
+def serve(engine, cfg: dict, prompts: list, max_new: int, pk: dict) -> dict:
+    """Submits every prompt at once and steps the engine until all are done (host token
+    lists in, host token ids out). Times the whole run, and within it the phase in
+    which every request is decoding (from the step after the last prompt ends to the
+    first request's end), whose steps are compared with the bytes they must read."""
+    import torch
+
+    from pulsarlm_b200 import SamplingParams
+
+    greedy = SamplingParams(temperature=0.0)
+    captures_before = engine.runner.graph_captures
+    steps_before = engine.runner.steps
+    preempted_before = engine.scheduler.preemptions
+    torch.cuda.synchronize()
+    t_start = time.perf_counter()
+    requests = [engine.submit(p, sampling=greedy, max_tokens=max_new, ignore_eos=True) for p in prompts]
+    weights = weight_bytes(cfg)
+    per_token = kv_bytes_per_token(cfg)
+    phase = None  # [seconds at start, tokens generated at start, steps, bytes]
+    closed = None
+    while engine.has_work():
+        everyone_decodes = closed is None and all(r.output and not r.finished for r in requests)
+        if everyone_decodes and phase is None:
+            engine.sync()
+            torch.cuda.synchronize()
+            phase = [time.perf_counter(), sum(len(r.output) for r in requests), 0, 0.0]
+        elif phase is not None and closed is None and not everyone_decodes:
+            engine.sync()
+            torch.cuda.synchronize()
+            closed = (time.perf_counter(), sum(len(r.output) for r in requests))
+        if phase is not None and closed is None:
+            phase[2] += 1
+            phase[3] += weights + per_token * sum(len(r.prompt) + len(r.output) for r in requests)
+        engine.step()
+    engine.sync()
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t_start
+    engine.runner.check_status()
+    assert all(r.finish_reason == "length" and len(r.output) == max_new for r in requests), "a request fell short"
+    prompt_tokens = sum(len(p) for p in prompts)
+    generated = sum(len(r.output) for r in requests)
+    out = {"requests": len(prompts), "prompt_tokens": prompt_tokens, "generated_tokens": generated,
+           "seconds": seconds, "tok_s": (prompt_tokens + generated) / seconds,
+           "steps": engine.runner.steps - steps_before,
+           "preemptions": engine.scheduler.preemptions - preempted_before,
+           "graph_captures_in_run": engine.runner.graph_captures - captures_before}
+    if phase is not None and closed is not None and phase[2] > 0:
+        span = closed[0] - phase[0]
+        bytes_per_step = phase[3] / phase[2]
+        ms = span / phase[2] * 1e3
+        out.update({"decode_tok_s": (closed[1] - phase[1]) / span, "decode_steps": phase[2], "decode_ms_per_step": ms,
+                    "decode_bytes_per_step": bytes_per_step,
+                    "decode_floor_ms": bytes_per_step / (pk["hbm_gbs"] * 1e9) * 1e3,
+                    "decode_frac": bytes_per_step / (ms / 1e3) / 1e9 / pk["hbm_gbs"]})
+    return out
+
+
+def run_serving(name: str, cfg: dict, lengths: list, max_new: int, pk: dict, tight: bool) -> dict:
+    """Builds the model, serves a short warm-up pass over the same prompts (library set-up,
+    the decode steps' captures), then the timed pass; with `tight`, once more with a third
+    of the pages, so that the scheduler has to preempt and recompute."""
+    import gc
+
+    import torch
+
+    from pulsarlm_b200 import Engine
+
+    gen = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist() for n in lengths]
+    need_pages = sum(-(-(n + max_new + 2) // PAGE_SIZE) for n in lengths)
+    engine = Engine(cfg, dtype="bfloat16", device="cuda:0", n_pages=need_pages + 64, page_size=PAGE_SIZE,
+                    prefill_tokens_per_step=512, max_requests=len(lengths), seed=0)
+    serve(engine, cfg, prompts, min(32, max_new), pk)
+    result = serve(engine, cfg, prompts, max_new, pk)
+    result["model"] = describe(cfg)
+    result["prefill_tokens_per_step"] = 512
+    if tight:
+        small = Engine(engine.model, n_pages=max(need_pages // 3, -(-(max(lengths) + max_new + 2) // PAGE_SIZE) + 1),
+                       page_size=PAGE_SIZE, prefill_tokens_per_step=512, max_requests=len(lengths))
+        pressed = serve(small, cfg, prompts, min(128, max_new), pk)
+        result["tight_pages"] = {k: pressed[k] for k in ("tok_s", "seconds", "steps", "preemptions",
+                                                          "generated_tokens")}
+        result["tight_pages"]["pages"] = small.cache.n_pages
+        result["tight_pages"]["pages_for_everyone"] = need_pages
+        del small
+    del engine
+    gc.collect()
+    torch.cuda.empty_cache()
+    return result
+
+
 def run_ours(args) -> dict:
     import torch
 
@@ -195,7 +334,9 @@ def run_ours(args) -> dict:
     torch.manual_seed(0)
     device = "cuda:0"
     max_batch = max(64, batch)
-    tokens_room = max_batch * (PROMPT_LEN + 2 * (args.steps + args.warmup) + 128) + 4 * PROMPT_LEN
+    phases = set(args.phases.split(","))
+    per_request = CONTEXT_LEN + 64 if "ctx4096" in phases else PROMPT_LEN + 2 * (args.steps + args.warmup) + 128
+    tokens_room = max_batch * per_request + 4 * PROMPT_LEN
     tokens_room = max(tokens_room, args.prefill_tokens + 4 * PROMPT_LEN)
     n_pages = -(-tokens_room // PAGE_SIZE)
     t0 = time.time()
@@ -207,9 +348,23 @@ def run_ours(args) -> dict:
     gen = torch.Generator().manual_seed(1)
     setup_s = time.time() - t0
 
-    phases = set(args.phases.split(","))
     prefill = e2e = None
     points: dict = {}
+    rooflines: dict = {}
+    serving: dict = {}
+
+    def decode_point(name: str, b: int, first_context: int, steps: int) -> None:
+        ids = fill_cache(engine, b, first_context, name)
+        ms, _ = time_decode(engine, ids, steps, args.warmup, vocab)
+        mid_context = first_context + args.warmup + steps / 2
+        step_bytes = weight_bytes(cfg) + b * mid_context * kv_bytes_per_token(cfg)
+        points[name] = b / (ms / 1e3)
+        rooflines[name] = {"ms": ms, "context": mid_context, "bytes_per_step": step_bytes,
+                           "achieved": step_bytes / (ms / 1e3) / 1e9,
+                           "frac": step_bytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"]}
+        for rid in ids:
+            engine.cache.close(rid)
+
     ms_per_step, launches, achieved, step_bytes = None, 0, None, None
     clocks = ClockSampler()
 
@@ -275,11 +430,7 @@ def run_ours(args) -> dict:
     # ---- other batch sizes.
     if "points" in phases:
         for b in (1, 64):
-            ids = fill_cache(engine, b, PROMPT_LEN, f"b{b}")
-            ms, _ = time_decode(engine, ids, max(8, args.steps // 2), args.warmup, vocab)
-            points[f"decode_b{b}"] = b / (ms / 1e3)
-            for rid in ids:
-                engine.cache.close(rid)
+            decode_point(f"decode_b{b}", b, PROMPT_LEN, max(8, args.steps // 2))
 
         # a long prompt in the default portions: 8,192 tokens, 256 a step (tokens a second)
         long_prompt = torch.randint(0, vocab, (4 * PROMPT_LEN,), generator=gen).tolist()
@@ -308,6 +459,34 @@ def run_ours(args) -> dict:
             served.sync()
             points["first_token_ms_2048_by_256"] = (time.perf_counter() - t_start) * 1e3
 
+    # ---- the end of the configuration's context: the timed steps end at 4,096 tokens.
+    if "ctx4096" in phases:
+        steps = max(8, args.steps // 2)
+        for b in (1, 8, 64):
+            decode_point(f"decode_b{b}_ctx4096", b, CONTEXT_LEN - steps - args.warmup, steps)
+
+    # ---- serving runs on the other two shapes, each with its own model.
+    if phases & {"mixed_1b", "serve_13b"}:
+        import gc
+
+        served = None
+        del engine
+        gc.collect()
+        torch.cuda.empty_cache()
+        if "mixed_1b" in phases:
+            lengths = torch.randint(128, 4097, (64,), generator=torch.Generator().manual_seed(3)).tolist()
+            serving["mixed_1b"] = run_serving("mixed_1b", LLAMA32_1B, lengths, 512, pk, tight=True)
+        if "serve_13b" in phases:
+            serving["serve_13b"] = run_serving("serve_13b", LLAMA2_13B, [1024] * 32, 512, pk, tight=False)
+        for name, run in serving.items():
+            points[f"{name}_tok_s"] = run["tok_s"]
+            if "decode_tok_s" in run:
+                points[f"{name}_decode_tok_s"] = run["decode_tok_s"]
+                rooflines[f"{name}_decode"] = {"ms": run["decode_ms_per_step"],
+                                               "bytes_per_step": run["decode_bytes_per_step"],
+                                               "achieved": run["decode_bytes_per_step"] / run["decode_ms_per_step"] / 1e6,
+                                               "frac": run["decode_frac"]}
+
     clock_summary = clocks.summary()
     return {
         "metric": "decode tok/s at batch 8 (Llama-3.1-8B shape, 2,048-token prompts)",
@@ -332,6 +511,8 @@ def run_ours(args) -> dict:
             "decode_context_start": PROMPT_LEN + args.warmup, "page_size": PAGE_SIZE,
             "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 16 GB)",
             "peaks": pk["source"],
+            "mixed_1b_model": "Llama-3.2-1B shape: " + describe(LLAMA32_1B),
+            "serve_13b_model": "Llama-2-13B shape: " + describe(LLAMA2_13B),
         },
         "e2e": e2e,
         "gpu_launches": launches,
@@ -339,6 +520,8 @@ def run_ours(args) -> dict:
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"] if achieved else None, "bytes_per_step": step_bytes},
         "points": points,
+        "rooflines": rooflines,
+        "serving": serving,
         "clocks": {"sm_mhz": clock_summary["sm_mhz"], "sm_max_mhz": clock_summary["sm_max_mhz"],
                    "reasons": clock_summary["reasons"]},
         "setup_s": setup_s,
@@ -355,8 +538,9 @@ def main() -> int:
     p.add_argument("--layers", type=int, default=32, help="fewer layers than the model's 32 (named in config)")
     p.add_argument("--prefill_tokens", type=int, default=PROMPT_LEN,
                    help="length of the prompt of the prefill phase (the contract's figure is the default's)")
-    p.add_argument("--phases", default="prefill,e2e,decode,points",
-                   help="which measurements to run (a profiler run wants one): prefill,e2e,decode,points")
+    p.add_argument("--phases", default="prefill,e2e,decode,points,ctx4096,mixed_1b,serve_13b",
+                   help="which measurements to run (a profiler run wants one): "
+                        "prefill,e2e,decode,points,ctx4096,mixed_1b,serve_13b")
     args = p.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

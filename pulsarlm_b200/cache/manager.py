@@ -3,7 +3,8 @@ request, and fixed-size state slots.
 
 Layers whose mixers ask for the same KVCacheNeed (kv heads, head size, window)
 form a group. A group has its own page pool: one tensor
-[layers in group, pages, 2 (K, V), kv heads, page size, head size], so one page
+[layers in group, pages + 1, 2 (K, V), kv heads, page size, head size] (the last
+page is never handed out: padding rows of captured steps use it), so one page
 id holds `page_size` tokens of every layer of the group, and a request has one
 block table per group. Groups with a window give pages back as soon as every
 token in them is out of every future query's reach. Mixers that ask for a
@@ -88,9 +89,14 @@ class CacheManager:
         self.mass_decay = mass_decay
         self.page_size = page_size
         self.n_pages = n_pages
+        # One more page than the pools hand out: the padding page, which no request ever
+        # holds. Rows that pad a captured decode step to its size write and read there.
+        self.n_physical_pages = n_pages + 1
+        self.pad_page = n_pages
         self.max_requests = max_requests
         self.dtype = dtype
         self.device = torch.device(device) if device is not None else None
+        self.n_layers = len(needs)
         self.groups: list[_Group] = []
         self.layer_group: dict[int, int] = {}
         self.state_layers: dict[int, StateNeed] = {}
@@ -113,10 +119,10 @@ class CacheManager:
             for group in self.groups:
                 n = group.need
                 group.tensor = torch.zeros(
-                    (len(group.layers), n_pages, 2, n.n_kv_heads, page_size, n.head_dim), dtype=dtype, device=device)
+                    (len(group.layers), n_pages + 1, 2, n.n_kv_heads, page_size, n.head_dim), dtype=dtype, device=device)
             if mass_decay is not None:
                 for group in self.groups:
-                    shape = (len(group.layers), n_pages, max(1, group.need.n_heads))
+                    shape = (len(group.layers), n_pages + 1, max(1, group.need.n_heads))
                     group.mass_sum = torch.zeros(shape, dtype=torch.float32, device=device)
                     group.step_mass = torch.zeros(shape, dtype=torch.float32, device=device)
                     group.weight_sum = torch.zeros(shape[:2], dtype=torch.float32, device=device)
@@ -179,7 +185,7 @@ class CacheManager:
     # ------------------------------------------------------------------ bindings
     def bindings(self) -> list:
         """Per layer: KVBinding, StateBinding or None, for `Model.bind_caches`."""
-        n_layers = max([*self.layer_group, *self.state_layers, -1]) + 1
+        n_layers = self.n_layers
         out: list = [None] * n_layers
         for layer, g in self.layer_group.items():
             group = self.groups[g]

@@ -4,8 +4,11 @@ Commands and options follow the reference's CLI where it has them
 (pulsarlm/src/pulsarlm/cli/__init__.py:179-340; its option names use
 underscores): `chat MODEL --system --temperature --top_p --top_k --dtype
 --kv_cache_gib --prefill_tokens_per_step --device`. Added for an engine without
-a model catalogue: `generate` (token ids in, token ids out), `models random`
-(write a random model folder) and `replay` (trace replay).
+a model catalogue: `generate` (token ids in, token ids out), `bench` (tokens a
+second of a batch of random prompts), `models random` (write a random model
+folder) and `replay` (trace replay). Wherever a model folder is taken,
+`--random_weights SEED --config FILE` stands for one: the model FILE (a
+config.json) describes, with weights drawn from SEED on the device.
 """
 
 from __future__ import annotations
@@ -17,7 +20,11 @@ import sys
 
 
 def _engine_options(p: argparse.ArgumentParser) -> None:
-    p.add_argument("model", help="model folder (config.json, model.safetensors[, tokenizer.json])")
+    p.add_argument("model", nargs="?", default=None,
+                   help="model folder (config.json, model.safetensors[, tokenizer.json])")
+    p.add_argument("--random_weights", "--random-weights", type=int, default=None, metavar="SEED",
+                   help="instead of a model folder: random weights drawn from this seed (needs --config)")
+    p.add_argument("--config", default=None, help="with --random_weights: the config.json that gives the sizes")
     p.add_argument("--device", default="cuda:0", help="CUDA device to run on")
     p.add_argument("--dtype", default="bfloat16", choices=["float32", "bfloat16"], help="weight and KV dtype")
     p.add_argument("--kv_cache_gib", type=float, default=4.0, help="size of the KV cache pool in GiB")
@@ -53,6 +60,13 @@ def build_parser() -> argparse.ArgumentParser:
     gen.add_argument("--prompt", action="append", default=[], help="text prompt (needs tokenizer.json)")
     gen.add_argument("--ignore_eos", action="store_true", help="do not stop at eos_token_id")
 
+    bench = sub.add_parser("bench", help="tokens a second of a batch of random prompts")
+    _engine_options(bench)
+    bench.add_argument("--batch", type=int, default=8, help="requests submitted at once")
+    bench.add_argument("--prompt_len", type=int, default=512, help="tokens of every prompt")
+    bench.add_argument("--new_tokens", type=int, default=128, help="tokens generated per request")
+    bench.add_argument("--seed", type=int, default=0, help="seed of the prompts")
+
     models = sub.add_parser("models", help="model folders")
     msub = models.add_subparsers(dest="models_command", required=True)
     rnd = msub.add_parser("random", help="write a model folder with random weights")
@@ -79,11 +93,72 @@ def _load_tokenizer(model_dir: str):
     return Tokenizer.from_file(path)
 
 
-def _make_engine(args):
+class UsageError(ValueError):
+    pass
+
+
+def _model_argument(args):
+    """The model folder, or the configuration to draw random weights for."""
+    if args.random_weights is not None:
+        if args.model is not None or args.config is None:
+            raise UsageError("--random_weights SEED takes --config FILE and no model folder")
+        with open(args.config, "r", encoding="utf-8") as f:
+            return json.load(f), args.random_weights
+    if args.model is None:
+        raise UsageError("give a model folder, or --random_weights SEED --config FILE")
+    if args.config is not None:
+        raise UsageError("--config goes with --random_weights")
+    return args.model, None
+
+
+def _make_engine(args, **more):
     from .engine.engine import Engine
 
-    return Engine(args.model, dtype=args.dtype, device=args.device, kv_cache_gib=args.kv_cache_gib,
-                  page_size=args.page_size, prefill_tokens_per_step=args.prefill_tokens_per_step)
+    model, seed = _model_argument(args)
+    return Engine(model, dtype=args.dtype, device=args.device, kv_cache_gib=args.kv_cache_gib,
+                  page_size=args.page_size, prefill_tokens_per_step=args.prefill_tokens_per_step, seed=seed, **more)
+
+
+def run_bench(args) -> int:
+    """Submits `batch` prompts of `prompt_len` random token ids, generates `new_tokens`
+    for each (stop tokens ignored) and prints one JSON line: tokens a second over the
+    whole run, and of the prompt phase and the decode phase apart (host clock around
+    device synchronisations; a warm-up pass runs first)."""
+    import time
+
+    import torch
+
+    from .sampling.params import SamplingParams
+
+    engine = _make_engine(args, max_requests=max(1, args.batch))
+    gen = torch.Generator().manual_seed(args.seed)
+    prompts = [torch.randint(0, engine.vocab_size, (args.prompt_len,), generator=gen).tolist()
+               for _ in range(args.batch)]
+    greedy = SamplingParams(temperature=0.0)
+    record = {}
+    for attempt in ("warm-up", "timed"):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        requests = [engine.submit(p, sampling=greedy, max_tokens=args.new_tokens, ignore_eos=True) for p in prompts]
+        while any(not r.output and not r.finished for r in requests):
+            engine.step()
+        engine.sync()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        while engine.has_work():
+            engine.step()
+        engine.sync()
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        generated = sum(len(r.output) for r in requests)
+        record = {"batch": args.batch, "prompt_len": args.prompt_len, "new_tokens": args.new_tokens,
+                  "dtype": args.dtype, "prompt_tok_s": args.batch * args.prompt_len / (t1 - t0),
+                  "decode_tok_s": (generated - args.batch) / (t2 - t1) if t2 > t1 and generated > args.batch else None,
+                  "tok_s": (args.batch * args.prompt_len + generated) / (t2 - t0), "seconds": t2 - t0,
+                  "preemptions": engine.scheduler.preemptions}
+    engine.runner.check_status()
+    print(json.dumps(record))
+    return 0
 
 
 def _sampling(args):
@@ -105,7 +180,7 @@ def run_chat(args) -> int:
     from .engine.engine import complete
 
     engine = _make_engine(args)
-    tokenizer = _load_tokenizer(args.model)
+    tokenizer = _load_tokenizer(args.model) if args.model else None
     sampling = _sampling(args)
     history: list[int] = []
     if tokenizer is None:
@@ -161,7 +236,7 @@ def run_chat(args) -> int:
 
 def run_generate(args) -> int:
     engine = _make_engine(args)
-    tokenizer = _load_tokenizer(args.model)
+    tokenizer = _load_tokenizer(args.model) if args.model else None
     prompts = [[int(t) for t in ids.replace(",", " ").split()] for ids in args.prompt_ids]
     if args.prompt:
         if tokenizer is None:
@@ -211,13 +286,15 @@ def main(argv=None) -> int:
             return run_chat(args)
         if args.command == "generate":
             return run_generate(args)
+        if args.command == "bench":
+            return run_bench(args)
         if args.command == "models":
             return run_models(args)
         if args.command == "replay":
             from .engine.trace import run
 
             return run(args.rest)
-    except (ConfigError, WeightsError) as error:
+    except (ConfigError, WeightsError, UsageError) as error:
         print(f"error: {error}", file=sys.stderr)
         return 1
     return 2

@@ -682,9 +682,12 @@ PL_API int pl_attention_decode_static(const void* q, int64_t q_row_stride, const
                                       const int32_t* entry, void* out, int64_t out_row_stride, int n_tokens,
                                       int n_heads, int n_kv_heads, int head_dim, int window, float scale,
                                       int n_splits, int32_t* status, cudaStream_t stream) {
-    PL_REQUIRE(n_tokens >= 0 && n_heads > 0 && head_dim > 0 && n_splits >= 1,
-               "attention_decode_static: bad sizes tokens=%d heads=%d head_dim=%d splits=%d", n_tokens, n_heads,
-               head_dim, n_splits);
+    // The same limits as the launcher's, checked before the sizes are multiplied: with them
+    // the product below stays far inside 64 bits.
+    PL_REQUIRE(n_tokens >= 0 && n_tokens <= 65535 && n_heads > 0 && n_heads <= 65535 && n_kv_heads > 0 &&
+                   n_kv_heads <= 65535 && (head_dim == 64 || head_dim == 128) && n_splits >= 1 && n_splits <= 65535,
+               "attention_decode_static: bad sizes tokens=%d heads=%d kv_heads=%d head_dim=%d splits=%d (at most 65535 "
+               "each; head size 64 or 128)", n_tokens, n_heads, n_kv_heads, head_dim, n_splits);
     const int64_t needed = pl_attention_decode_scratch_floats(n_tokens, n_heads, head_dim, n_splits);
     PL_REQUIRE(needed <= PL_STATIC_SCRATCH_FLOATS,
                "attention_decode_static: %d tokens x %d heads x %d splits need %lld floats of scratch, the built-in "

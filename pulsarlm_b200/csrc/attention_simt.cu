@@ -71,9 +71,9 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
                                       const int32_t* __restrict__ table, int table_width,
                                       const int32_t* __restrict__ pos, const int32_t* __restrict__ entry,
                                       scalar_t* __restrict__ out, int64_t out_row_stride, int n_heads, int group,
-                                      int head_dim, int window, float scale, float* __restrict__ mass_sum,
-                                      float* __restrict__ weight_sum, const float* __restrict__ query_weights,
-                                      int32_t* status) {
+                                      int head_dim, int window, float scale, float softcap,
+                                      float* __restrict__ mass_sum, float* __restrict__ weight_sum,
+                                      const float* __restrict__ query_weights, int32_t* status) {
     extern __shared__ float q_shared[];  // [warps][head_dim]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const int t = blockIdx.x;
@@ -128,6 +128,9 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
                     offset = page * page_stride + kv_head * head_stride +
                         static_cast<int64_t>(j % page_size) * head_dim;
                     s = dot_row<scalar_t>(qs, k_pool + offset, head_dim) * scale;
+                    if (softcap > 0.0f) {
+                        s = softcap * tanhf(s / softcap);  // scores squashed into (-cap, cap) before the softmax
+                    }
                 } else if (status != nullptr) {
                     atomicOr(status, 4);
                 }
@@ -202,13 +205,14 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
 // n_heads] and weight_sum [n_pages] (fp32, may be nullptr) are added to: for every
 // page a query attends, query_weights[t] (1 when nullptr) times the query's largest
 // scaled score in the page, per head, and the weight itself once per page
-// (pulsarlm-core/inc/pulsarlm/kernels/ops.hpp:150-160).
+// (pulsarlm-core/inc/pulsarlm/kernels/ops.hpp:150-160). softcap > 0: every scaled
+// score s becomes softcap * tanh(s / softcap) before the softmax (0: off).
 PL_API int pl_attention_simt(const void* q, int64_t q_row_stride, const void* k_pool, const void* v_pool,
                              int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
                              const int32_t* table, int table_width, const int32_t* pos, const int32_t* entry,
                              void* out, int64_t out_row_stride, int n_tokens, int n_heads, int n_kv_heads,
-                             int head_dim, int window, float scale, int dtype, float* mass_sum, float* weight_sum,
-                             const float* query_weights, int32_t* status, cudaStream_t stream) {
+                             int head_dim, int window, float scale, float softcap, int dtype, float* mass_sum,
+                             float* weight_sum, const float* query_weights, int32_t* status, cudaStream_t stream) {
     PL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && head_dim > 0 && page_size > 0,
                "attention: bad sizes tokens=%d heads=%d kv_heads=%d head_dim=%d page=%d", n_tokens, n_heads,
                n_kv_heads, head_dim, page_size);
@@ -230,7 +234,7 @@ PL_API int pl_attention_simt(const void* q, int64_t q_row_stride, const void* k_
             static_cast<const scalar_t*>(q), q_row_stride, static_cast<const scalar_t*>(k_pool),
             static_cast<const scalar_t*>(v_pool), page_stride, head_stride, page_size, n_pages, table, table_width,
             pos, entry, static_cast<scalar_t*>(out), out_row_stride, n_heads, group, head_dim, window, scale,
-            mass_sum, weight_sum, query_weights, status);
+            softcap, mass_sum, weight_sum, query_weights, status);
     });
     PL_CHECK_LAUNCH("attention");
     return 0;

@@ -23,7 +23,9 @@
 //    launched. Use fewer splits, or fewer tokens per call.
 //  * The first call on each device looks up the array's device address (with that
 //    device current) and remembers it. Make that first call outside any stream
-//    capture.
+//    capture, and from one host thread: the remembered address is written without
+//    a lock (two threads racing on the first call would both look it up and store
+//    the same value, which is harmless but not guaranteed by the language).
 //  * All calls share the one array, and it keeps what the last call left in it.
 //    Nothing in it needs to start at zero: every partial a call reads was written
 //    by that same call. But two calls that overlap on the GPU (different streams,

@@ -4,7 +4,11 @@
 // the token's place in the paged cache (keys are stored rotated: positions are
 // absolute and never change). The angle pos * f_j is formed in fp64 from an fp64
 // table, reduced to (-pi, pi] in fp64, and only then rounded to fp32 for sincosf;
-// the rotation itself is fp32. The reference rotates q in
+// the rotation itself is fp32. Optionally each q head and each k head is first
+// normalised over its head_dim (x * rsqrt(mean(x^2) + eps) * weight[d], fp32 weights
+// shared by all heads; statistics and product in fp32, one rounding when the rotated
+// value is stored): the per-head q/k norm some decoders of this family put before the
+// rotation. The reference rotates q in
 // pulsarlm-core/src/kernels/rope.cu:33-84 and writes k, v in
 // src/kernels/paged_attention.cu:52-98.
 #include "common.cuh"
@@ -34,8 +38,9 @@ __global__ void rope_kv_write_kernel(scalar_t* __restrict__ q, const scalar_t* _
                                      scalar_t* __restrict__ k_pool, scalar_t* __restrict__ v_pool,
                                      int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
                                      const double* __restrict__ inv_freq, int rotary, int n_heads, int n_kv_heads,
-                                     int head_dim, int heads_per_block, int32_t* status) {
-    extern __shared__ float sincos[];  // [rotary/2] cos then [rotary/2] sin
+                                     int head_dim, int heads_per_block, const float* __restrict__ q_norm,
+                                     const float* __restrict__ k_norm, float norm_eps, int32_t* status) {
+    extern __shared__ float sincos[];  // [rotary/2] cos, [rotary/2] sin, then [heads_per_block] norm factors
     pl_grid_trigger();  // positions are step inputs: the angles need not wait for the projection
     const int t = blockIdx.x;
     const int p = pos[t];
@@ -61,16 +66,53 @@ __global__ void rope_kv_write_kernel(scalar_t* __restrict__ q, const scalar_t* _
         }
     }
     pl_grid_wait();
+    float* factor = sincos + rotary;  // per slot of this block: rsqrt(mean(x^2) + eps), or 1
+    if (q_norm != nullptr || k_norm != nullptr) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+        for (int slot = slot0 + warp; slot < slot1; slot += warps) {
+            const bool is_q = slot < n_heads;
+            float sum = 0.0f;
+            if (is_q ? q_norm != nullptr : k_norm != nullptr) {
+                const scalar_t* x = is_q ? q + t * row_stride + static_cast<int64_t>(slot) * head_dim
+                                         : k + t * row_stride + static_cast<int64_t>(slot - n_heads) * head_dim;
+                for (int d = lane; d < head_dim; d += 32) {
+                    const float value = pl_load(x + d);
+                    sum = fmaf(value, value, sum);
+                }
+                sum = pl_warp_sum(sum);
+                if (lane == 0) {
+                    factor[slot - slot0] = rsqrtf(sum / static_cast<float>(head_dim) + norm_eps);
+                }
+            } else if (lane == 0) {
+                factor[slot - slot0] = 1.0f;
+            }
+        }
+    }
     __syncthreads();
 
     const int pairs = head_dim - half;  // per head: `half` rotated pairs, then the unrotated dims
     for (int idx = threadIdx.x; idx < (slot1 - slot0) * pairs; idx += blockDim.x) {
         const int slot = slot0 + idx / pairs, j = idx % pairs;
         if (slot < n_heads) {
+            scalar_t* x = q + t * row_stride + static_cast<int64_t>(slot) * head_dim;
+            if (q_norm != nullptr) {
+                const float r = factor[slot - slot0];
+                if (inv_freq == nullptr || j >= half) {  // unrotated dims: normalised only
+                    const int d0 = j >= half ? j + half : j;
+                    pl_store(x + d0, pl_load(x + d0) * r * q_norm[d0]);
+                    if (j < half) {
+                        pl_store(x + j + half, pl_load(x + j + half) * r * q_norm[j + half]);
+                    }
+                    continue;
+                }
+                const float lo = pl_load(x + j) * r * q_norm[j], hi = pl_load(x + j + half) * r * q_norm[j + half];
+                pl_store(x + j, lo * cs[j] - hi * sn[j]);
+                pl_store(x + j + half, hi * cs[j] + lo * sn[j]);
+                continue;
+            }
             if (inv_freq == nullptr || j >= half) {
                 continue;  // q passes through
             }
-            scalar_t* x = q + t * row_stride + static_cast<int64_t>(slot) * head_dim;
             const float lo = pl_load(x + j), hi = pl_load(x + j + half);
             pl_store(x + j, lo * cs[j] - hi * sn[j]);
             pl_store(x + j + half, hi * cs[j] + lo * sn[j]);
@@ -79,11 +121,19 @@ __global__ void rope_kv_write_kernel(scalar_t* __restrict__ q, const scalar_t* _
             const scalar_t* x = k + t * row_stride + static_cast<int64_t>(h) * head_dim;
             const scalar_t* y = v + t * row_stride + static_cast<int64_t>(h) * head_dim;
             const int64_t at = page * page_stride + h * head_stride + static_cast<int64_t>(p % page_size) * head_dim;
+            const float r = k_norm != nullptr ? factor[slot - slot0] : 1.0f;
             if (j < half) {
-                const float lo = pl_load(x + j), hi = pl_load(x + j + half);
+                float lo = pl_load(x + j), hi = pl_load(x + j + half);
+                if (k_norm != nullptr) {
+                    lo *= r * k_norm[j];
+                    hi *= r * k_norm[j + half];
+                }
                 if (inv_freq != nullptr) {
                     pl_store(k_pool + at + j, lo * cs[j] - hi * sn[j]);
                     pl_store(k_pool + at + j + half, hi * cs[j] + lo * sn[j]);
+                } else if (k_norm != nullptr) {
+                    pl_store(k_pool + at + j, lo);
+                    pl_store(k_pool + at + j + half, hi);
                 } else {
                     k_pool[at + j] = x[j];
                     k_pool[at + j + half] = x[j + half];
@@ -92,7 +142,11 @@ __global__ void rope_kv_write_kernel(scalar_t* __restrict__ q, const scalar_t* _
                 v_pool[at + j + half] = y[j + half];
             } else {
                 const int d = j + half;  // dims rotary .. head_dim-1
-                k_pool[at + d] = x[d];
+                if (k_norm != nullptr) {
+                    pl_store(k_pool + at + d, pl_load(x + d) * r * k_norm[d]);
+                } else {
+                    k_pool[at + d] = x[d];
+                }
                 v_pool[at + d] = y[d];
             }
         }
@@ -109,7 +163,9 @@ __global__ void rope_kv_write_vec_kernel(scalar_t* __restrict__ q, const scalar_
                                          scalar_t* __restrict__ k_pool, scalar_t* __restrict__ v_pool,
                                          int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
                                          const double* __restrict__ inv_freq, int rotary, int n_heads,
-                                         int n_kv_heads, int head_dim, int heads_per_block, int32_t* status) {
+                                         int n_kv_heads, int head_dim, int heads_per_block,
+                                         const float* __restrict__ q_norm, const float* __restrict__ k_norm,
+                                         float norm_eps, int32_t* status) {
     extern __shared__ float sincos[];
     pl_grid_trigger();
     const int t = blockIdx.x;
@@ -136,6 +192,28 @@ __global__ void rope_kv_write_vec_kernel(scalar_t* __restrict__ q, const scalar_
         }
     }
     pl_grid_wait();
+    float* factor = sincos + rotary;  // per slot of this block: rsqrt(mean(x^2) + eps), or 1
+    if (q_norm != nullptr || k_norm != nullptr) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+        for (int slot = slot0 + warp; slot < slot1; slot += warps) {
+            const bool is_q = slot < n_heads;
+            float sum = 0.0f;
+            if (is_q ? q_norm != nullptr : k_norm != nullptr) {
+                const scalar_t* x = is_q ? q + t * row_stride + static_cast<int64_t>(slot) * head_dim
+                                         : k + t * row_stride + static_cast<int64_t>(slot - n_heads) * head_dim;
+                for (int d = lane; d < head_dim; d += 32) {
+                    const float value = pl_load(x + d);
+                    sum = fmaf(value, value, sum);
+                }
+                sum = pl_warp_sum(sum);
+                if (lane == 0) {
+                    factor[slot - slot0] = rsqrtf(sum / static_cast<float>(head_dim) + norm_eps);
+                }
+            } else if (lane == 0) {
+                factor[slot - slot0] = 1.0f;
+            }
+        }
+    }
     __syncthreads();
 
     const int groups = (head_dim - half) / 4;  // per head: half/4 rotated groups, then the unrotated tail
@@ -188,11 +266,14 @@ __global__ void rope_kv_write_vec_kernel(scalar_t* __restrict__ q, const scalar_
 // Pools: element (page, head, slot, d) of K at k_pool[page * page_stride + head *
 // head_stride + slot * head_dim + d], V likewise. inv_freq == nullptr: no rotation.
 // k_pool == nullptr: only q is rotated (a layer that reads another layer's cache).
+// q_norm, k_norm: fp32 [head_dim] scales of a per-head RMS norm applied before the
+// rotation (nullptr: none), with norm_eps inside the root.
 PL_API int pl_rope_kv_write(void* q, const void* k, const void* v, int64_t row_stride, const int32_t* pos,
                             const int32_t* entry, const int32_t* table, int table_width, void* k_pool,
                             void* v_pool, int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
                             const double* inv_freq, int rotary, int n_tokens, int n_heads, int n_kv_heads,
-                            int head_dim, int dtype, int32_t* status, cudaStream_t stream) {
+                            int head_dim, int dtype, const float* q_norm, const float* k_norm, float norm_eps,
+                            int32_t* status, cudaStream_t stream) {
     PL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && head_dim > 0 && page_size > 0,
                "rope_kv_write: bad sizes tokens=%d heads=%d kv_heads=%d head_dim=%d page=%d", n_tokens, n_heads,
                n_kv_heads, head_dim, page_size);
@@ -201,15 +282,16 @@ PL_API int pl_rope_kv_write(void* q, const void* k, const void* v, int64_t row_s
     if (n_tokens == 0) {
         return 0;
     }
-    const size_t smem = static_cast<size_t>(rotary) * sizeof(float);
-    PL_REQUIRE(smem <= 48 * 1024, "rope_kv_write: rotary width %d is too large", rotary);
     const int n_slots = n_heads + (k_pool != nullptr ? n_kv_heads : 0);
     const int heads_per_block = n_tokens >= 64 ? n_slots : 4;
+    const size_t smem = static_cast<size_t>(rotary + heads_per_block) * sizeof(float);
+    PL_REQUIRE(smem <= 48 * 1024, "rope_kv_write: rotary width %d and %d heads are too large", rotary, n_slots);
+    PL_REQUIRE(k_norm == nullptr || k_pool != nullptr, "rope_kv_write: a k norm needs keys to write");
     const dim3 grid(n_tokens, (n_slots + heads_per_block - 1) / heads_per_block);
     PL_REQUIRE(grid.y <= 65535, "rope_kv_write: too many heads (%d)", n_slots);
     const int half = rotary / 2;
     const uintptr_t align = dtype == PL_F32 ? 15 : 7;
-    const bool vec = half % 4 == 0 && (head_dim - rotary) % 4 == 0 && head_dim % 4 == 0 && row_stride % 4 == 0 &&
+    const bool vec = q_norm == nullptr && k_norm == nullptr && half % 4 == 0 && (head_dim - rotary) % 4 == 0 && head_dim % 4 == 0 && row_stride % 4 == 0 &&
         page_stride % 4 == 0 && head_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(q) & align) == 0 &&
         (reinterpret_cast<uintptr_t>(k) & align) == 0 && (reinterpret_cast<uintptr_t>(v) & align) == 0 &&
         (reinterpret_cast<uintptr_t>(k_pool) & align) == 0 && (reinterpret_cast<uintptr_t>(v_pool) & align) == 0;
@@ -221,7 +303,7 @@ PL_API int pl_rope_kv_write(void* q, const void* k, const void* v, int64_t row_s
             kernel, grid, threads, smem, stream, static_cast<scalar_t*>(q), static_cast<const scalar_t*>(k), static_cast<const scalar_t*>(v), row_stride,
             pos, entry, table, table_width, static_cast<scalar_t*>(k_pool), static_cast<scalar_t*>(v_pool),
             page_stride, head_stride, page_size, n_pages, inv_freq, rotary, n_heads, n_kv_heads, head_dim,
-            heads_per_block, status);
+            heads_per_block, q_norm, k_norm, norm_eps, status);
     });
     PL_CHECK_LAUNCH("rope_kv_write");
     return 0;

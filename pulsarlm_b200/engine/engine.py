@@ -32,23 +32,28 @@ DEFAULT_PAGE_SIZE = 16
 class _Flight:
     """A decode step that was launched and whose sampled ids have not been read yet."""
 
-    def __init__(self, entries: list[PlannedEntry], ids: torch.Tensor, pending):
+    def __init__(self, entries: list[PlannedEntry], ids: torch.Tensor, pending, logits=None):
         self.entries = entries
         self.ids = ids          # int32 [entries] on the device
         self.pending = pending  # their copy to the host
+        self.logits = logits    # with record_logits: a copy of the rows the ids were drawn from
 
 
 class Engine:
     def __init__(self, model, dtype="bfloat16", device="cuda:0", kv_cache_gib: float = 4.0,
                  page_size: int = DEFAULT_PAGE_SIZE, prefill_tokens_per_step: int = 256,
                  max_requests: int = 64, n_pages: int | None = None, stop_ids=None, seed: int | None = None,
-                 cuda_graphs: bool = True, attention_mass_decay: float | None = None, lookahead: bool = True):
+                 cuda_graphs: bool = True, attention_mass_decay: float | None = None, lookahead: bool = True,
+                 record_logits: bool = False):
         """model: a model folder, a built Model, or a config.json dict (random
         weights from `seed`). kv_cache_gib sizes the page pools unless n_pages
         gives the number of pages outright. stop_ids default to config.json's
         eos_token_id. attention_mass_decay: measure per-page attention mass with this
         decay (see CacheManager; slower: attention then runs on the CUDA cores).
-        lookahead: pipeline decode steps one deep (see step())."""
+        lookahead: pipeline decode steps one deep (see step()). record_logits: keep, for
+        every generated token, the fp32 logits row it was drawn from in
+        `request.logits` (host tensors; for inspection and tests, it costs a copy of
+        [vocab] floats per token)."""
         ops.require_device()
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
@@ -73,6 +78,7 @@ class Engine:
         self.scheduler = Scheduler(self.cache, stops, prefill_tokens_per_step)
         self.cuda_graphs = cuda_graphs and self.runner.graphs_allowed
         self.lookahead = lookahead and self.cuda_graphs
+        self.record_logits = record_logits
         self._inflight: _Flight | None = None
         self._ids = itertools.count()
         self.vocab_size = self.model.spec.vocab_size
@@ -153,9 +159,24 @@ class Engine:
             drawn = self.sampler.sample(
                 logits, [e.request.sampling for e in samplers], [e.request.seed for e in samplers],
                 [e.request.draw_count for e in samplers])
-            host = drawn.cpu().tolist()  # the step's one synchronisation
+            # the step's one synchronisation; the kernels' status word rides along
+            host = torch.cat([drawn.to(torch.int32), self.runner.status]).cpu().tolist()
+            if host[-1]:
+                self.runner.raise_status(host[-1])
             sampled = {e.request.id: t for e, t in zip(samplers, host)}
+            return self._record(samplers, sampled, logits, entries)
         return self.scheduler.finish_step(entries, sampled)
+
+    def _record(self, samplers: list[PlannedEntry], sampled: dict, logits, entries=None) -> list[Request]:
+        """finish_step, and with record_logits the rows of the tokens that were kept."""
+        before = [len(e.request.output) for e in samplers] if self.record_logits else None
+        done = self.scheduler.finish_step(samplers if entries is None else entries, sampled)
+        if self.record_logits and logits is not None:
+            rows = logits[: len(samplers)].float().cpu()
+            for e, had, row in zip(samplers, before, rows):
+                if len(e.request.output) > had:
+                    e.request.logits.append(row)
+        return done
 
     def _launch_decode(self, entries: list[PlannedEntry], device_tokens: torch.Tensor | None = None,
                        count_offset: int = 0) -> "_Flight":
@@ -163,11 +184,13 @@ class Engine:
         ids = self.runner.decode_step(
             step_entries, [e.request.sampling for e in entries], [e.request.seed for e in entries],
             [e.request.draw_count + count_offset for e in entries], device_tokens=device_tokens)
-        return _Flight(entries, ids, self.runner.last_graph.read_back())
+        graph = self.runner.last_graph
+        kept = graph.logits[: len(entries)].clone() if self.record_logits else None  # the next replay overwrites them
+        return _Flight(entries, ids, graph.read_back(), kept)
 
     def _finish(self, flight: "_Flight") -> list[Request]:
         host = flight.pending.wait()
-        return self.scheduler.finish_step(flight.entries, {e.request.id: t for e, t in zip(flight.entries, host)})
+        return self._record(flight.entries, {e.request.id: t for e, t in zip(flight.entries, host)}, flight.logits)
 
     def _can_look_ahead(self, flight: "_Flight") -> bool:
         """True when the step after `flight` is certain to be its requests again."""

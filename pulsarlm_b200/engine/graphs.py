@@ -1,8 +1,10 @@
 """CUDA graphs for steps made of single decode tokens.
 
 A decode step launches a few hundred small kernels; captured once per (number of
-entries, block-table width) and replayed, the host's part of a step is one
-buffer fill, one host-to-device copy and one graph launch. The captured work is
+entries, block-table width), both rounded up to a few sizes, and replayed, the
+host's part of a step is one buffer fill, one host-to-device copy and one graph
+launch. Captures share one memory pool and the runner keeps a bounded number of
+them, least recently used first out. The captured work is
 the same Model.forward the eager step runs, followed by the sampling kernel;
 only where its inputs live differs (fixed device buffers).
 """
@@ -15,7 +17,7 @@ import numpy as np
 import torch
 
 from ..kernels import ops
-from ..models.model import StepBatch
+from ..models.model import HostStep, StepBatch
 
 _ALIGN = 16
 
@@ -56,6 +58,19 @@ class GraphedDecode:
                   ("temperature", np.float32, (n,)), ("top_p", np.float32, (n,)),
                   ("seed", np.int64, (n,)), ("count", np.int64, (n,))]
         fields += [(f"table{g.index}", np.int32, (n, width)) for g in cache.groups]
+        # What the parts plan for a step of this shape: arrays get a place in the packed
+        # buffer and are refreshed before every replay; the rest is kept as first planned.
+        self.bound = width * cache.page_size
+        first = self._host_step([self.bound] * n)
+        self.plans: dict = {}
+        self._planned_arrays: list[tuple] = []  # (part, key, name, field)
+        for index, (key, part) in enumerate(runner._planners):
+            plan = self.plans[key] = dict(part.plan_step(first))
+            for name, value in plan.items():
+                if isinstance(value, np.ndarray):
+                    field = f"plan{index}.{name}"
+                    fields.append((field, value.dtype, value.shape))
+                    self._planned_arrays.append((part, key, name, field))
         self.layout = _Layout(fields)
         self.host = torch.empty(self.layout.nbytes, dtype=torch.uint8, pin_memory=True)
         self.h = self.layout.host_views(self.host.numpy())
@@ -63,12 +78,14 @@ class GraphedDecode:
         self.d = self.layout.device_views(self.dev)
         self.h["entry"][:] = np.arange(n, dtype=np.int32)
         self.h["want"][:] = np.arange(n, dtype=np.int32)
+        for part, key, name, field in self._planned_arrays:
+            self.plans[key][name] = self.d[field]
         self.batch = StepBatch(
             tokens=self.d["tokens"], pos=self.d["pos"], entry=self.d["entry"],
             tables={g.index: self.d[f"table{g.index}"] for g in cache.groups},
             slots=self.d["slots"], want_rows=self.d["want"], status=runner.status,
-            n_tokens=n, n_entries=n, n_decode=n, host_query_lens=[1] * n, host_context_lens=[],
-            extras={"graph": True, "max_context": width * cache.page_size},
+            n_tokens=n, n_entries=n, n_decode=n, host_query_lens=[1] * n, host_context_lens=[self.bound] * n,
+            extras={"graph": True}, plans=self.plans,
         )
         self.logits: torch.Tensor | None = None
         self.ids: torch.Tensor | None = None
@@ -79,11 +96,56 @@ class GraphedDecode:
         self._result_events: list[torch.cuda.Event] = []
         self._turn = 0
 
+    def _host_step(self, context_lens: list[int]) -> HostStep:
+        n = self.n
+        lens = list(context_lens) + [1] * (n - len(context_lens))  # padding rows hold one token
+        return HostStep(n_entries=n, n_tokens=n, n_decode=n, query_lens=[1] * n, context_lens=lens,
+                        first_rows=list(range(n)), page_size=self.runner.cache.page_size, fixed_shape=True,
+                        context_bound=self.bound)
+
+    def pad_rows(self, n_real: int, pad_page: int) -> None:
+        """Rows past the step's `n_real` entries: token 0 at position 0 of the cache's
+        padding page, drawn greedily; nothing reads what they compute."""
+        if n_real == self.n:
+            return
+        h = self.h
+        for name in ("tokens", "pos", "slots", "top_k"):
+            h[name][n_real:] = 0
+        h["temperature"][n_real:] = 0.0
+        h["top_p"][n_real:] = 2.0
+        h["seed"][n_real:] = 0
+        h["count"][n_real:] = 0
+        for g in self.runner.cache.groups:
+            table = h[f"table{g.index}"]
+            table[n_real:] = -1
+            table[n_real:, 0] = pad_page
+
+    def plan(self, context_lens: list[int]) -> None:
+        """Refreshes the arrays the parts planned, for this replay's lengths."""
+        if not self._planned_arrays:
+            return
+        step = self._host_step(context_lens)
+        fresh: dict = {}
+        for part, key, name, field in self._planned_arrays:
+            if key not in fresh:
+                fresh[key] = part.plan_step(step)
+            value = fresh[key][name]
+            if value.shape != self.h[field].shape or value.dtype != self.h[field].dtype:
+                raise ValueError(f"{type(part).__name__}.plan_step: array {name!r} changed from "
+                                 f"{self.h[field].dtype}{self.h[field].shape} to {value.dtype}{value.shape} between "
+                                 f"replays of one captured step; its shape may depend on the number of entries and "
+                                 f"the context bound only")
+            self.h[field][...] = value
+
     def _forward(self) -> None:
         self.logits = self.runner.model.forward(self.batch)
-        self.ids = torch.empty(self.n, dtype=torch.int32, device=self.runner.device)
+        # The sampled ids, and behind them the kernels' status word as it stands after
+        # this step: both reach the host in the step's one copy.
+        self._result = torch.empty(self.n + 1, dtype=torch.int32, device=self.runner.device)
+        self.ids = self._result[: self.n]
         ops.sample(self.logits, self.d["temperature"], self.d["top_k"], self.d["top_p"], self.d["seed"],
                    self.d["count"], self.ids)
+        self._result[self.n :].copy_(self.runner.status)
 
     def capture(self) -> None:
         """Runs the step once eagerly on a side stream (libraries set themselves up),
@@ -104,43 +166,52 @@ class GraphedDecode:
         collecting = gc.isenabled()
         gc.disable()
         try:
-            with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
+            if self.runner._graph_pool is None:
+                self.runner._graph_pool = torch.cuda.graph_pool_handle()
+            with torch.cuda.graph(self.graph, pool=self.runner._graph_pool, capture_error_mode="thread_local"):
                 self._forward()
         finally:
             if collecting:
                 gc.enable()
         self.launches = ops.launch_count() - before
 
-    def replay(self, device_tokens: torch.Tensor | None = None) -> None:
-        """Copies the packed inputs and launches the graph. With `device_tokens` (int32 [n],
-        e.g. the ids another replay sampled) the step's tokens are taken from there
-        instead of from the host buffer: the copy is ordered after whatever wrote them."""
+    def replay(self, device_tokens: torch.Tensor | None = None, n_real: int | None = None) -> None:
+        """Copies the packed inputs and launches the graph. With `device_tokens` (int32,
+        e.g. the ids another replay sampled) the tokens of the first `n_real` entries are
+        taken from there instead of from the host buffer: the copy is ordered after
+        whatever wrote them."""
         self.dev.copy_(self.host, non_blocking=True)
         self.copied.record()
         if device_tokens is not None:
-            self.d["tokens"].copy_(device_tokens, non_blocking=True)
+            n_real = self.n if n_real is None else n_real
+            self.d["tokens"][:n_real].copy_(device_tokens[:n_real], non_blocking=True)
         self.graph.replay()
 
     def read_back(self) -> "PendingIds":
         """Starts the copy of this replay's sampled ids to the host; `wait()` on the result
         gives them. Two host buffers alternate, so one earlier result may still be unread."""
         if self._results is None:
-            self._results = [torch.empty(self.n, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+            self._results = [torch.empty(self.n + 1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
             self._result_events = [torch.cuda.Event(), torch.cuda.Event()]
         slot = self._turn
         self._turn ^= 1
-        self._results[slot].copy_(self.ids, non_blocking=True)
+        self._results[slot].copy_(self._result, non_blocking=True)
         self._result_events[slot].record()
-        return PendingIds(self._results[slot], self._result_events[slot])
+        return PendingIds(self._results[slot], self._result_events[slot], self.runner)
 
 
 class PendingIds:
     """Sampled token ids on their way to the host."""
 
-    def __init__(self, host: torch.Tensor, event: torch.cuda.Event):
+    def __init__(self, host: torch.Tensor, event: torch.cuda.Event, runner):
         self._host = host
         self._event = event
+        self._runner = runner
 
     def wait(self) -> list[int]:
+        """The ids; raises if a kernel had flagged an error by the end of that step."""
         self._event.synchronize()  # the step's one synchronisation
-        return self._host.tolist()
+        values = self._host.tolist()
+        if values[-1]:
+            self._runner.raise_status(values[-1])
+        return values[:-1]

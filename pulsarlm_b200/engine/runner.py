@@ -12,6 +12,7 @@ tokens share one pass.
 
 from __future__ import annotations
 
+import collections
 import dataclasses
 
 import numpy as np
@@ -19,7 +20,7 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..kernels import ops
-from ..models.model import Model, StepBatch
+from ..models.model import HostStep, Model, StepBatch
 
 
 class OutOfPages(RuntimeError):
@@ -44,7 +45,29 @@ STATUS_MESSAGES = {
     1: "a token id outside the vocabulary reached the embedding kernel",
     2: "a token's block-table entry was not a page of the pool when its key was written",
     4: "a block-table entry was not a page of the pool when attention read it",
+    8: "a bounded wait inside a kernel gave up (a barrier or a copy that never arrived)",
 }
+
+
+def graph_entries_bucket(n: int) -> int:
+    """How many entries the captured decode step that serves `n` entries has: n itself
+    up to 4, then the next multiple of 4 up to 16, of 8 up to 64, of 16 beyond. The
+    rows past n are padding (a token at position 0 of a page of their own that no
+    request holds; their outputs are dropped), so a batch that shrinks as requests
+    end passes through few captures."""
+    if n <= 4:
+        return n
+    step = 4 if n <= 16 else 8 if n <= 64 else 16
+    return -(-n // step) * step
+
+
+def graph_width_bucket(pages: int) -> int:
+    """Block-table width of the captured decode step that serves rows of `pages`
+    pages: multiples of 64 up to 512, of 256 up to 2,048, of 1,024 beyond (at most an
+    eighth more than needed from 512 pages on)."""
+    step = 64 if pages <= 512 else 256 if pages <= 2048 else 1024
+    return -(-pages // step) * step
+
 
 
 class ModelRunner:
@@ -54,11 +77,18 @@ class ModelRunner:
         self.cache = cache
         self.device = model.ctx.device
         self.vocab = model.spec.vocab_size
-        model.bind_caches(cache.bindings())
+        self._bindings = cache.bindings()
+        self._bind()
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._staging: torch.Tensor | None = None
-        self._tile_rows = ops.attention_prefill_tile_rows()
-        self._graphs: dict = {}
+        self._planners = model.planners()
+        # Captured decode steps, least recently used first; at most `max_graphs` are kept
+        # (each holds its own logits [entries, vocab] and small buffers; activations come
+        # from one memory pool that all captures share).
+        self._graphs: collections.OrderedDict = collections.OrderedDict()
+        self.max_graphs = 24
+        self._graph_pool = None
+        self.graph_captures = 0
         # Replaying a captured step re-runs the capture's warm-up on the same tokens,
         # which is harmless for caches written by position but not for states updated
         # in place, so models with state slots step eagerly.
@@ -68,6 +98,14 @@ class ModelRunner:
         self.graph_steps = 0
 
     # ------------------------------------------------------------------ helpers
+    def _bind(self) -> None:
+        """Points the model's layers at this runner's cache. A model serves one cache at a
+        time: when another runner was made over the same model since (a second engine
+        sharing the weights), the layers are pointed back before this one steps."""
+        if getattr(self.model, "bound_to", None) is not self:
+            self.model.bind_caches(self._bindings)
+            self.model.bound_to = self
+
     def _stage(self, arrays: list[np.ndarray]) -> list[torch.Tensor]:
         """Copies int32 arrays to the device through one pinned buffer and one copy;
         returns device views in the same order."""
@@ -120,8 +158,8 @@ class ModelRunner:
 
         if getattr(self, "_copy_done", None) is not None:
             self._copy_done.synchronize()
-        # Entries of one token go first (the attention part sends the leading single
-        # tokens to its decode kernel); the wanted rows still come back in the
+        # Entries of one token go first (StepBatch's contract: mixers may send the leading
+        # single tokens to a kernel of their own); the wanted rows still come back in the
         # caller's order of entries.
         order = sorted(range(len(entries)), key=lambda i: len(entries[i].tokens) != 1)
         n_decode = sum(1 for e in entries if len(e.tokens) == 1)
@@ -130,8 +168,6 @@ class ModelRunner:
         pos = np.empty(n_tokens, dtype=np.int32)
         entry = np.empty(n_tokens, dtype=np.int32)
         first_row = [0] * len(entries)
-        tiles: list[tuple[int, int, int, int]] = []
-        wide_tiles: list[tuple[int, int, int, int]] = []  # the same rows in tiles twice as long
         at = 0
         for place, i in enumerate(order):
             e = entries[i]
@@ -141,21 +177,31 @@ class ModelRunner:
             pos[at : at + n] = np.arange(start, start + n, dtype=np.int32)
             entry[at : at + n] = place
             first_row[i] = at
-            if n > 1:  # tiles of consecutive rows for the prompt-portion attention kernel
-                for r in range(0, n, self._tile_rows):
-                    tiles.append((at + r, min(self._tile_rows, n - r), start + r, place))
-                for r in range(0, n, 2 * self._tile_rows):
-                    wide_tiles.append((at + r, min(2 * self._tile_rows, n - r), start + r, place))
             at += n
-        tiles.sort(key=lambda t: -(t[2] + t[1]))  # the tiles with the most keys start first
-        wide_tiles.sort(key=lambda t: -(t[2] + t[1]))
         want_rows = [first_row[i] + w for i, e in enumerate(entries) for w in e.want]
         requests = [entries[i].request for i in order]
         slots = np.array([self.cache.slot(r) for r in requests], dtype=np.int32)
         tables = [self.cache.table_rows(g.index, requests) for g in self.cache.groups]
-        tile_array = np.array(tiles, dtype=np.int32).reshape(len(tiles), 4)
-        arrays = [tokens, pos, entry, slots, np.array(want_rows, dtype=np.int32), tile_array, *tables]
+        host = HostStep(n_entries=len(entries), n_tokens=n_tokens, n_decode=n_decode,
+                        query_lens=[len(entries[i].tokens) for i in order],
+                        context_lens=[new_lens[i] for i in order],
+                        first_rows=[first_row[i] for i in order], page_size=self.cache.page_size)
+        arrays = [tokens, pos, entry, slots, np.array(want_rows, dtype=np.int32), *tables]
+        n_fixed = len(arrays)
+        # What the parts plan for this step: their arrays travel in the same copy.
+        plans: dict = {}
+        staged: list[tuple] = []  # (plan key, name, index into arrays, is float)
+        for key, part in self._planners:
+            plan = plans[key] = dict(part.plan_step(host))
+            for name, value in plan.items():
+                if isinstance(value, np.ndarray):
+                    if value.dtype not in (np.int32, np.float32):
+                        raise TypeError(f"{type(part).__name__}.plan_step: array {name!r} must be int32 or float32, "
+                                        f"not {value.dtype}")
+                    staged.append((key, name, len(arrays), value.dtype == np.float32))
+                    arrays.append(np.ascontiguousarray(value).view(np.int32))
         decay = self.cache.mass_decay
+        n_planned = len(arrays)
         if decay is not None:
             # Query weights a (1 - a)^age within each portion, and per page what the
             # accumulators keep: (1 - a)^tokens for pages the step's requests held, 0
@@ -168,34 +214,31 @@ class ModelRunner:
                 at += n
             arrays.append(weights.view(np.int32))
             for g in self.cache.groups:
-                keep = np.ones(self.cache.n_pages, dtype=np.float32)
+                keep = np.ones(self.cache.n_physical_pages, dtype=np.float32)
                 for e in entries:
                     keep[self.cache.held_pages(e.request, g.index)] = (1.0 - decay) ** len(e.tokens)
                 keep[list(self.cache.take_fresh_pages(g.index))] = 0.0
                 arrays.append(keep.view(np.int32))
-        arrays.append(np.array(wide_tiles, dtype=np.int32).reshape(len(wide_tiles), 4))  # last: dev[-1]
         dev = self._stage(arrays)
+        for key, name, index, is_float in staged:
+            plans[key][name] = dev[index].view(torch.float32) if is_float else dev[index]
         batch = StepBatch(
             tokens=dev[0], pos=dev[1], entry=dev[2],
-            tables={g.index: dev[6 + i] for i, g in enumerate(self.cache.groups)},
+            tables={g.index: dev[5 + i] for i, g in enumerate(self.cache.groups)},
             slots=dev[3],
             want_rows=dev[4] if want_rows else None,
             status=self.status,
             n_tokens=n_tokens,
             n_entries=len(entries),
             n_decode=n_decode,
-            host_query_lens=[len(entries[i].tokens) for i in order],
-            host_context_lens=[new_lens[i] for i in order],
-            extras={"prefill_tiles": dev[5] if tiles else None,
-                    # (worth using only if some portion is longer than one narrow tile)
-                    "prefill_tiles_wide": dev[-1] if any(t[1] > self._tile_rows for t in wide_tiles) else None,
-                    # the most keys any tile reads (the attention part sizes its launch by it)
-                    "prefill_max_keys": max((t[2] + t[1] for t in tiles), default=0)},
+            host_query_lens=host.query_lens,
+            host_context_lens=host.context_lens,
+            plans=plans,
         )
+        assert n_fixed == 5 + len(self.cache.groups)
         if decay is not None:
-            n_groups = len(self.cache.groups)
-            batch.extras["query_weights"] = dev[6 + n_groups].view(torch.float32)
-            batch.extras["mass_retained"] = {g.index: dev[7 + n_groups + i].view(torch.float32)
+            batch.extras["query_weights"] = dev[n_planned].view(torch.float32)
+            batch.extras["mass_retained"] = {g.index: dev[n_planned + 1 + i].view(torch.float32)
                                              for i, g in enumerate(self.cache.groups)}
         return batch, new_lens
 
@@ -203,6 +246,7 @@ class ModelRunner:
     def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
         """Runs the entries' tokens; returns fp32 logits [wanted, vocab] on the device
         in the order of the entries and of each entry's `want`, or None."""
+        self._bind()
         batch, new_lens = self.prepare(entries)
         logits = self.model.forward(batch)
         if self.cache.mass_decay is not None:
@@ -216,13 +260,15 @@ class ModelRunner:
     def decode_step(self, entries: list[StepEntry], sampling, seeds: list[int], counts: list[int],
                     device_tokens: torch.Tensor | None = None) -> torch.Tensor:
         """A step of single tokens, one per entry, each sampling its next token:
-        replays a CUDA graph captured for this number of entries. Returns int32
-        [entries] token ids in a device buffer that the next call overwrites
+        replays a CUDA graph captured for this number of entries (rounded up, see
+        graph_entries_bucket). Returns int32 token ids, the entries' first, in a device
+        buffer that the next call overwrites
         (`self.last_graph.read_back()` starts their copy to the host). With
         `device_tokens` the entries' tokens are read from that device tensor (the ids
         a step still in flight is sampling) and the entries' own tokens are ignored."""
         from .graphs import GraphedDecode
 
+        self._bind()  # (a replay runs on the pools it was captured with; a capture needs the binding)
         n = len(entries)
         new_lens = []
         for e in entries:
@@ -235,13 +281,20 @@ class ModelRunner:
                 raise OutOfPages(e.request, f"too few free pages for request {e.request!r} to reach {new_len} tokens")
             new_lens.append(new_len)
         pages = -(-max(new_lens) // self.cache.page_size)
-        width = -(-pages // 64) * 64
-        key = (n, width)
+        width = graph_width_bucket(pages)
+        n_graph = graph_entries_bucket(n)
+        key = (n_graph, width)
         graph = self._graphs.get(key)
         fresh = graph is None
         if fresh:
-            graph = self._graphs[key] = GraphedDecode(self, n, width)
+            graph = GraphedDecode(self, n_graph, width)
+            self._graphs[key] = graph
+            while len(self._graphs) > max(2, self.max_graphs):
+                # The least recently used capture goes; its buffers return to the shared
+                # pool once nothing in flight holds them (the two most recent never go).
+                self._graphs.popitem(last=False)
         else:
+            self._graphs.move_to_end(key)
             graph.copied.synchronize()
         h = graph.h
         requests = [e.request for e in entries]
@@ -256,10 +309,14 @@ class ModelRunner:
             h["count"][i] = counts[i]
         handles = [self.cache.handle(r) for r in requests]
         for g in self.cache.groups:
-            self.cache.fill_tables(g.index, handles, h[f"table{g.index}"], h["slots"])
+            table = h[f"table{g.index}"]
+            self.cache.fill_tables(g.index, handles, table[:n], h["slots"][:n])
+        graph.pad_rows(n, self.cache.pad_page)
+        graph.plan(new_lens)
         if fresh:
             graph.capture()
-        graph.replay(device_tokens)
+            self.graph_captures += 1
+        graph.replay(device_tokens, n)
         self.last_graph = graph
         for e, new_len in zip(entries, new_lens):
             self.cache.commit(e.request, new_len)
@@ -277,6 +334,10 @@ class ModelRunner:
         """Raises if a kernel flagged an error since the last check (synchronises)."""
         code = int(self.status.item())
         if code:
-            self.status.zero_()
-            reasons = [m for bit, m in STATUS_MESSAGES.items() if code & bit]
-            raise RuntimeError("kernel status %d: %s" % (code, "; ".join(reasons) or "unknown"))
+            self.raise_status(code)
+
+    def raise_status(self, code: int) -> None:
+        """Clears the device status word and raises what `code` (a copy of it) says."""
+        self.status.zero_()
+        reasons = [m for bit, m in STATUS_MESSAGES.items() if code & bit]
+        raise RuntimeError("kernel status %d: %s" % (code, "; ".join(reasons) or "unknown"))

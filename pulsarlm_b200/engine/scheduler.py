@@ -56,6 +56,7 @@ class Request:
     finish_reason: str | None = None  # stop | length | cancelled | oom
     cancelled: bool = False
     preemptions: int = 0
+    logits: list = dataclasses.field(default_factory=list)  # filled by an engine that records logits
 
     def take(self) -> list[int]:
         """Tokens generated since the last take()."""
@@ -88,8 +89,6 @@ class Scheduler:
     counts alone; this class keeps the token lists and the Request objects in step
     with it."""
 
-    _CAPACITY = 4096
-
     def __init__(self, cache: CacheManager, stop_ids=(), prefill_tokens_per_step: int = 256,
                  max_step_entries: int | None = None):
         if prefill_tokens_per_step <= 0:
@@ -103,11 +102,20 @@ class Scheduler:
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []  # admission order
         self.stop_ids = stop_ids
-        n = self._CAPACITY
+        self._counts = (ctypes.c_int32 * 3)()
+        self._capacity = 0
+        self._ensure_capacity(max(64, 2 * cache.max_requests))
+
+    def _ensure_capacity(self, n: int) -> None:
+        """Room in the buffers the core writes a plan into: a plan names each known
+        request at most once as an entry, once as ended and once as preempted."""
+        if n <= self._capacity:
+            return
+        n = max(n, 2 * self._capacity)
+        self._capacity = n
         self._entries = (ctypes.c_int64 * (3 * n))()
         self._ended = (ctypes.c_int64 * (2 * n))()
         self._preempted = (ctypes.c_int64 * n)()
-        self._counts = (ctypes.c_int32 * 3)()
         self._tokens = (ctypes.c_int32 * n)()
 
     def __del__(self):
@@ -168,7 +176,8 @@ class Scheduler:
         for request in self._requests.values():
             if request.cancelled:
                 self._lib.plh_sched_cancel(self._core, self.cache.handle(request.id))
-        code = self._lib.plh_sched_plan(self._core, self._entries, self._ended, self._preempted, self._CAPACITY,
+        self._ensure_capacity(len(self._requests) + 1)
+        code = self._lib.plh_sched_plan(self._core, self._entries, self._ended, self._preempted, self._capacity,
                                         self._counts)
         if code != 0:
             raise RuntimeError("the scheduler core planned more entries than fit its buffers")
@@ -218,5 +227,5 @@ class Scheduler:
             if entry.samples and request.max_tokens != 0:
                 request.output.append(int(token))
                 request.pending = [int(token)]
-        n_ended = self._lib.plh_sched_finish_step(self._core, flat, self._tokens, n, self._ended, self._CAPACITY)
+        n_ended = self._lib.plh_sched_finish_step(self._core, flat, self._tokens, n, self._ended, self._capacity)
         return [self._end(self._ended[2 * i], core.REASONS[self._ended[2 * i + 1]]) for i in range(n_ended)]

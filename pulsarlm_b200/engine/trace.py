@@ -32,7 +32,10 @@ MAX_LIVE_REQUESTS = 16
 
 def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
-    p.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    p.add_argument("--model", default=None, help="folder with config.json and model.safetensors")
+    p.add_argument("--random-weights", "--random_weights", type=int, default=None, metavar="SEED",
+                   help="instead of --model: random weights drawn from this seed for the model --config describes")
+    p.add_argument("--config", default=None, help="with --random-weights: a config.json")
     p.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     p.add_argument("--out", required=True, help="folder for <step>.f32 files")
     p.add_argument("--max-tokens", type=int, required=True,
@@ -46,6 +49,10 @@ def run(argv=None, stdin=None, stdout=None) -> int:
     args = build_parser().parse_args(argv)
     stdin = stdin or sys.stdin
     stdout = stdout or sys.stdout
+    if (args.model is None) == (args.random_weights is None) or (args.random_weights is not None) != (
+            args.config is not None):
+        print("trace_run: give --model DIR, or --random-weights SEED with --config FILE", file=sys.stderr)
+        return 2
     if args.max_tokens <= 0:
         print("trace_run: --max-tokens must be positive", file=sys.stderr)
         return 2
@@ -57,7 +64,7 @@ def run(argv=None, stdin=None, stdout=None) -> int:
 
     from ..cache.manager import CacheManager
     from ..kernels import ops
-    from .loading import load_model, parse_dtype
+    from .loading import load_model, parse_dtype, random_model
     from .runner import ModelRunner, StepEntry
 
     ops.require_device()
@@ -65,7 +72,11 @@ def run(argv=None, stdin=None, stdout=None) -> int:
     dtype = parse_dtype(args.dtype)
     device = torch.device(args.device)
     torch.cuda.set_device(device)
-    model = load_model(args.model, dtype, device)
+    if args.random_weights is not None:
+        with open(args.config, "r", encoding="utf-8") as f:
+            model = random_model(json.load(f), args.random_weights, dtype, device)
+    else:
+        model = load_model(args.model, dtype, device)
     n_pages = -(-args.max_tokens // args.page_size)
     cache = CacheManager(model.cache_needs(), args.page_size, n_pages, MAX_LIVE_REQUESTS, dtype, device)
     runner = ModelRunner(model, cache)

@@ -25,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 12
+ABI_VERSION = 13
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -41,9 +41,9 @@ _SIGNATURES = {
     "pl_bf16_to_f32": [_PTR, _PTR, _I64, _PTR],
     "pl_gemm_f32": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _PTR],
     "pl_rope_kv_write": [_PTR, _PTR, _PTR, _I64, _PTR, _PTR, _PTR, _I32, _PTR, _PTR, _I64, _I64, _I32, _I32,
-                         _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _PTR, _PTR],
+                         _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _PTR, _PTR, _F32, _PTR, _PTR],
     "pl_attention_simt": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
-                          _I32, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR, _PTR, _PTR, _PTR],
+                          _I32, _I32, _I32, _I32, _I32, _F32, _F32, _I32, _PTR, _PTR, _PTR, _PTR, _PTR],
     "pl_attention_decode": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
                             _I32, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR, _PTR],
     "pl_attention_decode_supports": [_I32, _I32, _I32, _I32],
@@ -267,10 +267,16 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch
 def rope_kv_write(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | None, pos: torch.Tensor,
                   entry: torch.Tensor, table: torch.Tensor, k_pool: torch.Tensor | None,
                   v_pool: torch.Tensor | None, page_size: int, inv_freq: torch.Tensor | None, rotary: int,
-                  status: torch.Tensor | None = None) -> None:
+                  status: torch.Tensor | None = None, q_norm: torch.Tensor | None = None,
+                  k_norm: torch.Tensor | None = None, norm_eps: float = 0.0) -> None:
     """Rotates q [T, nh, hd] in place and writes rotated k and v [T, nkv, hd] into
-    the pools [pages, nkv, page_size, hd] (views of one layer's K and V)."""
-    _dev(q, k, v, pos, entry, table, k_pool, v_pool, inv_freq, status)
+    the pools [pages, nkv, page_size, hd] (views of one layer's K and V). q_norm and
+    k_norm (fp32 [hd]): each head of q, of k, is first normalised over its hd
+    (x * rsqrt(mean(x^2) + norm_eps) * scale) in fp32."""
+    _dev(q, k, v, pos, entry, table, k_pool, v_pool, inv_freq, status, q_norm, k_norm)
+    for scale_ in (q_norm, k_norm):
+        if scale_ is not None:
+            assert scale_.dtype == torch.float32 and scale_.shape == (q.shape[2],) and scale_.is_contiguous()
     tokens, n_heads, head_dim = q.shape
     assert q.stride(2) == 1 and q.stride(1) == head_dim
     row_stride = q.stride(0)
@@ -299,11 +305,13 @@ def rope_kv_write(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | Non
 def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,
                    pos: torch.Tensor, entry: torch.Tensor, out: torch.Tensor, page_size: int, window: int | None,
                    scale: float, status: torch.Tensor | None = None, mass_sum: torch.Tensor | None = None,
-                   weight_sum: torch.Tensor | None = None, query_weights: torch.Tensor | None = None) -> None:
+                   weight_sum: torch.Tensor | None = None, query_weights: torch.Tensor | None = None,
+                   softcap: float = 0.0) -> None:
     """Causal paged attention; q and out [T, nh, hd] (row strides free), pools
     [pages, nkv, page_size, hd]. With mass_sum fp32 [pages, nh] and weight_sum fp32
     [pages], the attention mass of every attended page is added to them
-    (query_weights fp32 [T], all 1 when None)."""
+    (query_weights fp32 [T], all 1 when None). softcap > 0: scaled scores pass through
+    softcap * tanh(s / softcap) before the softmax."""
     _dev(q, k_pool, v_pool, table, pos, entry, out, status, mass_sum, weight_sum, query_weights)
     if mass_sum is not None:
         assert mass_sum.dtype == torch.float32 and mass_sum.shape == (k_pool.shape[0], q.shape[1])
@@ -322,8 +330,8 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
     assert table.dim() == 2 and table.is_contiguous()
     _call("pl_attention_simt", _p(q), q.stride(0), _p(k_pool), _p(v_pool), k_pool.stride(0), k_pool.stride(1),
           page_size, n_pages, _p(table), table.shape[1], _p(pos), _p(entry), _p(out), out.stride(0), tokens,
-          n_heads, n_kv, head_dim, int(window or 0), float(scale), _code(q.dtype), _p(mass_sum), _p(weight_sum),
-          _p(query_weights), _p(status), _stream())
+          n_heads, n_kv, head_dim, int(window or 0), float(scale), float(softcap or 0.0), _code(q.dtype),
+          _p(mass_sum), _p(weight_sum), _p(query_weights), _p(status), _stream())
 
 
 def attention_decode_supports(head_dim: int, group: int, page_size: int, dtype: torch.dtype) -> bool:

@@ -146,6 +146,20 @@ class Model:
                 continue
             if not 0 <= src < len(self.blocks) or needs[src] is None or sources[src] is not None:
                 raise ValueError(f"layer {layer} reads the cache of layer {src}, which keeps none of its own")
+            # The reader must see the cache as its owner keeps it: the same heads and head
+            # size, and no further back than the owner's window (pages behind that window
+            # are given back while the request runs).
+            reads = getattr(self.blocks[layer].mixer, "cache_read_need", None)
+            want, have = (reads() if reads is not None else None), needs[src]
+            if want is not None and hasattr(have, "n_kv_heads"):
+                if (want.n_kv_heads, want.head_dim) != (have.n_kv_heads, have.head_dim):
+                    raise ValueError(
+                        f"layer {layer} reads the cache of layer {src} as {want.n_kv_heads} kv heads of size "
+                        f"{want.head_dim}, but it holds {have.n_kv_heads} of size {have.head_dim}")
+                if have.window is not None and (want.window is None or want.window > have.window):
+                    raise ValueError(
+                        f"layer {layer} reads {'every key' if want.window is None else f'a window of {want.window}'} "
+                        f"of layer {src}'s cache, which keeps a window of {have.window} only")
         return sources
 
     def planners(self) -> list:

@@ -132,9 +132,13 @@ class Attention(Part):
     params: hidden_size, n_heads, n_kv_heads, head_dim, position (a PartSpec of the
     "position" registry), scale (optional), window (optional: a query reads only
     the last `window` keys), cache_from (optional: index of the layer whose cache
-    this layer reads; it then has no k and v projections and writes nothing).
-    tensors: q [nh*hd, H], k and v [nkv*hd, H], o [H, nh*hd]. q, k and v are
-    stacked into one operand at load.
+    this layer reads; it then has no k and v projections and writes nothing),
+    softcap (optional: scaled scores pass through softcap * tanh(s / softcap) before
+    the softmax; such a layer attends on the CUDA-core kernel, the only one that
+    squashes scores), qk_norm_eps (with the q_norm / k_norm tensors: eps of the
+    per-head RMS norm applied to q and k before the position encoding).
+    tensors: q [nh*hd, H], k and v [nkv*hd, H], o [H, nh*hd]; optional q_norm and
+    k_norm [hd] (kept in float32). q, k and v are stacked into one operand at load.
     """
 
     def __init__(self, spec: PartSpec, ctx: BuildContext):
@@ -149,6 +153,10 @@ class Attention(Part):
         self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.head_dim)
         self.window = int(p["window"]) if p.get("window") else None
         self.cache_from = p.get("cache_from")
+        self.softcap = float(p["softcap"]) if p.get("softcap") else 0.0
+        self.qk_norm_eps = float(p.get("qk_norm_eps") or 0.0)
+        self.q_norm: torch.Tensor | None = None
+        self.k_norm: torch.Tensor | None = None
         self.position = build_part("position", self.param("position"), ctx)
         self.qkv: torch.Tensor | None = None
         self.o: torch.Tensor | None = None
@@ -165,6 +173,10 @@ class Attention(Part):
         if p.get("cache_from") is None:
             needs[t["k"]] = TensorNeed((nkv * hd, h))
             needs[t["v"]] = TensorNeed((nkv * hd, h))
+            if t.get("k_norm"):
+                needs[t["k_norm"]] = TensorNeed((hd,), role="vector")
+        if t.get("q_norm"):
+            needs[t["q_norm"]] = TensorNeed((hd,), role="vector")
         return needs
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
@@ -174,10 +186,18 @@ class Attention(Part):
         else:
             self.qkv = tensors[t["q"]].contiguous()
         self.o = tensors[t["o"]].contiguous()
+        if t.get("q_norm"):
+            self.q_norm = tensors[t["q_norm"]].float().contiguous()
+        if t.get("k_norm") and self.cache_from is None:
+            self.k_norm = tensors[t["k_norm"]].float().contiguous()
 
     def cache_need(self) -> KVCacheNeed | None:
         if self.cache_from is not None:
             return None
+        return KVCacheNeed(self.n_kv, self.head_dim, self.window, self.n_heads)
+
+    def cache_read_need(self) -> KVCacheNeed:
+        """How this layer reads a cache, its own or the one `cache_from` names."""
         return KVCacheNeed(self.n_kv, self.head_dim, self.window, self.n_heads)
 
     def bind_cache(self, binding: KVBinding) -> None:
@@ -195,10 +215,10 @@ class Attention(Part):
             k = qkv[:, nh * hd : (nh + nkv) * hd].view(tokens, nkv, hd)
             v = qkv[:, (nh + nkv) * hd :].view(tokens, nkv, hd)
             ops.rope_kv_write(q, k, v, batch.pos, batch.entry, table, cache.k_pool, cache.v_pool, cache.page_size,
-                              inv_freq, rotary, batch.status)
+                              inv_freq, rotary, batch.status, self.q_norm, self.k_norm, self.qk_norm_eps)
         else:
             ops.rope_kv_write(q, None, None, batch.pos, batch.entry, table, None, None, cache.page_size, inv_freq,
-                              rotary, batch.status)
+                              rotary, batch.status, self.q_norm, None, self.qk_norm_eps)
         out = torch.empty((tokens, nh, hd), dtype=h.dtype, device=h.device)
         self.attend(q, out, table, batch)
         return linear(out.view(tokens, nh * hd), self.o)
@@ -220,7 +240,7 @@ class Attention(Part):
             return None
         wide = (self.n_heads // self.n_kv) % 2 == 1
         return ("attention", self.cache.page_size, self.head_dim, self.n_heads // self.n_kv, wide,
-                self.ctx.dtype)
+                self.ctx.dtype, bool(self.softcap))
 
     def plan_step(self, step) -> dict:
         """The tile list of the prompt-portion kernels: int32 [tiles, 4] rows of {first
@@ -231,6 +251,8 @@ class Attention(Part):
         is captured and replayed: the most it may come to read)."""
         decode_kernel, prefill_kernel = self._kernels(self.ctx.dtype)
         plan: dict = {"tiles": None, "tiles_wide": None, "max_keys": 0, "max_context": 0}
+        if self.softcap:
+            return plan  # every token goes to the CUDA-core kernel, which needs no plan
         n_decode = step.n_decode if decode_kernel else 0
         if n_decode:
             plan["max_context"] = step.context_bound if step.fixed_shape else max(step.context_lens[:n_decode])
@@ -268,6 +290,10 @@ class Attention(Part):
             ops.attention_simt(q, cache.k_pool, cache.v_pool, table, batch.pos, batch.entry, out, cache.page_size,
                                self.window, self.scale, batch.status, cache.mass_sum, cache.weight_sum,
                                batch.extras["query_weights"])
+            return
+        if self.softcap:
+            ops.attention_simt(q, cache.k_pool, cache.v_pool, table, batch.pos, batch.entry, out, cache.page_size,
+                               self.window, self.scale, batch.status, softcap=self.softcap)
             return
         plan = batch.plans.get(self.plan_key()) or {}
         decode_kernel, prefill_kernel = self._kernels(q.dtype)

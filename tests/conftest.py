@@ -25,3 +25,15 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """The worst error each comparison with the plain implementation saw, by dtype and
+    schedule (harness.record_error): how far the engine stays from its bars."""
+    import harness
+
+    if not harness.WORST:
+        return
+    terminalreporter.write_sep("-", "worst relative error against the plain implementation")
+    for (dtype, what), (err, bar) in sorted(harness.WORST.items()):
+        terminalreporter.write_line(f"{dtype:9s} {what:60s} {err:.3e}  (bar {bar:.0e})")

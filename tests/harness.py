@@ -10,12 +10,22 @@ import torch
 import plain_llama
 import tiny
 
-# Chosen before the first run and not widened since: the reference's own bars for
-# its Llama test (pulsarlm-core/tests/model/test_llama.cpp:278-289) are 1e-4 in
-# fp32 and 1e-2 in bf16 on a 2-layer model; bf16 here allows 2e-2, the reference's
-# kernel-level bf16 bar (tests/kernels/test_ops.cpp:567-741), since the tiny models
-# go to 3 layers and hundreds of positions.
-TOLERANCE = {"float32": 1e-4, "bfloat16": 2e-2}
+# The reference's own bars for its Llama test (pulsarlm-core/tests/model/test_llama.cpp:
+# 278-289): 1e-4 in fp32 and 1e-2 in bf16, max|difference| / max|expected|. (bf16
+# started at 2e-2 here and was tightened once every comparison printed its worst error:
+# the largest seen is 7.4e-3, fp32 stays below 1e-6; the run's summary lists them.)
+TOLERANCE = {"float32": 1e-4, "bfloat16": 1e-2}
+
+# (dtype, what) -> (worst relative error seen in this run, the bar it was held to)
+WORST: dict = {}
+
+
+def record_error(dtype: str, what: str, err: float, bar: float) -> None:
+    """Remembers the worst error of a kind of comparison; printed at the end of the run."""
+    key = (dtype, what)
+    if key not in WORST or err > WORST[key][0]:
+        WORST[key] = (err, bar)
+
 
 CONFIGS = {
     "A": (tiny.TINY_A, tiny.PAGE_A),
@@ -97,4 +107,5 @@ def assert_matches_plain(tm: TinyModel, request_tokens: dict, got: dict, what: s
             raise AssertionError(f"{what}: request {r!r} differs from the plain implementation: max rel error "
                                  f"{err:.3e} (bar {TOLERANCE[tm.dtype]:.0e}); first wrong position {first} "
                                  f"of {len(request_tokens[r])}")
+    record_error(tm.dtype, what, worst, TOLERANCE[tm.dtype])
     return worst

@@ -104,3 +104,31 @@ def test_spec_names_every_checkpoint_tensor():
         needs = tensor_needs_of(arch.describe(cfg))
         required = {n: need.shape for n, need in needs.items() if not need.optional}
         assert required == tiny.tensor_shapes(text)
+
+
+def test_a_layer_may_only_read_a_cache_it_can_see_whole():
+    """A layer that reads another layer's cache must have that layer's kv heads and head
+    size, and a window no wider than the owner's: pages behind the owner's window are
+    given back while the request runs."""
+    import torch
+
+    from pulsarlm_b200.models.llama import describe_llama
+    from pulsarlm_b200.models.model import Model
+
+    def model_with(reader: dict, owner: dict) -> Model:
+        spec = describe_llama(LlamaConfig.from_text(tiny.TINY_A))
+        spec.layers[0].mixer.params.update(owner)
+        spec.layers[1].mixer.params.update({"cache_from": 0, **reader})
+        return Model(spec, torch.float32, torch.device("cpu"))
+
+    assert model_with({}, {}).cache_sources() == [None, 0]
+    assert model_with({"window": 8}, {"window": 24}).cache_sources() == [None, 0]
+    assert model_with({"window": 8}, {}).cache_sources() == [None, 0]
+    with pytest.raises(ValueError, match="keeps a window of 8 only"):
+        model_with({}, {"window": 8}).cache_sources()
+    with pytest.raises(ValueError, match="keeps a window of 8 only"):
+        model_with({"window": 9}, {"window": 8}).cache_sources()
+    with pytest.raises(ValueError, match="kv heads of size"):
+        model_with({"n_kv_heads": 2}, {}).cache_sources()
+    with pytest.raises(ValueError, match="kv heads of size"):
+        model_with({"head_dim": 32}, {}).cache_sources()

@@ -105,10 +105,10 @@ def test_seeded_sampling_does_not_depend_on_the_company(seed):
 @pytest.mark.parametrize("seed", [1, 9, 17, 58])
 def test_bfloat16_generation_with_graphs_at_tensor_core_head_sizes(seed):
     """bfloat16, head sizes 64 and 128, one to seventeen requests with prompts of up to
-    900 tokens through `Engine.generate` (scheduler's portions, graph-replayed and
-    pipelined decode steps): bfloat16 may flip a near-tie, so every generated token
-    must be the plain implementation's argmax for its own prefix or within the
-    rounding bar of it."""
+    900 tokens through the engine (scheduler's portions, graph-replayed and pipelined
+    decode steps): bfloat16 may flip a near-tie, so the tokens are not compared; the
+    logits row each token was drawn from must match the plain implementation's row
+    for the generated sequence, and the token must be that row's argmax."""
     import plain_llama as plain
     from pulsarlm_b200 import Engine, SamplingParams
     from pulsarlm_b200.engine.loading import load_model
@@ -129,12 +129,21 @@ def test_bfloat16_generation_with_graphs_at_tensor_core_head_sizes(seed):
     page = rng.choice([16, 32])
     engine = Engine(model, n_pages=sum(len(p) + new_tokens for p in prompts) // page + n_requests + 4, page_size=page,
                     prefill_tokens_per_step=rng.choice([64, 256, 1024]), max_requests=32, stop_ids=[],
-                    lookahead=rng.random() < 0.7)
-    outputs = engine.generate(prompts, SamplingParams(temperature=0.0), max_tokens=new_tokens, ignore_eos=True)
+                    lookahead=rng.random() < 0.7, record_logits=True)
+    requests = [engine.submit(p, sampling=SamplingParams(temperature=0.0), max_tokens=new_tokens, ignore_eos=True)
+                for p in prompts]
+    while any(not r.finished for r in requests):
+        engine.step()
+    engine.sync()
+    engine.runner.check_status()
     assert engine.runner.graph_steps > 0
-    for prompt, output in zip(prompts, outputs):
-        assert len(output) == new_tokens
-        logits = plain.forward(cfg, weights, list(prompt) + list(output), dtype=torch.float32)
-        for i, token in enumerate(output):
-            row = logits[len(prompt) - 1 + i]
-            assert float((row.max() - row[token]) / row.abs().max()) <= 2e-2, (i, cfg)
+    from harness import TOLERANCE, record_error
+
+    for prompt, request in zip(prompts, requests):
+        output = list(request.output)
+        assert len(output) == new_tokens == len(request.logits)
+        assert output == [int(row.argmax()) for row in request.logits]
+        reference = plain.forward(cfg, weights, list(prompt) + output[:-1], dtype=torch.float32)
+        err = plain.max_relative_error(torch.stack(request.logits), reference[len(prompt) - 1:])
+        record_error("bfloat16", "random configurations through the engine with graphs", err, TOLERANCE["bfloat16"])
+        assert err < TOLERANCE["bfloat16"], (err, cfg)

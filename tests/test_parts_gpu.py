@@ -277,3 +277,63 @@ def test_windows_at_tensor_core_head_sizes_with_long_histories(seed):
         positions = sorted(rows)
         err = plain_llama.max_relative_error(torch.stack([rows[p] for p in positions]), want[r][positions])
         assert err < TOLERANCE["bfloat16"], (r, err, cfg, windows)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("cfg_key", ["A", "B"])
+def test_attention_with_per_head_norms_and_squashed_scores(dtype, tol, cfg_key):
+    """Options of the attention part that Llama leaves off: an RMS norm over each head of
+    q and of k before the rotation (own scales, own eps), and scores squashed by
+    cap * tanh(s / cap). Layer 0 has the norms, layer 1 the cap and the norms, the rest
+    is Llama's; prompts in a portion and single tokens, against the formulas written out."""
+    from pulsarlm_b200.parts.spec import TensorNeed  # noqa: F401
+
+    cfg = {"A": tiny.TINY_A, "B": tiny.TINY_B}[cfg_key]
+    hd = plain_llama.head_dim_of(cfg)
+    nh, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    w = tiny.random_weights(cfg, 12, dtype)
+    gen = torch.Generator().manual_seed(4)
+    spec = llama_spec(cfg)
+    eps, cap = 1e-3, 1.5
+    for layer in (0, 1):
+        p = f"model.layers.{layer}.self_attn."
+        spec.layers[layer].mixer.params["qk_norm_eps"] = eps
+        spec.layers[layer].mixer.tensors.update({"q_norm": p + "q_norm.weight", "k_norm": p + "k_norm.weight"})
+        w[p + "q_norm.weight"] = (1.0 + 0.3 * torch.randn(hd, generator=gen)).float()
+        w[p + "k_norm.weight"] = (1.0 + 0.3 * torch.randn(hd, generator=gen)).float()
+    spec.layers[1].mixer.params["softcap"] = cap
+    tokens = tiny.random_tokens(cfg, 45, 6)
+    got, _ = run_whole(spec, w, dtype, tokens)
+
+    wd = {k: v.double() for k, v in w.items()}
+    n = len(tokens)
+    pos = torch.arange(n)
+    rope = plain_llama.rope_settings(cfg)
+    inv = plain_llama.rope_inverse_frequency(rope["theta"], hd, rope["llama3"])
+    rms = cfg["rms_norm_eps"]
+    x = plain_llama.embed(wd["model.embed_tokens.weight"], torch.tensor(tokens))
+    for layer in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{layer}."
+        h = plain_llama.rms_norm(x, wd[p + "input_layernorm.weight"], rms)
+        if layer in (0, 1):
+            q = (h @ wd[p + "self_attn.q_proj.weight"].T).view(n, nh, hd)
+            k = (h @ wd[p + "self_attn.k_proj.weight"].T).view(n, nkv, hd)
+            v = (h @ wd[p + "self_attn.v_proj.weight"].T).view(n, nkv, hd)
+            q = plain_llama.rms_norm(q, wd[p + "self_attn.q_norm.weight"], eps)
+            k = plain_llama.rms_norm(k, wd[p + "self_attn.k_norm.weight"], eps)
+            q, k = plain_llama.rope_rotate(q, pos, inv), plain_llama.rope_rotate(k, pos, inv)
+            group = nh // nkv
+            scores = torch.einsum("qhd,khd->hqk", q, k.repeat_interleave(group, dim=1)) / math.sqrt(hd)
+            if layer == 1:
+                scores = cap * torch.tanh(scores / cap)
+            scores = scores.masked_fill(pos[None, :] > pos[:, None], float("-inf"))
+            o = torch.einsum("hqk,khd->qhd", torch.softmax(scores, dim=-1), v.repeat_interleave(group, dim=1))
+            x = x + o.reshape(n, nh * hd) @ wd[p + "self_attn.o_proj.weight"].T
+        else:
+            x = x + plain_llama.attention_block(h, wd, p, cfg, pos)
+        h = plain_llama.rms_norm(x, wd[p + "post_attention_layernorm.weight"], rms)
+        x = x + plain_llama.swiglu_mlp(h, wd[p + "mlp.gate_proj.weight"], wd[p + "mlp.up_proj.weight"],
+                                       wd[p + "mlp.down_proj.weight"])
+    head = wd.get("lm_head.weight", wd["model.embed_tokens.weight"])
+    want = plain_llama.rms_norm(x, wd["model.norm.weight"], rms) @ head.T
+    assert rel(got, want) < tol

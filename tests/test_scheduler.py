@@ -204,3 +204,21 @@ def test_many_requests_under_page_pressure_all_finish_right():
     for r in reqs:
         assert r.output == expected_output(r.prompt, r.max_tokens), r.id
     assert cache.free_pages() == 12
+
+
+def test_more_requests_than_any_fixed_buffer_can_end_in_one_plan():
+    """A queue far longer than the slots, cancelled all at once: one plan ends every
+    request (its buffers grow with the number of known requests), and the few that
+    ran give back what they held."""
+    cache, sched, stepper = make(pages=64, slots=2)
+    requests = [Request(i, [1 + i % 5, 2, 3], max_tokens=4) for i in range(700)]
+    for r in requests:
+        sched.add(r)
+    entries, gone = sched.plan()
+    assert len(entries) == 2 and not gone
+    sched.finish_step(entries, stepper.run(entries))
+    for r in requests:
+        r.cancel()
+    entries, gone = sched.plan()
+    assert not entries and len(gone) == 700 and all(r.finish_reason == "cancelled" for r in requests)
+    assert not sched.has_work() and cache.free_pages() == 64 and cache.stats()["slots_used"] == 0

@@ -8,7 +8,10 @@ device memory away at start-up. They can still pass inputs and outputs they
 already own. This test stands in for such a caller: it reaches the exported C
 symbol through ctypes with raw pointers, twice in a row (the second call finds
 the first call's leftovers in the shared array), and checks the result against
-the ordinary entry point given scratch of its own. The file sorts last so that a
+the ordinary entry point given scratch of its own and against a dense float64
+attention; that the driver's count of free device memory does not move across a
+call; a split count above what a thread-block cluster merges; and a call that
+fills the built-in array almost to its end. The file sorts last so that a
 run that stops at the first failure has already run every other test; it also
 passes when it is the only test in a fresh process.
 """
@@ -49,6 +52,24 @@ def call_static(lib, q, kp, vp, table, pos, entry, out, page, splits, status):
               torch.cuda.current_stream().cuda_stream)
 
 
+def dense_attention(q, kp, vp, table, pos, entry, page):
+    """Softmax attention of each query over its request's keys 0..pos, float64 on the CPU."""
+    out = torch.empty(q.shape, dtype=torch.float64)
+    qd, kd, vd = q.double().cpu(), kp.double().cpu(), vp.double().cpu()
+    group = q.shape[1] // kp.shape[1]
+    scale = 1.0 / math.sqrt(q.shape[2])
+    for t in range(q.shape[0]):
+        n = int(pos[t]) + 1
+        row = table[int(entry[t])].tolist()
+        pages = -(-n // page)
+        keys = torch.cat([kd[row[j]] for j in range(pages)], dim=1)[:, :n]  # [nkv, n, hd]
+        vals = torch.cat([vd[row[j]] for j in range(pages)], dim=1)[:, :n]
+        for h in range(q.shape[1]):
+            s = (keys[h // group] @ qd[t, h]) * scale
+            out[t, h] = torch.softmax(s, 0) @ vals[h // group]
+    return out
+
+
 def test_static_scratch_entry_point_matches_the_allocating_one_twice_in_a_row():
     from pulsarlm_b200.kernels import ops
 
@@ -57,10 +78,16 @@ def test_static_scratch_entry_point_matches_the_allocating_one_twice_in_a_row():
     lib.pl_static_scratch_floats.restype = ctypes.c_int64
     assert lib.pl_static_scratch_floats() == 4 * 1024 * 1024
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    # two different calls back to back: other lengths, other split counts, so the
-    # second reads nothing the first left behind unless the kernel is wrong
-    for seed, lengths, splits in ((1, [700, 33, 250, 1], 5), (2, [90, 1200], 3)):
-        q, kp, vp, table, pos, entry, page = make_case(seed, lengths)
+    # different calls back to back: other lengths, other split counts, so a call
+    # reads nothing an earlier one left behind unless the kernel is wrong. The third
+    # splits 24 ways (more than a cluster merges); the fourth needs 4,193,280 of the
+    # array's 4,194,304 floats.
+    cases = ((1, [700, 33, 250, 1], 5, 8, 2), (2, [90, 1200], 3, 8, 2), (3, [3000, 450], 24, 8, 2),
+             (4, [300 + 7 * i for i in range(42)], 24, 32, 8))
+    for seed, lengths, splits, nh, nkv in cases:
+        q, kp, vp, table, pos, entry, page = make_case(seed, lengths, nh=nh, nkv=nkv)
+        needed = ops.attention_decode_scratch_floats(q.shape[0], q.shape[1], q.shape[2], splits)
+        assert needed <= 4 * 1024 * 1024 and (seed != 4 or needed > 4 * 1024 * 1024 - 2048)
         want = torch.empty_like(q)
         scratch = torch.empty(ops.attention_decode_scratch_floats(q.shape[0], q.shape[1], q.shape[2], splits),
                               device=DEV)
@@ -74,10 +101,23 @@ def test_static_scratch_entry_point_matches_the_allocating_one_twice_in_a_row():
         assert code == 0, lib.pl_last_error().decode()
         assert torch.cuda.memory_allocated() == before
         assert int(status) == 0
+        # Once more with the driver's own count of free memory around the call: it sees any
+        # cudaMalloc, not only torch's. (Measured on a repeated call: the first launch of a
+        # kernel may make the driver load its code, which is not an allocation of the call's.)
+        again = torch.full_like(q, float("nan"))
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        assert call_static(lib, q, kp, vp, table, pos, entry, again, page, splits, status) == 0
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before
+        assert torch.equal(again, got)
         # same kernel, same split boundaries: the two agree to the bit, which is
         # well inside the 1e-2 bar the other bfloat16 attention tests use
         err = float((got.float() - want.float()).abs().max() / want.float().abs().max())
         assert err < 1e-2 and torch.equal(got, want)
+        # and against the dense attention, at the bar of the other bfloat16 attention tests
+        dense = dense_attention(q, kp, vp, table.cpu(), pos.cpu(), entry.cpu(), page)
+        assert float((got.double().cpu() - dense).abs().max() / dense.abs().max()) < 1e-2
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():
