@@ -192,7 +192,10 @@ class CacheManager:
             where = group.layers.index(layer)
             out[layer] = KVBinding(g, group.tensor[where, :, 0], group.tensor[where, :, 1], self.page_size,
                                    group.step_mass[where] if group.step_mass is not None else None,
-                                   group.step_weight[where] if group.step_weight is not None else None)
+                                   group.step_weight[where] if group.step_weight is not None else None,
+                                   group.mass_sum[where] if group.mass_sum is not None else None,
+                                   group.weight_sum[where] if group.weight_sum is not None else None,
+                                   self.mass_decay)
         for layer in self.state_layers:
             out[layer] = StateBinding(self.states[layer])
         return out

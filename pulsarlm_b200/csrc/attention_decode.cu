@@ -53,6 +53,10 @@ struct DecodeParams {
     int n_splits;
     int cluster;  // 1: the splits are the ranks of a thread-block cluster and merge among themselves
     int32_t* status;
+    // Attention mass (optional): every 16-key tile's largest masked score per head, in the
+    // exponent's units (scaled score * log2 e), at [(token * heads + head) * max_tiles + tile].
+    float* tile_max;
+    int max_tiles;
 };
 
 // In-cluster merge: outputs are counted in groups of four dims ("vecs"); rank r owns
@@ -219,6 +223,17 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Deco
         tile_lo = fmaxf(tile_lo, __shfl_xor_sync(0xffffffffu, tile_lo, 2));
         tile_hi = fmaxf(tile_hi, __shfl_xor_sync(0xffffffffu, tile_hi, 1));
         tile_hi = fmaxf(tile_hi, __shfl_xor_sync(0xffffffffu, tile_hi, 2));
+        if (p.tile_max != nullptr && tig == 0) {
+            // One warp of one split owns this tile: a plain store, the same whatever the split count.
+            const int tile = key0 / kTile;
+            const int64_t head0 = static_cast<int64_t>(t) * p.n_heads + kv_head * p.group;
+            if (g < p.group) {
+                p.tile_max[(head0 + g) * p.max_tiles + tile] = tile_lo;
+            }
+            if (g + 8 < p.group) {
+                p.tile_max[(head0 + g + 8) * p.max_tiles + tile] = tile_hi;
+            }
+        }
         const float new_lo = fmaxf(m_lo, tile_lo), new_hi = fmaxf(m_hi, tile_hi);
         // A row that has seen no key yet keeps exponent base 0 (all its p are 0).
         const float base_lo = new_lo == -INFINITY ? 0.0f : new_lo;
@@ -567,7 +582,7 @@ int run_attention_decode(bool allow_cluster, const void* q, int64_t q_row_stride
                                const int32_t* table, int table_width, const int32_t* pos, const int32_t* entry,
                                void* out, int64_t out_row_stride, int n_tokens, int n_heads, int n_kv_heads,
                                int head_dim, int window, float scale, int n_splits, float* scratch,
-                               int32_t* status, cudaStream_t stream) {
+                               int32_t* status, cudaStream_t stream, float* tile_max = nullptr, int max_tiles = 0) {
     PL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
                "attention_decode: bad sizes tokens=%d heads=%d kv_heads=%d", n_tokens, n_heads, n_kv_heads);
     const int group = n_heads / n_kv_heads;
@@ -610,6 +625,11 @@ int run_attention_decode(bool allow_cluster, const void* q, int64_t q_row_stride
     p.scale_log2 = scale * 1.4426950408889634f;
     p.n_splits = n_splits;
     p.status = status;
+    p.tile_max = tile_max;
+    p.max_tiles = max_tiles;
+    PL_REQUIRE(tile_max == nullptr || max_tiles >= static_cast<int64_t>(table_width) * page_size / kTile,
+               "attention_decode: %d tiles per row of tile maxima do not cover a table of %d pages", max_tiles,
+               table_width);
     if (head_dim == 64) {
         return launch_decode<64>(p, n_tokens, n_kv_heads, allow_cluster, stream);
     }
@@ -631,6 +651,85 @@ PL_API int pl_attention_decode(const void* q, int64_t q_row_stride, const void* 
     return run_attention_decode(true, q, q_row_stride, k_pool, v_pool, page_stride, head_stride, page_size, n_pages,
                                 table, table_width, pos, entry, out, out_row_stride, n_tokens, n_heads, n_kv_heads,
                                 head_dim, window, scale, n_splits, scratch, status, stream);
+}
+
+namespace {
+
+// One thread per (page of the request, head): folds a decode step's tile maxima into the
+// per-page accumulators. mass[page, head] = mass * keep + w * (largest scaled score of the
+// token over the page's keys it attends), weight[page] likewise with w alone, where w =
+// decay, keep = 1 - decay for pages the request already held and 0 for the page this
+// token opens (it may hold a former owner's sums). Every page belongs to one request and
+// a request has one token in the step: no two threads touch the same element.
+__global__ void attention_mass_fold_decode_kernel(const float* __restrict__ tile_max, int max_tiles,
+                                                  const int32_t* __restrict__ table, int table_width,
+                                                  const int32_t* __restrict__ pos, const int32_t* __restrict__ entry,
+                                                  float* __restrict__ mass, float* __restrict__ weight, int n_pages,
+                                                  int n_heads, int page_size, int window, float decay) {
+    pl_grid_trigger();
+    pl_grid_wait();
+    const int t = blockIdx.y;
+    const int position = pos[t];
+    const int ctx = position + 1;
+    const int first = window > 0 ? max(0, ctx - window) : 0;
+    const int page_first = first / page_size, page_last = position / page_size;
+    const int32_t* row = table + static_cast<int64_t>(entry[t]) * table_width;
+    const int tiles_per_page = page_size / kTile;
+    const int items = (page_last - page_first + 1) * n_heads;
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < items; idx += gridDim.x * blockDim.x) {
+        const int j = page_first + idx / n_heads, h = idx % n_heads;
+        const int page = row[j];
+        if (page < 0 || page >= n_pages) {
+            continue;  // (the attention kernel has flagged it)
+        }
+        // the tiles of the page that hold attended keys
+        const int tile0 = max(j * tiles_per_page, first / kTile);
+        const int tile1 = min((j + 1) * tiles_per_page, (ctx + kTile - 1) / kTile);
+        float largest = -INFINITY;
+        const float* maxima = tile_max + (static_cast<int64_t>(t) * n_heads + h) * max_tiles;
+        for (int tile = tile0; tile < tile1; ++tile) {
+            largest = fmaxf(largest, maxima[tile]);
+        }
+        if (!(largest > -INFINITY)) {
+            continue;
+        }
+        const float keep = j * page_size >= position ? 0.0f : 1.0f - decay;
+        const int64_t at = static_cast<int64_t>(page) * n_heads + h;
+        mass[at] = mass[at] * keep + decay * (largest * 0.6931471805599453f);  // back from base-2 units
+        if (h == 0) {
+            weight[page] = weight[page] * keep + decay;
+        }
+    }
+}
+
+}  // namespace
+
+// pl_attention_decode that also measures attention mass: the kernel records every
+// tile's largest score in tile_max (fp32 [tokens, heads, max_tiles], max_tiles >=
+// table_width * page_size / 16), and a second kernel folds them into mass [pages,
+// heads] and weight [pages] (see attention_mass_fold_decode_kernel). decay in (0, 1].
+PL_API int pl_attention_decode_mass(const void* q, int64_t q_row_stride, const void* k_pool, const void* v_pool,
+                                    int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
+                                    const int32_t* table, int table_width, const int32_t* pos, const int32_t* entry,
+                                    void* out, int64_t out_row_stride, int n_tokens, int n_heads, int n_kv_heads,
+                                    int head_dim, int window, float scale, int n_splits, float* scratch,
+                                    float* tile_max, int max_tiles, float* mass, float* weight, float decay,
+                                    int32_t* status, cudaStream_t stream) {
+    PL_REQUIRE(tile_max != nullptr && mass != nullptr && weight != nullptr && decay > 0.0f && decay <= 1.0f,
+               "attention_decode_mass: needs tile_max, mass, weight and a decay in (0, 1]");
+    const int code = run_attention_decode(true, q, q_row_stride, k_pool, v_pool, page_stride, head_stride, page_size,
+                                          n_pages, table, table_width, pos, entry, out, out_row_stride, n_tokens,
+                                          n_heads, n_kv_heads, head_dim, window, scale, n_splits, scratch, status,
+                                          stream, tile_max, max_tiles);
+    if (code != 0 || n_tokens == 0) {
+        return code;
+    }
+    const int items = table_width * n_heads;
+    const dim3 grid(items < 256 ? 1 : (items + 255) / 256 > 64 ? 64 : (items + 255) / 256, n_tokens);
+    pl_launch_overlapped(attention_mass_fold_decode_kernel, grid, 256, 0, stream, tile_max, max_tiles, table,
+                         table_width, pos, entry, mass, weight, n_pages, n_heads, page_size, window, decay);
+    PL_CHECK_LAUNCH("attention_mass_fold_decode");
+    return 0;
 }
 
 // ---------------------------------------------------------------------------

@@ -151,11 +151,24 @@ class GraphedDecode:
         """Runs the step once eagerly on a side stream (libraries set themselves up),
         then records it. The buffers must hold a valid batch."""
         self.dev.copy_(self.host, non_blocking=True)
-        side = torch.cuda.Stream()
+        # The warm-up run really runs the step. Keys and values are written by position, so
+        # running it twice changes nothing; the attention-mass accumulators are added to, so
+        # they are put back as they were.
+        cache = self.runner.cache
+        kept = [(g.mass_sum, g.mass_sum.clone(), g.weight_sum, g.weight_sum.clone())
+                for g in cache.groups if g.mass_sum is not None]
+        # One side stream for every capture of this runner: the allocator keeps freed blocks
+        # per stream, so a new stream per capture would strand the warm-up's buffers.
+        if self.runner._capture_stream is None:
+            self.runner._capture_stream = torch.cuda.Stream()
+        side = self.runner._capture_stream
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             self._forward()
         torch.cuda.current_stream().wait_stream(side)
+        for mass, mass_before, weight, weight_before in kept:
+            mass.copy_(mass_before)
+            weight.copy_(weight_before)
         torch.cuda.synchronize()
         self.graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()

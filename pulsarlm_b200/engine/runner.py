@@ -88,11 +88,14 @@ class ModelRunner:
         self._graphs: collections.OrderedDict = collections.OrderedDict()
         self.max_graphs = 24
         self._graph_pool = None
+        self._capture_stream = None
         self.graph_captures = 0
         # Replaying a captured step re-runs the capture's warm-up on the same tokens,
         # which is harmless for caches written by position but not for states updated
-        # in place, so models with state slots step eagerly.
-        self.graphs_allowed = not cache.state_layers and cache.mass_decay is None
+        # in place, so models with state slots step eagerly. With attention mass measured,
+        # steps are captured only if every mixer can measure inside one.
+        self.graphs_allowed = not cache.state_layers and (cache.mass_decay is None or all(
+            getattr(part, "measures_mass_in_captured_steps", lambda: True)() for part in model.parts()))
         self.steps = 0
         self.tokens_run = 0
         self.graph_steps = 0
@@ -311,6 +314,11 @@ class ModelRunner:
         for g in self.cache.groups:
             table = h[f"table{g.index}"]
             self.cache.fill_tables(g.index, handles, table[:n], h["slots"][:n])
+        if self.cache.mass_decay is not None:
+            # The kernels see which page a token opens; the host's list of pages taken since
+            # the last eager step is not needed and must not reach that step.
+            for g in self.cache.groups:
+                self.cache.take_fresh_pages(g.index)
         graph.pad_rows(n, self.cache.pad_page)
         graph.plan(new_lens)
         if fresh:

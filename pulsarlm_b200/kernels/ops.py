@@ -25,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 13
+ABI_VERSION = 14
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -46,6 +46,9 @@ _SIGNATURES = {
                           _I32, _I32, _I32, _I32, _I32, _F32, _F32, _I32, _PTR, _PTR, _PTR, _PTR, _PTR],
     "pl_attention_decode": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
                             _I32, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR, _PTR],
+    "pl_attention_decode_mass": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
+                                 _I32, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR, _I32, _PTR, _PTR, _F32, _PTR,
+                                 _PTR],
     "pl_attention_decode_supports": [_I32, _I32, _I32, _I32],
     "pl_attention_prefill": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _I32, _PTR, _I64,
                              _I32, _I32, _I32, _I32, _F32, _PTR, _PTR],
@@ -299,7 +302,7 @@ def rope_kv_write(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | Non
         assert inv_freq.dtype == torch.float64 and inv_freq.numel() == rotary // 2 and inv_freq.is_contiguous()
     _call("pl_rope_kv_write", _p(q), _p(k), _p(v), row_stride, _p(pos), _p(entry), _p(table), table.shape[1],
           _p(k_pool), _p(v_pool), page_stride, head_stride, page_size, n_pages, _p(inv_freq), rotary, tokens,
-          n_heads, n_kv, head_dim, _code(q.dtype), _p(status), _stream())
+          n_heads, n_kv, head_dim, _code(q.dtype), _p(q_norm), _p(k_norm), float(norm_eps), _p(status), _stream())
 
 
 def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,
@@ -346,9 +349,15 @@ def attention_decode_scratch_floats(n_tokens: int, n_heads: int, head_dim: int, 
 def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,
                      pos: torch.Tensor, entry: torch.Tensor, out: torch.Tensor, page_size: int, window: int | None,
                      scale: float, n_splits: int, scratch: torch.Tensor | None,
-                     status: torch.Tensor | None = None) -> None:
+                     status: torch.Tensor | None = None, mass: tuple | None = None) -> None:
     """bf16 attention of single decode tokens, split over the keys `n_splits` ways;
-    shapes as attention_simt. `scratch`: fp32, attention_decode_scratch_floats long."""
+    shapes as attention_simt. `scratch`: fp32, attention_decode_scratch_floats long.
+    `mass` = (tile_max, mass_sum, weight_sum, decay): also measures attention mass.
+    tile_max is fp32 scratch of tokens * heads * (table width * page_size / 16) floats;
+    mass_sum fp32 [pages, nh] and weight_sum fp32 [pages] are the running accumulators:
+    what the request's pages hold is scaled by 1 - decay (the page the token opens
+    restarts at zero) and decay * (the token's largest scaled score in the page), per
+    head, and decay, per page, are added."""
     _dev(q, k_pool, v_pool, table, pos, entry, out, scratch, status)
     tokens, n_heads, head_dim = q.shape
     n_pages, n_kv = k_pool.shape[0], k_pool.shape[1]
@@ -362,6 +371,20 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     if n_splits > 1:
         assert scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous()
         assert scratch.numel() >= attention_decode_scratch_floats(tokens, n_heads, head_dim, n_splits)
+    if mass is not None:
+        tile_max, mass_sum, weight_sum, decay = mass
+        max_tiles = table.shape[1] * page_size // 16
+        _dev(tile_max, mass_sum, weight_sum)
+        assert tile_max.dtype == torch.float32 and tile_max.is_contiguous()
+        assert tile_max.numel() >= tokens * n_heads * max_tiles
+        assert mass_sum.dtype == torch.float32 and mass_sum.shape == (n_pages, n_heads) and mass_sum.is_contiguous()
+        assert weight_sum.dtype == torch.float32 and weight_sum.shape == (n_pages,) and weight_sum.is_contiguous()
+        _call("pl_attention_decode_mass", _p(q), q.stride(0), _p(k_pool), _p(v_pool), k_pool.stride(0),
+              k_pool.stride(1), page_size, n_pages, _p(table), table.shape[1], _p(pos), _p(entry), _p(out),
+              out.stride(0), tokens, n_heads, n_kv, head_dim, int(window or 0), float(scale), int(n_splits),
+              _p(scratch), _p(tile_max), max_tiles, _p(mass_sum), _p(weight_sum), float(decay), _p(status),
+              _stream())
+        return
     _call("pl_attention_decode", _p(q), q.stride(0), _p(k_pool), _p(v_pool), k_pool.stride(0), k_pool.stride(1),
           page_size, n_pages, _p(table), table.shape[1], _p(pos), _p(entry), _p(out), out.stride(0), tokens,
           n_heads, n_kv, head_dim, int(window or 0), float(scale), int(n_splits), _p(scratch), _p(status),

@@ -28,6 +28,11 @@ class KVBinding:
     # when the cache manager measures it (else None).
     mass_sum: torch.Tensor | None = None
     weight_sum: torch.Tensor | None = None
+    # The running accumulators themselves [pages, n_heads] and [pages], and the decay: the
+    # tensor-core decode kernel folds a step's mass into them on the device.
+    mass_total: torch.Tensor | None = None
+    weight_total: torch.Tensor | None = None
+    mass_decay: float | None = None
 
 
 _SM_COUNT: dict = {}
@@ -233,6 +238,13 @@ class Attention(Part):
             self._prefill_kernel = ops.attention_prefill_supports(self.head_dim, self.cache.page_size, dtype)
         return self._decode_kernel, self._prefill_kernel
 
+    def measures_mass_in_captured_steps(self) -> bool:
+        """Whether this layer can measure attention mass inside a captured decode step
+        (the tensor-core decode kernel takes its shape and it has no score cap)."""
+        if self.cache is None or self.softcap:
+            return False
+        return self._kernels(self.ctx.dtype)[0]
+
     def plan_key(self):
         """Layers of equal tiling share one plan: the tile lists depend on the kernels'
         tile heights only (twice as high when a CTA works on one head: an odd group)."""
@@ -285,7 +297,26 @@ class Attention(Part):
         everything else (float32, unusual shapes) goes to the CUDA-core kernel."""
         cache = self.cache
         tokens = q.shape[0]
-        if cache.mass_sum is not None and self.cache_from is None and batch.extras.get("query_weights") is not None:
+        measuring = cache.mass_sum is not None and self.cache_from is None
+        if measuring and batch.extras.get("graph") and self.measures_mass_in_captured_steps() \
+                and int(batch.n_decode) == tokens:
+            # A captured step of single tokens: the tensor-core kernel records every tile's
+            # largest score and a second kernel folds them into the accumulators.
+            max_context = (batch.plans.get(self.plan_key()) or {}).get("max_context") or 0
+            if self.window:
+                max_context = min(max_context, self.window + 16)
+            splits = decode_splits(tokens * self.n_kv, max_context, q.device, self.head_dim, self.n_heads // self.n_kv)
+            scratch = None
+            if splits > 1:
+                scratch = torch.empty(ops.attention_decode_scratch_floats(tokens, self.n_heads, self.head_dim, splits),
+                                      dtype=torch.float32, device=q.device)
+            tile_max = torch.empty(tokens * self.n_heads * (table.shape[1] * cache.page_size // 16),
+                                   dtype=torch.float32, device=q.device)
+            ops.attention_decode(q, cache.k_pool, cache.v_pool, table, batch.pos, batch.entry, out, cache.page_size,
+                                 self.window, self.scale, splits, scratch, batch.status,
+                                 mass=(tile_max, cache.mass_total, cache.weight_total, cache.mass_decay))
+            return
+        if measuring and batch.extras.get("query_weights") is not None:
             # Measuring attention mass: the CUDA-core kernel writes it beside the output.
             ops.attention_simt(q, cache.k_pool, cache.v_pool, table, batch.pos, batch.entry, out, cache.page_size,
                                self.window, self.scale, batch.status, cache.mass_sum, cache.weight_sum,

@@ -23,7 +23,7 @@ def test_attention_mass_matches_dense_scores(key, dtype, tol):
     model = load_model(tm.folder, dtype, "cuda:0")
     cache = CacheManager(model.cache_needs(), tm.page, 12, 2, model.ctx.dtype, "cuda:0", mass_decay=decay)
     runner = ModelRunner(model, cache)
-    assert not runner.graphs_allowed
+    assert runner.graphs_allowed == (dtype == "bfloat16")  # (the tensor-core decode kernel can measure)
 
     # an earlier request leaves sums on pages that "a" will then take
     old = tiny.random_tokens(tm.cfg, 70, seed=8)
@@ -69,3 +69,60 @@ def test_logits_do_not_change_when_mass_is_measured():
     want = plain.generate([prompt], max_tokens=6, ignore_eos=True)
     assert measuring.generate([prompt], max_tokens=6, ignore_eos=True) == want
     assert measuring.runner.graph_steps == 0
+
+
+@pytest.mark.parametrize("head_dim,n_heads,n_kv,page", [(128, 4, 1, 16), (64, 8, 2, 32)])
+def test_attention_mass_from_captured_decode_steps(head_dim, n_heads, n_kv, page):
+    """bfloat16 at the tensor-core head sizes: five requests are prefilled (eager steps,
+    the CUDA-core kernel measures), then decode through captured steps (padded to eight
+    entries), where the tensor-core kernel records each tile's largest score and a fold
+    kernel updates the accumulators on the device; one request ends and its pages go to
+    a newcomer. Sums per page against the plain definition over dense scores."""
+    from harness import record_error
+    from pulsarlm_b200.cache.manager import CacheManager
+    from pulsarlm_b200.engine.runner import ModelRunner, StepEntry
+    from pulsarlm_b200.sampling.params import SamplingParams
+    from test_schedules_gpu import load, small_config
+
+    cfg = small_config(head_dim, n_heads, n_kv, layers=2)
+    weights = tiny.random_weights(cfg, 31, torch.bfloat16)
+    model = load(cfg, weights, "bfloat16")
+    decay = 0.2
+    cache = CacheManager(model.cache_needs(), page, 40, 6, torch.bfloat16, "cuda:0", mass_decay=decay)
+    runner = ModelRunner(model, cache)
+    assert runner.graphs_allowed
+    greedy = SamplingParams(temperature=0.0)
+    lengths = {"a": 37, "b": 5, "c": 64, "d": 90, "e": 16}
+    n_decode = 40
+    tokens = {r: tiny.random_tokens(cfg, n + n_decode, seed=200 + n) for r, n in lengths.items()}
+    portions = {r: [(0, n)] for r, n in lengths.items()}
+    runner.step([StepEntry(r, tokens[r][:n], []) for r, n in lengths.items()])
+    fed = dict(lengths)
+    live = list(lengths)
+    for step in range(n_decode):
+        if step == 12:  # b ends; a newcomer takes its pages and is prefilled in an eager step
+            runner.end("b")
+            live.remove("b")
+            tokens["f"] = tiny.random_tokens(cfg, 20 + n_decode, seed=77)
+            runner.step([StepEntry("f", tokens["f"][:20], [])])
+            portions["f"], fed["f"] = [(0, 20)], 20
+            live.append("f")
+        entries = [StepEntry(r, [tokens[r][fed[r]]], [0]) for r in live]
+        runner.decode_step(entries, [greedy] * len(live), [0] * len(live), [0] * len(live))
+        for r in live:
+            portions[r].append((fed[r], fed[r] + 1))
+            fed[r] += 1
+    runner.check_status()
+    assert runner.graph_steps == n_decode and all(n == 8 for n, _ in runner._graphs)
+    worst = 0.0
+    for r in live:
+        scores: list = []
+        plain_llama.forward(cfg, weights, tokens[r][: fed[r]], scores_out=scores)
+        got_mass, got_weight = cache.page_mass(r)
+        for layer in range(cfg["num_hidden_layers"]):
+            want_mass, want_weight = plain_llama.page_attention_mass(scores[layer], portions[r], page, decay)
+            assert torch.allclose(got_weight[layer].double().cpu(), want_weight, rtol=1e-5, atol=1e-7), (r, layer)
+            err = float((got_mass[layer].double().cpu() - want_mass).abs().max() / want_mass.abs().max())
+            worst = max(worst, err)
+            assert err < 2e-2, (r, layer, err)
+    record_error("bfloat16", f"attention mass from captured decode steps, head size {head_dim}", worst, 2e-2)

@@ -204,7 +204,8 @@ def test_mixed_batches_with_page_reuse_at_real_layer_sizes(dtype):
     n_pages = sum(sorted(-(-n // page) for n in lengths)[-4:])
     runner = ModelRunner(model, CacheManager(model.cache_needs(), page, n_pages, 4, torch_dtype, device))
     got = replay(runner, mixed_schedule(reqs, random.Random(5)))
-    assert runner.cache.groups[0].pool.high_water > n_pages // 2
+    # The requests need more pages in all than the pool has: some page served two requests.
+    assert sum(-(-n // page) for n in lengths) > n_pages >= runner.cache.groups[0].pool.high_water > n_pages // 3
     assert runner.cache.free_pages() == n_pages
     worst = 0.0
     for r, rows in got.items():
@@ -257,7 +258,7 @@ def test_captured_steps_hold_a_bounded_amount_of_memory():
 
     cfg = small_config(64, 4, 2, layers=1, vocab=4096)
     model = load(cfg, tiny.random_weights(cfg, 1, torch.bfloat16), "bfloat16")
-    cache = CacheManager(model.cache_needs(), 16, 40 * 130, 40, torch.bfloat16, "cuda:0")
+    cache = CacheManager(model.cache_needs(), 16, 40 * 184, 40, torch.bfloat16, "cuda:0")
     runner = ModelRunner(model, cache)
     runner.max_graphs = 6
     greedy = SamplingParams(temperature=0.0)
