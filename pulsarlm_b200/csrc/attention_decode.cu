@@ -57,6 +57,16 @@ struct DecodeParams {
     // exponent's units (scaled score * log2 e), at [(token * heads + head) * max_tiles + tile].
     float* tile_max;
     int max_tiles;
+    // Work-list mode (optional; never with `cluster`): CTA x takes item x = {token, first
+    // tile, tiles, split | splits << 12} instead of an equal share of token blockIdx.z. The
+    // partial results of token t's split s sit at slot token_slot[t] + s of the scratch
+    // ([slot][head]); the last CTA of a (token, kv head) to finish, by counters[token *
+    // kv heads + kv head] (zero before the launch and again after it), merges them.
+    const int32_t* items;
+    int n_items;
+    int n_kv_heads;
+    const int32_t* token_slot;
+    int32_t* counters;
 };
 
 // In-cluster merge: outputs are counted in groups of four dims ("vecs"); rank r owns
@@ -71,19 +81,20 @@ __host__ __device__ constexpr int merge_bytes(int n_vec, int splits) {
     return splits * owned_vecs_max(n_vec, splits) * 16 + splits * 16 * 8;
 }
 
+// One share of one (token, kv head): split `split` of `n_splits` equal shares, or in
+// work-list mode the tiles [item_first, item_first + item_tiles).
 template <int HD, int WARPS, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const DecodeParams p) {
+__device__ __forceinline__ void attention_decode_share(const DecodeParams& p, unsigned char* smem, const int split,
+                                                       const int kv_head, const int t, const int n_splits,
+                                                       const int item_first, const int item_tiles) {
     constexpr int kRowBytes = HD * 2;
     constexpr int kChunks = HD / 8;             // 16-byte chunks per row
     constexpr int kTileBytes = kTile * kRowBytes;
     constexpr int kStageBytes = 2 * kTileBytes;  // K tile then V tile
-    extern __shared__ __align__(128) unsigned char smem[];
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, tig = lane & 3;
-    const int split = blockIdx.x, kv_head = blockIdx.y, t = blockIdx.z;
 
-    pl_grid_trigger();  // positions and block tables are step inputs, read before the wait
     __shared__ __align__(8) uint64_t recv_bar;
     __shared__ int abort_flag;
     const int n_vec = p.group * (HD / 4);
@@ -103,8 +114,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Deco
     const int ctx = p.pos[t] + 1;
     const int first = p.window > 0 ? max(0, ctx - p.window) : 0;
     const int tile_first = first / kTile, tile_end = (ctx + kTile - 1) / kTile;
-    const int per_split = (tile_end - tile_first + p.n_splits - 1) / p.n_splits;
-    const int t0 = tile_first + split * per_split;
+    const int per_split = p.items != nullptr ? item_tiles : (tile_end - tile_first + n_splits - 1) / n_splits;
+    const int t0 = p.items != nullptr ? item_first : tile_first + split * per_split;
     const int t1 = min(t0 + per_split, tile_end);
     const int32_t* row = p.table + static_cast<int64_t>(p.entry[t]) * p.table_width;
 
@@ -409,16 +420,118 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Deco
             }
         }
         const int h = kv_head * p.group + r;
-        if (p.n_splits == 1) {
+        if (n_splits == 1) {
             p.out[t * p.out_row_stride + static_cast<int64_t>(h) * HD + d] =
                 __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
         } else {
-            const int64_t slot = (static_cast<int64_t>(t) * p.n_heads + h) * p.n_splits + split;
+            const int64_t slot = p.items != nullptr
+                ? static_cast<int64_t>(p.token_slot[t] + split) * p.n_heads + h
+                : (static_cast<int64_t>(t) * p.n_heads + h) * n_splits + split;
             p.part_o[slot * HD + d] = acc;
             if (d == 0) {
                 p.part_ml[slot * 2] = m;
                 p.part_ml[slot * 2 + 1] = l;
             }
+        }
+    }
+    if (p.items == nullptr || n_splits == 1) {
+        return;
+    }
+    // Work-list mode: whoever finishes a (token, kv head) last merges its splits, in split
+    // order with the merge kernel's arithmetic, and leaves the counter at zero.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int32_t* counter = p.counters + 2 + static_cast<int64_t>(t) * p.n_kv_heads + kv_head;
+        is_last = atomicAdd(counter, 1) == n_splits - 1;
+        if (is_last) {
+            *counter = 0;
+        }
+    }
+    __syncthreads();
+    if (!is_last) {
+        return;
+    }
+    __threadfence();
+    const int64_t slot0 = static_cast<int64_t>(p.token_slot[t]) * p.n_heads + kv_head * p.group;
+    for (int idx = threadIdx.x; idx < p.group * HD; idx += WARPS * 32) {
+        const int r = idx / HD, d = idx % HD;
+        float m = -INFINITY;
+        for (int s = 0; s < n_splits; ++s) {
+            m = fmaxf(m, __ldcg(&p.part_ml[(slot0 + static_cast<int64_t>(s) * p.n_heads + r) * 2]));
+        }
+        float l = 0.0f, acc = 0.0f;
+        if (m > -INFINITY) {
+            for (int s = 0; s < n_splits; ++s) {
+                const int64_t slot = slot0 + static_cast<int64_t>(s) * p.n_heads + r;
+                const float scale = exp2f(__ldcg(&p.part_ml[slot * 2]) - m);
+                l += __ldcg(&p.part_ml[slot * 2 + 1]) * scale;
+                acc += __ldcg(&p.part_o[slot * HD + d]) * scale;
+            }
+        }
+        p.out[t * p.out_row_stride + static_cast<int64_t>(kv_head * p.group + r) * HD + d] =
+            __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+    }
+}
+
+// Grid (splits, kv heads, tokens), or in work-list mode a line of CTAs that take (item, kv
+// head) pairs off a queue, in list order, each as soon as it is free: counters[0] is the
+// queue's head and counters[1] counts the CTAs that found it empty; the last of them puts
+// both back to zero for the next launch.
+template <int HD, int WARPS, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32, HD == 64 ? 4 : 2) attention_decode_kernel(const DecodeParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    pl_grid_trigger();  // positions and block tables are step inputs, read before the wait
+    // One loop for both modes (the share's code once, and few registers live across it): with
+    // equal shares it runs once; with a work list it runs until the list's pairs are used up.
+    __shared__ int next;
+    int work = blockIdx.x, n_work = 1;
+    bool queued = false;
+    if (p.items != nullptr) {
+        // Rows of no tiles are padding; the last of them says in its first field how many rows are not.
+        const int4 last_row = reinterpret_cast<const int4*>(p.items)[p.n_items - 1];
+        n_work = (last_row.z > 0 ? p.n_items : min(max(last_row.x, 0), p.n_items)) * p.n_kv_heads;
+        queued = static_cast<int>(gridDim.x) < n_work;  // else a CTA for every pair: nobody needs the queue
+        if (work >= n_work) {
+            return;
+        }
+    }
+    // (Claiming a pair ahead of the one in work, to hide the queue's answer time, measured
+    // much slower: with two or three pairs per CTA the early claims leave CTAs idle.)
+    while (true) {
+        int split = blockIdx.x, kv_head = blockIdx.y, t = blockIdx.z, n_splits = p.n_splits, first = 0, tiles = 0;
+        if (p.items != nullptr) {
+            const int4 item = reinterpret_cast<const int4*>(p.items)[work / p.n_kv_heads];
+            split = item.w & 4095;
+            kv_head = work % p.n_kv_heads;
+            t = item.x;
+            n_splits = item.w >> 12;
+            first = item.y;
+            tiles = item.z;
+        }
+        attention_decode_share<HD, WARPS, STAGES>(p, smem, split, kv_head, t, n_splits, first, tiles);
+        if (!queued) {
+            return;
+        }
+        // (The counters are touched only after the kernels before this one have ended: an
+        // earlier launch that shares them is among those. The share has waited for them.)
+        __syncthreads();  // the next pair reuses the rings, and `next` has been read by all
+        if (threadIdx.x == 0) {
+            next = static_cast<int>(gridDim.x) + atomicAdd(p.counters, 1);
+        }
+        __syncthreads();
+        work = next;
+        if (work >= n_work) {
+            break;
+        }
+    }
+    if (threadIdx.x == 0) {
+        if (atomicAdd(p.counters + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+            // Everyone has taken its last look at the queue: this launch is done with it.
+            p.counters[0] = 0;
+            p.counters[1] = 0;
+            __threadfence();
         }
     }
 }
@@ -450,30 +563,32 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
 }
 
 constexpr int kWarps = 4;
-constexpr int kStages = 3;
+// Ring depth per warp. (Six stages at head size 64, the same bytes as three at 128, measured slower: two CTAs
+// per SM instead of four, 47.9 -> 55.4 us at batch 64 and 2,400 keys. The kernel wants warps, not depth.)
+constexpr int stages_of(int) { return 3; }
 
 constexpr int kClusterSplitsMax = 16;  // the largest cluster the part takes (above 8: opted into per kernel)
 
 template <int HD>
 int launch_decode(const DecodeParams& params, int n_tokens, int n_kv_heads, bool allow_cluster, cudaStream_t stream) {
-    constexpr int rings = kWarps * kStages * 2 * kTile * HD * 2;
+    constexpr int rings = kWarps * stages_of(HD) * 2 * kTile * HD * 2;
     static_assert(rings >= kWarps * 16 * (HD + 2) * 4, "the merge buffers must fit in the rings");
     constexpr int most_merge = merge_bytes(16 * (HD / 4), kClusterSplitsMax) + 1024;
     static bool configured = false, big_clusters = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(attention_decode_kernel<HD, kWarps, kStages>,
+        cudaError_t err = cudaFuncSetAttribute(attention_decode_kernel<HD, kWarps, stages_of(HD)>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, rings + most_merge);
         if (err != cudaSuccess) {
             return pl_fail(3, "attention_decode: cannot set shared memory size: %s", cudaGetErrorString(err));
         }
         // clusters of more than eight CTAs (if the device refuses, such split counts go through scratch)
-        big_clusters = cudaFuncSetAttribute(attention_decode_kernel<HD, kWarps, kStages>,
+        big_clusters = cudaFuncSetAttribute(attention_decode_kernel<HD, kWarps, stages_of(HD)>,
                                             cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
         cudaGetLastError();
         configured = true;
     }
     DecodeParams p = params;
-    p.cluster = allow_cluster && p.n_splits >= 2 && p.n_splits <= (big_clusters ? kClusterSplitsMax : 8);
+    p.cluster = p.items == nullptr && allow_cluster && p.n_splits >= 2 && p.n_splits <= (big_clusters ? kClusterSplitsMax : 8);
     if (p.cluster && p.n_splits > 8) {
         // a cluster this large has to find its SMs within one GPC: ask once whether any fits
         static int room[17][kClusterSplitsMax + 1] = {};
@@ -486,7 +601,35 @@ int launch_decode(const DecodeParams& params, int n_tokens, int n_kv_heads, bool
     if (!p.cluster && p.n_splits > 1 && p.part_o == nullptr) {
         return pl_fail(2, "attention_decode: %d splits need scratch memory", p.n_splits);
     }
-    const dim3 grid(p.n_splits, n_kv_heads, n_tokens);
+    const dim3 grid(p.n_splits, n_kv_heads, n_tokens);  // work-list mode: n_splits carries the item count here
+    if (p.items != nullptr) {
+        // As many CTAs as the device holds at once (or as there are items); each walks the list in strides.
+        static int resident = 0;
+        if (resident == 0) {
+            int device = 0, sms = 0, each = 0;
+            cudaGetDevice(&device);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&each, attention_decode_kernel<HD, kWarps, stages_of(HD)>,
+                                                              kWarps * 32, rings) != cudaSuccess || each < 1) {
+                cudaGetLastError();
+                each = 1;
+            }
+            resident = sms * each;
+        }
+        p.n_items = p.n_splits;
+        p.n_splits = 1;
+        p.n_kv_heads = n_kv_heads;
+        // A CTA for every (token, kv head), at least as many as the device holds at once, at most one
+        // per pair: requests left whole then never touch the queue, and what cutting adds goes through it.
+        const int64_t n_work = static_cast<int64_t>(p.n_items) * n_kv_heads;
+        int64_t ctas = static_cast<int64_t>(n_tokens) * n_kv_heads;
+        ctas = ctas < resident ? resident : ctas;
+        ctas = ctas > n_work ? n_work : ctas;
+        pl_launch_overlapped(attention_decode_kernel<HD, kWarps, stages_of(HD)>, dim3(static_cast<int>(ctas), 1, 1),
+                             kWarps * 32, rings, stream, p);
+        PL_CHECK_LAUNCH("attention_decode (work list)");
+        return 0;
+    }
     if (p.cluster) {
         cudaLaunchConfig_t config = {};
         config.gridDim = grid;
@@ -502,13 +645,13 @@ int launch_decode(const DecodeParams& params, int n_tokens, int n_kv_heads, bool
         attributes[1].val.programmaticStreamSerializationAllowed = 1;
         config.attrs = attributes;
         config.numAttrs = pl_overlap_enabled() ? 2 : 1;
-        const cudaError_t err = cudaLaunchKernelEx(&config, attention_decode_kernel<HD, kWarps, kStages>, p);
+        const cudaError_t err = cudaLaunchKernelEx(&config, attention_decode_kernel<HD, kWarps, stages_of(HD)>, p);
         if (err != cudaSuccess) {
             return pl_fail(3, "attention_decode: launch failed: %s", cudaGetErrorString(err));
         }
         return 0;
     }
-    pl_launch_overlapped(attention_decode_kernel<HD, kWarps, kStages>, grid, kWarps * 32, rings, stream, p);
+    pl_launch_overlapped(attention_decode_kernel<HD, kWarps, stages_of(HD)>, grid, kWarps * 32, rings, stream, p);
     PL_CHECK_LAUNCH("attention_decode");
     if (p.n_splits > 1) {
         pl_launch_overlapped(attention_decode_merge_kernel<HD>, dim3(p.n_heads, n_tokens), HD <= 64 ? 64 : 128, 0,
@@ -547,21 +690,21 @@ PL_API int pl_attention_decode_resident_clusters(int head_dim, int group, int n_
     int clusters = 0;
     cudaError_t err;
     if (head_dim == 64) {
-        constexpr int rings = kWarps * kStages * 2 * kTile * 64 * 2;
-        cudaFuncSetAttribute(attention_decode_kernel<64, kWarps, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        constexpr int rings = kWarps * stages_of(64) * 2 * kTile * 64 * 2;
+        cudaFuncSetAttribute(attention_decode_kernel<64, kWarps, stages_of(64)>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              rings + merge_bytes(16 * 16, kClusterSplitsMax) + 1024);
-        cudaFuncSetAttribute(attention_decode_kernel<64, kWarps, kStages>,
+        cudaFuncSetAttribute(attention_decode_kernel<64, kWarps, stages_of(64)>,
                              cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         config.dynamicSmemBytes = rings + merge_bytes(group * 16, n_splits);
-        err = cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel<64, kWarps, kStages>, &config);
+        err = cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel<64, kWarps, stages_of(64)>, &config);
     } else {
-        constexpr int rings = kWarps * kStages * 2 * kTile * 128 * 2;
-        cudaFuncSetAttribute(attention_decode_kernel<128, kWarps, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        constexpr int rings = kWarps * stages_of(128) * 2 * kTile * 128 * 2;
+        cudaFuncSetAttribute(attention_decode_kernel<128, kWarps, stages_of(128)>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              rings + merge_bytes(16 * 32, kClusterSplitsMax) + 1024);
-        cudaFuncSetAttribute(attention_decode_kernel<128, kWarps, kStages>,
+        cudaFuncSetAttribute(attention_decode_kernel<128, kWarps, stages_of(128)>,
                              cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         config.dynamicSmemBytes = rings + merge_bytes(group * 32, n_splits);
-        err = cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel<128, kWarps, kStages>, &config);
+        err = cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel<128, kWarps, stages_of(128)>, &config);
     }
     if (err != cudaSuccess) {
         cudaGetLastError();
@@ -582,7 +725,9 @@ int run_attention_decode(bool allow_cluster, const void* q, int64_t q_row_stride
                                const int32_t* table, int table_width, const int32_t* pos, const int32_t* entry,
                                void* out, int64_t out_row_stride, int n_tokens, int n_heads, int n_kv_heads,
                                int head_dim, int window, float scale, int n_splits, float* scratch,
-                               int32_t* status, cudaStream_t stream, float* tile_max = nullptr, int max_tiles = 0) {
+                               int32_t* status, cudaStream_t stream, float* tile_max = nullptr, int max_tiles = 0,
+                               const int32_t* items = nullptr, const int32_t* token_slot = nullptr,
+                               int32_t* counters = nullptr) {
     PL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
                "attention_decode: bad sizes tokens=%d heads=%d kv_heads=%d", n_tokens, n_heads, n_kv_heads);
     const int group = n_heads / n_kv_heads;
@@ -618,7 +763,14 @@ int run_attention_decode(bool allow_cluster, const void* q, int64_t q_row_stride
     p.out = static_cast<__nv_bfloat16*>(out);
     p.out_row_stride = out_row_stride;
     p.part_o = scratch;
-    p.part_ml = scratch != nullptr ? scratch + static_cast<int64_t>(n_tokens) * n_heads * n_splits * head_dim : nullptr;
+    // (work-list mode: n_splits is the number of items, which bounds the slots in use)
+    p.part_ml = scratch == nullptr ? nullptr
+        : scratch + static_cast<int64_t>(items != nullptr ? 1 : n_tokens) * n_heads * n_splits * head_dim;
+    p.items = items;
+    p.n_items = 0;
+    p.n_kv_heads = n_kv_heads;
+    p.token_slot = token_slot;
+    p.counters = counters;
     p.n_heads = n_heads;
     p.group = group;
     p.window = window;
@@ -651,6 +803,59 @@ PL_API int pl_attention_decode(const void* q, int64_t q_row_stride, const void* 
     return run_attention_decode(true, q, q_row_stride, k_pool, v_pool, page_stride, head_stride, page_size, n_pages,
                                 table, table_width, pos, entry, out, out_row_stride, n_tokens, n_heads, n_kv_heads,
                                 head_dim, window, scale, n_splits, scratch, status, stream);
+}
+
+// pl_attention_decode over a work list instead of equal shares: for batches whose requests
+// differ in length, or are many. items: int32 [n_items, 4] rows {token, first 16-key tile,
+// tiles, split | splits << 12}; rows of no tiles are padding and come last, and the last row,
+// if it is padding, holds in its first field the number of rows that are not. The pairs
+// (item, kv head) go to CTAs in list order: the first by position, the rest off a queue. A token of one split writes its output itself. The splits of a token
+// with more write partial results to slot token_slot[token] + split of scratch (fp32,
+// n_items * n_heads * (head_dim + 2) floats; slots below n_items), and the CTA that
+// finishes a (token, kv head) last merges them in split order. counters: int32 [2 + n_tokens *
+// n_kv_heads], all zero before the call and again after it (the work queue's head, its
+// leavers, and arrivals per token and kv head). The caller makes the items
+// cover each token's tiles [first attended key / 16, ceil((pos + 1) / 16)) exactly once.
+PL_API int pl_attention_decode_items(const void* q, int64_t q_row_stride, const void* k_pool, const void* v_pool,
+                                     int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
+                                     const int32_t* table, int table_width, const int32_t* pos,
+                                     const int32_t* entry, void* out, int64_t out_row_stride, int n_tokens,
+                                     int n_heads, int n_kv_heads, int head_dim, int window, float scale,
+                                     const int32_t* items, int n_items, const int32_t* token_slot, float* scratch,
+                                     int32_t* counters, int32_t* status, cudaStream_t stream) {
+    PL_REQUIRE(items != nullptr && token_slot != nullptr && counters != nullptr && scratch != nullptr && n_items >= 1,
+               "attention_decode_items: needs items, token_slot, counters and scratch");
+    PL_REQUIRE((reinterpret_cast<uintptr_t>(items) & 15) == 0, "attention_decode_items: items must be 16-byte aligned");
+    return run_attention_decode(false, q, q_row_stride, k_pool, v_pool, page_stride, head_stride, page_size, n_pages,
+                                table, table_width, pos, entry, out, out_row_stride, n_tokens, n_heads, n_kv_heads,
+                                head_dim, window, scale, n_items, scratch, status, stream, nullptr, 0, items, token_slot,
+                                counters);
+}
+
+// How many CTAs of the decode kernel one SM holds at once.
+PL_API int pl_attention_decode_ctas_per_sm(int head_dim) {
+    int ctas = 0;
+    cudaError_t err;
+    if (head_dim == 64) {
+        constexpr int rings = kWarps * stages_of(64) * 2 * kTile * 64 * 2;
+        cudaFuncSetAttribute(attention_decode_kernel<64, kWarps, stages_of(64)>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             rings + merge_bytes(16 * 16, kClusterSplitsMax) + 1024);
+        err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, attention_decode_kernel<64, kWarps, stages_of(64)>,
+                                                            kWarps * 32, rings);
+    } else if (head_dim == 128) {
+        constexpr int rings = kWarps * stages_of(128) * 2 * kTile * 128 * 2;
+        cudaFuncSetAttribute(attention_decode_kernel<128, kWarps, stages_of(128)>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             rings + merge_bytes(16 * 32, kClusterSplitsMax) + 1024);
+        err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, attention_decode_kernel<128, kWarps, stages_of(128)>,
+                                                            kWarps * 32, rings);
+    } else {
+        return 0;
+    }
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return ctas;
 }
 
 namespace {

@@ -4,6 +4,7 @@
     python -m pulsarlm_b200.kernels.microbench attention_prefill [--tokens 2048 ...]
     python -m pulsarlm_b200.kernels.microbench attention_decode [--batch 8 --context 2048 ...]
     python -m pulsarlm_b200.kernels.microbench decode_timeline [--layers 8 --batch 8 --context 2048]
+        [--shape 1b --batch 64 --context 128 4608]   (contexts spread evenly between the two)
 
 Each timing replays a CUDA graph of several launches (so host time does not
 count) over inputs rotated through enough copies to exceed L2, after warm-up,
@@ -110,7 +111,9 @@ def bench_attention_prefill(tokens_list, n_heads, n_kv, head_dim, page, prior=0,
                   f"{flops / us / 1e6:.0f} TFLOP/s (causal flops)", flush=True)
 
 
-def bench_attention_decode(batches, contexts, n_heads, n_kv, head_dim, page, force_splits=0) -> None:
+def bench_attention_decode(batches, contexts, n_heads, n_kv, head_dim, page, force_splits=0, shortest=0,
+                           items_per_slot=0) -> None:
+    from ..parts import attention as attention_part
     from ..parts.attention import decode_splits
 
     for batch in batches:
@@ -124,7 +127,10 @@ def bench_attention_decode(batches, contexts, n_heads, n_kv, head_dim, page, for
             table = torch.randperm(n_pages, device="cuda").to(torch.int32).view(batch, pages_each)
             q = torch.randn(batch, n_heads, head_dim, device="cuda").to(torch.bfloat16)
             out = torch.empty_like(q)
-            pos = torch.full((batch,), context - 1, dtype=torch.int32, device="cuda")
+            # everyone at `context` keys, or lengths spread evenly from `shortest` up to it
+            lengths = [context if not shortest else shortest + (context - shortest) * b // max(1, batch - 1)
+                       for b in range(batch)]
+            pos = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device="cuda")
             entry = torch.arange(batch, dtype=torch.int32, device="cuda")
             splits = force_splits or decode_splits(batch * n_kv, context, q.device, head_dim, n_heads // n_kv)
             scratch = torch.empty(max(1, ops.attention_decode_scratch_floats(batch, n_heads, head_dim, splits)),
@@ -132,15 +138,27 @@ def bench_attention_decode(batches, contexts, n_heads, n_kv, head_dim, page, for
             scale = 1 / math.sqrt(head_dim)
             turn = [0]
 
+            if items_per_slot:  # the work list the engine makes for many or unequal requests
+                ctas = attention_part.decode_item_ctas(q.device, head_dim, n_kv)
+                host_items, host_slots = attention_part.decode_work_items(lengths, None, items_per_slot * ctas)
+                items, slots = torch.from_numpy(host_items).cuda(), torch.from_numpy(host_slots).cuda()
+                scratch = torch.empty(items.shape[0] * n_heads * (head_dim + 2), device="cuda")
+                splits = f"work list of {int((host_items[:, 2] > 0).sum())} items"
+
             def run():
                 pool = pools[turn[0] % copies]
                 turn[0] += 1
-                ops.attention_decode(q, pool[:, 0], pool[:, 1], table, pos, entry, out, page, None, scale, splits,
-                                     scratch)
+                if items_per_slot:
+                    ops.attention_decode_items(q, pool[:, 0], pool[:, 1], table, pos, entry, out, page, None, scale,
+                                               items, slots, scratch)
+                else:
+                    ops.attention_decode(q, pool[:, 0], pool[:, 1], table, pos, entry, out, page, None, scale,
+                                         splits, scratch)
 
             us = graph_time_us(run, reps=max(10, copies))
-            gb = batch * context * 2 * n_kv * head_dim * 2 / 1e9
-            print(f"attention_decode batch={batch} context={context} heads={n_heads}/{n_kv} head_dim={head_dim} "
+            gb = sum(lengths) * 2 * n_kv * head_dim * 2 / 1e9
+            span = f"{shortest}..{context}" if shortest else f"{context}"
+            print(f"attention_decode batch={batch} context={span} heads={n_heads}/{n_kv} head_dim={head_dim} "
                   f"splits={splits}: {us:.1f} us, {gb / us * 1e6:.0f} GB/s", flush=True)
 
 
@@ -151,7 +169,20 @@ LLAMA31_8B_SHAPE = {
 }
 
 
-def decode_timeline(layers: int, batch: int, context: int, page: int) -> None:
+LLAMA32_1B_SHAPE = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": 2048, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192, "vocab_size": 128256,
+    "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 131072,
+}
+LLAMA2_13B_SHAPE = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": 5120, "num_attention_heads": 40,
+    "num_key_value_heads": 40, "head_dim": 128, "intermediate_size": 13824, "vocab_size": 32000,
+    "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 4096,
+}
+MODEL_SHAPES = {"8b": LLAMA31_8B_SHAPE, "1b": LLAMA32_1B_SHAPE, "13b": LLAMA2_13B_SHAPE}
+
+
+def decode_timeline(layers: int, batch: int, contexts: list[int], page: int, shape: str = "8b") -> None:
     import collections
     import re
 
@@ -161,8 +192,12 @@ def decode_timeline(layers: int, batch: int, context: int, page: int) -> None:
     from ..engine.runner import StepEntry
     from ..sampling.params import SamplingParams
 
-    config = dict(LLAMA31_8B_SHAPE, num_hidden_layers=layers)
-    n_pages = batch * (context + 256) // page + 64
+    config = dict(MODEL_SHAPES[shape], num_hidden_layers=layers)
+    # one context for everyone, or contexts spread evenly from the first to the second
+    lo, hi = contexts[0], contexts[-1]
+    lengths = [lo + (hi - lo) * b // max(1, batch - 1) for b in range(batch)]
+    context = f"{lo}" if lo == hi else f"{lo}..{hi}"
+    n_pages = sum(-(-(n + 256) // page) for n in lengths) + 64
     engine = Engine(config, dtype="bfloat16", device="cuda:0", n_pages=n_pages, page_size=page,
                     prefill_tokens_per_step=2048, max_requests=batch + 2, seed=0)
     for group in engine.cache.groups:
@@ -170,8 +205,8 @@ def decode_timeline(layers: int, batch: int, context: int, page: int) -> None:
     ids = []
     for b in range(batch):  # requests that hold `context` tokens, without running a prefill
         engine.cache.open(("timeline", b))
-        engine.cache.reserve(("timeline", b), context)
-        engine.cache.commit(("timeline", b), context)
+        engine.cache.reserve(("timeline", b), lengths[b])
+        engine.cache.commit(("timeline", b), lengths[b])
         ids.append(("timeline", b))
     params = [SamplingParams()] * batch
     entries = [StepEntry(r, [(7 * i + 3) % 1000], [0]) for i, r in enumerate(ids)]
@@ -198,7 +233,7 @@ def decode_timeline(layers: int, batch: int, context: int, page: int) -> None:
         return (base.group(0) if base else name[:40]) + ("<" + args.group(1) + ">" if args else "")
 
     t0 = last[0][1]
-    print(f"decode step: batch {batch}, context {context}, {layers} layers: {per_step} device activities, "
+    print(f"decode step ({shape} shape): batch {batch}, context {context}, {layers} layers: {per_step} device activities, "
           f"{last[-1][2] - t0:.1f} us from first start to last end")
     totals = collections.OrderedDict()
     for name, start, end in last:
@@ -226,26 +261,37 @@ def main() -> None:
     parser.add_argument("--splits", type=int, default=0, help="attention_prefill, attention_decode: split the keys this many ways "
                         "(default: as the engine would)")
     parser.add_argument("--batch", type=int, nargs="*", default=[1, 8, 64])
-    parser.add_argument("--context", type=int, nargs="*", default=[2048, 4096])
+    parser.add_argument("--context", type=int, nargs="*", default=None)
+    parser.add_argument("--shortest", type=int, default=0, help="attention_decode: the requests' lengths are spread "
+                        "evenly from here up to --context (default: all at --context)")
+    parser.add_argument("--items_per_slot", type=int, default=0, help="attention_decode: run the work-list form, "
+                        "the keys cut into about this many items per resident CTA (the engine uses 4)")
     parser.add_argument("--heads", type=int, default=32)
     parser.add_argument("--kv_heads", type=int, default=8)
     parser.add_argument("--head_dim", type=int, default=128)
     parser.add_argument("--page_size", type=int, default=16)
     parser.add_argument("--layers", type=int, default=8, help="layers of the decode_timeline model")
+    parser.add_argument("--shape", default="8b", choices=sorted(MODEL_SHAPES),
+                        help="decode_timeline: layer sizes of Llama-3.1-8B, Llama-3.2-1B or Llama-2-13B")
     args = parser.parse_args()
     ops.require_device()
+    if args.items_per_slot and args.what == "decode_timeline":
+        from ..parts import attention as attention_part
+
+        attention_part.DECODE_ITEMS_PER_SLOT = args.items_per_slot
     if args.what == "gemm":
         shapes = LLAMA8B_SHAPES if not args.shapes else [tuple(int(v) for v in s.split(",")) for s in args.shapes]
         bench_gemm(shapes)
     elif args.what == "decode_timeline":
         decode_timeline(args.layers, args.batch[0] if len(args.batch) == 1 else 8,
-                        args.context[0] if len(args.context) == 1 else 2048, args.page_size)
+                        args.context if args.context and len(args.context) <= 2 else [2048], args.page_size,
+                        args.shape)
     elif args.what == "attention_prefill":
         bench_attention_prefill(args.tokens, args.heads, args.kv_heads, args.head_dim, args.page_size, args.prior,
-                                args.splits)
+                                args.splits, args.shortest, args.items_per_slot)
     else:
-        bench_attention_decode(args.batch, args.context, args.heads, args.kv_heads, args.head_dim, args.page_size,
-                               args.splits)
+        bench_attention_decode(args.batch, args.context or [2048, 4096], args.heads, args.kv_heads, args.head_dim, args.page_size,
+                               args.splits, args.shortest, args.items_per_slot)
 
 
 if __name__ == "__main__":

@@ -25,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 14
+ABI_VERSION = 15
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -49,6 +49,9 @@ _SIGNATURES = {
     "pl_attention_decode_mass": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
                                  _I32, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR, _I32, _PTR, _PTR, _F32, _PTR,
                                  _PTR],
+    "pl_attention_decode_items": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
+                                  _I32, _I32, _I32, _I32, _I32, _F32, _PTR, _I32, _PTR, _PTR, _PTR, _PTR, _PTR],
+    "pl_attention_decode_ctas_per_sm": [_I32],
     "pl_attention_decode_supports": [_I32, _I32, _I32, _I32],
     "pl_attention_prefill": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _I32, _PTR, _I64,
                              _I32, _I32, _I32, _I32, _F32, _PTR, _PTR],
@@ -344,6 +347,58 @@ def attention_decode_supports(head_dim: int, group: int, page_size: int, dtype: 
 
 def attention_decode_scratch_floats(n_tokens: int, n_heads: int, head_dim: int, n_splits: int) -> int:
     return int(library().pl_attention_decode_scratch_floats(n_tokens, n_heads, head_dim, n_splits))
+
+
+_DECODE_COUNTERS: dict[torch.device, torch.Tensor] = {}
+DECODE_COUNTERS = 1 << 20
+
+
+def attention_decode_counters(device: torch.device) -> torch.Tensor:
+    """The zeroed counters attention_decode_items works with (int32, DECODE_COUNTERS of
+    them, one set per device: launches on one stream share it, each leaves it zero)."""
+    device = torch.device(device)
+    if device not in _DECODE_COUNTERS:
+        _DECODE_COUNTERS[device] = torch.zeros(DECODE_COUNTERS, dtype=torch.int32, device=device)
+    return _DECODE_COUNTERS[device]
+
+
+def attention_decode_items(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,
+                           pos: torch.Tensor, entry: torch.Tensor, out: torch.Tensor, page_size: int,
+                           window: int | None, scale: float, items: torch.Tensor, token_slot: torch.Tensor,
+                           scratch: torch.Tensor, status: torch.Tensor | None = None) -> None:
+    """bf16 attention of single decode tokens over a work list (shapes as
+    attention_decode). items: int32 [n, 4] rows {token, first 16-key tile, tiles, split |
+    splits << 12}, rows of no tiles are padding; the rows of a token cover its tiles once.
+    token_slot int32 [tokens]: first slot of a token's partial results in `scratch`
+    (fp32, n * n_heads * (head_dim + 2) floats). The CTA that finishes a token's kv head
+    last merges its splits in split order."""
+    _dev(q, k_pool, v_pool, table, pos, entry, out, items, token_slot, scratch, status)
+    tokens, n_heads, head_dim = q.shape
+    n_pages, n_kv = k_pool.shape[0], k_pool.shape[1]
+    assert q.dtype == torch.bfloat16 == k_pool.dtype == out.dtype
+    assert k_pool.shape == v_pool.shape and k_pool.stride() == v_pool.stride()
+    assert k_pool.stride(3) == 1 and k_pool.stride(2) == head_dim
+    assert q.stride(2) == 1 and q.stride(1) == head_dim and out.stride(2) == 1 and out.stride(1) == head_dim
+    assert table.dtype == torch.int32 and table.is_contiguous() and pos.dtype == torch.int32 == entry.dtype
+    assert pos.numel() == tokens == entry.numel() == token_slot.numel()
+    assert items.dtype == torch.int32 == token_slot.dtype and items.dim() == 2 and items.shape[1] == 4
+    assert items.is_contiguous() and token_slot.is_contiguous()
+    n_items = items.shape[0]
+    assert scratch.dtype == torch.float32 and scratch.is_contiguous()
+    assert scratch.numel() >= n_items * n_heads * (head_dim + 2)
+    if 2 + tokens * n_kv > DECODE_COUNTERS:
+        raise KernelError(f"attention_decode_items: {tokens} tokens x {n_kv} kv heads need more than "
+                          f"{DECODE_COUNTERS} counters")
+    counters = attention_decode_counters(q.device)
+    _call("pl_attention_decode_items", _p(q), q.stride(0), _p(k_pool), _p(v_pool), k_pool.stride(0),
+          k_pool.stride(1), page_size, n_pages, _p(table), table.shape[1], _p(pos), _p(entry), _p(out),
+          out.stride(0), tokens, n_heads, n_kv, head_dim, int(window or 0), float(scale), _p(items), n_items,
+          _p(token_slot), _p(scratch), _p(counters), _p(status), _stream())
+
+
+def attention_decode_ctas_per_sm(head_dim: int) -> int:
+    """How many CTAs of the decode attention kernel an SM holds at once."""
+    return int(library().pl_attention_decode_ctas_per_sm(head_dim))
 
 
 def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,

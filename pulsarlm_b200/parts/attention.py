@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import dataclasses
 import math
+import os
 
 import numpy as np
 import torch
@@ -98,6 +99,69 @@ def _decode_splits(n_ctas: int, max_context: int, device: torch.device, head_dim
         if cost < best_cost:
             best, best_cost = splits, cost
     return best
+
+
+_CTAS_PER_SM: dict[tuple, int] = {}
+DECODE_ITEM_MIN_TILES = 32     # no work item much shorter than 32 16-key tiles (a warp's ring must fill)
+DECODE_ITEMS_PER_SLOT = 1      # unequal requests are cut into about this many items per resident CTA
+DECODE_ITEMS = os.environ.get("PULSARLM_B200_DECODE_ITEMS", "1") != "0"  # (0: equal shares only, for comparison)
+DECODE_EVEN_ENOUGH = 1.3       # longest / mean length up to which nothing is cut
+
+
+def decode_item_ctas(device: torch.device, head_dim: int, n_kv: int) -> int:
+    """How many CTAs per kv head walk a work list: what the device holds at once of the
+    decode kernel, over the kv heads (the kernel launches the same number)."""
+    key = (device, head_dim)
+    if key not in _CTAS_PER_SM:
+        _CTAS_PER_SM[key] = max(1, ops.attention_decode_ctas_per_sm(head_dim))
+    if device not in _SM_COUNT:
+        _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return max(1, -(-_CTAS_PER_SM[key] * _SM_COUNT[device] // n_kv))
+
+
+def decode_work_items(context_lens: list[int], window: int | None, target: int,
+                      pad_to: int | None = None, stride: int | None = None,
+                      min_tiles: int = DECODE_ITEM_MIN_TILES) -> tuple[np.ndarray, np.ndarray]:
+    """The work list of a step's single tokens for ops.attention_decode_items: int32
+    [items, 4] rows {token, first 16-key tile, tiles, split | splits << 12}, longest first,
+    and int32 [tokens] first scratch slot of each token's splits. Requests of about equal
+    length (longest within DECODE_EVEN_ENOUGH of the mean) are not cut: one item each.
+    Else the tiles are cut into about `target` items of equal size, a request's share
+    rounded to whole items, so that the CTAs in flight stay many until the end instead of
+    the longest requests streaming alone. At most target + tokens items; `pad_to` pads the
+    list with empty rows to a fixed length (the last row then holds the count of real rows). With `stride` (the number of CTAs that walk the
+    list, CTA x taking rows x, x + stride, ...) every second full round of rows is turned
+    around, so that the CTA with the longest item of one round gets the shortest of the next."""
+    n = len(context_lens)
+    firsts = [(max(0, c - window) if window else 0) // 16 for c in context_lens]
+    tiles = [max(0, -(-c // 16) - f) for c, f in zip(context_lens, firsts)]
+    total = sum(tiles)
+    chunk = max(min_tiles, -(-total // max(1, target)))
+    even = max(tiles, default=0) * n <= DECODE_EVEN_ENOUGH * total
+    rows = []
+    slots = np.zeros(n, dtype=np.int32)
+    slot = 0
+    for t in range(n):
+        k = 1 if even else min(4095, max(1, int(tiles[t] / chunk + 0.5)))
+        slots[t] = slot
+        if k > 1:
+            slot += k
+        at = firsts[t]
+        for s in range(k):  # shares that differ by one tile at most
+            share = tiles[t] // k + (1 if s < tiles[t] % k else 0)
+            rows.append((t, at, share, s | (k << 12)))
+            at += share
+    rows.sort(key=lambda r: -r[2])
+    if stride:
+        for at in range(stride, len(rows) - stride + 1, 2 * stride):
+            rows[at : at + stride] = rows[at : at + stride][::-1]
+    length = max(len(rows), pad_to or 0, 1)
+    items = np.zeros((length, 4), dtype=np.int32)
+    if rows:
+        items[: len(rows)] = np.array(rows, dtype=np.int32)
+    if length > len(rows):
+        items[-1, 0] = len(rows)  # the last padding row tells how many rows are real
+    return items, slots
 
 
 def prefill_splits(n_ctas: int, max_keys: int, n_tokens: int, n_heads: int, head_dim: int,
@@ -252,7 +316,7 @@ class Attention(Part):
             return None
         wide = (self.n_heads // self.n_kv) % 2 == 1
         return ("attention", self.cache.page_size, self.head_dim, self.n_heads // self.n_kv, wide,
-                self.ctx.dtype, bool(self.softcap))
+                self.ctx.dtype, bool(self.softcap), self.n_kv, self.window)
 
     def plan_step(self, step) -> dict:
         """The tile list of the prompt-portion kernels: int32 [tiles, 4] rows of {first
@@ -268,6 +332,19 @@ class Attention(Part):
         n_decode = step.n_decode if decode_kernel else 0
         if n_decode:
             plan["max_context"] = step.context_bound if step.fixed_shape else max(step.context_lens[:n_decode])
+            # Many single tokens (so many that their keys would not be split at all): a work
+            # list cut by the requests' true lengths instead of one CTA per request and kv
+            # head, unless attention mass is measured (that path keeps equal shares).
+            measuring = self.cache.mass_sum is not None and self.cache_from is None
+            device = self.ctx.device
+            reach = min(plan["max_context"], self.window + 16) if self.window else plan["max_context"]
+            if DECODE_ITEMS and not measuring and 2 + n_decode * self.n_kv <= ops.DECODE_COUNTERS and decode_splits(
+                    n_decode * self.n_kv, reach, device, self.head_dim, self.n_heads // self.n_kv) == 1:
+                ctas = decode_item_ctas(device, self.head_dim, self.n_kv)
+                target = DECODE_ITEMS_PER_SLOT * ctas
+                items, slots = decode_work_items(step.context_lens[:n_decode], self.window, target,
+                                                 target + n_decode if step.fixed_shape else None)
+                plan["decode_items"], plan["decode_slots"] = items, slots
         if not prefill_kernel or step.n_decode == step.n_entries:
             return plan
         rows = ops.attention_prefill_tile_rows()
@@ -329,7 +406,14 @@ class Attention(Part):
         plan = batch.plans.get(self.plan_key()) or {}
         decode_kernel, prefill_kernel = self._kernels(q.dtype)
         n_decode = min(int(batch.n_decode), tokens) if decode_kernel else 0
-        if n_decode > 0:
+        if n_decode > 0 and plan.get("decode_items") is not None:
+            items = plan["decode_items"]
+            scratch = torch.empty(items.shape[0] * self.n_heads * (self.head_dim + 2), dtype=torch.float32,
+                                  device=q.device)
+            ops.attention_decode_items(q[:n_decode], cache.k_pool, cache.v_pool, table, batch.pos[:n_decode],
+                                       batch.entry[:n_decode], out[:n_decode], cache.page_size, self.window,
+                                       self.scale, items, plan["decode_slots"], scratch, batch.status)
+        elif n_decode > 0:
             max_context = plan.get("max_context") or max(batch.host_context_lens[:n_decode])
             if self.window:
                 max_context = min(max_context, self.window + 16)

@@ -367,6 +367,50 @@ def test_attention_decode(ops, nh, nkv, hd, page, splits, window):
     assert int(status) == 0 and rel(out, want) < 1e-2
 
 
+@pytest.mark.parametrize("nh,nkv,hd,page", [(8, 2, 64, 16), (8, 1, 128, 16), (32, 8, 128, 16), (16, 1, 64, 32),
+                                            (6, 2, 128, 64), (4, 4, 64, 16)])
+@pytest.mark.parametrize("target", [1, 7, 40, 500])
+@pytest.mark.parametrize("window", [None, 100])
+def test_attention_decode_over_a_work_list(ops, nh, nkv, hd, page, target, window):
+    """Requests of very different lengths, their keys cut into work items by the
+    part's own planner (from no cut at all to items of eight tiles), the list padded with
+    empty rows, twice in a row (the second call finds the counters as the first left them)."""
+    from pulsarlm_b200.parts.attention import decode_work_items
+
+    dtype = torch.bfloat16
+    lengths = [1, 15, 16, 17, 250, 700, 129, 2100]
+    pages_each = -(-max(lengths) // page)
+    n_pages = len(lengths) * pages_each + 3
+    table = scattered_tables(len(lengths), pages_each, n_pages, seed=hd + page)
+    kp, vp = make_pools(n_pages, nkv, page, hd, dtype, fill=1.0)
+    pos = [n - 1 for n in lengths]
+    entry = list(range(len(lengths)))
+    pos_t = torch.tensor(pos, dtype=torch.int32, device=DEV)
+    entry_t = torch.tensor(entry, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    items, slots = decode_work_items(lengths, window, target, pad_to=target + len(lengths) + 3,
+                                     stride=5 if target == 40 else None, min_tiles=2 if target == 500 else 32)
+    real = items[items[:, 2] > 0]
+    assert len(lengths) <= len(real) <= target + len(lengths)
+    assert window is not None or (target == 1) == (len(real) == len(lengths))
+    for t, n in enumerate(lengths):  # every attended tile of every request exactly once
+        first = (max(0, n - window) if window else 0) // 16
+        mine = sorted((r[1], r[2]) for r in real if r[0] == t)
+        assert mine[0][0] == first and mine[-1][0] + mine[-1][1] == -(-n // 16)
+        assert all(a[0] + a[1] == b[0] for a, b in zip(mine, mine[1:]))
+    items_t, slots_t = torch.from_numpy(items).to(DEV), torch.from_numpy(slots).to(DEV)
+    for _ in range(2):
+        q = torch.randn(len(pos), nh, hd, device=DEV).to(dtype)
+        out = torch.full_like(q, float("nan"))
+        scratch = torch.full((items.shape[0] * nh * (hd + 2),), float("nan"), device=DEV)
+        ops.attention_decode_items(q, kp, vp, table.to(DEV), pos_t, entry_t, out, page, window, scale, items_t,
+                                   slots_t, scratch, status)
+        want = reference_attention(q, kp, vp, table, pos, entry, page, window, scale)
+        assert int(status) == 0 and rel(out, want) < 1e-2
+    assert int(ops.attention_decode_counters(q.device).abs().sum()) == 0
+
+
 def test_attention_decode_refuses_what_it_cannot_do(ops):
     assert not ops.attention_decode_supports(80, 1, 16, torch.bfloat16)
     assert not ops.attention_decode_supports(128, 32, 16, torch.bfloat16)
@@ -381,7 +425,7 @@ def test_attention_decode_refuses_what_it_cannot_do(ops):
     assert "head_dim=80" in str(error.value)
 
 
-@pytest.mark.parametrize("kernel", ["simt_f32", "simt_bf16", "decode"])
+@pytest.mark.parametrize("kernel", ["simt_f32", "simt_bf16", "decode", "decode_items"])
 @pytest.mark.parametrize("far_key", [0, 15, 16, 511, 512, 1203])
 def test_one_far_key_among_many_is_found(ops, kernel, far_key):
     """One key (at a page's first slot, last slot, far back) matches the query
@@ -405,6 +449,20 @@ def test_one_far_key_among_many_is_found(ops, kernel, far_key):
     if kernel == "decode":
         scratch = torch.empty(ops.attention_decode_scratch_floats(1, nh, hd, 7), device=DEV)
         ops.attention_decode(q, kp, vp, table.to(DEV), pos_t, entry_t, out, page, None, 1.0, 7, scratch)
+    elif kernel == "decode_items":
+        from pulsarlm_b200.parts.attention import decode_work_items
+
+        # a second, short request makes the lengths unequal, so that the long one is cut
+        items, slots = decode_work_items([n, 20], None, 9, min_tiles=8)
+        assert len(items) > 5
+        q2 = torch.cat([q, q])
+        out2 = torch.empty_like(q2)
+        pos2 = torch.tensor([n - 1, 19], dtype=torch.int32, device=DEV)
+        scratch = torch.empty(items.shape[0] * nh * (hd + 2), device=DEV)
+        ops.attention_decode_items(q2, kp, vp, table.to(DEV), pos2, torch.zeros(2, dtype=torch.int32, device=DEV),
+                                   out2, page, None, 1.0, torch.from_numpy(items).to(DEV),
+                                   torch.from_numpy(slots).to(DEV), scratch)
+        out = out2[:1]
     else:
         ops.attention_simt(q, kp, vp, table.to(DEV), pos_t, entry_t, out, page, None, 1.0)
     want = reference_attention(q, kp, vp, table, [n - 1], [0], page, None, 1.0)

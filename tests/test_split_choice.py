@@ -53,3 +53,49 @@ def test_prefill_splits_only_for_few_tiles_over_many_keys(part):
             splits = pick(ctas, keys, 128)
             assert 1 <= splits <= 16
             assert splits == 1 or keys // splits >= 256
+
+
+def test_work_items_cover_every_tile_once_and_leave_even_batches_whole():
+    import random
+
+    from pulsarlm_b200.parts.attention import decode_work_items
+
+    rng = random.Random(4)
+    for trial in range(200):
+        n = rng.choice([1, 2, 7, 64, 130])
+        lengths = [rng.choice([1, 16, 17, rng.randrange(1, 9000)]) for _ in range(n)]
+        window = rng.choice([None, None, 40, 1000])
+        target = rng.choice([1, 5, 74, 300, 1200])
+        pad = rng.choice([None, target + n])
+        stride = rng.choice([None, None, 3, 37])
+        items, slots = decode_work_items(lengths, window, target, pad, stride, min_tiles=8)
+        assert items.dtype.name == "int32" and items.shape[1] == 4 and slots.shape == (n,)
+        assert pad is None or items.shape[0] == pad
+        real = [tuple(int(v) for v in r) for r in items if r[2] > 0]
+        assert len(real) <= target + n
+        if stride is None:
+            assert [r[2] for r in real] == sorted((r[2] for r in real), reverse=True)   # longest first
+        else:  # in rounds of `stride`, every second full round from its shortest to its longest
+            again = list(real)
+            for at in range(stride, len(again) - stride + 1, 2 * stride):
+                again[at : at + stride] = again[at : at + stride][::-1]
+            assert [r[2] for r in again] == sorted((r[2] for r in real), reverse=True)
+        used_slots = set()
+        for t, c in enumerate(lengths):
+            first = (max(0, c - window) if window else 0) // 16
+            mine = sorted(r for r in real if r[0] == t)
+            assert mine[0][1] == first and mine[-1][1] + mine[-1][2] == -(-c // 16)
+            assert all(a[1] + a[2] == b[1] for a, b in zip(mine, mine[1:]))
+            splits = {r[3] >> 12 for r in mine}
+            assert splits == {len(mine)} and sorted(r[3] & 4095 for r in mine) == list(range(len(mine)))
+            if len(mine) > 1:
+                assert all(r[2] >= 4 for r in mine)       # no sliver: at least half the smallest item
+                for s in range(len(mine)):
+                    assert slots[t] + s not in used_slots and slots[t] + s < items.shape[0]
+                    used_slots.add(int(slots[t]) + s)
+    # requests of about one length are left whole, whatever the target
+    items, _ = decode_work_items([2000, 2100, 1900, 2050], None, 1000)
+    assert int((items[:, 2] > 0).sum()) == 4
+    # one long request among short ones is cut into about `target` items
+    items, _ = decode_work_items([100000] + [500] * 31, None, 148)
+    assert 100 <= int((items[:, 2] > 0).sum()) <= 148 + 32
