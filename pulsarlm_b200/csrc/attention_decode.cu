@@ -22,8 +22,19 @@
 // combine kernels, pulsarlm-core/src/kernels/paged_attention.cu:432-584.
 #include "cluster_helpers.cuh"
 #include "mma_helpers.cuh"
+#include "rope_helpers.cuh"
 
 PL_API int pl_attention_decode_resident_clusters(int head_dim, int group, int n_splits);
+
+// Position encoding and the new keys' write folded into a decode attention call (see
+// DecodeParams): k_new and v_new [T, n_kv_heads, head_dim] bf16 with q's row stride,
+// inv_freq fp64 [rotary / 2]; only rotary == head_dim is taken.
+struct PlDecodeRope {
+    const void* k_new;
+    const void* v_new;
+    const double* inv_freq;
+    int rotary;
+};
 
 namespace {
 
@@ -62,6 +73,14 @@ struct DecodeParams {
     // partial results of token t's split s sit at slot token_slot[t] + s of the scratch
     // ([slot][head]); the last CTA of a (token, kv head) to finish, by counters[token *
     // kv heads + kv head] (zero before the launch and again after it), merges them.
+    // Position encoding and the new key's write folded in (optional): q arrives unrotated and
+    // is rotated as it is loaded; the CTA and warp whose share holds the token's own tile
+    // first rotates the token's new key k_new[t] (rows of q_row_stride elements, like q) and
+    // stores it with v_new[t] at the token's place in the pools. rope_freq: fp64
+    // [HD / 2] radians per position (the whole head is rotated).
+    const __nv_bfloat16* k_new;
+    const __nv_bfloat16* v_new;
+    const double* rope_freq;
     const int32_t* items;
     int n_items;
     int n_kv_heads;
@@ -118,6 +137,10 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
     const int t0 = p.items != nullptr ? item_first : tile_first + split * per_split;
     const int t1 = min(t0 + per_split, tile_end);
     const int32_t* row = p.table + static_cast<int64_t>(p.entry[t]) * p.table_width;
+    __shared__ float rope_cs[HD / 2], rope_sn[HD / 2];
+    if (p.rope_freq != nullptr && threadIdx.x < HD / 2) {  // (the position is a step input: before the wait)
+        rope_sincos(ctx - 1, p.rope_freq[threadIdx.x], rope_cs[threadIdx.x], rope_sn[threadIdx.x]);
+    }
 
     unsigned char* ring = smem + warp * (STAGES * kStageBytes);
     const int my_tiles = t1 > t0 + warp ? (t1 - t0 - warp + WARPS - 1) / WARPS : 0;
@@ -180,9 +203,9 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
     pl_grid_wait();
     // Q fragments: rows g and g + 8 of the group's heads (zero past the group).
     uint32_t qa[HD / 16][4];
-    {
-        const __nv_bfloat16* qbase = p.q + t * p.q_row_stride + static_cast<int64_t>(kv_head) * p.group * HD;
-        const bool lo_ok = g < p.group, hi_ok = g + 8 < p.group;
+    const __nv_bfloat16* qbase = p.q + t * p.q_row_stride + static_cast<int64_t>(kv_head) * p.group * HD;
+    const bool lo_ok = g < p.group, hi_ok = g + 8 < p.group;
+    if (p.rope_freq == nullptr) {
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
             const int d = 16 * kk + 2 * tig;
@@ -190,6 +213,56 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
             qa[kk][1] = hi_ok ? *reinterpret_cast<const uint32_t*>(qbase + (g + 8) * HD + d) : 0u;
             qa[kk][2] = lo_ok ? *reinterpret_cast<const uint32_t*>(qbase + g * HD + d + 8) : 0u;
             qa[kk][3] = hi_ok ? *reinterpret_cast<const uint32_t*>(qbase + (g + 8) * HD + d + 8) : 0u;
+        }
+    } else {
+        __syncthreads();  // the angles are in place
+        // Rotated as loaded: dims (d, d + HD/2) are a pair, and both lie in this thread's fragments
+        // kk and kk + HD/32. Rounded to bfloat16 once, like the rotation kernel's store.
+#pragma unroll
+        for (int kk = 0; kk < HD / 32; ++kk) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int d = 16 * kk + 2 * tig + (e >> 1) * 8;
+                const bool ok = (e & 1) ? hi_ok : lo_ok;
+                const __nv_bfloat16* x = qbase + (g + (e & 1) * 8) * HD + d;
+                float2 lo = make_float2(0.0f, 0.0f), hi = make_float2(0.0f, 0.0f);
+                if (ok) {
+                    lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x));
+                    hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + HD / 2));
+                }
+                const float c0 = rope_cs[d], s0 = rope_sn[d], c1 = rope_cs[d + 1], s1 = rope_sn[d + 1];
+                qa[kk][e] = pack_bf16(rope_lo(lo.x, hi.x, c0, s0), rope_lo(lo.y, hi.y, c1, s1));
+                qa[kk + HD / 32][e] = pack_bf16(rope_hi(lo.x, hi.x, c0, s0), rope_hi(lo.y, hi.y, c1, s1));
+            }
+        }
+        // The token's own key and value: rotated and stored by the warp whose tiles end with
+        // the token's tile, before that warp asks for the tile.
+        const int own_tile = tile_end - 1;
+        if (p.k_new != nullptr && own_tile >= t0 && own_tile < t1 && (own_tile - t0) % WARPS == warp) {
+            const int position = ctx - 1;
+            const int page = row[position / p.page_size];
+            if (page < 0 || page >= p.n_pages) {
+                if (lane == 0 && p.status != nullptr) {
+                    atomicOr(p.status, 2);
+                }
+            } else {
+                const int64_t from = t * p.q_row_stride + static_cast<int64_t>(kv_head) * HD;
+                const int64_t at = page * p.page_stride + kv_head * p.head_stride +
+                    static_cast<int64_t>(position % p.page_size) * HD;
+                __nv_bfloat16* k_out = const_cast<__nv_bfloat16*>(p.k_pool) + at;
+                __nv_bfloat16* v_out = const_cast<__nv_bfloat16*>(p.v_pool) + at;
+#pragma unroll
+                for (int j = lane; j < HD / 2; j += 32) {
+                    const float lo = __bfloat162float(p.k_new[from + j]);
+                    const float hi = __bfloat162float(p.k_new[from + j + HD / 2]);
+                    k_out[j] = __float2bfloat16_rn(rope_lo(lo, hi, rope_cs[j], rope_sn[j]));
+                    k_out[j + HD / 2] = __float2bfloat16_rn(rope_hi(lo, hi, rope_cs[j], rope_sn[j]));
+                    v_out[j] = p.v_new[from + j];
+                    v_out[j + HD / 2] = p.v_new[from + j + HD / 2];
+                }
+            }
+            __threadfence();
+            __syncwarp();
         }
     }
     if (!early) {
@@ -727,7 +800,7 @@ int run_attention_decode(bool allow_cluster, const void* q, int64_t q_row_stride
                                int head_dim, int window, float scale, int n_splits, float* scratch,
                                int32_t* status, cudaStream_t stream, float* tile_max = nullptr, int max_tiles = 0,
                                const int32_t* items = nullptr, const int32_t* token_slot = nullptr,
-                               int32_t* counters = nullptr) {
+                               int32_t* counters = nullptr, const PlDecodeRope* rope = nullptr) {
     PL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
                "attention_decode: bad sizes tokens=%d heads=%d kv_heads=%d", n_tokens, n_heads, n_kv_heads);
     const int group = n_heads / n_kv_heads;
@@ -769,6 +842,17 @@ int run_attention_decode(bool allow_cluster, const void* q, int64_t q_row_stride
     p.items = items;
     p.n_items = 0;
     p.n_kv_heads = n_kv_heads;
+    p.k_new = p.v_new = nullptr;
+    p.rope_freq = nullptr;
+    if (rope != nullptr) {
+        PL_REQUIRE(rope->rotary == head_dim && rope->inv_freq != nullptr && (rope->k_new == nullptr) == (rope->v_new == nullptr),
+                   "attention_decode: the folded position encoding rotates the whole head (rotary %d, head_dim %d) and "
+                   "takes k and v together",
+                   rope->rotary, head_dim);
+        p.k_new = static_cast<const __nv_bfloat16*>(rope->k_new);
+        p.v_new = static_cast<const __nv_bfloat16*>(rope->v_new);
+        p.rope_freq = rope->inv_freq;
+    }
     p.token_slot = token_slot;
     p.counters = counters;
     p.n_heads = n_heads;
@@ -793,16 +877,18 @@ int run_attention_decode(bool allow_cluster, const void* q, int64_t q_row_stride
 // bf16 only. q and out [T, n_heads, head_dim] with row strides; one query per token
 // at position pos[t]; pools and table as in pl_attention_simt. scratch: at least
 // pl_attention_decode_scratch_floats floats when n_splits > 8 (fewer splits merge
-// inside a cluster and leave it untouched).
+// inside a cluster and leave it untouched). rope (optional): q arrives unrotated and the
+// call also rotates and stores the tokens' new keys and values (see PlDecodeRope).
 PL_API int pl_attention_decode(const void* q, int64_t q_row_stride, const void* k_pool, const void* v_pool,
                                int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
                                const int32_t* table, int table_width, const int32_t* pos, const int32_t* entry,
                                void* out, int64_t out_row_stride, int n_tokens, int n_heads, int n_kv_heads,
                                int head_dim, int window, float scale, int n_splits, float* scratch,
-                               int32_t* status, cudaStream_t stream) {
+                               const PlDecodeRope* rope, int32_t* status, cudaStream_t stream) {
     return run_attention_decode(true, q, q_row_stride, k_pool, v_pool, page_stride, head_stride, page_size, n_pages,
                                 table, table_width, pos, entry, out, out_row_stride, n_tokens, n_heads, n_kv_heads,
-                                head_dim, window, scale, n_splits, scratch, status, stream);
+                                head_dim, window, scale, n_splits, scratch, status, stream, nullptr, 0, nullptr,
+                                nullptr, nullptr, rope);
 }
 
 // pl_attention_decode over a work list instead of equal shares: for batches whose requests
@@ -822,14 +908,15 @@ PL_API int pl_attention_decode_items(const void* q, int64_t q_row_stride, const 
                                      const int32_t* entry, void* out, int64_t out_row_stride, int n_tokens,
                                      int n_heads, int n_kv_heads, int head_dim, int window, float scale,
                                      const int32_t* items, int n_items, const int32_t* token_slot, float* scratch,
-                                     int32_t* counters, int32_t* status, cudaStream_t stream) {
+                                     int32_t* counters, const PlDecodeRope* rope, int32_t* status,
+                                     cudaStream_t stream) {
     PL_REQUIRE(items != nullptr && token_slot != nullptr && counters != nullptr && scratch != nullptr && n_items >= 1,
                "attention_decode_items: needs items, token_slot, counters and scratch");
     PL_REQUIRE((reinterpret_cast<uintptr_t>(items) & 15) == 0, "attention_decode_items: items must be 16-byte aligned");
     return run_attention_decode(false, q, q_row_stride, k_pool, v_pool, page_stride, head_stride, page_size, n_pages,
                                 table, table_width, pos, entry, out, out_row_stride, n_tokens, n_heads, n_kv_heads,
                                 head_dim, window, scale, n_items, scratch, status, stream, nullptr, 0, items, token_slot,
-                                counters);
+                                counters, rope);
 }
 
 // How many CTAs of the decode kernel one SM holds at once.

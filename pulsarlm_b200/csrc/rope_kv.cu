@@ -11,17 +11,9 @@
 // rotation. The reference rotates q in
 // pulsarlm-core/src/kernels/rope.cu:33-84 and writes k, v in
 // src/kernels/paged_attention.cu:52-98.
-#include "common.cuh"
+#include "rope_helpers.cuh"
 
 namespace {
-
-__device__ __forceinline__ void rope_sincos(int pos, double radians_per_position, float& c, float& s) {
-    const double kInvTwoPi = 0.15915494309189533576888376337251436;
-    const double kTwoPi = 6.28318530717958647692528676655900577;
-    const double turns = static_cast<double>(pos) * radians_per_position * kInvTwoPi;
-    const double frac = turns - rint(turns);
-    sincosf(static_cast<float>(frac * kTwoPi), &s, &c);
-}
 
 // Block (t, y) handles token t and `heads_per_block` head slots from y * heads_per_block,
 // where slots 0 .. n_heads-1 are q heads (rotated in place) and the next n_kv_heads are
@@ -106,16 +98,16 @@ __global__ void rope_kv_write_kernel(scalar_t* __restrict__ q, const scalar_t* _
                     continue;
                 }
                 const float lo = pl_load(x + j) * r * q_norm[j], hi = pl_load(x + j + half) * r * q_norm[j + half];
-                pl_store(x + j, lo * cs[j] - hi * sn[j]);
-                pl_store(x + j + half, hi * cs[j] + lo * sn[j]);
+                pl_store(x + j, rope_lo(lo, hi, cs[j], sn[j]));
+                pl_store(x + j + half, rope_hi(lo, hi, cs[j], sn[j]));
                 continue;
             }
             if (inv_freq == nullptr || j >= half) {
                 continue;  // q passes through
             }
             const float lo = pl_load(x + j), hi = pl_load(x + j + half);
-            pl_store(x + j, lo * cs[j] - hi * sn[j]);
-            pl_store(x + j + half, hi * cs[j] + lo * sn[j]);
+            pl_store(x + j, rope_lo(lo, hi, cs[j], sn[j]));
+            pl_store(x + j + half, rope_hi(lo, hi, cs[j], sn[j]));
         } else if (page >= 0) {
             const int h = slot - n_heads;
             const scalar_t* x = k + t * row_stride + static_cast<int64_t>(h) * head_dim;
@@ -129,8 +121,8 @@ __global__ void rope_kv_write_kernel(scalar_t* __restrict__ q, const scalar_t* _
                     hi *= r * k_norm[j + half];
                 }
                 if (inv_freq != nullptr) {
-                    pl_store(k_pool + at + j, lo * cs[j] - hi * sn[j]);
-                    pl_store(k_pool + at + j + half, hi * cs[j] + lo * sn[j]);
+                    pl_store(k_pool + at + j, rope_lo(lo, hi, cs[j], sn[j]));
+                    pl_store(k_pool + at + j + half, rope_hi(lo, hi, cs[j], sn[j]));
                 } else if (k_norm != nullptr) {
                     pl_store(k_pool + at + j, lo);
                     pl_store(k_pool + at + j + half, hi);
@@ -226,10 +218,10 @@ __global__ void rope_kv_write_vec_kernel(scalar_t* __restrict__ q, const scalar_
             scalar_t* x = q + t * row_stride + static_cast<int64_t>(slot) * head_dim;
             const float4 lo = pl_load4(x + j), hi = pl_load4(x + j + half);
             const float4 c = *reinterpret_cast<const float4*>(cs + j), s = *reinterpret_cast<const float4*>(sn + j);
-            pl_store4(x + j, make_float4(lo.x * c.x - hi.x * s.x, lo.y * c.y - hi.y * s.y, lo.z * c.z - hi.z * s.z,
-                                         lo.w * c.w - hi.w * s.w));
-            pl_store4(x + j + half, make_float4(hi.x * c.x + lo.x * s.x, hi.y * c.y + lo.y * s.y,
-                                                hi.z * c.z + lo.z * s.z, hi.w * c.w + lo.w * s.w));
+            pl_store4(x + j, make_float4(rope_lo(lo.x, hi.x, c.x, s.x), rope_lo(lo.y, hi.y, c.y, s.y),
+                                         rope_lo(lo.z, hi.z, c.z, s.z), rope_lo(lo.w, hi.w, c.w, s.w)));
+            pl_store4(x + j + half, make_float4(rope_hi(lo.x, hi.x, c.x, s.x), rope_hi(lo.y, hi.y, c.y, s.y),
+                                                rope_hi(lo.z, hi.z, c.z, s.z), rope_hi(lo.w, hi.w, c.w, s.w)));
         } else if (page >= 0) {
             const int h = slot - n_heads;
             const scalar_t* x = k + t * row_stride + static_cast<int64_t>(h) * head_dim;
@@ -240,10 +232,11 @@ __global__ void rope_kv_write_vec_kernel(scalar_t* __restrict__ q, const scalar_
                 if (inv_freq != nullptr) {
                     const float4 c = *reinterpret_cast<const float4*>(cs + j);
                     const float4 s = *reinterpret_cast<const float4*>(sn + j);
-                    pl_store4(k_pool + at + j, make_float4(lo.x * c.x - hi.x * s.x, lo.y * c.y - hi.y * s.y,
-                                                           lo.z * c.z - hi.z * s.z, lo.w * c.w - hi.w * s.w));
-                    pl_store4(k_pool + at + j + half, make_float4(hi.x * c.x + lo.x * s.x, hi.y * c.y + lo.y * s.y,
-                                                                  hi.z * c.z + lo.z * s.z, hi.w * c.w + lo.w * s.w));
+                    pl_store4(k_pool + at + j, make_float4(rope_lo(lo.x, hi.x, c.x, s.x), rope_lo(lo.y, hi.y, c.y, s.y),
+                                                           rope_lo(lo.z, hi.z, c.z, s.z), rope_lo(lo.w, hi.w, c.w, s.w)));
+                    pl_store4(k_pool + at + j + half,
+                              make_float4(rope_hi(lo.x, hi.x, c.x, s.x), rope_hi(lo.y, hi.y, c.y, s.y),
+                                          rope_hi(lo.z, hi.z, c.z, s.z), rope_hi(lo.w, hi.w, c.w, s.w)));
                 } else {
                     pl_store4(k_pool + at + j, lo);
                     pl_store4(k_pool + at + j + half, hi);

@@ -25,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 15
+ABI_VERSION = 16
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -45,12 +45,12 @@ _SIGNATURES = {
     "pl_attention_simt": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
                           _I32, _I32, _I32, _I32, _I32, _F32, _F32, _I32, _PTR, _PTR, _PTR, _PTR, _PTR],
     "pl_attention_decode": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
-                            _I32, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR, _PTR],
+                            _I32, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR, _PTR, _PTR],
     "pl_attention_decode_mass": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
                                  _I32, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR, _I32, _PTR, _PTR, _F32, _PTR,
                                  _PTR],
     "pl_attention_decode_items": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
-                                  _I32, _I32, _I32, _I32, _I32, _F32, _PTR, _I32, _PTR, _PTR, _PTR, _PTR, _PTR],
+                                  _I32, _I32, _I32, _I32, _I32, _F32, _PTR, _I32, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR],
     "pl_attention_decode_ctas_per_sm": [_I32],
     "pl_attention_decode_supports": [_I32, _I32, _I32, _I32],
     "pl_attention_prefill": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _I32, _PTR, _I64,
@@ -349,6 +349,28 @@ def attention_decode_scratch_floats(n_tokens: int, n_heads: int, head_dim: int, 
     return int(library().pl_attention_decode_scratch_floats(n_tokens, n_heads, head_dim, n_splits))
 
 
+class _DecodeRope(ctypes.Structure):
+    _fields_ = [("k_new", _PTR), ("v_new", _PTR), ("inv_freq", _PTR), ("rotary", _I32)]
+
+
+def _decode_rope(rope: tuple | None, q: torch.Tensor, n_kv: int):
+    """The PlDecodeRope argument of the decode attention calls from (k_new, v_new,
+    inv_freq, rotary), or None. k_new, v_new [T, nkv, hd] share q's row stride (slices of
+    one projection output); None for both when the layer writes no keys."""
+    if rope is None:
+        return None
+    k_new, v_new, inv_freq, rotary = rope
+    tokens, _, head_dim = q.shape
+    _dev(k_new, v_new, inv_freq)
+    assert rotary == head_dim and inv_freq.dtype == torch.float64 and inv_freq.numel() == rotary // 2
+    assert inv_freq.is_contiguous()
+    for t in (k_new, v_new):
+        if t is not None:
+            assert t.dtype == q.dtype and t.shape == (tokens, n_kv, head_dim) and t.stride(2) == 1
+            assert t.stride(1) == head_dim and (tokens == 1 or t.stride(0) == q.stride(0))
+    return ctypes.byref(_DecodeRope(_p(k_new), _p(v_new), _p(inv_freq), int(rotary)))
+
+
 _DECODE_COUNTERS: dict[torch.device, torch.Tensor] = {}
 DECODE_COUNTERS = 1 << 20
 
@@ -365,13 +387,14 @@ def attention_decode_counters(device: torch.device) -> torch.Tensor:
 def attention_decode_items(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,
                            pos: torch.Tensor, entry: torch.Tensor, out: torch.Tensor, page_size: int,
                            window: int | None, scale: float, items: torch.Tensor, token_slot: torch.Tensor,
-                           scratch: torch.Tensor, status: torch.Tensor | None = None) -> None:
+                           scratch: torch.Tensor, status: torch.Tensor | None = None,
+                           rope: tuple | None = None) -> None:
     """bf16 attention of single decode tokens over a work list (shapes as
     attention_decode). items: int32 [n, 4] rows {token, first 16-key tile, tiles, split |
     splits << 12}, rows of no tiles are padding; the rows of a token cover its tiles once.
     token_slot int32 [tokens]: first slot of a token's partial results in `scratch`
     (fp32, n * n_heads * (head_dim + 2) floats). The CTA that finishes a token's kv head
-    last merges its splits in split order."""
+    last merges its splits in split order. `rope` as in attention_decode."""
     _dev(q, k_pool, v_pool, table, pos, entry, out, items, token_slot, scratch, status)
     tokens, n_heads, head_dim = q.shape
     n_pages, n_kv = k_pool.shape[0], k_pool.shape[1]
@@ -393,7 +416,7 @@ def attention_decode_items(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
     _call("pl_attention_decode_items", _p(q), q.stride(0), _p(k_pool), _p(v_pool), k_pool.stride(0),
           k_pool.stride(1), page_size, n_pages, _p(table), table.shape[1], _p(pos), _p(entry), _p(out),
           out.stride(0), tokens, n_heads, n_kv, head_dim, int(window or 0), float(scale), _p(items), n_items,
-          _p(token_slot), _p(scratch), _p(counters), _p(status), _stream())
+          _p(token_slot), _p(scratch), _p(counters), _decode_rope(rope, q, n_kv), _p(status), _stream())
 
 
 def attention_decode_ctas_per_sm(head_dim: int) -> int:
@@ -404,7 +427,8 @@ def attention_decode_ctas_per_sm(head_dim: int) -> int:
 def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,
                      pos: torch.Tensor, entry: torch.Tensor, out: torch.Tensor, page_size: int, window: int | None,
                      scale: float, n_splits: int, scratch: torch.Tensor | None,
-                     status: torch.Tensor | None = None, mass: tuple | None = None) -> None:
+                     status: torch.Tensor | None = None, mass: tuple | None = None,
+                     rope: tuple | None = None) -> None:
     """bf16 attention of single decode tokens, split over the keys `n_splits` ways;
     shapes as attention_simt. `scratch`: fp32, attention_decode_scratch_floats long.
     `mass` = (tile_max, mass_sum, weight_sum, decay): also measures attention mass.
@@ -412,7 +436,11 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     mass_sum fp32 [pages, nh] and weight_sum fp32 [pages] are the running accumulators:
     what the request's pages hold is scaled by 1 - decay (the page the token opens
     restarts at zero) and decay * (the token's largest scaled score in the page), per
-    head, and decay, per page, are added."""
+    head, and decay, per page, are added.
+    `rope` = (k_new, v_new, inv_freq, rotary): q is unrotated; the kernel rotates it as it
+    loads it, and rotates and stores each token's new key (with its value) at the token's
+    place in the pools before reading it: the position encoding and the cache write
+    folded into the attention (whole-head rotation only; not together with `mass`)."""
     _dev(q, k_pool, v_pool, table, pos, entry, out, scratch, status)
     tokens, n_heads, head_dim = q.shape
     n_pages, n_kv = k_pool.shape[0], k_pool.shape[1]
@@ -427,6 +455,7 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
         assert scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous()
         assert scratch.numel() >= attention_decode_scratch_floats(tokens, n_heads, head_dim, n_splits)
     if mass is not None:
+        assert rope is None, "the mass-measuring call does not fold the position encoding in"
         tile_max, mass_sum, weight_sum, decay = mass
         max_tiles = table.shape[1] * page_size // 16
         _dev(tile_max, mass_sum, weight_sum)
@@ -442,7 +471,8 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
         return
     _call("pl_attention_decode", _p(q), q.stride(0), _p(k_pool), _p(v_pool), k_pool.stride(0), k_pool.stride(1),
           page_size, n_pages, _p(table), table.shape[1], _p(pos), _p(entry), _p(out), out.stride(0), tokens,
-          n_heads, n_kv, head_dim, int(window or 0), float(scale), int(n_splits), _p(scratch), _p(status),
+          n_heads, n_kv, head_dim, int(window or 0), float(scale), int(n_splits), _p(scratch),
+          _decode_rope(rope, q, n_kv), _p(status),
           _stream())
 
 

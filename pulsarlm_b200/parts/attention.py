@@ -105,6 +105,7 @@ _CTAS_PER_SM: dict[tuple, int] = {}
 DECODE_ITEM_MIN_TILES = 32     # no work item much shorter than 32 16-key tiles (a warp's ring must fill)
 DECODE_ITEMS_PER_SLOT = 1      # unequal requests are cut into about this many items per resident CTA
 DECODE_ITEMS = os.environ.get("PULSARLM_B200_DECODE_ITEMS", "1") != "0"  # (0: equal shares only, for comparison)
+FOLD_ROPE = os.environ.get("PULSARLM_B200_FOLD_ROPE", "1") != "0"  # (0: always the separate rotation kernel)
 DECODE_EVEN_ENOUGH = 1.3       # longest / mean length up to which nothing is cut
 
 
@@ -280,6 +281,14 @@ class Attention(Part):
         qkv = linear(h, self.qkv)
         q = qkv[:, : nh * hd].view(tokens, nh, hd)
         inv_freq, rotary = self.position.table()
+        if self._folds_rope(tokens, batch, inv_freq, rotary):
+            # Single tokens only, all for the tensor-core decode kernel: it rotates q as it loads
+            # it and stores each token's rotated key and value itself, one launch fewer.
+            rope = (qkv[:, nh * hd : (nh + nkv) * hd].view(tokens, nkv, hd),
+                    qkv[:, (nh + nkv) * hd :].view(tokens, nkv, hd), inv_freq, rotary)
+            out = torch.empty((tokens, nh, hd), dtype=h.dtype, device=h.device)
+            self.attend(q, out, table, batch, rope)
+            return linear(out.view(tokens, nh * hd), self.o)
         if self.cache_from is None:
             k = qkv[:, nh * hd : (nh + nkv) * hd].view(tokens, nkv, hd)
             v = qkv[:, (nh + nkv) * hd :].view(tokens, nkv, hd)
@@ -291,6 +300,18 @@ class Attention(Part):
         out = torch.empty((tokens, nh, hd), dtype=h.dtype, device=h.device)
         self.attend(q, out, table, batch)
         return linear(out.view(tokens, nh * hd), self.o)
+
+    def _folds_rope(self, tokens: int, batch, inv_freq, rotary: int) -> bool:
+        """Whether this step's position encoding and cache write go into the decode
+        attention kernel: a step of single tokens that all take that kernel, a layer with a
+        cache of its own, whole-head rotation, no q/k norm, no score cap, no mass measured."""
+        if not FOLD_ROPE or int(batch.n_decode) != tokens or self.cache_from is not None or inv_freq is None:
+            return False
+        if rotary != self.head_dim or self.q_norm is not None or self.k_norm is not None or self.softcap:
+            return False
+        if self.cache.mass_sum is not None:
+            return False
+        return self._kernels(self.ctx.dtype)[0]
 
     # ------------------------------------------------------------------ planning a step
     def _kernels(self, dtype: torch.dtype) -> tuple[bool, bool]:
@@ -366,7 +387,7 @@ class Attention(Part):
             plan["tiles_wide"] = np.array(wide_tiles, dtype=np.int32).reshape(len(wide_tiles), 4)
         return plan
 
-    def attend(self, q: torch.Tensor, out: torch.Tensor, table: torch.Tensor, batch) -> None:
+    def attend(self, q: torch.Tensor, out: torch.Tensor, table: torch.Tensor, batch, rope: tuple | None = None) -> None:
         """out = attention of q over the cache. The batch's leading `n_decode` tokens
         are single tokens of their requests: in bfloat16 they go to the split-key
         tensor-core kernel and prompt portions to the tiled tensor-core kernel (tcgen05
@@ -412,7 +433,7 @@ class Attention(Part):
                                   device=q.device)
             ops.attention_decode_items(q[:n_decode], cache.k_pool, cache.v_pool, table, batch.pos[:n_decode],
                                        batch.entry[:n_decode], out[:n_decode], cache.page_size, self.window,
-                                       self.scale, items, plan["decode_slots"], scratch, batch.status)
+                                       self.scale, items, plan["decode_slots"], scratch, batch.status, rope)
         elif n_decode > 0:
             max_context = plan.get("max_context") or max(batch.host_context_lens[:n_decode])
             if self.window:
@@ -426,7 +447,7 @@ class Attention(Part):
                                       dtype=torch.float32, device=q.device)
             ops.attention_decode(q[:n_decode], cache.k_pool, cache.v_pool, table, batch.pos[:n_decode],
                                  batch.entry[:n_decode], out[:n_decode], cache.page_size, self.window, self.scale,
-                                 splits, scratch, batch.status)
+                                 splits, scratch, batch.status, rope=rope)
         tiles = plan.get("tiles")
         if n_decode < tokens and prefill_kernel and tiles is not None and n_decode == int(batch.n_decode):
             # The tile list covers exactly the tokens after the leading single tokens.

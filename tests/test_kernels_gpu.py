@@ -411,6 +411,70 @@ def test_attention_decode_over_a_work_list(ops, nh, nkv, hd, page, target, windo
     assert int(ops.attention_decode_counters(q.device).abs().sum()) == 0
 
 
+@pytest.mark.parametrize("nh,nkv,hd,page", [(8, 2, 64, 16), (32, 8, 128, 16), (6, 6, 128, 32), (16, 1, 64, 64)])
+@pytest.mark.parametrize("mode", ["splits1", "splits3", "splits12", "splits20", "items"])
+@pytest.mark.parametrize("window", [None, 100])
+def test_attention_decode_with_the_rotation_and_the_cache_write_folded_in(ops, nh, nkv, hd, page, mode, window):
+    """One call that rotates q, rotates and stores the new keys and values, and attends,
+    against the rotation kernel followed by the plain call: the same bits in the cache and
+    in the output, whichever CTA and warp the token's own tile falls to (lengths that put
+    it first, last and alone in a share), and nothing else written."""
+    from pulsarlm_b200.parts.attention import decode_work_items
+
+    dtype = torch.bfloat16
+    lengths = [1, 16, 17, 33, 250, 700, 129, 1041]
+    n = len(lengths)
+    pages_each = -(-max(lengths) // page)
+    n_pages = n * pages_each + 3
+    table = scattered_tables(n, pages_each, n_pages, seed=hd + page).to(DEV)
+    kp, vp = make_pools(n_pages, nkv, page, hd, dtype, fill=1.0)
+    pos_t = torch.tensor([c - 1 for c in lengths], dtype=torch.int32, device=DEV)
+    entry_t = torch.arange(n, dtype=torch.int32, device=DEV)
+    inv_freq = plain_llama.rope_inverse_frequency(500000.0, hd, None).to(DEV)
+    qkv = torch.randn(n, (nh + 2 * nkv) * hd, device=DEV).to(dtype)
+
+    def views(buffer):
+        return (buffer[:, : nh * hd].view(n, nh, hd), buffer[:, nh * hd : (nh + nkv) * hd].view(n, nkv, hd),
+                buffer[:, (nh + nkv) * hd :].view(n, nkv, hd))
+
+    scale = 1 / math.sqrt(hd)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+
+    def attend(q, k_pool, v_pool, out, rope):
+        if mode == "items":
+            items, slots = decode_work_items(lengths, window, 9, min_tiles=4)
+            scratch = torch.empty(items.shape[0] * nh * (hd + 2), device=DEV)
+            ops.attention_decode_items(q, k_pool, v_pool, table, pos_t, entry_t, out, page, window, scale,
+                                       torch.from_numpy(items).to(DEV), torch.from_numpy(slots).to(DEV), scratch,
+                                       status, rope)
+        else:
+            splits = int(mode[6:])
+            scratch = torch.empty(max(1, ops.attention_decode_scratch_floats(n, nh, hd, splits)), device=DEV)
+            ops.attention_decode(q, k_pool, v_pool, table, pos_t, entry_t, out, page, window, scale, splits, scratch,
+                                 status, rope=rope)
+
+    # the two kernels
+    first = qkv.clone()
+    q1, k1, v1 = views(first)
+    kp1, vp1 = kp.clone(), vp.clone()
+    ops.rope_kv_write(q1, k1, v1, pos_t, entry_t, table, kp1, vp1, page, inv_freq, hd, status)
+    out1 = torch.full((n, nh, hd), float("nan"), device=DEV, dtype=dtype)
+    attend(q1, kp1, vp1, out1, None)
+    # the one
+    second = qkv.clone()
+    q2, k2, v2 = views(second)
+    kp2, vp2 = kp.clone(), vp.clone()
+    out2 = torch.full((n, nh, hd), float("nan"), device=DEV, dtype=dtype)
+    attend(q2, kp2, vp2, out2, (k2, v2, inv_freq, hd))
+    assert int(status) == 0
+    assert torch.equal(second, qkv)                       # q, k, v are left as they came
+    assert torch.equal(kp1, kp2) and torch.equal(vp1, vp2)
+    assert not torch.equal(kp2, kp)
+    assert torch.equal(out1, out2)
+    want = reference_attention(q1, kp1, vp1, table.cpu(), pos_t.tolist(), entry_t.tolist(), page, window, scale)
+    assert rel(out2, want) < 1e-2
+
+
 def test_attention_decode_refuses_what_it_cannot_do(ops):
     assert not ops.attention_decode_supports(80, 1, 16, torch.bfloat16)
     assert not ops.attention_decode_supports(128, 32, 16, torch.bfloat16)
