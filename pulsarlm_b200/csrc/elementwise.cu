@@ -316,3 +316,42 @@ PL_API int pl_bf16_to_f32(const void* src, float* dst, int64_t n, cudaStream_t s
     PL_CHECK_LAUNCH("bf16_to_f32");
     return 0;
 }
+
+// ---------------------------------------------------------------------------
+// Random weights drawn in place (see random_values.h): out[i] = offset + scale * noise(i).
+#include "random_values.h"
+
+namespace {
+
+template <typename scalar_t>
+__global__ void fill_random_kernel(scalar_t* __restrict__ out, int64_t n, uint64_t key, float scale, float offset) {
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const float value = pl_random_value(key, static_cast<uint64_t>(i), scale, offset);
+        if constexpr (sizeof(scalar_t) == 2) {
+            reinterpret_cast<uint16_t*>(out)[i] = pl_random_bf16_bits(value);
+        } else {
+            out[i] = value;
+        }
+    }
+}
+
+}  // namespace
+
+// out (fp32 or bf16, n elements) = offset + scale * noise, the noise a function of
+// (seed, tensor_hash, element index) alone; the host core's plh_fill_random gives the
+// same bits.
+PL_API int pl_fill_random(void* out, int64_t n, int dtype, uint64_t seed, uint64_t tensor_hash, float scale,
+                          float offset, cudaStream_t stream) {
+    PL_REQUIRE(n >= 0, "fill_random: negative size");
+    if (n == 0) {
+        return 0;
+    }
+    const uint64_t key = pl_random_key(seed, tensor_hash);
+    const int blocks = static_cast<int>(n / 1024 + 1 < 148 * 16 ? n / 1024 + 1 : 148 * 16);
+    PL_DISPATCH_DTYPE(dtype, "fill_random", {
+        fill_random_kernel<scalar_t><<<blocks, 256, 0, stream>>>(static_cast<scalar_t*>(out), n, key, scale, offset);
+    });
+    PL_CHECK_LAUNCH("fill_random");
+    return 0;
+}

@@ -443,7 +443,7 @@ using plh::CacheBook;
 using plh::PagePool;
 using plh::SchedulerCore;
 
-PLH_API int plh_abi_version() { return 1; }
+PLH_API int plh_abi_version() { return 2; }
 
 PLH_API void* plh_pool_create(int n_pages) { return new PagePool(n_pages); }
 PLH_API void plh_pool_destroy(void* pool) { delete static_cast<PagePool*>(pool); }
@@ -589,4 +589,97 @@ PLH_API int plh_sched_finish_step(void* sched, const int64_t* entries, const int
         ended[2 * i + 1] = x[i].reason;
     }
     return static_cast<int>(x.size());
+}
+
+// ---------------------------------------------------------------------------
+// Random weights on the host (the device's twin is pl_fill_random; same bits).
+#include "../csrc/random_values.h"
+
+// out (fp32 when dtype is 0, bfloat16 bits when 1; n elements) = offset + scale * noise,
+// the noise a function of (seed, tensor_hash, element index) alone.
+PLH_API int plh_fill_random(void* out, int64_t n, int dtype, uint64_t seed, uint64_t tensor_hash, float scale,
+                            float offset) {
+    if (n < 0 || (dtype != 0 && dtype != 1) || (out == nullptr && n > 0)) {
+        return plh::kBadArgument;
+    }
+    const uint64_t key = pl_random_key(seed, tensor_hash);
+    if (dtype == 0) {
+        float* values = static_cast<float*>(out);
+        for (int64_t i = 0; i < n; ++i) {
+            values[i] = pl_random_value(key, static_cast<uint64_t>(i), scale, offset);
+        }
+    } else {
+        uint16_t* values = static_cast<uint16_t*>(out);
+        for (int64_t i = 0; i < n; ++i) {
+            values[i] = pl_random_bf16_bits(pl_random_value(key, static_cast<uint64_t>(i), scale, offset));
+        }
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// The work list of a step's single tokens for the decode attention kernel.
+//
+// lengths[n]: keys each token's request holds after the step; window: 0 or how many of
+// the last keys a query reads. The tokens' 16-key tiles are cut into about `target` items
+// of equal size (none much shorter than min_tiles), a request's share rounded to whole
+// items that differ by one tile at most; requests of about one length (longest within
+// even_percent of the mean) are left whole. Rows {token, first tile, tiles, split | splits
+// << 12}, longest first, go to items[capacity][4]; unused rows are zero and the last of
+// them holds the number of rows in use in its first field. slots[n]: first scratch slot of
+// each token's splits. Returns the number of rows in use, or a negative code when
+// `capacity` is too small (at most target + n are needed).
+PLH_API int plh_decode_work_items(const int32_t* lengths, int n, int window, int target, int min_tiles,
+                                  int even_percent, int32_t* items, int capacity, int32_t* slots) {
+    if (n < 0 || target < 1 || min_tiles < 1 || capacity < 1 || lengths == nullptr || items == nullptr ||
+        slots == nullptr) {
+        return plh::kBadArgument;
+    }
+    struct Row {
+        int32_t token, first, tiles, code;
+    };
+    std::vector<Row> rows;
+    rows.reserve(static_cast<size_t>(n) + target);
+    int64_t total = 0;
+    int32_t longest = 0;
+    std::vector<int32_t> first(n), tiles(n);
+    for (int t = 0; t < n; ++t) {
+        const int32_t context = lengths[t];
+        first[t] = (window > 0 && context > window ? context - window : 0) / 16;
+        tiles[t] = std::max<int32_t>(0, (context + 15) / 16 - first[t]);
+        total += tiles[t];
+        longest = std::max(longest, tiles[t]);
+    }
+    const int64_t chunk = std::max<int64_t>(min_tiles, (total + target - 1) / target);
+    const bool even = static_cast<int64_t>(longest) * n * 100 <= static_cast<int64_t>(even_percent) * total;
+    int32_t slot = 0;
+    for (int t = 0; t < n; ++t) {
+        int64_t k = even ? 1 : (2 * static_cast<int64_t>(tiles[t]) + chunk) / (2 * chunk);  // tiles / chunk, rounded
+        k = std::min<int64_t>(4095, std::max<int64_t>(1, k));
+        slots[t] = slot;
+        if (k > 1) {
+            slot += static_cast<int32_t>(k);
+        }
+        int32_t at = first[t];
+        for (int32_t s = 0; s < k; ++s) {
+            const int32_t share = tiles[t] / static_cast<int32_t>(k) + (s < tiles[t] % static_cast<int32_t>(k) ? 1 : 0);
+            rows.push_back({t, at, share, s | (static_cast<int32_t>(k) << 12)});
+            at += share;
+        }
+    }
+    std::stable_sort(rows.begin(), rows.end(), [](const Row& a, const Row& b) { return a.tiles > b.tiles; });
+    if (static_cast<int>(rows.size()) > capacity) {
+        return plh::kBadArgument;
+    }
+    std::fill(items, items + static_cast<size_t>(capacity) * 4, 0);
+    for (size_t i = 0; i < rows.size(); ++i) {
+        items[4 * i] = rows[i].token;
+        items[4 * i + 1] = rows[i].first;
+        items[4 * i + 2] = rows[i].tiles;
+        items[4 * i + 3] = rows[i].code;
+    }
+    if (static_cast<int>(rows.size()) < capacity) {
+        items[4 * (capacity - 1)] = static_cast<int32_t>(rows.size());
+    }
+    return static_cast<int>(rows.size());
 }

@@ -13,6 +13,7 @@ cancel(); pulsarlm/src/pulsarlm/completion.py:43-109: complete()).
 from __future__ import annotations
 
 import itertools
+import sys
 from typing import Iterator
 
 import torch
@@ -75,6 +76,12 @@ class Engine:
         self.cache = CacheManager(needs, page_size, n_pages, max_requests, self.dtype, self.device,
                                   mass_decay=attention_mass_decay)
         self.runner = ModelRunner(self.model, self.cache)
+        self.runner._bind()
+        # Said once: a shape that the fast kernels do not take still runs, only slower.
+        notes = sorted({note for part in self.model.parts()
+                        for note in [getattr(part, "slow_path_note", lambda: None)()] if note})
+        for note in notes:
+            print(f"[pulsarlm_b200] note: {note}", file=sys.stderr, flush=True)
         self.sampler = Sampler(self.device)
         stops = self.model.spec.eos_token_ids if stop_ids is None else stop_ids
         self.scheduler = Scheduler(self.cache, stops, prefill_tokens_per_step)

@@ -189,7 +189,8 @@ def library_path(build: bool = True, verbose: bool = True) -> str:
 
 HOST_SRC = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "csrc_host"))
 HOST_LIB_NAME = "libpulsarlm_host.so"
-HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall", "-ffp-contract=off"]
+HOST_SHARED_HEADERS = ["random_values.h"]  # headers of the kernel tree that the host core includes too
 
 
 def host_library_path(build: bool = True, verbose: bool = True) -> str:
@@ -202,6 +203,10 @@ def host_library_path(build: bool = True, verbose: bool = True) -> str:
     files = sorted(n for n in os.listdir(HOST_SRC) if n.endswith((".cpp", ".hpp", ".h")))
     for n in files:
         with open(os.path.join(HOST_SRC, n), "rb") as f:
+            digest.update(n.encode())
+            digest.update(f.read())
+    for n in HOST_SHARED_HEADERS:
+        with open(os.path.join(CSRC, n), "rb") as f:
             digest.update(n.encode())
             digest.update(f.read())
     current = None

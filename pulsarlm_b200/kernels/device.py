@@ -1,0 +1,61 @@
+"""What the host-side cost estimates know of the device: one description object.
+
+The attention part chooses how to split keys among CTAs by estimating times; every
+figure those estimates use that belongs to the device rather than to the kernel's
+shape lives here, with where it was measured, so that another device is another
+instance and not an edit of the part.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+
+
+@dataclasses.dataclass(frozen=True)
+class DeviceDescription:
+    """Figures of one GPU model as the engine's kernels see them."""
+
+    name: str
+    # What the split-key decode attention reaches when CTAs are many: a little under the
+    # copy bandwidth (measured with that kernel at batch 64, 2,048 and 8,192 keys).
+    stream_bytes_per_second: float
+    # What one CTA of that kernel takes in when CTAs are few (two 8 KB tiles in flight per
+    # warp against the memory's answer time).
+    cta_bytes_per_second: float
+    round_seconds: float          # start and end of a round of CTAs of the decode kernel
+    cluster_merge_seconds: float  # merging up to sixteen splits inside a thread-block cluster
+    merge_kernel_seconds: float   # merging more splits through scratch and a second kernel
+    # Prompt attention (tcgen05), head size 128: one key for one CTA, the fixed cost of a round
+    # of CTAs, the merge launch, and the bandwidth its partial rows are written and read at.
+    prefill_key_seconds: float
+    prefill_round_seconds: float
+    prefill_merge_seconds: float
+    prefill_scratch_bytes_per_second: float
+
+
+B200 = DeviceDescription(
+    name="B200",
+    stream_bytes_per_second=6.3e12,
+    cta_bytes_per_second=36e9,
+    round_seconds=2e-6,
+    cluster_merge_seconds=2e-6,
+    merge_kernel_seconds=5e-6,
+    prefill_key_seconds=17.3e-9,
+    prefill_round_seconds=6e-6,
+    prefill_merge_seconds=4e-6,
+    prefill_scratch_bytes_per_second=4e12,
+)
+
+_DESCRIPTIONS: dict = {}
+
+
+def describe(device: torch.device) -> DeviceDescription:
+    """The description the estimates use for `device`: the engine runs on sm_100 only, so
+    this is the B200's until another is registered with `register`."""
+    return _DESCRIPTIONS.get(device, B200)
+
+
+def register(device: torch.device, description: DeviceDescription) -> None:
+    _DESCRIPTIONS[device] = description

@@ -52,6 +52,7 @@ _SIGNATURES = {
     "pl_attention_decode_items": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
                                   _I32, _I32, _I32, _I32, _I32, _F32, _PTR, _I32, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR],
     "pl_attention_decode_ctas_per_sm": [_I32],
+    "pl_fill_random": [_PTR, _I64, _I32, ctypes.c_uint64, ctypes.c_uint64, _F32, _F32, _PTR],
     "pl_attention_decode_supports": [_I32, _I32, _I32, _I32],
     "pl_attention_prefill": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _I32, _PTR, _I64,
                              _I32, _I32, _I32, _I32, _F32, _PTR, _PTR],
@@ -208,6 +209,15 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     assert two_i % 2 == 0 and out.shape == (tokens, two_i // 2) and out.dtype == gate_up.dtype
     assert gate_up.is_contiguous() and out.is_contiguous()
     _call("pl_swiglu", _p(gate_up), _p(out), tokens, two_i // 2, _code(out.dtype), _stream())
+
+
+def fill_random(out: torch.Tensor, seed: int, tensor_hash: int, scale: float, offset: float = 0.0) -> None:
+    """out = offset + scale * noise(seed, tensor_hash, element index): random weights drawn in
+    place, the same bits as the host core draws (weights/random_init.py)."""
+    _dev(out)
+    assert out.is_contiguous()
+    _call("pl_fill_random", _p(out), out.numel(), _code(out.dtype), seed, tensor_hash, float(scale), float(offset),
+          _stream())
 
 
 def bf16_to_f32(src: torch.Tensor, dst: torch.Tensor) -> None:

@@ -10,6 +10,7 @@ import numpy as np
 import torch
 
 from ..kernels import ops
+from ..kernels.device import describe as describe_device
 from .linear import linear
 from .registry import BuildContext, Part, build_part, register_part
 from .spec import KVCacheNeed, PartSpec, TensorNeed
@@ -67,19 +68,20 @@ def _decode_splits(n_ctas: int, max_context: int, device: torch.device, head_dim
     splits): the count with the least estimated time. The CTAs of a launch run in rounds
     of what the device holds at once (two CTAs per SM; with splits, the thread-block
     clusters that fit); a round streams at the memory's bandwidth if it has CTAs enough
-    and at 36 GB/s per CTA if it has few, so few long CTAs, and a sparse last round of
-    them, are what splitting avoids. Constants measured with this kernel (they reproduce
-    its times at batch 1 to 64 within a tenth): 6.3 TB/s, 2 us per round, 2 us for the
-    merge inside a cluster (up to sixteen splits), 5 us for the merge kernel (more
-    splits, through scratch memory). No split shorter than eight 16-key tiles."""
+    and at one CTA's own rate times their number if it has few, so few long CTAs, and a
+    sparse last round of them, are what splitting avoids. The rates and fixed costs are the
+    device description's (kernels/device.py: measured with this kernel, they reproduce its
+    times at batch 1 to 64 within a tenth). No split shorter than eight 16-key tiles."""
     if device not in _SM_COUNT:
         _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
     slots = 2 * _SM_COUNT[device]
     most = max(1, min(-(-max_context // 16) // 8, max(16, slots // max(1, n_ctas))))
     key_bytes = 4.0 * head_dim  # K and V of one key and kv head
 
+    dev = describe_device(device)
+
     def round_seconds(ctas: int, bytes_each: float) -> float:
-        return ctas * bytes_each / min(6.3e12, ctas * 36e9) + 2e-6
+        return ctas * bytes_each / min(dev.stream_bytes_per_second, ctas * dev.cta_bytes_per_second) + dev.round_seconds
 
     best, best_cost = 1, float("inf")
     for splits in range(most, 0, -1):  # on a tie, the finer split
@@ -95,7 +97,7 @@ def _decode_splits(n_ctas: int, max_context: int, device: torch.device, head_dim
         if total % room:
             cost += round_seconds(total % room, bytes_each)
         if splits > 1:
-            cost += 2e-6 if splits <= 16 else 5e-6
+            cost += dev.cluster_merge_seconds if splits <= 16 else dev.merge_kernel_seconds
         if cost < best_cost:
             best, best_cost = splits, cost
     return best
@@ -120,8 +122,7 @@ def decode_item_ctas(device: torch.device, head_dim: int, n_kv: int) -> int:
     return max(1, -(-_CTAS_PER_SM[key] * _SM_COUNT[device] // n_kv))
 
 
-def decode_work_items(context_lens: list[int], window: int | None, target: int,
-                      pad_to: int | None = None, stride: int | None = None,
+def decode_work_items(context_lens: list[int], window: int | None, target: int, pad_to: int | None = None,
                       min_tiles: int = DECODE_ITEM_MIN_TILES) -> tuple[np.ndarray, np.ndarray]:
     """The work list of a step's single tokens for ops.attention_decode_items: int32
     [items, 4] rows {token, first 16-key tile, tiles, split | splits << 12}, longest first,
@@ -130,39 +131,21 @@ def decode_work_items(context_lens: list[int], window: int | None, target: int,
     Else the tiles are cut into about `target` items of equal size, a request's share
     rounded to whole items, so that the CTAs in flight stay many until the end instead of
     the longest requests streaming alone. At most target + tokens items; `pad_to` pads the
-    list with empty rows to a fixed length (the last row then holds the count of real rows). With `stride` (the number of CTAs that walk the
-    list, CTA x taking rows x, x + stride, ...) every second full round of rows is turned
-    around, so that the CTA with the longest item of one round gets the shortest of the next."""
+    list with empty rows to a fixed length (the last row then holds the count of real
+    rows). Made by the host core (csrc_host/host_core.cpp: plh_decode_work_items)."""
+    from ..host import core
+
     n = len(context_lens)
-    firsts = [(max(0, c - window) if window else 0) // 16 for c in context_lens]
-    tiles = [max(0, -(-c // 16) - f) for c, f in zip(context_lens, firsts)]
-    total = sum(tiles)
-    chunk = max(min_tiles, -(-total // max(1, target)))
-    even = max(tiles, default=0) * n <= DECODE_EVEN_ENOUGH * total
-    rows = []
-    slots = np.zeros(n, dtype=np.int32)
-    slot = 0
-    for t in range(n):
-        k = 1 if even else min(4095, max(1, int(tiles[t] / chunk + 0.5)))
-        slots[t] = slot
-        if k > 1:
-            slot += k
-        at = firsts[t]
-        for s in range(k):  # shares that differ by one tile at most
-            share = tiles[t] // k + (1 if s < tiles[t] % k else 0)
-            rows.append((t, at, share, s | (k << 12)))
-            at += share
-    rows.sort(key=lambda r: -r[2])
-    if stride:
-        for at in range(stride, len(rows) - stride + 1, 2 * stride):
-            rows[at : at + stride] = rows[at : at + stride][::-1]
-    length = max(len(rows), pad_to or 0, 1)
-    items = np.zeros((length, 4), dtype=np.int32)
-    if rows:
-        items[: len(rows)] = np.array(rows, dtype=np.int32)
-    if length > len(rows):
-        items[-1, 0] = len(rows)  # the last padding row tells how many rows are real
-    return items, slots
+    lengths = np.asarray(context_lens, dtype=np.int32)
+    capacity = max(pad_to or 0, target + n, 1)
+    items = np.empty((capacity, 4), dtype=np.int32)
+    slots = np.empty(max(n, 1), dtype=np.int32)
+    used = core.library().plh_decode_work_items(
+        lengths.ctypes.data, n, int(window or 0), int(target), int(min_tiles), int(round(DECODE_EVEN_ENOUGH * 100)),
+        items.ctypes.data, capacity, slots.ctypes.data)
+    if used < 0:
+        raise ValueError(f"decode_work_items: the host core refused the list (code {used})")
+    return items[: max(pad_to or 0, used, 1)], slots[:n]
 
 
 def prefill_splits(n_ctas: int, max_keys: int, n_tokens: int, n_heads: int, head_dim: int,
@@ -170,22 +153,24 @@ def prefill_splits(n_ctas: int, max_keys: int, n_tokens: int, n_heads: int, head
     """Ways to split every prompt tile's keys when the tiles alone (`n_ctas` CTAs, one per
     SM) leave SMs idle: a short portion of a long prompt. Picks the count with the least
     estimated time: rounds of CTAs, each a fixed start plus its share of the keys, plus
-    what the partial rows cost to write and merge; the constants are measurements of the
-    kernel at head size 128 (17 ns per key and CTA, 6 us per round, 4 us and the
-    scratch traffic at 4 TB/s for the merge). Splits only if that saves a tenth."""
+    what the partial rows cost to write and merge; the constants are the device
+    description's (kernels/device.py: measurements of the kernel at head size 128). Splits
+    only if that saves a tenth."""
     if device not in _SM_COUNT:
         _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
     sms = _SM_COUNT[device]
     most = min(max_keys // 256, 16, ops.PREFILL_SPLITS_MAX)
     if n_ctas <= 0 or n_ctas >= sms or most < 2:
         return 1
-    per_key = 17.3e-9 * head_dim / 128
+    dev = describe_device(device)
+    per_key = dev.prefill_key_seconds * head_dim / 128
 
     def cost(splits: int) -> float:
         rounds = -(-n_ctas * splits // sms)
-        seconds = rounds * (6e-6 + max_keys / splits * per_key)
+        seconds = rounds * (dev.prefill_round_seconds + max_keys / splits * per_key)
         if splits > 1:
-            seconds += 4e-6 + n_tokens * n_heads * splits * (head_dim + 2) * 8 / 4e12
+            seconds += dev.prefill_merge_seconds + (n_tokens * n_heads * splits * (head_dim + 2) * 8
+                                                    / dev.prefill_scratch_bytes_per_second)
         return seconds
 
     best = min(range(1, most + 1), key=cost)
@@ -322,6 +307,23 @@ class Attention(Part):
                 self.head_dim, self.n_heads // self.n_kv, self.cache.page_size, dtype)
             self._prefill_kernel = ops.attention_prefill_supports(self.head_dim, self.cache.page_size, dtype)
         return self._decode_kernel, self._prefill_kernel
+
+    def slow_path_note(self) -> str | None:
+        """A sentence for the user when this layer's shape keeps bfloat16 attention off the
+        tensor-core kernels (it then runs on the CUDA-core kernel: right, but several times
+        slower), else None. float32 attends on CUDA cores by design."""
+        if self.cache is None or self.ctx.dtype != torch.bfloat16:
+            return None
+        decode_kernel, prefill_kernel = self._kernels(self.ctx.dtype)
+        if self.softcap:
+            return (f"attention with a score cap ({self.softcap:g}) runs on the CUDA-core attention kernel, the "
+                    f"only one that squashes scores; expect it several times slower than uncapped attention")
+        if decode_kernel and prefill_kernel:
+            return None
+        return (f"attention with head size {self.head_dim}, {self.n_heads // self.n_kv} query heads per kv head and "
+                f"pages of {self.cache.page_size} tokens runs on the CUDA-core attention kernel (the tensor-core "
+                f"kernels take head sizes 64 and 128, groups up to 16 and pages that are multiples of 16 tokens); "
+                f"expect it several times slower")
 
     def measures_mass_in_captured_steps(self) -> bool:
         """Whether this layer can measure attention mass inside a captured decode step

@@ -18,8 +18,8 @@ accumulation, by one of three routes chosen by $PULSARLM_B200_GEMM:
   elsewhere;
 * "library": the library everywhere.
 
-The default is whichever measured faster on the Llama-3.1-8B shapes; see
-profiles/gemm_tcgen05_vs_library.md.
+The default is whichever measured faster on the Llama-3.1-8B shapes
+(`python -m pulsarlm_b200.kernels.microbench gemm` times both).
 """
 
 from __future__ import annotations

@@ -1,10 +1,14 @@
 """Random weights from a configuration and a seed.
 
-`random_tensors` draws every tensor the model's parts need: matrices from
-N(0, std), vectors (norm scales) as 1 + N(0, vector_std). Each tensor has its
-own generator seeded from (seed, tensor name), so a tensor's values do not
-depend on which other tensors exist. `write_random_model` writes a model
-folder (config.json, model.safetensors) that loads like any other.
+`random_tensors` draws every tensor the model's parts need: matrices as std *
+noise, vectors (norm scales) as 1 + vector_std * noise, the noise close to N(0, 1).
+A value is a function of (seed, hash of the tensor's name, element index) alone (a
+counter-based generator, csrc/random_values.h), computed by the host core for CPU
+tensors and by a kernel for device tensors with identical bits: a tensor does not
+depend on which other tensors exist, and a model drawn on the device for a
+measurement is the model that `write_random_model` writes for the same
+configuration and seed. `write_random_model` writes a model folder (config.json,
+model.safetensors) that loads like any other.
 
 The reference has random weights only inside its tests
 (pulsarlm-core/tests/model/test_llama.cpp:47-79).
@@ -23,9 +27,28 @@ from ..parts.spec import TensorNeed
 from .safetensors_io import write_safetensors
 
 
-def _tensor_seed(seed: int, name: str) -> int:
-    digest = hashlib.sha256(f"{seed}:{name}".encode("utf-8")).digest()
-    return int.from_bytes(digest[:8], "little") & 0x7FFFFFFFFFFFFFFF
+def tensor_hash(name: str) -> int:
+    """64 bits of the tensor's name: its stream among the seed's."""
+    return int.from_bytes(hashlib.sha256(name.encode("utf-8")).digest()[:8], "little")
+
+
+def fill_random(out: torch.Tensor, seed: int, name: str, scale: float, offset: float = 0.0) -> torch.Tensor:
+    """out (float32 or bfloat16, contiguous) = offset + scale * noise(seed, name, index), in
+    place; on the CPU by the host core, on a CUDA device by the kernel library."""
+    if out.dtype not in (torch.float32, torch.bfloat16) or not out.is_contiguous():
+        raise ValueError("fill_random takes contiguous float32 or bfloat16 tensors")
+    code = 0 if out.dtype == torch.float32 else 1
+    seed = int(seed) & 0xFFFFFFFFFFFFFFFF
+    if out.is_cuda:
+        from ..kernels import ops
+
+        ops.fill_random(out, seed, tensor_hash(name), scale, offset)
+    else:
+        from ..host import core
+
+        if core.library().plh_fill_random(out.data_ptr(), out.numel(), code, seed, tensor_hash(name), scale, offset):
+            raise ValueError("fill_random: the host core refused the arguments")
+    return out
 
 
 def random_tensors(
@@ -36,19 +59,18 @@ def random_tensors(
     std: float = 0.02,
     vector_std: float = 0.02,
 ) -> Iterator[tuple[str, torch.Tensor]]:
-    """(name, tensor) for every non-optional need, drawn on `device`."""
+    """(name, tensor) for every non-optional need, drawn on `device`. Values are made in
+    float32 and rounded once to `dtype`."""
     device = torch.device(device)
     for name, need in needs.items():
         if need.optional:
             continue
-        gen = torch.Generator(device=device)
-        gen.manual_seed(_tensor_seed(seed, name))
-        t = torch.randn(need.shape, generator=gen, device=device, dtype=torch.float32)
+        t = torch.empty(need.shape, dtype=dtype, device=device)
         if need.role == "vector":
-            t = 1.0 + vector_std * t
+            fill_random(t, seed, name, vector_std, 1.0)
         else:
-            t = std * t
-        yield name, t.to(dtype)
+            fill_random(t, seed, name, std)
+        yield name, t
 
 
 def write_random_model(

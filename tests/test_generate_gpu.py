@@ -204,3 +204,35 @@ def test_a_folder_that_does_not_fit_fails_with_one_clear_error(tmp_path):
     with pytest.raises(WeightsError) as error:
         Engine(str(tmp_path), dtype="bfloat16", n_pages=4)
     assert "down_proj" in str(error.value) and "extra.weight" in str(error.value)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_random_weights_are_the_same_bits_on_the_host_and_on_the_device(dtype):
+    """A model drawn on the device for a measurement is the model that a random model
+    folder holds for the same configuration and seed."""
+    from pulsarlm_b200.weights.random_init import fill_random
+
+    for name, n, scale, offset in (("a.weight", 1000003, 0.02, 0.0), ("norm", 4097, 0.02, 1.0), ("b", 1, 3.0, 0.0)):
+        host = fill_random(torch.empty(n, dtype=dtype), 11, name, scale, offset)
+        device = fill_random(torch.empty(n, dtype=dtype, device="cuda:0"), 11, name, scale, offset)
+        assert torch.equal(host, device.cpu()), name
+
+
+def test_a_model_drawn_on_the_device_matches_the_plain_implementation_of_its_folder(tmp_path):
+    """Engine(config, seed) draws weights on the device; write_random_model writes the same
+    weights to a folder on the CPU; the plain implementation run on the folder's tensors
+    predicts the engine's logits."""
+    from harness import assert_matches_plain  # noqa: F401  (the harness' bar)
+    from pulsarlm_b200 import Engine, SamplingParams
+    from pulsarlm_b200.weights.random_init import write_random_model
+    from pulsarlm_b200.weights.safetensors_io import SafetensorsFile
+
+    folder = write_random_model(str(tmp_path / "m"), tiny.TINY_B, seed=9, dtype=torch.float32)
+    file = SafetensorsFile(folder + "/model.safetensors")
+    weights = {name: file.tensor(name).clone() for name in file.names()}
+    file.close()
+    engine = Engine(tiny.TINY_B, dtype="float32", device="cuda:0", n_pages=32, page_size=tiny.PAGE_B, max_requests=2,
+                    seed=9)
+    prompt = tiny.random_tokens(tiny.TINY_B, 23, seed=2)
+    got = engine.generate([prompt], SamplingParams(temperature=0.0), max_tokens=5, ignore_eos=True)[0]
+    assert got == plain_llama.greedy_generate(tiny.TINY_B, weights, prompt, 5)

@@ -390,7 +390,7 @@ def test_attention_decode_over_a_work_list(ops, nh, nkv, hd, page, target, windo
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     scale = 1 / math.sqrt(hd)
     items, slots = decode_work_items(lengths, window, target, pad_to=target + len(lengths) + 3,
-                                     stride=5 if target == 40 else None, min_tiles=2 if target == 500 else 32)
+                                     min_tiles=2 if target == 500 else 32)
     real = items[items[:, 2] > 0]
     assert len(lengths) <= len(real) <= target + len(lengths)
     assert window is not None or (target == 1) == (len(real) == len(lengths))

@@ -123,3 +123,23 @@ def test_sharded_folder(tmp_path):
     assert len(model_files(str(tmp_path))) == 2
     loaded = load_checked(str(tmp_path), needs_of(cfg), torch.float32, CPU)
     assert all(torch.equal(loaded[n], w[n]) for n in w)
+
+
+def test_random_values_are_a_function_of_seed_name_and_index():
+    """The counter-based generator: a tensor's values do not depend on its length, on
+    other tensors or on the order of drawing; noise is centred with unit variance; the
+    bfloat16 form is the float32 form rounded once."""
+    from pulsarlm_b200.weights.random_init import fill_random
+
+    a = fill_random(torch.empty(200000), 7, "layers.0.w", 0.02)
+    assert torch.equal(a[:1000], fill_random(torch.empty(1000), 7, "layers.0.w", 0.02))
+    assert not torch.equal(a[:1000], fill_random(torch.empty(1000), 8, "layers.0.w", 0.02))
+    other = fill_random(torch.empty(200000), 7, "layers.1.w", 0.02)
+    assert abs(float(torch.corrcoef(torch.stack([a, other]))[0, 1])) < 0.01
+    assert abs(float(a.mean())) < 2e-4 and abs(float(a.std()) - 0.02) < 2e-4
+    assert 2.7 < float(((a / 0.02) ** 4).mean()) < 3.1          # close to a normal's 3
+    assert float(a.abs().max()) < 0.02 * 4.9                     # sum of eight uniforms: bounded
+    half = fill_random(torch.empty(1000, dtype=torch.bfloat16), 7, "layers.0.w", 0.02)
+    assert torch.equal(half, a[:1000].to(torch.bfloat16))
+    scale = fill_random(torch.empty(4096), 7, "norm", 0.02, 1.0)
+    assert abs(float(scale.mean()) - 1.0) < 2e-3 and abs(float(scale.std()) - 0.02) < 2e-3
