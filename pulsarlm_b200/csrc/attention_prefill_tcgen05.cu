@@ -69,6 +69,28 @@ struct TcPrefillParams {
     int n_splits;     // > 1: partial results go to scratch [token][head][split]
     float* part_o;    // ... [head_dim]: unnormalised output
     float2* part_ml;  // ... (base of the exponents (log2), sum)
+    // Attention mass (optional, two heads or halves per CTA only): every softmax warp adds
+    // up, over its 32 query rows, weight[row] * (the row's largest scaled score among the
+    // keys of a page it attends), and stores the sum at mass_part[((tile * heads + head) * 8
+    // + warp slot) * mass_pages + page of the request]; a second kernel folds the sums into
+    // the step's per-page accumulators in a fixed order.
+    const float* query_weights;  // [tokens]
+    float* mass_part;            // zero before the launch
+    int mass_pages;
+    float scale;
+};
+
+// What pl_attention_prefill_tcgen05 needs to measure attention mass: the rows' weights,
+// zeroed scratch of n_tiles * n_heads * 8 * pages floats (pages >= the block table's
+// width), the number of rows of the block table, and the step's sums step_mass [n_pages, n_heads] and step_weight [n_pages],
+// which the call adds to.
+struct PlPrefillMass {
+    const float* query_weights;
+    float* scratch;
+    int pages;
+    int table_rows;  // rows of the block table (requests of the step)
+    float* step_mass;
+    float* step_weight;
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -424,6 +446,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const int first = p.window > 0 ? pos - p.window + 1 : 0;
         float m = -INFINITY, l = 0.0f;  // m: the base of the exponents in use (lags the true maximum)
         bool ok = true;
+        const float mass_weight = p.mass_part != nullptr && rr < n_rows ? p.query_weights[row0 + rr] : 0.0f;
         if constexpr (kTurns) {
             // This thread's row of Q into tensor memory, where the first product reads its A
             // operand: lane = row, column c = dims 2c and 2c + 1 (rows past the tile: zeros).
@@ -489,6 +512,41 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 for (int c = 0; c < kMyKeys; ++c) {
                     const int key = key0 + c;
                     s[c] = (key <= pos && key >= first) ? s[c] : -INFINITY;
+                }
+            }
+            if constexpr (kMyKeys == kKeys) {
+                if (p.mass_part != nullptr) {
+                    // Largest raw product per 16 keys, then per page (16, 32 or 64 keys: a page lies
+                    // within the tile), weighed and added up over the warp's rows.
+                    float m16[4];
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        float best = s[16 * q4];
+#pragma unroll
+                        for (int c = 1; c < 16; ++c) {
+                            best = fmaxf(best, s[16 * q4 + c]);
+                        }
+                        m16[q4] = best;
+                    }
+                    const int per_page = p.page_size / 16;  // 1, 2 or 4 of those
+                    float* dst = p.mass_part +
+                        ((static_cast<int64_t>(blockIdx.y) * p.n_heads + head) * 8 + (WIDE ? hs * 4 : 0) + lane_group) *
+                            p.mass_pages;
+                    for (int q4 = 0; q4 < 4; q4 += per_page) {
+                        float best = m16[q4];
+                        for (int i = 1; i < per_page; ++i) {
+                            best = fmaxf(best, m16[q4 + i]);
+                        }
+                        float part_sum = best > -INFINITY ? mass_weight * (best * p.scale) : 0.0f;
+#pragma unroll
+                        for (int offset = 16; offset > 0; offset >>= 1) {
+                            part_sum += __shfl_xor_sync(0xffffffffu, part_sum, offset);
+                        }
+                        const int page_of_request = (key0 + 16 * q4) / p.page_size;
+                        if (lane == 0 && page_of_request < p.mass_pages) {
+                            dst[page_of_request] = part_sum;
+                        }
+                    }
                 }
             }
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -709,6 +767,59 @@ __global__ void __launch_bounds__(256) attention_prefill_merge_kernel(const TcPr
     }
 }
 
+// Folds the partial sums of a measuring launch into the step's accumulators. Block
+// (pages of a request in chunks, block-table row e); a thread owns one (page of request e,
+// head): it adds, tile after tile of e in list order, the tile's eight warp sums (in slot
+// order) for that page to step_mass[physical page, head], and (head 0) the weights of the
+// tile's rows that attend the page to step_weight[physical page]. A page belongs to one
+// request, so no two threads write one element, and the order of additions is fixed.
+__global__ void attention_mass_fold_prefill_kernel(const TcPrefillParams p, int n_tiles, int tile_rows,
+                                                   float* __restrict__ step_mass, float* __restrict__ step_weight) {
+    const int e = blockIdx.y;
+    const int32_t* row = p.table + static_cast<int64_t>(e) * p.table_width;
+    const int pages = min(p.mass_pages, p.table_width);
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < pages * p.n_heads; idx += gridDim.x * blockDim.x) {
+        const int j = idx / p.n_heads, h = idx % p.n_heads;
+        const int page = row[j];
+        if (page < 0 || page >= p.n_pages) {
+            continue;
+        }
+        const int key_lo = j * p.page_size, key_hi = key_lo + p.page_size - 1;
+        float mass = 0.0f, weight = 0.0f;
+        bool any = false;
+        for (int ti = 0; ti < n_tiles; ++ti) {
+            const int4 tile = p.tiles[ti];
+            const int n_rows = min(tile.y, tile_rows);
+            if (tile.w != e || key_lo > tile.z + n_rows - 1) {
+                continue;
+            }
+            if (p.window > 0 && key_hi < tile.z - p.window + 1) {
+                continue;  // behind every row's window
+            }
+            any = true;
+            const float* part = p.mass_part + (static_cast<int64_t>(ti) * p.n_heads + h) * 8 * p.mass_pages + j;
+#pragma unroll
+            for (int slot = 0; slot < 8; ++slot) {
+                mass += part[static_cast<int64_t>(slot) * p.mass_pages];
+            }
+            if (h == 0) {
+                for (int r = 0; r < n_rows; ++r) {
+                    const int pos = tile.z + r;
+                    if (key_lo <= pos && (p.window <= 0 || key_hi >= pos - p.window + 1)) {
+                        weight += p.query_weights[tile.x + r];
+                    }
+                }
+            }
+        }
+        if (any) {
+            step_mass[static_cast<int64_t>(page) * p.n_heads + h] += mass;
+            if (h == 0) {
+                step_weight[page] += weight;
+            }
+        }
+    }
+}
+
 template <int HD, int HEADS, bool WIDE>
 int launch_tc_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcPrefillParams& p,
                       int n_tiles, int n_heads, cudaStream_t stream) {
@@ -759,13 +870,14 @@ PL_API int64_t pl_attention_prefill_scratch_floats(int n_tokens, int n_heads, in
 // tile's keys are shared out over that many CTAs and merged by a second kernel
 // through `scratch` (pl_attention_prefill_scratch_floats floats, 16-byte aligned).
 // `wide` (odd groups only; ignored for even ones): the tiles have up to 256 rows
-// (pl_attention_prefill_tcgen05_tile_rows), else up to 128.
+// (pl_attention_prefill_tcgen05_tile_rows), else up to 128. `mass` (optional): also
+// measures attention mass (see PlPrefillMass).
 PL_API int pl_attention_prefill_tcgen05(const void* q, int64_t q_row_stride, int n_tokens, const void* k_pool,
                                         const void* v_pool, int64_t page_stride, int64_t head_stride, int page_size,
                                         int n_pages, const int32_t* table, int table_width, const int32_t* tiles,
                                         int n_tiles, void* out, int64_t out_row_stride, int n_heads, int n_kv_heads,
                                         int head_dim, int window, float scale, int n_splits, float* scratch,
-                                        int wide, int32_t* status, cudaStream_t stream) {
+                                        int wide, const PlPrefillMass* mass, int32_t* status, cudaStream_t stream) {
     PL_REQUIRE(n_tiles >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_tokens > 0,
                "attention_prefill_tcgen05: bad sizes tiles=%d heads=%d kv_heads=%d tokens=%d", n_tiles, n_heads,
                n_kv_heads, n_tokens);
@@ -827,12 +939,44 @@ PL_API int pl_attention_prefill_tcgen05(const void* q, int64_t q_row_stride, int
     // a tile of up to 256 rows as two halves (`wide`), or of up to 128 rows with both
     // warpgroups on it.
     const bool pairs = p.group % 2 == 0;
+    p.query_weights = nullptr;
+    p.mass_part = nullptr;
+    p.mass_pages = 0;
+    p.scale = scale;
+    if (mass != nullptr) {
+        PL_REQUIRE(pairs || wide, "attention_prefill_tcgen05: attention mass is measured with two heads or two halves "
+                                  "of a tile per CTA (an even group, or wide tiles)");
+        PL_REQUIRE(page_size == 16 || page_size == 32 || page_size == 64,
+                   "attention_prefill_tcgen05: attention mass is measured for pages of 16, 32 or 64 tokens, not %d",
+                   page_size);
+        PL_REQUIRE(mass->query_weights != nullptr && mass->scratch != nullptr && mass->step_mass != nullptr &&
+                       mass->step_weight != nullptr && mass->pages >= table_width && mass->table_rows >= 1 &&
+                       mass->table_rows <= 65535,
+                   "attention_prefill_tcgen05: attention mass needs weights, scratch for %d pages a row and the "
+                   "step's sums",
+                   table_width);
+        p.query_weights = mass->query_weights;
+        p.mass_part = mass->scratch;
+        p.mass_pages = mass->pages;
+    }
+    int code;
     if (head_dim == 64) {
-        return pairs ? launch_tc_prefill<64, 2, false>(mq, mk, mv, p, n_tiles, n_heads, stream)
+        code = pairs ? launch_tc_prefill<64, 2, false>(mq, mk, mv, p, n_tiles, n_heads, stream)
             : wide   ? launch_tc_prefill<64, 2, true>(mq, mk, mv, p, n_tiles, n_heads, stream)
                      : launch_tc_prefill<64, 1, false>(mq, mk, mv, p, n_tiles, n_heads, stream);
+    } else {
+        code = pairs ? launch_tc_prefill<128, 2, false>(mq, mk, mv, p, n_tiles, n_heads, stream)
+            : wide   ? launch_tc_prefill<128, 2, true>(mq, mk, mv, p, n_tiles, n_heads, stream)
+                     : launch_tc_prefill<128, 1, false>(mq, mk, mv, p, n_tiles, n_heads, stream);
     }
-    return pairs ? launch_tc_prefill<128, 2, false>(mq, mk, mv, p, n_tiles, n_heads, stream)
-        : wide   ? launch_tc_prefill<128, 2, true>(mq, mk, mv, p, n_tiles, n_heads, stream)
-                 : launch_tc_prefill<128, 1, false>(mq, mk, mv, p, n_tiles, n_heads, stream);
+    if (code != 0 || mass == nullptr) {
+        return code;
+    }
+    // Every block-table row may own tiles; rows without any find nothing to add.
+    const int items = table_width * n_heads;
+    const int blocks = (items + 255) / 256 > 32 ? 32 : (items + 255) / 256;
+    attention_mass_fold_prefill_kernel<<<dim3(blocks, mass->table_rows), 256, 0, stream>>>(
+        p, n_tiles, (!pairs && wide) ? 2 * kRows : kRows, mass->step_mass, mass->step_weight);
+    PL_CHECK_LAUNCH("attention_mass_fold_prefill");
+    return 0;
 }

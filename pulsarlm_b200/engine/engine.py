@@ -50,9 +50,9 @@ class Engine:
         weights from `seed`). kv_cache_gib sizes the page pools unless n_pages
         gives the number of pages outright. stop_ids default to config.json's
         eos_token_id. attention_mass_decay: measure per-page attention mass with this
-        decay (see CacheManager). Captured decode steps measure inside the tensor-core
-        kernel; prompt portions and eager steps then attend on the CUDA-core kernel,
-        which is slower.
+        decay (see CacheManager). The tensor-core kernels measure it themselves (captured
+        decode steps, and prompt portions at pages of 16 to 64 tokens); single tokens of
+        eager steps and shapes those kernels do not take attend on the CUDA-core kernel.
         lookahead: pipeline decode steps one deep (see step()). record_logits: keep, for
         every generated token, the fp32 logits row it was drawn from in
         `request.logits` (host tensors; for inspection and tests, it costs a copy of

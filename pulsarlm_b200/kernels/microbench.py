@@ -288,10 +288,10 @@ def main() -> None:
                         args.shape)
     elif args.what == "attention_prefill":
         bench_attention_prefill(args.tokens, args.heads, args.kv_heads, args.head_dim, args.page_size, args.prior,
-                                args.splits, args.shortest, args.items_per_slot)
+                                args.splits)
     else:
-        bench_attention_decode(args.batch, args.context or [2048, 4096], args.heads, args.kv_heads, args.head_dim, args.page_size,
-                               args.splits, args.shortest, args.items_per_slot)
+        bench_attention_decode(args.batch, args.context or [2048, 4096], args.heads, args.kv_heads, args.head_dim,
+                               args.page_size, args.splits, args.shortest, args.items_per_slot)
 
 
 if __name__ == "__main__":

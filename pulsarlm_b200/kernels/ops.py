@@ -25,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 16
+ABI_VERSION = 17
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -58,7 +58,7 @@ _SIGNATURES = {
                              _I32, _I32, _I32, _I32, _F32, _PTR, _PTR],
     "pl_attention_prefill_supports": [_I32, _I32, _I32],
     "pl_attention_prefill_tcgen05": [_PTR, _I64, _I32, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _I32,
-                                     _PTR, _I64, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _I32, _PTR, _PTR],
+                                     _PTR, _I64, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _I32, _PTR, _PTR, _PTR],
     "pl_attention_prefill_tcgen05_tile_rows": [_I32],
     "pl_attention_prefill_tcgen05_supports": [_I32, _I32, _I32, _I64, _I64, _I64, _I32],
     "pl_attention_prefill_tile_rows": [],
@@ -536,15 +536,44 @@ def attention_prefill_tcgen05_tile_rows(group: int) -> int:
     return int(library().pl_attention_prefill_tcgen05_tile_rows(group))
 
 
+class _PrefillMass(ctypes.Structure):
+    _fields_ = [("query_weights", _PTR), ("scratch", _PTR), ("pages", _I32), ("table_rows", _I32),
+                ("step_mass", _PTR), ("step_weight", _PTR)]
+
+
+def attention_prefill_tcgen05_measures_mass(group: int, page_size: int, wide: bool) -> bool:
+    """Whether attention_prefill_tcgen05 can measure attention mass for this shape: two
+    heads (an even group) or two halves of a wide tile per CTA, pages of 16, 32 or 64."""
+    return (group % 2 == 0 or wide) and page_size in (16, 32, 64)
+
+
 def attention_prefill_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,
                               tiles: torch.Tensor, out: torch.Tensor, page_size: int, window: int | None,
                               scale: float, status: torch.Tensor | None = None, n_splits: int = 1,
-                              scratch: torch.Tensor | None = None, wide: bool = False) -> None:
+                              scratch: torch.Tensor | None = None, wide: bool = False,
+                              mass: tuple | None = None) -> None:
     """As attention_prefill, on the tcgen05 tensor cores. With n_splits > 1 every tile's
     keys are shared out over that many CTAs and merged through `scratch` (float32,
     attention_prefill_scratch_floats elements): for few tiles over many keys. `wide`: the
-    tiles have up to attention_prefill_tcgen05_tile_rows(group) rows instead of 128."""
+    tiles have up to attention_prefill_tcgen05_tile_rows(group) rows instead of 128.
+    `mass` = (query_weights fp32 [T], step_mass fp32 [pages, nh], step_weight fp32
+    [pages]): also adds to the step's attention mass: per page and head the sum over the
+    query rows of weight * (the row's largest scaled score among the page's keys it
+    attends), and per page the sum of the weights of the rows that attend it; the rows'
+    sums are added in a fixed order (see attention_prefill_tcgen05_measures_mass)."""
     _dev(q, k_pool, v_pool, table, tiles, out, status, scratch)
+    mass_arg = None
+    if mass is not None:
+        query_weights, step_mass, step_weight = mass
+        _dev(query_weights, step_mass, step_weight)
+        assert query_weights.dtype == torch.float32 and query_weights.numel() >= q.shape[0]
+        assert query_weights.is_contiguous() and step_mass.is_contiguous() and step_weight.is_contiguous()
+        assert step_mass.dtype == torch.float32 and step_mass.shape == (k_pool.shape[0], q.shape[1])
+        assert step_weight.dtype == torch.float32 and step_weight.shape == (k_pool.shape[0],)
+        pages = table.shape[1]
+        mass_scratch = torch.zeros(tiles.shape[0] * q.shape[1] * 8 * pages, dtype=torch.float32, device=q.device)
+        mass_arg = ctypes.byref(_PrefillMass(_p(query_weights), _p(mass_scratch), pages, table.shape[0],
+                                             _p(step_mass), _p(step_weight)))
     if n_splits > 1:
         need = attention_prefill_scratch_floats(q.shape[0], q.shape[1], q.shape[2], n_splits)
         assert scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= need
@@ -560,7 +589,7 @@ def attention_prefill_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
     _call("pl_attention_prefill_tcgen05", _p(q), q.stride(0), tokens, _p(k_pool), _p(v_pool), k_pool.stride(0),
           k_pool.stride(1), page_size, n_pages, _p(table), table.shape[1], _p(tiles), tiles.shape[0], _p(out),
           out.stride(0), n_heads, n_kv, head_dim, int(window or 0), float(scale), int(n_splits), _p(scratch),
-          int(wide), _p(status), _stream())
+          int(wide), mass_arg, _p(status), _stream())
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor | None,

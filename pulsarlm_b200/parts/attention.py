@@ -417,10 +417,28 @@ class Attention(Part):
                                  mass=(tile_max, cache.mass_total, cache.weight_total, cache.mass_decay))
             return
         if measuring and batch.extras.get("query_weights") is not None:
-            # Measuring attention mass: the CUDA-core kernel writes it beside the output.
-            ops.attention_simt(q, cache.k_pool, cache.v_pool, table, batch.pos, batch.entry, out, cache.page_size,
-                               self.window, self.scale, batch.status, cache.mass_sum, cache.weight_sum,
-                               batch.extras["query_weights"])
+            # Measuring attention mass in an eager step. Prompt portions: the tcgen05 kernel adds up
+            # its rows' sums itself where it takes the shape; single tokens, and every shape it
+            # does not take: the CUDA-core kernel, which writes mass beside its output.
+            weights = batch.extras["query_weights"]
+            plan = batch.plans.get(self.plan_key()) or {}
+            n_single = min(int(batch.n_decode), tokens)
+            group = self.n_heads // self.n_kv
+            wide = group % 2 == 1 and plan.get("tiles_wide") is not None
+            tiles = plan.get("tiles_wide") if wide else plan.get("tiles")
+            fast = (not self.softcap and tiles is not None and n_single < tokens and self._kernels(q.dtype)[1]
+                    and ops.attention_prefill_tcgen05_measures_mass(group, cache.page_size, wide)
+                    and ops.attention_prefill_tcgen05_supports(q, cache.k_pool, cache.page_size))
+            n_simt = n_single if fast else tokens
+            if n_simt > 0:
+                ops.attention_simt(q[:n_simt], cache.k_pool, cache.v_pool, table, batch.pos[:n_simt],
+                                   batch.entry[:n_simt], out[:n_simt], cache.page_size, self.window, self.scale,
+                                   batch.status, cache.mass_sum, cache.weight_sum, weights[:n_simt],
+                                   softcap=self.softcap)
+            if fast:
+                ops.attention_prefill_tcgen05(q, cache.k_pool, cache.v_pool, table, tiles, out, cache.page_size,
+                                              self.window, self.scale, batch.status, 1, None, wide,
+                                              mass=(weights, cache.mass_sum, cache.weight_sum))
             return
         if self.softcap:
             ops.attention_simt(q, cache.k_pool, cache.v_pool, table, batch.pos, batch.entry, out, cache.page_size,

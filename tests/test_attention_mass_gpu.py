@@ -126,3 +126,68 @@ def test_attention_mass_from_captured_decode_steps(head_dim, n_heads, n_kv, page
             worst = max(worst, err)
             assert err < 2e-2, (r, layer, err)
     record_error("bfloat16", f"attention mass from captured decode steps, head size {head_dim}", worst, 2e-2)
+
+
+@pytest.mark.parametrize("head_dim,n_heads,n_kv,page", [(128, 4, 1, 16), (64, 8, 2, 32), (128, 3, 3, 64),
+                                                         (64, 4, 2, 16)])
+def test_attention_mass_from_prompt_portions_on_the_tensor_cores(head_dim, n_heads, n_kv, page, monkeypatch):
+    """bfloat16 at the tensor-core head sizes, eager steps: prompt portions go through the
+    tcgen05 kernel, whose softmax warps add up weight * (largest score in the page) over
+    their rows, and a fold kernel adds the warps' sums in a fixed order; single tokens beside
+    them go through the CUDA-core kernel. Portions that end inside a page and inside a
+    64-key tile, two requests in one step, one request's pages taken over by another, an
+    odd group (tiles of 256 rows in two halves). Against the plain definition over dense
+    scores; the same steps twice give the same bits."""
+    from harness import record_error
+    from pulsarlm_b200.cache.manager import CacheManager
+    from pulsarlm_b200.engine.runner import ModelRunner, StepEntry
+    from pulsarlm_b200.kernels import ops
+    from test_schedules_gpu import load, small_config
+
+    cfg = small_config(head_dim, n_heads, n_kv, layers=2)
+    weights = tiny.random_weights(cfg, 17, torch.bfloat16)
+    model = load(cfg, weights, "bfloat16")
+    decay = 0.05
+    measured = []
+    real = ops.attention_prefill_tcgen05
+
+    def spy(*args, **kwargs):
+        measured.append(kwargs.get("mass") is not None)
+        return real(*args, **kwargs)
+
+    monkeypatch.setattr(ops, "attention_prefill_tcgen05", spy)
+    a = tiny.random_tokens(cfg, 470, seed=1)
+    b = tiny.random_tokens(cfg, 150, seed=2)
+    old = tiny.random_tokens(cfg, 200, seed=3)
+    portions_a = [(0, 300), (300, 302), (302, 303), (303, 470)]
+
+    def run():
+        cache = CacheManager(model.cache_needs(), page, -(-470 // page) + -(-200 // page) + 2, 3, torch.bfloat16,
+                             "cuda:0", mass_decay=decay)
+        runner = ModelRunner(model, cache)
+        runner.step([StepEntry("old", old, [])])
+        runner.step([StepEntry("a", a[0:300], [])])
+        runner.end("old")  # its pages, with its sums on them, go to b and to the rest of a
+        runner.step([StepEntry("b", b[0:150], []), StepEntry("a", a[300:302], [])])
+        runner.step([StepEntry("a", a[302:303], []), StepEntry("b", b[150:], [])] if len(b) > 150 else
+                    [StepEntry("a", a[302:303], [])])
+        runner.step([StepEntry("a", a[303:470], [])])
+        runner.check_status()
+        return cache.page_mass("a"), cache.page_mass("b")
+
+    (mass_a, weight_a), (mass_b, weight_b) = run()
+    assert any(measured), "no prompt portion was measured by the tcgen05 kernel"
+    worst = 0.0
+    for tokens, portions, got_mass, got_weight in ((a, portions_a, mass_a, weight_a), (b, [(0, 150)], mass_b, weight_b)):
+        scores: list = []
+        plain_llama.forward(cfg, weights, tokens, scores_out=scores)
+        for layer in range(cfg["num_hidden_layers"]):
+            want_mass, want_weight = plain_llama.page_attention_mass(scores[layer], portions, page, decay)
+            assert torch.allclose(got_weight[layer].double().cpu(), want_weight, rtol=1e-4, atol=1e-7), layer
+            err = float((got_mass[layer].double().cpu() - want_mass).abs().max() / want_mass.abs().max())
+            worst = max(worst, err)
+            assert err < 2e-2, (layer, err)
+    record_error("bfloat16", f"attention mass from tcgen05 prompt portions, head size {head_dim}, page {page}", worst,
+                 2e-2)
+    (again_a, again_wa), _ = run()
+    assert torch.equal(again_a, mass_a) and torch.equal(again_wa, weight_a)
