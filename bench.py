@@ -289,7 +289,7 @@ def serve(engine, cfg: dict, prompts: list, max_new: int, pk: dict) -> dict:
 
 
 def run_serving(name: str, cfg: dict, lengths: list, max_new: int, pk: dict, tight: bool) -> dict:
-    """Builds the model, serves a short warm-up pass over the same prompts (library set-up,
+    """Builds the model, serves a warm-up pass over the same prompts (library set-up,
     the decode steps' captures), then the timed pass; with `tight`, once more with a third
     of the pages, so that the scheduler has to preempt and recompute."""
     import gc
@@ -303,7 +303,9 @@ def run_serving(name: str, cfg: dict, lengths: list, max_new: int, pk: dict, tig
     need_pages = sum(-(-(n + max_new + 2) // PAGE_SIZE) for n in lengths)
     engine = Engine(cfg, dtype="bfloat16", device="cuda:0", n_pages=need_pages + 64, page_size=PAGE_SIZE,
                     prefill_tokens_per_step=512, max_requests=len(lengths), seed=0)
-    serve(engine, cfg, prompts, min(32, max_new), pk)
+    # The warm-up pass is the whole workload once: every shape of decode step that the timed
+    # pass meets has then been captured, as in an engine that has been serving for a while.
+    serve(engine, cfg, prompts, max_new, pk)
     result = serve(engine, cfg, prompts, max_new, pk)
     result["model"] = describe(cfg)
     result["prefill_tokens_per_step"] = 512

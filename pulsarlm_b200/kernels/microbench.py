@@ -57,19 +57,21 @@ def bench_gemm(shapes) -> None:
         out = torch.empty(t, n, device="cuda", dtype=torch.bfloat16)
         turn = [0]
 
-        def own():
-            ops.gemm_bf16(x, weights[turn[0] % copies], out)
-            turn[0] += 1
+        def own(kernel):
+            def run():
+                ops.gemm_bf16(x, weights[turn[0] % copies], out, kernel=kernel)
+                turn[0] += 1
+            return run
 
         def library():
             torch.mm(x, weights[turn[0] % copies].t(), out=out)
             turn[0] += 1
 
         gb, tf = n * k * 2 / 1e9, 2.0 * t * n * k / 1e12
-        a, b = graph_time_us(own), graph_time_us(library)
-        name = "skinny" if t <= ops.GEMM_SKINNY_MAX_TOKENS else "pair"
-        line = (f"gemm t={t} n={n} k={k}: {name} {a:.1f} us ({gb / a * 1e6:.0f} GB/s, {tf / a * 1e6:.0f} TFLOP/s)"
-                f" | library {b:.1f} us ({gb / b * 1e6:.0f} GB/s, {tf / b * 1e6:.0f} TFLOP/s)")
+        line = f"gemm t={t} n={n} k={k}:"
+        for name in (["skinny"] if t <= ops.GEMM_SKINNY_MAX_TOKENS else []) + ["pair", "library"]:
+            us = graph_time_us(library if name == "library" else own(name))
+            line += f" | {name} {us:.1f} us ({gb / us * 1e6:.0f} GB/s, {tf / us * 1e6:.0f} TFLOP/s)"
         print(line, flush=True)
 
 

@@ -7,19 +7,22 @@ accumulation, by one of three routes chosen by $PULSARLM_B200_GEMM:
 * "mixed" (the default): the own tcgen05/TMEM kernels where they measured faster than
   the library, the library elsewhere. Up to 16 tokens (decode steps of small
   batches) csrc/gemm_skinny.cu, which overlaps its set-up and first weight loads
-  with the kernel before it; products of at least four 256 x 256 tiles per pair of
-  SMs (a prompt portion's gate/up projection, every projection of long portions)
-  csrc/gemm_pair.cu, which runs a tile on two SMs (`cta_group::2`); in between a
-  library matrix product (cuBLAS through torch), as the reference's engine does for
-  every projection (`at::linear`, pulsarlm-core/src/engine/model/llama.cpp:67-69,
-  81, 91, 93);
+  with the kernel before it, and up to 64 tokens too where the weights are large
+  (200 MB and more: a batch-64 step's gate/up projection and head, whose time is the
+  weights' stream); products of at least four 256 x 256 tiles per pair of SMs with
+  most of a 256-token tile filled (a prompt portion's gate/up projection, every
+  projection of long portions) csrc/gemm_pair.cu, which runs a tile on two SMs
+  (`cta_group::2`); in between a library matrix product (cuBLAS through torch), as
+  the reference's engine does for every projection (`at::linear`,
+  pulsarlm-core/src/engine/model/llama.cpp:67-69, 81, 91, 93);
 * "tcgen05": the own kernels at every size they take (rows starting on 16 bytes):
   csrc/gemm_skinny.cu up to 64 tokens, csrc/gemm_pair.cu above; the library
   elsewhere;
 * "library": the library everywhere.
 
-The default is whichever measured faster on the Llama-3.1-8B shapes
-(`python -m pulsarlm_b200.kernels.microbench gemm` times both).
+The default is whichever measured faster on the projection shapes of Llama-3.2-1B,
+Llama-3.1-8B and Llama-2-13B at 8 to 512 tokens
+(`python -m pulsarlm_b200.kernels.microbench gemm --shapes T,N,K ...` times all three).
 """
 
 from __future__ import annotations
@@ -32,7 +35,10 @@ from ..kernels import ops
 
 GEMM_ROUTE = os.environ.get("PULSARLM_B200_GEMM", "mixed")
 MIXED_MAX_TOKENS = 16  # the skinny kernel is ahead of the library up to here,
-MIXED_MIN_TILES_PER_PAIR = 4  # and the pair kernel from this many 256 x 256 tiles per pair of SMs
+MIXED_MAX_TOKENS_LARGE = 64  # and up to here where the weights are at least
+MIXED_LARGE_BYTES = 200e6  # this large;
+MIXED_MIN_TILES_PER_PAIR = 4  # the pair kernel from this many 256 x 256 tiles per pair of SMs
+MIXED_MIN_TOKENS_PAIR = 192  # with a token tile at least this full (at 128 tokens the library is ahead)
 if GEMM_ROUTE not in ("library", "tcgen05", "mixed"):
     raise ValueError(f"PULSARLM_B200_GEMM must be 'library', 'tcgen05' or 'mixed', got {GEMM_ROUTE!r}")
 
@@ -40,15 +46,19 @@ if GEMM_ROUTE not in ("library", "tcgen05", "mixed"):
 _PAIRS: dict[torch.device, int] = {}
 
 
-def own_kernel_for(tokens: int, n: int, device: torch.device) -> str | None:
+def own_kernel_for(tokens: int, n: int, device: torch.device, k: int = 0) -> str | None:
     """Which of the package's own tcgen05 kernels the route gives a [tokens, n] product
-    to ("skinny", "pair"), or None for the library."""
+    over k to ("skinny", "pair"), or None for the library."""
     if GEMM_ROUTE == "library":
         return None
     if GEMM_ROUTE == "tcgen05":
         return "skinny" if tokens <= ops.GEMM_SKINNY_MAX_TOKENS else "pair"
     if tokens <= MIXED_MAX_TOKENS:
         return "skinny"
+    if tokens <= MIXED_MAX_TOKENS_LARGE:
+        return "skinny" if 2.0 * n * k >= MIXED_LARGE_BYTES else None
+    if tokens < MIXED_MIN_TOKENS_PAIR:
+        return None
     if device not in _PAIRS:
         _PAIRS[device] = torch.cuda.get_device_properties(device).multi_processor_count // 2
     tiles = -(-n // 256) * -(-tokens // 256)
@@ -67,7 +77,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         return out
     if x.dtype == torch.bfloat16:
         k = x.shape[1]
-        kernel = own_kernel_for(tokens, n, x.device)
+        kernel = own_kernel_for(tokens, n, x.device, k)
         if kernel is not None and x.stride(1) == 1 and weight.stride(1) == 1 and ops.gemm_bf16_supports(
                 tokens, n, k, x.stride(0) if tokens > 1 else k, weight.stride(0) if n > 1 else k):
             out = torch.empty((tokens, n), dtype=out_dtype or torch.bfloat16, device=x.device)
@@ -89,7 +99,7 @@ def gated_linear(x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
     tokens, k = x.shape
     inter = gate_up.shape[0] // 2
     act = torch.empty((tokens, inter), dtype=x.dtype, device=x.device)
-    if (x.dtype == torch.bfloat16 == gate_up.dtype and own_kernel_for(tokens, 2 * inter, x.device) == "pair"
+    if (x.dtype == torch.bfloat16 == gate_up.dtype and own_kernel_for(tokens, 2 * inter, x.device, k) == "pair"
             and x.stride(1) == 1 and gate_up.stride(1) == 1
             and ops.gemm_bf16_supports(tokens, inter, k, x.stride(0) if tokens > 1 else k, gate_up.stride(0))):
         ops.gemm_bf16(x, gate_up, act, kernel="pair", gated=True)
