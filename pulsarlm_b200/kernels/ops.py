@@ -25,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 17
+ABI_VERSION = 18
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -52,6 +52,7 @@ _SIGNATURES = {
     "pl_attention_decode_items": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
                                   _I32, _I32, _I32, _I32, _I32, _F32, _PTR, _I32, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR],
     "pl_attention_decode_ctas_per_sm": [_I32],
+    "pl_layer_forward": [_PTR, _PTR, _PTR],
     "pl_fill_random": [_PTR, _I64, _I32, ctypes.c_uint64, ctypes.c_uint64, _F32, _F32, _PTR],
     "pl_attention_decode_supports": [_I32, _I32, _I32, _I32],
     "pl_attention_prefill": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _I32, _PTR, _I64,
@@ -158,6 +159,14 @@ def _call(name: str, *args) -> None:
     code = getattr(library(), name)(*args)
     if code != 0:
         raise KernelError(library().pl_last_error().decode("utf-8", "replace"))
+
+
+def call_native(name: str, *args, launches: int = 1) -> None:
+    """Calls an entry point that takes structs and the stream (the caller has checked what
+    the structs point at); `launches`: how many of the library's kernels it launches."""
+    global _launches
+    _launches += launches - 1
+    _call(name, *args, _stream())
 
 
 def _code(dtype: torch.dtype) -> int:

@@ -298,6 +298,63 @@ class Attention(Part):
             return False
         return self._kernels(self.ctx.dtype)[0]
 
+    def native_choice(self, tokens: int, batch, row_stride: int) -> dict | None:
+        """What `attend` would decide for this step, as plain values, for a caller that
+        launches the kernels itself (the block's native layer call): the number of leading
+        single tokens, whether the position encoding is folded in, the work list or the
+        split count of the decode kernel, the tile list, width and split count of the tcgen05
+        prompt kernel, and the fp32 scratch each needs. None when the step needs anything
+        else (another kernel, mass, a score cap, q/k norms, another layer's cache): the
+        caller then leaves the layer to `forward`. `row_stride`: elements between the tokens'
+        rows of q."""
+        cache = self.cache
+        if cache is None or self.softcap or self.cache_from is not None or self.q_norm is not None \
+                or self.k_norm is not None or cache.mass_sum is not None:
+            return None
+        dtype = self.ctx.dtype
+        decode_kernel, prefill_kernel = self._kernels(dtype)
+        if not decode_kernel:
+            return None
+        plan = batch.plans.get(self.plan_key()) or {}
+        n_decode = min(int(batch.n_decode), tokens)
+        inv_freq, rotary = self.position.table()
+        choice = {"n_decode": n_decode, "fold_rope": self._folds_rope(tokens, batch, inv_freq, rotary), "items": None,
+                  "slots": None, "decode_splits": 1, "decode_scratch": 0, "tiles": None, "wide": False,
+                  "prefill_splits": 1, "prefill_scratch": 0}
+        group = self.n_heads // self.n_kv
+        if n_decode > 0 and plan.get("decode_items") is not None:
+            choice["items"], choice["slots"] = plan["decode_items"], plan["decode_slots"]
+            choice["decode_scratch"] = plan["decode_items"].shape[0] * self.n_heads * (self.head_dim + 2)
+        elif n_decode > 0:
+            max_context = plan.get("max_context") or max(batch.host_context_lens[:n_decode])
+            if self.window:
+                max_context = min(max_context, self.window + 16)
+            splits = decode_splits(n_decode * self.n_kv, max_context, self.ctx.device, self.head_dim, group)
+            choice["decode_splits"] = splits
+            choice["decode_scratch"] = ops.attention_decode_scratch_floats(n_decode, self.n_heads, self.head_dim, splits)
+        if n_decode < tokens:
+            tiles = plan.get("tiles")
+            if not prefill_kernel or tiles is None or n_decode != int(batch.n_decode):
+                return None
+            if self._prefill_tcgen05 is None or not self._prefill_tcgen05:
+                supported = ops.library().pl_attention_prefill_tcgen05_supports(
+                    self.head_dim, cache.page_size, self.n_kv, cache.k_pool.stride(0), cache.k_pool.stride(1),
+                    row_stride, ops.DTYPE_CODE.get(dtype, -1))
+                if not supported:
+                    return None
+            wide = group % 2 == 1 and plan.get("tiles_wide") is not None
+            if wide:
+                tiles = plan["tiles_wide"]
+            ctas = tiles.shape[0] * (self.n_heads if wide or group % 2 else self.n_heads // 2)
+            max_keys = int(plan.get("max_keys") or 0)
+            if self.window:
+                max_keys = min(max_keys, self.window + ops.attention_prefill_tile_rows())
+            splits = prefill_splits(ctas, max_keys, tokens - n_decode, self.n_heads, self.head_dim, self.ctx.device)
+            choice.update(tiles=tiles, wide=wide, prefill_splits=splits,
+                          prefill_scratch=ops.attention_prefill_scratch_floats(tokens, self.n_heads, self.head_dim,
+                                                                               splits))
+        return choice
+
     # ------------------------------------------------------------------ planning a step
     def _kernels(self, dtype: torch.dtype) -> tuple[bool, bool]:
         """Whether the tensor-core kernels for single tokens and for prompt portions take

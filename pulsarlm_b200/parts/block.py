@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import torch
 
+from . import native_layer
 from .registry import BuildContext, build_part, register_part
 from .spec import LayerSpec
 
@@ -25,6 +26,7 @@ class PreNormBlock:
         self.mixer = build_part("mixer", spec.mixer, ctx)
         self.ff_norm = build_part("norm", spec.norms["feed_forward"], ctx)
         self.feed_forward = build_part("feed_forward", spec.feed_forward, ctx)
+        self._native: bool | None = None  # whether the parts are the ones the native layer call takes
 
     @classmethod
     def part_specs(cls, spec: LayerSpec):
@@ -36,6 +38,14 @@ class PreNormBlock:
         return [self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward]
 
     def forward(self, x: torch.Tensor, delta: torch.Tensor | None, batch) -> tuple[torch.Tensor, torch.Tensor]:
+        # The standard parts in bfloat16: the whole layer from one native call (the same kernels
+        # in the same order; see native_layer.py). Anything else: the parts' own calls below.
+        if self._native is None:
+            self._native = native_layer.eligible(self)
+        if self._native:
+            done = native_layer.forward(self, x, delta, batch)
+            if done is not None:
+                return done
         h = self.mixer_norm.forward(x, delta)
         mixed = self.mixer.forward(h, batch)
         h = self.ff_norm.forward(x, mixed)
