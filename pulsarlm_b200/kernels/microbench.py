@@ -5,6 +5,7 @@
     python -m pulsarlm_b200.kernels.microbench attention_decode [--batch 8 --context 2048 ...]
     python -m pulsarlm_b200.kernels.microbench decode_timeline [--layers 8 --batch 8 --context 2048]
         [--shape 1b --batch 64 --context 128 4608]   (contexts spread evenly between the two)
+    python -m pulsarlm_b200.kernels.microbench mixed_steps [--shape 1b --layers 16]
 
 Each timing replays a CUDA graph of several launches (so host time does not
 count) over inputs rotated through enough copies to exceed L2, after warm-up,
@@ -15,6 +16,8 @@ product torch.mm calls.
 model (random weights, fewer layers) under the torch profiler's CUDA activity trace and
 prints when each kernel of one layer starts and ends inside the graph: kernels overlap
 (programmatic dependent launch), so the differences of the END times are what each costs.
+`mixed_steps` runs the engine's eager steps under a serving load (prompt portions beside
+single tokens) and prints a step's wall time beside the sum of its kernels' times.
 """
 
 from __future__ import annotations
@@ -254,9 +257,61 @@ def decode_timeline(layers: int, batch: int, contexts: list[int], page: int, sha
         previous_end = end
 
 
+def mixed_steps(shape: str, layers: int, page: int, portion: int = 512, requests: int = 64) -> None:
+    """Eager steps as a server under load runs them: `requests` prompts of 128 to 4,096 tokens
+    fed in portions of `portion` tokens beside the single tokens of the requests already
+    decoding. Prints the wall time of a step and the sum of its kernels' times (the torch
+    profiler's CUDA activity trace): the difference is what the host costs."""
+    import time
+
+    from torch.profiler import ProfilerActivity, profile
+
+    from ..engine.engine import Engine
+    from ..sampling.params import SamplingParams
+
+    config = dict(MODEL_SHAPES[shape], num_hidden_layers=layers)
+    gen = torch.Generator().manual_seed(3)
+    lengths = torch.randint(128, 4097, (requests,), generator=gen).tolist()
+    prompts = [torch.randint(0, config["vocab_size"], (n,), generator=gen).tolist() for n in lengths]
+    n_pages = sum(-(-(n + 80) // page) for n in lengths) + 64
+    engine = Engine(config, dtype="bfloat16", device="cuda:0", n_pages=n_pages, page_size=page,
+                    prefill_tokens_per_step=portion, max_requests=requests, seed=0)
+    greedy = SamplingParams(temperature=0.0)
+
+    def submit():
+        return [engine.submit(p, sampling=greedy, max_tokens=64, ignore_eos=True) for p in prompts]
+
+    submit()
+    while engine.has_work():  # once through: libraries set up
+        engine.step()
+    engine.sync()
+    submit()
+    for _ in range(60):
+        engine.step()
+    torch.cuda.synchronize()
+    steps = 40
+    start = time.perf_counter()
+    for _ in range(steps):
+        engine.step()
+    torch.cuda.synchronize()
+    wall = (time.perf_counter() - start) / steps
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            engine.step()
+        torch.cuda.synchronize()
+    events = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+    busy = sum(e.time_range.end - e.time_range.start for e in events) / steps
+    print(f"mixed steps ({shape} shape, {layers} layers, portions of {portion} beside single tokens): "
+          f"{wall * 1e3:.2f} ms a step by the clock, {busy / 1e3:.2f} ms of kernels ({len(events) // steps} launches)")
+    while engine.has_work():
+        engine.step()
+    engine.sync()
+
+
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("what", choices=["gemm", "attention_prefill", "attention_decode", "decode_timeline"])
+    parser.add_argument("what", choices=["gemm", "attention_prefill", "attention_decode", "decode_timeline",
+                                         "mixed_steps"])
     parser.add_argument("--shapes", nargs="*", default=None, help="T,N,K triples for gemm")
     parser.add_argument("--tokens", type=int, nargs="*", default=[2048, 8192])
     parser.add_argument("--prior", type=int, default=0, help="keys in the cache before an attention_prefill portion")
@@ -284,6 +339,8 @@ def main() -> None:
     if args.what == "gemm":
         shapes = LLAMA8B_SHAPES if not args.shapes else [tuple(int(v) for v in s.split(",")) for s in args.shapes]
         bench_gemm(shapes)
+    elif args.what == "mixed_steps":
+        mixed_steps(args.shape, args.layers, args.page_size)
     elif args.what == "decode_timeline":
         decode_timeline(args.layers, args.batch[0] if len(args.batch) == 1 else 8,
                         args.context if args.context and len(args.context) <= 2 else [2048], args.page_size,
