@@ -251,6 +251,39 @@ class CacheManager:
         if code < 0:
             raise CacheError(f"request {request!r}: commit({new_len}) failed with code {code}")
 
+    def reserve_many(self, requests: list, n_new: list[int]) -> tuple[np.ndarray, np.ndarray, int]:
+        """A step's entries in one call of the host core: for open requests, in order, the
+        tokens each holds (int64) and its slot (int32), and pages reserved for n_new[i] more.
+        Returns (lengths, slots, done): done == len(requests), or the index of the first
+        request for which too few pages were free (what the earlier ones reserved stays)."""
+        n = len(requests)
+        handles = np.array([self._handles.get(r, -1) for r in requests], dtype=np.int64)
+        new = np.asarray(n_new, dtype=np.int32)
+        lens = np.empty(n, dtype=np.int64)
+        slots = np.empty(n, dtype=np.int32)
+        code = ctypes.c_int32(0)
+        done = self._lib.plh_cache_reserve_many(self._book, handles.ctypes.data, new.ctypes.data, n, lens.ctypes.data,
+                                                slots.ctypes.data, ctypes.byref(code))
+        if done < n and code.value != core.NO_ROOM:
+            if code.value == core.UNKNOWN_REQUEST:
+                raise KeyError(requests[done])
+            if code.value == core.SHRINK:
+                raise CacheError(f"request {requests[done]!r} cannot shrink")
+            raise CacheError(f"request {requests[done]!r}: reserve failed with code {code.value}")
+        return lens, slots, done
+
+    def commit_many(self, requests: list, new_lens: list[int]) -> None:
+        """commit(request, new_len) for a step's entries in one call of the host core."""
+        handles = np.array([self._handles.get(r, -1) for r in requests], dtype=np.int64)
+        lens = np.asarray(new_lens, dtype=np.int64)
+        code = self._lib.plh_cache_commit_many(self._book, handles.ctypes.data, lens.ctypes.data, len(requests))
+        if code == core.NOT_RESERVED:
+            raise CacheError("commit without pages reserved")
+        if code == core.BAD_PAGE:
+            raise PageError("a page was given back twice")
+        if code < 0:
+            raise CacheError(f"commit failed with code {code}")
+
     def close(self, request) -> None:
         """Gives back every page and the slot of the request."""
         code = self._lib.plh_cache_close(self._book, self._known(request))

@@ -443,7 +443,7 @@ using plh::CacheBook;
 using plh::PagePool;
 using plh::SchedulerCore;
 
-PLH_API int plh_abi_version() { return 2; }
+PLH_API int plh_abi_version() { return 3; }
 
 PLH_API void* plh_pool_create(int n_pages) { return new PagePool(n_pages); }
 PLH_API void plh_pool_destroy(void* pool) { delete static_cast<PagePool*>(pool); }
@@ -533,6 +533,42 @@ PLH_API int plh_cache_fill_tables(void* cache, int group, const int64_t* request
         }
     }
     return longest;
+}
+
+// A step's entries in one call. For entry i: lens[i] = tokens request i holds, slots[i] =
+// its slot, then pages are reserved for lens[i] + n_new[i] tokens. Returns the number of
+// entries done: `count`, or fewer, with *code the code that stopped entry [return value]
+// (kNoRoom: too few pages; reservations made for the entries before it stay).
+PLH_API int plh_cache_reserve_many(void* cache, const int64_t* requests, const int32_t* n_new, int count,
+                                   int64_t* lens, int32_t* slots, int32_t* code) {
+    auto* book = static_cast<CacheBook*>(cache);
+    *code = plh::kOk;
+    for (int i = 0; i < count; ++i) {
+        if (!book->is_open(requests[i])) {
+            *code = plh::kUnknownRequest;
+            return i;
+        }
+        lens[i] = book->length(requests[i]);
+        slots[i] = book->slot(requests[i]);
+        const int result = book->reserve(requests[i], lens[i] + n_new[i]);
+        if (result != plh::kOk) {
+            *code = result;
+            return i;
+        }
+    }
+    return count;
+}
+
+// commit(request i, new_lens[i]) for every entry; the first error code, or kOk.
+PLH_API int plh_cache_commit_many(void* cache, const int64_t* requests, const int64_t* new_lens, int count) {
+    auto* book = static_cast<CacheBook*>(cache);
+    for (int i = 0; i < count; ++i) {
+        const int result = book->commit(requests[i], new_lens[i]);
+        if (result != plh::kOk) {
+            return result;
+        }
+    }
+    return plh::kOk;
 }
 
 PLH_API void* plh_sched_create(void* cache, int prefill_tokens_per_step, int max_step_entries) {

@@ -128,7 +128,8 @@ class ModelRunner:
         dev = torch.empty(total, dtype=torch.int32, device=self.device)
         dev.copy_(host, non_blocking=True)
         # The pinned buffer is reused by the next step: the copy must have left it.
-        self._copy_done = torch.cuda.Event()
+        if getattr(self, "_copy_done", None) is None:
+            self._copy_done = torch.cuda.Event()
         self._copy_done.record()
         return [dev[start : start + a.size].view(a.shape) for a, start in zip(arrays, starts)]
 
@@ -142,22 +143,30 @@ class ModelRunner:
             if e.request in seen:
                 raise ValueError(f"request {e.request!r} appears twice in one step")
             seen.add(e.request)
-            if len(e.tokens) == 0:
+            n = len(e.tokens)
+            if n == 0:
                 raise ValueError(f"request {e.request!r}: a step entry needs at least one token")
-            bad = [t for t in e.tokens if not 0 <= int(t) < self.vocab]
-            if bad:
-                raise ValueError(f"request {e.request!r}: token id {bad[0]} is outside [0, {self.vocab})")
-            if any(not 0 <= w < len(e.tokens) for w in e.want):
-                raise ValueError(f"request {e.request!r}: wanted places {e.want} are outside its {len(e.tokens)} tokens")
-        new_lens = []
+            if n == 1:
+                if not 0 <= int(e.tokens[0]) < self.vocab:
+                    raise ValueError(f"request {e.request!r}: token id {e.tokens[0]} is outside [0, {self.vocab})")
+            else:
+                ids = np.asarray(e.tokens)
+                if int(ids.min()) < 0 or int(ids.max()) >= self.vocab:
+                    bad = [t for t in e.tokens if not 0 <= int(t) < self.vocab]
+                    raise ValueError(f"request {e.request!r}: token id {bad[0]} is outside [0, {self.vocab})")
+            if e.want and not all(0 <= w < n for w in e.want):
+                raise ValueError(f"request {e.request!r}: wanted places {e.want} are outside its {n} tokens")
         for e in entries:
             if not self.cache.is_open(e.request):
                 if self.cache.open(e.request) is None:
                     raise OutOfPages(e.request, f"no free slot for request {e.request!r}")
-            new_len = self.cache.length(e.request) + len(e.tokens)
-            if not self.cache.reserve(e.request, new_len):
-                raise OutOfPages(e.request, f"too few free pages for request {e.request!r} to reach {new_len} tokens")
-            new_lens.append(new_len)
+        all_requests = [e.request for e in entries]
+        starts, all_slots, done = self.cache.reserve_many(all_requests, [len(e.tokens) for e in entries])
+        if done < len(entries):
+            e = entries[done]
+            raise OutOfPages(e.request, f"too few free pages for request {e.request!r} to reach "
+                                        f"{int(starts[done]) + len(e.tokens)} tokens")
+        new_lens = [int(starts[i]) + len(e.tokens) for i, e in enumerate(entries)]
 
         if getattr(self, "_copy_done", None) is not None:
             self._copy_done.synchronize()
@@ -175,15 +184,18 @@ class ModelRunner:
         for place, i in enumerate(order):
             e = entries[i]
             n = len(e.tokens)
-            start = self.cache.length(e.request)
+            start = int(starts[i])
             tokens[at : at + n] = e.tokens
-            pos[at : at + n] = np.arange(start, start + n, dtype=np.int32)
+            if n == 1:
+                pos[at] = start
+            else:
+                pos[at : at + n] = np.arange(start, start + n, dtype=np.int32)
             entry[at : at + n] = place
             first_row[i] = at
             at += n
         want_rows = [first_row[i] + w for i, e in enumerate(entries) for w in e.want]
         requests = [entries[i].request for i in order]
-        slots = np.array([self.cache.slot(r) for r in requests], dtype=np.int32)
+        slots = all_slots[order]
         tables = [self.cache.table_rows(g.index, requests) for g in self.cache.groups]
         host = HostStep(n_entries=len(entries), n_tokens=n_tokens, n_decode=n_decode,
                         query_lens=[len(entries[i].tokens) for i in order],
@@ -254,8 +266,7 @@ class ModelRunner:
         logits = self.model.forward(batch)
         if self.cache.mass_decay is not None:
             self.cache.fold_mass(batch.extras["mass_retained"])
-        for e, new_len in zip(entries, new_lens):
-            self.cache.commit(e.request, new_len)
+        self.cache.commit_many([e.request for e in entries], new_lens)
         self.steps += 1
         self.tokens_run += batch.n_tokens
         return logits

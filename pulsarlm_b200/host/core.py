@@ -11,7 +11,7 @@ from ..kernels import build
 _I32, _I64, _PTR = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 # return codes of csrc_host/host_core.hpp
 OK, NO_ROOM = 0, 1
@@ -47,6 +47,8 @@ _SIGNATURES = {
     "plh_cache_fill_tables": ([_PTR, _I32, _PTR, _I32, _PTR, _I32, _PTR], _I32),
     "plh_fill_random": ([_PTR, _I64, _I32, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_float, ctypes.c_float], _I32),
     "plh_decode_work_items": ([_PTR, _I32, _I32, _I32, _I32, _I32, _PTR, _I32, _PTR], _I32),
+    "plh_cache_reserve_many": ([_PTR, _PTR, _PTR, _I32, _PTR, _PTR, _PTR], _I32),
+    "plh_cache_commit_many": ([_PTR, _PTR, _PTR, _I32], _I32),
     "plh_sched_create": ([_PTR, _I32, _I32], _PTR),
     "plh_sched_destroy": ([_PTR], None),
     "plh_sched_set_stop_ids": ([_PTR, _PTR, _I32], None),
