@@ -32,6 +32,9 @@ PL_API int pl_add_rmsnorm(float* x, const void* delta, const void* weight, int w
 PL_API int pl_swiglu(const void* in, void* out, int n_tokens, int width, int dtype, cudaStream_t stream);
 PL_API int pl_gemm_bf16_skinny(const void* x, const void* w, void* y, int t, int n, int k, int64_t ldx, int64_t ldw,
                                int64_t ldy, int out_f32, int32_t* status, cudaStream_t stream);
+PL_API int pl_gemm_bf16_skinny_gated_in(const void* gated, const void* w, void* y, int t, int n, int k,
+                                        int64_t ld_gated, int64_t ldw, int64_t ldy, int out_f32, int32_t* status,
+                                        cudaStream_t stream);
 PL_API int pl_gemm_bf16_pair(const void* x, const void* w, void* y, int t, int n, int k, int64_t ldx, int64_t ldw,
                              int64_t ldy, int out_f32, int gated, int32_t* status, cudaStream_t stream);
 PL_API int pl_rope_kv_write(void* q, const void* k, const void* v, int64_t row_stride, const int32_t* pos,
@@ -84,7 +87,15 @@ struct PlLayerWeights {
 };
 
 // Routes of a matrix product, as parts/linear.py names them.
-enum PlRoute : int { PL_ROUTE_LIBRARY = 0, PL_ROUTE_SKINNY = 1, PL_ROUTE_PAIR = 2, PL_ROUTE_PAIR_GATED = 3 };
+// (PAIR_GATED: the gate/up product applies SwiGLU in its epilogue; SKINNY_GATED_IN: the down
+// product forms silu(g) * u as it reads the gate/up product's output, no SwiGLU kernel.)
+enum PlRoute : int {
+    PL_ROUTE_LIBRARY = 0,
+    PL_ROUTE_SKINNY = 1,
+    PL_ROUTE_PAIR = 2,
+    PL_ROUTE_PAIR_GATED = 3,
+    PL_ROUTE_SKINNY_GATED_IN = 4
+};
 
 // One step's inputs, the parts' decisions for it, and its workspace (shared by the layers
 // of equal shape, which run one after the other).
@@ -274,12 +285,15 @@ PL_API int pl_layer_forward(const PlLayerWeights* w, const PlLayerStep* s, cudaS
                                      1, s->status, stream);
         } else {
             code = product(*s, s->route_gate_up, s->h, w->gate_up, s->gate_up, t, 2 * w->inter, w->hidden, stream);
-            if (code == 0) {
+            if (code == 0 && s->route_down != PL_ROUTE_SKINNY_GATED_IN) {
                 code = pl_swiglu(s->gate_up, s->act, t, w->inter, PL_BF16, stream);
             }
         }
     }
-    if (code == 0) {
+    if (code == 0 && s->route_down == PL_ROUTE_SKINNY_GATED_IN) {
+        code = pl_gemm_bf16_skinny_gated_in(s->gate_up, w->down, s->delta_out, t, w->hidden, w->inter, 2 * w->inter,
+                                            w->inter, w->hidden, 0, s->status, stream);
+    } else if (code == 0) {
         code = product(*s, s->route_down, s->act, w->down, s->delta_out, t, w->hidden, w->inter, stream);
     }
     return code;

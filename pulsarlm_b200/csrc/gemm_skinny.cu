@@ -51,6 +51,14 @@ struct SkinnyParams {
     int kb_per_split;  // k blocks per rank
     int stages;        // pipeline depth (shared memory given: stages * stage bytes + receive buffer)
     int32_t* status;
+    // Where the activations come from. 0: x itself, through TMA. 1: x = silu(g) * u made on
+    // the way in, g and u the two halves [T, K] of `gated` [T, 2K] (the gate/up projection's
+    // output): the epilogue warps, idle until the accumulator is done, read g and u, form
+    // the product in fp32, round it once and store it where the MMA reads its B operand
+    // (same layout as a TMA tile with 128-byte swizzle). T <= 16.
+    int x_mode;
+    const __nv_bfloat16* gated;
+    int64_t ld_gated;
 };
 
 // The receive buffer: [rank][feature of mine][token], rows of tn + 4 floats (16-byte
@@ -76,8 +84,10 @@ constexpr int stages_within(int tn, int budget) {
     return fit > kMaxStages ? kMaxStages : fit;
 }
 
+// (Two CTAs of a launch with a CTA for every SM and more share an SM: the registers must
+// allow it, 168 a thread at most.)
 template <int TN>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    const SkinnyParams p) {
     const int kStages = p.stages;
@@ -111,7 +121,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         tensormap_prefetch(&map_w);
         tensormap_prefetch(&map_x);
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(&full_bar[s], 1);
+            mbar_init(&full_bar[s], p.x_mode == 0 ? 1 : 2);  // (+ the warp that makes the stage's x)
             mbar_init(&empty_bar[s], 1);
         }
         mbar_init(&acc_full, 1);
@@ -145,13 +155,13 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         const int early = min(n_units, kStages);
         for (int u = 0; u < early; ++u) {  // weights: nobody writes them, no need to wait
             if (elect_one()) {
-                mbar_expect_tx(&full_bar[u], kStageBytes);
+                mbar_expect_tx(&full_bar[u], p.x_mode == 0 ? kStageBytes : kBytesA);
                 tma_load_2d(tiles + u * kStageBytes, &map_w, (kb0 + u) * kBlockK, n0, &full_bar[u]);
             }
             __syncwarp();
         }
         pl_grid_wait();
-        for (int u = 0; u < early; ++u) {
+        for (int u = 0; u < early && p.x_mode == 0; ++u) {
             if (elect_one()) {
                 tma_load_2d(tiles + u * kStageBytes + kBytesA, &map_x, (kb0 + u) * kBlockK, 0, &full_bar[u]);
             }
@@ -165,9 +175,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             }
             unsigned char* a = tiles + stage * kStageBytes;
             if (elect_one()) {
-                mbar_expect_tx(&full_bar[stage], kStageBytes);
+                mbar_expect_tx(&full_bar[stage], p.x_mode == 0 ? kStageBytes : kBytesA);
                 tma_load_2d(a, &map_w, (kb0 + u) * kBlockK, n0, &full_bar[stage]);
-                tma_load_2d(a + kBytesA, &map_x, (kb0 + u) * kBlockK, 0, &full_bar[stage]);
+                if (p.x_mode == 0) {
+                    tma_load_2d(a + kBytesA, &map_x, (kb0 + u) * kBlockK, 0, &full_bar[stage]);
+                }
             }
             __syncwarp();
             if (++stage == kStages) {
@@ -216,6 +228,75 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         const int n = n0 + feature;
         const uint32_t tmem_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16);
         pl_grid_wait();
+        if constexpr (TN == 16) {
+            if (p.x_mode == 1) {
+                // These four warps make the activation tiles, each every fourth stage, so that one
+                // warp's waits, fence and arrival overlap the others' arithmetic: lane (token, half
+                // a row) of a 16 x 64 tile, four 16-byte chunks each. A warp asks for its next
+                // stage's g and u before it works on the one it has.
+                const int mine = warp - 2;                     // stages mine, mine + 4, ...
+                const int token = lane >> 1, chunk0 = (lane & 1) * 4;
+                const bool row_ok = token < p.t;
+                const __nv_bfloat16* g_row = p.gated + static_cast<int64_t>(token) * p.ld_gated;
+                uint4 g_in[2][4], u_in[2][4];
+                auto fetch = [&](int u, uint4 (&g)[4], uint4 (&v)[4]) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int k = (kb0 + u) * kBlockK + (chunk0 + c) * 8;
+                        if (row_ok && u < n_units && k < p.k) {  // (k is a multiple of 8, and so is p.k)
+                            g[c] = *reinterpret_cast<const uint4*>(g_row + k);
+                            v[c] = *reinterpret_cast<const uint4*>(g_row + p.k + k);
+                        } else {
+                            g[c] = make_uint4(0u, 0u, 0u, 0u);
+                            v[c] = g[c];
+                        }
+                    }
+                };
+                auto make = [&](int u, const uint4 (&g_all)[4], const uint4 (&u_all)[4]) -> bool {
+                    const int stage = u % kStages;
+                    if (u >= kStages && !mbar_wait(&empty_bar[stage], ((u / kStages) & 1u) ^ 1u, &abort_flag)) {
+                        return false;
+                    }
+                    unsigned char* tile = tiles + stage * kStageBytes + kBytesA + token * 128;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g_all[c]);
+                        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u_all[c]);
+                        uint4 out;
+                        uint32_t* o = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float2 g = __bfloat1622float2(g2[j]), v = __bfloat1622float2(u2[j]);
+                            // (the SwiGLU kernel's own expression: the same bits)
+                            const __nv_bfloat162 pair = __floats2bfloat162_rn(
+                                __fdividef(g.x, 1.0f + __expf(-g.x)) * v.x, __fdividef(g.y, 1.0f + __expf(-g.y)) * v.y);
+                            o[j] = *reinterpret_cast<const uint32_t*>(&pair);
+                        }
+                        *reinterpret_cast<uint4*>(tile + (((chunk0 + c) ^ (token & 7)) << 4)) = out;
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(&full_bar[stage]);
+                    }
+                    return true;
+                };
+                fetch(mine, g_in[0], u_in[0]);
+                for (int u = mine; u < n_units; u += 8) {
+                    fetch(u + 4, g_in[1], u_in[1]);
+                    if (!make(u, g_in[0], u_in[0])) {
+                        break;
+                    }
+                    if (u + 4 >= n_units) {
+                        break;
+                    }
+                    fetch(u + 8, g_in[0], u_in[0]);
+                    if (!make(u + 4, g_in[1], u_in[1])) {
+                        break;
+                    }
+                }
+            }
+        }
         const bool have = mbar_wait(&acc_full, 0u, &abort_flag);
         tcgen05_fence_after();
         if (have && splits == 1) {
@@ -432,18 +513,10 @@ PL_API int pl_gemm_bf16_skinny_splits(int t, int n, int k) {
 // The most tokens pl_gemm_bf16_skinny takes.
 PL_API int pl_gemm_bf16_skinny_max_tokens() { return 64; }
 
-// y[T, N] (bf16, or fp32 when out_f32) = x[T, K] w[N, K]^T with bf16 x and w, for
-// T <= 64. k and the leading dimensions of x and w must be multiples of 8 (rows on
-// 16-byte boundaries for TMA); N with more than 65535 tiles of 128 is refused.
-PL_API int pl_gemm_bf16_skinny(const void* x, const void* w, void* y, int t, int n, int k, int64_t ldx, int64_t ldw,
-                               int64_t ldy, int out_f32, int32_t* status, cudaStream_t stream) {
-    PL_REQUIRE(t >= 1 && t <= 64 && n >= 1 && k >= 8 && k % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0,
-               "gemm_bf16_skinny: unsupported sizes t=%d n=%d k=%d ldx=%lld ldw=%lld (t <= 64; k and the leading "
-               "dimensions must be multiples of 8)",
-               t, n, k, static_cast<long long>(ldx), static_cast<long long>(ldw));
-    PL_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
-               "gemm_bf16_skinny: operands must be 16-byte aligned");
-    PL_REQUIRE(ldy >= n, "gemm_bf16_skinny: ldy=%lld is smaller than n=%d", static_cast<long long>(ldy), n);
+namespace {
+
+int run_skinny(const void* x, const void* w, void* y, int t, int n, int k, int64_t ldx, int64_t ldw, int64_t ldy,
+               int out_f32, int x_mode, int32_t* status, cudaStream_t stream) {
     const int tn = t <= 16 ? 16 : (t <= 32 ? 32 : 64);
     if (const int code = tn == 16 ? configure<16>() : (tn == 32 ? configure<32>() : configure<64>())) {
         return code;
@@ -469,9 +542,46 @@ PL_API int pl_gemm_bf16_skinny(const void* x, const void* w, void* y, int t, int
     p.kb_per_split = plan.kb_per_split;
     p.stages = plan.stages;
     p.status = status;
+    p.x_mode = x_mode;
+    p.gated = static_cast<const __nv_bfloat16*>(x);
+    p.ld_gated = ldx;
     switch (plan.tn) {
         case 16: return launch_skinny<16>(map_w, map_x, p, plan, stream);
         case 32: return launch_skinny<32>(map_w, map_x, p, plan, stream);
         default: return launch_skinny<64>(map_w, map_x, p, plan, stream);
     }
+}
+
+}  // namespace
+
+// y[T, N] (bf16, or fp32 when out_f32) = x[T, K] w[N, K]^T with bf16 x and w, for
+// T <= 64. k and the leading dimensions of x and w must be multiples of 8 (rows on
+// 16-byte boundaries for TMA); N with more than 65535 tiles of 128 is refused.
+PL_API int pl_gemm_bf16_skinny(const void* x, const void* w, void* y, int t, int n, int k, int64_t ldx, int64_t ldw,
+                               int64_t ldy, int out_f32, int32_t* status, cudaStream_t stream) {
+    PL_REQUIRE(t >= 1 && t <= 64 && n >= 1 && k >= 8 && k % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0,
+               "gemm_bf16_skinny: unsupported sizes t=%d n=%d k=%d ldx=%lld ldw=%lld (t <= 64; k and the leading "
+               "dimensions must be multiples of 8)",
+               t, n, k, static_cast<long long>(ldx), static_cast<long long>(ldw));
+    PL_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+               "gemm_bf16_skinny: operands must be 16-byte aligned");
+    PL_REQUIRE(ldy >= n, "gemm_bf16_skinny: ldy=%lld is smaller than n=%d", static_cast<long long>(ldy), n);
+    return run_skinny(x, w, y, t, n, k, ldx, ldw, ldy, out_f32, 0, status, stream);
+}
+
+// y[T, N] = (silu(g) * u)[T, K] w[N, K]^T for gated = [g | u] of [T, 2K] bf16 (a gate/up
+// projection's output, rows ld_gated apart): the gated activation is formed as the product
+// reads it (fp32, rounded once to bf16, as the SwiGLU kernel does) and never written. T <= 16.
+PL_API int pl_gemm_bf16_skinny_gated_in(const void* gated, const void* w, void* y, int t, int n, int k,
+                                        int64_t ld_gated, int64_t ldw, int64_t ldy, int out_f32, int32_t* status,
+                                        cudaStream_t stream) {
+    PL_REQUIRE(t >= 1 && t <= 16 && n >= 1 && k >= 8 && k % 8 == 0 && ld_gated % 8 == 0 && ldw % 8 == 0 &&
+                   ld_gated >= 2 * static_cast<int64_t>(k),
+               "gemm_bf16_skinny_gated_in: unsupported sizes t=%d n=%d k=%d ld=%lld ldw=%lld (t <= 16; k and the "
+               "leading dimensions multiples of 8; rows of at least 2k)",
+               t, n, k, static_cast<long long>(ld_gated), static_cast<long long>(ldw));
+    PL_REQUIRE((reinterpret_cast<uintptr_t>(gated) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+               "gemm_bf16_skinny_gated_in: operands must be 16-byte aligned");
+    PL_REQUIRE(ldy >= n, "gemm_bf16_skinny_gated_in: ldy=%lld is smaller than n=%d", static_cast<long long>(ldy), n);
+    return run_skinny(gated, w, y, t, n, k, ld_gated, ldw, ldy, out_f32, 1, status, stream);
 }

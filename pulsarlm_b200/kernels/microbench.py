@@ -72,6 +72,21 @@ def bench_gemm(shapes) -> None:
 
         gb, tf = n * k * 2 / 1e9, 2.0 * t * n * k / 1e12
         line = f"gemm t={t} n={n} k={k}:"
+        if t <= ops.GEMM_GATED_IN_MAX_TOKENS:
+            # the same product fed by a gate/up output: the SwiGLU kernel then the product, or the
+            # activation made inside the product
+            gate_up = torch.randn(t, 2 * k, device="cuda").to(torch.bfloat16)
+
+            def two_kernels():
+                ops.swiglu(gate_up, x)
+                ops.gemm_bf16(x, weights[turn[0] % copies], out, kernel="skinny")
+                turn[0] += 1
+
+            def one_kernel():
+                ops.gemm_bf16_gated_in(gate_up, weights[turn[0] % copies], out)
+                turn[0] += 1
+
+            line += f" | swiglu + skinny {graph_time_us(two_kernels):.1f} us | gated in {graph_time_us(one_kernel):.1f} us"
         for name in (["skinny"] if t <= ops.GEMM_SKINNY_MAX_TOKENS else []) + ["pair", "library"]:
             us = graph_time_us(library if name == "library" else own(name))
             line += f" | {name} {us:.1f} us ({gb / us * 1e6:.0f} GB/s, {tf / us * 1e6:.0f} TFLOP/s)"

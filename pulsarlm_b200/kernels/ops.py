@@ -25,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 18
+ABI_VERSION = 19
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -53,6 +53,7 @@ _SIGNATURES = {
                                   _I32, _I32, _I32, _I32, _I32, _F32, _PTR, _I32, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR],
     "pl_attention_decode_ctas_per_sm": [_I32],
     "pl_layer_forward": [_PTR, _PTR, _PTR],
+    "pl_gemm_bf16_skinny_gated_in": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I64, _I64, _I64, _I32, _PTR, _PTR],
     "pl_fill_random": [_PTR, _I64, _I32, ctypes.c_uint64, ctypes.c_uint64, _F32, _F32, _PTR],
     "pl_attention_decode_supports": [_I32, _I32, _I32, _I32],
     "pl_attention_prefill": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _I32, _PTR, _I64,
@@ -288,6 +289,25 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch
               int(out.dtype == torch.float32), int(gated), _p(status), _stream())
         return
     raise ValueError(f"gemm_bf16: unknown kernel {kernel!r}")
+
+GEMM_GATED_IN_MAX_TOKENS = 16
+
+
+def gemm_bf16_gated_in(gate_up: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
+                       status: torch.Tensor | None = None) -> None:
+    """out[T, N] = (silu(g) * u) @ w[N, K]^T for gate_up = [g | u] of [T, 2K] (a gate/up
+    projection's output): the skinny kernel forms the gated activation as it reads it
+    (fp32, one rounding, the SwiGLU kernel's expression) and never writes it. T <= 16."""
+    _dev(gate_up, w, out, status)
+    assert gate_up.dtype == w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
+    t, two_k = gate_up.shape
+    n, k = w.shape
+    assert two_k == 2 * k and out.shape == (t, n) and t <= GEMM_GATED_IN_MAX_TOKENS
+    assert gate_up.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    _call("pl_gemm_bf16_skinny_gated_in", _p(gate_up), _p(w), _p(out), t, n, k,
+          gate_up.stride(0) if t > 1 else two_k, w.stride(0) if n > 1 else k, out.stride(0) if t > 1 else n,
+          int(out.dtype == torch.float32), _p(status), _stream())
+
 
 def rope_kv_write(q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor | None, pos: torch.Tensor,
                   entry: torch.Tensor, table: torch.Tensor, k_pool: torch.Tensor | None,

@@ -11,7 +11,7 @@ import math
 import torch
 
 from ..kernels import ops
-from .linear import gated_linear, linear
+from .linear import gated_feed_forward, linear
 from .registry import BuildContext, Part, register_part
 from .spec import PartSpec, TensorNeed
 
@@ -194,4 +194,4 @@ class GatedMLP(Part):
         self.down = tensors[t["down"]].contiguous()
 
     def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
-        return linear(gated_linear(h, self.gate_up), self.down)
+        return gated_feed_forward(h, self.gate_up, self.down)

@@ -106,3 +106,24 @@ def gated_linear(x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
         return act
     ops.swiglu(linear(x, gate_up), act)
     return act
+
+
+GATED_IN = os.environ.get("PULSARLM_B200_GATED_IN", "1") != "0"  # (0: always the SwiGLU kernel, for comparison)
+
+
+def gated_feed_forward(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
+    """(silu(x Wg^T) * (x Wu^T)) Wd^T -> [T, H]. For a handful of tokens in bfloat16 the down
+    projection's skinny kernel forms the gated activation itself as it reads the gate/up
+    projection's output (one launch fewer, the [T, I] activation never written); else
+    `gated_linear` followed by `linear`."""
+    tokens, k = x.shape
+    inter = gate_up.shape[0] // 2
+    if (GATED_IN and x.dtype == torch.bfloat16 == gate_up.dtype == down.dtype
+            and tokens <= ops.GEMM_GATED_IN_MAX_TOKENS and down.stride(1) == 1
+            and own_kernel_for(tokens, down.shape[0], x.device, inter) == "skinny"
+            and own_kernel_for(tokens, 2 * inter, x.device, k) != "pair"
+            and ops.gemm_bf16_supports(tokens, down.shape[0], inter, 2 * inter, down.stride(0))):
+        out = torch.empty((tokens, down.shape[0]), dtype=x.dtype, device=x.device)
+        ops.gemm_bf16_gated_in(linear(x, gate_up), down, out)
+        return out
+    return linear(gated_linear(x, gate_up), down)

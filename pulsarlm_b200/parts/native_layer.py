@@ -52,6 +52,7 @@ class LayerStep(ctypes.Structure):
 
 ROUTES = {None: 0, "skinny": 1, "pair": 2}
 ROUTE_PAIR_GATED = 3
+ROUTE_SKINNY_GATED_IN = 4
 _WORKSPACES: dict[torch.device, torch.Tensor] = {}
 # (With 32 MB cuBLAS picked a slower kernel for a 256-token down projection of the 8B shape than
 # with 8 MB, 37 against 30 us; 8 MB gives the choices torch's own calls get.)
@@ -123,6 +124,10 @@ class StepState:
         c = self.choice
         gate_up = linear.own_kernel_for(tokens, 2 * ff.inter, device, hidden)
         gated = gate_up == "pair" and ops.gemm_bf16_supports(tokens, ff.inter, hidden, hidden, hidden)
+        # (as linear.gated_feed_forward decides: the down product makes the gated activation itself)
+        gated_in = (linear.GATED_IN and not gated and tokens <= ops.GEMM_GATED_IN_MAX_TOKENS
+                    and linear.own_kernel_for(tokens, hidden, device, ff.inter) == "skinny"
+                    and ops.gemm_bf16_supports(tokens, hidden, ff.inter, 2 * ff.inter, ff.inter))
         # one bf16 buffer for the activations, carved into parts that start on 512 bytes
         sizes = [tokens * hidden, tokens * qkv_width, tokens * q_width, tokens * hidden,
                  0 if gated else tokens * 2 * ff.inter, tokens * ff.inter, tokens * hidden, tokens * hidden]
@@ -148,7 +153,7 @@ class StepState:
             views[4].data_ptr() if not gated else None, views[5].data_ptr(),
             _route(tokens, qkv_width, hidden, device), _route(tokens, hidden, q_width, device),
             ROUTE_PAIR_GATED if gated else _route(tokens, 2 * ff.inter, hidden, device),
-            _route(tokens, hidden, ff.inter, device),
+            ROUTE_SKINNY_GATED_IN if gated_in else _route(tokens, hidden, ff.inter, device),
             int(c["fold_rope"]), items.data_ptr() if items is not None else None,
             items.shape[0] if items is not None else 0, c["slots"].data_ptr() if items is not None else None,
             ops.attention_decode_counters(device).data_ptr() if items is not None else None,
@@ -163,7 +168,7 @@ class StepState:
                          + (1 if c["n_decode"] > 0 else 0)
                          + (1 if c["n_decode"] > 0 and items is None and c["decode_splits"] > 16 else 0)
                          + ((1 if c["prefill_splits"] == 1 else 2) if tiles is not None else 0)
-                         + (0 if gated else 1))
+                         + (0 if gated or gated_in else 1))
 
 
 def forward(block, x: torch.Tensor, delta: torch.Tensor | None, batch):

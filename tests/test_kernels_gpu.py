@@ -166,6 +166,34 @@ def test_gemm_bf16_gated_epilogue(ops, t, n, k):
     assert torch.equal(out, two_step)
 
 
+@pytest.mark.parametrize("t,n,k", [(1, 64, 64), (8, 4096, 14336), (16, 172, 1000), (5, 2048, 8192), (13, 130, 72),
+                                   (8, 5120, 13824)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_bf16_with_the_gated_activation_made_on_the_way_in(ops, t, n, k, out_dtype):
+    """y = (silu(g) * u) w^T with the activation formed inside the product against the
+    SwiGLU kernel followed by the plain product: the same bits (same expression, same
+    rounding, same order of additions), and both close to float64."""
+    gate_up = (torch.randn(t, 2 * k, device=DEV) * 1.5).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
+    act = torch.empty(t, k, device=DEV, dtype=torch.bfloat16)
+    ops.swiglu(gate_up, act)
+    two = torch.empty(t, n, device=DEV, dtype=out_dtype)
+    ops.gemm_bf16(act, w, two, kernel="skinny")
+    one = torch.full((t, n), float("nan"), device=DEV, dtype=out_dtype)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.gemm_bf16_gated_in(gate_up, w, one, status)
+    assert int(status) == 0 and torch.equal(one, two)
+    g, u = gate_up[:, :k].double().cpu(), gate_up[:, k:].double().cpu()
+    want = (torch.nn.functional.silu(g) * u).to(torch.bfloat16).double() @ w.double().cpu().t()
+    assert rel(one, want) < (1e-2 if out_dtype == torch.bfloat16 else 2e-3)
+    # rows of a wider buffer (a slice of a larger activation)
+    wide = torch.zeros(t, 2 * k + 16, device=DEV, dtype=torch.bfloat16)
+    wide[:, : 2 * k] = gate_up
+    again = torch.empty_like(one)
+    ops.gemm_bf16_gated_in(wide[:, : 2 * k], w, again, status)
+    assert int(status) == 0 and torch.equal(again, one)
+
+
 def test_gemm_bf16_finds_one_large_product_among_many(ops):
     """One x[t, k] * w[n, k] pair far larger than the rest, at the last k of a k
     block, the first of the next, and in the tail: a dropped k block or a mis-stepped
