@@ -8,10 +8,9 @@
 //   on its N axis (16, 32 or 64), as in the large-product kernel (gemm_pair.cu):
 //   `tcgen05.mma.cta_group::1.kind::f16`, operands in shared memory through TMA with
 //   128-byte swizzle, the accumulator in tensor memory.
-// * One CTA computes one tile over one part of k. The grid is (splits, tiles) with
-//   `splits` the most parts that still lets all CTAs be resident at once (one per SM:
-//   kernels that allocate tensor memory do not share an SM), so that every SM streams
-//   from the start and nothing is lost to a last partial wave.
+// * One CTA computes one tile over one part of k. The grid is (splits, tiles), `splits`
+//   chosen so that about one and a half CTAs per SM stream at once where the shape allows
+//   (see make_skinny_plan for the rule and the measurements behind it).
 // * The CTAs that share a tile form a thread-block cluster and add their partial
 //   sums through distributed shared memory: the tile's 128 features are dealt out to
 //   the ranks in contiguous runs; every rank stores its values for a feature into
@@ -412,15 +411,17 @@ int configure() {
     return 0;
 }
 
-// How many clusters of `splits` CTAs the device holds at once (0 when it cannot say).
+// How many clusters of `splits` CTAs the device holds at once with the pipeline of the small
+// (`deep` false) or the large share of shared memory (0 when it cannot say).
 template <int TN>
-int resident_clusters(int splits) {
-    static int known[kMaxSplits + 1] = {0};
-    if (known[splits] == 0) {
+int resident_clusters(int splits, bool deep) {
+    static int known[2][kMaxSplits + 1] = {};
+    int& slot = known[deep ? 1 : 0][splits];
+    if (slot == 0) {
         cudaLaunchConfig_t config = {};
         config.gridDim = dim3(splits, 1024);
         config.blockDim = dim3(kThreads);
-        config.dynamicSmemBytes = smem_for(TN, stages_within(TN, kSmemLarge));
+        config.dynamicSmemBytes = smem_for(TN, stages_within(TN, deep ? kSmemLarge : kSmemSmall));
         cudaLaunchAttribute attribute[1];
         attribute[0].id = cudaLaunchAttributeClusterDimension;
         attribute[0].val.clusterDim.x = splits;
@@ -433,41 +434,59 @@ int resident_clusters(int splits) {
             cudaGetLastError();
             clusters = 0;
         }
-        known[splits] = clusters > 0 ? clusters : -1;
+        slot = clusters > 0 ? clusters : -1;
     }
-    return known[splits] > 0 ? known[splits] : 0;
+    return slot > 0 ? slot : 0;
 }
 
-// The k range of a tile is cut into as many parts as still lets every cluster be
-// resident at once (one wave), at most eight and at most one per k block.
+// The k range of a tile is cut into parts, at most eight (the portable cluster size) and at
+// most one per k block.
 template <int TN>
 SkinnyPlan make_skinny_plan(int n, int k) {
     SkinnyPlan plan;
     plan.tn = TN;
     plan.n_tiles = (n + kTileM - 1) / kTileM;
     plan.k_blocks = (k + kBlockK - 1) / kBlockK;
-    int splits = 1;
-    for (int s = kMaxSplits; s > 1; --s) {
-        if (s <= plan.k_blocks && plan.n_tiles <= resident_clusters<TN>(s)) {
-            splits = s;
-            break;
-        }
-    }
-    plan.kb_per_split = (plan.k_blocks + splits - 1) / splits;
-    plan.splits = (plan.k_blocks + plan.kb_per_split - 1) / plan.kb_per_split;  // no rank without work
-    // Depth of the pipeline. A launch with a CTA for every SM keeps to the smaller share
-    // of shared memory, so that CTAs of the next launch can settle beside its own and
-    // stream their weights under its tail; a launch of fewer CTAs takes the depth itself
-    // (the o and down projections of a Llama-3.1-8B step, 128 CTAs: 11.1 -> 7.5 us and
-    // 20.8 -> 19.9 us inside the step).
     static int sms = 0;
     if (sms == 0) {
         int device = 0;
         cudaGetDevice(&device);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     }
-    const int budget = plan.n_tiles * plan.splits >= sms ? kSmemSmall : kSmemLarge;
-    plan.stages = stages_within(TN, budget);
+    // How many parts. Inside a decode step the products stream best with about one and a half
+    // CTAs per SM (as many as the gate/up projection of the 8B shape has tiles, 224 on 148 SMs,
+    // which runs at the copy bandwidth), on the smaller share of shared memory, so that two of
+    // a launch's CTAs, or one and a CTA of the next launch, share an SM: the fewest parts that
+    // give between 1.5 and 1.75 CTAs per SM, if there are any with at least six k blocks
+    // each. Measured in the step (batch 8, one box): 8B shape q/k/v 2 -> 5 parts, o 4 -> 7, down
+    // 4 -> 7: 3.357 -> 3.28 ms (3 or 6 parts for q/k/v, 144 and 288 CTAs, 3.42 - 3.54; 8 for down
+    // 3.43); 13B shape 2 - 3 % faster; 1B shape gate/up 1 -> 2 parts 887 -> 858 us. Where no count
+    // lands in that band (the 1B shape's other products, 16 and 24 tiles) more parts measured
+    // worse (down 6 -> 8: 887 -> 984 us), and the rule is the earlier one: as many parts as still
+    // lets every cluster be resident at once with the deep pipeline, which such launches, of
+    // fewer CTAs than SMs, then take.
+    int splits = 0;
+    bool deep = false;
+    for (int s = 1; s <= kMaxSplits && s <= plan.k_blocks; ++s) {
+        const int total = plan.n_tiles * s;
+        if (2 * total >= 3 * sms && 4 * total <= 7 * sms && plan.k_blocks / s >= 6) {
+            splits = s;
+            break;
+        }
+    }
+    if (splits == 0) {
+        splits = 1;
+        for (int s = kMaxSplits; s > 1; --s) {
+            if (s <= plan.k_blocks && plan.n_tiles <= resident_clusters<TN>(s, true)) {
+                splits = s;
+                break;
+            }
+        }
+        deep = plan.n_tiles * splits < sms;
+    }
+    plan.kb_per_split = (plan.k_blocks + splits - 1) / splits;
+    plan.splits = (plan.k_blocks + plan.kb_per_split - 1) / plan.kb_per_split;  // no rank without work
+    plan.stages = stages_within(TN, deep ? kSmemLarge : kSmemSmall);
     plan.stages = plan.stages > plan.kb_per_split ? plan.kb_per_split : plan.stages;
     plan.stages = plan.stages < 2 ? 2 : plan.stages;
     return plan;
