@@ -220,7 +220,7 @@ def time_decode(engine, ids: list, steps: int, warmup: int, vocab: int):
     end.record()
     torch.cuda.synchronize()
     engine.runner.check_status()
-    graph = next(g for (n, _), g in engine.runner._graphs.items() if n == len(ids))
+    graph = engine.runner.last_graph
     launches = graph.launches * (engine.runner.graph_steps - before_steps)
     return start.elapsed_time(end) / steps, launches
 

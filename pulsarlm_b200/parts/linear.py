@@ -7,7 +7,11 @@ accumulation, by one of three routes chosen by $PULSARLM_B200_GEMM:
 * "mixed" (the default): the own tcgen05/TMEM kernels where they measured faster than
   the library, the library elsewhere. Up to 16 tokens (decode steps of small
   batches) csrc/gemm_skinny.cu, which overlaps its set-up and first weight loads
-  with the kernel before it, and up to 64 tokens too where the weights are large
+  with the kernel before it; up to 32 tokens too where the weights are 30 MB and more
+  (alone the two are even there; inside a step at batch 24 and 32 the 8B shape is 4 %
+  faster with it, the 13B shape 1 - 3 %, and the 1B shape, whose q/k/v and o
+  projections are smaller, 3 - 4 % with it for gate/up and down only); up to 64 tokens
+  where the weights are large
   (200 MB and more: a batch-64 step's gate/up projection and head, whose time is the
   weights' stream); products of at least four 256 x 256 tiles per pair of SMs with
   most of a 256-token tile filled (a prompt portion's gate/up projection, every
@@ -34,7 +38,9 @@ import os
 from ..kernels import ops
 
 GEMM_ROUTE = os.environ.get("PULSARLM_B200_GEMM", "mixed")
-MIXED_MAX_TOKENS = 16  # the skinny kernel is ahead of the library up to here,
+MIXED_MAX_TOKENS = int(os.environ.get("PULSARLM_B200_SKINNY_MAX_TOKENS", "16"))  # the skinny kernel is ahead of the library up to here,
+MIXED_MID_TOKENS = 32  # up to here where the weights are at least
+MIXED_MID_BYTES = 30e6  # this large,
 MIXED_MAX_TOKENS_LARGE = 64  # and up to here where the weights are at least
 MIXED_LARGE_BYTES = 200e6  # this large;
 MIXED_MIN_TILES_PER_PAIR = 4  # the pair kernel from this many 256 x 256 tiles per pair of SMs
@@ -54,6 +60,8 @@ def own_kernel_for(tokens: int, n: int, device: torch.device, k: int = 0) -> str
     if GEMM_ROUTE == "tcgen05":
         return "skinny" if tokens <= ops.GEMM_SKINNY_MAX_TOKENS else "pair"
     if tokens <= MIXED_MAX_TOKENS:
+        return "skinny"
+    if tokens <= MIXED_MID_TOKENS and 2.0 * n * k >= MIXED_MID_BYTES:
         return "skinny"
     if tokens <= MIXED_MAX_TOKENS_LARGE:
         return "skinny" if 2.0 * n * k >= MIXED_LARGE_BYTES else None
