@@ -527,24 +527,107 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
         return;
     }
     __threadfence();
+    // (The rings are free: every warp passed the barriers above after its last tile.) Per head
+    // the largest base, then per split its weight 2^(base - largest) and the weighed sum of the
+    // row sums, through shared memory; then every thread adds up four dims of one head over the
+    // splits, in split order, eight loads in flight at a time.
     const int64_t slot0 = static_cast<int64_t>(p.token_slot[t]) * p.n_heads + kv_head * p.group;
-    for (int idx = threadIdx.x; idx < p.group * HD; idx += WARPS * 32) {
-        const int r = idx / HD, d = idx % HD;
+    constexpr int kChunk = 128;                                  // splits per pass
+    float* weight = reinterpret_cast<float*>(smem);              // [kChunk][16]
+    float* row_max = weight + kChunk * 16;                       // [16]
+    float* row_sum = row_max + 16;                               // [16]
+    float* partial = row_sum + 16;                               // [WARPS * 32]
+    {
+        // largest base per head: thread (row = tid % 16, splits tid / 16, + 8, ...)
+        const int r = threadIdx.x & 15;
         float m = -INFINITY;
-        for (int s = 0; s < n_splits; ++s) {
-            m = fmaxf(m, __ldcg(&p.part_ml[(slot0 + static_cast<int64_t>(s) * p.n_heads + r) * 2]));
-        }
-        float l = 0.0f, acc = 0.0f;
-        if (m > -INFINITY) {
-            for (int s = 0; s < n_splits; ++s) {
-                const int64_t slot = slot0 + static_cast<int64_t>(s) * p.n_heads + r;
-                const float scale = exp2f(__ldcg(&p.part_ml[slot * 2]) - m);
-                l += __ldcg(&p.part_ml[slot * 2 + 1]) * scale;
-                acc += __ldcg(&p.part_o[slot * HD + d]) * scale;
+        if (r < p.group) {
+            for (int sp = threadIdx.x >> 4; sp < n_splits; sp += (WARPS * 32) >> 4) {
+                m = fmaxf(m, __ldcg(&p.part_ml[(slot0 + static_cast<int64_t>(sp) * p.n_heads + r) * 2]));
             }
         }
-        p.out[t * p.out_row_stride + static_cast<int64_t>(kv_head * p.group + r) * HD + d] =
-            __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+        partial[threadIdx.x] = m;
+        __syncthreads();
+        if (threadIdx.x < 16) {
+            for (int i = threadIdx.x + 16; i < WARPS * 32; i += 16) {
+                m = fmaxf(m, partial[i]);
+            }
+            row_max[threadIdx.x] = m;
+            row_sum[threadIdx.x] = 0.0f;
+        }
+        __syncthreads();
+    }
+    float4 acc[(16 * (HD / 4) + WARPS * 32 - 1) / (WARPS * 32)];
+#pragma unroll
+    for (int i = 0; i < static_cast<int>(sizeof(acc) / sizeof(acc[0])); ++i) {
+        acc[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    for (int s0 = 0; s0 < n_splits; s0 += kChunk) {
+        const int count = min(kChunk, n_splits - s0);
+        for (int i = threadIdx.x; i < count * 16; i += WARPS * 32) {
+            const int sp = i >> 4, r = i & 15;
+            float w = 0.0f;
+            if (r < p.group && row_max[r] > -INFINITY) {
+                w = exp2f(__ldcg(&p.part_ml[(slot0 + static_cast<int64_t>(s0 + sp) * p.n_heads + r) * 2]) - row_max[r]);
+            }
+            weight[i] = w;
+        }
+        __syncthreads();
+        if (threadIdx.x < p.group) {  // the row sums, in split order
+            float l = row_sum[threadIdx.x];
+            for (int sp = 0; sp < count; ++sp) {
+                l += __ldcg(&p.part_ml[(slot0 + static_cast<int64_t>(s0 + sp) * p.n_heads + threadIdx.x) * 2 + 1]) *
+                    weight[sp * 16 + threadIdx.x];
+            }
+            row_sum[threadIdx.x] = l;
+        }
+#pragma unroll
+        for (int i = 0; i < static_cast<int>(sizeof(acc) / sizeof(acc[0])); ++i) {
+            const int vec = threadIdx.x + i * WARPS * 32;
+            if (vec < n_vec) {
+                const int r = vec / (HD / 4), d = (vec % (HD / 4)) * 4;
+                const float* from = p.part_o + (slot0 + static_cast<int64_t>(s0) * p.n_heads + r) * HD + d;
+                const int64_t step = static_cast<int64_t>(p.n_heads) * HD;
+                int sp = 0;
+                for (; sp + 8 <= count; sp += 8) {
+                    float4 part[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        part[j] = __ldcg(reinterpret_cast<const float4*>(from + (sp + j) * step));
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float w = weight[(sp + j) * 16 + r];
+                        acc[i].x += part[j].x * w;
+                        acc[i].y += part[j].y * w;
+                        acc[i].z += part[j].z * w;
+                        acc[i].w += part[j].w * w;
+                    }
+                }
+                for (; sp < count; ++sp) {
+                    const float4 part = __ldcg(reinterpret_cast<const float4*>(from + sp * step));
+                    const float w = weight[sp * 16 + r];
+                    acc[i].x += part.x * w;
+                    acc[i].y += part.y * w;
+                    acc[i].z += part.z * w;
+                    acc[i].w += part.w * w;
+                }
+            }
+        }
+        __syncthreads();  // the weights are rewritten by the next pass; the row sums are in place
+    }
+#pragma unroll
+    for (int i = 0; i < static_cast<int>(sizeof(acc) / sizeof(acc[0])); ++i) {
+        const int vec = threadIdx.x + i * WARPS * 32;
+        if (vec < n_vec) {
+            const int r = vec / (HD / 4), d = (vec % (HD / 4)) * 4;
+            const float l = row_sum[r];
+            __nv_bfloat16* dst = p.out + t * p.out_row_stride + static_cast<int64_t>(kv_head * p.group + r) * HD + d;
+            dst[0] = __float2bfloat16_rn(l > 0.0f ? acc[i].x / l : 0.0f);
+            dst[1] = __float2bfloat16_rn(l > 0.0f ? acc[i].y / l : 0.0f);
+            dst[2] = __float2bfloat16_rn(l > 0.0f ? acc[i].z / l : 0.0f);
+            dst[3] = __float2bfloat16_rn(l > 0.0f ? acc[i].w / l : 0.0f);
+        }
     }
 }
 

@@ -123,11 +123,12 @@ def decode_item_ctas(device: torch.device, head_dim: int, n_kv: int) -> int:
 
 
 def decode_work_items(context_lens: list[int], window: int | None, target: int, pad_to: int | None = None,
-                      min_tiles: int = DECODE_ITEM_MIN_TILES) -> tuple[np.ndarray, np.ndarray]:
+                      min_tiles: int = DECODE_ITEM_MIN_TILES, leave_even: bool = True) -> tuple[np.ndarray, np.ndarray]:
     """The work list of a step's single tokens for ops.attention_decode_items: int32
     [items, 4] rows {token, first 16-key tile, tiles, split | splits << 12}, longest first,
     and int32 [tokens] first scratch slot of each token's splits. Requests of about equal
-    length (longest within DECODE_EVEN_ENOUGH of the mean) are not cut: one item each.
+    length (longest within DECODE_EVEN_ENOUGH of the mean) are not cut: one item each
+    (unless `leave_even` is off: few requests, which need cutting to fill the device).
     Else the tiles are cut into about `target` items of equal size, a request's share
     rounded to whole items, so that the CTAs in flight stay many until the end instead of
     the longest requests streaming alone. At most target + tokens items; `pad_to` pads the
@@ -141,7 +142,8 @@ def decode_work_items(context_lens: list[int], window: int | None, target: int, 
     items = np.empty((capacity, 4), dtype=np.int32)
     slots = np.empty(max(n, 1), dtype=np.int32)
     used = core.library().plh_decode_work_items(
-        lengths.ctypes.data, n, int(window or 0), int(target), int(min_tiles), int(round(DECODE_EVEN_ENOUGH * 100)),
+        lengths.ctypes.data, n, int(window or 0), int(target), int(min_tiles),
+        int(round(DECODE_EVEN_ENOUGH * 100)) if leave_even else 0,
         items.ctypes.data, capacity, slots.ctypes.data)
     if used < 0:
         raise ValueError(f"decode_work_items: the host core refused the list (code {used})")
@@ -418,6 +420,10 @@ class Attention(Part):
             measuring = self.cache.mass_sum is not None and self.cache_from is None
             device = self.ctx.device
             reach = min(plan["max_context"], self.window + 16) if self.window else plan["max_context"]
+            # (A work list also for few requests with long, unequal histories, where equal shares
+            # would split, measured better only when the lengths really differ: batch 8 with 1,000
+            # to 60,000 keys 214 -> 169 us, but 32,768 keys each 155 -> 168 us; a captured step
+            # cannot choose per replay, so equal shares stay there.)
             if DECODE_ITEMS and not measuring and 2 + n_decode * self.n_kv <= ops.DECODE_COUNTERS and decode_splits(
                     n_decode * self.n_kv, reach, device, self.head_dim, self.n_heads // self.n_kv) == 1:
                 ctas = decode_item_ctas(device, self.head_dim, self.n_kv)
