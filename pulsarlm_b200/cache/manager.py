@@ -94,6 +94,8 @@ class CacheManager:
         self.n_physical_pages = n_pages + 1
         self.pad_page = n_pages
         self.max_requests = max_requests
+        # Likewise one more state slot than requests: the rows that pad a captured step update it.
+        self.pad_slot = max_requests
         self.dtype = dtype
         self.device = torch.device(device) if device is not None else None
         self.n_layers = len(needs)
@@ -128,7 +130,7 @@ class CacheManager:
                     group.weight_sum = torch.zeros(shape[:2], dtype=torch.float32, device=device)
                     group.step_weight = torch.zeros(shape[:2], dtype=torch.float32, device=device)
             for layer, need in self.state_layers.items():
-                self.states[layer] = torch.zeros((max_requests, *need.shape), dtype=_STATE_DTYPES[need.dtype],
+                self.states[layer] = torch.zeros((max_requests + 1, *need.shape), dtype=_STATE_DTYPES[need.dtype],
                                                  device=device)
         self._lib = core.library()
         windows = (ctypes.c_int32 * max(1, len(self.groups)))(

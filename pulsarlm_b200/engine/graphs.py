@@ -105,12 +105,14 @@ class GraphedDecode:
 
     def pad_rows(self, n_real: int, pad_page: int) -> None:
         """Rows past the step's `n_real` entries: token 0 at position 0 of the cache's
-        padding page, drawn greedily; nothing reads what they compute."""
+        padding page, with the padding state slot, drawn greedily; nothing reads what they
+        compute."""
         if n_real == self.n:
             return
         h = self.h
-        for name in ("tokens", "pos", "slots", "top_k"):
+        for name in ("tokens", "pos", "top_k"):
             h[name][n_real:] = 0
+        h["slots"][n_real:] = self.runner.cache.pad_slot
         h["temperature"][n_real:] = 0.0
         h["top_p"][n_real:] = 2.0
         h["seed"][n_real:] = 0
@@ -152,11 +154,12 @@ class GraphedDecode:
         then records it. The buffers must hold a valid batch."""
         self.dev.copy_(self.host, non_blocking=True)
         # The warm-up run really runs the step. Keys and values are written by position, so
-        # running it twice changes nothing; the attention-mass accumulators are added to, so
-        # they are put back as they were.
+        # running it twice changes nothing; the attention-mass accumulators are added to and
+        # state slots are updated in place, so both are put back as they were.
         cache = self.runner.cache
         kept = [(g.mass_sum, g.mass_sum.clone(), g.weight_sum, g.weight_sum.clone())
                 for g in cache.groups if g.mass_sum is not None]
+        states = [(t, t.clone()) for t in cache.states.values()]  # (updated in place by their mixers)
         # One side stream for every capture of this runner: the allocator keeps freed blocks
         # per stream, so a new stream per capture would strand the warm-up's buffers.
         if self.runner._capture_stream is None:
@@ -169,6 +172,8 @@ class GraphedDecode:
         for mass, mass_before, weight, weight_before in kept:
             mass.copy_(mass_before)
             weight.copy_(weight_before)
+        for state, before in states:
+            state.copy_(before)
         torch.cuda.synchronize()
         self.graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()

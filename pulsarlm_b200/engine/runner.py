@@ -90,12 +90,15 @@ class ModelRunner:
         self._graph_pool = None
         self._capture_stream = None
         self.graph_captures = 0
-        # Replaying a captured step re-runs the capture's warm-up on the same tokens,
-        # which is harmless for caches written by position but not for states updated
-        # in place, so models with state slots step eagerly. With attention mass measured,
+        # Steps of single tokens are captured unless a part cannot take it. A mixer with state
+        # slots must say that its single-token step can be captured (no host round trip in it):
+        # `captures_state_steps()`; the capture's warm-up run then works on a copy of the states
+        # and rows that pad a step use a slot no request holds. With attention mass measured,
         # steps are captured only if every mixer can measure inside one.
-        self.graphs_allowed = not cache.state_layers and (cache.mass_decay is None or all(
-            getattr(part, "measures_mass_in_captured_steps", lambda: True)() for part in model.parts()))
+        state_mixers = [self.model.blocks[layer].mixer for layer in cache.state_layers]
+        self.graphs_allowed = all(getattr(m, "captures_state_steps", lambda: False)() for m in state_mixers) and (
+            cache.mass_decay is None or all(
+                getattr(part, "measures_mass_in_captured_steps", lambda: True)() for part in model.parts()))
         self.steps = 0
         self.tokens_run = 0
         self.graph_steps = 0

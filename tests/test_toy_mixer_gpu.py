@@ -141,3 +141,60 @@ def test_toy_mixer_registers_builds_and_steps(tmp_path):
     logits = runner.step([StepEntry("c", c, list(range(9)))]).cpu()
     assert cache.slot("c") == 0
     assert plain_llama.max_relative_error(logits, plain_toy(cfg, w, c)) < 1e-4
+
+
+def test_a_state_mixer_that_says_so_steps_in_captured_graphs(tmp_path):
+    """The same toy mixer with a single-token step that makes no host round trip
+    (`captures_state_steps`): the engine captures its decode steps. The capture's warm-up
+    run works on a copy of the states, rows that pad a step to its size update the padding
+    slot, and pipelined steps advance a state once each: the tokens generated with graphs
+    and lookahead equal those of eager steps and of the plain implementation."""
+    import plain_llama
+    from pulsarlm_b200 import Engine, SamplingParams
+    from pulsarlm_b200.engine.loading import load_model
+    from pulsarlm_b200.parts.registry import part_class, register_part
+
+    register_toy()
+    eager_class = part_class("mixer", "toy_decay")
+
+    @register_part("mixer", "toy_decay", replace=True)
+    class ToyDecayCapturable(eager_class):
+        def captures_state_steps(self):
+            return True
+
+        def forward(self, h, batch):
+            if int(batch.n_decode) != h.shape[0]:
+                return super().forward(h, batch)  # prompt portions: the loop over an entry's tokens
+            # one token per entry: state[slot] = decay * state[slot] + u, for all entries at once
+            u = h.float() @ self.w_in.T
+            slots = batch.slots.long()
+            states = self.binding.states
+            new = states[slots] * self.decay + u
+            states[slots] = new
+            return (new @ self.w_out.T).to(h.dtype)
+
+    cfg = dict(tiny.TINY_B, architectures=["ToyDecayForCausalLM"])
+    w = tiny.random_weights(cfg, 2)
+    for name in ("q_proj", "k_proj", "v_proj", "o_proj"):
+        del w[f"model.layers.1.self_attn.{name}.weight"]
+    gen = torch.Generator().manual_seed(1)
+    w["model.layers.1.toy.in.weight"] = torch.randn(24, 96, generator=gen) / 10
+    w["model.layers.1.toy.out.weight"] = torch.randn(96, 24, generator=gen) / 5
+    folder = tiny.write_model_dir(str(tmp_path), cfg, w)
+    model = load_model(folder, "float32", DEV)
+    prompts = [tiny.random_tokens(cfg, n, 10 + n) for n in (9, 30, 4)]  # three requests: steps padded to four rows
+    greedy = SamplingParams(temperature=0.0)
+    results = {}
+    for name, options in (("graphs", {}), ("eager", {"cuda_graphs": False})):
+        engine = Engine(model, n_pages=24, page_size=tiny.PAGE_B, max_requests=3, stop_ids=[], **options)
+        assert engine.runner.graphs_allowed
+        results[name] = engine.generate(prompts, greedy, max_tokens=12, ignore_eos=True)
+        assert (engine.runner.graph_steps > 0) == (name == "graphs")
+        # a second round on the same engine: slots are zeroed at hand-out, the padding slot is nobody's
+        assert engine.generate(prompts, greedy, max_tokens=12, ignore_eos=True) == results[name]
+    assert results["graphs"] == results["eager"]
+    for prompt, out in zip(prompts, results["graphs"]):
+        logits = plain_toy(cfg, w, list(prompt) + list(out))
+        for i, token in enumerate(out):
+            row = logits[len(prompt) - 1 + i]
+            assert float(row.max() - row[token]) <= 1e-4 * float(row.abs().max()), (i, token)
