@@ -132,6 +132,10 @@ struct PlLayerStep {
     // library products
     void* library_workspace;
     int64_t library_workspace_bytes;
+    // 1: in a step with both kinds of tokens the two attention kernels run side by side (the
+    // single tokens' on a second stream, forked and joined with events): a prompt portion's
+    // few tiles leave most SMs idle.
+    int attention_side_by_side;
 };
 
 namespace {
@@ -217,6 +221,32 @@ int library_product(const PlLayerStep& s, const void* x, const void* w, void* y,
     return 0;
 }
 
+// The second stream and the two events of the side-by-side attention (one set per process;
+// the engine works on one device and one stream).
+struct SideStream {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+    bool failed = false;
+};
+
+bool side_stream(SideStream& side) {
+    if (side.stream != nullptr) {
+        return true;
+    }
+    if (side.failed) {
+        return false;
+    }
+    if (cudaStreamCreateWithFlags(&side.stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&side.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&side.join, cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        side.failed = true;
+        side.stream = nullptr;
+        return false;
+    }
+    return true;
+}
+
 int product(const PlLayerStep& s, int route, const void* x, const void* w, void* y, int t, int n, int k,
             cudaStream_t stream) {
     switch (route) {
@@ -251,19 +281,41 @@ PL_API int pl_layer_forward(const PlLayerWeights* w, const PlLayerStep* s, cudaS
                                 w->n_pages, w->inv_freq, w->rotary, t, w->n_heads, w->n_kv_heads, hd, PL_BF16, nullptr,
                                 nullptr, 0.0f, s->status, stream);
     }
+    // The single tokens' attention beside the prompt portions' when the step has both and is
+    // not being captured: forked onto a second stream after what they both wait for, joined
+    // before the o projection.
+    static SideStream side;
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    bool forked = false;
+    cudaStream_t decode_stream = stream;
+    if (code == 0 && s->attention_side_by_side && s->n_decode > 0 && s->n_decode < t &&
+        cudaStreamIsCapturing(stream, &capturing) == cudaSuccess && capturing == cudaStreamCaptureStatusNone &&
+        side_stream(side)) {
+        if (cudaEventRecord(side.fork, stream) == cudaSuccess &&
+            cudaStreamWaitEvent(side.stream, side.fork, 0) == cudaSuccess) {
+            forked = true;
+            decode_stream = side.stream;
+        } else {
+            cudaGetLastError();
+        }
+    }
     if (code == 0 && s->n_decode > 0) {
         if (s->items != nullptr) {
             code = pl_attention_decode_items(qkv, qkv_width, w->k_pool, w->v_pool, w->page_stride, w->head_stride,
                                              w->page_size, w->n_pages, s->table, s->table_width, s->pos, s->entry,
                                              attended, q_width, s->n_decode, w->n_heads, w->n_kv_heads, hd, w->window,
                                              w->scale, s->items, s->n_items, s->item_slots, s->decode_scratch,
-                                             s->counters, fold, s->status, stream);
+                                             s->counters, fold, s->status, decode_stream);
         } else {
             code = pl_attention_decode(qkv, qkv_width, w->k_pool, w->v_pool, w->page_stride, w->head_stride,
                                        w->page_size, w->n_pages, s->table, s->table_width, s->pos, s->entry, attended,
                                        q_width, s->n_decode, w->n_heads, w->n_kv_heads, hd, w->window, w->scale,
-                                       s->decode_splits, s->decode_scratch, fold, s->status, stream);
+                                       s->decode_splits, s->decode_scratch, fold, s->status, decode_stream);
         }
+    }
+    if (forked && cudaEventRecord(side.join, side.stream) != cudaSuccess) {
+        return pl_fail(3, "layer_forward: cannot record the side stream's event: %s",
+                       cudaGetErrorString(cudaGetLastError()));
     }
     if (code == 0 && s->n_decode < t) {
         PL_REQUIRE(s->tiles != nullptr && s->n_tiles > 0, "layer_forward: prompt portions need their tile list");
@@ -271,6 +323,9 @@ PL_API int pl_layer_forward(const PlLayerWeights* w, const PlLayerStep* s, cudaS
                                             w->page_size, w->n_pages, s->table, s->table_width, s->tiles, s->n_tiles,
                                             attended, q_width, w->n_heads, w->n_kv_heads, hd, w->window, w->scale,
                                             s->prefill_splits, s->prefill_scratch, s->wide, nullptr, s->status, stream);
+    }
+    if (forked && cudaStreamWaitEvent(stream, side.join, 0) != cudaSuccess) {
+        return pl_fail(3, "layer_forward: cannot join the side stream: %s", cudaGetErrorString(cudaGetLastError()));
     }
     if (code == 0) {
         code = product(*s, s->route_o, attended, w->o, s->mixed, t, w->hidden, q_width, stream);

@@ -25,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 19
+ABI_VERSION = 20
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 

@@ -25,6 +25,8 @@ from ..kernels import ops
 from . import linear
 
 ENABLED = os.environ.get("PULSARLM_B200_NATIVE_LAYERS", "1") != "0"
+# (0: the two attention kernels of a step with both kinds of tokens one after the other)
+SIDE_BY_SIDE = os.environ.get("PULSARLM_B200_ATTENTION_SIDE_BY_SIDE", "1") != "0"
 
 _PTR, _I32, _I64, _F32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
 
@@ -47,7 +49,7 @@ class LayerStep(ctypes.Structure):
                 ("decode_splits", _I32), ("decode_scratch", _PTR),
                 ("tiles", _PTR), ("n_tiles", _I32), ("wide", _I32), ("prefill_splits", _I32),
                 ("prefill_scratch", _PTR),
-                ("library_workspace", _PTR), ("library_workspace_bytes", _I64)]
+                ("library_workspace", _PTR), ("library_workspace_bytes", _I64), ("attention_side_by_side", _I32)]
 
 
 ROUTES = {None: 0, "skinny": 1, "pair": 2}
@@ -161,7 +163,7 @@ class StepState:
             tiles.data_ptr() if tiles is not None else None, tiles.shape[0] if tiles is not None else 0,
             int(c["wide"]), int(c["prefill_splits"]),
             self.scratch[decode_floats:].data_ptr(),
-            workspace.data_ptr(), workspace.numel())
+            workspace.data_ptr(), workspace.numel(), int(SIDE_BY_SIDE))
         # how many of the package's own kernels one call launches (library products are not ours)
         routes = (self.struct.route_qkv, self.struct.route_o, self.struct.route_gate_up, self.struct.route_down)
         self.launches = (2 + sum(1 for r in routes if r != 0) + (0 if c["fold_rope"] else 1)
