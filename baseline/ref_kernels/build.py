@@ -32,7 +32,7 @@ def load(reference: str | None = None, build: bool = True):
     import torch  # noqa: F401  (the extension links against it)
     from torch.utils import cpp_extension
 
-    reference = reference or os.environ.get("PULSARLM_REFERENCE", "/root/reference")
+    reference = reference or os.environ.get("PULSARLM_REFERENCE") or os.path.join(os.path.expanduser("~"), "reference")
     built = os.path.join(OUT, NAME + ".so")
     if os.path.isfile(built):
         import importlib.util
