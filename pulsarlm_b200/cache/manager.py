@@ -7,7 +7,9 @@ form a group. A group has its own page pool: one tensor
 page is never handed out: padding rows of captured steps use it), so one page
 id holds `page_size` tokens of every layer of the group, and a request has one
 block table per group. Groups with a window give pages back as soon as every
-token in them is out of every future query's reach. Mixers that ask for a
+token in them is out of every future query's reach, and when the caller bounds
+the tokens a request brings to one step their pools are made only as large as
+`max_requests` such requests can fill (`window_pages`). Mixers that ask for a
 StateNeed get a row per request slot in a tensor [slots, *shape], zeroed when
 the slot is handed out.
 
@@ -60,6 +62,7 @@ class _Group:
     layers: list[int]
     pool: GroupPoolView | None
     tensor: torch.Tensor | None
+    n_pages: int = 0    # pages the pool hands out; page `n_pages` of the tensor is the padding page
     # attention mass, when measured: accumulators and this step's sums
     mass_sum: torch.Tensor | None = None     # [layers, pages, query heads]
     weight_sum: torch.Tensor | None = None   # [layers, pages]
@@ -70,11 +73,47 @@ class _Group:
 _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
 
 
+def window_pages(window: int, page_size: int, step_tokens: int, max_requests: int) -> int:
+    """Pages that `max_requests` requests can hold at once in a group whose queries
+    reach `window` keys back, when no request brings more than `step_tokens` tokens to
+    a step. A request of length L that reserves n more tokens holds the pages from
+    that of key L - window + 1 to that of key L + n - 1: fewer than
+    (window + n - 1) / page_size + 2. One token more, for a step that is reserved
+    while the step before it has not been committed."""
+    per_request = -(-(window + step_tokens + 1) // page_size) + 1
+    return max_requests * per_request
+
+
+def pool_pages(need: KVCacheNeed, n_pages: int, page_size: int, step_tokens: int | None, max_requests: int) -> int:
+    """Pages of the pool of a group with this need, when groups that keep every key get n_pages."""
+    if need.window is None or step_tokens is None:
+        return n_pages
+    return min(n_pages, window_pages(need.window, page_size, step_tokens, max_requests))
+
+
+def cache_bytes(needs: list, n_pages: int, page_size: int, step_tokens: int | None, max_requests: int,
+                dtype: torch.dtype) -> int:
+    """Bytes of the page tensors `CacheManager(needs, page_size, n_pages, ...)` would make
+    (without the padding pages)."""
+    width = torch.empty((), dtype=dtype).element_size()
+    layers: dict[KVCacheNeed, int] = {}
+    for need in needs:
+        if isinstance(need, KVCacheNeed):
+            layers[need] = layers.get(need, 0) + 1
+    return sum(pool_pages(need, n_pages, page_size, step_tokens, max_requests)
+               * count * 2 * need.n_kv_heads * page_size * need.head_dim * width for need, count in layers.items())
+
+
 class CacheManager:
     def __init__(self, needs: list, page_size: int, n_pages: int, max_requests: int, dtype: torch.dtype,
-                 device: torch.device | str | None, allocate: bool = True, mass_decay: float | None = None):
-        """needs: per layer KVCacheNeed, StateNeed or None. n_pages: pages of every
-        group's pool. allocate=False keeps the bookkeeping only (no tensors).
+                 device: torch.device | str | None, allocate: bool = True, mass_decay: float | None = None,
+                 step_tokens: int | None = None):
+        """needs: per layer KVCacheNeed, StateNeed or None. n_pages: pages of the pool
+        of a group that keeps every key. step_tokens: the most tokens one request
+        brings to a step, if the caller keeps to such a bound (a scheduler's token
+        budget); a group with a window then gets `window_pages(...)` pages when that
+        is fewer. Without it every group gets n_pages.
+        allocate=False keeps the bookkeeping only (no tensors).
         mass_decay: when given (0 < a <= 1), per-page attention-mass accumulators are
         kept: each step the attention kernel adds, for every page a query attends,
         w * (the query's largest scaled score in the page) per head and w per page,
@@ -89,10 +128,6 @@ class CacheManager:
         self.mass_decay = mass_decay
         self.page_size = page_size
         self.n_pages = n_pages
-        # One more page than the pools hand out: the padding page, which no request ever
-        # holds. Rows that pad a captured decode step to its size write and read there.
-        self.n_physical_pages = n_pages + 1
-        self.pad_page = n_pages
         self.max_requests = max_requests
         # Likewise one more state slot than requests: the rows that pad a captured step update it.
         self.pad_slot = max_requests
@@ -117,14 +152,19 @@ class CacheManager:
                 self.state_layers[layer] = need
             elif need is not None:
                 raise ValueError(f"layer {layer}: unknown cache need {need!r}")
+        for group in self.groups:
+            group.n_pages = pool_pages(group.need, n_pages, page_size, step_tokens, max_requests)
         if allocate:
+            # One more page than a pool hands out: the padding page (`group.n_pages`), which no
+            # request ever holds. Rows that pad a captured decode step to its size write and read there.
             for group in self.groups:
                 n = group.need
                 group.tensor = torch.zeros(
-                    (len(group.layers), n_pages + 1, 2, n.n_kv_heads, page_size, n.head_dim), dtype=dtype, device=device)
+                    (len(group.layers), group.n_pages + 1, 2, n.n_kv_heads, page_size, n.head_dim), dtype=dtype,
+                    device=device)
             if mass_decay is not None:
                 for group in self.groups:
-                    shape = (len(group.layers), n_pages + 1, max(1, group.need.n_heads))
+                    shape = (len(group.layers), group.n_pages + 1, max(1, group.need.n_heads))
                     group.mass_sum = torch.zeros(shape, dtype=torch.float32, device=device)
                     group.step_mass = torch.zeros(shape, dtype=torch.float32, device=device)
                     group.weight_sum = torch.zeros(shape[:2], dtype=torch.float32, device=device)
@@ -135,10 +175,11 @@ class CacheManager:
         self._lib = core.library()
         windows = (ctypes.c_int32 * max(1, len(self.groups)))(
             *[g.need.window if g.need.window is not None else -1 for g in self.groups])
-        self._book = self._lib.plh_cache_create(len(self.groups), windows, page_size, n_pages, max_requests,
+        pages = (ctypes.c_int32 * max(1, len(self.groups)))(*[g.n_pages for g in self.groups])
+        self._book = self._lib.plh_cache_create(len(self.groups), windows, page_size, pages, max_requests,
                                                 int(mass_decay is not None))
         for group in self.groups:
-            group.pool = GroupPoolView(self._lib, self._book, group.index, n_pages)
+            group.pool = GroupPoolView(self._lib, self._book, group.index, group.n_pages)
         # The caller's request keys (any hashable) <-> the book's integer handles.
         self._handles: dict[object, int] = {}
         self._keys: dict[int, object] = {}
@@ -203,9 +244,13 @@ class CacheManager:
         return out
 
     def bytes_per_page(self) -> int:
+        """Bytes of one page id in every group (a token count's worth of every layer)."""
+        return sum(self.group_bytes_per_page(g.index) for g in self.groups)
+
+    def group_bytes_per_page(self, group: int) -> int:
+        g = self.groups[group]
         width = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.layers) * 2 * g.need.n_kv_heads * self.page_size * g.need.head_dim * width
-                   for g in self.groups)
+        return len(g.layers) * 2 * g.need.n_kv_heads * self.page_size * g.need.head_dim * width
 
     # ------------------------------------------------------------------ requests
     def open(self, request) -> int | None:
@@ -326,14 +371,14 @@ class CacheManager:
         return longest
 
     def held_pages(self, request, group: int) -> list[int]:
-        n = self._lib.plh_cache_held_pages(self._book, group, self._known(request), self._row, self.n_pages)
+        n = self._lib.plh_cache_held_pages(self._book, group, self._known(request), self._row, len(self._row))
         return list(self._row[:n])
 
     # ------------------------------------------------------------------ attention mass
     def take_fresh_pages(self, group: int) -> list[int]:
         """Pages of `group` taken since the last call: their accumulators hold a former
         owner's sums until the next fold clears them."""
-        n = self._lib.plh_cache_take_fresh(self._book, group, self._row, self.n_pages)
+        n = self._lib.plh_cache_take_fresh(self._book, group, self._row, len(self._row))
         return list(self._row[:n])
 
     def fold_mass(self, retained: dict[int, torch.Tensor]) -> None:

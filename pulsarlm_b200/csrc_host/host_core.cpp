@@ -42,11 +42,12 @@ bool PagePool::give(const int* pages, int count) {
 
 // ------------------------------------------------------------------ CacheBook
 
-CacheBook::CacheBook(int n_groups, const int* windows, int page_size, int n_pages, int max_requests, bool track_fresh)
+CacheBook::CacheBook(int n_groups, const int* windows, int page_size, const int* n_pages, int max_requests,
+                     bool track_fresh)
 : page_size_(page_size), max_requests_(max_requests), track_fresh_(track_fresh) {
     for (int g = 0; g < n_groups; ++g) {
         windows_.push_back(windows != nullptr ? windows[g] : -1);
-        pools_.emplace_back(n_pages);
+        pools_.emplace_back(n_pages[g]);  // (a group whose window lets pages go needs fewer than one that keeps all)
         fresh_.emplace_back();
     }
     for (int slot = max_requests - 1; slot >= 0; --slot) {
@@ -443,7 +444,7 @@ using plh::CacheBook;
 using plh::PagePool;
 using plh::SchedulerCore;
 
-PLH_API int plh_abi_version() { return 3; }
+PLH_API int plh_abi_version() { return 4; }
 
 PLH_API void* plh_pool_create(int n_pages) { return new PagePool(n_pages); }
 PLH_API void plh_pool_destroy(void* pool) { delete static_cast<PagePool*>(pool); }
@@ -465,8 +466,8 @@ PLH_API int plh_pool_stat(void* pool, int what) {
 }
 PLH_API int plh_pool_is_held(void* pool, int page) { return static_cast<PagePool*>(pool)->is_held(page) ? 1 : 0; }
 
-PLH_API void* plh_cache_create(int n_groups, const int32_t* windows, int page_size, int n_pages, int max_requests,
-                               int track_fresh) {
+PLH_API void* plh_cache_create(int n_groups, const int32_t* windows, int page_size, const int32_t* n_pages,
+                               int max_requests, int track_fresh) {
     return new CacheBook(n_groups, windows, page_size, n_pages, max_requests, track_fresh != 0);
 }
 PLH_API void plh_cache_destroy(void* cache) { delete static_cast<CacheBook*>(cache); }

@@ -55,7 +55,7 @@ enum Code : int {
 // gave the page back).
 class CacheBook {
 public:
-    CacheBook(int n_groups, const int* windows, int page_size, int n_pages, int max_requests, bool track_fresh);
+    CacheBook(int n_groups, const int* windows, int page_size, const int* n_pages, int max_requests, bool track_fresh);
 
     int open(int64_t request);  // slot, kNoRoom as -100, or kAlreadyOpen
     bool is_open(int64_t request) const { return requests_.count(request) != 0; }

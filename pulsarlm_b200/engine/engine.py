@@ -18,7 +18,7 @@ from typing import Iterator
 
 import torch
 
-from ..cache.manager import CacheManager
+from ..cache.manager import CacheManager, cache_bytes
 from ..kernels import ops
 from ..models.model import Model
 from ..sampling.params import SamplingParams
@@ -38,6 +38,25 @@ class _Flight:
         self.ids = ids          # int32 [entries] on the device
         self.pending = pending  # their copy to the host
         self.logits = logits    # with record_logits: a copy of the rows the ids were drawn from
+
+
+def pages_for_bytes(needs: list, page_size: int, max_requests: int, dtype: torch.dtype, step_tokens: int,
+                    budget: int) -> int:
+    """The largest n_pages whose cache fits `budget` bytes: groups that keep every key get
+    n_pages pages each, groups with a window at most what their requests can hold."""
+    def total(n: int) -> int:
+        return cache_bytes(needs, n, page_size, step_tokens, max_requests, dtype)
+
+    low, high = 1, 2
+    while total(high) <= budget and total(high) > total(low) and high < 1 << 30:
+        low, high = high, high * 2
+    while high - low > 1:
+        mid = (low + high) // 2
+        if total(mid) <= budget:
+            low = mid
+        else:
+            high = mid
+    return low
 
 
 class Engine:
@@ -69,12 +88,14 @@ class Engine:
         else:
             self.model = load_model(str(model), self.dtype, self.device)
         needs = self.model.cache_needs()
+        # The scheduler gives a request at most prefill_tokens_per_step tokens a step, so a layer
+        # group with a window needs only the pages that max_requests such requests can hold.
+        step_tokens = max(1, int(prefill_tokens_per_step))
         if n_pages is None:
-            probe = CacheManager(needs, page_size, 1, 1, self.dtype, None, allocate=False)
-            per_page = max(1, probe.bytes_per_page())
-            n_pages = max(1, int(kv_cache_gib * (1 << 30)) // per_page)
+            n_pages = pages_for_bytes(needs, page_size, max_requests, self.dtype, step_tokens,
+                                      int(kv_cache_gib * (1 << 30)))
         self.cache = CacheManager(needs, page_size, n_pages, max_requests, self.dtype, self.device,
-                                  mass_decay=attention_mass_decay)
+                                  mass_decay=attention_mass_decay, step_tokens=step_tokens)
         self.runner = ModelRunner(self.model, self.cache)
         self.runner._bind()
         # Said once: a shape that the fast kernels do not take still runs, only slower.

@@ -103,8 +103,8 @@ class GraphedDecode:
                         first_rows=list(range(n)), page_size=self.runner.cache.page_size, fixed_shape=True,
                         context_bound=self.bound)
 
-    def pad_rows(self, n_real: int, pad_page: int) -> None:
-        """Rows past the step's `n_real` entries: token 0 at position 0 of the cache's
+    def pad_rows(self, n_real: int) -> None:
+        """Rows past the step's `n_real` entries: token 0 at position 0 of each group's
         padding page, with the padding state slot, drawn greedily; nothing reads what they
         compute."""
         if n_real == self.n:
@@ -120,7 +120,7 @@ class GraphedDecode:
         for g in self.runner.cache.groups:
             table = h[f"table{g.index}"]
             table[n_real:] = -1
-            table[n_real:, 0] = pad_page
+            table[n_real:, 0] = g.n_pages  # (the group's padding page)
 
     def plan(self, context_lens: list[int]) -> None:
         """Refreshes the arrays the parts planned, for this replay's lengths."""

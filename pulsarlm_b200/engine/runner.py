@@ -232,7 +232,7 @@ class ModelRunner:
                 at += n
             arrays.append(weights.view(np.int32))
             for g in self.cache.groups:
-                keep = np.ones(self.cache.n_physical_pages, dtype=np.float32)
+                keep = np.ones(g.n_pages + 1, dtype=np.float32)
                 for e in entries:
                     keep[self.cache.held_pages(e.request, g.index)] = (1.0 - decay) ** len(e.tokens)
                 keep[list(self.cache.take_fresh_pages(g.index))] = 0.0
@@ -333,7 +333,7 @@ class ModelRunner:
             # the last eager step is not needed and must not reach that step.
             for g in self.cache.groups:
                 self.cache.take_fresh_pages(g.index)
-        graph.pad_rows(n, self.cache.pad_page)
+        graph.pad_rows(n)
         graph.plan(new_lens)
         if fresh:
             graph.capture()

@@ -11,7 +11,7 @@ from ..kernels import build
 _I32, _I64, _PTR = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 # return codes of csrc_host/host_core.hpp
 OK, NO_ROOM = 0, 1
@@ -26,7 +26,7 @@ _SIGNATURES = {
     "plh_pool_give": ([_PTR, _PTR, _I32], _I32),
     "plh_pool_stat": ([_PTR, _I32], _I32),
     "plh_pool_is_held": ([_PTR, _I32], _I32),
-    "plh_cache_create": ([_I32, _PTR, _I32, _I32, _I32, _I32], _PTR),
+    "plh_cache_create": ([_I32, _PTR, _I32, _PTR, _I32, _I32], _PTR),
     "plh_cache_destroy": ([_PTR], None),
     "plh_cache_open": ([_PTR, _I64], _I32),
     "plh_cache_is_open": ([_PTR, _I64], _I32),

@@ -133,3 +133,59 @@ def test_random_orders_keep_the_invariants(seed):
     for rid in list(lengths):
         m.close(rid)
     assert all(g.pool.used_count == 0 for g in m.groups) and m.stats()["slots_used"] == 0
+
+
+def test_a_windowed_group_gets_only_the_pages_its_requests_can_hold():
+    import torch
+
+    needs = [KVCacheNeed(2, 8), KVCacheNeed(2, 8, window=10), KVCacheNeed(2, 8, window=300)]
+    m = CacheManager(needs, 4, 100, 3, torch.float32, None, allocate=False, step_tokens=6)
+    # window 10, at most 6 tokens a step, pages of 4: ceil(17 / 4) + 1 = 6 pages a request
+    assert [g.pool.n_pages for g in m.groups] == [100, 3 * 6, 100]
+    # without a bound on a step's tokens every group is sized alike
+    same = CacheManager(needs, 4, 100, 3, torch.float32, None, allocate=False)
+    assert [g.pool.n_pages for g in same.groups] == [100, 100, 100]
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_the_smaller_pool_of_a_windowed_group_never_runs_out_first(seed):
+    """Requests that bring at most `step_tokens` tokens a step: as long as the group that
+    keeps every key has room, so has the windowed one (also when the step before is
+    committed only after the next was reserved, as pipelined decode steps do)."""
+    import torch
+
+    rng = random.Random(seed)
+    page, window, step_tokens, slots = rng.choice([2, 4, 8]), rng.randint(1, 40), rng.randint(1, 12), 3
+    needs = [KVCacheNeed(1, 4), KVCacheNeed(1, 4, window=window)]
+    m = CacheManager(needs, page, 4000, slots, torch.float32, None, allocate=False, step_tokens=step_tokens)
+    assert m.groups[1].pool.n_pages < 4000
+    lengths, late = {}, {}
+    for step in range(600):
+        live = list(lengths)
+        if len(live) < slots and rng.random() < 0.3:
+            name = f"r{step}"
+            assert m.open(name) is not None
+            lengths[name] = 0
+        elif live and rng.random() < 0.05:
+            name = rng.choice(live)
+            m.close(name)
+            del lengths[name]
+            late.pop(name, None)
+        for name in lengths:
+            n = rng.randint(1, step_tokens) if lengths[name] == 0 or rng.random() < 0.3 else 1
+            if name in late:
+                # a single token reserved before the step before it is committed
+                assert m.reserve(name, late[name] + 1)
+                m.commit(name, late[name])
+                m.commit(name, late[name] + 1)
+                lengths[name] = late.pop(name) + 1
+                continue
+            new_len = lengths[name] + n
+            assert m.reserve(name, new_len), (name, lengths[name], n, m.stats())
+            if rng.random() < 0.3:
+                late[name] = new_len
+            else:
+                m.commit(name, new_len)
+            lengths[name] = new_len
+        check_invariants(m)
+        assert m.groups[1].pool.high_water <= m.groups[1].pool.n_pages

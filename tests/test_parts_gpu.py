@@ -279,6 +279,60 @@ def test_windows_at_tensor_core_head_sizes_with_long_histories(seed):
         assert err < TOLERANCE["bfloat16"], (r, err, cfg, windows)
 
 
+@pytest.mark.parametrize("seed", [1, 4, 6])
+def test_windowed_groups_with_pools_of_their_own_size_through_the_engine(seed):
+    """A windowed layer beside a full one through `Engine` (scheduler, captured decode steps
+    with padding rows, pipelined or not): the windowed group's pool is only as large as its
+    requests can fill, so the two groups' page ids and padding pages differ; more requests
+    than fit at once keep the pools turning over. Logits of every generated token against
+    the plain implementation."""
+    import random
+
+    from harness import TOLERANCE, record_error
+    from pulsarlm_b200 import Engine, SamplingParams
+    from pulsarlm_b200.models.model import Model
+    from pulsarlm_b200.weights.loader import check_tensors
+
+    rng = random.Random(seed)
+    n_kv = rng.choice([1, 2])
+    cfg = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 2,
+           "hidden_size": 128, "num_attention_heads": n_kv * rng.choice([1, 2, 4]),
+           "num_key_value_heads": n_kv, "head_dim": rng.choice([64, 128]), "intermediate_size": 256,
+           "vocab_size": 300, "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+           "max_position_embeddings": 8192}
+    w = tiny.random_weights(cfg, seed, torch.bfloat16)
+    spec = llama_spec(cfg)
+    windows = {rng.choice([0, 1]): rng.choice([17, 40, 100])}
+    for layer, window in windows.items():
+        spec.layers[layer].mixer.params["window"] = window
+    model = Model(spec, torch.bfloat16, DEV)
+    model.load(check_tensors("test", model.tensor_needs(), w, torch.bfloat16, DEV))
+    prompts = [tiny.random_tokens(cfg, rng.choice([5, 90, 300, 520]), 31 * seed + i) for i in range(7)]
+    new_tokens, page, slots = 20, 16, 3
+    portion = rng.choice([32, 64])
+    engine = Engine(model, n_pages=3 * (-(-(540 + new_tokens) // page) + 1), page_size=page, max_requests=slots,
+                    prefill_tokens_per_step=portion, stop_ids=[], lookahead=seed % 2 == 0, record_logits=True)
+    full, windowed = (engine.cache.groups[engine.cache.layer_group[layer]] for layer in (1 - list(windows)[0],
+                                                                                         list(windows)[0]))
+    assert windowed.n_pages < full.n_pages and windowed.tensor.shape[1] == windowed.n_pages + 1
+    requests = [engine.submit(p, sampling=SamplingParams(temperature=0.0), max_tokens=new_tokens, ignore_eos=True)
+                for p in prompts]
+    while any(not r.finished for r in requests):
+        engine.step()
+    engine.sync()
+    engine.runner.check_status()
+    assert engine.runner.graph_steps > 0
+    assert windowed.pool.high_water <= windowed.n_pages and engine.scheduler.preemptions == 0
+    for prompt, request in zip(prompts, requests):
+        output = list(request.output)
+        assert len(output) == new_tokens == len(request.logits)
+        want = plain_variant(cfg, w, list(prompt) + output[:-1], spec.order, windows=windows)
+        err = plain_llama.max_relative_error(torch.stack(request.logits), want[len(prompt) - 1:])
+        record_error("bfloat16", "windowed group with a pool of its own size through the engine", err,
+                     TOLERANCE["bfloat16"])
+        assert err < TOLERANCE["bfloat16"], (err, cfg, windows)
+
+
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("cfg_key", ["A", "B"])
 def test_attention_with_per_head_norms_and_squashed_scores(dtype, tol, cfg_key):
