@@ -106,10 +106,12 @@ template <int HD, int WARPS, int STAGES>
 __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, unsigned char* smem, const int split,
                                                        const int kv_head, const int t, const int n_splits,
                                                        const int item_first, const int item_tiles) {
-    constexpr int kRowBytes = HD * 2;
-    constexpr int kChunks = HD / 8;             // 16-byte chunks per row
-    constexpr int kTileBytes = kTile * kRowBytes;
+    constexpr int kRowBytes = HD * 2;            // a row of the cache
+    constexpr int kRowSmem = padded_row_bytes(HD);  // a row in shared memory (the swizzle stays inside it)
+    constexpr int kChunks = HD / 8;              // 16-byte chunks per row
+    constexpr int kTileBytes = kTile * kRowSmem;
     constexpr int kStageBytes = 2 * kTileBytes;  // K tile then V tile
+    constexpr bool kFoldsRope = HD % 32 == 0;    // (a rotated pair's halves lie in whole fragments of q)
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, tig = lane & 3;
@@ -138,7 +140,7 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
     const int t1 = min(t0 + per_split, tile_end);
     const int32_t* row = p.table + static_cast<int64_t>(p.entry[t]) * p.table_width;
     __shared__ float rope_cs[HD / 2], rope_sn[HD / 2];
-    if (p.rope_freq != nullptr && threadIdx.x < HD / 2) {  // (the position is a step input: before the wait)
+    if (kFoldsRope && p.rope_freq != nullptr && threadIdx.x < HD / 2) {  // (the position is a step input: before the wait)
         rope_sincos(ctx - 1, p.rope_freq[threadIdx.x], rope_cs[threadIdx.x], rope_sn[threadIdx.x]);
     }
 
@@ -170,7 +172,7 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
 #pragma unroll
             for (int c = lane; c < kTile * kChunks; c += 32) {
                 const int r = c / kChunks, ch = c % kChunks;
-                const int dst = r * kRowBytes + ((ch ^ (r & 7)) * 16);
+                const int dst = r * kRowSmem + ((ch ^ (r & 7)) * 16);
                 cp_async_16(stage + dst, ksrc + r * kRowBytes + ch * 16);
                 cp_async_16(stage + kTileBytes + dst, vsrc + r * kRowBytes + ch * 16);
             }
@@ -205,7 +207,7 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
     uint32_t qa[HD / 16][4];
     const __nv_bfloat16* qbase = p.q + t * p.q_row_stride + static_cast<int64_t>(kv_head) * p.group * HD;
     const bool lo_ok = g < p.group, hi_ok = g + 8 < p.group;
-    if (p.rope_freq == nullptr) {
+    if (!kFoldsRope || p.rope_freq == nullptr) {
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
             const int d = 16 * kk + 2 * tig;
@@ -285,7 +287,7 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
             for (int kk = 0; kk < HD / 16; ++kk) {
                 uint32_t b[4];
                 const int chunk = 2 * kk + (mi & 1);
-                ldmatrix_x4(b, stage + key * kRowBytes + ((chunk ^ (key & 7)) * 16));
+                ldmatrix_x4(b, stage + key * kRowSmem + ((chunk ^ (key & 7)) * 16));
                 mma_bf16(s[0], qa[kk], b[0], b[1]);
                 mma_bf16(s[1], qa[kk], b[2], b[3]);
             }
@@ -353,7 +355,7 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
             for (int dp = 0; dp < HD / 16; ++dp) {
                 uint32_t b[4];
                 const int chunk = 2 * dp + (mi >> 1);
-                ldmatrix_x4_trans(b, vt + key * kRowBytes + ((chunk ^ (key & 7)) * 16));
+                ldmatrix_x4_trans(b, vt + key * kRowSmem + ((chunk ^ (key & 7)) * 16));
                 mma_bf16(o[2 * dp], pa, b[0], b[1]);
                 mma_bf16(o[2 * dp + 1], pa, b[2], b[3]);
             }
@@ -636,7 +638,7 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
 // queue's head and counters[1] counts the CTAs that found it empty; the last of them puts
 // both back to zero for the next launch.
 template <int HD, int WARPS, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32, HD == 64 ? 4 : 2) attention_decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(WARPS * 32, HD <= 64 ? 4 : 2) attention_decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     pl_grid_trigger();  // positions and block tables are step inputs, read before the wait
     // One loop for both modes (the share's code once, and few registers live across it): with
@@ -722,12 +724,27 @@ constexpr int kWarps = 4;
 // Ring depth per warp. (Six stages at head size 64, the same bytes as three at 128, measured slower: two CTAs
 // per SM instead of four, 47.9 -> 55.4 us at batch 64 and 2,400 keys. The kernel wants warps, not depth.)
 constexpr int stages_of(int) { return 3; }
+// Shared memory of the warps' rings at one head size.
+constexpr int ring_bytes(int head_dim) { return kWarps * stages_of(head_dim) * 2 * kTile * padded_row_bytes(head_dim); }
+
+// `return CALL(HD);` with the head size as a constant, for the sizes the kernel is built for.
+#define PL_DECODE_HEAD_SIZES(head_dim, CALL, otherwise) \
+    switch (head_dim) {                                 \
+        case 32: return CALL(32);                       \
+        case 48: return CALL(48);                       \
+        case 64: return CALL(64);                       \
+        case 80: return CALL(80);                       \
+        case 96: return CALL(96);                       \
+        case 112: return CALL(112);                     \
+        case 128: return CALL(128);                     \
+        default: return otherwise;                      \
+    }
 
 constexpr int kClusterSplitsMax = 16;  // the largest cluster the part takes (above 8: opted into per kernel)
 
 template <int HD>
 int launch_decode(const DecodeParams& params, int n_tokens, int n_kv_heads, bool allow_cluster, cudaStream_t stream) {
-    constexpr int rings = kWarps * stages_of(HD) * 2 * kTile * HD * 2;
+    constexpr int rings = ring_bytes(HD);
     static_assert(rings >= kWarps * 16 * (HD + 2) * 4, "the merge buffers must fit in the rings");
     constexpr int most_merge = merge_bytes(16 * (HD / 4), kClusterSplitsMax) + 1024;
     static bool configured = false, big_clusters = false;
@@ -822,17 +839,14 @@ int launch_decode(const DecodeParams& params, int n_tokens, int n_kv_heads, bool
 // 1 when pl_attention_decode takes this shape, else 0 (the caller then uses the
 // CUDA-core kernel, which takes every shape).
 PL_API int pl_attention_decode_supports(int head_dim, int group, int page_size, int dtype) {
-    return dtype == PL_BF16 && (head_dim == 64 || head_dim == 128) && group >= 1 && group <= 16 &&
-        page_size % kTile == 0;
+    return dtype == PL_BF16 && head_dim % 16 == 0 && head_dim >= 32 && head_dim <= 128 && group >= 1 &&
+        group <= 16 && page_size % kTile == 0;
 }
 
-// How many clusters of `n_splits` CTAs of the decode kernel the device holds at once
-// (0: unknown or not a cluster size). A launch with more (kv head, token) pairs than
-// this runs its clusters in more than one wave.
-PL_API int pl_attention_decode_resident_clusters(int head_dim, int group, int n_splits) {
-    if (n_splits < 2 || n_splits > kClusterSplitsMax || (head_dim != 64 && head_dim != 128)) {
-        return 0;
-    }
+namespace {
+
+template <int HD>
+int resident_clusters_of(int group, int n_splits) {
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(n_splits, 64, 64);
     config.blockDim = dim3(kWarps * 32);
@@ -844,29 +858,46 @@ PL_API int pl_attention_decode_resident_clusters(int head_dim, int group, int n_
     config.attrs = attribute;
     config.numAttrs = 1;
     int clusters = 0;
-    cudaError_t err;
-    if (head_dim == 64) {
-        constexpr int rings = kWarps * stages_of(64) * 2 * kTile * 64 * 2;
-        cudaFuncSetAttribute(attention_decode_kernel<64, kWarps, stages_of(64)>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             rings + merge_bytes(16 * 16, kClusterSplitsMax) + 1024);
-        cudaFuncSetAttribute(attention_decode_kernel<64, kWarps, stages_of(64)>,
-                             cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-        config.dynamicSmemBytes = rings + merge_bytes(group * 16, n_splits);
-        err = cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel<64, kWarps, stages_of(64)>, &config);
-    } else {
-        constexpr int rings = kWarps * stages_of(128) * 2 * kTile * 128 * 2;
-        cudaFuncSetAttribute(attention_decode_kernel<128, kWarps, stages_of(128)>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             rings + merge_bytes(16 * 32, kClusterSplitsMax) + 1024);
-        cudaFuncSetAttribute(attention_decode_kernel<128, kWarps, stages_of(128)>,
-                             cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-        config.dynamicSmemBytes = rings + merge_bytes(group * 32, n_splits);
-        err = cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel<128, kWarps, stages_of(128)>, &config);
-    }
-    if (err != cudaSuccess) {
+    constexpr int rings = ring_bytes(HD);
+    cudaFuncSetAttribute(attention_decode_kernel<HD, kWarps, stages_of(HD)>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         rings + merge_bytes(16 * (HD / 4), kClusterSplitsMax) + 1024);
+    cudaFuncSetAttribute(attention_decode_kernel<HD, kWarps, stages_of(HD)>,
+                         cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    config.dynamicSmemBytes = rings + merge_bytes(group * (HD / 4), n_splits);
+    if (cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel<HD, kWarps, stages_of(HD)>, &config) !=
+        cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
     return clusters;
+}
+
+template <int HD>
+int ctas_per_sm_of() {
+    int ctas = 0;
+    constexpr int rings = ring_bytes(HD);
+    cudaFuncSetAttribute(attention_decode_kernel<HD, kWarps, stages_of(HD)>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         rings + merge_bytes(16 * (HD / 4), kClusterSplitsMax) + 1024);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, attention_decode_kernel<HD, kWarps, stages_of(HD)>,
+                                                      kWarps * 32, rings) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return ctas;
+}
+
+}  // namespace
+
+// How many clusters of `n_splits` CTAs of the decode kernel the device holds at once
+// (0: unknown or not a cluster size). A launch with more (kv head, token) pairs than
+// this runs its clusters in more than one wave.
+PL_API int pl_attention_decode_resident_clusters(int head_dim, int group, int n_splits) {
+    if (n_splits < 2 || n_splits > kClusterSplitsMax) {
+        return 0;
+    }
+#define PL_CALL(HD) resident_clusters_of<HD>(group, n_splits)
+    PL_DECODE_HEAD_SIZES(head_dim, PL_CALL, 0)
+#undef PL_CALL
 }
 
 // Scratch floats needed for `n_tokens` tokens at `n_splits` splits.
@@ -888,7 +919,7 @@ int run_attention_decode(bool allow_cluster, const void* q, int64_t q_row_stride
                "attention_decode: bad sizes tokens=%d heads=%d kv_heads=%d", n_tokens, n_heads, n_kv_heads);
     const int group = n_heads / n_kv_heads;
     PL_REQUIRE(pl_attention_decode_supports(head_dim, group, page_size, PL_BF16),
-               "attention_decode: unsupported shape head_dim=%d group=%d page=%d (takes head_dim 64 or 128, "
+               "attention_decode: unsupported shape head_dim=%d group=%d page=%d (takes head sizes 32 to 128 in steps of 16, "
                "groups of at most 16 heads, pages that are multiples of 16 tokens)",
                head_dim, group, page_size);
     PL_REQUIRE(n_splits >= 1 && n_splits <= 65535 && n_kv_heads <= 65535 && n_tokens <= 65535,
@@ -928,9 +959,10 @@ int run_attention_decode(bool allow_cluster, const void* q, int64_t q_row_stride
     p.k_new = p.v_new = nullptr;
     p.rope_freq = nullptr;
     if (rope != nullptr) {
-        PL_REQUIRE(rope->rotary == head_dim && rope->inv_freq != nullptr && (rope->k_new == nullptr) == (rope->v_new == nullptr),
-                   "attention_decode: the folded position encoding rotates the whole head (rotary %d, head_dim %d) and "
-                   "takes k and v together",
+        PL_REQUIRE(rope->rotary == head_dim && head_dim % 32 == 0 && rope->inv_freq != nullptr &&
+                       (rope->k_new == nullptr) == (rope->v_new == nullptr),
+                   "attention_decode: the folded position encoding rotates the whole head (rotary %d, head_dim %d), takes "
+                   "head sizes that are multiples of 32, and k and v together",
                    rope->rotary, head_dim);
         p.k_new = static_cast<const __nv_bfloat16*>(rope->k_new);
         p.v_new = static_cast<const __nv_bfloat16*>(rope->v_new);
@@ -949,10 +981,9 @@ int run_attention_decode(bool allow_cluster, const void* q, int64_t q_row_stride
     PL_REQUIRE(tile_max == nullptr || max_tiles >= static_cast<int64_t>(table_width) * page_size / kTile,
                "attention_decode: %d tiles per row of tile maxima do not cover a table of %d pages", max_tiles,
                table_width);
-    if (head_dim == 64) {
-        return launch_decode<64>(p, n_tokens, n_kv_heads, allow_cluster, stream);
-    }
-    return launch_decode<128>(p, n_tokens, n_kv_heads, allow_cluster, stream);
+#define PL_CALL(HD) launch_decode<HD>(p, n_tokens, n_kv_heads, allow_cluster, stream)
+    PL_DECODE_HEAD_SIZES(head_dim, PL_CALL, pl_fail(2, "attention_decode: head size %d", head_dim))
+#undef PL_CALL
 }
 
 }  // namespace
@@ -1004,28 +1035,9 @@ PL_API int pl_attention_decode_items(const void* q, int64_t q_row_stride, const 
 
 // How many CTAs of the decode kernel one SM holds at once.
 PL_API int pl_attention_decode_ctas_per_sm(int head_dim) {
-    int ctas = 0;
-    cudaError_t err;
-    if (head_dim == 64) {
-        constexpr int rings = kWarps * stages_of(64) * 2 * kTile * 64 * 2;
-        cudaFuncSetAttribute(attention_decode_kernel<64, kWarps, stages_of(64)>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             rings + merge_bytes(16 * 16, kClusterSplitsMax) + 1024);
-        err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, attention_decode_kernel<64, kWarps, stages_of(64)>,
-                                                            kWarps * 32, rings);
-    } else if (head_dim == 128) {
-        constexpr int rings = kWarps * stages_of(128) * 2 * kTile * 128 * 2;
-        cudaFuncSetAttribute(attention_decode_kernel<128, kWarps, stages_of(128)>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             rings + merge_bytes(16 * 32, kClusterSplitsMax) + 1024);
-        err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, attention_decode_kernel<128, kWarps, stages_of(128)>,
-                                                            kWarps * 32, rings);
-    } else {
-        return 0;
-    }
-    if (err != cudaSuccess) {
-        cudaGetLastError();
-        return 0;
-    }
-    return ctas;
+#define PL_CALL(HD) ctas_per_sm_of<HD>()
+    PL_DECODE_HEAD_SIZES(head_dim, PL_CALL, 0)
+#undef PL_CALL
 }
 
 namespace {

@@ -45,7 +45,9 @@ struct PrefillParams {
 
 template <int HD>
 __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const PrefillParams p) {
-    constexpr int kRowBytes = HD * 2;
+    // Rows in shared memory are as long as the next multiple of 64 elements, so that the swizzle
+    // (which permutes a row's first eight or sixteen chunks) stays inside the row at any head size.
+    constexpr int kRowBytes = padded_row_bytes(HD);
     constexpr int kChunks = HD / 8;
     constexpr int kTileBytes = kBN * kRowBytes;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -261,7 +263,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
 
 template <int HD>
 int launch_prefill(const PrefillParams& p, int n_tiles, int n_heads, cudaStream_t stream) {
-    constexpr int smem = kBM * HD * 2 + 2 * 2 * kBN * HD * 2;
+    constexpr int smem = kBM * padded_row_bytes(HD) + 2 * 2 * kBN * padded_row_bytes(HD);
     static bool configured = false;
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(attention_prefill_kernel<HD>,
@@ -282,7 +284,7 @@ int launch_prefill(const PrefillParams& p, int n_tiles, int n_heads, cudaStream_
 PL_API int pl_attention_prefill_tile_rows() { return kBM; }
 
 PL_API int pl_attention_prefill_supports(int head_dim, int page_size, int dtype) {
-    return dtype == PL_BF16 && (head_dim == 64 || head_dim == 128) && page_size >= 1;
+    return dtype == PL_BF16 && head_dim % 16 == 0 && head_dim >= 32 && head_dim <= 128 && page_size >= 1;
 }
 
 // bf16 only. tiles: int32 [n_tiles, 4] = {first token row, rows (1..128), position of
@@ -297,7 +299,7 @@ PL_API int pl_attention_prefill(const void* q, int64_t q_row_stride, const void*
     PL_REQUIRE(n_tiles >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
                "attention_prefill: bad sizes tiles=%d heads=%d kv_heads=%d", n_tiles, n_heads, n_kv_heads);
     PL_REQUIRE(pl_attention_prefill_supports(head_dim, page_size, PL_BF16),
-               "attention_prefill: unsupported shape head_dim=%d page=%d (takes head_dim 64 or 128)", head_dim,
+               "attention_prefill: unsupported shape head_dim=%d page=%d (takes head sizes 32 to 128 in steps of 16)", head_dim,
                page_size);
     PL_REQUIRE(n_heads <= 65535, "attention_prefill: too many heads (%d)", n_heads);
     PL_REQUIRE((reinterpret_cast<uintptr_t>(q) & 15) == 0 && q_row_stride % 8 == 0 &&
@@ -327,8 +329,13 @@ PL_API int pl_attention_prefill(const void* q, int64_t q_row_stride, const void*
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = status;
-    if (head_dim == 64) {
-        return launch_prefill<64>(p, n_tiles, n_heads, stream);
+    switch (head_dim) {
+        case 32: return launch_prefill<32>(p, n_tiles, n_heads, stream);
+        case 48: return launch_prefill<48>(p, n_tiles, n_heads, stream);
+        case 64: return launch_prefill<64>(p, n_tiles, n_heads, stream);
+        case 80: return launch_prefill<80>(p, n_tiles, n_heads, stream);
+        case 96: return launch_prefill<96>(p, n_tiles, n_heads, stream);
+        case 112: return launch_prefill<112>(p, n_tiles, n_heads, stream);
+        default: return launch_prefill<128>(p, n_tiles, n_heads, stream);
     }
-    return launch_prefill<128>(p, n_tiles, n_heads, stream);
 }

@@ -54,6 +54,10 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// Bytes of a shared-memory row that holds `head_dim` bfloat16 values: a multiple of 128,
+// so that `swizzled` never leaves the row.
+__host__ __device__ constexpr int padded_row_bytes(int head_dim) { return (head_dim + 63) / 64 * 128; }
+
 // Byte offset of 16-byte chunk `chunk` of row `row` in a swizzled tile whose rows
 // are `row_bytes` long (a multiple of 128).
 __device__ __forceinline__ int swizzled(int row, int chunk, int row_bytes) {

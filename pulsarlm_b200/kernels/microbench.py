@@ -93,7 +93,8 @@ def bench_gemm(shapes) -> None:
         print(line, flush=True)
 
 
-def bench_attention_prefill(tokens_list, n_heads, n_kv, head_dim, page, prior=0, force_splits=0) -> None:
+def bench_attention_prefill(tokens_list, n_heads, n_kv, head_dim, page, prior=0, force_splits=0,
+                            cuda_cores=False) -> None:
     """A portion of `tokens` queries that follows `prior` keys already in the cache."""
     from ..parts.attention import prefill_splits
 
@@ -125,14 +126,23 @@ def bench_attention_prefill(tokens_list, n_heads, n_kv, head_dim, page, prior=0,
             ops.attention_prefill_tcgen05(q, kp, vp, table, wide_tiles if wide else tiles, *args, None, splits,
                                           scratch, wide)
 
-        for name, kernel in ((f"tcgen05 splits={splits}", tcgen05), ("mma.sync", ops.attention_prefill)):
+        def simt(q, kp, vp, table, tiles, out, page, window, scale):
+            ops.attention_simt(q, kp, vp, table, positions, torch.zeros_like(positions), out, page, window, scale)
+
+        positions = torch.arange(prior, prior + tokens, dtype=torch.int32, device="cuda")
+        kernels = [("mma.sync", ops.attention_prefill)]
+        if head_dim in (64, 128):
+            kernels.insert(0, (f"tcgen05 splits={splits}", tcgen05))
+        if cuda_cores:
+            kernels.append(("CUDA cores", simt))
+        for name, kernel in kernels:
             us = graph_time_us(lambda: kernel(q, kp, vp, table, tiles, out, page, None, scale), reps=4)
             print(f"attention_prefill {name} tokens={tokens} prior={prior} heads={n_heads}/{n_kv} head_dim={head_dim}: {us:.1f} us, "
                   f"{flops / us / 1e6:.0f} TFLOP/s (causal flops)", flush=True)
 
 
 def bench_attention_decode(batches, contexts, n_heads, n_kv, head_dim, page, force_splits=0, shortest=0,
-                           items_per_slot=0) -> None:
+                           items_per_slot=0, cuda_cores=False) -> None:
     from ..parts import attention as attention_part
     from ..parts.attention import decode_splits
 
@@ -178,8 +188,14 @@ def bench_attention_decode(batches, contexts, n_heads, n_kv, head_dim, page, for
             us = graph_time_us(run, reps=max(10, copies))
             gb = sum(lengths) * 2 * n_kv * head_dim * 2 / 1e9
             span = f"{shortest}..{context}" if shortest else f"{context}"
+            other = ""
+            if cuda_cores:  # the kernel that takes every shape, for comparison
+                pool = pools[0]
+                simt = graph_time_us(lambda: ops.attention_simt(q, pool[:, 0], pool[:, 1], table, pos, entry, out, page,
+                                                                None, scale), reps=4)
+                other = f"; CUDA-core kernel {simt:.1f} us"
             print(f"attention_decode batch={batch} context={span} heads={n_heads}/{n_kv} head_dim={head_dim} "
-                  f"splits={splits}: {us:.1f} us, {gb / us * 1e6:.0f} GB/s", flush=True)
+                  f"splits={splits}: {us:.1f} us, {gb / us * 1e6:.0f} GB/s{other}", flush=True)
 
 
 LLAMA31_8B_SHAPE = {
@@ -338,6 +354,8 @@ def main() -> None:
                         "evenly from here up to --context (default: all at --context)")
     parser.add_argument("--items_per_slot", type=int, default=0, help="attention_decode: run the work-list form, "
                         "the keys cut into about this many items per resident CTA (the engine uses 4)")
+    parser.add_argument("--cuda_cores", action="store_true", help="attention_decode, attention_prefill: also time "
+                        "the CUDA-core kernel that takes every shape")
     parser.add_argument("--heads", type=int, default=32)
     parser.add_argument("--kv_heads", type=int, default=8)
     parser.add_argument("--head_dim", type=int, default=128)
@@ -362,10 +380,10 @@ def main() -> None:
                         args.shape)
     elif args.what == "attention_prefill":
         bench_attention_prefill(args.tokens, args.heads, args.kv_heads, args.head_dim, args.page_size, args.prior,
-                                args.splits)
+                                args.splits, args.cuda_cores)
     else:
         bench_attention_decode(args.batch, args.context or [2048, 4096], args.heads, args.kv_heads, args.head_dim,
-                               args.page_size, args.splits, args.shortest, args.items_per_slot)
+                               args.page_size, args.splits, args.shortest, args.items_per_slot, args.cuda_cores)
 
 
 if __name__ == "__main__":

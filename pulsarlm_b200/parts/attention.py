@@ -296,6 +296,8 @@ class Attention(Part):
             return False
         if rotary != self.head_dim or self.q_norm is not None or self.k_norm is not None or self.softcap:
             return False
+        if self.head_dim % 32 != 0:  # (the kernel rotates q in its fragments: pairs must not straddle one)
+            return False
         if self.cache.mass_sum is not None:
             return False
         return self._kernels(self.ctx.dtype)[0]
@@ -381,7 +383,7 @@ class Attention(Part):
             return None
         return (f"attention with head size {self.head_dim}, {self.n_heads // self.n_kv} query heads per kv head and "
                 f"pages of {self.cache.page_size} tokens runs on the CUDA-core attention kernel (the tensor-core "
-                f"kernels take head sizes 64 and 128, groups up to 16 and pages that are multiples of 16 tokens); "
+                f"kernels take head sizes 32 to 128 in steps of 16, groups up to 16 and pages that are multiples of 16 tokens); "
                 f"expect it several times slower")
 
     def measures_mass_in_captured_steps(self) -> bool:
@@ -399,6 +401,13 @@ class Attention(Part):
         wide = (self.n_heads // self.n_kv) % 2 == 1
         return ("attention", self.cache.page_size, self.head_dim, self.n_heads // self.n_kv, wide,
                 self.ctx.dtype, bool(self.softcap), self.n_kv, self.window)
+
+    def native_key(self):
+        """What `native_choice` depends on beyond `plan_key`: layers that agree in both get
+        the same answer for a step, so a caller may ask once for all of them."""
+        inv_freq, rotary = self.position.table()
+        return (self.n_heads, inv_freq is not None, int(rotary), self.q_norm is None, self.k_norm is None,
+                self.cache_from is None, self.cache is not None and self.cache.mass_sum is not None)
 
     def plan_step(self, step) -> dict:
         """The tile list of the prompt-portion kernels: int32 [tiles, 4] rows of {first

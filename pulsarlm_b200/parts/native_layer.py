@@ -181,7 +181,7 @@ def forward(block, x: torch.Tensor, delta: torch.Tensor | None, batch):
         return None
     if delta is not None and (delta.dtype != torch.bfloat16 or not delta.is_contiguous()):
         return None
-    key = ("native_layer", mixer.plan_key(), mixer.hidden, block.feed_forward.inter, mixer.scale)
+    key = ("native_layer", mixer.plan_key(), mixer.native_key(), mixer.hidden, block.feed_forward.inter, mixer.scale)
     states = batch.extras.setdefault("native_layers", {})
     state = states.get(key)
     if state is None:

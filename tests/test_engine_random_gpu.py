@@ -109,6 +109,18 @@ def test_bfloat16_generation_with_graphs_at_tensor_core_head_sizes(seed):
     decode steps): bfloat16 may flip a near-tie, so the tokens are not compared; the
     logits row each token was drawn from must match the plain implementation's row
     for the generated sequence, and the token must be that row's argmax."""
+    generation_against_plain(seed, random.Random(seed).choice([64, 128]))
+
+
+@pytest.mark.parametrize("seed,head_dim", [(3, 96), (4, 80), (5, 32), (6, 48), (7, 112), (8, 96)])
+def test_bfloat16_generation_with_graphs_at_the_other_head_sizes_of_the_mma_kernels(seed, head_dim):
+    """The same at the head sizes that only the mma.sync attention kernels take (prompt
+    portions on `attention_prefill`, single tokens on `attention_decode`, the rotation
+    folded in where the head size is a multiple of 32)."""
+    generation_against_plain(seed, head_dim)
+
+
+def generation_against_plain(seed, head_dim):
     import plain_llama as plain
     from pulsarlm_b200 import Engine, SamplingParams
     from pulsarlm_b200.engine.loading import load_model
@@ -117,7 +129,7 @@ def test_bfloat16_generation_with_graphs_at_tensor_core_head_sizes(seed):
     n_kv = rng.choice([1, 2, 4])
     cfg = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": rng.choice([1, 2]),
            "hidden_size": rng.choice([256, 384]), "num_attention_heads": n_kv * rng.choice([1, 2, 3, 4, 8]),
-           "num_key_value_heads": n_kv, "head_dim": rng.choice([64, 128]), "intermediate_size": 512,
+           "num_key_value_heads": n_kv, "head_dim": head_dim, "intermediate_size": 512,
            "vocab_size": 512, "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
            "max_position_embeddings": 8192}
     weights = tiny.random_weights(cfg, seed, torch.bfloat16)

@@ -369,7 +369,8 @@ def test_attention_simt(ops, dtype, nh, nkv, hd, page, window):
 
 
 @pytest.mark.parametrize("nh,nkv,hd,page", [(8, 2, 64, 16), (8, 1, 128, 16), (32, 8, 128, 16), (16, 1, 64, 32),
-                                            (6, 2, 128, 64), (4, 4, 64, 16)])
+                                            (6, 2, 128, 64), (4, 4, 64, 16), (6, 2, 96, 16), (5, 5, 32, 16),
+                                            (9, 3, 48, 32), (4, 1, 80, 16), (14, 2, 112, 48)])
 @pytest.mark.parametrize("splits", [1, 2, 5, 8, 12, 16, 20])
 @pytest.mark.parametrize("window", [None, 100])
 def test_attention_decode(ops, nh, nkv, hd, page, splits, window):
@@ -396,7 +397,8 @@ def test_attention_decode(ops, nh, nkv, hd, page, splits, window):
 
 
 @pytest.mark.parametrize("nh,nkv,hd,page", [(8, 2, 64, 16), (8, 1, 128, 16), (32, 8, 128, 16), (16, 1, 64, 32),
-                                            (6, 2, 128, 64), (4, 4, 64, 16)])
+                                            (6, 2, 128, 64), (4, 4, 64, 16), (6, 2, 96, 16), (9, 3, 48, 32),
+                                            (3, 1, 80, 16)])
 @pytest.mark.parametrize("target", [1, 7, 40, 500])
 @pytest.mark.parametrize("window", [None, 100])
 def test_attention_decode_over_a_work_list(ops, nh, nkv, hd, page, target, window):
@@ -439,7 +441,8 @@ def test_attention_decode_over_a_work_list(ops, nh, nkv, hd, page, target, windo
     assert int(ops.attention_decode_counters(q.device).abs().sum()) == 0
 
 
-@pytest.mark.parametrize("nh,nkv,hd,page", [(8, 2, 64, 16), (32, 8, 128, 16), (6, 6, 128, 32), (16, 1, 64, 64)])
+@pytest.mark.parametrize("nh,nkv,hd,page", [(8, 2, 64, 16), (32, 8, 128, 16), (6, 6, 128, 32), (16, 1, 64, 64),
+                                            (6, 2, 96, 16), (4, 4, 32, 32)])
 @pytest.mark.parametrize("mode", ["splits1", "splits3", "splits12", "splits20", "items"])
 @pytest.mark.parametrize("window", [None, 100])
 def test_attention_decode_with_the_rotation_and_the_cache_write_folded_in(ops, nh, nkv, hd, page, mode, window):
@@ -504,17 +507,19 @@ def test_attention_decode_with_the_rotation_and_the_cache_write_folded_in(ops, n
 
 
 def test_attention_decode_refuses_what_it_cannot_do(ops):
-    assert not ops.attention_decode_supports(80, 1, 16, torch.bfloat16)
+    assert not ops.attention_decode_supports(160, 1, 16, torch.bfloat16)
+    assert not ops.attention_decode_supports(72, 1, 16, torch.bfloat16)
+    assert not ops.attention_decode_supports(16, 1, 16, torch.bfloat16)
     assert not ops.attention_decode_supports(128, 32, 16, torch.bfloat16)
     assert not ops.attention_decode_supports(128, 4, 8, torch.bfloat16)
     assert not ops.attention_decode_supports(128, 4, 16, torch.float32)
-    q = torch.randn(1, 2, 80, device=DEV).to(torch.bfloat16)
-    kp, vp = make_pools(2, 2, 16, 80, torch.bfloat16)
+    q = torch.randn(1, 2, 160, device=DEV).to(torch.bfloat16)
+    kp, vp = make_pools(2, 2, 16, 160, torch.bfloat16)
     z = torch.zeros(1, dtype=torch.int32, device=DEV)
     with pytest.raises(ops.KernelError) as error:
         ops.attention_decode(q, kp, vp, torch.zeros(1, 1, dtype=torch.int32, device=DEV), z, z, torch.empty_like(q),
                              16, None, 1.0, 1, None)
-    assert "head_dim=80" in str(error.value)
+    assert "head_dim=160" in str(error.value)
 
 
 @pytest.mark.parametrize("kernel", ["simt_f32", "simt_bf16", "decode", "decode_items"])
@@ -626,13 +631,14 @@ def prefill_kernel(ops, name):
 
 @pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
 @pytest.mark.parametrize("nh,nkv,hd,page", [(8, 2, 64, 16), (4, 1, 128, 16), (6, 6, 64, 32), (5, 1, 128, 8),
-                                            (3, 3, 128, 64)])
+                                            (3, 3, 128, 64), (6, 2, 96, 16), (5, 5, 32, 8), (9, 3, 48, 32),
+                                            (4, 1, 80, 16), (14, 2, 112, 48)])
 @pytest.mark.parametrize("window", [None, 70])
 def test_attention_prefill(ops, kernel, nh, nkv, hd, page, window):
     dtype = torch.bfloat16
     assert ops.attention_prefill_supports(hd, page, dtype)
-    if kernel == "tcgen05" and page % 16:
-        pytest.skip("the tcgen05 kernel takes pages that are multiples of 16 tokens")
+    if kernel == "tcgen05" and (page % 16 or hd not in (64, 128)):
+        pytest.skip("the tcgen05 kernel takes head sizes 64 and 128 and pages that are multiples of 16 tokens")
     # request 0: a whole prompt of 150 from position 0; request 1: a portion of 2 at 300..301;
     # request 2: a portion of 131 starting at 77 (not aligned to anything)
     lengths = [150, 302, 208]
