@@ -35,6 +35,25 @@ __global__ void embed_kernel(const scalar_t* __restrict__ table, const int32_t* 
     }
 }
 
+// tokens[i] = ids[source[i]] where source[i] >= 0 (other rows keep what the host wrote).
+__global__ void take_tokens_kernel(int32_t* __restrict__ tokens, const int32_t* __restrict__ source,
+                                   const int32_t* __restrict__ ids, int n, int n_ids, int32_t* status) {
+    pl_grid_trigger();
+    pl_grid_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) {
+        return;
+    }
+    const int from = source[i];
+    if (from >= n_ids) {
+        if (status != nullptr) {
+            atomicOr(status, 1);  // (as a bad token id: the row keeps the host's value)
+        }
+    } else if (from >= 0) {
+        tokens[i] = ids[from];
+    }
+}
+
 // One block per output row r; source row s = rows ? rows[r] : r.
 //   v = x[s] + delta[s]   (delta optional)
 //   x[s] = v              (only when rows == nullptr)
@@ -228,6 +247,21 @@ PL_API int pl_embed(const void* table, const int32_t* tokens, float* x, int n_to
                              static_cast<const scalar_t*>(table), tokens, x, hidden, vocab, status);
     });
     PL_CHECK_LAUNCH("embed");
+    return 0;
+}
+
+// The tokens of entries that go on from a step still under way: tokens[i] = ids[source[i]]
+// for the rows with source[i] >= 0 (ids: the int32 token ids that step is drawing, n_ids of
+// them, on the device). Ordered on the stream after whatever writes ids.
+PL_API int pl_take_tokens(int32_t* tokens, const int32_t* source, const int32_t* ids, int n, int n_ids,
+                          int32_t* status, cudaStream_t stream) {
+    PL_REQUIRE(n >= 0 && n_ids >= 0 && tokens != nullptr && source != nullptr && (ids != nullptr || n_ids == 0),
+               "take_tokens: bad arguments n=%d ids=%d", n, n_ids);
+    if (n == 0) {
+        return 0;
+    }
+    pl_launch_overlapped(take_tokens_kernel, (n + 127) / 128, 128, 0, stream, tokens, source, ids, n, n_ids, status);
+    PL_CHECK_LAUNCH("take_tokens");
     return 0;
 }
 

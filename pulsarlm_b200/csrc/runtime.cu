@@ -30,7 +30,7 @@ PL_API const char* pl_last_error() { return last_error; }
 
 // Bumped when an entry point's signature changes; the Python side checks it so a
 // stale build is rebuilt instead of being called with the wrong arguments.
-PL_API int pl_abi_version() { return 20; }
+PL_API int pl_abi_version() { return 21; }
 
 // Compute capability of the current device as major * 10 + minor, or -1.
 PL_API int pl_device_arch() {

@@ -292,6 +292,7 @@ void SchedulerCore::preempt(int64_t id, std::vector<int64_t>& preempted) {
     cache_->close(id);
     running_.erase(std::find(running_.begin(), running_.end(), id));
     r.pending = r.prompt_len + r.output_len;  // everything it computed is recomputed later
+    r.unsettled = 0;                          // (a token still being drawn is dropped and drawn again)
     r.running = false;
     ++r.preemptions;
     ++preemptions_;
@@ -406,11 +407,12 @@ void SchedulerCore::plan(std::vector<PlannedEntry>& entries, std::vector<Ended>&
     entries.insert(entries.end(), others.begin(), others.end());
 }
 
-void SchedulerCore::finish_step(const PlannedEntry* entries, const int32_t* tokens, int count,
-                                std::vector<Ended>& ended) {
+// A step leaves for the device. Its prompt tokens are consumed; a request that samples in it
+// is taken to go on with the token being drawn (one pending token, not yet known to the host),
+// unless that token is certain to be its last: then nothing is planned for it until `settle`.
+void SchedulerCore::advance(const PlannedEntry* entries, int count) {
     for (int i = 0; i < count; ++i) {
-        const int64_t id = entries[i].request;
-        const auto it = requests_.find(id);
+        const auto it = requests_.find(entries[i].request);
         if (it == requests_.end() || !it->second.running) {
             continue;
         }
@@ -420,18 +422,44 @@ void SchedulerCore::finish_step(const PlannedEntry* entries, const int32_t* toke
             continue;
         }
         if (r.max_tokens == 0) {
+            r.pending = 0;
+            continue;
+        }
+        ++r.unsettled;
+        r.pending = (r.max_tokens >= 0 && r.output_len + r.unsettled >= r.max_tokens) ? 0 : 1;
+    }
+}
+
+// The tokens of a step that `advance` saw are known. The caller leaves out entries whose
+// request was preempted or ended since the step left.
+void SchedulerCore::settle(const PlannedEntry* entries, const int32_t* tokens, int count, std::vector<Ended>& ended) {
+    for (int i = 0; i < count; ++i) {
+        const int64_t id = entries[i].request;
+        const auto it = requests_.find(id);
+        if (it == requests_.end() || !it->second.running || !entries[i].samples) {
+            continue;
+        }
+        Request& r = it->second;
+        if (r.max_tokens == 0) {
             finish(id, kLength, ended);
             continue;
         }
+        if (r.unsettled > 0) {
+            --r.unsettled;
+        }
         ++r.output_len;
         if (stop_ids_.count(tokens[i]) && !r.ignore_eos) {
-            finish(id, kStop, ended);
+            finish(id, kStop, ended);  // (what a later step in flight computes for it is dropped)
         } else if (r.max_tokens >= 0 && r.output_len >= r.max_tokens) {
             finish(id, kLength, ended);
-        } else {
-            r.pending = 1;
         }
     }
+}
+
+void SchedulerCore::finish_step(const PlannedEntry* entries, const int32_t* tokens, int count,
+                                std::vector<Ended>& ended) {
+    advance(entries, count);
+    settle(entries, tokens, count, ended);
 }
 
 }  // namespace plh
@@ -444,7 +472,7 @@ using plh::CacheBook;
 using plh::PagePool;
 using plh::SchedulerCore;
 
-PLH_API int plh_abi_version() { return 4; }
+PLH_API int plh_abi_version() { return 5; }
 
 PLH_API void* plh_pool_create(int n_pages) { return new PagePool(n_pages); }
 PLH_API void plh_pool_destroy(void* pool) { delete static_cast<PagePool*>(pool); }
@@ -621,6 +649,28 @@ PLH_API int plh_sched_finish_step(void* sched, const int64_t* entries, const int
     }
     std::vector<plh::Ended> x;
     static_cast<SchedulerCore*>(sched)->finish_step(e.data(), tokens, count, x);
+    for (size_t i = 0; i < x.size() && static_cast<int>(i) < capacity; ++i) {
+        ended[2 * i] = x[i].request;
+        ended[2 * i + 1] = x[i].reason;
+    }
+    return static_cast<int>(x.size());
+}
+
+PLH_API void plh_sched_advance(void* sched, const int64_t* entries, int count) {
+    std::vector<plh::PlannedEntry> e(count);
+    for (int i = 0; i < count; ++i) {
+        e[i] = {entries[3 * i], static_cast<int>(entries[3 * i + 1]), static_cast<int>(entries[3 * i + 2])};
+    }
+    static_cast<SchedulerCore*>(sched)->advance(e.data(), count);
+}
+PLH_API int plh_sched_settle(void* sched, const int64_t* entries, const int32_t* tokens, int count, int64_t* ended,
+                             int capacity) {
+    std::vector<plh::PlannedEntry> e(count);
+    for (int i = 0; i < count; ++i) {
+        e[i] = {entries[3 * i], static_cast<int>(entries[3 * i + 1]), static_cast<int>(entries[3 * i + 2])};
+    }
+    std::vector<plh::Ended> x;
+    static_cast<SchedulerCore*>(sched)->settle(e.data(), tokens, count, x);
     for (size_t i = 0; i < x.size() && static_cast<int>(i) < capacity; ++i) {
         ended[2 * i] = x[i].request;
         ended[2 * i + 1] = x[i].reason;

@@ -125,7 +125,12 @@ public:
     // Plans a step. Entries come single-token first. `preempted` lists requests sent
     // back to the queue (the caller rebuilds their pending tokens as prompt + output).
     void plan(std::vector<PlannedEntry>& entries, std::vector<Ended>& ended, std::vector<int64_t>& preempted);
-    // Records a step: tokens[i] is the token drawn for entries[i] (ignored unless it samples).
+    // A step in two halves, so that the next one can be planned while it runs: `advance` when it
+    // leaves for the device (what it consumes is known), `settle` when its tokens are known
+    // (tokens[i] is the token drawn for entries[i], ignored unless it samples).
+    void advance(const PlannedEntry* entries, int count);
+    void settle(const PlannedEntry* entries, const int32_t* tokens, int count, std::vector<Ended>& ended);
+    // Both at once.
     void finish_step(const PlannedEntry* entries, const int32_t* tokens, int count, std::vector<Ended>& ended);
 
     std::vector<int64_t> running() const { return running_; }
@@ -134,7 +139,8 @@ public:
 private:
     struct Request {
         int prompt_len = 0;
-        int output_len = 0;
+        int output_len = 0;  // tokens drawn and known
+        int unsettled = 0;   // tokens being drawn by steps that have left and are not settled yet
         int pending = 0;
         int64_t max_tokens = -1;  // -1: no limit
         bool ignore_eos = false;

@@ -25,19 +25,38 @@ from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .loading import load_model, parse_dtype, random_model
 from .runner import ModelRunner, StepEntry
-from .scheduler import PlannedEntry, Request, Scheduler
+from .scheduler import FROM_DEVICE, PlannedEntry, Request, Scheduler
 
 DEFAULT_PAGE_SIZE = 16
 
 
 class _Flight:
-    """A decode step that was launched and whose sampled ids have not been read yet."""
+    """A step that has left for the device and whose sampled ids have not been read yet."""
 
-    def __init__(self, entries: list[PlannedEntry], ids: torch.Tensor, pending, logits=None):
+    def __init__(self, entries: list[PlannedEntry], ids: torch.Tensor | None, pending, logits=None):
         self.entries = entries
-        self.ids = ids          # int32 [entries] on the device
-        self.pending = pending  # their copy to the host
-        self.logits = logits    # with record_logits: a copy of the rows the ids were drawn from
+        self.ids = ids          # int32 on the device: the tokens drawn, in the order of the entries that sample
+        self.pending = pending  # their copy to the host (wait() gives them), or None when nothing samples
+        self.logits = logits    # with record_logits: the rows the ids were drawn from
+        samplers = [e for e in entries if e.samples]
+        self.samplers = samplers
+        self.row = {e.request.id: i for i, e in enumerate(samplers)}
+        # A request that is preempted while the step runs has nothing to record when it ends.
+        self.epochs = {e.request.id: e.request.preemptions for e in entries}
+
+
+class _PendingCopy:
+    """Token ids (and the kernels' status word behind them) on their way to the host."""
+
+    def __init__(self, host: torch.Tensor, event: torch.cuda.Event, runner):
+        self._host, self._event, self._runner = host, event, runner
+
+    def wait(self) -> list[int]:
+        self._event.synchronize()  # the step's one synchronisation
+        values = self._host.tolist()
+        if values[-1]:
+            self._runner.raise_status(values[-1])
+        return values[:-1]
 
 
 def pages_for_bytes(needs: list, page_size: int, max_requests: int, dtype: torch.dtype, step_tokens: int,
@@ -107,9 +126,11 @@ class Engine:
         stops = self.model.spec.eos_token_ids if stop_ids is None else stop_ids
         self.scheduler = Scheduler(self.cache, stops, prefill_tokens_per_step)
         self.cuda_graphs = cuda_graphs and self.runner.graphs_allowed
-        self.lookahead = lookahead and self.cuda_graphs
+        self.lookahead = lookahead
         self.record_logits = record_logits
         self._inflight: _Flight | None = None
+        self._host_ids: list[torch.Tensor] | None = None
+        self._host_turn = 0
         self._ids = itertools.count()
         self.vocab_size = self.model.spec.vocab_size
 
@@ -136,108 +157,88 @@ class Engine:
         """Advances the engine by one scheduler step on the GPU; returns the requests
         that ended.
 
-        Steps made of single decode tokens are pipelined one deep (`lookahead`): the
-        call launches the step and returns; the next call first launches the step
-        after it, whose tokens the GPU takes from the ids the earlier step is still
-        sampling, and only then reads the earlier step's ids. The host's work for a
-        step thus overlaps the GPU's, and a request's output lags its step by one
-        call. The step after is launched early only when it is certain to be the same
-        requests again (nobody waiting or cancelled, nobody at its token limit, pages
-        to spare); a request that ends on a stop token has then computed one token too
-        many, which is dropped."""
-        done: list[Request] = []
-        flight = self._inflight
-        if flight is not None:
-            self._inflight = None
-            if self._can_look_ahead(flight):
-                entries, ended = self.scheduler.plan()
-                same = not ended and len(entries) == len(flight.entries) and all(
-                    e.request is f.request and len(e.tokens) == 1 and e.samples
-                    for e, f in zip(entries, flight.entries))
-                if same:
-                    ahead = self._launch_decode(entries, device_tokens=flight.ids, count_offset=1)
-                    done = self._finish(flight)
-                    self._inflight = ahead
-                    return done
-                # (not expected under the conditions checked) finish, then run what was planned
-                done = self._finish(flight)
-                entries = [PlannedEntry(e.request, e.request.pending[: len(e.tokens)], e.samples)
-                           for e in entries if e.request.state == "running"]
-                return done + ended + self._execute(entries)
-            done = self._finish(flight)
+        With `lookahead` steps are pipelined one deep: the call launches a step and
+        returns; the next call first plans and launches the step after it, and only then
+        reads the earlier step's token ids. The host's work for a step thus overlaps the
+        GPU's, and a request's output lags its step by one call. The later step is planned
+        as if every request of the earlier one went on (unless the token being drawn is
+        certain to be its last): their tokens are taken on the device from the ids the
+        earlier step is still drawing. A request that then ends on a stop token has
+        computed one token too many, which is dropped."""
+        flight, self._inflight = self._inflight, None
         entries, ended = self.scheduler.plan()
-        return done + ended + self._execute(entries)
-
-    def _execute(self, entries: list[PlannedEntry]) -> list[Request]:
-        """Runs planned entries; returns the requests that ended (none yet when the step
-        stays in flight)."""
-        if not entries:
-            return []
-        if self.cuda_graphs and all(len(e.tokens) == 1 and e.samples and e.request.max_tokens != 0
-                                    for e in entries):
-            flight = self._launch_decode(entries)
+        launched = self._launch(entries, flight) if entries else None
+        done = self._settle(flight) if flight is not None else []
+        if launched is not None:
             if self.lookahead:
-                self._inflight = flight
-                return []
-            return self._finish(flight)
-        step_entries = [StepEntry(e.request.id, e.tokens, [len(e.tokens) - 1] if e.samples else [])
-                        for e in entries]
-        sampled: dict = {}
-        samplers = [e for e in entries if e.samples]
-        logits = self.runner.step(step_entries)
-        if samplers and logits is not None:
-            drawn = self.sampler.sample(
-                logits, [e.request.sampling for e in samplers], [e.request.seed for e in samplers],
-                [e.request.draw_count for e in samplers])
-            # the step's one synchronisation; the kernels' status word rides along
-            host = torch.cat([drawn.to(torch.int32), self.runner.status]).cpu().tolist()
-            if host[-1]:
-                self.runner.raise_status(host[-1])
-            sampled = {e.request.id: t for e, t in zip(samplers, host)}
-            return self._record(samplers, sampled, logits, entries)
-        return self.scheduler.finish_step(entries, sampled)
+                self._inflight = launched
+            else:
+                done = done + self._settle(launched)
+        return done + ended
 
-    def _record(self, samplers: list[PlannedEntry], sampled: dict, logits, entries=None) -> list[Request]:
-        """finish_step, and with record_logits the rows of the tokens that were kept."""
-        before = [len(e.request.output) for e in samplers] if self.record_logits else None
-        done = self.scheduler.finish_step(samplers if entries is None else entries, sampled)
-        if self.record_logits and logits is not None:
-            rows = logits[: len(samplers)].float().cpu()
-            for e, had, row in zip(samplers, before, rows):
+    def _launch(self, entries: list[PlannedEntry], earlier: "_Flight | None") -> "_Flight":
+        """Launches the planned entries (a captured decode step when all are single tokens
+        that sample, else an eager step), starts the copy of the drawn ids to the host
+        and tells the scheduler that the step has left."""
+        taken = None
+        if any(e.tokens == [FROM_DEVICE] for e in entries):
+            rows = [earlier.row[e.request.id] if e.tokens == [FROM_DEVICE] else -1 for e in entries]
+            taken = (earlier.ids, rows)
+        step_entries = [StepEntry(e.request.id, e.tokens if e.tokens != [FROM_DEVICE] else [0],
+                                  [len(e.tokens) - 1] if e.samples else []) for e in entries]
+        samplers = [e for e in entries if e.samples]
+        sampling = [e.request.sampling for e in samplers]
+        seeds = [e.request.seed for e in samplers]
+        counts = [e.request.draw_count for e in samplers]
+        if self.cuda_graphs and len(samplers) == len(entries) and all(
+                len(e.tokens) == 1 and e.request.max_tokens != 0 for e in entries):
+            ids = self.runner.decode_step(step_entries, sampling, seeds, counts, taken=taken)
+            graph = self.runner.last_graph
+            kept = graph.logits[: len(entries)].clone() if self.record_logits else None  # (the next replay overwrites them)
+            flight = _Flight(entries, ids, graph.read_back(), kept)
+        else:
+            logits = self.runner.step(step_entries, taken=taken)
+            ids = pending = None
+            if samplers and logits is not None:
+                ids = self.sampler.sample(logits, sampling, seeds, counts).to(torch.int32)
+                pending = self._read_back(ids)
+            flight = _Flight(entries, ids, pending, logits if self.record_logits else None)
+        self.scheduler.advance(entries)
+        return flight
+
+    def _read_back(self, ids: torch.Tensor) -> _PendingCopy:
+        """Starts the copy of an eager step's ids to the host, the kernels' status word
+        behind them. Two pinned buffers alternate: one earlier result may still be unread."""
+        n = ids.numel()
+        if self._host_ids is None or self._host_ids[0].numel() < n + 1:
+            size = max(n + 1, self.cache.max_requests + 1)
+            self._host_ids = [torch.empty(size, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+            self._host_events = [torch.cuda.Event(), torch.cuda.Event()]
+        turn, self._host_turn = self._host_turn, self._host_turn ^ 1
+        host = self._host_ids[turn][: n + 1]
+        host.copy_(torch.cat([ids, self.runner.status]), non_blocking=True)
+        self._host_events[turn].record()
+        return _PendingCopy(host, self._host_events[turn], self.runner)
+
+    def _settle(self, flight: "_Flight") -> list[Request]:
+        """Reads a launched step's ids and records them; returns the requests that ended."""
+        host = flight.pending.wait() if flight.pending is not None else []
+        sampled = {e.request.id: t for e, t in zip(flight.samplers, host)}
+        before = None
+        if self.record_logits and flight.logits is not None:
+            before = [len(e.request.output) for e in flight.samplers]
+        done = self.scheduler.settle(flight.entries, sampled, flight.epochs)
+        if before is not None:
+            rows = flight.logits[: len(flight.samplers)].float().cpu()
+            for e, had, row in zip(flight.samplers, before, rows):
                 if len(e.request.output) > had:
                     e.request.logits.append(row)
         return done
 
-    def _launch_decode(self, entries: list[PlannedEntry], device_tokens: torch.Tensor | None = None,
-                       count_offset: int = 0) -> "_Flight":
-        step_entries = [StepEntry(e.request.id, e.tokens, [0]) for e in entries]
-        ids = self.runner.decode_step(
-            step_entries, [e.request.sampling for e in entries], [e.request.seed for e in entries],
-            [e.request.draw_count + count_offset for e in entries], device_tokens=device_tokens)
-        graph = self.runner.last_graph
-        kept = graph.logits[: len(entries)].clone() if self.record_logits else None  # the next replay overwrites them
-        return _Flight(entries, ids, graph.read_back(), kept)
-
-    def _finish(self, flight: "_Flight") -> list[Request]:
-        host = flight.pending.wait()
-        return self._record(flight.entries, {e.request.id: t for e, t in zip(flight.entries, host)}, flight.logits)
-
-    def _can_look_ahead(self, flight: "_Flight") -> bool:
-        """True when the step after `flight` is certain to be its requests again."""
-        if not self.lookahead or self.scheduler.waiting or len(self.scheduler.running) != len(flight.entries):
-            return False
-        for e in flight.entries:
-            r = e.request
-            if r.cancelled or r.state != "running":
-                return False
-            if r.max_tokens is not None and len(r.output) + 1 >= r.max_tokens:
-                return False  # the step in flight brings it to its limit
-        return self.cache.free_pages() >= len(flight.entries)
-
     def sync(self) -> list[Request]:
         """Reads a step still in flight; returns the requests that ended in it."""
         flight, self._inflight = self._inflight, None
-        return self._finish(flight) if flight is not None else []
+        return self._settle(flight) if flight is not None else []
 
     # ------------------------------------------------------------------ whole runs
     def generate(self, prompts: list[list[int]], sampling=None, max_tokens: int | None = 16,

@@ -53,7 +53,8 @@ class GraphedDecode:
         self.n = n
         self.width = width
         cache = runner.cache
-        fields = [("tokens", np.int32, (n,)), ("pos", np.int32, (n,)), ("entry", np.int32, (n,)),
+        fields = [("tokens", np.int32, (n,)), ("source", np.int32, (n,)), ("pos", np.int32, (n,)),
+                  ("entry", np.int32, (n,)),
                   ("slots", np.int32, (n,)), ("want", np.int32, (n,)), ("top_k", np.int32, (n,)),
                   ("temperature", np.float32, (n,)), ("top_p", np.float32, (n,)),
                   ("seed", np.int64, (n,)), ("count", np.int64, (n,))]
@@ -112,6 +113,7 @@ class GraphedDecode:
         h = self.h
         for name in ("tokens", "pos", "top_k"):
             h[name][n_real:] = 0
+        h["source"][n_real:] = -1
         h["slots"][n_real:] = self.runner.cache.pad_slot
         h["temperature"][n_real:] = 0.0
         h["top_p"][n_real:] = 2.0
@@ -193,16 +195,15 @@ class GraphedDecode:
                 gc.enable()
         self.launches = ops.launch_count() - before
 
-    def replay(self, device_tokens: torch.Tensor | None = None, n_real: int | None = None) -> None:
-        """Copies the packed inputs and launches the graph. With `device_tokens` (int32,
-        e.g. the ids another replay sampled) the tokens of the first `n_real` entries are
-        taken from there instead of from the host buffer: the copy is ordered after
-        whatever wrote them."""
+    def replay(self, ids: torch.Tensor | None = None) -> None:
+        """Copies the packed inputs and launches the graph. With `ids` (int32 on the device,
+        the token ids an earlier step is drawing) the entries whose `source` row is not
+        negative take their token from `ids[source]` instead of from the host buffer; the
+        kernel that moves them is ordered after whatever writes `ids`."""
         self.dev.copy_(self.host, non_blocking=True)
         self.copied.record()
-        if device_tokens is not None:
-            n_real = self.n if n_real is None else n_real
-            self.d["tokens"][:n_real].copy_(device_tokens[:n_real], non_blocking=True)
+        if ids is not None:
+            ops.take_tokens(self.d["tokens"], self.d["source"], ids, self.runner.status)
         self.graph.replay()
 
     def read_back(self) -> "PendingIds":

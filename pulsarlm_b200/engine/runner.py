@@ -136,13 +136,16 @@ class ModelRunner:
         self._copy_done.record()
         return [dev[start : start + a.size].view(a.shape) for a, start in zip(arrays, starts)]
 
-    def prepare(self, entries: list[StepEntry]) -> tuple[StepBatch, list[int]]:
+    def prepare(self, entries: list[StepEntry], taken: tuple | None = None) -> tuple[StepBatch, list[int]]:
         """Reserves pages and builds the device batch; returns it with each entry's
-        new length (to commit after the forward)."""
+        new length (to commit after the forward). taken: see `step`."""
         if not entries:
             raise ValueError("a step needs at least one entry")
+        sources = list(taken[1]) if taken is not None else [-1] * len(entries)
+        if len(sources) != len(entries) or any(s >= 0 and len(e.tokens) != 1 for s, e in zip(sources, entries)):
+            raise ValueError("tokens taken from the device: one row per entry, and only for entries of one token")
         seen = set()
-        for e in entries:
+        for e, source in zip(entries, sources):
             if e.request in seen:
                 raise ValueError(f"request {e.request!r} appears twice in one step")
             seen.add(e.request)
@@ -150,7 +153,7 @@ class ModelRunner:
             if n == 0:
                 raise ValueError(f"request {e.request!r}: a step entry needs at least one token")
             if n == 1:
-                if not 0 <= int(e.tokens[0]) < self.vocab:
+                if source < 0 and not 0 <= int(e.tokens[0]) < self.vocab:
                     raise ValueError(f"request {e.request!r}: token id {e.tokens[0]} is outside [0, {self.vocab})")
             else:
                 ids = np.asarray(e.tokens)
@@ -188,7 +191,7 @@ class ModelRunner:
             e = entries[i]
             n = len(e.tokens)
             start = int(starts[i])
-            tokens[at : at + n] = e.tokens
+            tokens[at : at + n] = e.tokens if sources[i] < 0 else 0
             if n == 1:
                 pos[at] = start
             else:
@@ -237,7 +240,14 @@ class ModelRunner:
                     keep[self.cache.held_pages(e.request, g.index)] = (1.0 - decay) ** len(e.tokens)
                 keep[list(self.cache.take_fresh_pages(g.index))] = 0.0
                 arrays.append(keep.view(np.int32))
+        if taken is not None and n_decode and max(sources) >= 0:
+            # (entries of one token lead the batch: their rows are the first n_decode)
+            arrays.append(np.array([sources[i] for i in order[:n_decode]], dtype=np.int32))
+        else:
+            taken = None
         dev = self._stage(arrays)
+        if taken is not None:
+            ops.take_tokens(dev[0], dev[-1], taken[0], self.status)
         for key, name, index, is_float in staged:
             plans[key][name] = dev[index].view(torch.float32) if is_float else dev[index]
         batch = StepBatch(
@@ -261,11 +271,14 @@ class ModelRunner:
         return batch, new_lens
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+    def step(self, entries: list[StepEntry], taken: tuple | None = None) -> torch.Tensor | None:
         """Runs the entries' tokens; returns fp32 logits [wanted, vocab] on the device
-        in the order of the entries and of each entry's `want`, or None."""
+        in the order of the entries and of each entry's `want`, or None. taken: (ids,
+        rows) with `ids` an int32 device tensor (the token ids an earlier step is still
+        drawing) and `rows[i]` the row of `ids` that holds entry i's one token, or -1 for
+        an entry whose tokens are its own."""
         self._bind()
-        batch, new_lens = self.prepare(entries)
+        batch, new_lens = self.prepare(entries, taken)
         logits = self.model.forward(batch)
         if self.cache.mass_decay is not None:
             self.cache.fold_mass(batch.extras["mass_retained"])
@@ -275,14 +288,13 @@ class ModelRunner:
         return logits
 
     def decode_step(self, entries: list[StepEntry], sampling, seeds: list[int], counts: list[int],
-                    device_tokens: torch.Tensor | None = None) -> torch.Tensor:
+                    taken: tuple | None = None) -> torch.Tensor:
         """A step of single tokens, one per entry, each sampling its next token:
         replays a CUDA graph captured for this number of entries (rounded up, see
         graph_entries_bucket). Returns int32 token ids, the entries' first, in a device
         buffer that the next call overwrites
-        (`self.last_graph.read_back()` starts their copy to the host). With
-        `device_tokens` the entries' tokens are read from that device tensor (the ids
-        a step still in flight is sampling) and the entries' own tokens are ignored."""
+        (`self.last_graph.read_back()` starts their copy to the host). taken: as in
+        `step` (tokens that a step still under way is drawing)."""
         from .graphs import GraphedDecode
 
         self._bind()  # (a replay runs on the pools it was captured with; a capture needs the binding)
@@ -316,7 +328,9 @@ class ModelRunner:
         h = graph.h
         requests = [e.request for e in entries]
         for i, e in enumerate(entries):
-            h["tokens"][i] = e.tokens[0]
+            source = taken[1][i] if taken is not None else -1
+            h["tokens"][i] = e.tokens[0] if source < 0 else 0
+            h["source"][i] = source
             h["pos"][i] = new_lens[i] - 1
             p = sampling[i]
             h["temperature"][i] = p.temperature if p.draws else 0.0
@@ -338,7 +352,7 @@ class ModelRunner:
         if fresh:
             graph.capture()
             self.graph_captures += 1
-        graph.replay(device_tokens, n)
+        graph.replay(taken[0] if taken is not None and max(taken[1]) >= 0 else None)
         self.last_graph = graph
         for e, new_len in zip(entries, new_lens):
             self.cache.commit(e.request, new_len)

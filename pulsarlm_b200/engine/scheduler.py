@@ -22,7 +22,13 @@ Decisions, all deterministic:
   executor.cpp:862-870.)
 
 The scheduler only does bookkeeping against the cache manager; the caller runs
-the model on what `plan()` returns and reports sampled tokens to `finish_step()`.
+the model on what `plan()` returns and reports sampled tokens to `finish_step()`,
+or in two halves: `advance()` when the step has left for the device and `settle()`
+when its tokens have arrived. Between the two the next step can be planned: a
+request that samples in the step under way is planned with the token being drawn
+(`FROM_DEVICE` in its entry: the caller takes it from the earlier step's ids on the
+device), unless that token is certain to be its last. A request that then stops on
+a stop id has computed one token too many, which is dropped.
 The decisions are made in C++ (SchedulerCore, pulsarlm_b200/csrc_host); the class
 below keeps the Python-side Request objects and token lists in step with it.
 """
@@ -36,6 +42,9 @@ from collections import deque
 from ..cache.manager import CacheManager
 from ..host import core
 from ..sampling.params import SamplingParams
+
+
+FROM_DEVICE = -1  # in an entry's tokens: the token a step still under way is drawing for this request
 
 
 @dataclasses.dataclass
@@ -56,6 +65,7 @@ class Request:
     finish_reason: str | None = None  # stop | length | cancelled | oom
     cancelled: bool = False
     preemptions: int = 0
+    unsettled: int = 0  # tokens being drawn by steps that have left and are not settled yet
     logits: list = dataclasses.field(default_factory=list)  # filled by an engine that records logits
 
     def take(self) -> list[int]:
@@ -73,7 +83,8 @@ class Request:
 
     @property
     def draw_count(self) -> int:
-        return len(self.output)
+        """How many tokens were drawn for the request before the one to draw next."""
+        return len(self.output) + self.unsettled
 
 
 @dataclasses.dataclass
@@ -188,6 +199,7 @@ class Scheduler:
             if request in self.running:
                 self.running.remove(request)
             request.pending = list(request.prompt) + list(request.output)
+            request.unsettled = 0  # (a token still being drawn is dropped; it is drawn again later)
             request.state = "waiting"
             request.preemptions += 1
             self.waiting.appendleft(request)
@@ -207,25 +219,50 @@ class Scheduler:
         return entries, ended
 
     # ------------------------------------------------------------------ after a step
-    def finish_step(self, entries: list[PlannedEntry], sampled: dict) -> list[Request]:
-        """Records a step: `sampled[request.id]` is the token drawn for each entry
-        that samples. Returns the requests that finished."""
-        # (an entry whose request ended while its step was in flight has nothing to record)
-        entries = [e for e in entries if e.request.state == "running"]
-        n = len(entries)
-        flat = (ctypes.c_int64 * (3 * max(1, n)))()
+    def _flat(self, entries: list[PlannedEntry]):
+        flat = (ctypes.c_int64 * (3 * max(1, len(entries))))()
         for i, entry in enumerate(entries):
             flat[3 * i] = self.cache.handle(entry.request.id)
             flat[3 * i + 1] = len(entry.tokens)
             flat[3 * i + 2] = int(entry.samples)
-            token = sampled.get(entry.request.id, 0) if entry.samples else 0
-            self._tokens[i] = int(token)
+        return flat
+
+    def advance(self, entries: list[PlannedEntry]) -> None:
+        """The step has left for the device: its tokens are consumed, and a request that
+        samples in it goes on with the token being drawn (`FROM_DEVICE`) unless that token
+        is its last."""
+        self._lib.plh_sched_advance(self._core, self._flat(entries), len(entries))
+        for entry in entries:
             request = entry.request
-            if request.state != "running":
-                continue
             del request.pending[: len(entry.tokens)]
             if entry.samples and request.max_tokens != 0:
-                request.output.append(int(token))
-                request.pending = [int(token)]
-        n_ended = self._lib.plh_sched_finish_step(self._core, flat, self._tokens, n, self._ended, self._capacity)
+                request.unsettled += 1
+                last = request.max_tokens is not None and request.draw_count >= request.max_tokens
+                request.pending = [] if last else [FROM_DEVICE]
+
+    def settle(self, entries: list[PlannedEntry], sampled: dict, epochs: dict | None = None) -> list[Request]:
+        """The tokens of a step that `advance` saw: `sampled[request.id]` for each entry
+        that samples. `epochs[request.id]`: the request's `preemptions` when the step left;
+        an entry whose request was preempted or ended since has nothing to record. Returns
+        the requests that finished."""
+        entries = [e for e in entries if e.request.state == "running"
+                   and (epochs is None or epochs.get(e.request.id) == e.request.preemptions)]
+        for i, entry in enumerate(entries):
+            request = entry.request
+            token = int(sampled.get(request.id, 0)) if entry.samples else 0
+            self._tokens[i] = token
+            if entry.samples and request.max_tokens != 0:
+                request.output.append(token)
+                request.unsettled -= 1
+                if request.unsettled == 0 and request.pending == [FROM_DEVICE]:
+                    request.pending = [token]  # no later step has taken it from the device
+        n_ended = self._lib.plh_sched_settle(self._core, self._flat(entries), self._tokens, len(entries), self._ended,
+                                             self._capacity)
         return [self._end(self._ended[2 * i], core.REASONS[self._ended[2 * i + 1]]) for i in range(n_ended)]
+
+    def finish_step(self, entries: list[PlannedEntry], sampled: dict) -> list[Request]:
+        """Records a step at once: `sampled[request.id]` is the token drawn for each entry
+        that samples. Returns the requests that finished."""
+        entries = [e for e in entries if e.request.state == "running"]
+        self.advance(entries)
+        return self.settle(entries, sampled)

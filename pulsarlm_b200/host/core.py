@@ -11,7 +11,7 @@ from ..kernels import build
 _I32, _I64, _PTR = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 # return codes of csrc_host/host_core.hpp
 OK, NO_ROOM = 0, 1
@@ -58,6 +58,8 @@ _SIGNATURES = {
     "plh_sched_preemptions": ([_PTR], _I32),
     "plh_sched_plan": ([_PTR, _PTR, _PTR, _PTR, _I32, _PTR], _I32),
     "plh_sched_finish_step": ([_PTR, _PTR, _PTR, _I32, _PTR, _I32], _I32),
+    "plh_sched_advance": ([_PTR, _PTR, _I32], None),
+    "plh_sched_settle": ([_PTR, _PTR, _PTR, _I32, _PTR, _I32], _I32),
 }
 
 

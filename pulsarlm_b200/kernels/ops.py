@@ -25,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 20
+ABI_VERSION = 21
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -36,6 +36,7 @@ class KernelError(RuntimeError):
 
 _SIGNATURES = {
     "pl_embed": [_PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _PTR, _PTR],
+    "pl_take_tokens": [_PTR, _PTR, _PTR, _I32, _I32, _PTR, _PTR],
     "pl_add_rmsnorm": [_PTR, _PTR, _PTR, _I32, _PTR, _PTR, _I32, _I32, _F32, _I32, _PTR],
     "pl_swiglu": [_PTR, _PTR, _I32, _I32, _I32, _PTR],
     "pl_bf16_to_f32": [_PTR, _PTR, _I64, _PTR],
@@ -193,6 +194,17 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, status: 
     vocab, hidden = table.shape
     _call("pl_embed", _p(table), _p(tokens), _p(out), tokens.numel(), hidden, vocab, _code(table.dtype),
           _p(status), _stream())
+
+
+def take_tokens(tokens: torch.Tensor, source: torch.Tensor, ids: torch.Tensor,
+                status: torch.Tensor | None = None) -> None:
+    """tokens[i] = ids[source[i]] for the rows with source[i] >= 0 (all int32, on the
+    device): the tokens of entries that go on from a step whose ids are still being drawn."""
+    _dev(tokens, source, ids, status)
+    assert tokens.dtype == source.dtype == ids.dtype == torch.int32
+    assert tokens.is_contiguous() and source.is_contiguous() and ids.is_contiguous()
+    assert source.numel() <= tokens.numel()
+    _call("pl_take_tokens", _p(tokens), _p(source), _p(ids), source.numel(), ids.numel(), _p(status), _stream())
 
 
 def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float, out: torch.Tensor,

@@ -102,6 +102,65 @@ def test_seeded_sampling_does_not_depend_on_the_company(seed):
         assert list(request.output) == want[i], (i, params[i])
 
 
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6])
+def test_stop_tokens_under_pipelined_steps(seed):
+    """Steps pipelined one deep plan a request on as if it did not stop; one that draws a
+    stop id has then run one token too many, which must leave no trace: the same tokens
+    and reasons as an engine that reads every step's ids before it plans the next, under
+    seeded sampling, tight pages, prompt portions beside single tokens, a cancellation,
+    with and without captured steps. Everything is given back at the end."""
+    from pulsarlm_b200 import Engine, SamplingParams
+    from pulsarlm_b200.engine.loading import load_model
+
+    rng = random.Random(seed)
+    cfg, page = rng.choice([(tiny.TINY_A, tiny.PAGE_A), (tiny.TINY_B, tiny.PAGE_B)])
+    weights = tiny.random_weights(cfg, seed, torch.float32)
+    with tempfile.TemporaryDirectory() as folder:
+        model = load_model(tiny.write_model_dir(folder, cfg, weights), "float32", "cuda:0")
+    n_requests = 8
+    prompts = [tiny.random_tokens(cfg, rng.choice([1, 4, 20, 33, 70]), seed * 100 + i) for i in range(n_requests)]
+    new_tokens = [rng.choice([0, 1, 2, 9, 20]) for _ in range(n_requests)]
+    params = [SamplingParams(temperature=rng.choice([0.0, 0.9]), top_k=rng.choice([0, 20]), seed=rng.randrange(1 << 40))
+              for _ in range(n_requests)]
+    largest = max(len(p) + n for p, n in zip(prompts, new_tokens))
+    plain = Engine(model, n_pages=-(-largest // page) + 2, page_size=page, max_requests=2, stop_ids=[],
+                   cuda_graphs=False, lookahead=False)
+    free_run = [plain.generate([p], s, max_tokens=n, ignore_eos=True)[0] for p, s, n in zip(prompts, params, new_tokens)]
+    # stop ids that some requests meet on the way (not as their last token), and some never
+    stops = sorted({out[len(out) // 2] for out in free_run[::2] if len(out) >= 3})
+    assert stops
+    ignore = [rng.random() < 0.25 for _ in range(n_requests)]
+    want = []
+    for out, ignores in zip(free_run, ignore):
+        cut = next((i + 1 for i, t in enumerate(out) if t in stops), len(out)) if not ignores else len(out)
+        want.append((out[:cut], "stop" if cut < len(out) or (out and out[-1] in stops and not ignores) else "length"))
+    engine = Engine(model, n_pages=-(-largest // page) + rng.choice([0, 2, 10]), page_size=page,
+                    prefill_tokens_per_step=rng.choice([3, 16, 256]), max_requests=rng.choice([2, 4, 8]),
+                    stop_ids=stops, cuda_graphs=rng.random() < 0.6, lookahead=True)
+    waiting = list(range(n_requests))
+    requests, cancelled = {}, None
+    steps = 0
+    while waiting or any(not r.finished for r in requests.values()):
+        while waiting and rng.random() < 0.5:
+            i = waiting.pop(0)
+            requests[i] = engine.submit(prompts[i], sampling=params[i], max_tokens=new_tokens[i], ignore_eos=ignore[i])
+        if cancelled is None and steps == 7 and requests:
+            cancelled = rng.choice(list(requests))
+            requests[cancelled].cancel()
+        engine.step()
+        steps += 1
+        assert steps < 5000, "the engine makes no progress"
+    engine.sync()
+    engine.runner.check_status()
+    for i, request in requests.items():
+        if i == cancelled and request.finish_reason == "cancelled":
+            assert list(request.output) == want[i][0][: len(request.output)]
+        else:
+            assert (list(request.output), request.finish_reason) == want[i], (i, stops, free_run[i])
+    stats = engine.cache.stats()
+    assert stats["slots_used"] == 0 and all(group["used"] == 0 for group in stats["groups"])
+
+
 @pytest.mark.parametrize("seed", [1, 9, 17, 58])
 def test_bfloat16_generation_with_graphs_at_tensor_core_head_sizes(seed):
     """bfloat16, head sizes 64 and 128, one to seventeen requests with prompts of up to

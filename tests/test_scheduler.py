@@ -222,3 +222,105 @@ def test_more_requests_than_any_fixed_buffer_can_end_in_one_plan():
     entries, gone = sched.plan()
     assert not entries and len(gone) == 700 and all(r.finish_reason == "cancelled" for r in requests)
     assert not sched.has_work() and cache.free_pages() == 64 and cache.stats()["slots_used"] == 0
+
+
+# ---------------------------------------------------------------- steps planned while the one before runs
+
+def drive_pipelined(sched, stepper, limit=10000, cancel_at=None):
+    """As the engine with lookahead: plan and launch the next step, then settle the one before."""
+    from pulsarlm_b200.engine.scheduler import FROM_DEVICE
+
+    ended, flight, device = [], None, {}
+    for step in range(limit):
+        if not sched.has_work() and flight is None:
+            return ended
+        if cancel_at and step in cancel_at:
+            cancel_at[step].cancel()
+        entries, gone = sched.plan()
+        ended += gone
+        launched = None
+        if entries:
+            for e in entries:
+                if e.tokens == [FROM_DEVICE]:
+                    e.tokens = [device[e.request.id]]  # what the device holds: the id the earlier step drew
+            epochs = {e.request.id: e.request.preemptions for e in entries}
+            sampled = stepper.run(entries)
+            device.update(sampled)
+            sched.advance(entries)
+            launched = (entries, sampled, epochs)
+        if flight is not None:
+            ended += sched.settle(*flight)
+        flight = launched
+    raise AssertionError("the scheduler did not finish")
+
+
+def test_the_next_step_is_planned_while_one_runs():
+    from pulsarlm_b200.engine.scheduler import FROM_DEVICE
+
+    cache, sched, stepper = make(budget=8)
+    a = Request("a", list(range(1, 20)), max_tokens=2)   # 19 tokens: portions of 8, 8, 3
+    b = Request("b", [5, 6], max_tokens=1)
+    sched.add(a)
+    first, _ = sched.plan()
+    assert [(e.request.id, len(e.tokens), e.samples) for e in first] == [("a", 8, False)]
+    stepper.run(first)
+    sched.advance(first)
+    sched.add(b)
+    second, _ = sched.plan()  # the first step is not settled: the prompt goes on where it will stand
+    assert [(e.request.id, e.tokens, e.samples) for e in second] == [("a", list(range(9, 17)), False)]
+    assert sched.settle(first, {}) == []
+    stepper.run(second)
+    sched.advance(second)
+    third, _ = sched.plan()
+    assert [(e.request.id, len(e.tokens), e.samples) for e in third] == [("a", 3, True), ("b", 2, True)]
+    sampled = stepper.run(third)
+    sched.advance(third)
+    # a goes on with the token being drawn; b is drawing its only token and is not planned again
+    fourth, _ = sched.plan()
+    assert [(e.request.id, e.tokens, e.samples) for e in fourth] == [("a", [FROM_DEVICE], True)] and a.draw_count == 1
+    fourth[0].tokens = [sampled["a"]]
+    later = stepper.run(fourth)
+    sched.advance(fourth)
+    assert sched.plan() == ([], [])  # a's second token is its last
+    assert [r.id for r in sched.settle(third, sampled)] == ["b"] and a.output == [sampled["a"]]
+    assert [r.id for r in sched.settle(fourth, later)] == ["a"]
+    assert a.output == expected_output(a.prompt, 2) and b.output == expected_output(b.prompt, 1)
+    assert not sched.has_work() and cache.free_pages() == 64
+
+
+def test_a_stop_token_drops_what_the_step_after_computed():
+    prompt = [3, 4, 5]
+    want = expected_output(prompt, 6)
+    cache, sched, stepper = make(stop=[want[2]])
+    r = Request("r", prompt, max_tokens=6)
+    sched.add(r)
+    drive_pipelined(sched, stepper)
+    assert r.output == want[:3] and r.finish_reason == "stop"
+    assert len(stepper.fed["r"]) == len(prompt) + 3  # one token more than needed was run, and dropped
+    assert cache.free_pages() == 64 and cache.stats()["slots_used"] == 0
+
+
+def test_pipelined_steps_under_page_pressure_give_the_same_tokens():
+    import random
+
+    preemptions = 0
+    for seed in range(8):
+        rng = random.Random(seed)
+        stop = [rng.randrange(VOCAB) for _ in range(3)]
+        cache, sched, stepper = make(pages=rng.choice([8, 10, 12, 20]), page=4, slots=rng.choice([2, 4]), budget=8,
+                                     stop=stop)
+        reqs = [Request(i, [rng.randrange(VOCAB) for _ in range(rng.randrange(1, 20))],
+                        max_tokens=rng.randrange(0, 12), ignore_eos=rng.random() < 0.3) for i in range(14)]
+        for r in reqs:
+            sched.add(r)
+        cancelled = reqs[rng.randrange(len(reqs))]
+        drive_pipelined(sched, stepper, cancel_at={rng.randrange(3, 30): cancelled})
+        for r in reqs:
+            want = expected_output(r.prompt, r.max_tokens, () if r.ignore_eos else stop)
+            if r is cancelled and r.finish_reason == "cancelled":
+                assert r.output == want[: len(r.output)]
+            else:
+                assert r.output == want and r.finish_reason in ("stop", "length"), (seed, r.id)
+        assert cache.free_pages() == cache.n_pages and cache.stats()["slots_used"] == 0
+        preemptions += sched.preemptions
+    assert preemptions > 0

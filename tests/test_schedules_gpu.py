@@ -123,8 +123,8 @@ def test_a_captured_step_padded_to_its_size_serves_fewer_entries():
         assert err < TOLERANCE["bfloat16"], (i, err, where)
 
 
-@pytest.mark.parametrize("seed,preempts", [(2, True), (3, True), (5, True), (8, False)])
-def test_bfloat16_scheduler_under_page_pressure_over_the_tensor_core_kernels(seed, preempts):
+@pytest.mark.parametrize("seed", [2, 3, 5, 8])
+def test_bfloat16_scheduler_under_page_pressure_over_the_tensor_core_kernels(seed):
     """Requests arrive at random into an engine whose pages do not hold them all: bfloat16
     at head sizes 64 and 128, prompts up to 700 tokens cut into portions (the tcgen05
     prompt kernel), captured and pipelined decode steps, the newest request preempted and
@@ -160,8 +160,7 @@ def test_bfloat16_scheduler_under_page_pressure_over_the_tensor_core_kernels(see
         assert steps < 5000, "the engine makes no progress"
     engine.sync()
     engine.runner.check_status()
-    # (with seed 8 everyone happens to fit: requests only wait for pages)
-    assert (engine.scheduler.preemptions > 0) == preempts, "the pages were meant to run out"
+    assert engine.scheduler.preemptions > 0, "the pages were meant to run out"
     assert engine.runner.graph_steps > 0
     worst = 0.0
     for i, request in requests.items():
