@@ -91,7 +91,7 @@ class Engine:
         decay (see CacheManager). The tensor-core kernels measure it themselves (captured
         decode steps, and prompt portions at pages of 16 to 64 tokens); single tokens of
         eager steps and shapes those kernels do not take attend on the CUDA-core kernel.
-        lookahead: pipeline decode steps one deep (see step()). record_logits: keep, for
+        lookahead: pipeline steps one deep (see step()). record_logits: keep, for
         every generated token, the fp32 logits row it was drawn from in
         `request.logits` (host tensors; for inspection and tests, it costs a copy of
         [vocab] floats per token)."""
