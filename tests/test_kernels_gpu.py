@@ -567,6 +567,138 @@ def test_one_far_key_among_many_is_found(ops, kernel, far_key):
     assert rel(out, want) < (1e-5 if dtype == torch.float32 else 1e-2)
 
 
+def dense_attention(q, kp, vp, table_row, positions, page, scale):
+    """Attention of query t over keys 0..positions[t] of one request, gathered through
+    its block-table row in one indexing step (for histories too long for
+    `reference_attention`'s loop); float64 on the device."""
+    n = max(positions) + 1
+    index = torch.arange(n, device=q.device)
+    rows = table_row.to(q.device).long()[index // page]
+    keys, vals = kp[rows, :, index % page].double(), vp[rows, :, index % page].double()  # [n, nkv, hd]
+    group = q.shape[1] // kp.shape[1]
+    out = torch.empty(q.shape, dtype=torch.float64, device=q.device)
+    for t, p in enumerate(positions):
+        for h in range(q.shape[1]):
+            s = (keys[: p + 1, h // group] @ q[t, h].double()) * scale
+            out[t, h] = torch.softmax(s, 0) @ vals[: p + 1, h // group]
+    return out.cpu()
+
+
+@pytest.mark.parametrize("kernel", ["decode", "decode_items", "simt_bf16", "tcgen05", "mma"])
+@pytest.mark.parametrize("hd,far_key", [(128, 70_001), (64, 3), (128, 131_000)])
+def test_one_far_key_among_a_hundred_thousand(ops, kernel, hd, far_key):
+    """A history of 131,072 keys (8,192 pages): one key far back, or almost the newest,
+    takes nearly all the weight. The decode kernel with the
+    split count the part chooses for such a request (more than a cluster holds: through
+    scratch memory and the merge kernel) and over a work list; the prompt kernels for a
+    portion of 130 tokens at the history's end, split over the keys as the part chooses."""
+    from pulsarlm_b200.parts.attention import decode_splits, decode_work_items, prefill_splits
+
+    dtype = torch.bfloat16
+    nh, nkv, page, n = 4, 2, 16, 131_072
+    pages_each = n // page
+    table = scattered_tables(1, pages_each, pages_each + 5, seed=hd)
+    kp, vp = make_pools(pages_each + 5, nkv, page, hd, dtype, fill=0.3)
+    direction = torch.randn(hd, device=DEV)
+    n_q = 1 if kernel in ("decode", "decode_items", "simt_bf16") else 130
+    q = (direction[None, None, :] + 0.05 * torch.randn(n_q, nh, hd, device=DEV)).to(dtype)
+    page_id = int(table[0, far_key // page])
+    kp[page_id, :, far_key % page] = (direction * (14 if hd == 128 else 20)).to(dtype)
+    vp[page_id, :, far_key % page] = 5.0
+    positions = list(range(n - n_q, n))
+    out = torch.full_like(q, float("nan"))
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    pos_t = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    entry_t = torch.zeros(n_q, dtype=torch.int32, device=DEV)
+    if kernel == "decode":
+        splits = decode_splits(nkv, n, torch.device(DEV), hd, nh // nkv)
+        assert splits > 16
+        scratch = torch.empty(ops.attention_decode_scratch_floats(1, nh, hd, splits), device=DEV)
+        ops.attention_decode(q, kp, vp, table.to(DEV), pos_t, entry_t, out, page, None, scale, splits, scratch, status)
+    elif kernel == "decode_items":
+        items, slots = decode_work_items([n, 3000], None, 150)
+        assert int((items[:, 2] > 0).sum()) > 100
+        q2, out2 = torch.cat([q, q]), torch.full((2, nh, hd), float("nan"), device=DEV, dtype=dtype)
+        pos2 = torch.tensor([n - 1, 2999], dtype=torch.int32, device=DEV)
+        scratch = torch.empty(items.shape[0] * nh * (hd + 2), device=DEV)
+        ops.attention_decode_items(q2, kp, vp, table.to(DEV), pos2, torch.zeros(2, dtype=torch.int32, device=DEV),
+                                   out2, page, None, scale, torch.from_numpy(items).to(DEV),
+                                   torch.from_numpy(slots).to(DEV), scratch, status)
+        out = out2[:1]
+    elif kernel == "simt_bf16":
+        ops.attention_simt(q, kp, vp, table.to(DEV), pos_t, entry_t, out, page, None, scale, status)
+    elif kernel == "tcgen05":
+        tiles = make_tiles([(0, n_q, n - n_q, 0)], 128)
+        splits = prefill_splits(tiles.shape[0] * nh // 2, n, n_q, nh, hd, torch.device(DEV))
+        assert splits > 1
+        ops.attention_prefill_tcgen05(q, kp, vp, table.to(DEV), tiles, out, page, None, scale, status, splits,
+                                      split_scratch(ops, q, splits))
+    else:
+        ops.attention_prefill(q, kp, vp, table.to(DEV), make_tiles([(0, n_q, n - n_q, 0)], 128), out, page, None,
+                              scale, status)
+    want = dense_attention(q, kp, vp, table[0], positions, page, scale)
+    sees = torch.tensor([p >= far_key for p in positions])
+    assert bool((want[sees].amin(dim=(1, 2)) > 4.0).all())  # the construction works where the key is visible
+    assert int(status) == 0 and rel(out, want) < 1e-2
+
+
+@pytest.mark.parametrize("kernel", ["rope_then_decode", "decode_folded", "simt_bf16", "tcgen05", "mma"])
+def test_pages_more_than_two_to_the_31_elements_into_the_pool(ops, kernel):
+    """A pool of 70,000 pages at the 8B model's page size (4.6 GB for one layer's keys and
+    values): the request's pages lie above element 2^31 of the pool, where an offset kept
+    in 32 bits would wrap. The rotation kernel writes there, the attention kernels read."""
+    dtype = torch.bfloat16
+    nh, nkv, hd, page, n_pages, n = 32, 8, 128, 16, 70_000, 600
+    pool = torch.zeros(n_pages, 2, nkv, page, hd, device=DEV, dtype=dtype)
+    kp, vp = pool[:, 0], pool[:, 1]
+    assert kp.stride(0) * 65_600 > 2 ** 31
+    pages_each = -(-n // page)
+    g = torch.Generator().manual_seed(4)
+    table = (65_600 + torch.randperm(n_pages - 65_600, generator=g)[:pages_each]).view(1, -1).to(torch.int32)
+    rows = table[0].long().to(DEV)
+    kp[rows] = (0.3 * torch.randn(pages_each, nkv, page, hd, device=DEV)).to(dtype)
+    vp[rows] = (0.3 * torch.randn(pages_each, nkv, page, hd, device=DEV)).to(dtype)
+    scale = 1 / math.sqrt(hd)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    if kernel in ("rope_then_decode", "decode_folded"):
+        # the newest token's key and value are written by the kernels themselves
+        inv_freq = plain_llama.rope_inverse_frequency(500000.0, hd, None).to(DEV)
+        qkv = torch.randn(1, (nh + 2 * nkv) * hd, device=DEV).to(dtype)
+        q = qkv[:, : nh * hd].view(1, nh, hd)
+        k = qkv[:, nh * hd : (nh + nkv) * hd].view(1, nkv, hd)
+        v = qkv[:, (nh + nkv) * hd :].view(1, nkv, hd)
+        pos_t = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+        entry_t = torch.zeros(1, dtype=torch.int32, device=DEV)
+        out = torch.full((1, nh, hd), float("nan"), device=DEV, dtype=dtype)
+        pos64 = torch.tensor([n - 1])
+        want_k = plain_llama.rope_rotate(k.double().cpu(), pos64, inv_freq.cpu())
+        want_q = plain_llama.rope_rotate(q.double().cpu(), pos64, inv_freq.cpu())
+        if kernel == "rope_then_decode":
+            ops.rope_kv_write(q, k, v, pos_t, entry_t, table.to(DEV), kp, vp, page, inv_freq, hd, status)
+            ops.attention_decode(q, kp, vp, table.to(DEV), pos_t, entry_t, out, page, None, scale, 1, None, status)
+        else:
+            scratch = torch.empty(ops.attention_decode_scratch_floats(1, nh, hd, 3), device=DEV)
+            ops.attention_decode(q, kp, vp, table.to(DEV), pos_t, entry_t, out, page, None, scale, 3, scratch, status,
+                                 rope=(k, v, inv_freq, hd))
+        at = (int(table[0, (n - 1) // page]), slice(None), (n - 1) % page)
+        assert rel(kp[at], want_k[0]) < 1e-2 and torch.equal(vp[at], v[0])
+        want = dense_attention(want_q.to(DEV).to(dtype), kp, vp, table[0], [n - 1], page, scale)
+    else:
+        n_q = 1 if kernel == "simt_bf16" else 130
+        q = torch.randn(n_q, nh, hd, device=DEV).to(dtype)
+        out = torch.full_like(q, float("nan"))
+        positions = list(range(n - n_q, n))
+        if kernel == "simt_bf16":
+            ops.attention_simt(q, kp, vp, table.to(DEV), torch.tensor(positions, dtype=torch.int32, device=DEV),
+                               torch.zeros(n_q, dtype=torch.int32, device=DEV), out, page, None, scale, status)
+        else:
+            prefill_kernel(ops, kernel)(q, kp, vp, table.to(DEV), make_tiles([(0, n_q, n - n_q, 0)], 128), out, page,
+                                        None, scale, status)
+        want = dense_attention(q, kp, vp, table[0], positions, page, scale)
+    assert int(status) == 0 and rel(out, want) < 1e-2
+
+
 @pytest.mark.parametrize("kernel", ["simt_f32", "simt_bf16", "decode"])
 def test_window_edges(ops, kernel):
     """A loud key just inside the window must be read, the same key just outside
