@@ -24,9 +24,14 @@ class DeviceDescription:
     # What one CTA of that kernel takes in when CTAs are few (two 8 KB tiles in flight per
     # warp against the memory's answer time).
     cta_bytes_per_second: float
+    # With more than sixteen splits (no cluster: partial results through scratch) a CTA reaches this
+    # fraction of that rate (fitted: batch 1 at 131,072 keys and head size 128 takes 90 us in 22
+    # splits, 84 in 28, 87 in 37; at head size 64 57 us in 44 splits, 50 in 56).
+    scratch_cta_fraction: float
     round_seconds: float          # start and end of a round of CTAs of the decode kernel
     cluster_merge_seconds: float  # merging up to sixteen splits inside a thread-block cluster
-    merge_kernel_seconds: float   # merging more splits through scratch and a second kernel
+    merge_kernel_seconds: float   # merging more splits through scratch and a second kernel,
+    merge_split_seconds: float    # and what each split adds to that (the merge reads every split's partial row)
     # Prompt attention (tcgen05), head size 128: one key for one CTA, the fixed cost of a round
     # of CTAs, the merge launch, and the bandwidth its partial rows are written and read at.
     prefill_key_seconds: float
@@ -39,9 +44,11 @@ B200 = DeviceDescription(
     name="B200",
     stream_bytes_per_second=6.3e12,
     cta_bytes_per_second=36e9,
+    scratch_cta_fraction=0.8,
     round_seconds=2e-6,
     cluster_merge_seconds=2e-6,
     merge_kernel_seconds=5e-6,
+    merge_split_seconds=0.1e-6,
     prefill_key_seconds=17.3e-9,
     prefill_round_seconds=6e-6,
     prefill_merge_seconds=4e-6,

@@ -74,14 +74,18 @@ def _decode_splits(n_ctas: int, max_context: int, device: torch.device, head_dim
     times at batch 1 to 64 within a tenth). No split shorter than eight 16-key tiles."""
     if device not in _SM_COUNT:
         _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
-    slots = 2 * _SM_COUNT[device]
+    # what the device holds of the kernel at once: two CTAs per SM at head sizes above 64, four below
+    slots = (4 if head_dim <= 64 else 2) * _SM_COUNT[device]
     most = max(1, min(-(-max_context // 16) // 8, max(16, slots // max(1, n_ctas))))
     key_bytes = 4.0 * head_dim  # K and V of one key and kv head
 
     dev = describe_device(device)
+    # (a CTA's own rate is the bytes its warps keep in flight over the memory's answer time:
+    # measured at head size 128, half of that with rows half as long)
+    cta_rate = dev.cta_bytes_per_second * min(1.0, head_dim / 128)
 
-    def round_seconds(ctas: int, bytes_each: float) -> float:
-        return ctas * bytes_each / min(dev.stream_bytes_per_second, ctas * dev.cta_bytes_per_second) + dev.round_seconds
+    def round_seconds(ctas: int, bytes_each: float, rate: float) -> float:
+        return ctas * bytes_each / min(dev.stream_bytes_per_second, ctas * rate) + dev.round_seconds
 
     best, best_cost = 1, float("inf")
     for splits in range(most, 0, -1):  # on a tie, the finer split
@@ -93,11 +97,13 @@ def _decode_splits(n_ctas: int, max_context: int, device: torch.device, head_dim
             room = slots
         total = n_ctas * splits
         bytes_each = max_context / splits * key_bytes
-        cost = (total // room) * round_seconds(room, bytes_each)
+        rate = cta_rate * (dev.scratch_cta_fraction if splits > 16 else 1.0)
+        cost = (total // room) * round_seconds(room, bytes_each, rate)
         if total % room:
-            cost += round_seconds(total % room, bytes_each)
+            cost += round_seconds(total % room, bytes_each, rate)
         if splits > 1:
-            cost += dev.cluster_merge_seconds if splits <= 16 else dev.merge_kernel_seconds
+            cost += (dev.cluster_merge_seconds if splits <= 16
+                     else dev.merge_kernel_seconds + splits * dev.merge_split_seconds)
         if cost < best_cost:
             best, best_cost = splits, cost
     return best
