@@ -48,10 +48,11 @@ class _Layout:
 class GraphedDecode:
     """One captured decode step for `n` entries and block tables `width` wide."""
 
-    def __init__(self, runner, n: int, width: int):
+    def __init__(self, runner, n: int, width: int, variants: dict | None = None):
         self.runner = runner
         self.n = n
         self.width = width
+        self.variants = dict(variants or {})  # what the parts' plan_variant answered: see HostStep
         cache = runner.cache
         fields = [("tokens", np.int32, (n,)), ("source", np.int32, (n,)), ("pos", np.int32, (n,)),
                   ("entry", np.int32, (n,)),
@@ -102,7 +103,7 @@ class GraphedDecode:
         lens = list(context_lens) + [1] * (n - len(context_lens))  # padding rows hold one token
         return HostStep(n_entries=n, n_tokens=n, n_decode=n, query_lens=[1] * n, context_lens=lens,
                         first_rows=list(range(n)), page_size=self.runner.cache.page_size, fixed_shape=True,
-                        context_bound=self.bound)
+                        context_bound=self.bound, variants=self.variants)
 
     def pad_rows(self, n_real: int) -> None:
         """Rows past the step's `n_real` entries: token 0 at position 0 of each group's

@@ -82,6 +82,7 @@ class ModelRunner:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._staging: torch.Tensor | None = None
         self._planners = model.planners()
+        self._variant_planners = [(key, part) for key, part in self._planners if hasattr(part, "plan_variant")]
         # Captured decode steps, least recently used first; at most `max_graphs` are kept
         # (each holds its own logits [entries, vocab] and small buffers; activations come
         # from one memory pool that all captures share).
@@ -312,11 +313,18 @@ class ModelRunner:
         pages = -(-max(new_lens) // self.cache.page_size)
         width = graph_width_bucket(pages)
         n_graph = graph_entries_bucket(n)
-        key = (n_graph, width)
+        # Parts may want a capture of their own for some replays (see HostStep.variants).
+        variants = {}
+        if self._variant_planners:
+            host = HostStep(n_entries=n, n_tokens=n, n_decode=n, query_lens=[1] * n, context_lens=new_lens,
+                            first_rows=list(range(n)), page_size=self.cache.page_size, fixed_shape=True,
+                            context_bound=width * self.cache.page_size)
+            variants = {key: part.plan_variant(host) for key, part in self._variant_planners}
+        key = (n_graph, width, *sorted((repr(k), repr(v)) for k, v in variants.items() if v is not None))
         graph = self._graphs.get(key)
         fresh = graph is None
         if fresh:
-            graph = GraphedDecode(self, n_graph, width)
+            graph = GraphedDecode(self, n_graph, width, variants)
             self._graphs[key] = graph
             while len(self._graphs) > max(2, self.max_graphs):
                 # The least recently used capture goes; its buffers return to the shared

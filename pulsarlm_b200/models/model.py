@@ -63,7 +63,11 @@ class HostStep:
     planned anew before every replay: the arrays a part returns must then have shapes
     that depend only on n_entries and context_bound (the most tokens any entry of a
     replay may hold), and what it returns besides arrays is kept from the first call,
-    so it must depend on nothing else either."""
+    so it must depend on nothing else either. A part that wants different kernels for
+    different replays of one shape (say, for requests of equal and of unequal lengths)
+    answers `plan_variant(step)` with a hashable value: replays whose values differ get
+    captures of their own, and `variants[part.plan_key()]` holds the value the capture
+    at hand was made for."""
 
     n_entries: int
     n_tokens: int
@@ -74,6 +78,7 @@ class HostStep:
     page_size: int
     fixed_shape: bool = False
     context_bound: int | None = None
+    variants: dict = dataclasses.field(default_factory=dict)
 
 
 def _all_part_specs(spec: ModelSpec):

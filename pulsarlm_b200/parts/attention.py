@@ -115,6 +115,13 @@ DECODE_ITEMS_PER_SLOT = 1      # unequal requests are cut into about this many i
 DECODE_ITEMS = os.environ.get("PULSARLM_B200_DECODE_ITEMS", "1") != "0"  # (0: equal shares only, for comparison)
 FOLD_ROPE = os.environ.get("PULSARLM_B200_FOLD_ROPE", "1") != "0"  # (0: always the separate rotation kernel)
 DECODE_EVEN_ENOUGH = 1.3       # longest / mean length up to which nothing is cut
+DECODE_ITEMS_MOST_SPLITS = 3   # unequal requests walk a work list where equal shares would split in up to this many
+
+
+def _uneven(context_lens) -> bool:
+    """Whether the longest request is more than DECODE_EVEN_ENOUGH times the mean."""
+    n = len(context_lens)
+    return n > 1 and max(context_lens) * n > DECODE_EVEN_ENOUGH * sum(context_lens)
 
 
 def decode_item_ctas(device: torch.device, head_dim: int, n_kv: int) -> int:
@@ -415,6 +422,27 @@ class Attention(Part):
         return (self.n_heads, inv_freq is not None, int(rotary), self.q_norm is None, self.k_norm is None,
                 self.cache_from is None, self.cache is not None and self.cache.mass_sum is not None)
 
+    def plan_variant(self, step):
+        """For a captured step of single tokens: "work list" when the requests' lengths
+        differ and there are enough of them that equal shares would split in two or three
+        only; such replays get a capture of their own, whose decode attention walks a work
+        list (see plan_step). Else None."""
+        decode_kernel, _ = self._kernels(self.ctx.dtype)
+        if not decode_kernel or self.softcap or not DECODE_ITEMS or not step.n_decode:
+            return None
+        if self.cache.mass_sum is not None and self.cache_from is None:
+            return None
+        reach = min(step.context_bound, self.window + 16) if self.window else step.context_bound
+        splits = decode_splits(step.n_decode * self.n_kv, reach, self.ctx.device, self.head_dim,
+                               self.n_heads // self.n_kv)
+        if 1 < splits <= DECODE_ITEMS_MOST_SPLITS and _uneven(self._keys_read(step.context_lens[: step.n_decode])):
+            return "work list"
+        return None
+
+    def _keys_read(self, context_lens) -> list[int]:
+        """How many keys a single token of each request reads (its history, or the window)."""
+        return [min(c, self.window) for c in context_lens] if self.window else list(context_lens)
+
     def plan_step(self, step) -> dict:
         """The tile list of the prompt-portion kernels: int32 [tiles, 4] rows of {first
         token row, rows, position of the first row, block-table row}, the tiles that read
@@ -435,12 +463,17 @@ class Attention(Part):
             measuring = self.cache.mass_sum is not None and self.cache_from is None
             device = self.ctx.device
             reach = min(plan["max_context"], self.window + 16) if self.window else plan["max_context"]
-            # (A work list also for few requests with long, unequal histories, where equal shares
-            # would split, measured better only when the lengths really differ: batch 8 with 1,000
-            # to 60,000 keys 214 -> 169 us, but 32,768 keys each 155 -> 168 us; a captured step
-            # cannot choose per replay, so equal shares stay there.)
-            if DECODE_ITEMS and not measuring and 2 + n_decode * self.n_kv <= ops.DECODE_COUNTERS and decode_splits(
-                    n_decode * self.n_kv, reach, device, self.head_dim, self.n_heads // self.n_kv) == 1:
+            # Also for fewer requests, where equal shares would split in two or three, when their
+            # lengths differ (`_uneven`): batch 24 at head size 128 with 300 to 4,500 keys 55.6 -> 43.4
+            # us, batch 12 29.2 -> 23.6; with equal lengths the shares in a cluster are ahead (batch 20
+            # at 8,192 keys: 101 against 144 us), so a captured step is captured for either case
+            # (`plan_variant`). Few requests with long histories keep their equal shares.
+            splits = decode_splits(n_decode * self.n_kv, reach, device, self.head_dim, self.n_heads // self.n_kv)
+            listed = splits == 1
+            if 1 < splits <= DECODE_ITEMS_MOST_SPLITS:
+                listed = (step.variants.get(self.plan_key()) == "work list" if step.fixed_shape
+                          else _uneven(self._keys_read(step.context_lens[:n_decode])))
+            if DECODE_ITEMS and not measuring and 2 + n_decode * self.n_kv <= ops.DECODE_COUNTERS and listed:
                 ctas = decode_item_ctas(device, self.head_dim, self.n_kv)
                 target = DECODE_ITEMS_PER_SLOT * ctas
                 items, slots = decode_work_items(step.context_lens[:n_decode], self.window, target,

@@ -220,20 +220,26 @@ def generation_against_plain(seed, head_dim):
         assert err < TOLERANCE["bfloat16"], (err, cfg)
 
 
-@pytest.mark.parametrize("seed", [2, 7, 14, 22])
-def test_many_requests_of_unequal_lengths_through_work_lists_and_native_layers(seed):
+@pytest.mark.parametrize("seed,shape", [(2, None), (7, None), (14, None), (22, None),
+                                        (31, (128, 8, 1, 20)), (32, (64, 8, 2, 24)), (33, (128, 4, 4, 33))])
+def test_many_requests_of_unequal_lengths_through_work_lists_and_native_layers(seed, shape):
     """bfloat16 at tensor-core head sizes, 20 to 48 requests whose prompts run from 3 to
     2,600 tokens, drawn at random: prompt portions beside single tokens (a layer from one
     native call), captured decode steps with the decode kernel's work list cut by the true
     lengths and refreshed before every replay, the rotation folded into it, pipelined or
     not. The logits every generated token was drawn from, for the longest, the shortest and
-    a few other requests, against the plain implementation on the request's own prefix."""
+    a few other requests, against the plain implementation on the request's own prefix.
+    The cases with a shape (head size, kv heads, group, requests) are so many requests that
+    equal shares of their keys would split in two or three: replays with unequal lengths
+    then have captures of their own that walk a work list."""
     from harness import TOLERANCE, record_error
     from pulsarlm_b200 import Engine, SamplingParams
     from pulsarlm_b200.engine.loading import load_model
 
     rng = random.Random(seed)
     hd, nkv, group = rng.choice([64, 128]), rng.choice([1, 2, 4, 8]), rng.choice([1, 2, 4])
+    if shape is not None:
+        hd, nkv, group = shape[:3]
     cfg = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": rng.choice([1, 2]),
            "hidden_size": rng.choice([256, 384]), "num_attention_heads": nkv * group, "num_key_value_heads": nkv,
            "head_dim": hd, "intermediate_size": 512, "vocab_size": 512, "rope_theta": 500000.0,
@@ -241,14 +247,15 @@ def test_many_requests_of_unequal_lengths_through_work_lists_and_native_layers(s
     weights = tiny.random_weights(cfg, seed, torch.bfloat16)
     with tempfile.TemporaryDirectory() as folder:
         model = load_model(tiny.write_model_dir(folder, cfg, weights), "bfloat16", "cuda:0")
-    n_req = rng.choice([20, 33, 48])
+    n_req = rng.choice([20, 33, 48]) if shape is None else shape[3]
     lens = [rng.choice([3, 40, 200, 700, 1500, 2600]) + rng.randrange(0, 30) for _ in range(n_req)]
     prompts = [tiny.random_tokens(cfg, n, seed * 100 + i) for i, n in enumerate(lens)]
     new = rng.choice([3, 9, 20])
     page = rng.choice([16, 32, 64])
     engine = Engine(model, n_pages=sum(-(-(len(p) + new + 1) // page) for p in prompts) + 8, page_size=page,
-                    prefill_tokens_per_step=rng.choice([256, 512, 2048]), max_requests=64, stop_ids=[],
-                    lookahead=rng.random() < 0.7, record_logits=True)
+                    # (with a shape: every prompt in the first step, so that all decode together)
+                    prefill_tokens_per_step=rng.choice([256, 512, 2048]) if shape is None else 1 << 17,
+                    max_requests=64, stop_ids=[], lookahead=rng.random() < 0.7, record_logits=True)
     greedy = SamplingParams(temperature=0.0)
     requests = [engine.submit(p, sampling=greedy, max_tokens=new, ignore_eos=True) for p in prompts]
     while engine.has_work():
@@ -256,6 +263,8 @@ def test_many_requests_of_unequal_lengths_through_work_lists_and_native_layers(s
     engine.sync()
     engine.runner.check_status()
     assert engine.runner.graph_steps > 0
+    if shape is not None:
+        assert any(len(key) > 2 for key in engine.runner._graphs), list(engine.runner._graphs)
     order = sorted(range(n_req), key=lambda i: lens[i])
     picks = {order[0], order[-1], order[len(order) // 2]} | set(rng.sample(range(n_req), 3))
     worst = 0.0
