@@ -1,7 +1,8 @@
 """A toy mixer that plans every step on the host: it returns an array of its own from
 `plan_step`, finds it on the device in `batch.plans`, and works in eager steps, in
-captured decode steps (where the array is refreshed before every replay) and through
-the engine's pipelined decoding, without a change to the package's files."""
+captured decode steps (where the array is refreshed before every replay; replays it
+names a variant for get a capture of their own) and through the engine's pipelined
+decoding, without a change to the package's files."""
 
 import numpy as np
 import pytest
@@ -33,6 +34,7 @@ def register_toy():
         expert offsets a real part would plan."""
 
         planned = 0  # how often plan_step ran (the test reads it)
+        regimes: set = set()  # which variants of a captured step plan_step was asked for
 
         def __init__(self, spec, ctx):
             super().__init__(spec, ctx)
@@ -52,8 +54,15 @@ def register_toy():
         def plan_key(self):
             return ("toy_gain",)
 
+        def plan_variant(self, step):
+            # a capture of its own for replays in which some request is past 40 tokens (a stand-in
+            # for a part that changes kernels with the lengths)
+            return "long" if max(step.context_lens) > 40 else None
+
         def plan_step(self, step):
             type(self).planned += 1
+            if step.fixed_shape:
+                type(self).regimes.add(step.variants.get(self.plan_key()))
             gains = np.empty(step.n_tokens, dtype=np.float32)
             for e in range(step.n_entries):
                 first = step.context_lens[e] - step.query_lens[e]
@@ -138,6 +147,8 @@ def test_a_part_that_plans_its_steps_on_the_host(tmp_path):
     engine.sync()
     engine.runner.check_status()
     assert engine.runner.graph_steps >= 29 and engine.lookahead
+    # replays before and after a request passed 40 tokens ran captures of their own
+    assert toy.regimes == {None, "long"} and {len(key) for key in engine.runner._graphs} == {2, 3}
     assert toy.planned - before >= engine.runner.steps  # every step was planned, the replays too
     for request in requests:
         sequence = list(request.prompt) + list(request.output)
