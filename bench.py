@@ -211,8 +211,6 @@ def time_decode(engine, ids: list, steps: int, warmup: int, vocab: int):
         engine.runner.decode_step(entries, params, seeds, [0] * len(ids))
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    from pulsarlm_b200.kernels import ops
-
     before_steps = engine.runner.graph_steps
     start.record()
     for _ in range(steps):

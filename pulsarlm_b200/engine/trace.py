@@ -24,7 +24,6 @@ import json
 import os
 import sys
 
-import numpy as np
 
 DEFAULT_PAGE_SIZE = 16
 MAX_LIVE_REQUESTS = 16
