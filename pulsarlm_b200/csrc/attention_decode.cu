@@ -189,12 +189,20 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
 
     // The first tiles are asked for before the wait on earlier kernels: they hold keys of
     // earlier steps, which no kernel of this step writes. Only the tile with the newest
-    // key (the last of the request) is written by this step's RoPE kernel; a warp whose
-    // first tiles include it waits first.
+    // key (the last of the request) is written in this step. By another kernel (the rotation
+    // kernel, or the layer whose cache this one reads): a warp whose first tiles include it
+    // waits first. By this kernel (the rotation folded in): the warp that owns the tile asks
+    // for it like for any other and puts the token's own row into the tile in shared memory
+    // once it has landed; no round trip through global memory, no fence.
+    const bool writes_own = kFoldsRope && p.rope_freq != nullptr && p.k_new != nullptr;
+    __shared__ __align__(16) __nv_bfloat16 own_kv[2][HD];  // the token's rotated key and its value
+    bool patch = false;
     bool early = true;
+    if (!writes_own) {
 #pragma unroll
-    for (int i = 0; i < STAGES - 1; ++i) {
-        early = early && !(i < my_tiles && t0 + warp + i * WARPS == tile_end - 1);
+        for (int i = 0; i < STAGES - 1; ++i) {
+            early = early && !(i < my_tiles && t0 + warp + i * WARPS == tile_end - 1);
+        }
     }
     if (early) {
 #pragma unroll
@@ -238,7 +246,7 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
             }
         }
         // The token's own key and value: rotated and stored by the warp whose tiles end with
-        // the token's tile, before that warp asks for the tile.
+        // the token's tile (for later steps), and kept for that tile in shared memory.
         const int own_tile = tile_end - 1;
         if (p.k_new != nullptr && own_tile >= t0 && own_tile < t1 && (own_tile - t0) % WARPS == warp) {
             const int position = ctx - 1;
@@ -257,13 +265,14 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
                 for (int j = lane; j < HD / 2; j += 32) {
                     const float lo = __bfloat162float(p.k_new[from + j]);
                     const float hi = __bfloat162float(p.k_new[from + j + HD / 2]);
-                    k_out[j] = __float2bfloat16_rn(rope_lo(lo, hi, rope_cs[j], rope_sn[j]));
-                    k_out[j + HD / 2] = __float2bfloat16_rn(rope_hi(lo, hi, rope_cs[j], rope_sn[j]));
-                    v_out[j] = p.v_new[from + j];
-                    v_out[j + HD / 2] = p.v_new[from + j + HD / 2];
+                    own_kv[0][j] = k_out[j] = __float2bfloat16_rn(rope_lo(lo, hi, rope_cs[j], rope_sn[j]));
+                    own_kv[0][j + HD / 2] = k_out[j + HD / 2] =
+                        __float2bfloat16_rn(rope_hi(lo, hi, rope_cs[j], rope_sn[j]));
+                    own_kv[1][j] = v_out[j] = p.v_new[from + j];
+                    own_kv[1][j + HD / 2] = v_out[j + HD / 2] = p.v_new[from + j + HD / 2];
                 }
+                patch = true;
             }
-            __threadfence();
             __syncwarp();
         }
     }
@@ -278,6 +287,17 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
         __syncwarp();
         const unsigned char* stage = ring + (i % STAGES) * kStageBytes;
         const int key0 = (t0 + warp + i * WARPS) * kTile;
+        if (patch && i == my_tiles - 1) {
+            // the token's own tile: its row as this warp made it, over what the copy brought
+            unsigned char* tile = ring + (i % STAGES) * kStageBytes;
+            const int r = (ctx - 1) % kTile;
+            for (int c = lane; c < 2 * kChunks; c += 32) {
+                const int which = c / kChunks, ch = c % kChunks;
+                *reinterpret_cast<uint4*>(tile + which * kTileBytes + r * kRowSmem + ((ch ^ (r & 7)) * 16)) =
+                    *reinterpret_cast<const uint4*>(&own_kv[which][ch * 8]);
+            }
+            __syncwarp();
+        }
 
         float s[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
         {
