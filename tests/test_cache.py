@@ -189,3 +189,21 @@ def test_the_smaller_pool_of_a_windowed_group_never_runs_out_first(seed):
             lengths[name] = new_len
         check_invariants(m)
         assert m.groups[1].pool.high_water <= m.groups[1].pool.n_pages
+
+
+def test_a_byte_budget_is_split_among_groups_by_what_they_can_hold():
+    import torch
+
+    from pulsarlm_b200.cache.manager import cache_bytes
+    from pulsarlm_b200.engine.engine import pages_for_bytes
+
+    needs = [KVCacheNeed(2, 16), KVCacheNeed(2, 16, window=40), KVCacheNeed(2, 16), None, StateNeed((4,))]
+    for budget in (1 << 16, 1 << 20, 3 << 20):
+        n = pages_for_bytes(needs, 8, 4, torch.float32, 32, budget)
+        assert cache_bytes(needs, n, 8, 32, 4, torch.float32) <= budget < cache_bytes(needs, n + 1, 8, 32, 4, torch.float32)
+    # the windowed layer's pool stops growing at what four requests can hold: more of the budget goes to the others
+    even = (1 << 20) // (3 * 2 * 2 * 8 * 16 * 4)
+    assert pages_for_bytes(needs, 8, 4, torch.float32, 32, 1 << 20) > even
+    # a model whose groups all have windows, or that keeps no keys at all, still gets an answer
+    assert pages_for_bytes([KVCacheNeed(1, 8, window=16)], 8, 2, torch.float32, 8, 1 << 30) >= 1
+    assert pages_for_bytes([None, StateNeed((2,))], 8, 2, torch.float32, 8, 1 << 30) >= 1
