@@ -28,6 +28,11 @@ class DeviceDescription:
     # fraction of that rate (fitted: batch 1 at 131,072 keys and head size 128 takes 90 us in 22
     # splits, 84 in 28, 87 in 37; at head size 64 57 us in 44 splits, 50 in 56).
     scratch_cta_fraction: float
+    # Of the clusters of s > 4 CTAs that the occupancy query says fit at once, the fraction 1 - s x this
+    # finds room inside a step, between the CTAs of the kernels before and after (fitted in the step,
+    # 8B shape at 2,060 keys: batch 4 in 8 shares 1,750 us for 16 layers, in 6 1,657; batch 2 in 13
+    # 1,696, in 11 1,607; batch 3 in 10 1,670, in 8 1,638; batch 16 in 2 1,946, unsplit 2,039).
+    cluster_room_loss_per_cta: float
     round_seconds: float          # start and end of a round of CTAs of the decode kernel
     cluster_merge_seconds: float  # merging up to sixteen splits inside a thread-block cluster
     merge_kernel_seconds: float   # merging more splits through scratch and a second kernel,
@@ -45,6 +50,7 @@ B200 = DeviceDescription(
     stream_bytes_per_second=6.3e12,
     cta_bytes_per_second=36e9,
     scratch_cta_fraction=0.8,
+    cluster_room_loss_per_cta=0.025,
     round_seconds=2e-6,
     cluster_merge_seconds=2e-6,
     merge_kernel_seconds=5e-6,

@@ -92,7 +92,10 @@ def _decode_splits(n_ctas: int, max_context: int, device: torch.device, head_dim
         if splits == 1:
             room = slots
         elif splits <= 16:
-            room = (_cluster_room(device, head_dim, group, splits) or slots // splits) * splits
+            clusters = _cluster_room(device, head_dim, group, splits) or slots // splits
+            if splits > 4:  # (clusters of up to four CTAs all find their room inside a step, larger ones do not)
+                clusters = max(1, int(clusters * (1.0 - dev.cluster_room_loss_per_cta * splits)))
+            room = clusters * splits
         else:
             room = slots
         total = n_ctas * splits
