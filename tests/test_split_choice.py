@@ -93,3 +93,16 @@ def test_work_items_cover_every_tile_once_and_leave_even_batches_whole():
     # one long request among short ones is cut into about `target` items
     items, _ = decode_work_items([100000] + [500] * 31, None, 148)
     assert 100 <= int((items[:, 2] > 0).sum()) <= 148 + 32
+
+
+def test_unequal_lengths_are_told_from_equal_ones(part):
+    assert not part._uneven([2048] * 24) and not part._uneven([7])
+    assert not part._uneven([2000, 2100, 2200, 2500])            # the longest within 1.3 of the mean
+    assert part._uneven([300, 900, 2400, 4500]) and part._uneven([100] * 23 + [4000])
+
+
+def test_small_batches_take_clusters_that_find_room_inside_a_step(part):
+    pick = lambda n, context: part.decode_splits(n, context, DEVICE, 128, 4)  # noqa: E731
+    # (two, three and four requests of 8 kv heads: not the 13, 10 and 8 shares the occupancy query alone allows)
+    assert [pick(16, 2048), pick(24, 2048), pick(32, 2048)] == [10, 8, 6]
+    assert pick(8, 2048) == 16 and pick(128, 2048) == 2
