@@ -165,9 +165,10 @@ class Engine:
         certain to be its last): their tokens are taken on the device from the ids the
         earlier step is still drawing. A request that then ends on a stop token has
         computed one token too many, which is dropped."""
-        flight, self._inflight = self._inflight, None
+        flight = self._inflight
         entries, ended = self.scheduler.plan()
-        launched = self._launch(entries, flight) if entries else None
+        launched = self._launch(entries, flight) if entries else None  # (if this raises, `flight` stays to be read)
+        self._inflight = None
         done = self._settle(flight) if flight is not None else []
         if launched is not None:
             if self.lookahead:
