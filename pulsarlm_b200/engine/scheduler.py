@@ -214,8 +214,6 @@ class Scheduler:
                 request.state = "running"
                 self.cache.zero_states(self.cache.slot(request.id))
             entries.append(PlannedEntry(request, request.pending[:count], samples))
-        self._planned = [(self._entries[3 * i], self._entries[3 * i + 1], self._entries[3 * i + 2])
-                         for i in range(n_entries)]
         return entries, ended
 
     # ------------------------------------------------------------------ after a step
