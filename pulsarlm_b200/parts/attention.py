@@ -311,7 +311,8 @@ class Attention(Part):
         """Whether this step's position encoding and cache write go into the decode
         attention kernel: a step of single tokens that all take that kernel, a layer with a
         cache of its own, whole-head rotation, no q/k norm, no score cap, no mass measured,
-        and a launch of few, short CTAs (the keys in 2 to 8 equal shares). There the launch
+        and a launch of few, short CTAs (the keys in 2 to 8 equal shares; or a work list at
+        head sizes up to 64). There the launch
         saved counts (Llama-3.1-8B shape at batch 8: 3.350 -> 3.321 ms a step, batch 16 1.7 %;
         1B shape at batch 8 4 %); every CTA rotates q for itself, which costs more than the
         rotation kernel where CTAs are many or take several (token, kv head) pairs in turn
@@ -329,7 +330,11 @@ class Attention(Part):
             return False
         plan = batch.plans.get(self.plan_key()) or {}
         if plan.get("decode_items") is not None:
-            return False
+            # Over a work list: where an SM holds four CTAs of the kernel (head sizes up to 64) the
+            # others stream while one rotates (Llama-3.2-1B shape with 300 to 4,500 keys, 16 layers:
+            # batch 32 1,458 -> 1,404 us a step, batch 48 1,736 -> 1,644, batch 64 unchanged); with two
+            # per SM it does not pay (8B shape at batch 32 and 64: 0.2 - 0.4 % slower).
+            return self.head_dim <= 64
         max_context = plan.get("max_context") or max(batch.host_context_lens[:tokens])
         if self.window:
             max_context = min(max_context, self.window + 16)
